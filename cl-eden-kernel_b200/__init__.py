@@ -1,0 +1,280 @@
+"""ctypes binding of libenn_b200.so, the C ABI over the sm_100a quantized-operator kernels.
+
+This module is plumbing for tests, the benchmark and Python callers: every operator call goes through the
+same `extern "C"` entry points (include/enn_b200.h) that a C++ userdriver binds.  There is no CPU
+fallback: if the shared library is missing, import fails; if no CUDA device is present, creating a
+`Context` fails.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libenn_b200.so")
+
+SUCCESS, FAILURE, CUDA_FAILURE, INVALID_PARAMS = 0, 1, 2, 3
+ACT_NONE, ACT_RELU, ACT_RELU1, ACT_RELU6 = 0, 1, 2, 3
+U8, S8 = 0, 1
+W_OIHW, W_OHWI, W_IOHW = 0, 1, 2
+IMPL_DIRECT, IMPL_TCGEN05, IMPL_GEMV, IMPL_DEPTHWISE, IMPL_ELTWISE = 0, 1, 2, 3, 4
+
+
+class ConvDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "n", "h", "w", "cin", "cout", "kh", "kw", "stride_h", "stride_w", "dil_h", "dil_w",
+        "pad_t", "pad_r", "pad_b", "pad_l", "groups", "activation", "act_dtype", "weight_dtype",
+        "weight_layout", "per_channel")] + [
+        ("in_scale", C.c_float), ("in_zp", C.c_int32), ("w_scale", C.c_float), ("w_zp", C.c_int32),
+        ("bias_scale", C.c_float), ("out_scale", C.c_float), ("out_zp", C.c_int32),
+        ("out_h", C.c_int32), ("out_w", C.c_int32)]
+
+
+class FcDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("m", "k", "n", "activation", "act_dtype", "weight_dtype", "per_channel")] + [
+        ("in_scale", C.c_float), ("in_zp", C.c_int32), ("w_scale", C.c_float), ("w_zp", C.c_int32),
+        ("bias_scale", C.c_float), ("out_scale", C.c_float), ("out_zp", C.c_int32)]
+
+
+class AddDesc(C.Structure):
+    _fields_ = [("count", C.c_int64), ("activation", C.c_int32), ("act_dtype", C.c_int32),
+                ("in0_scale", C.c_float), ("in0_zp", C.c_int32), ("in1_scale", C.c_float), ("in1_zp", C.c_int32),
+                ("out_scale", C.c_float), ("out_zp", C.c_int32)]
+
+
+class PoolDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n", "h", "w", "c", "kh", "kw", "stride_h", "stride_w", "pad_t", "pad_l",
+                                          "out_h", "out_w", "activation", "act_dtype")] + [
+        ("out_scale", C.c_float), ("out_zp", C.c_int32)]
+
+
+class OpInfo(C.Structure):
+    _fields_ = [("impl", C.c_int32), ("out_n", C.c_int32), ("out_h", C.c_int32), ("out_w", C.c_int32),
+                ("out_c", C.c_int32), ("in_bytes", C.c_int64), ("out_bytes", C.c_int64), ("macs", C.c_int64),
+                ("algorithmic_bytes", C.c_int64), ("act_min", C.c_int32), ("act_max", C.c_int32),
+                ("kernel_launches", C.c_int32)]
+
+
+def conv_desc(**kw):
+    """ConvDesc with the reference's defaults (stride/dilation 1, one group, no activation, u8/u8, OHWI)."""
+    d = ConvDesc()
+    d.stride_h = d.stride_w = d.dil_h = d.dil_w = 1
+    d.groups = 1
+    d.weight_layout = W_OHWI
+    d.in_scale = d.w_scale = d.out_scale = 1.0
+    d.bias_scale = 1.0
+    for k, v in kw.items():
+        if not hasattr(d, k):
+            raise AttributeError(k)
+        setattr(d, k, v)
+    if "bias_scale" not in kw:
+        d.bias_scale = np.float32(d.in_scale) * np.float32(d.w_scale)
+    return d
+
+
+# Every symbol include/enn_b200.h declares, with its prototype: (restype, argtypes).
+_P = C.c_void_p
+PROTOTYPES = {
+    "enn_b200_context_create": (C.c_int32, [C.c_int32, C.POINTER(_P)]),
+    "enn_b200_context_destroy": (C.c_int32, [_P]),
+    "enn_b200_malloc": (C.c_int32, [_P, C.c_size_t, C.POINTER(_P)]),
+    "enn_b200_free": (C.c_int32, [_P, _P]),
+    "enn_b200_upload": (C.c_int32, [_P, _P, _P, C.c_size_t]),
+    "enn_b200_download": (C.c_int32, [_P, _P, _P, C.c_size_t]),
+    "enn_b200_stream_sync": (C.c_int32, [_P]),
+    "enn_b200_host_alloc": (C.c_int32, [C.c_size_t, C.POINTER(_P)]),
+    "enn_b200_host_free": (C.c_int32, [_P]),
+    "enn_b200_last_error": (C.c_int32, [_P, C.c_char_p, C.c_size_t]),
+    "enn_b200_stream": (_P, [_P]),
+    "enn_b200_conv2d_prepare": (C.c_int32, [_P, C.POINTER(ConvDesc), _P, _P, _P, C.POINTER(_P)]),
+    "enn_b200_depthwise_prepare": (C.c_int32, [_P, C.POINTER(ConvDesc), _P, _P, _P, C.POINTER(_P)]),
+    "enn_b200_deconv_prepare": (C.c_int32, [_P, C.POINTER(ConvDesc), _P, _P, _P, C.POINTER(_P)]),
+    "enn_b200_fc_prepare": (C.c_int32, [_P, C.POINTER(FcDesc), _P, _P, _P, C.POINTER(_P)]),
+    "enn_b200_add_prepare": (C.c_int32, [_P, C.POINTER(AddDesc), C.POINTER(_P)]),
+    "enn_b200_avgpool_prepare": (C.c_int32, [_P, C.POINTER(PoolDesc), C.POINTER(_P)]),
+    "enn_b200_op_set_impl": (C.c_int32, [_P, C.c_int32]),
+    "enn_b200_op_execute": (C.c_int32, [_P, _P, _P]),
+    "enn_b200_op_execute2": (C.c_int32, [_P, _P, _P, _P]),
+    "enn_b200_op_info": (C.c_int32, [_P, C.POINTER(OpInfo)]),
+    "enn_b200_op_release": (C.c_int32, [_P]),
+    "enn_b200_nchw_to_nhwc": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "enn_b200_nhwc_to_nchw": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "enn_b200_quantize_multiplier": (None, [C.c_double, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "enn_b200_conv_multiplier": (C.c_int32, [C.c_double, C.c_double, C.c_double, C.c_double, C.POINTER(C.c_double)]),
+    "enn_b200_activation_range": (None, [C.c_int32, C.c_int32, C.c_float, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "enn_b200_requant_host": (C.c_int32, [C.c_int32] * 6),
+    "enn_b200_version": (C.c_char_p, []),
+}
+
+
+def build(verbose=False):
+    """Compile libenn_b200.so for sm_100a in-tree (nvcc; works without a GPU)."""
+    r = subprocess.run(["make", "-C", _HERE, "-j8"], capture_output=True, text=True)
+    if verbose or r.returncode:
+        print(r.stdout[-4000:], r.stderr[-4000:])
+    if r.returncode:
+        raise RuntimeError("building libenn_b200.so failed")
+
+
+def load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: run `make -C {_HERE}` (there is no CPU fallback)")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = load()
+
+
+class EnnError(RuntimeError):
+    def __init__(self, status, msg):
+        super().__init__(f"status {status}: {msg}")
+        self.status = status
+
+
+def _np_ptr(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+class Context:
+    """One device + one in-order stream (the reference's CLRuntime command queue)."""
+
+    def __init__(self, device=0):
+        h = C.c_void_p()
+        st = lib.enn_b200_context_create(device, C.byref(h))
+        if st != SUCCESS:
+            raise EnnError(st, "enn_b200_context_create failed (no CUDA device?)")
+        self.h = h
+        self.device = device
+
+    def check(self, st):
+        if st != SUCCESS:
+            buf = C.create_string_buffer(512)
+            lib.enn_b200_last_error(self.h, buf, 512)
+            raise EnnError(st, buf.value.decode())
+
+    def malloc(self, nbytes):
+        p = C.c_void_p()
+        self.check(lib.enn_b200_malloc(self.h, nbytes, C.byref(p)))
+        return p
+
+    def free(self, p):
+        self.check(lib.enn_b200_free(self.h, p))
+
+    def upload(self, dev, arr):
+        arr = np.ascontiguousarray(arr)
+        self.check(lib.enn_b200_upload(self.h, dev, _np_ptr(arr), arr.nbytes))
+        self.sync()  # arr may be a temporary
+
+    def to_device(self, arr):
+        arr = np.ascontiguousarray(arr)
+        p = self.malloc(arr.nbytes)
+        self.upload(p, arr)
+        return p
+
+    def download(self, dev, shape, dtype=np.uint8):
+        out = np.empty(shape, dtype=dtype)
+        self.check(lib.enn_b200_download(self.h, _np_ptr(out), dev, out.nbytes))
+        return out
+
+    def sync(self):
+        self.check(lib.enn_b200_stream_sync(self.h))
+
+    @property
+    def stream(self):
+        return lib.enn_b200_stream(self.h)
+
+    def close(self):
+        if self.h:
+            lib.enn_b200_context_destroy(self.h)
+            self.h = None
+
+
+class Op:
+    """A prepared operator handle (CLConvolution / CLDepthwiseConvolution / ... after initialize())."""
+
+    def __init__(self, ctx, handle):
+        self.ctx, self.h = ctx, handle
+        self.info = OpInfo()
+        ctx.check(lib.enn_b200_op_info(handle, C.byref(self.info)))
+
+    def set_impl(self, impl):
+        self.ctx.check(lib.enn_b200_op_set_impl(self.h, impl))
+        self.ctx.check(lib.enn_b200_op_info(self.h, C.byref(self.info)))
+
+    def execute(self, in_dev, out_dev):
+        self.ctx.check(lib.enn_b200_op_execute(self.h, in_dev, out_dev))
+
+    def execute2(self, a_dev, b_dev, out_dev):
+        self.ctx.check(lib.enn_b200_op_execute2(self.h, a_dev, b_dev, out_dev))
+
+    @property
+    def out_shape(self):
+        i = self.info
+        return (i.out_n, i.out_h, i.out_w, i.out_c)
+
+    def run(self, x, x2=None):
+        """Upload host array(s), execute, download: convenience for tests."""
+        act = np.int8 if x.dtype == np.int8 else np.uint8
+        a = self.ctx.to_device(x)
+        b = self.ctx.to_device(x2) if x2 is not None else None
+        nbytes = max(1, self.info.out_bytes)
+        o = self.ctx.malloc(nbytes)
+        try:
+            if x2 is None:
+                self.execute(a, o)
+            else:
+                self.execute2(a, b, o)
+            return self.ctx.download(o, (self.info.out_bytes,), act)
+        finally:
+            self.ctx.free(a)
+            self.ctx.free(o)
+            if b is not None:
+                self.ctx.free(b)
+
+    def release(self):
+        if self.h:
+            lib.enn_b200_op_release(self.h)
+            self.h = None
+
+
+def _prepare(ctx, fn, desc, w, bias, scales):
+    h = C.c_void_p()
+    w = np.ascontiguousarray(w)
+    bias = np.ascontiguousarray(bias, dtype=np.int32)
+    sc = np.ascontiguousarray(scales, dtype=np.float32) if scales is not None else None
+    ctx.check(fn(ctx.h, C.byref(desc), _np_ptr(w), _np_ptr(bias), _np_ptr(sc), C.byref(h)))
+    return Op(ctx, h)
+
+
+def conv2d(ctx, desc, w, bias, scales=None):
+    return _prepare(ctx, lib.enn_b200_conv2d_prepare, desc, w, bias, scales)
+
+
+def depthwise(ctx, desc, w, bias, scales=None):
+    return _prepare(ctx, lib.enn_b200_depthwise_prepare, desc, w, bias, scales)
+
+
+def deconv(ctx, desc, w, bias, scales=None):
+    return _prepare(ctx, lib.enn_b200_deconv_prepare, desc, w, bias, scales)
+
+
+def fully_connected(ctx, desc, w, bias, scales=None):
+    return _prepare(ctx, lib.enn_b200_fc_prepare, desc, w, bias, scales)
+
+
+def add(ctx, desc):
+    h = C.c_void_p()
+    ctx.check(lib.enn_b200_add_prepare(ctx.h, C.byref(desc), C.byref(h)))
+    return Op(ctx, h)
+
+
+def avgpool(ctx, desc):
+    h = C.c_void_p()
+    ctx.check(lib.enn_b200_avgpool_prepare(ctx.h, C.byref(desc), C.byref(h)))
+    return Op(ctx, h)

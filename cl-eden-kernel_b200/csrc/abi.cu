@@ -1,0 +1,499 @@
+// extern "C" surface of the library: context / memory shim and operator prepare / execute / release.
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "internal.h"
+#include "quant_host.h"
+#include "requant.h"
+
+using namespace enn_b200;
+
+namespace {
+
+int32_t fail(enn_b200_context *ctx, int32_t status, const std::string &msg) {
+    if (ctx) ctx->last_error = msg;
+    return status;
+}
+
+int32_t cuda_fail(enn_b200_context *ctx, cudaError_t e, const char *what) {
+    return fail(ctx, ENN_B200_CUDA_FAILURE, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+#define ENN_CUDA(ctx, call)                                        \
+    do {                                                           \
+        cudaError_t e__ = (call);                                  \
+        if (e__ != cudaSuccess) return cuda_fail(ctx, e__, #call); \
+    } while (0)
+
+template <typename T>
+int32_t upload_vec(enn_b200_op *op, const std::vector<T> &v, T **dev) {
+    void *p = nullptr;
+    const size_t bytes = (v.size() ? v.size() : 1) * sizeof(T);
+    ENN_CUDA(op->ctx, cudaMalloc(&p, bytes));
+    op->owned.push_back(p);
+    if (!v.empty()) ENN_CUDA(op->ctx, cudaMemcpyAsync(p, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice, op->ctx->stream));
+    // The source vector is a host temporary: finish the copy before it dies.
+    ENN_CUDA(op->ctx, cudaStreamSynchronize(op->ctx->stream));
+    *dev = static_cast<T *>(p);
+    return ENN_B200_SUCCESS;
+}
+
+
+int32_t conv_out_dim(int32_t in, int32_t p0, int32_t p1, int32_t k, int32_t d, int32_t s) {
+    return (in + p0 + p1 - ((k - 1) * d + 1) + s) / s;  // CLConvolution.cpp:99-104
+}
+
+bool valid_common(const enn_b200_conv_desc *d) {
+    if (d->n < 0 || d->h <= 0 || d->w <= 0 || d->cin <= 0 || d->cout <= 0) return false;
+    if (d->kh <= 0 || d->kw <= 0 || d->stride_h <= 0 || d->stride_w <= 0) return false;
+    if (d->pad_t < 0 || d->pad_b < 0 || d->pad_l < 0 || d->pad_r < 0) return false;
+    if (d->act_dtype != ENN_B200_U8 && d->act_dtype != ENN_B200_S8) return false;
+    if (d->weight_dtype != ENN_B200_U8 && d->weight_dtype != ENN_B200_S8) return false;
+    if (d->activation < ENN_B200_ACT_NONE || d->activation > ENN_B200_ACT_RELU6) return false;
+    if (!(d->in_scale > 0.f) || !(d->out_scale > 0.f)) return false;
+    return true;
+}
+
+// Fills geometry, clamp range and the per-channel requant vectors shared by conv / depthwise / deconv / fc.
+int32_t setup_quant(enn_b200_op *op, const enn_b200_conv_desc *d, const int32_t *bias_host, const float *pc_scales) {
+    ConvGeom &g = op->g;
+    g.in_zp = d->in_zp;
+    g.w_zp = d->per_channel ? 0 : d->w_zp;  // per-channel kernels are handed weight_offset 0
+    g.out_zp = d->out_zp;
+    g.a_signed = d->act_dtype == ENN_B200_S8;
+    g.w_signed = d->weight_dtype == ENN_B200_S8;
+    activation_range(d->activation, d->act_dtype, d->out_scale, d->out_zp, &g.act_min, &g.act_max);
+    if (d->per_channel && !pc_scales) return fail(op->ctx, ENN_B200_INVALID_PARAMS, "per_channel set but per_channel_scales is null");
+    std::vector<int32_t> mult, shift;
+    if (!derive_requant(d->cout, d->per_channel != 0, d->in_scale, d->w_scale, d->bias_scale, d->out_scale, pc_scales, &mult, &shift))
+        return fail(op->ctx, ENN_B200_INVALID_PARAMS, "requantisation shift outside [-31, 30]");
+    std::vector<int32_t> bias(bias_host, bias_host + d->cout);
+    int32_t *dm = nullptr, *ds = nullptr, *db = nullptr;
+    int32_t st;
+    if ((st = upload_vec(op, mult, &dm)) || (st = upload_vec(op, shift, &ds)) || (st = upload_vec(op, bias, &db))) return st;
+    op->rq = Requant{dm, ds, db};
+    op->info.act_min = g.act_min;
+    op->info.act_max = g.act_max;
+    return ENN_B200_SUCCESS;
+}
+
+void fill_info(enn_b200_op *op, int64_t in_elems, int64_t out_elems, int64_t macs, int64_t weight_bytes, int32_t cout,
+               bool per_channel) {
+    op->info.in_bytes = in_elems;
+    op->info.out_bytes = out_elems;
+    op->info.macs = macs;
+    op->info.algorithmic_bytes = in_elems + out_elems + weight_bytes + static_cast<int64_t>(cout) * 4 * (per_channel ? 3 : 1);
+    op->info.kernel_launches = 1;
+}
+
+}  // namespace
+
+namespace enn_b200 {
+// gemm_tc.cu
+int32_t tc_plan_conv(enn_b200_op *op, const void *weights_hwio_host);
+int32_t tc_execute(enn_b200_op *op, const void *in, void *out);
+void tc_release(enn_b200_op *op);
+bool tc_available(const enn_b200_context *ctx);
+}  // namespace enn_b200
+
+extern "C" {
+
+const char *enn_b200_version(void) { return "enn_b200 0.1 (sm_100a)"; }
+
+int32_t enn_b200_context_create(int32_t device, enn_b200_context **out) {
+    if (!out) return ENN_B200_INVALID_PARAMS;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) return ENN_B200_CUDA_FAILURE;
+    if (device < 0 || device >= count) return ENN_B200_INVALID_PARAMS;
+    enn_b200_context *ctx = new (std::nothrow) enn_b200_context();
+    if (!ctx) return ENN_B200_FAILURE;
+    ctx->device = device;
+    if (cudaSetDevice(device) != cudaSuccess || cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        delete ctx;
+        return ENN_B200_CUDA_FAILURE;
+    }
+    cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device);
+    cudaDeviceGetAttribute(&ctx->cc_major, cudaDevAttrComputeCapabilityMajor, device);
+    cudaDeviceGetAttribute(&ctx->cc_minor, cudaDevAttrComputeCapabilityMinor, device);
+    cudaDriverEntryPointQueryResult qres;
+    void *fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+        ctx->encode_tiled = fn;
+    *out = ctx;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_context_destroy(enn_b200_context *ctx) {
+    if (!ctx) return ENN_B200_INVALID_PARAMS;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_malloc(enn_b200_context *ctx, size_t bytes, void **dev_ptr) {
+    if (!ctx || !dev_ptr) return ENN_B200_INVALID_PARAMS;
+    *dev_ptr = nullptr;
+    ENN_CUDA(ctx, cudaSetDevice(ctx->device));
+    ENN_CUDA(ctx, cudaMalloc(dev_ptr, bytes ? bytes : 1));
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_free(enn_b200_context *ctx, void *dev_ptr) {
+    if (!ctx) return ENN_B200_INVALID_PARAMS;
+    if (!dev_ptr) return ENN_B200_SUCCESS;
+    ENN_CUDA(ctx, cudaSetDevice(ctx->device));
+    ENN_CUDA(ctx, cudaFree(dev_ptr));
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_upload(enn_b200_context *ctx, void *dev_dst, const void *host_src, size_t bytes) {
+    if (!ctx || (bytes && (!dev_dst || !host_src))) return ENN_B200_INVALID_PARAMS;
+    if (!bytes) return ENN_B200_SUCCESS;
+    ENN_CUDA(ctx, cudaMemcpyAsync(dev_dst, host_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_download(enn_b200_context *ctx, void *host_dst, const void *dev_src, size_t bytes) {
+    if (!ctx || (bytes && (!host_dst || !dev_src))) return ENN_B200_INVALID_PARAMS;
+    if (bytes) ENN_CUDA(ctx, cudaMemcpyAsync(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    ENN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_stream_sync(enn_b200_context *ctx) {
+    if (!ctx) return ENN_B200_INVALID_PARAMS;
+    ENN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_host_alloc(size_t bytes, void **host_ptr) {
+    if (!host_ptr) return ENN_B200_INVALID_PARAMS;
+    return cudaHostAlloc(host_ptr, bytes ? bytes : 1, cudaHostAllocDefault) == cudaSuccess ? ENN_B200_SUCCESS : ENN_B200_CUDA_FAILURE;
+}
+
+int32_t enn_b200_host_free(void *host_ptr) {
+    if (!host_ptr) return ENN_B200_SUCCESS;
+    return cudaFreeHost(host_ptr) == cudaSuccess ? ENN_B200_SUCCESS : ENN_B200_CUDA_FAILURE;
+}
+
+int32_t enn_b200_last_error(enn_b200_context *ctx, char *buf, size_t buf_len) {
+    if (!buf || !buf_len) return ENN_B200_SUCCESS;
+    const std::string s = ctx ? ctx->last_error : std::string("null context");
+    std::snprintf(buf, buf_len, "%s", s.c_str());
+    return ENN_B200_SUCCESS;
+}
+
+void *enn_b200_stream(enn_b200_context *ctx) { return ctx ? static_cast<void *>(ctx->stream) : nullptr; }
+
+void enn_b200_quantize_multiplier(double real_multiplier, int32_t *quantized_multiplier, int32_t *shift) {
+    quantize_multiplier(real_multiplier, quantized_multiplier, shift);
+}
+
+int32_t enn_b200_conv_multiplier(double in_scale, double w_scale, double bias_scale, double out_scale, double *multiplier) {
+    return conv_multiplier(in_scale, w_scale, bias_scale, out_scale, multiplier) ? ENN_B200_SUCCESS : ENN_B200_FAILURE;
+}
+
+void enn_b200_activation_range(int32_t activation, int32_t act_dtype, float scale, int32_t zero_point, int32_t *act_min,
+                               int32_t *act_max) {
+    activation_range(activation, act_dtype, scale, zero_point, act_min, act_max);
+}
+
+int32_t enn_b200_requant_host(int32_t acc, int32_t mult, int32_t shift, int32_t out_zp, int32_t act_min, int32_t act_max) {
+    return enn_requant(acc, mult, shift, out_zp, act_min, act_max);
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Conv2D
+// ------------------------------------------------------------------------------------------------------
+static int32_t conv_like_prepare(enn_b200_context *ctx, const enn_b200_conv_desc *d, const void *w_host,
+                                 const int32_t *bias_host, const float *pc_scales, int kind, enn_b200_op **out) {
+    if (!ctx || !d || !w_host || !bias_host || !out) return fail(ctx, ENN_B200_INVALID_PARAMS, "null argument");
+    *out = nullptr;
+    if (!valid_common(d)) return fail(ctx, ENN_B200_INVALID_PARAMS, "bad descriptor");
+    const int32_t groups = d->groups > 0 ? d->groups : 1;
+    const int32_t dil_h = d->dil_h > 0 ? d->dil_h : 1, dil_w = d->dil_w > 0 ? d->dil_w : 1;
+    if (kind == OP_CONV && (d->cin % groups || d->cout % groups)) return fail(ctx, ENN_B200_INVALID_PARAMS, "channels not divisible by groups");
+    if (kind == OP_DEPTHWISE && d->cout != d->cin * groups) return fail(ctx, ENN_B200_INVALID_PARAMS, "depthwise cout != cin * depth_multiplier");
+    if (kind == OP_DECONV && groups != 1) return fail(ctx, ENN_B200_INVALID_PARAMS, "quantized deconvolution supports group_size 1 only");
+    if (kind == OP_DECONV && d->weight_layout == ENN_B200_W_OIHW) return fail(ctx, ENN_B200_INVALID_PARAMS, "deconvolution weights are IOHW or OHWI");
+    if (kind != OP_DECONV && d->weight_layout == ENN_B200_W_IOHW) return fail(ctx, ENN_B200_INVALID_PARAMS, "IOHW is a deconvolution layout");
+    ENN_CUDA(ctx, cudaSetDevice(ctx->device));
+
+    enn_b200_op *op = new (std::nothrow) enn_b200_op();
+    if (!op) return fail(ctx, ENN_B200_FAILURE, "out of host memory");
+    op->ctx = ctx;
+    op->kind = kind;
+    ConvGeom &g = op->g;
+    g.n = d->n; g.h = d->h; g.w = d->w; g.cin = d->cin;
+    g.cout = d->cout; g.kh = d->kh; g.kw = d->kw;
+    g.sh = d->stride_h; g.sw = d->stride_w; g.dh = dil_h; g.dw = dil_w;
+    g.pt = d->pad_t; g.pl = d->pad_l;
+    g.groups = groups;
+    g.cin_g = kind == OP_CONV ? d->cin / groups : d->cin;
+    g.cout_g = kind == OP_CONV ? d->cout / groups : d->cout;
+    if (kind == OP_DECONV) {
+        // CLDeconvolution.cpp:82-87 (explicit output size wins, as TRANSPOSE_CONV carries one)
+        g.oh = d->out_h > 0 ? d->out_h : d->h * d->stride_h + d->kh - d->stride_h - d->pad_t - d->pad_b;
+        g.ow = d->out_w > 0 ? d->out_w : d->w * d->stride_w + d->kw - d->stride_w - d->pad_l - d->pad_r;
+    } else {
+        g.oh = d->out_h > 0 ? d->out_h : conv_out_dim(d->h, d->pad_t, d->pad_b, d->kh, dil_h, d->stride_h);
+        g.ow = d->out_w > 0 ? d->out_w : conv_out_dim(d->w, d->pad_l, d->pad_r, d->kw, dil_w, d->stride_w);
+    }
+    if (g.oh <= 0 || g.ow <= 0) {
+        delete op;
+        return fail(ctx, ENN_B200_INVALID_PARAMS, "empty output");
+    }
+    int32_t st = setup_quant(op, d, bias_host, pc_scales);
+    if (st) {
+        enn_b200_op_release(op);
+        return st;
+    }
+
+    // Re-pack weights once, on the host, into [Kh][Kw][Cin/g][Cout] (conv, deconv) or [Kh][Kw][Cout]
+    // (depthwise), raw bytes.  This replaces the reference's alignQuantizedWeight_gemm / matrixTrans /
+    // convertToNCHW passes run in initialize().
+    const int32_t kh = d->kh, kw = d->kw, cout = d->cout;
+    const int32_t cig = kind == OP_DEPTHWISE ? 1 : g.cin_g;
+    std::vector<uint8_t> packed(static_cast<size_t>(kh) * kw * cig * cout);
+    const uint8_t *src = static_cast<const uint8_t *>(w_host);
+    for (int32_t oc = 0; oc < cout; ++oc) {
+        const int32_t grp = kind == OP_CONV ? oc / g.cout_g : 0, ocg = kind == OP_CONV ? oc % g.cout_g : oc;
+        for (int32_t ky = 0; ky < kh; ++ky)
+            for (int32_t kx = 0; kx < kw; ++kx)
+                for (int32_t ic = 0; ic < cig; ++ic) {
+                    int64_t si;
+                    if (kind == OP_DEPTHWISE) {
+                        si = d->weight_layout == ENN_B200_W_OHWI ? (static_cast<int64_t>(ky) * kw + kx) * cout + oc
+                                                                  : static_cast<int64_t>(oc) * kh * kw + ky * kw + kx;
+                    } else if (d->weight_layout == ENN_B200_W_OHWI) {
+                        si = ((static_cast<int64_t>(oc) * kh + ky) * kw + kx) * cig + ic;
+                    } else if (d->weight_layout == ENN_B200_W_IOHW) {
+                        si = static_cast<int64_t>(ic) * cout * kh * kw + static_cast<int64_t>(oc) * kh * kw + ky * kw + kx;
+                    } else {
+                        si = static_cast<int64_t>(grp) * cig * g.cout_g * kh * kw + static_cast<int64_t>(ocg) * cig * kh * kw +
+                             static_cast<int64_t>(ic) * kh * kw + ky * kw + kx;
+                    }
+                    packed[((static_cast<size_t>(ky) * kw + kx) * cig + ic) * cout + oc] = src[si];
+                }
+    }
+    uint8_t *wd = nullptr;
+    if ((st = upload_vec(op, packed, &wd))) {
+        enn_b200_op_release(op);
+        return st;
+    }
+    op->w_direct = wd;
+
+    const int64_t out_px = static_cast<int64_t>(g.n) * g.oh * g.ow;
+    int64_t macs;
+    if (kind == OP_DEPTHWISE)
+        macs = out_px * cout * kh * kw;
+    else if (kind == OP_DECONV)
+        macs = static_cast<int64_t>(g.n) * g.h * g.w * g.cin * cout * kh * kw;
+    else
+        macs = out_px * cout * kh * kw * g.cin_g;
+    fill_info(op, static_cast<int64_t>(g.n) * g.h * g.w * g.cin, out_px * cout, macs, static_cast<int64_t>(packed.size()), cout,
+              d->per_channel != 0);
+    op->info.out_n = g.n; op->info.out_h = g.oh; op->info.out_w = g.ow; op->info.out_c = cout;
+    op->impl = kind == OP_DEPTHWISE ? ENN_B200_IMPL_DEPTHWISE : ENN_B200_IMPL_DIRECT;
+    if (kind != OP_DEPTHWISE && tc_available(ctx)) {
+        st = tc_plan_conv(op, packed.data());
+        if (st == ENN_B200_SUCCESS && op->tc) op->impl = ENN_B200_IMPL_TCGEN05;
+        else if (st != ENN_B200_SUCCESS && st != ENN_B200_INVALID_PARAMS) {
+            enn_b200_op_release(op);
+            return st;
+        }
+    }
+    op->info.impl = op->impl;
+    *out = op;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_conv2d_prepare(enn_b200_context *ctx, const enn_b200_conv_desc *desc, const void *weights_host,
+                                const int32_t *bias_host, const float *per_channel_scales, enn_b200_op **op) {
+    return conv_like_prepare(ctx, desc, weights_host, bias_host, per_channel_scales, OP_CONV, op);
+}
+
+int32_t enn_b200_depthwise_prepare(enn_b200_context *ctx, const enn_b200_conv_desc *desc, const void *weights_host,
+                                   const int32_t *bias_host, const float *per_channel_scales, enn_b200_op **op) {
+    return conv_like_prepare(ctx, desc, weights_host, bias_host, per_channel_scales, OP_DEPTHWISE, op);
+}
+
+int32_t enn_b200_deconv_prepare(enn_b200_context *ctx, const enn_b200_conv_desc *desc, const void *weights_host,
+                                const int32_t *bias_host, const float *per_channel_scales, enn_b200_op **op) {
+    return conv_like_prepare(ctx, desc, weights_host, bias_host, per_channel_scales, OP_DECONV, op);
+}
+
+int32_t enn_b200_fc_prepare(enn_b200_context *ctx, const enn_b200_fc_desc *d, const void *weights_host,
+                            const int32_t *bias_host, const float *per_channel_scales, enn_b200_op **op) {
+    if (!d) return fail(ctx, ENN_B200_INVALID_PARAMS, "null descriptor");
+    if (d->m < 0 || d->k <= 0 || d->n <= 0) return fail(ctx, ENN_B200_INVALID_PARAMS, "bad FC shape");
+    // [M][K] x [N][K]^T is the 1x1 convolution over M "pixels" with OHWI weights.
+    enn_b200_conv_desc c;
+    std::memset(&c, 0, sizeof(c));
+    c.n = d->m; c.h = 1; c.w = 1; c.cin = d->k;
+    c.cout = d->n; c.kh = 1; c.kw = 1;
+    c.stride_h = c.stride_w = 1; c.dil_h = c.dil_w = 1;
+    c.groups = 1;
+    c.activation = d->activation; c.act_dtype = d->act_dtype; c.weight_dtype = d->weight_dtype;
+    c.weight_layout = ENN_B200_W_OHWI;
+    c.per_channel = d->per_channel;
+    c.in_scale = d->in_scale; c.in_zp = d->in_zp; c.w_scale = d->w_scale; c.w_zp = d->w_zp;
+    c.bias_scale = d->bias_scale; c.out_scale = d->out_scale; c.out_zp = d->out_zp;
+    int32_t st = conv_like_prepare(ctx, &c, weights_host, bias_host, per_channel_scales, OP_CONV, op);
+    if (st == ENN_B200_SUCCESS) (*op)->kind = OP_FC;
+    return st;
+}
+
+int32_t enn_b200_add_prepare(enn_b200_context *ctx, const enn_b200_add_desc *d, enn_b200_op **out) {
+    if (!ctx || !d || !out) return fail(ctx, ENN_B200_INVALID_PARAMS, "null argument");
+    *out = nullptr;
+    if (d->count < 0 || !(d->in0_scale > 0.f) || !(d->in1_scale > 0.f) || !(d->out_scale > 0.f))
+        return fail(ctx, ENN_B200_INVALID_PARAMS, "bad add descriptor");
+    enn_b200_op *op = new (std::nothrow) enn_b200_op();
+    if (!op) return fail(ctx, ENN_B200_FAILURE, "out of host memory");
+    op->ctx = ctx;
+    op->kind = OP_ADD;
+    op->impl = ENN_B200_IMPL_ELTWISE;
+    op->count = d->count;
+    AddParams &p = op->add;
+    // CLAddQuantized.cpp:72-88: `2 * std::max(float, float)` is a float product, widened afterwards.
+    const float twice_f = 2 * (d->in0_scale > d->in1_scale ? d->in0_scale : d->in1_scale);
+    const double twice = twice_f;
+    quantize_multiplier(d->in0_scale / twice, &p.m0, &p.s0);
+    quantize_multiplier(d->in1_scale / twice, &p.m1, &p.s1);
+    quantize_multiplier(twice / ((1 << 20) * d->out_scale), &p.mo, &p.so);
+    if (p.s0 > 0 || p.s0 < -31 || p.s1 > 0 || p.s1 < -31 || p.so > 0 || p.so < -31) {
+        delete op;
+        return fail(ctx, ENN_B200_INVALID_PARAMS, "add: a stage shift is outside [-31, 0] (undefined in the reference kernel)");
+    }
+    p.in0_off = -d->in0_zp; p.in1_off = -d->in1_zp; p.out_off = d->out_zp;
+    p.is_signed = d->act_dtype == ENN_B200_S8;
+    if (d->activation != ENN_B200_ACT_NONE) {
+        activation_range(d->activation, d->act_dtype, d->out_scale, d->out_zp, &p.act_min, &p.act_max);
+    } else {
+        p.act_min = p.is_signed ? -128 : 0;
+        p.act_max = p.is_signed ? 127 : 255;
+    }
+    op->info.impl = op->impl;
+    op->info.in_bytes = 2 * d->count; op->info.out_bytes = d->count;
+    op->info.algorithmic_bytes = 3 * d->count;
+    op->info.act_min = p.act_min; op->info.act_max = p.act_max;
+    op->info.kernel_launches = 1;
+    op->info.out_n = 1; op->info.out_h = 1; op->info.out_w = 1; op->info.out_c = static_cast<int32_t>(d->count);
+    *out = op;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_avgpool_prepare(enn_b200_context *ctx, const enn_b200_pool_desc *d, enn_b200_op **out) {
+    if (!ctx || !d || !out) return fail(ctx, ENN_B200_INVALID_PARAMS, "null argument");
+    *out = nullptr;
+    if (d->n < 0 || d->h <= 0 || d->w <= 0 || d->c <= 0 || d->kh <= 0 || d->kw <= 0 || d->stride_h <= 0 || d->stride_w <= 0 ||
+        d->out_h <= 0 || d->out_w <= 0 || d->pad_t < 0 || d->pad_l < 0 || !(d->out_scale > 0.f))
+        return fail(ctx, ENN_B200_INVALID_PARAMS, "bad pool descriptor");
+    enn_b200_op *op = new (std::nothrow) enn_b200_op();
+    if (!op) return fail(ctx, ENN_B200_FAILURE, "out of host memory");
+    op->ctx = ctx;
+    op->kind = OP_AVGPOOL;
+    op->impl = ENN_B200_IMPL_ELTWISE;
+    PoolGeom &p = op->pool;
+    p.n = d->n; p.h = d->h; p.w = d->w; p.c = d->c; p.kh = d->kh; p.kw = d->kw; p.sh = d->stride_h; p.sw = d->stride_w;
+    p.pt = d->pad_t; p.pl = d->pad_l; p.oh = d->out_h; p.ow = d->out_w;
+    p.is_signed = d->act_dtype == ENN_B200_S8;
+    activation_range(d->activation, d->act_dtype, d->out_scale, d->out_zp, &p.act_min, &p.act_max);
+    op->info.impl = op->impl;
+    op->info.in_bytes = static_cast<int64_t>(d->n) * d->h * d->w * d->c;
+    op->info.out_bytes = static_cast<int64_t>(d->n) * d->out_h * d->out_w * d->c;
+    op->info.algorithmic_bytes = op->info.in_bytes + op->info.out_bytes;
+    op->info.act_min = p.act_min; op->info.act_max = p.act_max;
+    op->info.kernel_launches = 1;
+    op->info.out_n = d->n; op->info.out_h = d->out_h; op->info.out_w = d->out_w; op->info.out_c = d->c;
+    *out = op;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_op_set_impl(enn_b200_op *op, int32_t impl) {
+    if (!op) return ENN_B200_INVALID_PARAMS;
+    if (op->kind == OP_CONV || op->kind == OP_FC || op->kind == OP_DECONV) {
+        if (impl == ENN_B200_IMPL_DIRECT) {
+            op->impl = impl;
+        } else if (impl == ENN_B200_IMPL_TCGEN05 && op->tc) {
+            op->impl = impl;
+        } else {
+            return fail(op->ctx, ENN_B200_INVALID_PARAMS, "kernel family not available for this op");
+        }
+        op->info.impl = op->impl;
+        return ENN_B200_SUCCESS;
+    }
+    return impl == op->impl ? ENN_B200_SUCCESS : fail(op->ctx, ENN_B200_INVALID_PARAMS, "op has a single kernel family");
+}
+
+int32_t enn_b200_op_execute(enn_b200_op *op, const void *in, void *out) {
+    if (!op) return ENN_B200_INVALID_PARAMS;
+    enn_b200_context *ctx = op->ctx;
+    if (!in || !out) return fail(ctx, ENN_B200_INVALID_PARAMS, "null device pointer");
+    cudaError_t e = cudaSuccess;
+    switch (op->kind) {
+        case OP_CONV:
+        case OP_FC:
+            if (op->impl == ENN_B200_IMPL_TCGEN05) return tc_execute(op, in, out);
+            e = launch_conv_direct(op->g, op->rq, in, op->w_direct, out, ctx->stream);
+            break;
+        case OP_DECONV:
+            if (op->impl == ENN_B200_IMPL_TCGEN05) return tc_execute(op, in, out);
+            e = launch_deconv_direct(op->g, op->rq, in, op->w_direct, out, ctx->stream);
+            break;
+        case OP_DEPTHWISE:
+            e = launch_depthwise(op->g, op->rq, in, op->w_direct, out, ctx->sm_count, ctx->stream);
+            break;
+        case OP_AVGPOOL:
+            e = launch_avgpool(op->pool, in, out, ctx->stream);
+            break;
+        default:
+            return fail(ctx, ENN_B200_INVALID_PARAMS, "op needs enn_b200_op_execute2");
+    }
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "kernel launch");
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_op_execute2(enn_b200_op *op, const void *in0, const void *in1, void *out) {
+    if (!op) return ENN_B200_INVALID_PARAMS;
+    if (op->kind != OP_ADD) return fail(op->ctx, ENN_B200_INVALID_PARAMS, "not a two-input op");
+    if (!in0 || !in1 || !out) return fail(op->ctx, ENN_B200_INVALID_PARAMS, "null device pointer");
+    cudaError_t e = launch_add(op->add, op->count, in0, in1, out, op->ctx->sm_count, op->ctx->stream);
+    if (e != cudaSuccess) return cuda_fail(op->ctx, e, "add launch");
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_op_info(const enn_b200_op *op, enn_b200_op_info_t *info) {
+    if (!op || !info) return ENN_B200_INVALID_PARAMS;
+    *info = op->info;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_op_release(enn_b200_op *op) {
+    if (!op) return ENN_B200_INVALID_PARAMS;
+    if (op->ctx) cudaSetDevice(op->ctx->device);
+    if (op->tc) tc_release(op);
+    for (void *p : op->owned) cudaFree(p);
+    delete op;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_nchw_to_nhwc(enn_b200_context *ctx, const void *src, void *dst, int32_t n, int32_t c, int32_t h, int32_t w) {
+    if (!ctx || !src || !dst || n < 0 || c <= 0 || h <= 0 || w <= 0) return fail(ctx, ENN_B200_INVALID_PARAMS, "bad transpose arguments");
+    cudaError_t e = launch_transpose_nchw_nhwc(src, dst, n, c, h, w, true, ctx->stream);
+    return e == cudaSuccess ? ENN_B200_SUCCESS : cuda_fail(ctx, e, "transpose launch");
+}
+
+int32_t enn_b200_nhwc_to_nchw(enn_b200_context *ctx, const void *src, void *dst, int32_t n, int32_t c, int32_t h, int32_t w) {
+    if (!ctx || !src || !dst || n < 0 || c <= 0 || h <= 0 || w <= 0) return fail(ctx, ENN_B200_INVALID_PARAMS, "bad transpose arguments");
+    cudaError_t e = launch_transpose_nchw_nhwc(src, dst, n, c, h, w, false, ctx->stream);
+    return e == cudaSuccess ? ENN_B200_SUCCESS : cuda_fail(ctx, e, "transpose launch");
+}
+
+}  // extern "C"

@@ -1,0 +1,87 @@
+// Internal structures shared by the C-ABI translation units.  Not part of the public interface.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/enn_b200.h"
+
+struct enn_b200_context {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    std::string last_error;
+    void *encode_tiled = nullptr;   // cuTensorMapEncodeTiled, resolved through the runtime
+};
+
+namespace enn_b200 {
+
+enum OpKind { OP_CONV = 0, OP_DEPTHWISE = 1, OP_DECONV = 2, OP_FC = 3, OP_ADD = 4, OP_AVGPOOL = 5 };
+
+// Geometry + quantisation handed to kernels by value.
+struct ConvGeom {
+    int32_t n, h, w, cin;
+    int32_t cout, kh, kw;
+    int32_t sh, sw, dh, dw;
+    int32_t pt, pl;
+    int32_t oh, ow;
+    int32_t groups, cin_g, cout_g;   // depthwise: groups = depth multiplier
+    int32_t in_zp, w_zp, out_zp;
+    int32_t act_min, act_max;
+    int32_t a_signed, w_signed;
+};
+
+struct Requant {
+    const int32_t *mult;    // [cout] Q0.31 multipliers
+    const int32_t *shift;   // [cout] signed exponents (>0 left, <=0 right)
+    const int32_t *bias;    // [cout]
+};
+
+struct AddParams {
+    int32_t in0_off, in1_off, out_off;
+    int32_t m0, s0, m1, s1, mo, so;   // multipliers and (non-positive) shifts
+    int32_t act_min, act_max;
+    int32_t is_signed;
+};
+
+struct PoolGeom {
+    int32_t n, h, w, c, kh, kw, sh, sw, pt, pl, oh, ow;
+    int32_t act_min, act_max, is_signed;
+};
+
+}  // namespace enn_b200
+
+struct enn_b200_op {
+    enn_b200_context *ctx = nullptr;
+    int kind = 0;
+    int impl = 0;
+    enn_b200::ConvGeom g{};
+    enn_b200::Requant rq{};
+    enn_b200::AddParams add{};
+    enn_b200::PoolGeom pool{};
+    int64_t count = 0;                 // add: element count
+    void *w_direct = nullptr;          // weights in the direct kernels' layout
+    std::vector<void *> owned;         // device allocations released with the op
+    enn_b200_op_info_t info{};
+    void *tc = nullptr;                // tensor-core plan (gemm_tc.cu), owned
+};
+
+namespace enn_b200 {
+
+// kernels_direct.cu
+cudaError_t launch_conv_direct(const ConvGeom &g, const Requant &rq, const void *in, const void *w, void *out,
+                               cudaStream_t s);
+cudaError_t launch_deconv_direct(const ConvGeom &g, const Requant &rq, const void *in, const void *w, void *out,
+                                 cudaStream_t s);
+cudaError_t launch_depthwise(const ConvGeom &g, const Requant &rq, const void *in, const void *w, void *out,
+                             int sm_count, cudaStream_t s);
+cudaError_t launch_add(const AddParams &p, int64_t count, const void *a, const void *b, void *out, int sm_count,
+                       cudaStream_t s);
+cudaError_t launch_avgpool(const PoolGeom &p, const void *in, void *out, cudaStream_t s);
+cudaError_t launch_transpose_nchw_nhwc(const void *src, void *dst, int n, int c, int h, int w, bool to_nhwc,
+                                       cudaStream_t s);
+
+}  // namespace enn_b200

@@ -1,0 +1,205 @@
+/*
+ * enn_b200.h - C ABI of the B200 (sm_100a) quantized-operator library that stands in for the
+ * OpenCL operator path of the ENN GPU userdriver (reference project: src/userdriver/gpu).
+ *
+ * Every entry point is extern "C", takes plain pointers / sizes / POD descriptors, and returns an
+ * int32_t status that mirrors the reference's `enum class Status`
+ * (src/userdriver/common/operator_interfaces/common/Common.hpp:113-119).
+ *
+ * Lifecycle mirrors the reference operator interface
+ *   initialize(inputs, outputs, parameters)  ->  enn_b200_<op>_prepare(ctx, desc, weights, bias, ..., &op)
+ *   execute()                                ->  enn_b200_op_execute(op, in_dev, out_dev)   (enqueue only, no host sync)
+ *   release()                                ->  enn_b200_op_release(op)
+ * and the reference runtime shim (CLRuntime / CLTensor / CLBuffer) becomes
+ *   enn_b200_context_create / _malloc / _upload / _download / _stream_sync.
+ *
+ * Activation tensors are NHWC, channel innermost.  All arithmetic is integer and reproduces the
+ * reference's fixed-point requantisation bit for bit.
+ */
+#ifndef ENN_B200_H_
+#define ENN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes: same values as enn::ud::Status (Common.hpp:113-119); CL_FAILURE becomes CUDA_FAILURE. */
+enum {
+    ENN_B200_SUCCESS = 0,
+    ENN_B200_FAILURE = 1,
+    ENN_B200_CUDA_FAILURE = 2,
+    ENN_B200_INVALID_PARAMS = 3
+};
+
+/* ActivationInfo::ActivationType (common/ActivationInfo.hpp:5-12); only the quantized clamps exist here. */
+enum { ENN_B200_ACT_NONE = 0, ENN_B200_ACT_RELU = 1, ENN_B200_ACT_RELU1 = 2, ENN_B200_ACT_RELU6 = 3 };
+
+/* Element types of activations / weights (PrecisionType::UINT8 / INT8, Common.hpp:96-104). */
+enum { ENN_B200_U8 = 0, ENN_B200_S8 = 1 };
+
+/* Weight memory layouts accepted at prepare time (they are re-packed once on the device):
+ *   OIHW  [Cout][Cin/g][Kh][Kw]   reference NCHW models (CLConvolution.cpp:97-98)
+ *   OHWI  [Cout][Kh][Kw][Cin/g]   ANDROID_NN models (CLGEMMConvolutionQuantized.cpp:59-72)
+ *   IOHW  [Cin][Cout/g][Kh][Kw]   Caffe deconvolution (CLDeconvolutionQuantized.cpp:39-46)
+ * Depthwise: OIHW means [Cout][1][Kh][Kw], OHWI means [1][Kh][Kw][Cout]
+ * (CLDepthwiseConvolution.cpp:126-143).  FullyConnected weights are [Nout][K] (OI) in both. */
+enum { ENN_B200_W_OIHW = 0, ENN_B200_W_OHWI = 1, ENN_B200_W_IOHW = 2 };
+
+/* Which kernel family an op handle was bound to (reported by enn_b200_op_info). */
+enum {
+    ENN_B200_IMPL_DIRECT = 0,    /* CUDA-core dp4a direct kernel (any geometry) */
+    ENN_B200_IMPL_TCGEN05 = 1,   /* TMA + tcgen05.mma kind::i8 implicit GEMM */
+    ENN_B200_IMPL_GEMV = 2,      /* HBM-bound small-M FullyConnected */
+    ENN_B200_IMPL_DEPTHWISE = 3,
+    ENN_B200_IMPL_ELTWISE = 4
+};
+
+typedef struct enn_b200_context enn_b200_context; /* one device + one in-order stream (CLRuntime's queue) */
+typedef struct enn_b200_op enn_b200_op;           /* one prepared operator (CLConvolution etc.) */
+
+/* Conv2D / DepthwiseConv2D / Deconvolution geometry + quantisation.
+ * Fields are what ConvolutionParameters (CLConvolution.hpp:31-44), DepthwiseConvolutionParameters
+ * (CLDepthwiseConvolution.hpp:18-29), DeconvolutionParameters (CLDeconvolution.hpp:20-31) and the
+ * three CLTensors (scale, zero point, dims) carry into initialize(). */
+typedef struct enn_b200_conv_desc {
+    int32_t n, h, w, cin;           /* input NHWC */
+    int32_t cout, kh, kw;           /* depthwise: cout = cin * depth_multiplier */
+    int32_t stride_h, stride_w;
+    int32_t dil_h, dil_w;           /* ignored by deconvolution */
+    int32_t pad_t, pad_r, pad_b, pad_l;  /* Pad4 order (Common.hpp:152-154) */
+    int32_t groups;                 /* conv/deconv group_size; depthwise: depth_multiplier */
+    int32_t activation;             /* ENN_B200_ACT_* */
+    int32_t act_dtype;              /* ENN_B200_U8 | ENN_B200_S8: type of input and output bytes */
+    int32_t weight_dtype;           /* ENN_B200_U8 | ENN_B200_S8 */
+    int32_t weight_layout;          /* ENN_B200_W_* */
+    int32_t per_channel;            /* 1: per_channel_scales[cout] given, weight zero point is 0 */
+    float in_scale;   int32_t in_zp;
+    float w_scale;    int32_t w_zp;     /* per-tensor weights */
+    float bias_scale;                    /* must equal in_scale*w_scale (KernelUtil.cpp:14-16) or multiplier is 0 */
+    float out_scale;  int32_t out_zp;
+    int32_t out_h, out_w;           /* 0 = derive; deconvolution may pass explicit output size */
+} enn_b200_conv_desc;
+
+/* FullyConnected: out[m][n] = requant(bias[n] + sum_k (a[m][k]-in_zp)(w[n][k]-w_zp)), the integer
+ * contraction the reference computes for the same shape expressed as a 1x1 CONV_2D. */
+typedef struct enn_b200_fc_desc {
+    int32_t m, k, n;
+    int32_t activation, act_dtype, weight_dtype, per_channel;
+    float in_scale;   int32_t in_zp;
+    float w_scale;    int32_t w_zp;
+    float bias_scale;
+    float out_scale;  int32_t out_zp;
+} enn_b200_fc_desc;
+
+/* Quantized elementwise add (CLAddQuantized.cpp:70-165) and average pool (CLAveragepool.cpp:175-224). */
+typedef struct enn_b200_add_desc {
+    int64_t count;                  /* number of elements */
+    int32_t activation, act_dtype;
+    float in0_scale;  int32_t in0_zp;
+    float in1_scale;  int32_t in1_zp;
+    float out_scale;  int32_t out_zp;
+} enn_b200_add_desc;
+
+typedef struct enn_b200_pool_desc {
+    int32_t n, h, w, c;
+    int32_t kh, kw, stride_h, stride_w, pad_t, pad_l;
+    int32_t out_h, out_w;
+    int32_t activation, act_dtype;
+    float out_scale;  int32_t out_zp;
+} enn_b200_pool_desc;
+
+/* Derived per-op facts, for callers that size buffers or report work. */
+typedef struct enn_b200_op_info_t {
+    int32_t impl;                   /* ENN_B200_IMPL_* */
+    int32_t out_n, out_h, out_w, out_c;
+    int64_t in_bytes, out_bytes;
+    int64_t macs;                   /* multiply-accumulates of one execute */
+    int64_t algorithmic_bytes;      /* input + weights + bias/params + output, each once */
+    int32_t act_min, act_max;       /* clamp derived as KernelUtil.cpp:27-71 */
+    int32_t kernel_launches;        /* kernels one execute enqueues */
+} enn_b200_op_info_t;
+
+/* ---- runtime shim: replaces CLRuntime / CLBuffer / CLTensor::readData,writeData
+ *      (gpu/common/CLRuntime.cpp:34-157, CLTensor.hpp:39-331, CLComputeLibrary.cpp:15-186) ---- */
+int32_t enn_b200_context_create(int32_t device, enn_b200_context **ctx);
+int32_t enn_b200_context_destroy(enn_b200_context *ctx);
+int32_t enn_b200_malloc(enn_b200_context *ctx, size_t bytes, void **dev_ptr);
+int32_t enn_b200_free(enn_b200_context *ctx, void *dev_ptr);
+/* Asynchronous on the context stream, like the reference's non-blocking writeData
+ * (gpu_userdriver.cc set_input_data); host memory should be pinned for overlap. */
+int32_t enn_b200_upload(enn_b200_context *ctx, void *dev_dst, const void *host_src, size_t bytes);
+/* Copies device->host on the stream and blocks until done, like the blocking readData in set_output_data. */
+int32_t enn_b200_download(enn_b200_context *ctx, void *host_dst, const void *dev_src, size_t bytes);
+int32_t enn_b200_stream_sync(enn_b200_context *ctx);            /* CLComputeLibrary::synchronize */
+int32_t enn_b200_host_alloc(size_t bytes, void **host_ptr);      /* pinned host staging */
+int32_t enn_b200_host_free(void *host_ptr);
+/* Last error text of this context (empty string if none); never fails. */
+int32_t enn_b200_last_error(enn_b200_context *ctx, char *buf, size_t buf_len);
+/* cudaStream_t of the context, as void*, so a caller can order its own work against it. */
+void *enn_b200_stream(enn_b200_context *ctx);
+
+/* ---- operators.  *_prepare uploads + re-packs constant tensors once (the reference does this in
+ *      initialize(): alignQuantizedWeightGEMM, align_weight_direct, matrixTrans ...) and derives the
+ *      requantisation parameters the reference recomputes on every execute.  Host pointers are not
+ *      retained (gpu_op_constructor.cc:2130-2147). ---- */
+
+/* CLConvolution::initialize (CLConvolution.cpp:34-456) -> per-tensor CLGEMMConvolutionQuantized /
+ * CLQuantizedDirectConvolution / CLGEMM1xXConvolutionQuantized or CLConvolutionPerChannelQuantized. */
+int32_t enn_b200_conv2d_prepare(enn_b200_context *ctx, const enn_b200_conv_desc *desc, const void *weights_host,
+                                const int32_t *bias_host, const float *per_channel_scales, enn_b200_op **op);
+/* CLDepthwiseConvolution::initialize (CLDepthwiseConvolution.cpp:88-215). */
+int32_t enn_b200_depthwise_prepare(enn_b200_context *ctx, const enn_b200_conv_desc *desc, const void *weights_host,
+                                   const int32_t *bias_host, const float *per_channel_scales, enn_b200_op **op);
+/* CLDeconvolution::initialize (CLDeconvolution.cpp:36-215). */
+int32_t enn_b200_deconv_prepare(enn_b200_context *ctx, const enn_b200_conv_desc *desc, const void *weights_host,
+                                const int32_t *bias_host, const float *per_channel_scales, enn_b200_op **op);
+/* CLFullyConnected::initialize (CLFullyConnected.cpp:22-102). */
+int32_t enn_b200_fc_prepare(enn_b200_context *ctx, const enn_b200_fc_desc *desc, const void *weights_host,
+                            const int32_t *bias_host, const float *per_channel_scales, enn_b200_op **op);
+/* CLAdd::initialize -> CLAddQuantized (CLAddQuantized.cpp:20-68). */
+int32_t enn_b200_add_prepare(enn_b200_context *ctx, const enn_b200_add_desc *desc, enn_b200_op **op);
+/* CLAveragepool::initialize (CLAveragepool.cpp). */
+int32_t enn_b200_avgpool_prepare(enn_b200_context *ctx, const enn_b200_pool_desc *desc, enn_b200_op **op);
+
+/* Force the kernel family of a prepared conv / fc / deconv handle (ENN_B200_IMPL_DIRECT or
+ * ENN_B200_IMPL_TCGEN05 ...); INVALID_PARAMS if that family cannot run the geometry.  For tests and benches. */
+int32_t enn_b200_op_set_impl(enn_b200_op *op, int32_t impl);
+
+/* EnnUDOperator<T>::execute -> op_->execute() (userdriver_operator.h:32-44): enqueue on the context
+ * stream, no host synchronisation.  Device pointers are read at call time because the reference only
+ * assigns pooled activation buffers after every initialize() has run (gpu_op_constructor.cc:1839-1843). */
+int32_t enn_b200_op_execute(enn_b200_op *op, const void *in_dev, void *out_dev);
+/* Two-input form for the quantized add (inputs = {a, b}). */
+int32_t enn_b200_op_execute2(enn_b200_op *op, const void *in0_dev, const void *in1_dev, void *out_dev);
+int32_t enn_b200_op_info(const enn_b200_op *op, enn_b200_op_info_t *info);
+int32_t enn_b200_op_release(enn_b200_op *op);
+
+/* Layout converters for NCHW models (CLRuntime.cpp:1477-1620 NHWC2NCHW_* / NCHW2NHWC_*), 1-byte elements. */
+int32_t enn_b200_nchw_to_nhwc(enn_b200_context *ctx, const void *src_dev, void *dst_dev, int32_t n, int32_t c,
+                              int32_t h, int32_t w);
+int32_t enn_b200_nhwc_to_nchw(enn_b200_context *ctx, const void *src_dev, void *dst_dev, int32_t n, int32_t c,
+                              int32_t h, int32_t w);
+
+/* Host-side quantisation helpers (cl_quantized_utils/QuantizationUtil.cpp:8-35, KernelUtil.cpp:7-71),
+ * exported so a caller can inspect what prepare derived. */
+void enn_b200_quantize_multiplier(double real_multiplier, int32_t *quantized_multiplier, int32_t *shift);
+int32_t enn_b200_conv_multiplier(double in_scale, double w_scale, double bias_scale, double out_scale,
+                                 double *multiplier);
+void enn_b200_activation_range(int32_t activation, int32_t act_dtype, float scale, int32_t zero_point,
+                               int32_t *act_min, int32_t *act_max);
+
+/* The kernels' requantisation tail evaluated on the host with the same inline code the device uses
+ * (CLKernels.hpp:121-168: left shift, SaturatingRoundingDoublingHighMul, RoundingDivideByPOT, + zero point, clamp). */
+int32_t enn_b200_requant_host(int32_t acc, int32_t multiplier, int32_t shift, int32_t out_zp, int32_t act_min,
+                              int32_t act_max);
+
+/* Library identification: returns a static string naming the build (arch, version). */
+const char *enn_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ENN_B200_H_ */

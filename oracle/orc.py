@@ -1,0 +1,136 @@
+"""ctypes wrapper of the CPU oracle (oracle/liboracle.so) and, when built, of the reference's own host
+code (oracle/_ref/libennref.so).  TEST INFRASTRUCTURE ONLY: imported by tests/, the smoke test and the
+benchmark's CPU-baseline leg, never by the library."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_HERE, "liboracle.so")
+_REF = os.path.join(_HERE, "_ref", "libennref.so")
+
+
+def build():
+    r = subprocess.run(["make", "-C", _HERE], capture_output=True, text=True)
+    if r.returncode:
+        raise RuntimeError("building the oracle failed:\n" + r.stdout[-3000:] + r.stderr[-3000:])
+
+
+if not os.path.exists(_LIB):
+    build()
+lib = C.CDLL(_LIB)
+ref = C.CDLL(_REF) if os.path.exists(_REF) else None
+
+_i32, _p, _f, _d = C.c_int32, C.c_void_p, C.c_float, C.c_double
+_pi32 = C.POINTER(C.c_int32)
+for _l, _pre in ((lib, "orc_"), (ref, "ref_")):
+    if _l is None:
+        continue
+    getattr(_l, _pre + "quantize_multiplier").argtypes = [_d, _pi32, _pi32]
+    getattr(_l, _pre + "quantize_multiplier").restype = None
+    getattr(_l, _pre + "conv_multiplier").argtypes = [_d, _d, _d, _d, C.POINTER(_d)]
+    getattr(_l, _pre + "conv_multiplier").restype = _i32
+    getattr(_l, _pre + "activation_range").argtypes = [_i32, _i32, _f, _i32, _pi32, _pi32]
+    getattr(_l, _pre + "activation_range").restype = None
+    getattr(_l, _pre + "srdhm").argtypes = [_i32, _i32]
+    getattr(_l, _pre + "srdhm").restype = _i32
+    getattr(_l, _pre + "rdivpot").argtypes = [_i32, _i32]
+    getattr(_l, _pre + "rdivpot").restype = _i32
+lib.orc_requant.argtypes = [_i32] * 6
+lib.orc_requant.restype = _i32
+lib.orc_num_threads.restype = _i32
+if ref is not None:
+    ref.ref_multiply_by_quantized_multiplier.argtypes = [_i32, _i32, _i32]
+    ref.ref_multiply_by_quantized_multiplier.restype = _i32
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def quantize_multiplier(m, which=None):
+    l, pre = (which or lib), ("orc_" if (which or lib) is lib else "ref_")
+    qm, sh = C.c_int32(), C.c_int32()
+    getattr(l, pre + "quantize_multiplier")(m, C.byref(qm), C.byref(sh))
+    return qm.value, sh.value
+
+
+def conv_multiplier(a, b, c, d, which=None):
+    l, pre = (which or lib), ("orc_" if (which or lib) is lib else "ref_")
+    m = C.c_double(0.0)
+    st = getattr(l, pre + "conv_multiplier")(a, b, c, d, C.byref(m))
+    return st, m.value
+
+
+def activation_range(act, dtype, scale, zp, which=None):
+    l, pre = (which or lib), ("orc_" if (which or lib) is lib else "ref_")
+    lo, hi = C.c_int32(), C.c_int32()
+    getattr(l, pre + "activation_range")(act, dtype, scale, zp, C.byref(lo), C.byref(hi))
+    return lo.value, hi.value
+
+
+def _act_np(dtype):
+    return np.int8 if dtype == 1 else np.uint8
+
+
+def _run_conv_like(fn, dims_fn, desc, x, w, bias, scales):
+    oh, ow = C.c_int32(), C.c_int32()
+    dims_fn(C.byref(desc), C.byref(oh), C.byref(ow))
+    x = np.ascontiguousarray(x)
+    w = np.ascontiguousarray(w)
+    bias = np.ascontiguousarray(bias, dtype=np.int32)
+    sc = np.ascontiguousarray(scales, dtype=np.float32) if scales is not None else None
+    out = np.empty((desc.n, oh.value, ow.value, desc.cout), dtype=_act_np(desc.act_dtype))
+    st = fn(C.byref(desc), _ptr(x), _ptr(w), _ptr(bias), _ptr(sc), _ptr(out))
+    assert st == 0
+    return out
+
+
+def conv2d(desc, x, w, bias, scales=None):
+    return _run_conv_like(lib.orc_conv2d, lib.orc_conv_out_dims, desc, x, w, bias, scales)
+
+
+def depthwise(desc, x, w, bias, scales=None):
+    return _run_conv_like(lib.orc_depthwise, lib.orc_conv_out_dims, desc, x, w, bias, scales)
+
+
+def deconv(desc, x, w, bias, scales=None):
+    return _run_conv_like(lib.orc_deconv, lib.orc_deconv_out_dims, desc, x, w, bias, scales)
+
+
+def fully_connected(desc, x, w, bias, scales=None, float_emulation=False):
+    x = np.ascontiguousarray(x)
+    w = np.ascontiguousarray(w)
+    bias = np.ascontiguousarray(bias, dtype=np.int32)
+    sc = np.ascontiguousarray(scales, dtype=np.float32) if scales is not None else None
+    out = np.empty((desc.m, desc.n), dtype=_act_np(desc.act_dtype))
+    if float_emulation:
+        st = lib.orc_fc_float(C.byref(desc), _ptr(x), _ptr(w), _ptr(bias), _ptr(out))
+    else:
+        st = lib.orc_fc(C.byref(desc), _ptr(x), _ptr(w), _ptr(bias), _ptr(sc), _ptr(out))
+    assert st == 0
+    return out
+
+
+def add(desc, a, b):
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b)
+    out = np.empty(a.shape, dtype=a.dtype)
+    st = lib.orc_add(C.byref(desc), _ptr(a), _ptr(b), _ptr(out))
+    if st:
+        raise ValueError(f"orc_add rejected the parameters ({st})")
+    return out
+
+
+def avgpool(desc, x):
+    x = np.ascontiguousarray(x)
+    out = np.empty((desc.n, desc.out_h, desc.out_w, desc.c), dtype=x.dtype)
+    st = lib.orc_avgpool(C.byref(desc), _ptr(x), _ptr(out))
+    assert st == 0
+    return out
+
+
+def num_threads():
+    return lib.orc_num_threads()

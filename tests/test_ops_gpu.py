@@ -1,0 +1,213 @@
+"""GPU parity tests: every operator through the C ABI against the CPU oracle, bit for bit."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import cases
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _check(op, y_ref, x, x2=None):
+    y = op.run(x, x2).reshape(y_ref.shape)
+    bad = np.nonzero(y != y_ref)
+    assert bad[0].size == 0, f"{bad[0].size} of {y.size} differ; first at {[int(b[0]) for b in bad]}: " \
+                             f"got {y[tuple(b[0] for b in bad)]} want {y_ref[tuple(b[0] for b in bad)]}"
+
+
+def _impls(enn, op):
+    """Every kernel family this op can run with (direct always; tensor core when planned)."""
+    out = [op.info.impl]
+    for impl in (enn.IMPL_DIRECT, enn.IMPL_TCGEN05):
+        if impl not in out:
+            try:
+                op.set_impl(impl)
+                out.append(impl)
+            except enn.EnnError:
+                pass
+    return out
+
+
+CONV_CASES = {
+    "config1_3x3_64": dict(),
+    "ragged_5x7": dict(n=2, h=5, w=7, cin=3, cout=5, k=3),
+    "stride2": dict(n=2, h=15, w=14, cin=8, cout=12, k=3, stride=2),
+    "dilated": dict(n=1, h=13, w=13, cin=8, cout=8, k=3, dil=2),
+    "grouped_oihw": dict(n=2, h=9, w=9, cin=8, cout=12, k=3, groups=4, layout=cases.enn.W_OIHW),
+    "pointwise": dict(n=2, h=14, w=14, cin=96, cout=24, k=1, act=cases.enn.ACT_NONE),
+    "per_channel": dict(n=2, h=14, w=14, cin=32, cout=48, k=3, per_channel=True, out_scale=0.3),
+    "per_channel_1x1": dict(n=3, h=7, w=7, cin=160, cout=320, k=1, per_channel=True, out_scale=0.5, act=cases.enn.ACT_NONE),
+    "relu": dict(n=1, h=8, w=8, cin=16, cout=16, k=3, act=cases.enn.ACT_RELU),
+    "relu1": dict(n=1, h=8, w=8, cin=16, cout=16, k=3, act=cases.enn.ACT_RELU1, out_scale=0.01),
+    "valid_pad": dict(n=1, h=10, w=11, cin=8, cout=8, k=3, pad="valid"),
+    "asym_kernel": dict(n=1, h=9, w=12, cin=8, cout=8, kh=1, kw=5),
+    "signed_act": dict(n=1, h=8, w=8, cin=8, cout=8, k=3, act_dtype=cases.enn.S8, in_zp=-3, out_zp=5, per_channel=True, out_scale=0.2),
+    "big_multiplier": dict(n=1, h=6, w=6, cin=4, cout=4, k=1, in_scale=0.5, w_scale=0.5, out_scale=0.05, w_zp=3),
+    "batch_stem_like": dict(n=2, h=32, w=32, cin=3, cout=32, k=3, stride=2, per_channel=True, out_scale=0.1),
+}
+
+
+@pytest.mark.parametrize("name", list(CONV_CASES))
+def test_conv2d_parity(enn, orc, ctx, name):
+    d, x, w, b, sc = cases.conv_case(seed=hash(name) % 1000, **CONV_CASES[name])
+    y_ref = orc.conv2d(d, x, w, b, sc)
+    op = enn.conv2d(ctx, d, w, b, sc)
+    try:
+        for impl in _impls(enn, op):
+            op.set_impl(impl)
+            _check(op, y_ref, x)
+    finally:
+        op.release()
+
+
+def test_kat_perchannel_conv_gpu(enn, ctx):
+    """Reference known-answer test gpu_userdriver_test.cc:474-575 through NCHW upload + layout conversion."""
+    k = json.load(open(os.path.join(HERE, "golden", "kat_perchannel_conv.json")))
+    n, c, h, w = k["input_dims_nchw"]
+    x_nchw = np.array(k["input"], np.uint8)
+    d = enn.conv_desc(n=n, h=h, w=w, cin=c, cout=3, kh=1, kw=1, per_channel=1, weight_dtype=enn.S8,
+                      weight_layout=enn.W_OHWI, in_scale=k["input_scale"], in_zp=k["zero_point"],
+                      out_scale=k["output_scale"], out_zp=k["zero_point"])
+    op = enn.conv2d(ctx, d, np.array(k["weight"], np.int8), np.array(k["bias"], np.int32), np.array(k["scales"], np.float32))
+    src = ctx.to_device(x_nchw)
+    nhwc, out, out_nchw = ctx.malloc(6), ctx.malloc(9), ctx.malloc(9)
+    ctx.check(enn.lib.enn_b200_nchw_to_nhwc(ctx.h, src, nhwc, n, c, h, w))
+    op.execute(nhwc, out)
+    ctx.check(enn.lib.enn_b200_nhwc_to_nchw(ctx.h, out, out_nchw, 1, 3, 3, 1))
+    assert ctx.download(out_nchw, (9,)).tolist() == k["expect"]
+    for p in (src, nhwc, out, out_nchw):
+        ctx.free(p)
+    op.release()
+
+
+DW_CASES = {
+    "config2_s1": dict(n=2),
+    "config2_s2": dict(n=2, stride=2),
+    "per_tensor": dict(n=1, h=17, w=19, c=24, per_channel=False, out_scale=0.08, out_zp=3),
+    "multiplier2": dict(n=1, h=9, w=9, c=6, dm=2),
+    "ohwi_5x5": dict(n=1, h=12, w=12, c=16, k=5, layout=cases.enn.W_OHWI),
+    "odd_channels": dict(n=2, h=7, w=7, c=5),
+    "dilated": dict(n=1, h=14, w=14, c=8, dil=2),
+    "wide_c": dict(n=1, h=14, w=14, c=576),
+    "c960_7x7": dict(n=2, h=7, w=7, c=960),
+    "signed": dict(n=1, h=9, w=9, c=8, act_dtype=cases.enn.S8, in_zp=-5, out_zp=-128),
+    "tiny": dict(n=1, h=1, w=1, c=4),
+}
+
+
+@pytest.mark.parametrize("name", list(DW_CASES))
+def test_depthwise_parity(enn, orc, ctx, name):
+    d, x, w, b, sc = cases.depthwise_case(seed=hash(name) % 1000, **DW_CASES[name])
+    y_ref = orc.depthwise(d, x, w, b, sc)
+    op = enn.depthwise(ctx, d, w, b, sc)
+    try:
+        _check(op, y_ref, x)
+    finally:
+        op.release()
+
+
+DECONV_CASES = {
+    "config4_small": dict(n=1, h=16, w=16),
+    "ohwi": dict(n=2, h=6, w=5, cin=16, cout=8, layout=cases.enn.W_OHWI),
+    "per_channel": dict(n=1, h=8, w=8, cin=32, cout=16, per_channel=True, out_scale=0.5),
+    "k3_s2": dict(n=1, h=7, w=7, cin=8, cout=8, k=3, stride=2, pad=0),
+    "k2_s2": dict(n=1, h=7, w=9, cin=8, cout=4, k=2, stride=2, pad=0),
+    "s1": dict(n=1, h=6, w=6, cin=8, cout=8, k=3, stride=1, pad=1),
+    "relu6": dict(n=1, h=5, w=5, cin=4, cout=4, act=cases.enn.ACT_RELU6),
+}
+
+
+@pytest.mark.parametrize("name", list(DECONV_CASES))
+def test_deconv_parity(enn, orc, ctx, name):
+    d, x, w, b, sc = cases.deconv_case(seed=hash(name) % 1000, **DECONV_CASES[name])
+    y_ref = orc.deconv(d, x, w, b, sc)
+    op = enn.deconv(ctx, d, w, b, sc)
+    try:
+        for impl in _impls(enn, op):
+            op.set_impl(impl)
+            _check(op, y_ref, x)
+    finally:
+        op.release()
+
+
+FC_CASES = {
+    "gemv": dict(m=1, k=512, n=256),
+    "small": dict(m=4, k=256, n=64),
+    "mid": dict(m=256, k=1024, n=1024),
+    "ragged": dict(m=37, k=100, n=29),
+    "per_tensor": dict(m=8, k=128, n=64, per_channel=False),
+    "relu6": dict(m=8, k=128, n=64, act=cases.enn.ACT_RELU6),
+}
+
+
+@pytest.mark.parametrize("name", list(FC_CASES))
+def test_fc_parity(enn, orc, ctx, name):
+    d, x, w, b, sc = cases.fc_case(seed=hash(name) % 1000, **FC_CASES[name])
+    y_ref = orc.fully_connected(d, x, w, b, sc)
+    op = enn.fully_connected(ctx, d, w, b, sc)
+    try:
+        for impl in _impls(enn, op):
+            op.set_impl(impl)
+            _check(op, y_ref, x)
+    finally:
+        op.release()
+
+
+@pytest.mark.parametrize("count,act", [(1, 0), (15, 0), (4097, 3), (1 << 20, 0), (56 * 56 * 24 * 3, 0)])
+def test_add_parity(enn, orc, ctx, count, act):
+    rng = np.random.default_rng(count)
+    a = rng.integers(0, 256, count, dtype=np.int64).astype(np.uint8)
+    b = rng.integers(0, 256, count, dtype=np.int64).astype(np.uint8)
+    d = enn.AddDesc(count=count, activation=act, act_dtype=enn.U8, in0_scale=0.031, in0_zp=120, in1_scale=0.047,
+                    in1_zp=131, out_scale=0.06, out_zp=126)
+    op = enn.add(ctx, d)
+    try:
+        _check(op, orc.add(d, a, b), a, b)
+    finally:
+        op.release()
+
+
+@pytest.mark.parametrize("shape", [(2, 7, 7, 1280, 7, 1), (1, 9, 9, 16, 3, 2), (3, 5, 6, 7, 2, 2)])
+def test_avgpool_parity(enn, orc, ctx, shape):
+    n, h, w, c, k, s = shape
+    rng = np.random.default_rng(h * w)
+    x = rng.integers(0, 256, (n, h, w, c), dtype=np.int64).astype(np.uint8)
+    oh, ow = (h - k) // s + 1, (w - k) // s + 1
+    d = enn.PoolDesc(n=n, h=h, w=w, c=c, kh=k, kw=k, stride_h=s, stride_w=s, pad_t=0, pad_l=0, out_h=oh, out_w=ow,
+                     activation=0, act_dtype=enn.U8, out_scale=0.02, out_zp=0)
+    op = enn.avgpool(ctx, d)
+    try:
+        _check(op, orc.avgpool(d, x), x)
+    finally:
+        op.release()
+
+
+def test_error_paths(enn, ctx):
+    d, x, w, b, sc = cases.conv_case(h=4, w=4, cin=4, cout=4)
+    d.cin = 0
+    with pytest.raises(enn.EnnError) as e:
+        enn.conv2d(ctx, d, w, b, sc)
+    assert e.value.status == enn.INVALID_PARAMS
+    d, x, w, b, sc = cases.conv_case(h=4, w=4, cin=4, cout=4, per_channel=True)
+    with pytest.raises(enn.EnnError):
+        enn.conv2d(ctx, d, w, b, None)          # per-channel without scales
+    d, x, w, b, sc = cases.conv_case(h=4, w=4, cin=6, cout=4, groups=4)
+    with pytest.raises(enn.EnnError):
+        enn.conv2d(ctx, d, w, b, sc)            # channels not divisible by groups
+    d, x, w, b, sc = cases.conv_case(h=4, w=4, cin=4, cout=4)
+    op = enn.conv2d(ctx, d, w, b, sc)
+    with pytest.raises(enn.EnnError):
+        op.execute(None, None)
+    op.release()
+
+
+def test_bias_scale_mismatch_gpu(enn, orc, ctx):
+    d, x, w, b, sc = cases.conv_case(seed=1, h=6, w=6, cin=4, cout=4, act=enn.ACT_NONE)
+    d.bias_scale = 0.5
+    op = enn.conv2d(ctx, d, w, b, sc)
+    y = op.run(x)
+    assert np.all(y == d.out_zp)
+    op.release()
