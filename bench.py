@@ -244,7 +244,7 @@ def run_ours(args):
         "clocks": clocks,
     }
     if rank == 0:
-        if world == 1:
+        if world == 1 and not args.skip_cpu_baseline:
             result["cpu_baseline"] = cpu_baseline(args, wl)
         print(json.dumps(result), flush=True)
     if multi:
@@ -307,6 +307,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="depthwise3x3_s1_64x112x112x32")
+    ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU leg (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

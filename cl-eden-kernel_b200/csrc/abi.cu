@@ -300,6 +300,54 @@ static int32_t conv_like_prepare(enn_b200_context *ctx, const enn_b200_conv_desc
               d->per_channel != 0);
     op->info.out_n = g.n; op->info.out_h = g.oh; op->info.out_w = g.ow; op->info.out_c = cout;
     op->impl = kind == OP_DEPTHWISE ? ENN_B200_IMPL_DEPTHWISE : ENN_B200_IMPL_DIRECT;
+    if (kind == OP_DEPTHWISE && dw3x3_eligible(g)) {
+        // Constants of the 3x3 fast path (depthwise.cu): folded bias, stage-2 addend, packed tap words.
+        std::vector<int32_t> mult, shift;
+        derive_requant(cout, d->per_channel != 0, d->in_scale, d->w_scale, d->bias_scale, d->out_scale, pc_scales, &mult, &shift);
+        std::vector<int32_t> chan(static_cast<size_t>(cout) * 4);
+        std::vector<uint32_t> wp(static_cast<size_t>(cout) * 3);
+        bool ok = true;
+        for (int32_t c = 0; c < cout && ok; ++c) {
+            int64_t wsum = 0, wabs = 0;
+            for (int32_t ky = 0; ky < 3; ++ky) {
+                uint32_t word = 0;
+                for (int32_t kx = 0; kx < 3; ++kx) {
+                    const uint8_t raw = packed[(static_cast<size_t>(ky) * 3 + kx) * cout + c];
+                    const int32_t wv = g.w_signed ? static_cast<int32_t>(static_cast<int8_t>(raw)) : static_cast<int32_t>(raw);
+                    wsum += wv;
+                    wabs += wv < 0 ? -wv : wv;
+                    word |= static_cast<uint32_t>(raw) << (8 * kx);
+                }
+                wp[static_cast<size_t>(c) * 3 + ky] = word;
+            }
+            const int64_t folded = static_cast<int64_t>(bias_host[c]) - static_cast<int64_t>(g.in_zp) * wsum +
+                                   9ll * g.in_zp * g.w_zp;
+            const int32_t e = shift[c] > 0 ? -1 : -shift[c];
+            // |accumulator| bound: 9 taps of a in [0,255] against w, the w_zp * sum(a) term and the folded bias.
+            const int64_t acc_bound = 255 * wabs + 9ll * 255 * (g.w_zp < 0 ? -g.w_zp : g.w_zp) + (folded < 0 ? -folded : folded);
+            // stage-2 addend with the output zero point and the (negated) lower clamp folded in
+            const int64_t zo_eff = static_cast<int64_t>(g.out_zp) - g.act_min;
+            const int64_t addend = e > 0 ? (1ll << (e - 1)) + zo_eff * (1ll << e) : zo_eff;
+            if (e < 0 || folded > INT32_MAX || folded < INT32_MIN || acc_bound + 2 + (addend < 0 ? -addend : addend) >= (1ll << 31)) {
+                ok = false;   // left shift or possible overflow of the fused stage-2 form: keep the general kernel
+                break;
+            }
+            chan[c * 4 + 0] = mult[c];
+            chan[c * 4 + 1] = static_cast<int32_t>(addend);
+            chan[c * 4 + 2] = e | ((e > 0 ? 31 : 32) << 8);
+            chan[c * 4 + 3] = static_cast<int32_t>(folded);
+        }
+        if (ok) {
+            int32_t *dc = nullptr;
+            uint32_t *dwp = nullptr;
+            if ((st = upload_vec(op, chan, &dc)) || (st = upload_vec(op, wp, &dwp))) {
+                enn_b200_op_release(op);
+                return st;
+            }
+            op->dw_chan = dc;
+            op->dw_w = dwp;
+        }
+    }
     if (kind != OP_DEPTHWISE && tc_available(ctx)) {
         st = tc_plan_conv(op, packed.data());
         if (st == ENN_B200_SUCCESS && op->tc) op->impl = ENN_B200_IMPL_TCGEN05;
@@ -429,6 +477,12 @@ int32_t enn_b200_op_set_impl(enn_b200_op *op, int32_t impl) {
         op->info.impl = op->impl;
         return ENN_B200_SUCCESS;
     }
+    if (op->kind == OP_DEPTHWISE && (impl == ENN_B200_IMPL_DIRECT || impl == ENN_B200_IMPL_DEPTHWISE)) {
+        // DIRECT selects the general kernel, DEPTHWISE the 3x3 fast path when the geometry has one.
+        op->impl = impl;
+        op->info.impl = impl;
+        return ENN_B200_SUCCESS;
+    }
     return impl == op->impl ? ENN_B200_SUCCESS : fail(op->ctx, ENN_B200_INVALID_PARAMS, "op has a single kernel family");
 }
 
@@ -448,6 +502,10 @@ int32_t enn_b200_op_execute(enn_b200_op *op, const void *in, void *out) {
             e = launch_deconv_direct(op->g, op->rq, in, op->w_direct, out, ctx->stream);
             break;
         case OP_DEPTHWISE:
+            if (op->dw_chan && op->impl == ENN_B200_IMPL_DEPTHWISE) {
+                e = launch_dw3x3(op->g, op->dw_chan, op->dw_w, in, out, ctx->sm_count, ctx->stream);
+                break;
+            }
             e = launch_depthwise(op->g, op->rq, in, op->w_direct, out, ctx->sm_count, ctx->stream);
             break;
         case OP_AVGPOOL:

@@ -1,12 +1,18 @@
 // DepthwiseConv2D, NHWC.  Value: DepthwiseconvolutionKernels.cpp:1273-1371 after the zero-point `pad`
 // pre-pass (border taps contribute nothing).  HBM-bound: no tensor cores.
+//
+// Two kernels:
+//   depthwise_generic_kernel  any kernel size / stride / dilation / depth multiplier / signedness;
+//   dw3x3_kernel              3x3, stride 1 or 2, dilation 1, multiplier 1, C % 4 == 0, u8 activations: the
+//                             case every reference 3x3 variant (depthwise_conv_3x3s1_pad_merge, ..3x3s2..,
+//                             depthwise_conv_per_channel) covers and the one the benchmark configuration uses.
+#include <cstdlib>
+
 #include "internal.h"
 #include "requant.h"
 
 namespace enn_b200 {
 
-// General form: any kernel size, stride, dilation, depth multiplier, signedness.  One thread per
-// (pixel, output channel), channel fastest.  Weights packed [Kh][Kw][Cout].
 __global__ void depthwise_generic_kernel(ConvGeom g, Requant rq, const void *__restrict__ in,
                                          const void *__restrict__ w, uint8_t *__restrict__ out, int64_t total) {
     const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -35,6 +41,325 @@ __global__ void depthwise_generic_kernel(ConvGeom g, Requant rq, const void *__r
         }
     }
     out[idx] = static_cast<uint8_t>(enn_requant(acc, rq.mult[oc], rq.shift[oc], g.out_zp, g.act_min, g.act_max));
+}
+
+// ------------------------------------------------------------------------------------------------------
+// 3x3 fast path.
+//
+// A thread owns 4 channels (one 32-bit word of an NHWC pixel) x a strip of 4 output pixels along W and walks
+// down TH output rows.  Each input row of the strip (6 pixels for stride 1, 9 for stride 2) is read once,
+// byte-transposed with PRMT so that one register holds 4 consecutive pixels of ONE channel, and kept in a
+// ring of three rows.  A 3-tap row product is then one dp4a against a packed weight word (w0,w1,w2,0) or
+// (0,w0,w1,w2): 12 dp4a + 4 PRMT replace 36 multiply-adds per channel and output row.
+//
+// Zero points: the border is filled with the input zero point (what the reference's `pad` kernel writes), so
+//   sum (a - za)(w - zw) = sum a*w - zw * sum a - za * sum w + 9 za zw
+// with the last two terms folded into the bias at prepare time.  Per-channel int8 filters have zw == 0; the
+// u8 per-tensor case carries `sum a` in a second dp4a chain (NEED_ASUM).
+//
+// Requantisation per output: one 32x32->64 multiply-add (stage 1), one funnel shift, and stage 2 written as
+//   (x + 2^(e-1) + (zo << e) - [x < 0 and e > 0]) >> e
+// which equals RoundingDivideByPOT(x, e) + zo (ties away from zero); prepare checks that it cannot overflow.
+// ------------------------------------------------------------------------------------------------------
+struct DwChan {   // per-channel constants, 16 bytes
+    int32_t mult;
+    int32_t addend;   // 2^(e-1) + (out_zp << e), e = right shift
+    int32_t e;        // right shift | (sign shift << 8): sign shift is 31 when e > 0 else 32
+    int32_t bias;     // bias - za * sum(w) + 9 * za * zw
+};
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+template <bool W_SIGNED>
+__device__ __forceinline__ int32_t dp4a_us(uint32_t a, uint32_t b, int32_t c) {
+    int32_t d;
+    if (W_SIGNED)
+        asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    else
+        asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t shr_clamp(uint32_t a, uint32_t s) {   // PTX shr clamps s >= 32 to 0 result
+    uint32_t d;
+    asm("shr.u32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(s));
+    return d;
+}
+__device__ __forceinline__ uint32_t pack_sat_u8(int32_t hi, int32_t lo, uint32_t upper) {
+    uint32_t d;   // d = { upper[15:0], sat_u8(hi), sat_u8(lo) }
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(upper));
+    return d;
+}
+
+// Transposed input row for 4 channels: lo[c] holds the first four pixels of channel c's window, hi[c] the
+// four pixels starting two (stride 1) or four (stride 2) positions later, x8[c] (stride 2) positions 6,7,8.
+template <int STRIDE>
+struct DwRow {
+    uint32_t lo[4], hi[4], x8[STRIDE == 2 ? 4 : 1];
+};
+
+template <int STRIDE>
+struct DwRaw {
+    uint32_t p[STRIDE == 1 ? 6 : 9];
+};
+
+// Issues the global loads of one input row of the strip (border positions read as the input zero point).
+// `colp` points at (batch b, row 0, pixel ix0, channel quad) and `colmask` has bit i set when pixel ix0+i lies
+// inside the image, so the per-row work is one row offset and predicated loads.
+template <int STRIDE>
+__device__ __forceinline__ void dw_issue_row(DwRaw<STRIDE> &raw, const uint8_t *__restrict__ colp, uint32_t row_pitch,
+                                             uint32_t cin, int h, int iy, uint32_t colmask, uint32_t zaw) {
+    constexpr int NP = STRIDE == 1 ? 6 : 9;
+    const bool row_ok = iy >= 0 && iy < h;
+    const uint8_t *rowp = colp + static_cast<uint32_t>(row_ok ? iy : 0) * row_pitch;
+    const uint32_t m = row_ok ? colmask : 0u;
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+        raw.p[i] = zaw;
+        if (m & (1u << i)) raw.p[i] = __ldg(reinterpret_cast<const uint32_t *>(rowp + static_cast<uint32_t>(i) * cin));
+    }
+}
+
+// 4x4 byte transposes: pixel-major words -> channel-major words.
+template <int STRIDE>
+__device__ __forceinline__ void dw_transpose_row(DwRow<STRIDE> &r, const DwRaw<STRIDE> &raw) {
+    constexpr int NP = STRIDE == 1 ? 6 : 9;
+    const uint32_t *p = raw.p;
+    {
+        const uint32_t t0 = prmt(p[0], p[1], 0x5140), t1 = prmt(p[0], p[1], 0x7362);
+        const uint32_t t2 = prmt(p[2], p[3], 0x5140), t3 = prmt(p[2], p[3], 0x7362);
+        r.lo[0] = prmt(t0, t2, 0x5410); r.lo[1] = prmt(t0, t2, 0x7632);
+        r.lo[2] = prmt(t1, t3, 0x5410); r.lo[3] = prmt(t1, t3, 0x7632);
+    }
+    if (STRIDE == 1) {
+        // hi = pixels 2..5
+        const uint32_t t0 = prmt(p[2], p[3], 0x5140), t1 = prmt(p[2], p[3], 0x7362);
+        const uint32_t t2 = prmt(p[4], p[5], 0x5140), t3 = prmt(p[4], p[5], 0x7362);
+        r.hi[0] = prmt(t0, t2, 0x5410); r.hi[1] = prmt(t0, t2, 0x7632);
+        r.hi[2] = prmt(t1, t3, 0x5410); r.hi[3] = prmt(t1, t3, 0x7632);
+    } else {
+        // hi = pixels 4..7, x8 = pixels 6,7,8 (bytes 2,3 of hi and the channel byte of pixel 8)
+        const uint32_t t0 = prmt(p[4], p[5], 0x5140), t1 = prmt(p[4], p[5], 0x7362);
+        const uint32_t t2 = prmt(p[6], p[7], 0x5140), t3 = prmt(p[6], p[7], 0x7362);
+        r.hi[0] = prmt(t0, t2, 0x5410); r.hi[1] = prmt(t0, t2, 0x7632);
+        r.hi[2] = prmt(t1, t3, 0x5410); r.hi[3] = prmt(t1, t3, 0x7632);
+        const uint32_t q = p[NP - 1];
+        r.x8[0] = prmt(r.hi[0], q, 0x0432); r.x8[1] = prmt(r.hi[1], q, 0x0532);
+        r.x8[2] = prmt(r.hi[2], q, 0x0632); r.x8[3] = prmt(r.hi[3], q, 0x0732);
+    }
+}
+
+template <int STRIDE, bool W_SIGNED, bool NEED_ASUM, bool FIRST>
+__device__ __forceinline__ void dw_accumulate(int32_t (&acc)[4][4], int32_t (&asum)[NEED_ASUM ? 4 : 1][4],
+                                              const DwRow<STRIDE> &r, const uint32_t (&wlo)[4], const uint32_t (&whi)[4],
+                                              const int32_t (&bias)[4]) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        if (FIRST) {   // the first tap row starts every chain from the folded bias: no separate initialisation
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc[c][j] = bias[c];
+                if (NEED_ASUM) asum[c][j] = 0;
+            }
+        }
+        if (STRIDE == 1) {
+            acc[c][0] = dp4a_us<W_SIGNED>(r.lo[c], wlo[c], acc[c][0]);
+            acc[c][1] = dp4a_us<W_SIGNED>(r.lo[c], whi[c], acc[c][1]);
+            acc[c][2] = dp4a_us<W_SIGNED>(r.hi[c], wlo[c], acc[c][2]);
+            acc[c][3] = dp4a_us<W_SIGNED>(r.hi[c], whi[c], acc[c][3]);
+            if (NEED_ASUM) {
+                asum[c][0] = dp4a_us<false>(r.lo[c], 0x00010101u, asum[c][0]);
+                asum[c][1] = dp4a_us<false>(r.lo[c], 0x01010100u, asum[c][1]);
+                asum[c][2] = dp4a_us<false>(r.hi[c], 0x00010101u, asum[c][2]);
+                asum[c][3] = dp4a_us<false>(r.hi[c], 0x01010100u, asum[c][3]);
+            }
+        } else {
+            // outputs use window positions {0,1,2}, {2,3,4}, {4,5,6}, {6,7,8}
+            const uint32_t mid = prmt(r.lo[c], r.hi[c], 0x0432);   // positions 2,3,4
+            acc[c][0] = dp4a_us<W_SIGNED>(r.lo[c], wlo[c], acc[c][0]);
+            acc[c][1] = dp4a_us<W_SIGNED>(mid, wlo[c], acc[c][1]);
+            acc[c][2] = dp4a_us<W_SIGNED>(r.hi[c], wlo[c], acc[c][2]);
+            acc[c][3] = dp4a_us<W_SIGNED>(r.x8[c], wlo[c], acc[c][3]);
+            if (NEED_ASUM) {
+                asum[c][0] = dp4a_us<false>(r.lo[c], 0x00010101u, asum[c][0]);
+                asum[c][1] = dp4a_us<false>(mid, 0x00010101u, asum[c][1]);
+                asum[c][2] = dp4a_us<false>(r.hi[c], 0x00010101u, asum[c][2]);
+                asum[c][3] = dp4a_us<false>(r.x8[c], 0x00010101u, asum[c][3]);
+            }
+        }
+    }
+}
+
+// w_packed: [C][3] words, bytes (w[ky][0], w[ky][1], w[ky][2], 0) of channel c.
+// The lower clamp is folded into the stage-2 addend (addend -= act_min << e), so the epilogue clamps
+// (v - act_min) to [0, act_max - act_min] with one min-with-relu and adds act_min back per packed word.
+template <int STRIDE, bool W_SIGNED, bool NEED_ASUM>
+__global__ void __launch_bounds__(256, 2)
+dw3x3_kernel(ConvGeom g, const DwChan *__restrict__ chan, const uint32_t *__restrict__ w_packed,
+             const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int th, int nyt, int nstrip, int64_t total) {
+    const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (tid >= total) return;
+    const int cqn = g.cin >> 2;
+    const int cq = static_cast<int>(tid % cqn);
+    int64_t t = tid / cqn;
+    const int strip = static_cast<int>(t % nstrip);
+    t /= nstrip;
+    const int yt = static_cast<int>(t % nyt);
+    const int b = static_cast<int>(t / nyt);
+
+    uint32_t wlo[3][4], whi[3][4];
+    int32_t mult[4], addend[4], esh[4], bias[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const DwChan ch = chan[cq * 4 + c];
+        mult[c] = ch.mult; addend[c] = ch.addend; esh[c] = ch.e; bias[c] = ch.bias;
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky) {
+            wlo[ky][c] = w_packed[(cq * 4 + c) * 3 + ky];
+            whi[ky][c] = wlo[ky][c] << 8;
+        }
+    }
+    const uint32_t zaw = (static_cast<uint32_t>(g.in_zp) & 0xff) * 0x01010101u;
+    const int ox0 = strip * 4;
+    const int ix0 = ox0 * STRIDE - g.pl;
+    const int oy0 = yt * th;
+    const int oy1 = min(oy0 + th, g.oh);
+    const int h = g.h;
+    const uint32_t cin = static_cast<uint32_t>(g.cin);
+    const uint32_t row_pitch = static_cast<uint32_t>(g.w) * cin;
+    constexpr int NP = STRIDE == 1 ? 6 : 9;
+    uint32_t colmask = 0;
+#pragma unroll
+    for (int i = 0; i < NP; ++i)
+        if (ix0 + i >= 0 && ix0 + i < g.w) colmask |= 1u << i;
+    // Pointer to (b, row 0, pixel ix0, quad cq); ix0 may be negative, masked loads never touch those bytes.
+    const uint8_t *colp = in + (static_cast<int64_t>(b) * h * g.w + ix0) * static_cast<int64_t>(cin) + cq * 4;
+    const int32_t hi_clamp = g.act_max - g.act_min;
+    const uint32_t lo_word = (static_cast<uint32_t>(g.act_min) & 0xff) * 0x01010101u;
+    const uint32_t cout = static_cast<uint32_t>(g.cout);
+    uint8_t *orow = out + ((static_cast<int64_t>(b) * g.oh + oy0) * g.ow + ox0) * static_cast<int64_t>(cout) + cq * 4;
+    const uint32_t out_pitch = static_cast<uint32_t>(g.ow) * cout;
+    uint32_t omask = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (ox0 + j < g.ow) omask |= 1u << j;
+
+    // One output row: accumulate three input rows, requantise, store 4 pixels x 4 channels.
+    auto emit = [&](const DwRow<STRIDE> &r0, const DwRow<STRIDE> &r1, const DwRow<STRIDE> &r2) {
+        int32_t acc[4][4];
+        int32_t asum[NEED_ASUM ? 4 : 1][4];
+        dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, true>(acc, asum, r0, wlo[0], whi[0], bias);
+        dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r1, wlo[1], whi[1], bias);
+        dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r2, wlo[2], whi[2], bias);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int32_t y[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                int32_t a = acc[c][j];
+                if (NEED_ASUM) a -= g.w_zp * asum[c][j];
+                const int64_t p = static_cast<int64_t>(a) * mult[c] + (1ll << 30);
+                const int32_t x = static_cast<int32_t>(p >> 31);
+                const int32_t v = (x + addend[c] - static_cast<int32_t>(shr_clamp(static_cast<uint32_t>(x), esh[c] >> 8))) >> (esh[c] & 0xff);
+                y[c] = __vimin_s32_relu(v, hi_clamp);
+            }
+            if (omask & (1u << j)) {
+                const uint32_t hi = pack_sat_u8(y[3], y[2], 0);
+                *reinterpret_cast<uint32_t *>(orow + static_cast<uint32_t>(j) * cout) = pack_sat_u8(y[1], y[0], hi) + lo_word;
+            }
+        }
+        orow += out_pitch;
+    };
+
+    // Ring of three transposed rows; the loop is unrolled over the ring so no register copies are needed.
+    // The raw loads of the next input row(s) are issued before the current output row is computed, so
+    // their latency overlaps the dp4a / requantisation work.
+    DwRow<STRIDE> ra, rb, rc;
+    const int iy0 = oy0 * STRIDE - g.pt;
+    {
+        DwRaw<STRIDE> r0;
+        dw_issue_row<STRIDE>(r0, colp, row_pitch, cin, h, iy0, colmask, zaw);
+        dw_transpose_row<STRIDE>(ra, r0);
+    }
+    if constexpr (STRIDE == 1) {
+        DwRaw<STRIDE> nx;
+        dw_issue_row<STRIDE>(nx, colp, row_pitch, cin, h, iy0 + 1, colmask, zaw);
+        dw_transpose_row<STRIDE>(rb, nx);
+        dw_issue_row<STRIDE>(nx, colp, row_pitch, cin, h, iy0 + 2, colmask, zaw);
+        for (int oy = oy0; oy < oy1; oy += 3) {
+            const int iy = oy - g.pt;
+            dw_transpose_row<STRIDE>(rc, nx);
+            dw_issue_row<STRIDE>(nx, colp, row_pitch, cin, h, iy + 3, colmask, zaw);
+            emit(ra, rb, rc);
+            if (oy + 1 < oy1) {
+                dw_transpose_row<STRIDE>(ra, nx);
+                dw_issue_row<STRIDE>(nx, colp, row_pitch, cin, h, iy + 4, colmask, zaw);
+                emit(rb, rc, ra);
+            }
+            if (oy + 2 < oy1) {
+                dw_transpose_row<STRIDE>(rb, nx);
+                dw_issue_row<STRIDE>(nx, colp, row_pitch, cin, h, iy + 5, colmask, zaw);
+                emit(rc, ra, rb);
+            }
+        }
+    } else {
+        DwRaw<STRIDE> n1, n2;
+        dw_issue_row<STRIDE>(n1, colp, row_pitch, cin, h, iy0 + 1, colmask, zaw);
+        dw_issue_row<STRIDE>(n2, colp, row_pitch, cin, h, iy0 + 2, colmask, zaw);
+        for (int oy = oy0; oy < oy1; oy += 2) {
+            const int iy = oy * 2 - g.pt;
+            dw_transpose_row<STRIDE>(rb, n1);
+            dw_transpose_row<STRIDE>(rc, n2);
+            dw_issue_row<STRIDE>(n1, colp, row_pitch, cin, h, iy + 3, colmask, zaw);
+            dw_issue_row<STRIDE>(n2, colp, row_pitch, cin, h, iy + 4, colmask, zaw);
+            emit(ra, rb, rc);
+            if (oy + 1 < oy1) {
+                dw_transpose_row<STRIDE>(rb, n1);
+                dw_transpose_row<STRIDE>(ra, n2);
+                dw_issue_row<STRIDE>(n1, colp, row_pitch, cin, h, iy + 5, colmask, zaw);
+                dw_issue_row<STRIDE>(n2, colp, row_pitch, cin, h, iy + 6, colmask, zaw);
+                emit(rc, rb, ra);
+            }
+        }
+    }
+}
+
+bool dw3x3_eligible(const ConvGeom &g) {
+    return g.kh == 3 && g.kw == 3 && g.dh == 1 && g.dw == 1 && g.groups == 1 && g.sh == g.sw && (g.sh == 1 || g.sh == 2) &&
+           (g.cin % 4) == 0 && !g.a_signed;
+}
+
+cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, const void *w_packed, const void *in, void *out,
+                         int sm_count, cudaStream_t s) {
+    const int nstrip = (g.ow + 3) / 4;
+    const int cqn = g.cin / 4;
+    // Rows per thread: as tall as possible while the grid still fills the machine several times over.
+    const int64_t want_threads = static_cast<int64_t>(sm_count) * 512 * 2;
+    int th = g.oh;
+    while (th > 8 && static_cast<int64_t>(g.n) * ((g.oh + th - 1) / th) * nstrip * cqn < want_threads) th = (th + 1) / 2;
+    if (const char *ev = getenv("ENN_B200_DW_TH")) th = atoi(ev) > 0 ? atoi(ev) : th;   // tuning override
+    const int nyt = (g.oh + th - 1) / th;
+    const int64_t total = static_cast<int64_t>(g.n) * nyt * nstrip * cqn;
+    if (total == 0) return cudaSuccess;
+    const int threads = 256;
+    const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
+    const DwChan *c = static_cast<const DwChan *>(chan);
+    const uint32_t *w = static_cast<const uint32_t *>(w_packed);
+    const uint8_t *i = static_cast<const uint8_t *>(in);
+    uint8_t *o = static_cast<uint8_t *>(out);
+    const bool need_asum = g.w_zp != 0;
+#define ENN_DW_LAUNCH(ST, WS, AS) dw3x3_kernel<ST, WS, AS><<<blocks, threads, 0, s>>>(g, c, w, i, o, th, nyt, nstrip, total)
+    if (g.sh == 1) {
+        if (g.w_signed) { if (need_asum) ENN_DW_LAUNCH(1, true, true); else ENN_DW_LAUNCH(1, true, false); }
+        else            { if (need_asum) ENN_DW_LAUNCH(1, false, true); else ENN_DW_LAUNCH(1, false, false); }
+    } else {
+        if (g.w_signed) { if (need_asum) ENN_DW_LAUNCH(2, true, true); else ENN_DW_LAUNCH(2, true, false); }
+        else            { if (need_asum) ENN_DW_LAUNCH(2, false, true); else ENN_DW_LAUNCH(2, false, false); }
+    }
+#undef ENN_DW_LAUNCH
+    return cudaGetLastError();
 }
 
 cudaError_t launch_depthwise(const ConvGeom &g, const Requant &rq, const void *in, const void *w, void *out,

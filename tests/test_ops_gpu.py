@@ -95,6 +95,14 @@ DW_CASES = {
     "c960_7x7": dict(n=2, h=7, w=7, c=960),
     "signed": dict(n=1, h=9, w=9, c=8, act_dtype=cases.enn.S8, in_zp=-5, out_zp=-128),
     "tiny": dict(n=1, h=1, w=1, c=4),
+    "per_tensor_s2": dict(n=2, h=15, w=13, c=12, stride=2, per_channel=False, out_scale=0.08, out_zp=3),
+    "s2_even": dict(n=1, h=16, w=16, c=8, stride=2),
+    "ragged_rows": dict(n=3, h=10, w=6, c=4),
+    "single_row": dict(n=1, h=1, w=9, c=8),
+    "single_col": dict(n=1, h=9, w=1, c=8, stride=2),
+    "relu": dict(n=1, h=8, w=8, c=8, act=cases.enn.ACT_RELU, out_zp=20),
+    "none_act_zp128": dict(n=1, h=8, w=11, c=16, act=cases.enn.ACT_NONE, out_zp=128, out_scale=0.1),
+    "tall": dict(n=1, h=70, w=5, c=4),
 }
 
 
@@ -104,7 +112,9 @@ def test_depthwise_parity(enn, orc, ctx, name):
     y_ref = orc.depthwise(d, x, w, b, sc)
     op = enn.depthwise(ctx, d, w, b, sc)
     try:
-        _check(op, y_ref, x)
+        for impl in (enn.IMPL_DEPTHWISE, enn.IMPL_DIRECT):     # 3x3 fast path (when eligible) and general kernel
+            op.set_impl(impl)
+            _check(op, y_ref, x)
     finally:
         op.release()
 
