@@ -104,6 +104,7 @@ PROTOTYPES = {
     "enn_b200_conv_multiplier": (C.c_int32, [C.c_double, C.c_double, C.c_double, C.c_double, C.POINTER(C.c_double)]),
     "enn_b200_activation_range": (None, [C.c_int32, C.c_int32, C.c_float, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "enn_b200_requant_host": (C.c_int32, [C.c_int32] * 6),
+    "enn_b200_measure_mma_peak": (C.c_int32, [_P, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_double)]),
     "enn_b200_version": (C.c_char_p, []),
 }
 
@@ -188,6 +189,12 @@ class Context:
     @property
     def stream(self):
         return lib.enn_b200_stream(self.h)
+
+    def mma_peak(self, kind=0, n=256, iters=4096):
+        """Measured tcgen05.mma rate in tera-ops/s (kind 0: int8, kind 1: bf16)."""
+        v = C.c_double()
+        self.check(lib.enn_b200_measure_mma_peak(self.h, kind, n, iters, C.byref(v)))
+        return v.value
 
     def close(self):
         if self.h:

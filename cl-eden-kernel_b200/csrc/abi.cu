@@ -90,6 +90,8 @@ void fill_info(enn_b200_op *op, int64_t in_elems, int64_t out_elems, int64_t mac
 }  // namespace
 
 namespace enn_b200 {
+// mma_peak.cu
+double measure_mma_peak(enn_b200_context *ctx, int kind, int n, int iters);
 // gemm_tc.cu
 int32_t tc_plan_conv(enn_b200_op *op, const void *weights_hwio_host);
 int32_t tc_execute(enn_b200_op *op, const void *in, void *out);
@@ -201,6 +203,14 @@ int32_t enn_b200_conv_multiplier(double in_scale, double w_scale, double bias_sc
 void enn_b200_activation_range(int32_t activation, int32_t act_dtype, float scale, int32_t zero_point, int32_t *act_min,
                                int32_t *act_max) {
     activation_range(activation, act_dtype, scale, zero_point, act_min, act_max);
+}
+
+int32_t enn_b200_measure_mma_peak(enn_b200_context *ctx, int32_t kind, int32_t n, int32_t iters, double *tera_ops) {
+    if (!ctx || !tera_ops) return ENN_B200_INVALID_PARAMS;
+    const double v = measure_mma_peak(ctx, kind, n, iters);
+    if (v < 0) return fail(ctx, ENN_B200_FAILURE, "tensor-pipe peak measurement failed");
+    *tera_ops = v;
+    return ENN_B200_SUCCESS;
 }
 
 int32_t enn_b200_requant_host(int32_t acc, int32_t mult, int32_t shift, int32_t out_zp, int32_t act_min, int32_t act_max) {

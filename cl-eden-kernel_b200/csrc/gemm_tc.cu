@@ -1,15 +1,590 @@
-// Tensor-core implicit GEMM (TMA + tcgen05.mma kind::i8).  Placeholder plan: no geometry accepted yet.
+// Tensor-core path for the dense contractions (Conv2D, FullyConnected, Deconvolution):
+// TMA -> 128B-swizzled shared memory -> tcgen05.mma kind::i8 (int32 accumulators in TMEM) -> tcgen05.ld ->
+// fused bias / zero-point / fixed-point requantisation / clamp epilogue -> NHWC bytes.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer (one lane)
+//   warp 1      TMEM allocation, MMA issue (one lane)
+//   warps 2..5  epilogue: each thread owns one accumulator row (= one output pixel)
+// Two accumulator buffers in TMEM let the epilogue of tile i overlap the MMAs of tile i+1.
+//
+// Value computed (ConvolutionKernels.cpp:956-1274 / :1317-1375): for output row m, column n
+//   acc = sum_k (a[m][k] - za) (w[n][k] - zw) + bias[n]
+// evaluated as  sum_k a*w'  -  zw' * sum_k a  +  bias'[n]   with w' = w - 128 for u8 weights (always fits int8),
+// zw' = zw - 128 (0 for per-channel int8 filters) and bias'[n] = bias[n] - za * sum_k w'[n][k] + K za zw'.
+// sum_k a comes out of the same MMA as one extra all-ones weight row per N tile (only when zw' != 0).
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit failed polls the thread records an error code in
+// host-visible memory, raises a CTA-wide abort flag and every role falls through to the common exit, where
+// TMEM is released.
+#include <cuda.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
 #include "internal.h"
+#include "requant.h"
 
 namespace enn_b200 {
-bool tc_available(const enn_b200_context *ctx) { return false && ctx != nullptr; }
-int32_t tc_plan_conv(enn_b200_op *op, const void *weights_hwio_host) {
-    (void)op; (void)weights_hwio_host;
-    return ENN_B200_INVALID_PARAMS;
+
+bool tc_available(const enn_b200_context *ctx);
+int32_t tc_plan_conv(enn_b200_op *op, const void *weights_hwio_host);
+int32_t tc_execute(enn_b200_op *op, const void *in, void *out);
+void tc_release(enn_b200_op *op);
+
+namespace {
+
+constexpr int kBM = 128;            // rows per tile = UMMA M
+constexpr int kBK = 128;            // bytes of K per stage = one 128B swizzle atom = 4 UMMA K steps
+constexpr int kMaxBN = 256;         // UMMA N limit
+constexpr int kThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+struct ColParam {   // per output column, 16 bytes
+    int32_t mult;
+    int32_t addend;   // stage-2 addend: 2^(e-1) + ((out_zp - act_min) << e)
+    int32_t esh;      // e | sign-shift << 8 (31 when e > 0 else 32); bit 31 set: use the general requantisation
+    int32_t bias;     // folded bias'
+};
+
+struct TcParams {
+    int32_t M, N, K;
+    int32_t tiles_m, tiles_n, k_blocks;
+    int32_t bn_rows;        // B rows per N tile in shared memory (= UMMA N), multiple of 16
+    int32_t bn_data;        // real output columns per N tile
+    int32_t stages;
+    int32_t need_asum;      // 1: column bn_data of each accumulator tile holds sum_k a
+    int32_t zw_eff;         // zw'
+    int32_t a_signed;
+    int32_t act_min, act_max, out_zp;
+    int32_t general;        // 1: some column needs the general (left shift / wide) requantisation
+    uint32_t idesc;
+    const ColParam *cols;   // [tiles_n][bn_rows]
+    uint8_t *out;           // [M][N]
+    int32_t *err;           // host-mapped error word
+    long long *dbg;         // optional per-CTA cycle counters [grid][8] (null in normal use)
+    int32_t dbg_mode;       // development switches (0 in normal use)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false after the limit (or when another thread already aborted the CTA).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *err, int code) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (err) *reinterpret_cast<volatile int32_t *>(err) = code;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t c0, int32_t c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_x1(uint32_t taddr, uint32_t &r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile in shared memory, 128-byte rows, 128B swizzle: rows are 128 bytes apart, groups of 8
+// rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);        // start address, 16-byte units
+    d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (unused for swizzled K-major)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset
+    d |= static_cast<uint64_t>(1) << 46;                            // descriptor version
+    d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ uint32_t pack_sat_u8_tc(int32_t hi, int32_t lo, uint32_t upper) {
+    uint32_t d;
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(upper));
+    return d;
+}
+__device__ __forceinline__ uint32_t shr_clamp_tc(uint32_t a, uint32_t s) {
+    uint32_t d;
+    asm("shr.u32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(s));
+    return d;
+}
+
+// Requantise one accumulator to (value - act_min) in [0, act_max - act_min].
+__device__ __forceinline__ int32_t tc_requant(int32_t acc, const ColParam &c, int32_t hi_clamp, bool general, int32_t out_zp,
+                                              int32_t act_min, int32_t act_max) {
+    if (general && c.esh < 0) {
+        // Left shift or accumulator range too wide for the fused form: shift is stored in `addend`.
+        return enn_requant(acc, c.mult, c.addend, out_zp, act_min, act_max) - act_min;
+    }
+    const int64_t p = static_cast<int64_t>(acc) * c.mult + (1ll << 30);
+    const int32_t x = static_cast<int32_t>(p >> 31);
+    const int32_t v = (x + c.addend - static_cast<int32_t>(shr_clamp_tc(static_cast<uint32_t>(x), (c.esh >> 8) & 0xff))) >> (c.esh & 0xff);
+    return __vimin_s32_relu(v, hi_clamp);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment for the swizzled tiles.
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const uint32_t a_bytes = kBM * kBK;
+    const uint32_t b_bytes = static_cast<uint32_t>(p.bn_rows) * kBK;
+    const uint32_t stage_bytes = a_bytes + b_bytes;     // both multiples of 1024
+    uint8_t *tiles = smem;
+    // Per-epilogue-warp copies of the N tile's column constants (4 x 256 x 16 bytes): private to a warp, so
+    // refreshing them needs only a warp-level sync.
+    int4 *s_cols = reinterpret_cast<int4 *>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_cols + 4 * kMaxBN);
+    // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * p.stages + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + p.stages);
+    const uint32_t tfull0 = smem_u32(bars + 2 * p.stages), tempty0 = smem_u32(bars + 2 * p.stages + 2);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tfull0 + 8 * b, 1);
+            mbar_init(tempty0 + 8 * b, 4);      // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = p.tiles_m * p.tiles_n;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            long long t_wait = 0, t_begin = clock64();
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    const long long t0 = clock64();
+                    if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.err, 1)) { ok = false; break; }
+                    t_wait += clock64() - t0;
+                    const uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
+                    mbar_expect_tx(full0 + 8 * stage, stage_bytes);
+                    tma_load_2d(sa, &map_a, full0 + 8 * stage, kb * kBK, tm * kBM);
+                    tma_load_2d(sa + a_bytes, &map_b, full0 + 8 * stage, kb * kBK, tn * p.bn_rows);
+                    if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (p.dbg) { p.dbg[blockIdx.x * 8 + 0] = t_wait; p.dbg[blockIdx.x * 8 + 1] = clock64() - t_begin; }
+            if (!ok) {
+                // Give copies already in flight a bounded chance to land before shared memory is released.
+                for (int s = 0; s < p.stages; ++s)
+                    for (uint32_t i = 0; i < (1u << 16); ++i)
+                        if (mbar_try_wait(full0 + 8 * s, 0) || mbar_try_wait(full0 + 8 * s, 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            uint32_t it = 0;
+            bool ok = true;
+            long long t_full = 0, t_tempty = 0, t_begin = clock64();
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+                const uint32_t ab = it & 1, use = it >> 1;
+                // wait until the epilogue has drained this accumulator buffer
+                const long long t0 = clock64();
+                if (!mbar_wait(tempty0 + 8 * ab, (use & 1) ^ 1, abort_flag, p.err, 2)) { ok = false; break; }
+                t_tempty += clock64() - t0;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + ab * kMaxBN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    const long long t1 = clock64();
+                    if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.err, 3)) { ok = false; break; }
+                    t_full += clock64() - t1;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
+                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + a_bytes);
+                    const int ksteps = min(4, (p.K - kb * kBK + 31) >> 5);
+                    for (int k = 0; k < ksteps; ++k)
+                        umma_i8(d_tmem, da + 2 * k, db + 2 * k, p.idesc, (kb | k) != 0);
+                    umma_commit(empty0 + 8 * stage);      // frees the stage when these MMAs have read it
+                    if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(tfull0 + 8 * ab);     // accumulator complete
+            }
+            if (p.dbg) { p.dbg[blockIdx.x * 8 + 2] = t_full; p.dbg[blockIdx.x * 8 + 3] = t_tempty; p.dbg[blockIdx.x * 8 + 4] = clock64() - t_begin; }
+        }
+    } else {
+        // ---------------- epilogue: 4 warps, thread = accumulator row ----------------
+        const int q = warp & 3;                            // TMEM lane group this warp may access
+        const int row_in_tile = q * 32 + lane;
+        const int32_t hi_clamp = p.act_max - p.act_min;
+        const uint32_t lo_word = (static_cast<uint32_t>(p.act_min) & 0xff) * 0x01010101u;
+        const bool vec16 = (p.N & 15) == 0;
+        uint32_t it = 0;
+        bool ok = true;
+        int loaded_tn = -1;
+        long long t_tfull = 0, t_begin = clock64();
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            const uint32_t ab = it & 1, use = it >> 1;
+            const long long t0 = clock64();
+            int4 *my_cols = s_cols + q * kMaxBN;
+            if (tn != loaded_tn) {
+                const int4 *src = reinterpret_cast<const int4 *>(p.cols + static_cast<size_t>(tn) * p.bn_rows);
+                __syncwarp();
+                for (int i = lane; i < p.bn_rows; i += 32) my_cols[i] = __ldg(src + i);
+                __syncwarp();
+                loaded_tn = tn;
+            }
+            if (!mbar_wait(tfull0 + 8 * ab, use & 1, abort_flag, p.err, 4)) { ok = false; break; }
+            t_tfull += clock64() - t0;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ab * kMaxBN + (static_cast<uint32_t>(q * 32) << 16);
+            const int m = tm * kBM + row_in_tile;
+            int32_t asum_term = 0;
+            if (p.need_asum) {
+                uint32_t rs;
+                tmem_ld_x1(t_row + p.bn_data, rs);
+                tmem_ld_wait();
+                asum_term = p.zw_eff * static_cast<int32_t>(rs);
+            }
+            const int n_base = tn * p.bn_data;
+            const int n_cols = min(p.bn_data, p.N - n_base);
+            uint8_t *orow = p.out + static_cast<size_t>(m) * p.N + n_base;
+            for (int c0 = 0; c0 < n_cols; c0 += 16) {
+                uint32_t r[16];
+                if (!(p.dbg_mode & 4)) {
+                tmem_ld_x16(t_row + c0, r);                 // warp-collective: executed by all lanes
+                tmem_ld_wait();
+                } else { for (int i = 0; i < 16; ++i) r[i] = c0 + i; }
+                if (m < p.M) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        int32_t y[4];
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {
+                            const int4 cv = my_cols[c0 + j * 4 + b];
+                            const ColParam cp = {cv.x, cv.y, cv.z, cv.w};
+                            const int32_t acc = static_cast<int32_t>(r[j * 4 + b]) - asum_term + cp.bias;
+                            y[b] = tc_requant(acc, cp, hi_clamp, p.general != 0, p.out_zp, p.act_min, p.act_max);
+                        }
+                        const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
+                        w[j] = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
+                    }
+                    const int left = n_cols - c0;
+                    if (p.dbg_mode & 1) { if (w[0] + w[1] + w[2] + w[3] == 0x12345) orow[0] = 1; } else
+                    if (vec16 && left >= 16) {
+                        *reinterpret_cast<uint4 *>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                    } else {
+                        for (int b = 0; b < 16 && b < left; ++b) orow[c0 + b] = static_cast<uint8_t>(w[b >> 2] >> (8 * (b & 3)));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * ab);
+        }
+        if (p.dbg && threadIdx.x == 64) { p.dbg[blockIdx.x * 8 + 5] = t_tfull; p.dbg[blockIdx.x * 8 + 6] = clock64() - t_begin; }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct TcPlan {
+    TcParams prm{};
+    CUtensorMap map_b{};
+    CUtensorMap map_a{};
+    const void *map_a_ptr = nullptr;   // input pointer map_a was encoded for
+    void *w_dev = nullptr;
+    void *cols_dev = nullptr;
+    int32_t *err_host = nullptr;       // pinned + mapped
+    int32_t *err_dev = nullptr;
+    size_t smem_bytes = 0;
+    int grid = 0;
+};
+
+bool encode_2d(enn_b200_context *ctx, CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint64_t pitch,
+               uint32_t box_inner, uint32_t box_outer) {
+    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    if (!fn) return false;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {pitch};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool tc_available(const enn_b200_context *ctx) { return ctx && ctx->cc_major == 10 && ctx->encode_tiled != nullptr; }
+
+// Plans the tensor-core kernel for a 1x1 / FullyConnected contraction.  `w_hwio` is the host copy of the
+// weights in [Kh][Kw][Cin/g][Cout] order (raw bytes).  Returns INVALID_PARAMS when the geometry is not one
+// this kernel tiles (the caller keeps the direct kernel).
+int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
+    const ConvGeom &g = op->g;
+    enn_b200_context *ctx = op->ctx;
+    if (op->kind == OP_DECONV) return ENN_B200_INVALID_PARAMS;
+    if (!(g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.groups == 1 && g.pt == 0 && g.pl == 0)) return ENN_B200_INVALID_PARAMS;
+    if (g.oh != g.h || g.ow != g.w) return ENN_B200_INVALID_PARAMS;
+    const int64_t M64 = static_cast<int64_t>(g.n) * g.h * g.w;
+    const int32_t K = g.cin, N = g.cout;
+    if ((K & 15) != 0 || M64 <= 0 || M64 > INT32_MAX) return ENN_B200_INVALID_PARAMS;   // TMA: 16-byte row pitch
+    const int32_t M = static_cast<int32_t>(M64);
+
+    TcPlan *plan = new (std::nothrow) TcPlan();
+    if (!plan) return ENN_B200_FAILURE;
+    TcParams &p = plan->prm;
+    p.M = M; p.N = N; p.K = K;
+    // Weights as signed bytes: int8 stays, u8 becomes w - 128.
+    const int32_t zw_eff = g.w_signed ? g.w_zp : g.w_zp - 128;
+    p.zw_eff = zw_eff;
+    p.need_asum = zw_eff != 0;
+    p.a_signed = g.a_signed;
+    p.act_min = g.act_min; p.act_max = g.act_max; p.out_zp = g.out_zp;
+    const int32_t extra = p.need_asum ? 16 : 0;
+    int32_t max_data = kMaxBN - extra;
+    if (const char *ev = getenv("ENN_B200_TC_BN")) max_data = atoi(ev) >= 16 && atoi(ev) <= max_data ? (atoi(ev) & ~15) : max_data;   // tuning override
+    p.tiles_m = (M + kBM - 1) / kBM;
+    // N tiling: as few tiles as possible, but split further while the grid would leave SMs idle.
+    int32_t tiles_n = (N + max_data - 1) / max_data;
+    while (static_cast<int64_t>(p.tiles_m) * tiles_n < ctx->sm_count && (N + tiles_n) / (tiles_n + 1) >= 32) ++tiles_n;
+    int32_t bn_data = (((N + tiles_n - 1) / tiles_n) + 15) & ~15;
+    tiles_n = (N + bn_data - 1) / bn_data;
+    p.tiles_n = tiles_n;
+    p.bn_data = bn_data;
+    p.bn_rows = bn_data + extra;
+    p.k_blocks = (K + kBK - 1) / kBK;
+    const int32_t k_pad = p.k_blocks * kBK;
+    p.idesc = (2u << 4) | (static_cast<uint32_t>(g.a_signed ? 1 : 0) << 7) | (1u << 10) |
+              (static_cast<uint32_t>(p.bn_rows >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+
+    // Packed B: [tiles_n][bn_rows][k_pad] int8, zero padded; row bn_data of each tile is all ones (sum_k a).
+    const uint8_t *w = static_cast<const uint8_t *>(w_hwio);   // [K][N] for 1x1
+    std::vector<int8_t> wb(static_cast<size_t>(tiles_n) * p.bn_rows * k_pad, 0);
+    std::vector<int32_t> mult, shift;
+    std::vector<ColParam> cols(static_cast<size_t>(tiles_n) * p.bn_rows);
+    std::memset(cols.data(), 0, cols.size() * sizeof(ColParam));
+    // requant vectors were uploaded by setup_quant; re-derive them here from the device copies' host twins
+    mult.resize(N); shift.resize(N);
+    std::vector<int32_t> bias(N);
+    cudaMemcpy(mult.data(), op->rq.mult, sizeof(int32_t) * N, cudaMemcpyDeviceToHost);
+    cudaMemcpy(shift.data(), op->rq.shift, sizeof(int32_t) * N, cudaMemcpyDeviceToHost);
+    cudaMemcpy(bias.data(), op->rq.bias, sizeof(int32_t) * N, cudaMemcpyDeviceToHost);
+    p.general = 0;
+    const int64_t amax = g.a_signed ? 128 : 255;
+    for (int32_t n = 0; n < N; ++n) {
+        const int32_t tn = n / bn_data, r = n % bn_data;
+        int8_t *dst = wb.data() + (static_cast<size_t>(tn) * p.bn_rows + r) * k_pad;
+        int64_t wsum = 0, wabs = 0;
+        for (int32_t k = 0; k < K; ++k) {
+            const uint8_t raw = w[static_cast<size_t>(k) * N + n];
+            const int32_t wv = g.w_signed ? static_cast<int32_t>(static_cast<int8_t>(raw)) : static_cast<int32_t>(raw) - 128;
+            dst[k] = static_cast<int8_t>(wv);
+            wsum += wv;
+            wabs += wv < 0 ? -wv : wv;
+        }
+        const int64_t folded = static_cast<int64_t>(bias[n]) - static_cast<int64_t>(g.in_zp) * wsum +
+                               static_cast<int64_t>(K) * g.in_zp * zw_eff;
+        ColParam &c = cols[static_cast<size_t>(tn) * p.bn_rows + r];
+        c.mult = mult[n];
+        c.bias = static_cast<int32_t>(folded);     // wraps like the reference's int32 accumulation
+        const int32_t e = shift[n] > 0 ? -1 : -shift[n];
+        const int64_t zo_eff = static_cast<int64_t>(g.out_zp) - g.act_min;
+        const int64_t addend = e > 0 ? (1ll << (e - 1)) + zo_eff * (1ll << e) : zo_eff;
+        const int64_t acc_bound = amax * wabs + static_cast<int64_t>(K) * amax * (zw_eff < 0 ? -zw_eff : zw_eff) +
+                                  (folded < 0 ? -folded : folded);
+        if (e < 0 || folded > INT32_MAX || folded < INT32_MIN || acc_bound + 2 + (addend < 0 ? -addend : addend) >= (1ll << 31)) {
+            c.addend = shift[n];                   // general path keeps the raw signed shift
+            c.esh = INT32_MIN;
+            p.general = 1;
+        } else {
+            c.addend = static_cast<int32_t>(addend);
+            c.esh = e | ((e > 0 ? 31 : 32) << 8);
+        }
+    }
+    if (p.need_asum)
+        for (int32_t tn = 0; tn < tiles_n; ++tn) {
+            int8_t *dst = wb.data() + (static_cast<size_t>(tn) * p.bn_rows + bn_data) * k_pad;
+            for (int32_t k = 0; k < K; ++k) dst[k] = 1;
+        }
+
+    cudaError_t e;
+    if ((e = cudaMalloc(&plan->w_dev, wb.size())) != cudaSuccess || (e = cudaMalloc(&plan->cols_dev, cols.size() * sizeof(ColParam))) != cudaSuccess ||
+        (e = cudaMemcpy(plan->w_dev, wb.data(), wb.size(), cudaMemcpyHostToDevice)) != cudaSuccess ||
+        (e = cudaMemcpy(plan->cols_dev, cols.data(), cols.size() * sizeof(ColParam), cudaMemcpyHostToDevice)) != cudaSuccess ||
+        (e = cudaHostAlloc(reinterpret_cast<void **>(&plan->err_host), sizeof(int32_t), cudaHostAllocMapped)) != cudaSuccess ||
+        (e = cudaHostGetDevicePointer(reinterpret_cast<void **>(&plan->err_dev), plan->err_host, 0)) != cudaSuccess) {
+        ctx->last_error = std::string("tensor-core plan: ") + cudaGetErrorString(e);
+        op->tc = plan;
+        tc_release(op);
+        return ENN_B200_CUDA_FAILURE;
+    }
+    *plan->err_host = 0;
+    p.cols = static_cast<const ColParam *>(plan->cols_dev);
+    p.err = plan->err_dev;
+    if (!encode_2d(ctx, &plan->map_b, plan->w_dev, k_pad, static_cast<uint64_t>(tiles_n) * p.bn_rows, k_pad, kBK, p.bn_rows)) {
+        ctx->last_error = "cuTensorMapEncodeTiled failed for the weight tensor";
+        op->tc = plan;
+        tc_release(op);
+        return ENN_B200_CUDA_FAILURE;
+    }
+    const size_t stage_bytes = static_cast<size_t>(kBM) * kBK + static_cast<size_t>(p.bn_rows) * kBK;
+    const size_t fixed = 4 * kMaxBN * sizeof(ColParam) + 256 + 1024;   // column constants, barriers, alignment slack
+    int stages = static_cast<int>((227 * 1024 - fixed) / stage_bytes);
+    if (stages > 8) stages = 8;
+    if (stages < 2) {
+        op->tc = plan;
+        tc_release(op);
+        return ENN_B200_INVALID_PARAMS;
+    }
+    p.stages = stages;
+    plan->smem_bytes = stages * stage_bytes + fixed;
+    const int total_tiles = p.tiles_m * p.tiles_n;
+    plan->grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        attr_set = true;
+    }
+    op->tc = plan;
+    return ENN_B200_SUCCESS;
+}
+
 int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
-    (void)op; (void)in; (void)out;
-    return ENN_B200_FAILURE;
+    TcPlan *plan = static_cast<TcPlan *>(op->tc);
+    enn_b200_context *ctx = op->ctx;
+    if (!plan) return ENN_B200_FAILURE;
+    if (*plan->err_host != 0) {
+        char buf[96];
+        std::snprintf(buf, sizeof(buf), "tensor-core kernel gave up on a barrier wait (code %d)", *plan->err_host);
+        ctx->last_error = buf;
+        return ENN_B200_CUDA_FAILURE;
+    }
+    TcParams &p = plan->prm;
+    if (p.M == 0) return ENN_B200_SUCCESS;
+    if ((reinterpret_cast<uintptr_t>(in) & 15) != 0) {
+        ctx->last_error = "tensor-core path needs a 16-byte aligned input pointer";
+        return ENN_B200_INVALID_PARAMS;
+    }
+    if (plan->map_a_ptr != in) {
+        if (!encode_2d(ctx, &plan->map_a, in, p.K, p.M, p.K, kBK, kBM)) {
+            ctx->last_error = "cuTensorMapEncodeTiled failed for the activation tensor";
+            return ENN_B200_CUDA_FAILURE;
+        }
+        plan->map_a_ptr = in;
+    }
+    p.out = static_cast<uint8_t *>(out);
+    static long long *dbg_buf = nullptr;
+    p.dbg_mode = getenv("ENN_B200_TC_MODE") ? atoi(getenv("ENN_B200_TC_MODE")) : 0;
+    if (getenv("ENN_B200_TC_DEBUG")) {      // development aid: per-CTA wait-cycle counters printed after the launch
+        if (!dbg_buf) cudaMallocManaged(&dbg_buf, sizeof(long long) * 8 * 1024);
+        p.dbg = dbg_buf;
+    }
+    tc_gemm_kernel<<<plan->grid, kThreads, plan->smem_bytes, ctx->stream>>>(plan->map_a, plan->map_b, p);
+    if (p.dbg) {
+        cudaStreamSynchronize(ctx->stream);
+        const long long *d = p.dbg;
+        std::printf("tc dbg cta0: producer wait %lld / %lld | mma full-wait %lld tempty-wait %lld / %lld | epi tfull-wait %lld / %lld\n",
+                    d[0], d[1], d[2], d[3], d[4], d[5], d[6]);
+        p.dbg = nullptr;
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        ctx->last_error = std::string("tc_gemm_kernel launch: ") + cudaGetErrorString(e);
+        return ENN_B200_CUDA_FAILURE;
+    }
+    return ENN_B200_SUCCESS;
 }
-void tc_release(enn_b200_op *op) { (void)op; }
+
+void tc_release(enn_b200_op *op) {
+    TcPlan *plan = static_cast<TcPlan *>(op->tc);
+    if (!plan) return;
+    if (plan->w_dev) cudaFree(plan->w_dev);
+    if (plan->cols_dev) cudaFree(plan->cols_dev);
+    if (plan->err_host) cudaFreeHost(plan->err_host);
+    delete plan;
+    op->tc = nullptr;
+}
+
 }  // namespace enn_b200

@@ -196,6 +196,12 @@ void enn_b200_activation_range(int32_t activation, int32_t act_dtype, float scal
 int32_t enn_b200_requant_host(int32_t acc, int32_t multiplier, int32_t shift, int32_t out_zp, int32_t act_min,
                               int32_t act_max);
 
+/* Measures the sustained tcgen05.mma rate of the device (no reference counterpart: it provides the measured
+ * tensor-pipe ceiling that GEMM-shaped operators are reported against).  kind 0: kind::i8 (u8 x s8 -> s32),
+ * kind 1: kind::f16 with bf16 operands.  n: MMA N (16..256, multiple of 16); iters: MMA groups of 4 per SM.
+ * Writes tera-operations (2 x MAC) per second summed over all SMs. */
+int32_t enn_b200_measure_mma_peak(enn_b200_context *ctx, int32_t kind, int32_t n, int32_t iters, double *tera_ops);
+
 /* Library identification: returns a static string naming the build (arch, version). */
 const char *enn_b200_version(void);
 

@@ -150,6 +150,11 @@ FC_CASES = {
     "ragged": dict(m=37, k=100, n=29),
     "per_tensor": dict(m=8, k=128, n=64, per_channel=False),
     "relu6": dict(m=8, k=128, n=64, act=cases.enn.ACT_RELU6),
+    "fc1000": dict(m=200, k=1280, n=1000),
+    "big_k": dict(m=130, k=4096, n=272),
+    "per_tensor_wide": dict(m=300, k=256, n=520, per_channel=False),
+    "per_tensor_zp128": dict(m=129, k=64, n=48, per_channel=False, w_zp=128),
+    "k16_n16": dict(m=1000, k=16, n=16),
 }
 
 
@@ -162,6 +167,22 @@ def test_fc_parity(enn, orc, ctx, name):
         for impl in _impls(enn, op):
             op.set_impl(impl)
             _check(op, y_ref, x)
+    finally:
+        op.release()
+
+
+def test_fc_full_size_sampled_rows(enn, orc, ctx):
+    """4096 x 4096 x 4096 (the largest benchmark GEMM): rows sampled across all M tiles against the oracle."""
+    d, x, w, b, sc = cases.fc_case(seed=5, m=4096, k=4096, n=4096)
+    op = enn.fully_connected(ctx, d, w, b, sc)
+    try:
+        y = op.run(x).reshape(4096, 4096)
+        rows = np.r_[0:4, 127:130, 2047:2050, 4092:4096, np.random.default_rng(0).integers(0, 4096, 18)]
+        ds = type(d).from_buffer_copy(d)
+        ds.m = len(rows)
+        y_ref = orc.fully_connected(ds, np.ascontiguousarray(x[rows]), w, b, sc)
+        assert np.array_equal(y[rows], y_ref)
+        assert len(np.unique(y)) > 100          # outputs are not saturated
     finally:
         op.release()
 
