@@ -98,6 +98,16 @@ PROTOTYPES = {
     "enn_b200_op_execute2": (C.c_int32, [_P, _P, _P, _P]),
     "enn_b200_op_info": (C.c_int32, [_P, C.POINTER(OpInfo)]),
     "enn_b200_op_release": (C.c_int32, [_P]),
+    "enn_b200_oplist_create": (C.c_int32, [_P, C.POINTER(_P)]),
+    "enn_b200_oplist_add_tensor": (C.c_int32, [_P, C.c_int64, C.POINTER(C.c_int32)]),
+    "enn_b200_oplist_add_op": (C.c_int32, [_P, _P, C.POINTER(C.c_int32), C.c_int32, C.c_int32]),
+    "enn_b200_oplist_set_io": (C.c_int32, [_P, C.POINTER(C.c_int32), C.c_int32, C.POINTER(C.c_int32), C.c_int32]),
+    "enn_b200_oplist_finalize": (C.c_int32, [_P]),
+    "enn_b200_oplist_execute": (C.c_int32, [_P, C.POINTER(_P), C.POINTER(_P)]),
+    "enn_b200_oplist_execute_device": (C.c_int32, [_P]),
+    "enn_b200_oplist_tensor_ptr": (C.c_int32, [_P, C.c_int32, C.POINTER(_P)]),
+    "enn_b200_oplist_stats": (C.c_int32, [_P, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "enn_b200_oplist_destroy": (C.c_int32, [_P]),
     "enn_b200_nchw_to_nhwc": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "enn_b200_nhwc_to_nchw": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "enn_b200_quantize_multiplier": (None, [C.c_double, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
@@ -285,3 +295,64 @@ def avgpool(ctx, desc):
     h = C.c_void_p()
     ctx.check(lib.enn_b200_avgpool_prepare(ctx.h, C.byref(desc), C.byref(h)))
     return Op(ctx, h)
+
+
+class OpList:
+    """Operator list with BufferTable-style tensor ids (GpuUserDriver Open/Execute/CloseSubGraph)."""
+
+    def __init__(self, ctx):
+        self.ctx = ctx
+        h = C.c_void_p()
+        ctx.check(lib.enn_b200_oplist_create(ctx.h, C.byref(h)))
+        self.h = h
+        self.n_in = self.n_out = 0
+        self.out_bytes = []
+
+    def tensor(self, nbytes):
+        tid = C.c_int32()
+        self.ctx.check(lib.enn_b200_oplist_add_tensor(self.h, int(nbytes), C.byref(tid)))
+        return tid.value
+
+    def add(self, op, in_ids, out_id):
+        ids = (C.c_int32 * len(in_ids))(*in_ids)
+        self.ctx.check(lib.enn_b200_oplist_add_op(self.h, op.h, ids, len(in_ids), out_id))
+        op.h = None        # owned by the list now
+
+    def set_io(self, inputs, outputs, out_bytes):
+        a = (C.c_int32 * len(inputs))(*inputs)
+        b = (C.c_int32 * len(outputs))(*outputs)
+        self.ctx.check(lib.enn_b200_oplist_set_io(self.h, a, len(inputs), b, len(outputs)))
+        self.n_in, self.n_out, self.out_bytes = len(inputs), len(outputs), list(out_bytes)
+
+    def finalize(self):
+        self.ctx.check(lib.enn_b200_oplist_finalize(self.h))
+
+    def execute_host_ptrs(self, in_ptrs, out_ptrs):
+        a = (C.c_void_p * len(in_ptrs))(*in_ptrs)
+        b = (C.c_void_p * len(out_ptrs))(*out_ptrs)
+        self.ctx.check(lib.enn_b200_oplist_execute(self.h, a, b))
+
+    def execute(self, inputs):
+        """inputs: list of numpy arrays; returns list of uint8 arrays (flat)."""
+        ins = [np.ascontiguousarray(x) for x in inputs]
+        outs = [np.empty(n, np.uint8) for n in self.out_bytes]
+        self.execute_host_ptrs([x.ctypes.data for x in ins], [o.ctypes.data for o in outs])
+        return outs
+
+    def execute_device(self):
+        self.ctx.check(lib.enn_b200_oplist_execute_device(self.h))
+
+    def tensor_ptr(self, tid):
+        p = C.c_void_p()
+        self.ctx.check(lib.enn_b200_oplist_tensor_ptr(self.h, tid, C.byref(p)))
+        return p
+
+    def stats(self):
+        a, b, c = C.c_int64(), C.c_int32(), C.c_int32()
+        self.ctx.check(lib.enn_b200_oplist_stats(self.h, C.byref(a), C.byref(b), C.byref(c)))
+        return {"device_bytes": a.value, "buffers": b.value, "kernel_launches": c.value}
+
+    def destroy(self):
+        if self.h:
+            lib.enn_b200_oplist_destroy(self.h)
+            self.h = None

@@ -5,7 +5,7 @@
 // One persistent CTA per SM, warp-specialised:
 //   warp 0      TMA producer (one lane)
 //   warp 1      TMEM allocation, MMA issue (one lane)
-//   warps 2..5  epilogue: each thread owns one accumulator row (= one output pixel)
+//   warps 2..17 epilogue: each thread owns one accumulator row (= one output pixel) and a quarter of its columns
 // Two accumulator buffers in TMEM let the epilogue of tile i overlap the MMAs of tile i+1.
 //
 // Value computed (ConvolutionKernels.cpp:956-1274 / :1317-1375): for output row m, column n
@@ -39,13 +39,14 @@ namespace {
 constexpr int kBM = 128;            // rows per tile = UMMA M
 constexpr int kBK = 128;            // bytes of K per stage = one 128B swizzle atom = 4 UMMA K steps
 constexpr int kMaxBN = 256;         // UMMA N limit
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 16;         // epilogue warps: 4 per TMEM lane quarter, splitting the columns
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 struct ColParam {   // per output column, 16 bytes
     int32_t mult;
     int32_t addend;   // stage-2 addend: 2^(e-1) + ((out_zp - act_min) << e)
-    int32_t esh;      // e | sign-shift << 8 (31 when e > 0 else 32); bit 31 set: use the general requantisation
+    int32_t esh;      // right shift e >= 1 of the fused form; negative: general requantisation, `addend` = raw shift
     int32_t bias;     // folded bias'
 };
 
@@ -160,25 +161,23 @@ __device__ __forceinline__ uint32_t pack_sat_u8_tc(int32_t hi, int32_t lo, uint3
     asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(upper));
     return d;
 }
-__device__ __forceinline__ uint32_t shr_clamp_tc(uint32_t a, uint32_t s) {
-    uint32_t d;
-    asm("shr.u32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(s));
-    return d;
-}
 
 // Requantise one accumulator to (value - act_min) in [0, act_max - act_min].
-__device__ __forceinline__ int32_t tc_requant(int32_t acc, const ColParam &c, int32_t hi_clamp, bool general, int32_t out_zp,
-                                              int32_t act_min, int32_t act_max) {
-    if (general && c.esh < 0) {
-        // Left shift or accumulator range too wide for the fused form: shift is stored in `addend`.
-        return enn_requant(acc, c.mult, c.addend, out_zp, act_min, act_max) - act_min;
-    }
-    const int64_t p = static_cast<int64_t>(acc) * c.mult + (1ll << 30);
+// Fast form (esh = right shift e >= 1): stage 1 is one 32x32->64 multiply-add and a funnel shift, stage 2 is
+// (x + addend - [x < 0]) >> e with addend = 2^(e-1) + ((out_zp - act_min) << e), i.e. RoundingDivideByPOT
+// (ties away from zero) with the zero point and the lower clamp folded in.  Columns that need a left shift,
+// e == 0, or whose accumulator range could overflow the fused form carry esh < 0 and take the general code.
+template <bool GENERAL>
+__device__ __forceinline__ int32_t tc_requant(int32_t acc, const int4 &c, int32_t hi_clamp, int32_t out_zp, int32_t act_min,
+                                              int32_t act_max) {
+    if (GENERAL && c.z < 0) return enn_requant(acc, c.x, c.y, out_zp, act_min, act_max) - act_min;   // c.y = raw shift
+    const int64_t p = static_cast<int64_t>(acc) * c.x + (1ll << 30);
     const int32_t x = static_cast<int32_t>(p >> 31);
-    const int32_t v = (x + c.addend - static_cast<int32_t>(shr_clamp_tc(static_cast<uint32_t>(x), (c.esh >> 8) & 0xff))) >> (c.esh & 0xff);
+    const int32_t v = (x + c.y - static_cast<int32_t>(static_cast<uint32_t>(x) >> 31)) >> c.z;
     return __vimin_s32_relu(v, hi_clamp);
 }
 
+template <bool ASUM, bool GENERAL>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -188,10 +187,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t b_bytes = static_cast<uint32_t>(p.bn_rows) * kBK;
     const uint32_t stage_bytes = a_bytes + b_bytes;     // both multiples of 1024
     uint8_t *tiles = smem;
-    // Per-epilogue-warp copies of the N tile's column constants (4 x 256 x 16 bytes): private to a warp, so
+    // Per-epilogue-warp copies of the N tile's column constants (kEpiWarps x 256 x 16 bytes): private to a warp, so
     // refreshing them needs only a warp-level sync.
     int4 *s_cols = reinterpret_cast<int4 *>(smem + static_cast<size_t>(p.stages) * stage_bytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(s_cols + 4 * kMaxBN);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_cols + kEpiWarps * (kMaxBN / (kEpiWarps / 4)));
     // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2]
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * p.stages + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -207,7 +206,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull0 + 8 * b, 1);
-            mbar_init(tempty0 + 8 * b, 4);      // one arrival per epilogue warp
+            mbar_init(tempty0 + 8 * b, kEpiWarps);      // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -280,8 +279,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (p.dbg) { p.dbg[blockIdx.x * 8 + 2] = t_full; p.dbg[blockIdx.x * 8 + 3] = t_tempty; p.dbg[blockIdx.x * 8 + 4] = clock64() - t_begin; }
         }
     } else {
-        // ---------------- epilogue: 4 warps, thread = accumulator row ----------------
+        // ---------------- epilogue: thread = accumulator row, warp = (lane quarter, column share) ----------------
         const int q = warp & 3;                            // TMEM lane group this warp may access
+        const int cgrp = (warp - 2) >> 2;                  // which share of the 16-column chunks this warp takes
+        constexpr int kColGroups = kEpiWarps / 4;
         const int row_in_tile = q * 32 + lane;
         const int32_t hi_clamp = p.act_max - p.act_min;
         const uint32_t lo_word = (static_cast<uint32_t>(p.act_min) & 0xff) * 0x01010101u;
@@ -294,11 +295,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
             const uint32_t ab = it & 1, use = it >> 1;
             const long long t0 = clock64();
-            int4 *my_cols = s_cols + q * kMaxBN;
+            // Each warp keeps only the constants of the column chunks it processes (chunk k of this warp is
+            // global chunk cgrp + k * kColGroups).
+            int4 *my_cols = s_cols + (warp - 2) * (kMaxBN / kColGroups);
             if (tn != loaded_tn) {
                 const int4 *src = reinterpret_cast<const int4 *>(p.cols + static_cast<size_t>(tn) * p.bn_rows);
                 __syncwarp();
-                for (int i = lane; i < p.bn_rows; i += 32) my_cols[i] = __ldg(src + i);
+                for (int i = lane; i < kMaxBN / kColGroups; i += 32) {
+                    const int col = ((i >> 4) * kColGroups + cgrp) * 16 + (i & 15);
+                    if (col < p.bn_rows) my_cols[i] = __ldg(src + col);
+                }
                 __syncwarp();
                 loaded_tn = tn;
             }
@@ -308,7 +314,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t t_row = tmem_base + ab * kMaxBN + (static_cast<uint32_t>(q * 32) << 16);
             const int m = tm * kBM + row_in_tile;
             int32_t asum_term = 0;
-            if (p.need_asum) {
+            if (ASUM) {
                 uint32_t rs;
                 tmem_ld_x1(t_row + p.bn_data, rs);
                 tmem_ld_wait();
@@ -317,7 +323,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int n_base = tn * p.bn_data;
             const int n_cols = min(p.bn_data, p.N - n_base);
             uint8_t *orow = p.out + static_cast<size_t>(m) * p.N + n_base;
-            for (int c0 = 0; c0 < n_cols; c0 += 16) {
+            for (int c0 = cgrp * 16, lc = 0; c0 < n_cols; c0 += 16 * kColGroups, lc += 16) {
                 uint32_t r[16];
                 if (!(p.dbg_mode & 4)) {
                 tmem_ld_x16(t_row + c0, r);                 // warp-collective: executed by all lanes
@@ -330,10 +336,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         int32_t y[4];
 #pragma unroll
                         for (int b = 0; b < 4; ++b) {
-                            const int4 cv = my_cols[c0 + j * 4 + b];
-                            const ColParam cp = {cv.x, cv.y, cv.z, cv.w};
-                            const int32_t acc = static_cast<int32_t>(r[j * 4 + b]) - asum_term + cp.bias;
-                            y[b] = tc_requant(acc, cp, hi_clamp, p.general != 0, p.out_zp, p.act_min, p.act_max);
+                            const int4 cv = my_cols[lc + j * 4 + b];
+                            int32_t acc = static_cast<int32_t>(r[j * 4 + b]) + cv.w;
+                            if (ASUM) acc -= asum_term;
+                            y[b] = tc_requant<GENERAL>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
                         }
                         const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
                         w[j] = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
@@ -343,7 +349,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (vec16 && left >= 16) {
                         *reinterpret_cast<uint4 *>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
                     } else {
-                        for (int b = 0; b < 16 && b < left; ++b) orow[c0 + b] = static_cast<uint8_t>(w[b >> 2] >> (8 * (b & 3)));
+#pragma unroll
+                        for (int b = 0; b < 16; ++b)
+                            if (b < left) orow[c0 + b] = static_cast<uint8_t>(w[b >> 2] >> (8 * (b & 3)));
                     }
                 }
             }
@@ -474,13 +482,13 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         const int64_t addend = e > 0 ? (1ll << (e - 1)) + zo_eff * (1ll << e) : zo_eff;
         const int64_t acc_bound = amax * wabs + static_cast<int64_t>(K) * amax * (zw_eff < 0 ? -zw_eff : zw_eff) +
                                   (folded < 0 ? -folded : folded);
-        if (e < 0 || folded > INT32_MAX || folded < INT32_MIN || acc_bound + 2 + (addend < 0 ? -addend : addend) >= (1ll << 31)) {
+        if (e < 1 || folded > INT32_MAX || folded < INT32_MIN || acc_bound + 2 + (addend < 0 ? -addend : addend) >= (1ll << 31)) {
             c.addend = shift[n];                   // general path keeps the raw signed shift
             c.esh = INT32_MIN;
             p.general = 1;
         } else {
             c.addend = static_cast<int32_t>(addend);
-            c.esh = e | ((e > 0 ? 31 : 32) << 8);
+            c.esh = e;
         }
     }
     if (p.need_asum)
@@ -524,7 +532,10 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
     plan->grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(tc_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(tc_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(tc_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(tc_gemm_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         attr_set = true;
     }
     op->tc = plan;
@@ -561,7 +572,13 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
         if (!dbg_buf) cudaMallocManaged(&dbg_buf, sizeof(long long) * 8 * 1024);
         p.dbg = dbg_buf;
     }
-    tc_gemm_kernel<<<plan->grid, kThreads, plan->smem_bytes, ctx->stream>>>(plan->map_a, plan->map_b, p);
+    if (p.need_asum) {
+        if (p.general) tc_gemm_kernel<true, true><<<plan->grid, kThreads, plan->smem_bytes, ctx->stream>>>(plan->map_a, plan->map_b, p);
+        else tc_gemm_kernel<true, false><<<plan->grid, kThreads, plan->smem_bytes, ctx->stream>>>(plan->map_a, plan->map_b, p);
+    } else {
+        if (p.general) tc_gemm_kernel<false, true><<<plan->grid, kThreads, plan->smem_bytes, ctx->stream>>>(plan->map_a, plan->map_b, p);
+        else tc_gemm_kernel<false, false><<<plan->grid, kThreads, plan->smem_bytes, ctx->stream>>>(plan->map_a, plan->map_b, p);
+    }
     if (p.dbg) {
         cudaStreamSynchronize(ctx->stream);
         const long long *d = p.dbg;

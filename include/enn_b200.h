@@ -177,6 +177,27 @@ int32_t enn_b200_op_execute2(enn_b200_op *op, const void *in0_dev, const void *i
 int32_t enn_b200_op_info(const enn_b200_op *op, enn_b200_op_info_t *info);
 int32_t enn_b200_op_release(enn_b200_op *op);
 
+/* ---- operator list: GpuUserDriver::OpenSubGraph / ExecuteSubGraph / CloseSubGraph (gpu_userdriver.cc) and
+ *      OperationExecutor::execute (gpu_op_executor.cc).  Tensors are numbered like BufferTable indices. ---- */
+typedef struct enn_b200_oplist enn_b200_oplist;
+int32_t enn_b200_oplist_create(enn_b200_context *ctx, enn_b200_oplist **list);
+int32_t enn_b200_oplist_add_tensor(enn_b200_oplist *list, int64_t bytes, int32_t *tensor_id);
+/* Appends a prepared operator reading tensors in_ids[0..n_in) and writing out_id; the list owns the op from here on. */
+int32_t enn_b200_oplist_add_op(enn_b200_oplist *list, enn_b200_op *op, const int32_t *in_ids, int32_t n_in, int32_t out_id);
+int32_t enn_b200_oplist_set_io(enn_b200_oplist *list, const int32_t *input_ids, int32_t n_inputs, const int32_t *output_ids,
+                               int32_t n_outputs);
+/* assignBuffers (gpu_op_constructor.cc:1839-1843, CLRuntime.cpp:34-157): liveness-based device buffer assignment,
+ * then one eager pass and capture of the operator sequence into a CUDA graph. */
+int32_t enn_b200_oplist_finalize(enn_b200_oplist *list);
+/* ExecuteSubGraph: host_inputs[i] / host_outputs[i] follow the order given to set_io; copies in, runs, copies out, blocks. */
+int32_t enn_b200_oplist_execute(enn_b200_oplist *list, const void *const *host_inputs, void *const *host_outputs);
+/* Operators only, on device-resident tensors, asynchronous on the context stream. */
+int32_t enn_b200_oplist_execute_device(enn_b200_oplist *list);
+int32_t enn_b200_oplist_tensor_ptr(enn_b200_oplist *list, int32_t tensor_id, void **dev_ptr);
+int32_t enn_b200_oplist_stats(enn_b200_oplist *list, int64_t *device_bytes, int32_t *n_buffers, int32_t *kernel_launches);
+/* CloseSubGraph: releases the operators, the buffers and the graph. */
+int32_t enn_b200_oplist_destroy(enn_b200_oplist *list);
+
 /* Layout converters for NCHW models (CLRuntime.cpp:1477-1620 NHWC2NCHW_* / NCHW2NHWC_*), 1-byte elements. */
 int32_t enn_b200_nchw_to_nhwc(enn_b200_context *ctx, const void *src_dev, void *dst_dev, int32_t n, int32_t c,
                               int32_t h, int32_t w);

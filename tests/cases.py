@@ -106,7 +106,7 @@ def fc_out_scale(k, in_scale=0.02, w_scale_typ=0.01):
 
 
 def fc_case(seed=0, m=4, k=256, n=64, per_channel=True, act=enn.ACT_NONE, in_scale=0.02, in_zp=128, out_zp=128,
-            w_scale=0.01, w_zp=0):
+            w_scale=0.01, w_zp=0, out_scale=None):
     rng = np.random.default_rng(seed)
     x = rng.integers(0, 256, (m, k), dtype=np.int64).astype(np.uint8)
     if per_channel:
@@ -118,6 +118,6 @@ def fc_case(seed=0, m=4, k=256, n=64, per_channel=True, act=enn.ACT_NONE, in_sca
     scales = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), n)).astype(np.float32) if per_channel else None
     d = enn.FcDesc(m=m, k=k, n=n, activation=act, act_dtype=enn.U8, weight_dtype=enn.S8 if per_channel else enn.U8,
                    per_channel=int(per_channel), in_scale=in_scale, in_zp=in_zp, w_scale=w_scale, w_zp=w_zp,
-                   bias_scale=float(np.float32(in_scale) * np.float32(w_scale)), out_scale=fc_out_scale(k),
+                   bias_scale=float(np.float32(in_scale) * np.float32(w_scale)), out_scale=out_scale or fc_out_scale(k),
                    out_zp=out_zp)
     return d, x, wt, bias, scales

@@ -155,6 +155,9 @@ FC_CASES = {
     "per_tensor_wide": dict(m=300, k=256, n=520, per_channel=False),
     "per_tensor_zp128": dict(m=129, k=64, n=48, per_channel=False, w_zp=128),
     "k16_n16": dict(m=1000, k=16, n=16),
+    "mixed_shift": dict(m=150, k=64, n=80, out_scale=0.0015),      # multipliers 0.013 .. 1.33: e >= 1, e == 0 and left shifts
+    "mixed_shift_per_tensor": dict(m=150, k=32, n=40, per_channel=False, w_scale=0.05, out_scale=0.0012),
+    "n24": dict(m=300, k=96, n=24),
 }
 
 
@@ -242,3 +245,53 @@ def test_bias_scale_mismatch_gpu(enn, orc, ctx):
     y = op.run(x)
     assert np.all(y == d.out_zp)
     op.release()
+
+
+def test_oplist_mobilenet_small(enn, orc, ctx):
+    """Whole MobileNetV2-u8 graph (reduced 96x96 input) through the operator list, every layer bit-exact."""
+    import importlib
+    import mobilenet_ref
+    mn = importlib.import_module("cl_eden_kernel_b200.mobilenet")
+    layers, _ = mn.build_model(seed=3, calib_images=1, resolution=96, num_classes=100)
+    x = np.random.default_rng(7).integers(0, 256, (3, 96, 96, 3), dtype=np.int64).astype(np.uint8)
+    y_ref, acts = mobilenet_ref.run_oracle(layers, x, keep=True)
+    ol, info = mn.make_oplist(enn, ctx, layers, batch=3, resolution=96)
+    try:
+        (y,) = ol.execute([x])
+        # intermediate tensors share pooled buffers, so compare the ones still live plus the output
+        assert np.array_equal(y.reshape(y_ref.shape), y_ref)
+        (y2,) = ol.execute([x])                      # graph replay gives the same answer
+        assert np.array_equal(y, y2)
+        st = ol.stats()
+        assert st["buffers"] < len(layers)           # liveness-based reuse happened
+        assert len(np.unique(y_ref)) > 20
+    finally:
+        ol.destroy()
+
+
+def test_mobilenet_layers_individually(enn, orc, ctx):
+    """Each distinct MobileNetV2 layer shape at 224x224, batch 2, fed with the oracle's own activations."""
+    import importlib
+    import mobilenet_ref
+    mn = importlib.import_module("cl_eden_kernel_b200.mobilenet")
+    layers, _ = mn.build_model(seed=1, calib_images=1)
+    x = np.random.default_rng(8).integers(0, 256, (2, 224, 224, 3), dtype=np.int64).astype(np.uint8)
+    _, acts = mobilenet_ref.run_oracle(layers, x, keep=True)
+    for L in layers:
+        d = mn.layer_descs(enn, L, 2)
+        a = acts[L["src"]]
+        if L["kind"] == "conv":
+            op = enn.conv2d(ctx, d, L["w"], L["bias"], L["scales"])
+        elif L["kind"] == "dw":
+            op = enn.depthwise(ctx, d, L["w"], L["bias"], L["scales"])
+        elif L["kind"] == "fc":
+            op = enn.fully_connected(ctx, d, L["w"].reshape(L["cout"], L["cin"]), L["bias"], L["scales"])
+        elif L["kind"] == "add":
+            op = enn.add(ctx, d)
+        else:
+            op = enn.avgpool(ctx, d)
+        try:
+            y = op.run(a, acts[L["src2"]] if L["kind"] == "add" else None)
+            assert np.array_equal(y, acts[L["name"]].reshape(-1)), L["name"]
+        finally:
+            op.release()
