@@ -4,13 +4,19 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of seeded synthetic
-input.  `value` is measured with inputs already resident in HBM (CUDA events on the library's stream);
-`e2e` is the same metric through the C ABI with HOST buffers, host<->device copies inside the timed region.
-`--impl reference` times the CPU oracle (the reference has no CPU implementation of these operators and
-its OpenCL path cannot run on this machine) on a bounded sample of the same workload.
+input.  The default workload is the whole MobileNetV2-1.0 224x224 uint8 graph at batch 256 per GPU
+(metric: images/s, summed over GPUs; every rank runs its own 256 images, no collective on the data path).
+Single-operator workloads (--workload depthwise3x3_s1 ... ) report HBM GB/s or int8 TOPS of that operator.
+
+`value` is measured with inputs resident in HBM (CUDA events on the library's stream); `e2e` is the same
+metric through the operator-list C ABI with HOST buffers: host->device copy of the batch, the graph, and the
+device->host copy of the result inside the timed region.  `--impl reference` times the CPU oracle (the
+reference has no CPU implementation of these operators and its OpenCL path cannot run on this machine) on a
+bounded sample of the same workload, with all host threads.
 """
 import argparse
 import ctypes as C
+import importlib
 import importlib.util
 import json
 import os
@@ -24,6 +30,8 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+DEFAULT_WORKLOAD = "mobilenetv2_u8_b256"
 
 
 def load_package():
@@ -61,7 +69,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except OSError:
@@ -74,7 +82,7 @@ class ClockSampler:
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -97,36 +105,216 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# ---------------------------------------------------------------------------------------------------
-# Workloads
-# ---------------------------------------------------------------------------------------------------
-def make_workload(name, enn):
-    """Returns dict(desc tuple, prepare fn, oracle fn name, per-step units) for a named configuration."""
-    import cases
-    if name == "depthwise3x3_s1_64x112x112x32":
-        d, x, w, b, sc = cases.depthwise_case(seed=0, n=64, h=112, w=112, c=32, stride=1)
-        return dict(kind="depthwise", args=(d, x, w, b, sc), prepare=enn.depthwise, oracle="depthwise")
-    if name == "depthwise3x3_s2_64x112x112x32":
-        d, x, w, b, sc = cases.depthwise_case(seed=0, n=64, h=112, w=112, c=32, stride=2)
-        return dict(kind="depthwise", args=(d, x, w, b, sc), prepare=enn.depthwise, oracle="depthwise")
-    raise SystemExit(f"unknown workload {name}")
+class Cuda:
+    """The few runtime calls the benchmark needs on the library's own stream (events, memset)."""
+
+    def __init__(self):
+        rt = C.CDLL("libcudart.so")
+        rt.cudaEventCreate.argtypes = [C.POINTER(C.c_void_p)]
+        rt.cudaEventRecord.argtypes = [C.c_void_p, C.c_void_p]
+        rt.cudaEventSynchronize.argtypes = [C.c_void_p]
+        rt.cudaEventElapsedTime.argtypes = [C.POINTER(C.c_float), C.c_void_p, C.c_void_p]
+        rt.cudaMemsetAsync.argtypes = [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]
+        self.rt = rt
+
+    def event(self):
+        e = C.c_void_p()
+        assert self.rt.cudaEventCreate(C.byref(e)) == 0
+        return e
+
+    def record(self, e, stream):
+        assert self.rt.cudaEventRecord(e, stream) == 0
+
+    def elapsed_ms(self, e0, e1):
+        ms = C.c_float()
+        assert self.rt.cudaEventElapsedTime(C.byref(ms), e0, e1) == 0
+        return ms.value
 
 
 def dist_env():
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    return rank, world, local
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
 
 
-def flush_l2(ctx, enn, buf, nbytes):
-    """Between timed iterations: overwrite a buffer larger than L2 (126 MB) on the same stream."""
-    import torch
-    # cudaMemsetAsync through torch would use torch's stream; use a library upload-free path instead:
-    # the scratch buffer is written by a device memset issued on the library stream.
-    cudart = C.CDLL("libcudart.so")
-    cudart.cudaMemsetAsync.argtypes = [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]
-    cudart.cudaMemsetAsync(buf, 0, nbytes, ctx.stream)
+# ---------------------------------------------------------------------------------------------------
+# Single-operator configurations (BASELINE configs 1-4), timed over rotating buffer sets larger than L2
+# ---------------------------------------------------------------------------------------------------
+def op_configs(enn):
+    import cases
+    return {
+        "conv3x3_1x56x56x64": ("conv2d", lambda: cases.conv_case(seed=0), "tensor"),
+        "conv3x3_256x56x56x64": ("conv2d", lambda: cases.conv_case(seed=0, n=256), "tensor"),
+        "depthwise3x3_s1_64x112x112x32": ("depthwise", lambda: cases.depthwise_case(seed=0, n=64), "hbm"),
+        "depthwise3x3_s2_64x112x112x32": ("depthwise", lambda: cases.depthwise_case(seed=0, n=64, stride=2), "hbm"),
+        "fc_1x4096x4096": ("fully_connected", lambda: cases.fc_case(seed=0, m=1, k=4096, n=4096), "hbm"),
+        "fc_256x1024x1024": ("fully_connected", lambda: cases.fc_case(seed=0, m=256, k=1024, n=1024), "tensor"),
+        "fc_4096x4096x4096": ("fully_connected", lambda: cases.fc_case(seed=0, m=4096, k=4096, n=4096), "tensor"),
+        "deconv4x4_s2_8x64x64x128": ("deconv", lambda: cases.deconv_case(seed=0, n=8, h=64, w=64), "tensor"),
+    }
+
+
+def time_op(enn, ctx, cu, name, reps=20, warmup=3):
+    """Device-resident timing of one operator: `reps` back-to-back launches over rotating input/output
+    buffer sets whose total size exceeds twice the L2, bracketed by CUDA events."""
+    kind, mk, bound = op_configs(enn)[name]
+    d, x, w, b, sc = mk()
+    op = getattr(enn, kind)(ctx, d, w, b, sc)
+    info = op.info
+    per_set = x.nbytes + info.out_bytes
+    nsets = int(max(2, min(64, -(-(280 << 20) // per_set))))
+    xs = [ctx.to_device(x) for _ in range(nsets)]
+    ys = [ctx.malloc(max(1, info.out_bytes)) for _ in range(nsets)]
+    for i in range(warmup):
+        op.execute(xs[i % nsets], ys[i % nsets])
+    ctx.sync()
+    e0, e1 = cu.event(), cu.event()
+    cu.record(e0, ctx.stream)
+    for i in range(reps):
+        op.execute(xs[i % nsets], ys[i % nsets])
+    cu.record(e1, ctx.stream)
+    ctx.sync()
+    ms = cu.elapsed_ms(e0, e1) / reps
+    for p in xs + ys:
+        ctx.free(p)
+    res = dict(workload=name, impl=int(info.impl), bound=bound, ms=ms, launches_per_step=int(info.kernel_launches),
+               tops=2 * info.macs / (ms * 1e-3) / 1e12, gbs=info.algorithmic_bytes / (ms * 1e-3) / 1e9,
+               macs=int(info.macs), algorithmic_bytes=int(info.algorithmic_bytes), buffer_sets=nsets)
+    op.release()
+    return res, (d, x, w, b, sc, kind)
+
+
+# ---------------------------------------------------------------------------------------------------
+# MobileNetV2 graph
+# ---------------------------------------------------------------------------------------------------
+KERNEL_OF_IMPL = {0: "conv_direct_kernel", 1: "tc_gemm_kernel", 2: "gemv", 3: "dw3x3_kernel", 4: "eltwise"}
+
+
+def run_mobilenet(args, enn, ctx, cu, rank, world, local, barrier, batch=256):
+    mn = importlib.import_module("cl_eden_kernel_b200.mobilenet")
+    layers, _ = mn.build_model(seed=0, calib_images=1)
+    x = np.random.default_rng(1000 + rank).integers(0, 256, (batch, 224, 224, 3), dtype=np.int64).astype(np.uint8)
+    ol, info = mn.make_oplist(enn, ctx, layers, batch)
+    stats = ol.stats()
+    in_ptr = ol.tensor_ptr(info["tensor_ids"]["input"])
+    ctx.upload(in_ptr, x)
+    stream = ctx.stream
+
+    # ---- device-resident: K graph launches between two events ----
+    for _ in range(args.warmup):
+        ol.execute_device()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    e0, e1 = cu.event(), cu.event()
+    cu.record(e0, stream)
+    for _ in range(args.steps):
+        ol.execute_device()
+    cu.record(e1, stream)
+    barrier()
+    total_ms = cu.elapsed_ms(e0, e1)
+
+    # ---- end to end: host buffers (pinned) through enn_b200_oplist_execute ----
+    hin, hout = C.c_void_p(), C.c_void_p()
+    out_bytes = batch * layers[-1]["cout"]
+    enn.lib.enn_b200_host_alloc(x.nbytes, C.byref(hin))
+    enn.lib.enn_b200_host_alloc(out_bytes, C.byref(hout))
+    C.memmove(hin, x.ctypes.data, x.nbytes)
+    for _ in range(2):
+        ol.execute_host_ptrs([hin.value], [hout.value])
+    barrier()
+    t0 = cu.event()
+    t1 = cu.event()
+    cu.record(t0, stream)
+    for _ in range(args.steps):
+        ol.execute_host_ptrs([hin.value], [hout.value])
+    cu.record(t1, stream)
+    barrier()
+    e2e_ms = cu.elapsed_ms(t0, t1)
+    clocks = sampler.stop() if rank == 0 else None
+    logits = np.ctypeslib.as_array((C.c_uint8 * out_bytes).from_address(hout.value)).copy()
+
+    # ---- per-layer timing (rank 0): which kernel dominates, and its achieved bandwidth ----
+    per_kernel = {}
+    if rank == 0:
+        tid = info["tensor_ids"]
+        # eager per-layer timing uses fresh operator handles on private buffers (graph nodes are owned by the list)
+        for L, pl in zip(layers, info["per_layer"]):
+            d = mn.layer_descs(enn, L, batch)
+            if L["kind"] == "conv":
+                op = enn.conv2d(ctx, d, L["w"], L["bias"], L["scales"])
+            elif L["kind"] == "dw":
+                op = enn.depthwise(ctx, d, L["w"], L["bias"], L["scales"])
+            elif L["kind"] == "fc":
+                op = enn.fully_connected(ctx, d, L["w"].reshape(L["cout"], L["cin"]), L["bias"], L["scales"])
+            elif L["kind"] == "add":
+                op = enn.add(ctx, d)
+            else:
+                op = enn.avgpool(ctx, d)
+            a = ol.tensor_ptr(tid[L["src"]])
+            o = ol.tensor_ptr(tid[L["name"]])
+            b2 = ol.tensor_ptr(tid[L["src2"]]) if L["kind"] == "add" else None
+            run = (lambda: op.execute2(a, b2, o)) if b2 is not None else (lambda: op.execute(a, o))
+            run()
+            ea, eb = cu.event(), cu.event()
+            cu.record(ea, stream)
+            for _ in range(5):
+                run()
+            cu.record(eb, stream)
+            ctx.sync()
+            ms = cu.elapsed_ms(ea, eb) / 5
+            k = KERNEL_OF_IMPL.get(pl["impl"], "other")
+            acc = per_kernel.setdefault(k, dict(ms=0.0, bytes=0, macs=0, launches=0))
+            acc["ms"] += ms
+            acc["bytes"] += pl["bytes"]
+            acc["macs"] += pl["macs"]
+            acc["launches"] += pl["launches"]
+            op.release()
+    ol_info = dict(macs=info["macs"], bytes=info["bytes"], launches=info["launches"], stats=stats, layers=len(layers))
+    return dict(total_ms=total_ms, e2e_ms=e2e_ms, clocks=clocks, units_per_step=batch, h2d=int(x.nbytes), d2h=int(out_bytes),
+                per_kernel=per_kernel, info=ol_info, logits_checksum=int(logits.astype(np.int64).sum()), layers=layers, x=x)
+
+
+def cpu_baseline_mobilenet(layers, x, max_images=8):
+    """The oracle graph timed on the host cores over a bounded sample of the batch."""
+    import mobilenet_ref
+    from oracle import orc
+    xs = np.ascontiguousarray(x[:max_images])
+    mobilenet_ref.run_oracle(layers, xs[:1])
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        mobilenet_ref.run_oracle(layers, xs)
+        reps += 1
+        if time.perf_counter() - t0 > 8.0 or reps >= 10:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": len(xs) / dt, "unit": "images/s", "cores": orc.num_threads(), "kind": "port",
+            "sample": f"{len(xs)} of {x.shape[0]} images of the same MobileNetV2-u8 graph, {reps} repetitions, {dt * 1e3:.0f} ms each"}
+
+
+def cpu_baseline_op(cfg, max_seconds=8.0):
+    from oracle import orc
+    d, x, w, b, sc, kind = cfg
+    fn = getattr(orc, kind)
+    if kind == "fully_connected":
+        ns, total = min(d.m, 64), d.m
+        ds = type(d).from_buffer_copy(d)
+        ds.m = ns
+    else:
+        ns, total = min(d.n, 8), d.n
+        ds = type(d).from_buffer_copy(d)
+        ds.n = ns
+    xs = np.ascontiguousarray(x[:ns])
+    fn(ds, xs, w, b, sc)
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        fn(ds, xs, w, b, sc)
+        reps += 1
+        if time.perf_counter() - t0 > max_seconds or reps >= 20:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    return dt, ns, total, reps
 
 
 def run_ours(args):
@@ -134,37 +322,14 @@ def run_ours(args):
     import torch.distributed as dist
     enn = load_package()
     rank, world, local = dist_env()
-    if args.gpus != world and world > 1:
+    if world > 1 and args.gpus != world:
         raise SystemExit("--gpus must equal WORLD_SIZE under torchrun")
     multi = world > 1
     torch.cuda.set_device(local)
     if multi:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ctx = enn.Context(local)
-    cudart = C.CDLL("libcudart.so")
-    for fn in ("cudaEventCreate", "cudaEventRecord", "cudaEventSynchronize", "cudaEventElapsedTime", "cudaMemsetAsync"):
-        getattr(cudart, fn).restype = C.c_int
-    cudart.cudaEventCreate.argtypes = [C.POINTER(C.c_void_p)]
-    cudart.cudaEventRecord.argtypes = [C.c_void_p, C.c_void_p]
-    cudart.cudaEventSynchronize.argtypes = [C.c_void_p]
-    cudart.cudaEventElapsedTime.argtypes = [C.POINTER(C.c_float), C.c_void_p, C.c_void_p]
-    cudart.cudaMemsetAsync.argtypes = [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]
-
-    def event():
-        e = C.c_void_p()
-        assert cudart.cudaEventCreate(C.byref(e)) == 0
-        return e
-
-    wl = make_workload(args.workload, enn)
-    d, x, w, b, sc = wl["args"]
-    op = wl["prepare"](ctx, d, w, b, sc)
-    info = op.info
-    # Each rank owns its own copy of the batch (independent units, no data-path collective).
-    x_dev = ctx.to_device(x)
-    y_dev = ctx.malloc(info.out_bytes)
-    flush_bytes = 256 << 20
-    flush_buf = ctx.malloc(flush_bytes)
-    stream = ctx.stream
+    cu = Cuda()
 
     def barrier():
         ctx.sync()
@@ -173,141 +338,174 @@ def run_ours(args):
             dist.barrier()
         ctx.sync()
 
-    # ---- device-resident timing: per-step CUDA events on the library stream, L2 flushed between steps ----
-    for _ in range(args.warmup):
-        cudart.cudaMemsetAsync(flush_buf, 0, flush_bytes, stream)
-        op.execute(x_dev, y_dev)
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    barrier()
-    evs = [(event(), event()) for _ in range(args.steps)]
-    for e0, e1 in evs:
-        cudart.cudaMemsetAsync(flush_buf, 0, flush_bytes, stream)
-        cudart.cudaEventRecord(e0, stream)
-        op.execute(x_dev, y_dev)
-        cudart.cudaEventRecord(e1, stream)
-    barrier()
-    kernel_ms = []
-    for e0, e1 in evs:
-        ms = C.c_float()
-        cudart.cudaEventElapsedTime(C.byref(ms), e0, e1)
-        kernel_ms.append(ms.value)
-    total_ms = float(np.sum(kernel_ms))
-
-    # ---- end to end through the C ABI with host buffers (pinned), copies inside the timed region ----
-    hin, hout = C.c_void_p(), C.c_void_p()
-    enn.lib.enn_b200_host_alloc(x.nbytes, C.byref(hin))
-    enn.lib.enn_b200_host_alloc(info.out_bytes, C.byref(hout))
-    C.memmove(hin, x.ctypes.data, x.nbytes)
-    for _ in range(min(args.warmup, 3)):
-        enn.lib.enn_b200_upload(ctx.h, x_dev, hin, x.nbytes)
-        op.execute(x_dev, y_dev)
-        enn.lib.enn_b200_download(ctx.h, hout, y_dev, info.out_bytes)
-    barrier()
-    e0, e1 = event(), event()
-    cudart.cudaEventRecord(e0, stream)
-    for _ in range(args.steps):
-        enn.lib.enn_b200_upload(ctx.h, x_dev, hin, x.nbytes)
-        op.execute(x_dev, y_dev)
-        enn.lib.enn_b200_download(ctx.h, hout, y_dev, info.out_bytes)
-    cudart.cudaEventRecord(e1, stream)
-    barrier()
-    ms = C.c_float()
-    cudart.cudaEventElapsedTime(C.byref(ms), e0, e1)
-    e2e_ms = ms.value
-    clocks = sampler.stop() if rank == 0 else None
-
-    if multi:
-        t = torch.tensor([total_ms, e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms = t.tolist()
-
     peaks = measured_peaks()
-    units_per_step = info.algorithmic_bytes            # metric unit: GB/s of algorithmic bytes
-    value = world * units_per_step * args.steps / (total_ms * 1e-3) / 1e9
-    e2e_value = world * units_per_step * args.steps / (e2e_ms * 1e-3) / 1e9
-    avg_launch_ms = float(np.mean(kernel_ms))
-    achieved = units_per_step / (avg_launch_ms * 1e-3) / 1e9
-    result = {
-        "metric": "depthwise_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": args.workload, "l2": "flushed between steps (256 MiB memset)",
-                   "sharding": "independent replicas per rank, no collective"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                     "tops": 2 * info.macs / (avg_launch_ms * 1e-3) / 1e12},
-        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": int(x.nbytes),
-                "d2h_bytes_per_step": int(info.out_bytes)},
-        "gpu_launches": int(info.kernel_launches * args.steps),
-        "clocks": clocks,
-    }
-    if rank == 0:
-        if world == 1 and not args.skip_cpu_baseline:
-            result["cpu_baseline"] = cpu_baseline(args, wl)
+    result = None
+    if args.workload == DEFAULT_WORKLOAD:
+        r = run_mobilenet(args, enn, ctx, cu, rank, world, local, barrier)
+        total_ms, e2e_ms = r["total_ms"], r["e2e_ms"]
+        if multi:
+            t = torch.tensor([total_ms, e2e_ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            total_ms, e2e_ms = t.tolist()
+        if rank == 0:
+            units = r["units_per_step"] * world * args.steps
+            pk = r["per_kernel"]
+            dom = max(pk, key=lambda k: pk[k]["ms"]) if pk else None
+            roof = None
+            if dom:
+                launches = max(1, pk[dom]["launches"])
+                avg_ms = pk[dom]["ms"] / launches
+                ach = pk[dom]["bytes"] / (pk[dom]["ms"] * 1e-3) / 1e9
+                roof = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                        "avg_launch_ms": avg_ms, "launches_per_step": launches,
+                        "share_of_step": pk[dom]["ms"] / sum(v["ms"] for v in pk.values()),
+                        "per_kernel_ms": {k: round(v["ms"], 4) for k, v in pk.items()}}
+            result = {
+                "metric": "mobilenetv2_u8_images_per_s", "value": units / (total_ms * 1e-3), "unit": "images/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+                "config": {"workload": "MobileNetV2-1.0 224x224 uint8 graph (per-channel int8 weights), batch 256 per GPU",
+                           "l2": f"working set {r['info']['stats']['device_bytes'] >> 20} MiB of activations per step exceeds the 126 MB L2",
+                           "sharding": "each rank runs its own 256 images; no collective on the data path",
+                           "ops_per_step": r["info"]["layers"], "gmacs_per_step": r["info"]["macs"] / 1e9,
+                           "algorithmic_gbytes_per_step": r["info"]["bytes"] / 1e9},
+                "roofline": roof,
+                "e2e": {"value": units / (e2e_ms * 1e-3), "unit": "images/s", "h2d_bytes_per_step": r["h2d"],
+                        "d2h_bytes_per_step": r["d2h"]},
+                "gpu_launches": int(r["info"]["launches"] * args.steps),
+                "clocks": r["clocks"],
+                "logits_checksum": r["logits_checksum"],
+            }
+            if world == 1 and not args.skip_cpu_baseline:
+                result["cpu_baseline"] = cpu_baseline_mobilenet(r["layers"], r["x"])
+            if world == 1 and not args.skip_per_op:
+                per_op = []
+                i8_peak = ctx.mma_peak(0, 256, 8192)
+                for name in op_configs(enn):
+                    res, _ = time_op(enn, ctx, cu, name)
+                    res["frac_of_hbm_measured"] = res["gbs"] / peaks["hbm_gbs"]
+                    res["frac_of_int8_tensor_measured"] = res["tops"] / i8_peak
+                    res["frac_of_int8_tensor_nominal_4500"] = res["tops"] / 4500.0
+                    per_op.append(res)
+                result["per_op"] = per_op
+                result["int8_tensor_peak_measured_tops"] = i8_peak
+    else:
+        res, cfg = time_op(enn, ctx, cu, args.workload, reps=args.steps, warmup=args.warmup)
+        d, x, w, b, sc, kind = cfg
+        # end to end: one operator through upload / execute / download with pinned host buffers
+        op = getattr(enn, kind)(ctx, d, w, b, sc)
+        info = op.info
+        hin, hout = C.c_void_p(), C.c_void_p()
+        enn.lib.enn_b200_host_alloc(x.nbytes, C.byref(hin))
+        enn.lib.enn_b200_host_alloc(max(1, info.out_bytes), C.byref(hout))
+        C.memmove(hin, x.ctypes.data, x.nbytes)
+        xd, yd = ctx.malloc(x.nbytes), ctx.malloc(max(1, info.out_bytes))
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        for _ in range(2):
+            enn.lib.enn_b200_upload(ctx.h, xd, hin, x.nbytes)
+            op.execute(xd, yd)
+            enn.lib.enn_b200_download(ctx.h, hout, yd, info.out_bytes)
+        barrier()
+        e0, e1 = cu.event(), cu.event()
+        cu.record(e0, ctx.stream)
+        for _ in range(args.steps):
+            enn.lib.enn_b200_upload(ctx.h, xd, hin, x.nbytes)
+            op.execute(xd, yd)
+            enn.lib.enn_b200_download(ctx.h, hout, yd, info.out_bytes)
+        cu.record(e1, ctx.stream)
+        barrier()
+        e2e_ms = cu.elapsed_ms(e0, e1) / args.steps
+        clocks = sampler.stop() if rank == 0 else None
+        ms = res["ms"]
+        if multi:
+            t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms, e2e_ms = t.tolist()
+        if rank == 0:
+            hbm = res["bound"] == "hbm"
+            unit = "GB/s" if hbm else "TOP/s"
+            per_step = res["algorithmic_bytes"] / 1e9 if hbm else 2 * res["macs"] / 1e12
+            i8_peak = ctx.mma_peak(0, 256, 8192)
+            peak = peaks["hbm_gbs"] if hbm else i8_peak
+            ach = per_step / (res["ms"] * 1e-3)
+            result = {
+                "metric": ("hbm_gbs_" if hbm else "int8_tops_") + args.workload, "value": world * per_step / (ms * 1e-3),
+                "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+                "config": {"workload": args.workload, "l2": f"{res['buffer_sets']} rotating input/output buffer sets, together larger than twice the L2",
+                           "sharding": "independent replicas per rank, no collective"},
+                "roofline": {"bound": "hbm" if hbm else "tensor", "kernel": KERNEL_OF_IMPL.get(res["impl"]), "achieved": ach, "peak": peak,
+                             "unit": unit, "frac": ach / peak, "traffic": None,
+                             "peak_source": peaks["source"] if hbm else "measured tcgen05.mma kind::i8 rate (enn_b200_measure_mma_peak)",
+                             "frac_of_nominal_4500_tops": None if hbm else ach / 4500.0},
+                "e2e": {"value": world * per_step / (e2e_ms * 1e-3), "unit": unit, "h2d_bytes_per_step": int(x.nbytes),
+                        "d2h_bytes_per_step": int(info.out_bytes)},
+                "gpu_launches": int(res["launches_per_step"] * args.steps),
+                "clocks": clocks,
+            }
+            if world == 1 and not args.skip_cpu_baseline:
+                dt, ns, total, reps = cpu_baseline_op(cfg)
+                frac = ns / total
+                from oracle import orc
+                result["cpu_baseline"] = {"value": per_step * frac / dt, "unit": unit, "cores": orc.num_threads(), "kind": "port",
+                                          "sample": f"{ns} of {total} batch rows of {args.workload}, {reps} repetitions, {dt * 1e3:.1f} ms each"}
+    if rank == 0 and result is not None:
         print(json.dumps(result), flush=True)
     if multi:
         dist.destroy_process_group()
 
 
-def cpu_baseline(args, wl, max_seconds=20.0):
-    """The oracle timed on the host cores over a bounded sample (a batch slice) of the same workload."""
-    from oracle import orc
-    enn = load_package()
-    d, x, w, b, sc = wl["args"]
-    fn = getattr(orc, wl["oracle"])
-    n_sample = max(1, min(d.n, 8))
-    ds = type(d).from_buffer_copy(d)
-    ds.n = n_sample
-    xs = np.ascontiguousarray(x[:n_sample])
-    fn(ds, xs[:1].copy() if False else xs, w, b, sc)   # warm-up (thread pool, page faults)
-    t0 = time.perf_counter()
-    reps = 0
-    while True:
-        fn(ds, xs, w, b, sc)
-        reps += 1
-        if time.perf_counter() - t0 > min(max_seconds, 10.0) or reps >= 20:
-            break
-    dt = (time.perf_counter() - t0) / reps
-    out_elems = int(np.prod([ds.n, (d.h + d.pad_t + d.pad_b - d.kh) // d.stride_h + 1,
-                             (d.w + d.pad_l + d.pad_r - d.kw) // d.stride_w + 1, d.cout]))
-    bytes_ = xs.nbytes + out_elems + w.nbytes + 12 * d.cout
-    return {"value": bytes_ / dt / 1e9, "unit": "GB/s", "cores": orc.num_threads(), "kind": "port",
-            "sample": f"{n_sample} of {d.n} images of {args.workload}, {reps} repetitions, {dt * 1e3:.1f} ms each"}
-
-
 def run_reference(args):
+    """The CPU oracle on the host cores: K steps, each a bounded sample of the workload."""
     rank, world, _ = dist_env()
     if rank != 0:
         return
     enn = load_package()
-    wl = make_workload(args.workload, enn)
-    steps = []
-    base = None
-    for i in range(args.warmup + args.steps):
-        base = cpu_baseline(args, wl, max_seconds=3.0)
-        if i >= args.warmup:
-            steps.append(base["value"])
-    v = float(np.mean(steps))
-    base["value"] = v
+    from oracle import orc
+    if args.workload == DEFAULT_WORKLOAD:
+        import mobilenet_ref
+        mn = importlib.import_module("cl_eden_kernel_b200.mobilenet")
+        layers, _ = mn.build_model(seed=0, calib_images=1)
+        n = 8
+        x = np.random.default_rng(1000).integers(0, 256, (n, 224, 224, 3), dtype=np.int64).astype(np.uint8)
+        for _ in range(args.warmup):
+            mobilenet_ref.run_oracle(layers, x[:2])
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            mobilenet_ref.run_oracle(layers, x)
+        dt = (time.perf_counter() - t0) / args.steps
+        v, unit, metric = n / dt, "images/s", "mobilenetv2_u8_images_per_s"
+        sample = f"each step = {n} images (of the 256-image batch) through the CPU oracle graph"
+        cfg = {"workload": "MobileNetV2-1.0 224x224 uint8 graph (per-channel int8 weights), batch 256 per GPU"}
+    else:
+        kind, mk, bound = op_configs(enn)[args.workload]
+        d, x, w, b, sc = mk()
+        dt, ns, total, reps = cpu_baseline_op((d, x, w, b, sc, kind), max_seconds=3.0)
+        op_bytes = x.nbytes * ns / total
+        v, unit, metric = op_bytes / dt / 1e9, "GB/s (input bytes only)", "cpu_" + args.workload
+        sample = f"{ns} of {total} batch rows"
+        cfg = {"workload": args.workload}
     print(json.dumps({
-        "impl": "reference", "metric": "depthwise_hbm_gbs", "value": v, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "u8", "data": "synthetic", "config": {"workload": args.workload},
-        "cpu_baseline": base,
-        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8", "data": "synthetic", "config": cfg,
+        "cpu_baseline": {"value": v, "unit": unit, "cores": orc.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="depthwise3x3_s1_64x112x112x32")
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU leg (profiling runs)")
+    ap.add_argument("--skip-per-op", action="store_true", help="omit the single-operator table (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

@@ -63,7 +63,11 @@ struct TcParams {
     int32_t general;        // 1: some column needs the general (left shift / wide) requantisation
     uint32_t idesc;
     const ColParam *cols;   // [tiles_n][bn_rows]
-    uint8_t *out;           // [M][N]
+    uint8_t *out;           // output tensor base
+    // Row m of the GEMM is output position (img, qy, qx) of a qh x qw grid; its first byte lives at
+    // out + out_base + img * out_sn + qy * out_sy + qx * out_sx.  A plain [M][N] result uses qh = 1, qw = M.
+    int32_t qh, qw;
+    int64_t out_base, out_sn, out_sy, out_sx;
     int32_t *err;           // host-mapped error word
     long long *dbg;         // optional per-CTA cycle counters [grid][8] (null in normal use)
     int32_t dbg_mode;       // development switches (0 in normal use)
@@ -286,7 +290,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int row_in_tile = q * 32 + lane;
         const int32_t hi_clamp = p.act_max - p.act_min;
         const uint32_t lo_word = (static_cast<uint32_t>(p.act_min) & 0xff) * 0x01010101u;
-        const bool vec16 = (p.N & 15) == 0;
+        const bool vec16 = ((p.out_base | p.out_sn | p.out_sy | p.out_sx | p.bn_data) & 15) == 0;
         uint32_t it = 0;
         bool ok = true;
         int loaded_tn = -1;
@@ -322,7 +326,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             const int n_base = tn * p.bn_data;
             const int n_cols = min(p.bn_data, p.N - n_base);
-            uint8_t *orow = p.out + static_cast<size_t>(m) * p.N + n_base;
+            const int mq = m < p.M ? m : 0;
+            const int img = mq / (p.qh * p.qw), rem = mq - img * (p.qh * p.qw);
+            const int qy = rem / p.qw, qx = rem - qy * p.qw;
+            uint8_t *orow = p.out + p.out_base + img * p.out_sn + qy * p.out_sy + qx * p.out_sx + n_base;
             for (int c0 = cgrp * 16, lc = 0; c0 < n_cols; c0 += 16 * kColGroups, lc += 16) {
                 uint32_t r[16];
                 if (!(p.dbg_mode & 4)) {
@@ -369,23 +376,94 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------------------
+// im2col: gathers the A operand of a convolution that the kernel above cannot read in place (taps, strides,
+// dilation, channel counts that are not a multiple of 16) into a [M][Kp] byte matrix in scratch memory.
+// Positions outside the image are written as the input zero point (the reference's pad kernels do the same,
+// PadConvertKernels.cpp:241-373), so they contribute (za - za) * w = 0 and the bias fold is the same for every
+// output position; bytes k >= K pad the row to a multiple of 16 and meet zero weights.
+// Row m = (img, oy, ox) of an oh x ow grid; column k = (ky * kw + kx) * cin + c;
+// input pixel iy = oy * sy + ky * dy + y0, ix = ox * sx + kx * dx + x0.
+// ------------------------------------------------------------------------------------------------------
+struct Im2colGeom {
+    int32_t n, h, w, cin;
+    int32_t oh, ow, kh, kw;
+    int32_t sy, sx, dy, dx, y0, x0;
+    int32_t K, Kp;
+    uint32_t fill;      // input zero point replicated in 4 bytes
+};
+
+// One thread writes 16 output bytes.  VEC: cin % 16 == 0, so the 16 bytes are one aligned load.
+template <bool VEC>
+__global__ void im2col_kernel(Im2colGeom g, const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int64_t total16) {
+    const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= total16) return;
+    const int kp16 = g.Kp >> 4;
+    const int k0 = static_cast<int>(t % kp16) << 4;
+    int64_t m = t / kp16;
+    const int ox = static_cast<int>(m % g.ow);
+    m /= g.ow;
+    const int oy = static_cast<int>(m % g.oh);
+    const int img = static_cast<int>(m / g.oh);
+    uint4 v;
+    if (VEC) {
+        v = make_uint4(0, 0, 0, 0);
+        if (k0 < g.K) {
+            const int tap = k0 / g.cin, c = k0 - tap * g.cin;
+            const int ky = tap / g.kw, kx = tap - ky * g.kw;
+            const int iy = oy * g.sy + ky * g.dy + g.y0, ix = ox * g.sx + kx * g.dx + g.x0;
+            if (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w)
+                v = __ldg(reinterpret_cast<const uint4 *>(in + ((static_cast<int64_t>(img) * g.h + iy) * g.w + ix) * g.cin + c));
+            else
+                v = make_uint4(g.fill, g.fill, g.fill, g.fill);
+        }
+    } else {
+        uint32_t w[4] = {0, 0, 0, 0};
+        int tap = k0 / g.cin, c = k0 - tap * g.cin;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            uint32_t b = 0;
+            if (k0 + i < g.K) {
+                const int ky = tap / g.kw, kx = tap - ky * g.kw;
+                const int iy = oy * g.sy + ky * g.dy + g.y0, ix = ox * g.sx + kx * g.dx + g.x0;
+                b = g.fill & 0xff;
+                if (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w) b = __ldg(in + ((static_cast<int64_t>(img) * g.h + iy) * g.w + ix) * g.cin + c);
+            }
+            w[i >> 2] |= b << (8 * (i & 3));
+            if (++c == g.cin) { c = 0; ++tap; }
+        }
+        v = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    reinterpret_cast<uint4 *>(out)[t] = v;
+}
+
+// ------------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-struct TcPlan {
+// One GEMM launch: an operator is one of these (convolution, FullyConnected) or one per output parity class
+// (transposed convolution).
+struct TcGemm {
     TcParams prm{};
     CUtensorMap map_b{};
     CUtensorMap map_a{};
-    const void *map_a_ptr = nullptr;   // input pointer map_a was encoded for
+    const void *map_a_ptr = nullptr;   // A pointer map_a was encoded for
     void *w_dev = nullptr;
     void *cols_dev = nullptr;
-    int32_t *err_host = nullptr;       // pinned + mapped
-    int32_t *err_dev = nullptr;
     size_t smem_bytes = 0;
     int grid = 0;
+    bool gather = false;               // A is gathered into scratch by im2col first
+    Im2colGeom ig{};
+};
+
+struct TcPlan {
+    std::vector<TcGemm> gemms;
+    void *scratch = nullptr;           // im2col matrix, shared by the GEMMs of the op (they run in stream order)
+    size_t scratch_bytes = 0;
+    int32_t *err_host = nullptr;       // pinned + mapped
+    int32_t *err_dev = nullptr;
 };
 
 bool encode_2d(enn_b200_context *ctx, CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint64_t pitch,
@@ -402,30 +480,18 @@ bool encode_2d(enn_b200_context *ctx, CUtensorMap *map, const void *base, uint64
     return r == CUDA_SUCCESS;
 }
 
-}  // namespace
+struct QuantHost {   // host copies of what setup_quant uploaded
+    std::vector<int32_t> mult, shift, bias;
+};
 
-bool tc_available(const enn_b200_context *ctx) { return ctx && ctx->cc_major == 10 && ctx->encode_tiled != nullptr; }
-
-// Plans the tensor-core kernel for a 1x1 / FullyConnected contraction.  `w_hwio` is the host copy of the
-// weights in [Kh][Kw][Cin/g][Cout] order (raw bytes).  Returns INVALID_PARAMS when the geometry is not one
-// this kernel tiles (the caller keeps the direct kernel).
-int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
-    const ConvGeom &g = op->g;
-    enn_b200_context *ctx = op->ctx;
-    if (op->kind == OP_DECONV) return ENN_B200_INVALID_PARAMS;
-    if (!(g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.groups == 1 && g.pt == 0 && g.pl == 0)) return ENN_B200_INVALID_PARAMS;
-    if (g.oh != g.h || g.ow != g.w) return ENN_B200_INVALID_PARAMS;
-    const int64_t M64 = static_cast<int64_t>(g.n) * g.h * g.w;
-    const int32_t K = g.cin, N = g.cout;
-    if ((K & 15) != 0 || M64 <= 0 || M64 > INT32_MAX) return ENN_B200_INVALID_PARAMS;   // TMA: 16-byte row pitch
-    const int32_t M = static_cast<int32_t>(M64);
-
-    TcPlan *plan = new (std::nothrow) TcPlan();
-    if (!plan) return ENN_B200_FAILURE;
-    TcParams &p = plan->prm;
+// Builds one GEMM: packs B, folds zero points into the bias, derives the epilogue constants, sizes the launch.
+// weight(n, k) returns the raw weight byte of output column n at reduction index k (k < K).
+template <typename WeightFn>
+int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh, int32_t M, int32_t N, int32_t K, WeightFn weight,
+                   TcGemm *gm) {
+    TcParams &p = gm->prm;
     p.M = M; p.N = N; p.K = K;
-    // Weights as signed bytes: int8 stays, u8 becomes w - 128.
-    const int32_t zw_eff = g.w_signed ? g.w_zp : g.w_zp - 128;
+    const int32_t zw_eff = g.w_signed ? g.w_zp : g.w_zp - 128;   // weights as signed bytes: int8 stays, u8 becomes w - 128
     p.zw_eff = zw_eff;
     p.need_asum = zw_eff != 0;
     p.a_signed = g.a_signed;
@@ -448,17 +514,9 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
               (static_cast<uint32_t>(p.bn_rows >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
 
     // Packed B: [tiles_n][bn_rows][k_pad] int8, zero padded; row bn_data of each tile is all ones (sum_k a).
-    const uint8_t *w = static_cast<const uint8_t *>(w_hwio);   // [K][N] for 1x1
     std::vector<int8_t> wb(static_cast<size_t>(tiles_n) * p.bn_rows * k_pad, 0);
-    std::vector<int32_t> mult, shift;
     std::vector<ColParam> cols(static_cast<size_t>(tiles_n) * p.bn_rows);
     std::memset(cols.data(), 0, cols.size() * sizeof(ColParam));
-    // requant vectors were uploaded by setup_quant; re-derive them here from the device copies' host twins
-    mult.resize(N); shift.resize(N);
-    std::vector<int32_t> bias(N);
-    cudaMemcpy(mult.data(), op->rq.mult, sizeof(int32_t) * N, cudaMemcpyDeviceToHost);
-    cudaMemcpy(shift.data(), op->rq.shift, sizeof(int32_t) * N, cudaMemcpyDeviceToHost);
-    cudaMemcpy(bias.data(), op->rq.bias, sizeof(int32_t) * N, cudaMemcpyDeviceToHost);
     p.general = 0;
     const int64_t amax = g.a_signed ? 128 : 255;
     for (int32_t n = 0; n < N; ++n) {
@@ -466,24 +524,24 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         int8_t *dst = wb.data() + (static_cast<size_t>(tn) * p.bn_rows + r) * k_pad;
         int64_t wsum = 0, wabs = 0;
         for (int32_t k = 0; k < K; ++k) {
-            const uint8_t raw = w[static_cast<size_t>(k) * N + n];
+            const uint8_t raw = weight(n, k);
             const int32_t wv = g.w_signed ? static_cast<int32_t>(static_cast<int8_t>(raw)) : static_cast<int32_t>(raw) - 128;
             dst[k] = static_cast<int8_t>(wv);
             wsum += wv;
             wabs += wv < 0 ? -wv : wv;
         }
-        const int64_t folded = static_cast<int64_t>(bias[n]) - static_cast<int64_t>(g.in_zp) * wsum +
+        const int64_t folded = static_cast<int64_t>(qh.bias[n]) - static_cast<int64_t>(g.in_zp) * wsum +
                                static_cast<int64_t>(K) * g.in_zp * zw_eff;
         ColParam &c = cols[static_cast<size_t>(tn) * p.bn_rows + r];
-        c.mult = mult[n];
+        c.mult = qh.mult[n];
         c.bias = static_cast<int32_t>(folded);     // wraps like the reference's int32 accumulation
-        const int32_t e = shift[n] > 0 ? -1 : -shift[n];
+        const int32_t e = qh.shift[n] > 0 ? -1 : -qh.shift[n];
         const int64_t zo_eff = static_cast<int64_t>(g.out_zp) - g.act_min;
         const int64_t addend = e > 0 ? (1ll << (e - 1)) + zo_eff * (1ll << e) : zo_eff;
         const int64_t acc_bound = amax * wabs + static_cast<int64_t>(K) * amax * (zw_eff < 0 ? -zw_eff : zw_eff) +
                                   (folded < 0 ? -folded : folded);
         if (e < 1 || folded > INT32_MAX || folded < INT32_MIN || acc_bound + 2 + (addend < 0 ? -addend : addend) >= (1ll << 31)) {
-            c.addend = shift[n];                   // general path keeps the raw signed shift
+            c.addend = qh.shift[n];                // general path keeps the raw signed shift
             c.esh = INT32_MIN;
             p.general = 1;
         } else {
@@ -496,40 +554,168 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
             int8_t *dst = wb.data() + (static_cast<size_t>(tn) * p.bn_rows + bn_data) * k_pad;
             for (int32_t k = 0; k < K; ++k) dst[k] = 1;
         }
-
     cudaError_t e;
-    if ((e = cudaMalloc(&plan->w_dev, wb.size())) != cudaSuccess || (e = cudaMalloc(&plan->cols_dev, cols.size() * sizeof(ColParam))) != cudaSuccess ||
-        (e = cudaMemcpy(plan->w_dev, wb.data(), wb.size(), cudaMemcpyHostToDevice)) != cudaSuccess ||
-        (e = cudaMemcpy(plan->cols_dev, cols.data(), cols.size() * sizeof(ColParam), cudaMemcpyHostToDevice)) != cudaSuccess ||
-        (e = cudaHostAlloc(reinterpret_cast<void **>(&plan->err_host), sizeof(int32_t), cudaHostAllocMapped)) != cudaSuccess ||
-        (e = cudaHostGetDevicePointer(reinterpret_cast<void **>(&plan->err_dev), plan->err_host, 0)) != cudaSuccess) {
+    if ((e = cudaMalloc(&gm->w_dev, wb.size())) != cudaSuccess || (e = cudaMalloc(&gm->cols_dev, cols.size() * sizeof(ColParam))) != cudaSuccess ||
+        (e = cudaMemcpy(gm->w_dev, wb.data(), wb.size(), cudaMemcpyHostToDevice)) != cudaSuccess ||
+        (e = cudaMemcpy(gm->cols_dev, cols.data(), cols.size() * sizeof(ColParam), cudaMemcpyHostToDevice)) != cudaSuccess) {
         ctx->last_error = std::string("tensor-core plan: ") + cudaGetErrorString(e);
-        op->tc = plan;
-        tc_release(op);
         return ENN_B200_CUDA_FAILURE;
     }
-    *plan->err_host = 0;
-    p.cols = static_cast<const ColParam *>(plan->cols_dev);
-    p.err = plan->err_dev;
-    if (!encode_2d(ctx, &plan->map_b, plan->w_dev, k_pad, static_cast<uint64_t>(tiles_n) * p.bn_rows, k_pad, kBK, p.bn_rows)) {
+    p.cols = static_cast<const ColParam *>(gm->cols_dev);
+    if (!encode_2d(ctx, &gm->map_b, gm->w_dev, k_pad, static_cast<uint64_t>(tiles_n) * p.bn_rows, k_pad, kBK, p.bn_rows)) {
         ctx->last_error = "cuTensorMapEncodeTiled failed for the weight tensor";
-        op->tc = plan;
-        tc_release(op);
         return ENN_B200_CUDA_FAILURE;
     }
     const size_t stage_bytes = static_cast<size_t>(kBM) * kBK + static_cast<size_t>(p.bn_rows) * kBK;
     const size_t fixed = 4 * kMaxBN * sizeof(ColParam) + 256 + 1024;   // column constants, barriers, alignment slack
     int stages = static_cast<int>((227 * 1024 - fixed) / stage_bytes);
     if (stages > 8) stages = 8;
-    if (stages < 2) {
-        op->tc = plan;
-        tc_release(op);
-        return ENN_B200_INVALID_PARAMS;
-    }
+    if (stages < 2) return ENN_B200_INVALID_PARAMS;
     p.stages = stages;
-    plan->smem_bytes = stages * stage_bytes + fixed;
+    gm->smem_bytes = stages * stage_bytes + fixed;
     const int total_tiles = p.tiles_m * p.tiles_n;
-    plan->grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
+    gm->grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
+    return ENN_B200_SUCCESS;
+}
+
+void free_plan(TcPlan *plan) {
+    if (!plan) return;
+    for (auto &gm : plan->gemms) {
+        if (gm.w_dev) cudaFree(gm.w_dev);
+        if (gm.cols_dev) cudaFree(gm.cols_dev);
+    }
+    if (plan->scratch) cudaFree(plan->scratch);
+    if (plan->err_host) cudaFreeHost(plan->err_host);
+    delete plan;
+}
+
+}  // namespace
+
+bool tc_available(const enn_b200_context *ctx) { return ctx && ctx->cc_major == 10 && ctx->encode_tiled != nullptr; }
+
+// Plans the tensor-core path of a convolution, FullyConnected or transposed convolution.  `w_hwio` is the host
+// copy of the weights in [Kh][Kw][Cin][Cout] order (raw bytes).  Returns INVALID_PARAMS when the geometry is
+// not one this path covers (grouped convolutions); the caller then keeps the direct kernel.
+int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
+    const ConvGeom &g = op->g;
+    enn_b200_context *ctx = op->ctx;
+    if (g.groups != 1) return ENN_B200_INVALID_PARAMS;
+    const uint8_t *w = static_cast<const uint8_t *>(w_hwio);
+    const int32_t N = g.cout, cin = g.cin;
+
+    QuantHost qh;
+    qh.mult.resize(N); qh.shift.resize(N); qh.bias.resize(N);
+    if (cudaMemcpy(qh.mult.data(), op->rq.mult, sizeof(int32_t) * N, cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(qh.shift.data(), op->rq.shift, sizeof(int32_t) * N, cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(qh.bias.data(), op->rq.bias, sizeof(int32_t) * N, cudaMemcpyDeviceToHost) != cudaSuccess)
+        return ENN_B200_CUDA_FAILURE;
+
+    TcPlan *plan = new (std::nothrow) TcPlan();
+    if (!plan) return ENN_B200_FAILURE;
+    auto bail = [&](int32_t st) {
+        free_plan(plan);
+        return st;
+    };
+    const uint32_t fill = (static_cast<uint32_t>(g.in_zp) & 0xff) * 0x01010101u;
+    int32_t st = ENN_B200_SUCCESS;
+
+    if (op->kind != OP_DECONV) {
+        const int64_t M64 = static_cast<int64_t>(g.n) * g.oh * g.ow;
+        if (M64 <= 0 || M64 > INT32_MAX) return bail(ENN_B200_INVALID_PARAMS);
+        const int32_t K = g.kh * g.kw * cin;
+        const bool in_place = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.pt == 0 && g.pl == 0 && g.oh == g.h &&
+                              g.ow == g.w && (cin & 15) == 0;
+        plan->gemms.resize(1);
+        TcGemm &gm = plan->gemms[0];
+        st = build_gemm(ctx, g, qh, static_cast<int32_t>(M64), N, K, [&](int32_t n, int32_t k) { return w[static_cast<size_t>(k) * N + n]; }, &gm);
+        if (st != ENN_B200_SUCCESS) return bail(st);
+        gm.prm.qh = 1; gm.prm.qw = static_cast<int32_t>(M64);
+        gm.prm.out_base = 0; gm.prm.out_sn = 0; gm.prm.out_sy = 0; gm.prm.out_sx = N;
+        gm.gather = !in_place;
+        if (gm.gather) {
+            Im2colGeom &ig = gm.ig;
+            ig.n = g.n; ig.h = g.h; ig.w = g.w; ig.cin = cin;
+            ig.oh = g.oh; ig.ow = g.ow; ig.kh = g.kh; ig.kw = g.kw;
+            ig.sy = g.sh; ig.sx = g.sw; ig.dy = g.dh; ig.dx = g.dw; ig.y0 = -g.pt; ig.x0 = -g.pl;
+            ig.K = K; ig.Kp = (K + 15) & ~15; ig.fill = fill;
+            plan->scratch_bytes = static_cast<size_t>(M64) * ig.Kp;
+        }
+    } else {
+        // Transposed convolution (DeconvolutionKernels.cpp:24-198) split by output parity: outputs with
+        // (oy + pad_t) % sh == py only ever meet kernel rows ky = py + sh * jy, so each class (py, px) is a
+        // stride-1 correlation over the input with its own small filter:
+        //   out[n, sh*q - pad_t + py, ...] = sum_{jy,jx,c} in[n, q - jy, r - jx, c] * w[c][co][py + sh*jy][px + sw*jx].
+        for (int32_t py = 0; py < g.sh; ++py) {
+            for (int32_t px = 0; px < g.sw; ++px) {
+                const int32_t jy_n = py < g.kh ? (g.kh - py + g.sh - 1) / g.sh : 0;
+                const int32_t jx_n = px < g.kw ? (g.kw - px + g.sw - 1) / g.sw : 0;
+                // q range: 0 <= sh*q - pad_t + py < oh
+                const int32_t q_lo = (g.pt - py + g.sh - 1 >= 0) ? (g.pt - py + g.sh - 1) / g.sh : 0;
+                const int32_t q_hi = (g.oh - 1 + g.pt - py) >= 0 ? (g.oh - 1 + g.pt - py) / g.sh : -1;
+                const int32_t r_lo = (g.pl - px + g.sw - 1 >= 0) ? (g.pl - px + g.sw - 1) / g.sw : 0;
+                const int32_t r_hi = (g.ow - 1 + g.pl - px) >= 0 ? (g.ow - 1 + g.pl - px) / g.sw : -1;
+                const int32_t qh_n = q_hi - q_lo + 1, qw_n = r_hi - r_lo + 1;
+                if (qh_n <= 0 || qw_n <= 0) continue;
+                const int64_t M64 = static_cast<int64_t>(g.n) * qh_n * qw_n;
+                if (M64 > INT32_MAX) return bail(ENN_B200_INVALID_PARAMS);
+                // A class without taps (stride larger than the kernel) still has outputs: requant(bias).  One
+                // zero-weight dummy tap keeps it on the same code path.
+                const int32_t jy_e = jy_n > 0 ? jy_n : 1, jx_e = jx_n > 0 ? jx_n : 1;
+                const bool empty = jy_n == 0 || jx_n == 0;
+                const int32_t K = jy_e * jx_e * cin;
+                plan->gemms.emplace_back();
+                TcGemm &gm = plan->gemms.back();
+                st = build_gemm(ctx, g, qh, static_cast<int32_t>(M64), N, K,
+                                [&](int32_t n, int32_t k) -> uint8_t {
+                                    const int32_t tap = k / cin, c = k - tap * cin;
+                                    const int32_t jy = tap / jx_e, jx = tap - jy * jx_e;
+                                    if (empty) return g.w_signed ? static_cast<uint8_t>(g.w_zp) : static_cast<uint8_t>(g.w_zp);
+                                    const int32_t ky = py + g.sh * jy, kx = px + g.sw * jx;
+                                    return w[((static_cast<size_t>(ky) * g.kw + kx) * cin + c) * N + n];
+                                },
+                                &gm);
+                if (st != ENN_B200_SUCCESS) return bail(st);
+                gm.prm.qh = qh_n; gm.prm.qw = qw_n;
+                const int32_t oy0 = g.sh * q_lo - g.pt + py, ox0 = g.sw * r_lo - g.pl + px;
+                gm.prm.out_base = (static_cast<int64_t>(oy0) * g.ow + ox0) * N;
+                gm.prm.out_sn = static_cast<int64_t>(g.oh) * g.ow * N;
+                gm.prm.out_sy = static_cast<int64_t>(g.sh) * g.ow * N;
+                gm.prm.out_sx = static_cast<int64_t>(g.sw) * N;
+                gm.gather = true;
+                Im2colGeom &ig = gm.ig;
+                ig.n = g.n; ig.h = g.h; ig.w = g.w; ig.cin = cin;
+                ig.oh = qh_n; ig.ow = qw_n; ig.kh = jy_e; ig.kw = jx_e;
+                ig.sy = 1; ig.sx = 1; ig.dy = -1; ig.dx = -1; ig.y0 = q_lo; ig.x0 = r_lo;
+                ig.K = K; ig.Kp = (K + 15) & ~15; ig.fill = fill;
+                const size_t need = static_cast<size_t>(M64) * ig.Kp;
+                if (need > plan->scratch_bytes) plan->scratch_bytes = need;
+            }
+        }
+        if (plan->gemms.empty()) return bail(ENN_B200_INVALID_PARAMS);
+    }
+
+    if (plan->scratch_bytes > (static_cast<size_t>(8) << 30)) return bail(ENN_B200_INVALID_PARAMS);   // keep the direct kernel
+    cudaError_t e;
+    if ((plan->scratch_bytes && (e = cudaMalloc(&plan->scratch, plan->scratch_bytes)) != cudaSuccess) ||
+        (e = cudaHostAlloc(reinterpret_cast<void **>(&plan->err_host), sizeof(int32_t), cudaHostAllocMapped)) != cudaSuccess ||
+        (e = cudaHostGetDevicePointer(reinterpret_cast<void **>(&plan->err_dev), plan->err_host, 0)) != cudaSuccess) {
+        ctx->last_error = std::string("tensor-core plan: ") + cudaGetErrorString(e);
+        return bail(ENN_B200_CUDA_FAILURE);
+    }
+    *plan->err_host = 0;
+    int launches = 0;
+    for (auto &gm : plan->gemms) {
+        gm.prm.err = plan->err_dev;
+        launches += gm.gather ? 2 : 1;
+        if (gm.gather) {
+            if (!encode_2d(ctx, &gm.map_a, plan->scratch, gm.ig.Kp, gm.prm.M, gm.ig.Kp, kBK, kBM)) {
+                ctx->last_error = "cuTensorMapEncodeTiled failed for the gathered activation matrix";
+                return bail(ENN_B200_CUDA_FAILURE);
+            }
+            gm.map_a_ptr = plan->scratch;
+        }
+    }
+    op->info.kernel_launches = launches;
     static bool attr_set = false;
     if (!attr_set) {
         cudaFuncSetAttribute(tc_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -552,55 +738,49 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
         ctx->last_error = buf;
         return ENN_B200_CUDA_FAILURE;
     }
-    TcParams &p = plan->prm;
-    if (p.M == 0) return ENN_B200_SUCCESS;
-    if ((reinterpret_cast<uintptr_t>(in) & 15) != 0) {
-        ctx->last_error = "tensor-core path needs a 16-byte aligned input pointer";
-        return ENN_B200_INVALID_PARAMS;
-    }
-    if (plan->map_a_ptr != in) {
-        if (!encode_2d(ctx, &plan->map_a, in, p.K, p.M, p.K, kBK, kBM)) {
-            ctx->last_error = "cuTensorMapEncodeTiled failed for the activation tensor";
+    for (auto &gm : plan->gemms) {
+        TcParams &p = gm.prm;
+        if (p.M == 0) continue;
+        if (gm.gather) {
+            const int64_t total16 = static_cast<int64_t>(p.M) * (gm.ig.Kp >> 4);
+            const unsigned blocks = static_cast<unsigned>((total16 + 255) / 256);
+            if ((gm.ig.cin & 15) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0)
+                im2col_kernel<true><<<blocks, 256, 0, ctx->stream>>>(gm.ig, static_cast<const uint8_t *>(in), static_cast<uint8_t *>(plan->scratch), total16);
+            else
+                im2col_kernel<false><<<blocks, 256, 0, ctx->stream>>>(gm.ig, static_cast<const uint8_t *>(in), static_cast<uint8_t *>(plan->scratch), total16);
+        } else {
+            if ((reinterpret_cast<uintptr_t>(in) & 15) != 0) {
+                ctx->last_error = "tensor-core path needs a 16-byte aligned input pointer";
+                return ENN_B200_INVALID_PARAMS;
+            }
+            if (gm.map_a_ptr != in) {
+                if (!encode_2d(ctx, &gm.map_a, in, p.K, p.M, p.K, kBK, kBM)) {
+                    ctx->last_error = "cuTensorMapEncodeTiled failed for the activation tensor";
+                    return ENN_B200_CUDA_FAILURE;
+                }
+                gm.map_a_ptr = in;
+            }
+        }
+        p.out = static_cast<uint8_t *>(out);
+        p.dbg_mode = getenv("ENN_B200_TC_MODE") ? atoi(getenv("ENN_B200_TC_MODE")) : 0;
+        if (p.need_asum) {
+            if (p.general) tc_gemm_kernel<true, true><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a, gm.map_b, p);
+            else tc_gemm_kernel<true, false><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a, gm.map_b, p);
+        } else {
+            if (p.general) tc_gemm_kernel<false, true><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a, gm.map_b, p);
+            else tc_gemm_kernel<false, false><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a, gm.map_b, p);
+        }
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            ctx->last_error = std::string("tc_gemm_kernel launch: ") + cudaGetErrorString(e);
             return ENN_B200_CUDA_FAILURE;
         }
-        plan->map_a_ptr = in;
-    }
-    p.out = static_cast<uint8_t *>(out);
-    static long long *dbg_buf = nullptr;
-    p.dbg_mode = getenv("ENN_B200_TC_MODE") ? atoi(getenv("ENN_B200_TC_MODE")) : 0;
-    if (getenv("ENN_B200_TC_DEBUG")) {      // development aid: per-CTA wait-cycle counters printed after the launch
-        if (!dbg_buf) cudaMallocManaged(&dbg_buf, sizeof(long long) * 8 * 1024);
-        p.dbg = dbg_buf;
-    }
-    if (p.need_asum) {
-        if (p.general) tc_gemm_kernel<true, true><<<plan->grid, kThreads, plan->smem_bytes, ctx->stream>>>(plan->map_a, plan->map_b, p);
-        else tc_gemm_kernel<true, false><<<plan->grid, kThreads, plan->smem_bytes, ctx->stream>>>(plan->map_a, plan->map_b, p);
-    } else {
-        if (p.general) tc_gemm_kernel<false, true><<<plan->grid, kThreads, plan->smem_bytes, ctx->stream>>>(plan->map_a, plan->map_b, p);
-        else tc_gemm_kernel<false, false><<<plan->grid, kThreads, plan->smem_bytes, ctx->stream>>>(plan->map_a, plan->map_b, p);
-    }
-    if (p.dbg) {
-        cudaStreamSynchronize(ctx->stream);
-        const long long *d = p.dbg;
-        std::printf("tc dbg cta0: producer wait %lld / %lld | mma full-wait %lld tempty-wait %lld / %lld | epi tfull-wait %lld / %lld\n",
-                    d[0], d[1], d[2], d[3], d[4], d[5], d[6]);
-        p.dbg = nullptr;
-    }
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) {
-        ctx->last_error = std::string("tc_gemm_kernel launch: ") + cudaGetErrorString(e);
-        return ENN_B200_CUDA_FAILURE;
     }
     return ENN_B200_SUCCESS;
 }
 
 void tc_release(enn_b200_op *op) {
-    TcPlan *plan = static_cast<TcPlan *>(op->tc);
-    if (!plan) return;
-    if (plan->w_dev) cudaFree(plan->w_dev);
-    if (plan->cols_dev) cudaFree(plan->cols_dev);
-    if (plan->err_host) cudaFreeHost(plan->err_host);
-    delete plan;
+    free_plan(static_cast<TcPlan *>(op->tc));
     op->tc = nullptr;
 }
 
