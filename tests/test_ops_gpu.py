@@ -295,3 +295,19 @@ def test_mobilenet_layers_individually(enn, orc, ctx):
             assert np.array_equal(y, acts[L["name"]].reshape(-1)), L["name"]
         finally:
             op.release()
+
+
+def test_cpp_adapter_interface(enn):
+    """Builds and runs tests/adapter_test.cpp: the reference KAT and two seeded ops through the C++ classes that
+    mirror CLConvolution / CLDepthwiseConvolution (initialize / execute / release on ITensor inputs)."""
+    import subprocess
+    root = os.path.dirname(HERE)
+    pkg = os.path.join(root, "cl-eden-kernel_b200")
+    exe = os.path.join(root, "tests", "adapter_test.bin")
+    subprocess.run(["make", "-C", pkg, "libenn_b200_adapter.so"], check=True, capture_output=True)
+    subprocess.run(["make", "-C", os.path.join(root, "oracle"), "liboracle.so"], check=True, capture_output=True)
+    subprocess.run(["/usr/bin/g++", "-O1", "-std=c++17", "-o", exe, os.path.join(HERE, "adapter_test.cpp"),
+                    "-L" + pkg, "-lenn_b200_adapter", "-lenn_b200", "-L" + os.path.join(root, "oracle"), "-loracle",
+                    "-Wl,-rpath," + pkg, "-Wl,-rpath," + os.path.join(root, "oracle"), "-fopenmp"], check=True, capture_output=True)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "adapter test: OK" in r.stdout, r.stdout + r.stderr
