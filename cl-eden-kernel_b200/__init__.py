@@ -96,6 +96,7 @@ PROTOTYPES = {
     "enn_b200_op_set_impl": (C.c_int32, [_P, C.c_int32]),
     "enn_b200_op_execute": (C.c_int32, [_P, _P, _P]),
     "enn_b200_op_execute2": (C.c_int32, [_P, _P, _P, _P]),
+    "enn_b200_op_execute_noalloc": (C.c_int32, [_P, _P, _P]),
     "enn_b200_op_info": (C.c_int32, [_P, C.POINTER(OpInfo)]),
     "enn_b200_op_release": (C.c_int32, [_P]),
     "enn_b200_oplist_create": (C.c_int32, [_P, C.POINTER(_P)]),

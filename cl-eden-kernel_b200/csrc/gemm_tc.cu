@@ -456,6 +456,8 @@ struct TcGemm {
     int grid = 0;
     bool gather = false;               // A is gathered into scratch by im2col first
     Im2colGeom ig{};
+    CUtensorMap map_a_static{};        // A map over the library's static scratch array (no-allocation entry point)
+    const void *map_a_static_ptr = nullptr;
 };
 
 struct TcPlan {
@@ -784,4 +786,109 @@ void tc_release(enn_b200_op *op) {
     op->tc = nullptr;
 }
 
+// ------------------------------------------------------------------------------------------------------
+// Execution without any allocation: the gathered A matrix lives in a fixed device array that is part of the
+// loaded module instead of the plan's own scratch buffer.
+// ------------------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = static_cast<size_t>(32) << 20;
+static __device__ __align__(256) uint8_t g_static_scratch[kStaticScratchBytes];
+// The array's name is only a host-side handle; the device address differs per device and is looked up once per
+// device with that device current.
+static uint8_t *g_static_scratch_addr[64] = {nullptr};
+
+int32_t tc_execute_static(enn_b200_op *op, const void *in, void *out) {
+    enn_b200_context *ctx = op->ctx;
+    TcPlan *plan = static_cast<TcPlan *>(op->tc);
+    if (!plan || op->impl != ENN_B200_IMPL_TCGEN05) {
+        ctx->last_error = "enn_b200_op_execute_noalloc: the operator is not bound to the tensor-core path";
+        return ENN_B200_INVALID_PARAMS;
+    }
+    size_t need = 0;
+    for (auto &gm : plan->gemms) {
+        if (!gm.gather) {
+            ctx->last_error = "enn_b200_op_execute_noalloc: this operator reads its input in place and uses no scratch; call enn_b200_op_execute";
+            return ENN_B200_INVALID_PARAMS;
+        }
+        const size_t bytes = static_cast<size_t>(gm.prm.M) * gm.ig.Kp;
+        if (bytes > need) need = bytes;
+    }
+    if (need > kStaticScratchBytes) {
+        char buf[160];
+        std::snprintf(buf, sizeof(buf), "enn_b200_op_execute_noalloc: gathered matrix needs %zu bytes, the static scratch holds %zu",
+                      need, kStaticScratchBytes);
+        ctx->last_error = buf;
+        return ENN_B200_INVALID_PARAMS;
+    }
+    if (ctx->device < 0 || ctx->device >= 64) return ENN_B200_INVALID_PARAMS;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return ENN_B200_CUDA_FAILURE;
+    if (!g_static_scratch_addr[ctx->device]) {
+        void *addr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&addr, g_static_scratch);
+        if (e != cudaSuccess || !addr) {
+            ctx->last_error = std::string("enn_b200_op_execute_noalloc: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e);
+            return ENN_B200_CUDA_FAILURE;
+        }
+        g_static_scratch_addr[ctx->device] = static_cast<uint8_t *>(addr);
+    }
+    uint8_t *scratch = g_static_scratch_addr[ctx->device];
+    if (*plan->err_host != 0) {
+        ctx->last_error = "tensor-core kernel gave up on a barrier wait earlier";
+        return ENN_B200_CUDA_FAILURE;
+    }
+    for (auto &gm : plan->gemms) {
+        TcParams p = gm.prm;     // private copy: the handle's own launch state is left untouched
+        if (p.M == 0) continue;
+        if (gm.map_a_static_ptr != scratch) {
+            if (!encode_2d(ctx, &gm.map_a_static, scratch, gm.ig.Kp, p.M, gm.ig.Kp, kBK, kBM)) {
+                ctx->last_error = "cuTensorMapEncodeTiled failed for the static scratch";
+                return ENN_B200_CUDA_FAILURE;
+            }
+            gm.map_a_static_ptr = scratch;
+        }
+        const int64_t total16 = static_cast<int64_t>(p.M) * (gm.ig.Kp >> 4);
+        const unsigned blocks = static_cast<unsigned>((total16 + 255) / 256);
+        if ((gm.ig.cin & 15) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0)
+            im2col_kernel<true><<<blocks, 256, 0, ctx->stream>>>(gm.ig, static_cast<const uint8_t *>(in), scratch, total16);
+        else
+            im2col_kernel<false><<<blocks, 256, 0, ctx->stream>>>(gm.ig, static_cast<const uint8_t *>(in), scratch, total16);
+        p.out = static_cast<uint8_t *>(out);
+        p.dbg = nullptr;
+        p.dbg_mode = 0;
+        if (p.need_asum) {
+            if (p.general) tc_gemm_kernel<true, true><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a_static, gm.map_b, p);
+            else tc_gemm_kernel<true, false><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a_static, gm.map_b, p);
+        } else {
+            if (p.general) tc_gemm_kernel<false, true><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a_static, gm.map_b, p);
+            else tc_gemm_kernel<false, false><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a_static, gm.map_b, p);
+        }
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            ctx->last_error = std::string("enn_b200_op_execute_noalloc launch: ") + cudaGetErrorString(e);
+            return ENN_B200_CUDA_FAILURE;
+        }
+    }
+    return ENN_B200_SUCCESS;
+}
+
 }  // namespace enn_b200
+
+// For callers that must not allocate device memory at run time: a convolution or transposed convolution whose
+// input is gathered into a scratch matrix normally keeps that matrix in a buffer obtained with cudaMalloc when
+// the operator is prepared.  A component that runs where allocation is off limits (a real-time inference loop that
+// cannot afford the device-wide synchronisation an allocation may imply, or a host that pre-reserved all device
+// memory for something else) can run the same operator through this entry point instead: the gathered matrix is
+// placed in a 32 MiB array that belongs to the library image, so the call performs no cudaMalloc / cudaFree and no
+// allocating library routine.  The first call on a device looks the array's device address up
+// (cudaGetSymbolAddress) and encodes one tensor map; make that first call before any stream capture starts.
+// Every call on a device uses the same array and leaves its last gathered matrix there; the gather overwrites all
+// the bytes the GEMM will read, so nothing needs clearing, but two calls whose kernels overlap on the GPU (different
+// streams or contexts) race on it.  Operators that need more than 32 MiB of scratch, or none, are rejected with
+// ENN_B200_INVALID_PARAMS and a message.
+extern "C" int32_t enn_b200_op_execute_noalloc(enn_b200_op *op, const void *in_dev, void *out_dev) {
+    if (!op) return ENN_B200_INVALID_PARAMS;
+    if (!in_dev || !out_dev) {
+        op->ctx->last_error = "null device pointer";
+        return ENN_B200_INVALID_PARAMS;
+    }
+    return enn_b200::tc_execute_static(op, in_dev, out_dev);
+}

@@ -174,6 +174,12 @@ int32_t enn_b200_op_set_impl(enn_b200_op *op, int32_t impl);
 int32_t enn_b200_op_execute(enn_b200_op *op, const void *in_dev, void *out_dev);
 /* Two-input form for the quantized add (inputs = {a, b}). */
 int32_t enn_b200_op_execute2(enn_b200_op *op, const void *in0_dev, const void *in1_dev, void *out_dev);
+/* No counterpart in the reference.  Runs a prepared Conv2D / Deconvolution whose input is gathered into a scratch
+ * matrix without allocating anything: the matrix goes into a 32 MiB device array that is part of the library image.
+ * For callers that may not call cudaMalloc at run time.  Limits: the operator must be on the tensor-core path and
+ * need between 1 byte and 32 MiB of scratch (INVALID_PARAMS otherwise); calls that overlap on one GPU race on the
+ * shared array; the first call per device does a one-time address lookup and should precede any stream capture. */
+int32_t enn_b200_op_execute_noalloc(enn_b200_op *op, const void *in_dev, void *out_dev);
 int32_t enn_b200_op_info(const enn_b200_op *op, enn_b200_op_info_t *info);
 int32_t enn_b200_op_release(enn_b200_op *op);
 
