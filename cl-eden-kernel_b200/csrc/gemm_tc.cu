@@ -5,7 +5,7 @@
 // One persistent CTA per SM, warp-specialised:
 //   warp 0      TMA producer (one lane)
 //   warp 1      TMEM allocation, MMA issue (one lane)
-//   warps 2..17 epilogue: each thread owns one accumulator row (= one output pixel) and a quarter of its columns
+//   warps 2..25 epilogue: each thread owns one accumulator row (= one output pixel) and a quarter of its columns
 // Two accumulator buffers in TMEM let the epilogue of tile i overlap the MMAs of tile i+1.
 //
 // Value computed (ConvolutionKernels.cpp:956-1274 / :1317-1375): for output row m, column n
@@ -39,7 +39,9 @@ namespace {
 constexpr int kBM = 128;            // rows per tile = UMMA M
 constexpr int kBK = 128;            // bytes of K per stage = one 128B swizzle atom = 4 UMMA K steps
 constexpr int kMaxBN = 256;         // UMMA N limit
-constexpr int kEpiWarps = 16;         // epilogue warps: 4 per TMEM lane quarter, splitting the columns
+constexpr int kEpiWarps = 24;         // epilogue warps: 6 per TMEM lane quarter, splitting the 16-column chunks
+constexpr int kColGroups = kEpiWarps / 4;
+constexpr int kChunksPerWarp = (kMaxBN / 16 + kColGroups - 1) / kColGroups;   // chunks one warp can own
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr uint32_t kSpinLimit = 1u << 24;
 
@@ -53,6 +55,8 @@ struct ColParam {   // per output column, 16 bytes
 struct TcParams {
     int32_t M, N, K;
     int32_t tiles_m, tiles_n, k_blocks;
+    int32_t group;          // M tiles computed side by side in one accumulator buffer (group * bn_rows <= 256 columns)
+    int32_t tiles_mg;       // ceil(tiles_m / group)
     int32_t bn_rows;        // B rows per N tile in shared memory (= UMMA N), multiple of 16
     int32_t bn_data;        // real output columns per N tile
     int32_t stages;
@@ -194,7 +198,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // Per-epilogue-warp copies of the N tile's column constants (kEpiWarps x 256 x 16 bytes): private to a warp, so
     // refreshing them needs only a warp-level sync.
     int4 *s_cols = reinterpret_cast<int4 *>(smem + static_cast<size_t>(p.stages) * stage_bytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(s_cols + kEpiWarps * (kMaxBN / (kEpiWarps / 4)));
+    const uint32_t s_cols_u32 = smem_u32(s_cols);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_cols + kEpiWarps * kChunksPerWarp * 16);
     // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2]
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * p.stages + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -221,7 +226,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int total_tiles = p.tiles_m * p.tiles_n;
+    // Work unit = (N tile, group of `group` consecutive M tiles).  For narrow N several M tiles share one accumulator
+    // buffer, so that every epilogue warp has columns to work on.
+    const int total_tiles = p.tiles_mg * p.tiles_n;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -230,16 +237,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             bool ok = true;
             long long t_wait = 0, t_begin = clock64();
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    const long long t0 = clock64();
-                    if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.err, 1)) { ok = false; break; }
-                    t_wait += clock64() - t0;
-                    const uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
-                    mbar_expect_tx(full0 + 8 * stage, stage_bytes);
-                    tma_load_2d(sa, &map_a, full0 + 8 * stage, kb * kBK, tm * kBM);
-                    tma_load_2d(sa + a_bytes, &map_b, full0 + 8 * stage, kb * kBK, tn * p.bn_rows);
-                    if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+                const int tg = tile % p.tiles_mg, tn = tile / p.tiles_mg;
+                const int nsub = min(p.group, p.tiles_m - tg * p.group);
+                for (int j = 0; j < nsub && ok; ++j) {
+                    const int tm = tg * p.group + j;
+                    for (int kb = 0; kb < p.k_blocks; ++kb) {
+                        const long long t0 = clock64();
+                        if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.err, 1)) { ok = false; break; }
+                        t_wait += clock64() - t0;
+                        const uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
+                        mbar_expect_tx(full0 + 8 * stage, stage_bytes);
+                        tma_load_2d(sa, &map_a, full0 + 8 * stage, kb * kBK, tm * kBM);
+                        tma_load_2d(sa + a_bytes, &map_b, full0 + 8 * stage, kb * kBK, tn * p.bn_rows);
+                        if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+                    }
                 }
             }
             if (p.dbg) { p.dbg[blockIdx.x * 8 + 0] = t_wait; p.dbg[blockIdx.x * 8 + 1] = clock64() - t_begin; }
@@ -264,19 +275,23 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!mbar_wait(tempty0 + 8 * ab, (use & 1) ^ 1, abort_flag, p.err, 2)) { ok = false; break; }
                 t_tempty += clock64() - t0;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + ab * kMaxBN;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    const long long t1 = clock64();
-                    if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.err, 3)) { ok = false; break; }
-                    t_full += clock64() - t1;
-                    tc_fence_after();
-                    const uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
-                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + a_bytes);
-                    const int ksteps = min(4, (p.K - kb * kBK + 31) >> 5);
-                    for (int k = 0; k < ksteps; ++k)
-                        umma_i8(d_tmem, da + 2 * k, db + 2 * k, p.idesc, (kb | k) != 0);
-                    umma_commit(empty0 + 8 * stage);      // frees the stage when these MMAs have read it
-                    if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+                const int tg = tile % p.tiles_mg;
+                const int nsub = min(p.group, p.tiles_m - tg * p.group);
+                for (int j = 0; j < nsub && ok; ++j) {
+                    const uint32_t d_tmem = tmem_base + ab * kMaxBN + j * p.bn_rows;
+                    for (int kb = 0; kb < p.k_blocks; ++kb) {
+                        const long long t1 = clock64();
+                        if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.err, 3)) { ok = false; break; }
+                        t_full += clock64() - t1;
+                        tc_fence_after();
+                        const uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
+                        const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + a_bytes);
+                        const int ksteps = min(4, (p.K - kb * kBK + 31) >> 5);
+                        for (int k = 0; k < ksteps; ++k)
+                            umma_i8(d_tmem, da + 2 * k, db + 2 * k, p.idesc, (kb | k) != 0);
+                        umma_commit(empty0 + 8 * stage);      // frees the stage when these MMAs have read it
+                        if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+                    }
                 }
                 if (ok) umma_commit(tfull0 + 8 * ab);     // accumulator complete
             }
@@ -286,28 +301,33 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------- epilogue: thread = accumulator row, warp = (lane quarter, column share) ----------------
         const int q = warp & 3;                            // TMEM lane group this warp may access
         const int cgrp = (warp - 2) >> 2;                  // which share of the 16-column chunks this warp takes
-        constexpr int kColGroups = kEpiWarps / 4;
         const int row_in_tile = q * 32 + lane;
         const int32_t hi_clamp = p.act_max - p.act_min;
         const uint32_t lo_word = (static_cast<uint32_t>(p.act_min) & 0xff) * 0x01010101u;
-        const bool vec16 = ((p.out_base | p.out_sn | p.out_sy | p.out_sx | p.bn_data) & 15) == 0;
+        const int64_t st_bits = p.out_base | p.out_sn | p.out_sy | p.out_sx | p.bn_data | static_cast<int64_t>(reinterpret_cast<uintptr_t>(p.out));
+        const int st_align = (st_bits & 15) == 0 ? 16 : ((st_bits & 7) == 0 ? 8 : 1);   // widest store every row start allows
         uint32_t it = 0;
         bool ok = true;
         int loaded_tn = -1;
         long long t_tfull = 0, t_begin = clock64();
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            const int tg = tile % p.tiles_mg, tn = tile / p.tiles_mg;
+            const int nsub = min(p.group, p.tiles_m - tg * p.group);
             const uint32_t ab = it & 1, use = it >> 1;
             const long long t0 = clock64();
-            // Each warp keeps only the constants of the column chunks it processes (chunk k of this warp is
-            // global chunk cgrp + k * kColGroups).
-            int4 *my_cols = s_cols + (warp - 2) * (kMaxBN / kColGroups);
+            // Chunk c of the buffer = 16 columns cc of M tile j: c = j * cps + cc.  This warp owns chunks
+            // cgrp, cgrp + kColGroups, ...; it keeps private copies of the constants of the columns it meets.
+            const int cps = p.bn_data >> 4;
+            const uint32_t my_cols = s_cols_u32 + (warp - 2) * (kChunksPerWarp * 16 * 16);
             if (tn != loaded_tn) {
                 const int4 *src = reinterpret_cast<const int4 *>(p.cols + static_cast<size_t>(tn) * p.bn_rows);
                 __syncwarp();
-                for (int i = lane; i < kMaxBN / kColGroups; i += 32) {
-                    const int col = ((i >> 4) * kColGroups + cgrp) * 16 + (i & 15);
-                    if (col < p.bn_rows) my_cols[i] = __ldg(src + col);
+                for (int i = lane; i < kChunksPerWarp * 16; i += 32) {
+                    const int c = (i >> 4) * kColGroups + cgrp;
+                    if (c < p.group * cps) {
+                        const int4 v = __ldg(src + (c % cps) * 16 + (i & 15));
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_cols + i * 16), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                    }
                 }
                 __syncwarp();
                 loaded_tn = tn;
@@ -316,51 +336,79 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             t_tfull += clock64() - t0;
             tc_fence_after();
             const uint32_t t_row = tmem_base + ab * kMaxBN + (static_cast<uint32_t>(q * 32) << 16);
-            const int m = tm * kBM + row_in_tile;
-            int32_t asum_term = 0;
-            if (ASUM) {
-                uint32_t rs;
-                tmem_ld_x1(t_row + p.bn_data, rs);
-                tmem_ld_wait();
-                asum_term = p.zw_eff * static_cast<int32_t>(rs);
-            }
             const int n_base = tn * p.bn_data;
             const int n_cols = min(p.bn_data, p.N - n_base);
-            const int mq = m < p.M ? m : 0;
-            const int img = mq / (p.qh * p.qw), rem = mq - img * (p.qh * p.qw);
-            const int qy = rem / p.qw, qx = rem - qy * p.qw;
-            uint8_t *orow = p.out + p.out_base + img * p.out_sn + qy * p.out_sy + qx * p.out_sx + n_base;
-            for (int c0 = cgrp * 16, lc = 0; c0 < n_cols; c0 += 16 * kColGroups, lc += 16) {
+            const int nchunks = nsub * cps;
+
+            // Walk this warp's chunks; (j, cc) follow c = j * cps + cc incrementally (no divisions in the loop),
+            // and the output row pointer is recomputed only when the M tile j changes.
+            int j = 0, cc = cgrp;
+            while (cc >= cps) { cc -= cps; ++j; }
+            int cur_j = -1;
+            uint8_t *orow = nullptr;
+            bool row_ok = false;
+            int32_t asum_term = 0;
+            uint32_t lc = my_cols;
+            for (int c = cgrp; c < nchunks; c += kColGroups, lc += 256) {
                 uint32_t r[16];
-                if (!(p.dbg_mode & 4)) {
-                tmem_ld_x16(t_row + c0, r);                 // warp-collective: executed by all lanes
+                tmem_ld_x16(t_row + j * p.bn_rows + (cc << 4), r);     // warp-collective
+                if (j != cur_j) {
+                    cur_j = j;
+                    const int m = (tg * p.group + j) * kBM + row_in_tile;
+                    row_ok = m < p.M;
+                    const int mq = row_ok ? m : 0;
+                    if (p.qh == 1) {
+                        orow = p.out + p.out_base + static_cast<int64_t>(mq) * p.out_sx + n_base;
+                    } else {
+                        const int img = mq / (p.qh * p.qw), rem = mq - img * (p.qh * p.qw);
+                        const int qy = rem / p.qw, qx = rem - qy * p.qw;
+                        orow = p.out + p.out_base + img * p.out_sn + qy * p.out_sy + qx * p.out_sx + n_base;
+                    }
+                    if (ASUM) {
+                        uint32_t rs;
+                        tmem_ld_x1(t_row + j * p.bn_rows + p.bn_data, rs);
+                        tmem_ld_wait();
+                        asum_term = p.zw_eff * static_cast<int32_t>(rs);
+                    }
+                }
                 tmem_ld_wait();
-                } else { for (int i = 0; i < 16; ++i) r[i] = c0 + i; }
-                if (m < p.M) {
+                const int c0 = cc << 4;
+                if (row_ok && c0 < n_cols) {
                     uint32_t w[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int jj = 0; jj < 4; ++jj) {
                         int32_t y[4];
 #pragma unroll
                         for (int b = 0; b < 4; ++b) {
-                            const int4 cv = my_cols[lc + j * 4 + b];
-                            int32_t acc = static_cast<int32_t>(r[j * 4 + b]) + cv.w;
+                            int4 cv;
+                            asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(lc + (jj * 4 + b) * 16));
+                            int32_t acc = static_cast<int32_t>(r[jj * 4 + b]) + cv.w;
                             if (ASUM) acc -= asum_term;
                             y[b] = tc_requant<GENERAL>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
                         }
                         const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
-                        w[j] = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
+                        w[jj] = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
                     }
                     const int left = n_cols - c0;
-                    if (p.dbg_mode & 1) { if (w[0] + w[1] + w[2] + w[3] == 0x12345) orow[0] = 1; } else
-                    if (vec16 && left >= 16) {
+                    if (st_align == 16 && left >= 16) {
                         *reinterpret_cast<uint4 *>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                    } else if (st_align >= 8 && left >= 8) {
+                        *reinterpret_cast<uint2 *>(orow + c0) = make_uint2(w[0], w[1]);
+                        if (left >= 16) {
+                            *reinterpret_cast<uint2 *>(orow + c0 + 8) = make_uint2(w[2], w[3]);
+                        } else {
+#pragma unroll
+                            for (int b = 8; b < 16; ++b)
+                                if (b < left) orow[c0 + b] = static_cast<uint8_t>(w[b >> 2] >> (8 * (b & 3)));
+                        }
                     } else {
 #pragma unroll
                         for (int b = 0; b < 16; ++b)
                             if (b < left) orow[c0 + b] = static_cast<uint8_t>(w[b >> 2] >> (8 * (b & 3)));
                     }
                 }
+                cc += kColGroups;
+                while (cc >= cps) { cc -= cps; ++j; }
             }
             tc_fence_before();
             __syncwarp();
@@ -390,10 +438,12 @@ struct Im2colGeom {
     int32_t sy, sx, dy, dx, y0, x0;
     int32_t K, Kp;
     uint32_t fill;      // input zero point replicated in 4 bytes
+    const int2 *ktab;   // per reduction index k < Kp: {byte offset from the tap-(0,0) pixel, dy << 16 | (dx & 0xffff)}; offset < 0: padding
 };
 
-// One thread writes 16 output bytes.  VEC: cin % 16 == 0, so the 16 bytes are one aligned load.
-template <bool VEC>
+// One thread writes 16 output bytes.  GRAN = 16 / 8: cin is a multiple of GRAN, so the 16 bytes are 1 / 2 aligned
+// loads; GRAN = 1: any channel count, one byte at a time through the per-k offset table.
+template <int GRAN>
 __global__ void im2col_kernel(Im2colGeom g, const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int64_t total16) {
     const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (t >= total16) return;
@@ -404,32 +454,48 @@ __global__ void im2col_kernel(Im2colGeom g, const uint8_t *__restrict__ in, uint
     m /= g.ow;
     const int oy = static_cast<int>(m % g.oh);
     const int img = static_cast<int>(m / g.oh);
-    uint4 v;
-    if (VEC) {
-        v = make_uint4(0, 0, 0, 0);
+    const int by = oy * g.sy + g.y0, bx = ox * g.sx + g.x0;      // input pixel of tap (0, 0)
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (GRAN == 16) {
         if (k0 < g.K) {
             const int tap = k0 / g.cin, c = k0 - tap * g.cin;
             const int ky = tap / g.kw, kx = tap - ky * g.kw;
-            const int iy = oy * g.sy + ky * g.dy + g.y0, ix = ox * g.sx + kx * g.dx + g.x0;
+            const int iy = by + ky * g.dy, ix = bx + kx * g.dx;
             if (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w)
                 v = __ldg(reinterpret_cast<const uint4 *>(in + ((static_cast<int64_t>(img) * g.h + iy) * g.w + ix) * g.cin + c));
             else
                 v = make_uint4(g.fill, g.fill, g.fill, g.fill);
         }
+    } else if (GRAN == 8) {
+        uint2 h[2] = {make_uint2(0, 0), make_uint2(0, 0)};
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            const int k = k0 + 8 * s;
+            if (k < g.K) {
+                const int tap = k / g.cin, c = k - tap * g.cin;
+                const int ky = tap / g.kw, kx = tap - ky * g.kw;
+                const int iy = by + ky * g.dy, ix = bx + kx * g.dx;
+                if (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w)
+                    h[s] = __ldg(reinterpret_cast<const uint2 *>(in + ((static_cast<int64_t>(img) * g.h + iy) * g.w + ix) * g.cin + c));
+                else
+                    h[s] = make_uint2(g.fill, g.fill);
+            }
+        }
+        v = make_uint4(h[0].x, h[0].y, h[1].x, h[1].y);
     } else {
+        const uint8_t *base = in + ((static_cast<int64_t>(img) * g.h + by) * g.w + bx) * g.cin;
         uint32_t w[4] = {0, 0, 0, 0};
-        int tap = k0 / g.cin, c = k0 - tap * g.cin;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
+            const int2 e = __ldg(g.ktab + k0 + i);
             uint32_t b = 0;
+            const int dy = e.y >> 16, dx = static_cast<int16_t>(e.y & 0xffff);
             if (k0 + i < g.K) {
-                const int ky = tap / g.kw, kx = tap - ky * g.kw;
-                const int iy = oy * g.sy + ky * g.dy + g.y0, ix = ox * g.sx + kx * g.dx + g.x0;
+                const int iy = by + dy, ix = bx + dx;
                 b = g.fill & 0xff;
-                if (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w) b = __ldg(in + ((static_cast<int64_t>(img) * g.h + iy) * g.w + ix) * g.cin + c);
+                if (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w) b = __ldg(base + e.x);
             }
             w[i >> 2] |= b << (8 * (i & 3));
-            if (++c == g.cin) { c = 0; ++tap; }
         }
         v = make_uint4(w[0], w[1], w[2], w[3]);
     }
@@ -439,6 +505,14 @@ __global__ void im2col_kernel(Im2colGeom g, const uint8_t *__restrict__ in, uint
 // ------------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------------
+void launch_im2col(const Im2colGeom &ig, const void *in, uint8_t *dst, int64_t total16, unsigned blocks, cudaStream_t s) {
+    const uint8_t *src = static_cast<const uint8_t *>(in);
+    const uintptr_t a = reinterpret_cast<uintptr_t>(in);
+    if ((ig.cin & 15) == 0 && (a & 15) == 0) im2col_kernel<16><<<blocks, 256, 0, s>>>(ig, src, dst, total16);
+    else if ((ig.cin & 7) == 0 && (a & 7) == 0) im2col_kernel<8><<<blocks, 256, 0, s>>>(ig, src, dst, total16);
+    else if (ig.ktab) im2col_kernel<1><<<blocks, 256, 0, s>>>(ig, src, dst, total16);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -452,6 +526,7 @@ struct TcGemm {
     const void *map_a_ptr = nullptr;   // A pointer map_a was encoded for
     void *w_dev = nullptr;
     void *cols_dev = nullptr;
+    void *ktab_dev = nullptr;          // im2col offset table (byte-granular gather only)
     size_t smem_bytes = 0;
     int grid = 0;
     bool gather = false;               // A is gathered into scratch by im2col first
@@ -511,6 +586,11 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     p.bn_data = bn_data;
     p.bn_rows = bn_data + extra;
     p.k_blocks = (K + kBK - 1) / kBK;
+    p.group = kMaxBN / p.bn_rows;
+    if (p.group > p.tiles_m) p.group = p.tiles_m;
+    // keep at least ~2 work units per SM before widening the groups
+    while (p.group > 1 && static_cast<int64_t>((p.tiles_m + p.group - 1) / p.group) * tiles_n < 2ll * ctx->sm_count) --p.group;
+    p.tiles_mg = (p.tiles_m + p.group - 1) / p.group;
     const int32_t k_pad = p.k_blocks * kBK;
     p.idesc = (2u << 4) | (static_cast<uint32_t>(g.a_signed ? 1 : 0) << 7) | (1u << 10) |
               (static_cast<uint32_t>(p.bn_rows >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
@@ -569,13 +649,13 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         return ENN_B200_CUDA_FAILURE;
     }
     const size_t stage_bytes = static_cast<size_t>(kBM) * kBK + static_cast<size_t>(p.bn_rows) * kBK;
-    const size_t fixed = 4 * kMaxBN * sizeof(ColParam) + 256 + 1024;   // column constants, barriers, alignment slack
+    const size_t fixed = static_cast<size_t>(kEpiWarps) * kChunksPerWarp * 16 * sizeof(ColParam) + 256 + 1024;   // column constants, barriers, slack
     int stages = static_cast<int>((227 * 1024 - fixed) / stage_bytes);
     if (stages > 8) stages = 8;
     if (stages < 2) return ENN_B200_INVALID_PARAMS;
     p.stages = stages;
     gm->smem_bytes = stages * stage_bytes + fixed;
-    const int total_tiles = p.tiles_m * p.tiles_n;
+    const int total_tiles = p.tiles_mg * p.tiles_n;
     gm->grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
     return ENN_B200_SUCCESS;
 }
@@ -585,6 +665,7 @@ void free_plan(TcPlan *plan) {
     for (auto &gm : plan->gemms) {
         if (gm.w_dev) cudaFree(gm.w_dev);
         if (gm.cols_dev) cudaFree(gm.cols_dev);
+        if (gm.ktab_dev) cudaFree(gm.ktab_dev);
     }
     if (plan->scratch) cudaFree(plan->scratch);
     if (plan->err_host) cudaFreeHost(plan->err_host);
@@ -709,6 +790,25 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
     for (auto &gm : plan->gemms) {
         gm.prm.err = plan->err_dev;
         launches += gm.gather ? 2 : 1;
+        if (gm.gather) {   // the offset table also serves as the fallback for misaligned input pointers
+            // Byte-granular gather: per reduction index, the byte offset of (ky, kx, c) from the tap-(0,0) pixel
+            // and the tap's pixel displacement.
+            const Im2colGeom &ig = gm.ig;
+            std::vector<int2> tab(ig.Kp, make_int2(0, 0));
+            for (int32_t k = 0; k < ig.K; ++k) {
+                const int32_t tap = k / ig.cin, c = k - tap * ig.cin;
+                const int32_t ky = tap / ig.kw, kx = tap - ky * ig.kw;
+                const int32_t dy = ky * ig.dy, dx = kx * ig.dx;
+                tab[k].x = (dy * ig.w + dx) * ig.cin + c;
+                tab[k].y = (dy << 16) | (dx & 0xffff);
+            }
+            if (cudaMalloc(&gm.ktab_dev, tab.size() * sizeof(int2)) != cudaSuccess ||
+                cudaMemcpy(gm.ktab_dev, tab.data(), tab.size() * sizeof(int2), cudaMemcpyHostToDevice) != cudaSuccess) {
+                ctx->last_error = "tensor-core plan: offset table upload failed";
+                return bail(ENN_B200_CUDA_FAILURE);
+            }
+            gm.ig.ktab = static_cast<const int2 *>(gm.ktab_dev);
+        }
         if (gm.gather) {
             if (!encode_2d(ctx, &gm.map_a, plan->scratch, gm.ig.Kp, gm.prm.M, gm.ig.Kp, kBK, kBM)) {
                 ctx->last_error = "cuTensorMapEncodeTiled failed for the gathered activation matrix";
@@ -746,10 +846,7 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
         if (gm.gather) {
             const int64_t total16 = static_cast<int64_t>(p.M) * (gm.ig.Kp >> 4);
             const unsigned blocks = static_cast<unsigned>((total16 + 255) / 256);
-            if ((gm.ig.cin & 15) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0)
-                im2col_kernel<true><<<blocks, 256, 0, ctx->stream>>>(gm.ig, static_cast<const uint8_t *>(in), static_cast<uint8_t *>(plan->scratch), total16);
-            else
-                im2col_kernel<false><<<blocks, 256, 0, ctx->stream>>>(gm.ig, static_cast<const uint8_t *>(in), static_cast<uint8_t *>(plan->scratch), total16);
+            launch_im2col(gm.ig, in, static_cast<uint8_t *>(plan->scratch), total16, blocks, ctx->stream);
         } else {
             if ((reinterpret_cast<uintptr_t>(in) & 15) != 0) {
                 ctx->last_error = "tensor-core path needs a 16-byte aligned input pointer";
@@ -847,10 +944,7 @@ int32_t tc_execute_static(enn_b200_op *op, const void *in, void *out) {
         }
         const int64_t total16 = static_cast<int64_t>(p.M) * (gm.ig.Kp >> 4);
         const unsigned blocks = static_cast<unsigned>((total16 + 255) / 256);
-        if ((gm.ig.cin & 15) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0)
-            im2col_kernel<true><<<blocks, 256, 0, ctx->stream>>>(gm.ig, static_cast<const uint8_t *>(in), scratch, total16);
-        else
-            im2col_kernel<false><<<blocks, 256, 0, ctx->stream>>>(gm.ig, static_cast<const uint8_t *>(in), scratch, total16);
+        launch_im2col(gm.ig, in, scratch, total16, blocks, ctx->stream);
         p.out = static_cast<uint8_t *>(out);
         p.dbg = nullptr;
         p.dbg_mode = 0;
