@@ -1,5 +1,6 @@
 // extern "C" surface of the library: context / memory shim and operator prepare / execute / release.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -356,6 +357,9 @@ static int32_t conv_like_prepare(enn_b200_context *ctx, const enn_b200_conv_desc
             }
             op->dw_chan = dc;
             op->dw_w = dwp;
+            // TMA-staged variant (C % 16 == 0).  Measured on B200 it does not beat the register-streamed kernel (the
+            // depthwise path is bound by integer issue, not by load latency), so it is opt-in for experiments.
+            if (getenv("ENN_B200_DW_TMA")) dw_tma_plan(op);
         }
     }
     if (kind != OP_DEPTHWISE && tc_available(ctx)) {
@@ -512,6 +516,11 @@ int32_t enn_b200_op_execute(enn_b200_op *op, const void *in, void *out) {
             e = launch_deconv_direct(op->g, op->rq, in, op->w_direct, out, ctx->stream);
             break;
         case OP_DEPTHWISE:
+            if (op->dw_tma && op->impl == ENN_B200_IMPL_DEPTHWISE) {
+                e = dw_tma_launch(op, in, out);
+                if (e == cudaErrorLaunchFailure) return fail(ctx, ENN_B200_CUDA_FAILURE, "depthwise kernel gave up on a barrier wait earlier");
+                if (e != cudaErrorNotSupported) break;
+            }
             if (op->dw_chan && op->impl == ENN_B200_IMPL_DEPTHWISE) {
                 e = launch_dw3x3(op->g, op->dw_chan, op->dw_w, in, out, ctx->sm_count, ctx->stream);
                 break;
@@ -547,6 +556,7 @@ int32_t enn_b200_op_release(enn_b200_op *op) {
     if (!op) return ENN_B200_INVALID_PARAMS;
     if (op->ctx) cudaSetDevice(op->ctx->device);
     if (op->tc) tc_release(op);
+    if (op->dw_tma) dw_tma_release(op);
     for (void *p : op->owned) cudaFree(p);
     delete op;
     return ENN_B200_SUCCESS;

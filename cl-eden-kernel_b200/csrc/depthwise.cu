@@ -6,7 +6,10 @@
 //   dw3x3_kernel              3x3, stride 1 or 2, dilation 1, multiplier 1, C % 4 == 0, u8 activations: the
 //                             case every reference 3x3 variant (depthwise_conv_3x3s1_pad_merge, ..3x3s2..,
 //                             depthwise_conv_per_channel) covers and the one the benchmark configuration uses.
+#include <cuda.h>
+
 #include <cstdlib>
+#include <new>
 
 #include "internal.h"
 #include "requant.h"
@@ -326,10 +329,345 @@ dw3x3_kernel(ConvGeom g, const DwChan *__restrict__ chan, const uint32_t *__rest
     }
 }
 
+// ------------------------------------------------------------------------------------------------------
+// 3x3 fast path with TMA-staged input tiles (C % 16 == 0).
+//
+// A persistent CTA walks tiles of TH x (4 * NS) output pixels x CT channels.  The input window of a tile
+// (with its one-pixel halo) is fetched by ONE 4-D tensor-map copy into shared memory, double buffered, so the
+// copy of tile i+1 runs while tile i is computed; out-of-image positions arrive as zeros and are overwritten
+// with the input zero point before use.  Threads then run the same transposed-row / dp4a / fused requantisation
+// code as dw3x3_kernel, but every load is a shared-memory load at a compile-time offset: no per-load address
+// arithmetic, no border predicates, no global-load latency in the math loop.
+// Thread = (channel quad, strip of 4 output columns, row group); a row group owns R consecutive output rows.
+// ------------------------------------------------------------------------------------------------------
+struct DwTmaParams {
+    int32_t n, h, w, c, oh, ow, pt, pl;
+    int32_t ns, rg, r;            // strips per tile, row groups per tile, output rows per row group
+    int32_t th, wt;               // output rows / columns per tile (rg * r, 4 * ns)
+    int32_t win, hin;             // input window per tile (box extents in W and H)
+    int32_t tiles_x, tiles_y, cblks, total_tiles;
+    int32_t in_zp, w_zp, act_min, act_max;
+    uint32_t tile_bytes;          // bytes one tensor-map copy delivers (win * hin * CT)
+    uint32_t buf_pitch;           // distance between the two shared-memory buffers (tile_bytes rounded up to 128)
+    int32_t *err;                 // host-mapped error word
+};
+
+__device__ __forceinline__ uint32_t dw_smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ uint32_t dw_lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+template <int STRIDE, int CT, bool W_SIGNED, bool NEED_ASUM>
+__global__ void __launch_bounds__(256, 2)
+dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, DwTmaParams p, const DwChan *__restrict__ chan,
+                 const uint32_t *__restrict__ w_packed, uint8_t *__restrict__ out) {
+    extern __shared__ uint8_t dw_smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dw_smem_raw) + 127) & ~static_cast<uintptr_t>(127));
+    __shared__ uint64_t full_bar[2];
+    __shared__ int s_ok;
+    constexpr int QN = CT / 4;
+    constexpr int NP = STRIDE == 1 ? 6 : 9;
+    const int tid = threadIdx.x;
+    const int cq = tid % QN;
+    const int strip = (tid / QN) % p.ns;
+    const int rgi = tid / (QN * p.ns);
+    const uint32_t buf0 = dw_smem_u32(smem);
+    const uint32_t bar0 = dw_smem_u32(&full_bar[0]);
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + 8) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    auto tile_coords = [&](int tile, int &cb, int &img, int &ty, int &tx) {
+        tx = tile % p.tiles_x;
+        int t = tile / p.tiles_x;
+        ty = t % p.tiles_y;
+        t /= p.tiles_y;
+        img = t % p.n;
+        cb = t / p.n;              // channel block is the slowest index: a CTA keeps its weights for many tiles
+    };
+    auto issue = [&](int tile, int buf) {
+        int cb, img, ty, tx;
+        tile_coords(tile, cb, img, ty, tx);
+        const uint32_t bar = bar0 + 8 * buf;
+        const uint32_t dst = buf0 + buf * p.buf_pitch;
+        const int x = tx * p.wt * STRIDE - p.pl, y = ty * p.th * STRIDE - p.pt;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(p.tile_bytes) : "memory");
+        asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                     ::"r"(dst), "l"(&map_in), "r"(bar), "r"(cb * CT), "r"(x), "r"(y), "r"(img)
+                     : "memory");
+    };
+
+    uint32_t wlo[3][4], whi[3][4];
+    int32_t mult[4], addend[4], esh[4], bias[4];
+    int loaded_cb = -1;
+    const uint32_t zaw = (static_cast<uint32_t>(p.in_zp) & 0xff) * 0x01010101u;
+    const int32_t hi_clamp = p.act_max - p.act_min;
+    const uint32_t lo_word = (static_cast<uint32_t>(p.act_min) & 0xff) * 0x01010101u;
+    const uint32_t row_pitch = static_cast<uint32_t>(p.win) * CT;
+
+    int it = 0;
+    if (tid == 0 && static_cast<int>(blockIdx.x) < p.total_tiles) issue(blockIdx.x, 0);
+    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        int cb, img, ty, tx;
+        tile_coords(tile, cb, img, ty, tx);
+        // Prefetch the next tile into the other buffer (its last readers finished before the barrier that ended
+        // the previous iteration), then wait, bounded, for this tile.
+        if (tid == 0) {
+            const int next = tile + gridDim.x;
+            if (next < p.total_tiles) issue(next, buf ^ 1);
+            const uint32_t bar = bar0 + 8 * buf, parity = (it >> 1) & 1;
+            int ok = 0;
+            for (uint32_t i = 0; i < (1u << 24) && !ok; ++i) {
+                uint32_t done;
+                asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+                ok = done != 0;
+            }
+            if (!ok && p.err) *reinterpret_cast<volatile int32_t *>(p.err) = 7;
+            s_ok = ok;
+        }
+        __syncthreads();
+        if (!s_ok) break;            // uniform: every thread reads the same flag
+        {   // every thread observes the completed phase itself before touching the tile
+            uint32_t done;
+            asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                         : "=r"(done) : "r"(bar0 + 8 * buf), "r"((it >> 1) & 1) : "memory");
+            (void)done;
+        }
+        const uint32_t tbase = buf0 + buf * p.buf_pitch;
+        const int ix0 = tx * p.wt * STRIDE - p.pl, iy0 = ty * p.th * STRIDE - p.pt;
+        // Zero-filled positions outside the image become the input zero point (what the reference's pad kernel writes).
+        if (zaw != 0 && (ix0 < 0 || iy0 < 0 || ix0 + p.win > p.w || iy0 + p.hin > p.h)) {
+            for (int px = tid; px < p.win * p.hin; px += 256) {
+                const int ry = px / p.win, rx = px - ry * p.win;
+                if (iy0 + ry < 0 || iy0 + ry >= p.h || ix0 + rx < 0 || ix0 + rx >= p.w) {
+                    const uint32_t a = tbase + static_cast<uint32_t>(px) * CT;
+#pragma unroll
+                    for (int k = 0; k < CT; k += 16)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(a + k), "r"(zaw) : "memory");
+                }
+            }
+            __syncthreads();
+        }
+        if (cb != loaded_cb) {
+            loaded_cb = cb;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int ch = cb * CT + cq * 4 + c;
+                const DwChan v = chan[ch];
+                mult[c] = v.mult; addend[c] = v.addend; esh[c] = v.e; bias[c] = v.bias;
+#pragma unroll
+                for (int ky = 0; ky < 3; ++ky) {
+                    wlo[ky][c] = w_packed[ch * 3 + ky];
+                    whi[ky][c] = wlo[ky][c] << 8;
+                }
+            }
+        }
+        // This thread: output rows oy0 .. oy0 + r - 1 of the tile, columns ox0 .. ox0 + 3, channels cb*CT + cq*4 ..
+        const int oy0 = ty * p.th + rgi * p.r;
+        const int ox0 = tx * p.wt + strip * 4;
+        const int rows = min(p.r, p.oh - oy0);
+        if (rows > 0 && ox0 < p.ow) {
+            uint32_t omask = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (ox0 + j < p.ow) omask |= 1u << j;
+            // shared address of (local input row rgi*r*STRIDE, local pixel strip*4*STRIDE, channel quad)
+            uint32_t srow = tbase + (static_cast<uint32_t>(rgi * p.r * STRIDE) * p.win + static_cast<uint32_t>(strip * 4 * STRIDE)) * CT + cq * 4;
+            uint8_t *orow = out + ((static_cast<int64_t>(img) * p.oh + oy0) * p.ow + ox0) * static_cast<int64_t>(p.c) + cb * CT + cq * 4;
+            const uint32_t out_pitch = static_cast<uint32_t>(p.ow) * p.c;
+            const uint32_t cpix = static_cast<uint32_t>(p.c);
+
+            auto load_row = [&](DwRow<STRIDE> &r) {
+                DwRaw<STRIDE> raw;
+#pragma unroll
+                for (int i = 0; i < NP; ++i) raw.p[i] = dw_lds32(srow + i * CT);
+                srow += row_pitch;
+                dw_transpose_row<STRIDE>(r, raw);
+            };
+            auto emit = [&](const DwRow<STRIDE> &r0, const DwRow<STRIDE> &r1, const DwRow<STRIDE> &r2) {
+                int32_t acc[4][4];
+                int32_t asum[NEED_ASUM ? 4 : 1][4];
+                dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, true>(acc, asum, r0, wlo[0], whi[0], bias);
+                dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r1, wlo[1], whi[1], bias);
+                dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r2, wlo[2], whi[2], bias);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    int32_t y[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        int32_t a = acc[c][j];
+                        if (NEED_ASUM) a -= p.w_zp * asum[c][j];
+                        const int64_t pr = static_cast<int64_t>(a) * mult[c] + (1ll << 30);
+                        const int32_t x = static_cast<int32_t>(pr >> 31);
+                        const int32_t v = (x + addend[c] - static_cast<int32_t>(shr_clamp(static_cast<uint32_t>(x), esh[c] >> 8))) >> (esh[c] & 0xff);
+                        y[c] = __vimin_s32_relu(v, hi_clamp);
+                    }
+                    if (omask & (1u << j)) {
+                        const uint32_t hi = pack_sat_u8(y[3], y[2], 0);
+                        *reinterpret_cast<uint32_t *>(orow + static_cast<uint32_t>(j) * cpix) = pack_sat_u8(y[1], y[0], hi) + lo_word;
+                    }
+                }
+                orow += out_pitch;
+            };
+            DwRow<STRIDE> ra, rb, rc;
+            load_row(ra);
+            if constexpr (STRIDE == 1) {
+                load_row(rb);
+                for (int oy = 0; oy < rows; oy += 3) {
+                    load_row(rc);
+                    emit(ra, rb, rc);
+                    if (oy + 1 < rows) { load_row(ra); emit(rb, rc, ra); }
+                    if (oy + 2 < rows) { load_row(rb); emit(rc, ra, rb); }
+                }
+            } else {
+                for (int oy = 0; oy < rows; oy += 2) {
+                    load_row(rb);
+                    load_row(rc);
+                    emit(ra, rb, rc);
+                    if (oy + 1 < rows) { load_row(rb); load_row(ra); emit(rc, rb, ra); }
+                }
+            }
+        }
+        __syncthreads();             // all reads of this buffer are done before it is refilled two tiles later
+    }
+}
+
 bool dw3x3_eligible(const ConvGeom &g) {
     return g.kh == 3 && g.kw == 3 && g.dh == 1 && g.dw == 1 && g.groups == 1 && g.sh == g.sw && (g.sh == 1 || g.sh == 2) &&
            (g.cin % 4) == 0 && !g.a_signed;
 }
+
+typedef CUresult (*DwEncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DwTmaPlan {
+    DwTmaParams prm{};
+    int ct = 0;
+    int grid = 0;
+    size_t smem = 0;
+    CUtensorMap map{};
+    const void *map_ptr = nullptr;
+    int32_t *err_host = nullptr;
+    int32_t *err_dev = nullptr;
+};
+
+// Chooses the tile shape; returns false when the geometry is outside this kernel's domain.
+bool dw_tma_plan(enn_b200_op *op) {
+    const ConvGeom &g = op->g;
+    enn_b200_context *ctx = op->ctx;
+    if (!dw3x3_eligible(g) || (g.cin & 15) != 0 || !ctx->encode_tiled || ctx->cc_major != 10 || !op->dw_chan) return false;
+    if (g.n <= 0) return false;
+    DwTmaPlan *pl = new (std::nothrow) DwTmaPlan();
+    if (!pl) return false;
+    DwTmaParams &p = pl->prm;
+    const int s = g.sh;
+    pl->ct = (g.cin % 64 == 0) ? 64 : ((g.cin % 32 == 0) ? 32 : 16);
+    const int qn = pl->ct / 4;
+    int ns = 1;
+    while (ns < 8 && ns * 4 < g.ow) ns *= 2;
+    while (qn * ns > 256) ns /= 2;
+    const int rg = 256 / (qn * ns);
+    int r = (g.oh + rg - 1) / rg;
+    if (r > 8) r = 8;
+    if (r < 1) r = 1;
+    auto bytes_for = [&](int rr) {
+        const int th = rg * rr, wt = 4 * ns;
+        return static_cast<size_t>(wt * s + 3 - s) * (th * s + 3 - s) * pl->ct;
+    };
+    while (r > 1 && bytes_for(r) > 48 * 1024) --r;
+    if (bytes_for(r) > 100 * 1024) {
+        delete pl;
+        return false;
+    }
+    p.n = g.n; p.h = g.h; p.w = g.w; p.c = g.cin; p.oh = g.oh; p.ow = g.ow; p.pt = g.pt; p.pl = g.pl;
+    p.ns = ns; p.rg = rg; p.r = r; p.th = rg * r; p.wt = 4 * ns;
+    p.win = p.wt * s + 3 - s; p.hin = p.th * s + 3 - s;
+    p.tiles_x = (g.ow + p.wt - 1) / p.wt; p.tiles_y = (g.oh + p.th - 1) / p.th; p.cblks = g.cin / pl->ct;
+    const int64_t total = static_cast<int64_t>(p.tiles_x) * p.tiles_y * p.cblks * g.n;
+    if (total > INT32_MAX) {
+        delete pl;
+        return false;
+    }
+    p.total_tiles = static_cast<int32_t>(total);
+    p.in_zp = g.in_zp; p.w_zp = g.w_zp; p.act_min = g.act_min; p.act_max = g.act_max;
+    p.tile_bytes = static_cast<uint32_t>(bytes_for(r));
+    p.buf_pitch = (p.tile_bytes + 127u) & ~127u;
+    pl->smem = 2 * static_cast<size_t>(p.buf_pitch) + 128;
+    pl->grid = p.total_tiles < 2 * ctx->sm_count ? p.total_tiles : 2 * ctx->sm_count;
+    if (cudaHostAlloc(reinterpret_cast<void **>(&pl->err_host), sizeof(int32_t), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer(reinterpret_cast<void **>(&pl->err_dev), pl->err_host, 0) != cudaSuccess) {
+        if (pl->err_host) cudaFreeHost(pl->err_host);
+        delete pl;
+        return false;
+    }
+    *pl->err_host = 0;
+    p.err = pl->err_dev;
+    op->dw_tma = pl;
+    return true;
+}
+
+void dw_tma_release(enn_b200_op *op) {
+    DwTmaPlan *pl = static_cast<DwTmaPlan *>(op->dw_tma);
+    if (!pl) return;
+    if (pl->err_host) cudaFreeHost(pl->err_host);
+    delete pl;
+    op->dw_tma = nullptr;
+}
+
+template <int STRIDE, int CT>
+static cudaError_t dw_tma_launch_t(const DwTmaPlan *pl, const ConvGeom &g, const void *chan, const void *wp, void *out, cudaStream_t s) {
+    const DwChan *c = static_cast<const DwChan *>(chan);
+    const uint32_t *w = static_cast<const uint32_t *>(wp);
+    uint8_t *o = static_cast<uint8_t *>(out);
+    const bool asum = g.w_zp != 0;
+#define ENN_DWT(WS, AS)                                                                                                      \
+    do {                                                                                                                     \
+        cudaFuncSetAttribute(dw3x3_tma_kernel<STRIDE, CT, WS, AS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024); \
+        dw3x3_tma_kernel<STRIDE, CT, WS, AS><<<pl->grid, 256, pl->smem, s>>>(pl->map, pl->prm, c, w, o);                     \
+    } while (0)
+    if (g.w_signed) { if (asum) ENN_DWT(true, true); else ENN_DWT(true, false); }
+    else            { if (asum) ENN_DWT(false, true); else ENN_DWT(false, false); }
+#undef ENN_DWT
+    return cudaGetLastError();
+}
+
+// Returns cudaErrorNotSupported when the plan cannot be used for this call (misaligned input pointer).
+cudaError_t dw_tma_launch(enn_b200_op *op, const void *in, void *out) {
+    DwTmaPlan *pl = static_cast<DwTmaPlan *>(op->dw_tma);
+    enn_b200_context *ctx = op->ctx;
+    if (!pl || (reinterpret_cast<uintptr_t>(in) & 15) != 0) return cudaErrorNotSupported;
+    if (*pl->err_host != 0) return cudaErrorLaunchFailure;
+    const ConvGeom &g = op->g;
+    if (pl->map_ptr != in) {
+        DwEncodeTiledFn fn = reinterpret_cast<DwEncodeTiledFn>(ctx->encode_tiled);
+        cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.cin), static_cast<cuuint64_t>(g.w), static_cast<cuuint64_t>(g.h), static_cast<cuuint64_t>(g.n)};
+        cuuint64_t strides[3] = {static_cast<cuuint64_t>(g.cin), static_cast<cuuint64_t>(g.w) * g.cin, static_cast<cuuint64_t>(g.h) * g.w * g.cin};
+        cuuint32_t box[4] = {static_cast<cuuint32_t>(pl->ct), static_cast<cuuint32_t>(pl->prm.win), static_cast<cuuint32_t>(pl->prm.hin), 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        if (fn(&pl->map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(in), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorNotSupported;
+        pl->map_ptr = in;
+    }
+    cudaStream_t s = ctx->stream;
+    if (g.sh == 1) {
+        if (pl->ct == 64) return dw_tma_launch_t<1, 64>(pl, g, op->dw_chan, op->dw_w, out, s);
+        if (pl->ct == 32) return dw_tma_launch_t<1, 32>(pl, g, op->dw_chan, op->dw_w, out, s);
+        return dw_tma_launch_t<1, 16>(pl, g, op->dw_chan, op->dw_w, out, s);
+    }
+    if (pl->ct == 64) return dw_tma_launch_t<2, 64>(pl, g, op->dw_chan, op->dw_w, out, s);
+    if (pl->ct == 32) return dw_tma_launch_t<2, 32>(pl, g, op->dw_chan, op->dw_w, out, s);
+    return dw_tma_launch_t<2, 16>(pl, g, op->dw_chan, op->dw_w, out, s);
+}
+
 
 cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, const void *w_packed, const void *in, void *out,
                          int sm_count, cudaStream_t s) {

@@ -524,6 +524,11 @@ struct TcGemm {
     CUtensorMap map_b{};
     CUtensorMap map_a{};
     const void *map_a_ptr = nullptr;   // A pointer map_a was encoded for
+    // Small cache of activation maps for callers that alternate between a few input buffers.
+    static constexpr int kMapCache = 8;
+    CUtensorMap map_cache[kMapCache];
+    const void *map_cache_ptr[kMapCache] = {nullptr};
+    int map_cache_next = 0;
     void *w_dev = nullptr;
     void *cols_dev = nullptr;
     void *ktab_dev = nullptr;          // im2col offset table (byte-granular gather only)
@@ -853,10 +858,19 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
                 return ENN_B200_INVALID_PARAMS;
             }
             if (gm.map_a_ptr != in) {
-                if (!encode_2d(ctx, &gm.map_a, in, p.K, p.M, p.K, kBK, kBM)) {
-                    ctx->last_error = "cuTensorMapEncodeTiled failed for the activation tensor";
-                    return ENN_B200_CUDA_FAILURE;
+                int hit = -1;
+                for (int i = 0; i < TcGemm::kMapCache; ++i)
+                    if (gm.map_cache_ptr[i] == in) hit = i;
+                if (hit < 0) {
+                    hit = gm.map_cache_next;
+                    gm.map_cache_next = (gm.map_cache_next + 1) % TcGemm::kMapCache;
+                    if (!encode_2d(ctx, &gm.map_cache[hit], in, p.K, p.M, p.K, kBK, kBM)) {
+                        ctx->last_error = "cuTensorMapEncodeTiled failed for the activation tensor";
+                        return ENN_B200_CUDA_FAILURE;
+                    }
+                    gm.map_cache_ptr[hit] = in;
                 }
+                gm.map_a = gm.map_cache[hit];
                 gm.map_a_ptr = in;
             }
         }

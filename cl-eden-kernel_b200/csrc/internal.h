@@ -68,6 +68,7 @@ struct enn_b200_op {
     enn_b200_op_info_t info{};
     void *dw_chan = nullptr;           // depthwise 3x3 fast path: per-channel constants (in `owned`)
     void *dw_w = nullptr;              // depthwise 3x3 fast path: packed 3-tap weight words (in `owned`)
+    void *dw_tma = nullptr;            // depthwise TMA-tile plan (depthwise.cu), owned
     void *tc = nullptr;                // tensor-core plan (gemm_tc.cu), owned
 };
 
@@ -83,6 +84,9 @@ cudaError_t launch_depthwise(const ConvGeom &g, const Requant &rq, const void *i
 bool dw3x3_eligible(const ConvGeom &g);
 cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, const void *w_packed, const void *in, void *out,
                          int sm_count, cudaStream_t s);
+bool dw_tma_plan(enn_b200_op *op);
+cudaError_t dw_tma_launch(enn_b200_op *op, const void *in, void *out);
+void dw_tma_release(enn_b200_op *op);
 cudaError_t launch_add(const AddParams &p, int64_t count, const void *a, const void *b, void *out, int sm_count,
                        cudaStream_t s);
 cudaError_t launch_avgpool(const PoolGeom &p, const void *in, void *out, cudaStream_t s);

@@ -119,6 +119,18 @@ def test_depthwise_parity(enn, orc, ctx, name):
         op.release()
 
 
+@pytest.mark.parametrize("name", ["config2_s1", "config2_s2", "wide_c", "c960_7x7", "none_act_zp128", "s2_even"])
+def test_depthwise_tma_variant(enn, orc, ctx, name, monkeypatch):
+    """The opt-in TMA-staged depthwise kernel (ENN_B200_DW_TMA=1) on the cases with C % 16 == 0."""
+    monkeypatch.setenv("ENN_B200_DW_TMA", "1")
+    d, x, w, b, sc = cases.depthwise_case(seed=hash(name) % 1000, **DW_CASES[name])
+    op = enn.depthwise(ctx, d, w, b, sc)
+    try:
+        _check(op, orc.depthwise(d, x, w, b, sc), x)
+    finally:
+        op.release()
+
+
 DECONV_CASES = {
     "config4_small": dict(n=1, h=16, w=16),
     "ohwi": dict(n=2, h=6, w=5, cin=16, cout=8, layout=cases.enn.W_OHWI),
