@@ -15,10 +15,16 @@
 //     fixtures generated from that build (tests/golden/quant_host.json);
 //   * per-channel conv arithmetic is pinned by the reference known-answer test
 //     gpu_userdriver_test.cc:474-575 (tests/golden/kat_perchannel_conv.json);
-//   * kernel bodies (conv, depthwise, deconv col2im, avg-pool) are cross-checked against the reference's
-//     own kernel macros compiled as C++ (oracle/ref_shim.cpp -> oracle/_ref) where those macros compile.
-//   Per-tensor conv, depthwise, deconvolution and FullyConnected have no quantized golden vector in the
-//   reference's tests: for them parity is pinned by the restated kernel sources only.
+//   * the kernel restatements are pinned against the reference's OWN OpenCL C kernel text: oracle/ref_dump_kernels.cpp
+//     extracts the registered source strings at build time and oracle/ref_kernels_shim.cpp compiles them as C++ and
+//     replays the operators' host launch sequence.  Covered: conv_per_channel_quantized, depthwise_conv,
+//     depthwise_conv_per_channel, matrixTrans / weightAlign / convBackGemmRXR / PERCHANNELconvBackGemmRXR /
+//     convertBottomDiff2[_per_channel], avepooling_tflite, eltwiseAddQuantized_opt (live comparison where the reference
+//     tree is mounted, tests/golden/ref_kernels.npz elsewhere).
+//   * Not executed: the vectorised per-tensor conv kernels (quantizedGemmBlocked, direct3x3_8x4, gemm_block4x4: OpenCL
+//     vector types and ARM dot-product built-ins).  Per-tensor Conv2D is the same formula as the per-channel kernel
+//     with one multiplier and a weight zero point (ConvolutionKernels.cpp:956-1274 vs :1317-1375) and is pinned by the
+//     restated source only.  FullyConnected: see orc_fc / orc_fc_float below.
 #include <algorithm>
 #include <cmath>
 #include <cstdint>

@@ -134,3 +134,48 @@ def avgpool(desc, x):
 
 def num_threads():
     return lib.orc_num_threads()
+
+
+# ---- the reference's own kernel text compiled as C++ (oracle/ref_kernels_shim.cpp), when built ----
+def has_ref_kernels():
+    return ref is not None and hasattr(ref, "ref_has_kernels")
+
+
+def _ref_conv_like(fn, dims_fn, desc, x, w, bias, scales):
+    oh, ow = C.c_int32(), C.c_int32()
+    dims_fn(C.byref(desc), C.byref(oh), C.byref(ow))
+    x = np.ascontiguousarray(x)
+    w = np.ascontiguousarray(w)
+    bias = np.ascontiguousarray(bias, dtype=np.int32)
+    sc = np.ascontiguousarray(scales, dtype=np.float32) if scales is not None else None
+    out = np.empty((desc.n, oh.value, ow.value, desc.cout), dtype=np.uint8)
+    st = fn(C.byref(desc), _ptr(x), _ptr(w), _ptr(bias), _ptr(sc), _ptr(out))
+    if st:
+        raise ValueError(f"reference kernel wrapper rejected the case ({st})")
+    return out
+
+
+def ref_conv_per_channel(desc, x, w, bias, scales):
+    return _ref_conv_like(ref.ref_conv_per_channel, lib.orc_conv_out_dims, desc, x, w, bias, scales)
+
+
+def ref_depthwise(desc, x, w, bias, scales=None):
+    return _ref_conv_like(ref.ref_depthwise, lib.orc_conv_out_dims, desc, x, w, bias, scales)
+
+
+def ref_deconv(desc, x, w, bias, scales=None):
+    return _ref_conv_like(ref.ref_deconv, lib.orc_deconv_out_dims, desc, x, w, bias, scales)
+
+
+def ref_avgpool(desc, x):
+    x = np.ascontiguousarray(x)
+    out = np.empty((desc.n, desc.out_h, desc.out_w, desc.c), dtype=np.uint8)
+    assert ref.ref_avgpool(C.byref(desc), _ptr(x), _ptr(out)) == 0
+    return out
+
+
+def ref_add(desc, a, b):
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    out = np.empty(a.shape, dtype=np.uint8)
+    assert ref.ref_add(C.byref(desc), _ptr(a), _ptr(b), _ptr(out)) == 0
+    return out

@@ -1,0 +1,304 @@
+// Runs the REFERENCE's own OpenCL C kernel text on the CPU (test infrastructure only).
+//
+// oracle/ref_dump_kernels.cpp extracts, at build time, the source strings the reference registers for the
+// quantized kernels (operators/cl_kernels/*.cpp via common/CLKernels.hpp) into oracle/_ref/ref_kernels_gen.inc.
+// That text is plain C apart from a handful of OpenCL built-ins, which the prelude below supplies; the wrappers
+// replay the host launch sequence of the reference operators (argument order, global sizes, NCHW layout, the
+// zero-point padding pre-pass) and expose NHWC in / NHWC out entry points with the descriptor the oracle uses.
+// Requantisation parameters come from the reference's own host code (QuantizationUtil.cpp / KernelUtil.cpp).
+#include <algorithm>
+#include <climits>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+#include "../include/enn_b200.h"
+#include "userdriver/gpu/operators/cl_quantized_utils/KernelUtil.hpp"
+#include "userdriver/gpu/operators/cl_quantized_utils/QuantizationUtil.hpp"
+
+namespace ocl {
+
+// ---- OpenCL C compatibility prelude -------------------------------------------------------------------
+typedef unsigned char uchar;
+typedef unsigned int uint;
+static thread_local size_t g_id[3], g_size[3];
+static inline size_t get_global_id(int i) { return g_id[i]; }
+static inline size_t get_global_size(int i) { return g_size[i]; }
+#define __kernel static
+#define __global
+#undef max
+#undef min
+#define max(a, b) ((a) > (b) ? (a) : (b))
+#define min(a, b) ((a) < (b) ? (a) : (b))
+
+template <typename T>
+struct vec4 {
+    T s0, s1, s2, s3;
+    vec4() = default;
+    vec4(T v) : s0(v), s1(v), s2(v), s3(v) {}
+    vec4(T a, T b, T c, T d) : s0(a), s1(b), s2(c), s3(d) {}
+};
+typedef vec4<int> int4;
+typedef vec4<uchar> uchar4;
+typedef vec4<char> char4;
+static inline int4 operator+(const int4 &a, const int4 &b) { return int4(a.s0 + b.s0, a.s1 + b.s1, a.s2 + b.s2, a.s3 + b.s3); }
+static inline int4 operator*(const int4 &a, const int4 &b) { return int4(a.s0 * b.s0, a.s1 * b.s1, a.s2 * b.s2, a.s3 * b.s3); }
+static inline int4 &operator+=(int4 &a, const int4 &b) { a = a + b; return a; }
+template <typename T>
+static inline vec4<T> vload4(size_t off, const T *p) { return vec4<T>(p[4 * off], p[4 * off + 1], p[4 * off + 2], p[4 * off + 3]); }
+template <typename T>
+static inline int4 convert_int4(const vec4<T> &v) { return int4(v.s0, v.s1, v.s2, v.s3); }
+
+#include "_ref/ref_kernels_gen.inc"
+
+#undef max
+#undef min
+
+template <typename F>
+static void run3(size_t g0, size_t g1, size_t g2, F f) {
+    g_size[0] = g0; g_size[1] = g1; g_size[2] = g2;
+    for (size_t a = 0; a < g0; ++a)
+        for (size_t b = 0; b < g1; ++b)
+            for (size_t c = 0; c < g2; ++c) {
+                g_id[0] = a; g_id[1] = b; g_id[2] = c;
+                f();
+            }
+}
+
+}  // namespace ocl
+
+namespace {
+
+using enn::ud::gpu::CalculateActivationRangeUint8;
+using enn::ud::gpu::GetQuantizedConvolutionMultipler;
+using enn::ud::gpu::QuantizeMultiplierSmallerThanOneExp;
+
+ActivationInfo::ActivationType act_type(int a) {
+    switch (a) {
+        case ENN_B200_ACT_RELU: return ActivationInfo::ActivationType::RELU;
+        case ENN_B200_ACT_RELU1: return ActivationInfo::ActivationType::RELU1;
+        case ENN_B200_ACT_RELU6: return ActivationInfo::ActivationType::RELU6;
+        default: return ActivationInfo::ActivationType::NONE;
+    }
+}
+
+void act_range(const enn_b200_conv_desc *d, bool honour_disabled, int32_t *lo, int32_t *hi) {
+    if (honour_disabled && d->activation == ENN_B200_ACT_NONE) {   // `activation_info_.isEnabled() == false` branches
+        *lo = 0;
+        *hi = 255;
+        return;
+    }
+    CalculateActivationRangeUint8(act_type(d->activation), d->out_scale, d->out_zp, lo, hi);
+}
+
+// Per-channel multipliers as CLConvolutionPerChannelQuantized.cpp:87-99 (and the depthwise / deconv twins).
+void per_channel_params(const enn_b200_conv_desc *d, const float *scales, std::vector<int32_t> *m, std::vector<int32_t> *s) {
+    m->resize(d->cout);
+    s->resize(d->cout);
+    for (int i = 0; i < d->cout; ++i) {
+        double real = 0.0;
+        GetQuantizedConvolutionMultipler(d->in_scale, scales[i], d->in_scale * scales[i], d->out_scale, &real);
+        int sh = 0;
+        QuantizeMultiplierSmallerThanOneExp(real, &(*m)[i], &sh);
+        (*s)[i] = sh;
+    }
+}
+
+void per_tensor_params(const enn_b200_conv_desc *d, int32_t *m, int *s) {
+    double real = 0.0;
+    GetQuantizedConvolutionMultipler(d->in_scale, d->w_scale, d->bias_scale, d->out_scale, &real);
+    QuantizeMultiplierSmallerThanOneExp(real, m, s);
+}
+
+std::vector<uint8_t> nhwc_to_nchw(const uint8_t *x, int n, int h, int w, int c) {
+    std::vector<uint8_t> o(static_cast<size_t>(n) * c * h * w);
+    for (int b = 0; b < n; ++b)
+        for (int y = 0; y < h; ++y)
+            for (int xx = 0; xx < w; ++xx)
+                for (int k = 0; k < c; ++k) o[((static_cast<size_t>(b) * c + k) * h + y) * w + xx] = x[((static_cast<size_t>(b) * h + y) * w + xx) * c + k];
+    return o;
+}
+void nchw_to_nhwc(const std::vector<uint8_t> &x, uint8_t *o, int n, int h, int w, int c) {
+    for (int b = 0; b < n; ++b)
+        for (int k = 0; k < c; ++k)
+            for (int y = 0; y < h; ++y)
+                for (int xx = 0; xx < w; ++xx) o[((static_cast<size_t>(b) * h + y) * w + xx) * c + k] = x[((static_cast<size_t>(b) * c + k) * h + y) * w + xx];
+}
+int out_dim(int in, int p0, int p1, int k, int dil, int s) { return (in + p0 + p1 - ((k - 1) * dil + 1) + s) / s; }
+size_t align_to(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+extern "C" {
+
+// CLConvolutionPerChannelQuantized::execute (file lines 74-160) -> conv_per_channel_quantized.
+// Weights: OHWI (ANDROID_NN, converted to OIHW first as the operator does) or OIHW.  u8 activations, int8 weights.
+int32_t ref_conv_per_channel(const enn_b200_conv_desc *d, const uint8_t *in, const int8_t *w, const int32_t *bias, const float *scales,
+                             uint8_t *out) {
+    if (!d->per_channel || d->act_dtype != ENN_B200_U8 || d->dil_h > 1 || d->dil_w > 1) return 3;
+    const int g = d->groups > 0 ? d->groups : 1, cig = d->cin / g;
+    const int oh = out_dim(d->h, d->pad_t, d->pad_b, d->kh, 1, d->stride_h), ow = out_dim(d->w, d->pad_l, d->pad_r, d->kw, 1, d->stride_w);
+    std::vector<uint8_t> x = nhwc_to_nchw(in, d->n, d->h, d->w, d->cin);
+    std::vector<int8_t> wo(static_cast<size_t>(d->cout) * cig * d->kh * d->kw);
+    for (int o = 0; o < d->cout; ++o)
+        for (int i = 0; i < cig; ++i)
+            for (int ky = 0; ky < d->kh; ++ky)
+                for (int kx = 0; kx < d->kw; ++kx) {
+                    const size_t dst = ((static_cast<size_t>(o) * cig + i) * d->kh + ky) * d->kw + kx;
+                    wo[dst] = d->weight_layout == ENN_B200_W_OHWI ? w[((static_cast<size_t>(o) * d->kh + ky) * d->kw + kx) * cig + i] : w[dst];
+                }
+    std::vector<int32_t> m, s;
+    per_channel_params(d, scales, &m, &s);
+    int32_t lo, hi;
+    act_range(d, true, &lo, &hi);
+    std::vector<uint8_t> y(static_cast<size_t>(d->n) * d->cout * oh * ow);
+    for (int grp = 0; grp < g; ++grp)
+        ocl::run3(d->n, d->cout / g, static_cast<size_t>(oh) * ow, [&] {
+            ocl::conv_per_channel_quantized_INT8(x.data(), reinterpret_cast<const char *>(wo.data()), bias, m.data(), s.data(), y.data(), g, grp,
+                                                 d->kh, d->kw, d->stride_h, d->stride_w, d->pad_l, d->pad_t, d->cout, oh, ow, d->cin, d->h,
+                                                 d->w, -d->in_zp, 0, d->out_zp, lo, hi);
+        });
+    nchw_to_nhwc(y, out, d->n, oh, ow, d->cout);
+    return 0;
+}
+
+// CLDepthwiseConvolutionPerChannelQuantized::execute (file lines 99-264) and the general branch of
+// CLDepthwiseConvolutionQuantized: `pad` pre-pass with the input zero point, then depthwise_conv[_per_channel].
+// Weights [Cout][1][Kh][Kw] (OIHW) or [1][Kh][Kw][Cout] (ANDROID_NN, converted first).
+int32_t ref_depthwise(const enn_b200_conv_desc *d, const uint8_t *in, const void *w, const int32_t *bias, const float *scales,
+                      uint8_t *out) {
+    if (d->act_dtype != ENN_B200_U8 || d->dil_h > 1 || d->dil_w > 1) return 3;
+    const int dm = d->groups > 0 ? d->groups : 1;
+    const int oh = out_dim(d->h, d->pad_t, d->pad_b, d->kh, 1, d->stride_h), ow = out_dim(d->w, d->pad_l, d->pad_r, d->kw, 1, d->stride_w);
+    const int ph = d->h + d->pad_t + d->pad_b, pw = d->w + d->pad_l + d->pad_r;
+    std::vector<uint8_t> x = nhwc_to_nchw(in, d->n, d->h, d->w, d->cin);
+    std::vector<uint8_t> xp(static_cast<size_t>(d->n) * d->cin * ph * pw, static_cast<uint8_t>(d->in_zp));   // pad kernel: zero = input zero point
+    for (int b = 0; b < d->n * d->cin; ++b)
+        for (int yy = 0; yy < d->h; ++yy)
+            std::memcpy(&xp[(static_cast<size_t>(b) * ph + yy + d->pad_t) * pw + d->pad_l], &x[(static_cast<size_t>(b) * d->h + yy) * d->w], d->w);
+    std::vector<uint8_t> wo(static_cast<size_t>(d->cout) * d->kh * d->kw);
+    const uint8_t *wsrc = static_cast<const uint8_t *>(w);
+    for (int o = 0; o < d->cout; ++o)
+        for (int k = 0; k < d->kh * d->kw; ++k)
+            wo[static_cast<size_t>(o) * d->kh * d->kw + k] = d->weight_layout == ENN_B200_W_OHWI ? wsrc[static_cast<size_t>(k) * d->cout + o] : wsrc[static_cast<size_t>(o) * d->kh * d->kw + k];
+    std::vector<uint8_t> y(static_cast<size_t>(d->n) * d->cout * oh * ow);
+    int32_t lo, hi;
+    if (d->per_channel) {
+        std::vector<int32_t> m, s;
+        per_channel_params(d, scales, &m, &s);
+        act_range(d, true, &lo, &hi);
+        ocl::run3(d->n, d->cin, align_to(static_cast<size_t>(oh) * ow, 32), [&] {
+            ocl::depthwise_conv_per_channel_INT8(xp.data(), reinterpret_cast<const char *>(wo.data()), bias, y.data(), ph, pw, d->kh, d->kw,
+                                                 d->stride_h, d->stride_w, oh, ow, dm, -d->in_zp, -d->w_zp, d->out_zp, m.data(), s.data(), lo, hi);
+        });
+    } else {
+        int32_t m;
+        int s;
+        per_tensor_params(d, &m, &s);
+        s *= -1;   // CLDepthwiseConvolutionQuantized.cpp:223, undone inside the kernel
+        act_range(d, false, &lo, &hi);
+        ocl::run3(d->n, d->cin, align_to(static_cast<size_t>(oh) * ow, 32), [&] {
+            ocl::depthwise_conv_INT8(xp.data(), wo.data(), bias, y.data(), ph, pw, d->kh, d->kw, d->stride_h, d->stride_w, oh, ow, dm, -d->in_zp,
+                                     -d->w_zp, d->out_zp, m, s, lo, hi);
+        });
+    }
+    nchw_to_nhwc(y, out, d->n, oh, ow, d->cout);
+    return 0;
+}
+
+// CLDeconvolutionQuantized::execute (file lines 108-288) / CLDeconvolutionPerChannelQuantized::execute:
+// zero-point pre-filled aligned buffers, matrixTrans (or weightAlign for ANDROID_NN) of the filter, matrixTrans of
+// the input per batch, convBackGemmRXR per batch into the int32 column buffer, convertBottomDiff2.
+int32_t ref_deconv(const enn_b200_conv_desc *d, const uint8_t *in, const void *w, const int32_t *bias, const float *scales, uint8_t *out) {
+    if (d->act_dtype != ENN_B200_U8) return 3;
+    const int oh = d->out_h > 0 ? d->out_h : d->h * d->stride_h + d->kh - d->stride_h - d->pad_t - d->pad_b;
+    const int ow = d->out_w > 0 ? d->out_w : d->w * d->stride_w + d->kw - d->stride_w - d->pad_l - d->pad_r;
+    const uint32_t cin = d->cin, cout = d->cout, kk = d->kh * d->kw;
+    const uint32_t col = align_to(cin, 8), row_filter = kk * cout, row_input = d->h * d->w;
+    const uint32_t filter_align_height = align_to(row_filter, 8);
+    std::vector<uint8_t> x = nhwc_to_nchw(in, d->n, d->h, d->w, d->cin);
+    const uint8_t wfill = d->per_channel ? 0 : static_cast<uint8_t>(d->w_zp);
+    std::vector<uint8_t> fbuf(static_cast<size_t>(col) * filter_align_height, wfill);
+    std::vector<uint8_t> ibuf(static_cast<size_t>(d->n) * row_input * col, static_cast<uint8_t>(d->in_zp));
+    const uint8_t *wsrc = static_cast<const uint8_t *>(w);
+    if (d->weight_layout == ENN_B200_W_OHWI) {
+        ocl::run3(row_filter, cin, 1, [&] { ocl::weightAlign_INT8(wsrc, fbuf.data(), col, cin); });
+    } else {
+        ocl::run3(1, row_filter, cin, [&] { ocl::matrixTrans_INT8(wsrc, fbuf.data(), col, 0, 1); });
+    }
+    for (int b = 0; b < d->n; ++b) ocl::run3(1, row_input, cin, [&] { ocl::matrixTrans_INT8(x.data(), ibuf.data(), col, b, 1); });
+    std::vector<int32_t> cbuf(static_cast<size_t>(d->n) * row_input * row_filter, 0);
+    const size_t g1 = align_to((row_filter + 7) / 8, 4), g2 = align_to(row_input, 32);
+    for (int b = 0; b < d->n; ++b) {
+        if (d->per_channel)
+            ocl::run3(1, g1, g2, [&] {
+                ocl::PERCHANNELconvBackGemmRXR_INT8(reinterpret_cast<const char *>(fbuf.data()), ibuf.data(), cbuf.data(), row_filter, col, row_input, b, 1,
+                                                    -d->in_zp, 0);
+            });
+        else
+            ocl::run3(1, g1, g2, [&] {
+                ocl::convBackGemmRXR_INT8(fbuf.data(), ibuf.data(), cbuf.data(), row_filter, col, row_input, b, 1, -d->in_zp, -d->w_zp);
+            });
+    }
+    std::vector<uint8_t> y(static_cast<size_t>(d->n) * cout * oh * ow);
+    int32_t lo, hi;
+    CalculateActivationRangeUint8(act_type(d->activation), d->out_scale, d->out_zp, &lo, &hi);
+    if (d->per_channel) {
+        std::vector<int32_t> m, s;
+        per_channel_params(d, scales, &m, &s);
+        ocl::run3(static_cast<size_t>(d->n) * cout, align_to(oh, 4), align_to(ow, 32), [&] {
+            ocl::convertBottomDiff2_per_channel_INT8(cbuf.data(), bias, y.data(), oh, ow, cout, d->kh, d->kw, d->pad_t, d->pad_l, d->stride_h,
+                                                     d->stride_w, d->h, d->w, d->out_zp, m.data(), s.data(), lo, hi);
+        });
+    } else {
+        int32_t m;
+        int s;
+        per_tensor_params(d, &m, &s);
+        s *= -1;   // CLDeconvolutionQuantized.cpp:130
+        ocl::run3(static_cast<size_t>(d->n) * cout, align_to(oh, 4), align_to(ow, 32), [&] {
+            ocl::convertBottomDiff2_INT8(cbuf.data(), bias, y.data(), oh, ow, cout, d->kh, d->kw, d->pad_t, d->pad_l, d->stride_h, d->stride_w, d->h,
+                                         d->w, d->out_zp, m, s, lo, hi);
+        });
+    }
+    nchw_to_nhwc(y, out, d->n, oh, ow, cout);
+    return 0;
+}
+
+// CLAveragepool::averagepool_quant (CLAveragepool.cpp:175-224) -> avepooling_tflite.
+int32_t ref_avgpool(const enn_b200_pool_desc *d, const uint8_t *in, uint8_t *out) {
+    std::vector<uint8_t> x = nhwc_to_nchw(in, d->n, d->h, d->w, d->c);
+    std::vector<uint8_t> y(static_cast<size_t>(d->n) * d->c * d->out_h * d->out_w);
+    int32_t lo, hi;
+    CalculateActivationRangeUint8(act_type(d->activation), d->out_scale, d->out_zp, &lo, &hi);
+    ocl::run3(d->n, d->c, align_to(static_cast<size_t>(d->out_h) * d->out_w, 32), [&] {
+        ocl::avepooling_tflite_INT8(x.data(), y.data(), d->h, d->w, d->out_h, d->out_w, d->kh, d->kw, d->stride_h, d->stride_w, d->pad_t, d->pad_l,
+                                    hi, lo);
+    });
+    nchw_to_nhwc(y, out, d->n, d->out_h, d->out_w, d->c);
+    return 0;
+}
+
+// CLAddQuantized::execute (CLAddQuantized.cpp:70-165), u8 branch -> eltwiseAddQuantized_opt.
+int32_t ref_add(const enn_b200_add_desc *d, const uint8_t *a, const uint8_t *b, uint8_t *out) {
+    const int left_shift = 20;
+    const double twice_max_input_scale = 2 * std::max(d->in0_scale, d->in1_scale);
+    const double m0 = d->in0_scale / twice_max_input_scale, m1 = d->in1_scale / twice_max_input_scale;
+    const double mo = twice_max_input_scale / ((1 << left_shift) * d->out_scale);
+    int32_t q0, q1, qo;
+    int s0, s1, so;
+    QuantizeMultiplierSmallerThanOneExp(m0, &q0, &s0);
+    QuantizeMultiplierSmallerThanOneExp(m1, &q1, &s1);
+    QuantizeMultiplierSmallerThanOneExp(mo, &qo, &so);
+    int32_t lo = 0, hi = 255;
+    if (d->activation != ENN_B200_ACT_NONE) CalculateActivationRangeUint8(act_type(d->activation), d->out_scale, d->out_zp, &lo, &hi);
+    std::vector<uint8_t> ta(a, a + d->count), tb(b, b + d->count);
+    ocl::run3(1, static_cast<size_t>(d->count), 1, [&] {
+        ocl::eltwiseAddQuantized_opt_INT8(ta.data(), tb.data(), out, left_shift, -d->in0_zp, -d->in1_zp, d->out_zp, s0, s1, so, q0, q1, qo, lo, hi);
+    });
+    return 0;
+}
+
+int32_t ref_has_kernels(void) { return 1; }
+
+}  // extern "C"

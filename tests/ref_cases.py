@@ -1,0 +1,77 @@
+"""Seeded cases shared by the generator of tests/golden/ref_kernels.npz and the tests that replay them."""
+import numpy as np
+
+import cases
+
+enn = cases.enn
+
+
+def _pool(seed, n, h, w, c, k, s, act=0):
+    x = np.random.default_rng(seed).integers(0, 256, (n, h, w, c), dtype=np.int64).astype(np.uint8)
+    d = enn.PoolDesc(n=n, h=h, w=w, c=c, kh=k, kw=k, stride_h=s, stride_w=s, pad_t=0, pad_l=0, out_h=(h - k) // s + 1,
+                     out_w=(w - k) // s + 1, activation=act, act_dtype=enn.U8, out_scale=0.05, out_zp=10)
+    return d, x
+
+
+def _add(seed, count, act=0):
+    rng = np.random.default_rng(seed)
+    a = rng.integers(0, 256, count, dtype=np.int64).astype(np.uint8)
+    b = rng.integers(0, 256, count, dtype=np.int64).astype(np.uint8)
+    d = enn.AddDesc(count=count, activation=act, act_dtype=enn.U8, in0_scale=0.031, in0_zp=120, in1_scale=0.047, in1_zp=131,
+                    out_scale=0.06, out_zp=126)
+    return d, a, b
+
+
+CASES = {
+    "conv_pc_3x3": ("conv_pc", lambda: cases.conv_case(seed=101, n=2, h=9, w=10, cin=8, cout=12, k=3, per_channel=True, out_scale=0.2)),
+    "conv_pc_1x1_relu6": ("conv_pc", lambda: cases.conv_case(seed=102, n=1, h=7, w=7, cin=32, cout=16, k=1, per_channel=True, out_scale=0.1, out_zp=0)),
+    "conv_pc_s2_group": ("conv_pc", lambda: cases.conv_case(seed=103, n=1, h=11, w=9, cin=8, cout=8, k=3, stride=2, groups=2, per_channel=True,
+                                                               out_scale=0.15, layout=enn.W_OIHW, act=enn.ACT_NONE)),
+    "dw_pc_s1": ("dw", lambda: cases.depthwise_case(seed=104, n=2, h=12, w=12, c=8)),
+    "dw_pc_s2": ("dw", lambda: cases.depthwise_case(seed=105, n=1, h=13, w=11, c=12, stride=2)),
+    "dw_pt_s1": ("dw", lambda: cases.depthwise_case(seed=106, n=1, h=10, w=10, c=8, per_channel=False, out_scale=0.08, out_zp=3)),
+    "dw_pt_dm2_5x5": ("dw", lambda: cases.depthwise_case(seed=107, n=1, h=9, w=9, c=4, dm=2, k=5, per_channel=False, out_scale=0.2, out_zp=7,
+                                                           act=enn.ACT_NONE)),
+    "deconv_pt_4x4s2": ("deconv", lambda: cases.deconv_case(seed=108, n=2, h=6, w=5, cin=16, cout=8)),
+    "deconv_pt_ohwi_relu6": ("deconv", lambda: cases.deconv_case(seed=109, n=1, h=5, w=5, cin=8, cout=4, layout=enn.W_OHWI, act=enn.ACT_RELU6)),
+    "deconv_pc_3x3s2": ("deconv", lambda: cases.deconv_case(seed=110, n=1, h=5, w=6, cin=12, cout=8, k=3, stride=2, pad=0, per_channel=True,
+                                                              out_scale=0.5)),
+    "avgpool_7x7": ("pool", lambda: _pool(111, 2, 7, 7, 16, 7, 1)),
+    "avgpool_3x3s2": ("pool", lambda: _pool(112, 1, 9, 9, 8, 3, 2, act=enn.ACT_RELU6)),
+    "add": ("add", lambda: _add(113, 4099)),
+    "add_relu6": ("add", lambda: _add(114, 1000, act=enn.ACT_RELU6)),
+}
+
+
+def run_reference(orc, kind, case):
+    if kind == "conv_pc":
+        d, x, w, b, sc = case
+        return orc.ref_conv_per_channel(d, x, w, b, sc)
+    if kind == "dw":
+        d, x, w, b, sc = case
+        return orc.ref_depthwise(d, x, w, b, sc)
+    if kind == "deconv":
+        d, x, w, b, sc = case
+        return orc.ref_deconv(d, x, w, b, sc)
+    if kind == "pool":
+        d, x = case
+        return orc.ref_avgpool(d, x)
+    d, a, b = case
+    return orc.ref_add(d, a, b)
+
+
+def run_oracle(orc, kind, case):
+    if kind == "conv_pc":
+        d, x, w, b, sc = case
+        return orc.conv2d(d, x, w, b, sc)
+    if kind == "dw":
+        d, x, w, b, sc = case
+        return orc.depthwise(d, x, w, b, sc)
+    if kind == "deconv":
+        d, x, w, b, sc = case
+        return orc.deconv(d, x, w, b, sc)
+    if kind == "pool":
+        d, x = case
+        return orc.avgpool(d, x)
+    d, a, b = case
+    return orc.add(d, a, b)

@@ -323,3 +323,28 @@ def test_cpp_adapter_interface(enn):
                     "-Wl,-rpath," + pkg, "-Wl,-rpath," + os.path.join(root, "oracle"), "-fopenmp"], check=True, capture_output=True)
     r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "adapter test: OK" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("name", list(__import__("ref_cases").CASES))
+def test_library_matches_reference_kernel_text_golden(enn, ctx, name):
+    """The CUDA path through the C ABI against outputs of the reference's own kernel text (tests/golden/ref_kernels.npz)."""
+    import ref_cases
+    golden = np.load(os.path.join(HERE, "golden", "ref_kernels.npz"))[name]
+    kind, mk = ref_cases.CASES[name]
+    case = mk()
+    if kind in ("conv_pc", "dw", "deconv"):
+        d, x, w, b, sc = case
+        op = {"conv_pc": enn.conv2d, "dw": enn.depthwise, "deconv": enn.deconv}[kind](ctx, d, w, b, sc)
+        x2 = None
+    elif kind == "pool":
+        d, x = case
+        op, x2 = enn.avgpool(ctx, d), None
+    else:
+        d, x, x2 = case
+        op = enn.add(ctx, d)
+    try:
+        for impl in _impls(enn, op) if kind in ("conv_pc", "deconv") else [op.info.impl]:
+            op.set_impl(impl)
+            assert np.array_equal(op.run(x, x2), golden.reshape(-1)), (name, impl)
+    finally:
+        op.release()

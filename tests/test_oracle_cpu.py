@@ -186,3 +186,46 @@ def test_struct_sizes_match_header(enn):
     assert C.sizeof(enn.FcDesc) == 14 * 4
     assert C.sizeof(enn.AddDesc) == 8 + 8 * 4
     assert C.sizeof(enn.PoolDesc) == 16 * 4
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Outputs of the reference's own OpenCL C kernel text (compiled as C++ and run on the CPU when the reference tree
+# was mounted; tests/golden/gen_ref_kernels.py) pin the oracle's kernel restatements.
+# ---------------------------------------------------------------------------------------------------------
+import ref_cases  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def ref_golden():
+    return np.load(os.path.join(HERE, "golden", "ref_kernels.npz"))
+
+
+@pytest.mark.parametrize("name", list(ref_cases.CASES))
+def test_oracle_matches_reference_kernel_text_golden(orc, ref_golden, name):
+    kind, mk = ref_cases.CASES[name]
+    got = ref_cases.run_oracle(orc, kind, mk())
+    assert np.array_equal(got, ref_golden[name]), name
+
+
+def test_oracle_matches_reference_kernel_text_live(orc):
+    """Fresh random geometry against the live build of the reference kernels (this container only)."""
+    if not orc.has_ref_kernels():
+        pytest.skip("oracle/_ref kernel shim not built (reference tree absent)")
+    rng = np.random.default_rng(77)
+    for i in range(12):
+        h, w = int(rng.integers(3, 12)), int(rng.integers(3, 12))
+        stride = int(rng.integers(1, 3))
+        c = cases.conv_case(seed=200 + i, n=int(rng.integers(1, 3)), h=h, w=w, cin=int(rng.integers(1, 9)), cout=int(rng.integers(1, 9)),
+                            k=int(rng.choice([1, 3])), stride=stride, per_channel=True, out_scale=float(rng.uniform(0.05, 0.5)),
+                            out_zp=int(rng.integers(0, 256)), act=int(rng.integers(0, 4)))
+        assert np.array_equal(orc.conv2d(*c), orc.ref_conv_per_channel(*c))
+        for pc in (True, False):
+            dcase = cases.depthwise_case(seed=300 + i, n=1, h=h + 2, w=w + 2, c=int(rng.integers(1, 7)), stride=stride, per_channel=pc,
+                                         out_scale=float(rng.uniform(0.02, 0.2)), out_zp=int(rng.integers(0, 200)), act=int(rng.integers(0, 4)),
+                                         dm=int(rng.integers(1, 3)))
+            assert np.array_equal(orc.depthwise(*dcase), orc.ref_depthwise(*dcase))
+            k = int(rng.choice([2, 3, 4]))
+            tcase = cases.deconv_case(seed=400 + i, n=1, h=min(h, 6), w=min(w, 6), cin=int(rng.integers(1, 10)), cout=int(rng.integers(1, 6)), k=k,
+                                      stride=int(rng.integers(1, 3)), pad=int(rng.integers(0, 2)), per_channel=pc,
+                                      layout=int(rng.choice([cases.enn.W_IOHW, cases.enn.W_OHWI])), out_scale=float(rng.uniform(0.05, 0.6)))
+            assert np.array_equal(orc.deconv(*tcase), orc.ref_deconv(*tcase))
