@@ -370,7 +370,8 @@ static int32_t conv_like_prepare(enn_b200_context *ctx, const enn_b200_conv_desc
             return st;
         }
     }
-    op->info.impl = op->impl;
+    // The tensor-core plan may have chosen its weight-streaming GEMV for very small M; report that.
+    if (!(op->impl == ENN_B200_IMPL_TCGEN05 && op->info.impl == ENN_B200_IMPL_GEMV)) op->info.impl = op->impl;
     *out = op;
     return ENN_B200_SUCCESS;
 }
@@ -483,8 +484,9 @@ int32_t enn_b200_op_set_impl(enn_b200_op *op, int32_t impl) {
     if (op->kind == OP_CONV || op->kind == OP_FC || op->kind == OP_DECONV) {
         if (impl == ENN_B200_IMPL_DIRECT) {
             op->impl = impl;
-        } else if (impl == ENN_B200_IMPL_TCGEN05 && op->tc) {
-            op->impl = impl;
+        } else if ((impl == ENN_B200_IMPL_TCGEN05 || impl == ENN_B200_IMPL_GEMV) && op->tc) {
+            // GEMV is the tensor-core plan's own choice for M <= 8; both names select that plan.
+            op->impl = ENN_B200_IMPL_TCGEN05;
         } else {
             return fail(op->ctx, ENN_B200_INVALID_PARAMS, "kernel family not available for this op");
         }

@@ -424,6 +424,99 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------------------
+// GEMV for FullyConnected / 1x1 convolutions with very few rows (M <= 8): the contraction is bound by reading the
+// N x K weight matrix once from HBM, so tensor cores are not used.  A warp owns one output column: its lanes
+// stream that column's K bytes with 16-byte loads (the weights are the same K-major int8 tiles the tensor-core
+// kernel uses), multiply with dp4a against the activations held in shared memory, and reduce with shuffles.
+// The epilogue constants and the zero-point folding are the tensor-core kernel's (ColParam).
+// ------------------------------------------------------------------------------------------------------
+constexpr int kGemvMaxM = 8;
+constexpr int kGemvWarps = 8;
+
+template <bool A_SIGNED>
+__device__ __forceinline__ int32_t dp4a_as(uint32_t a, uint32_t w, int32_t c) {
+    int32_t d;
+    if (A_SIGNED)
+        asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(w), "r"(c));
+    else
+        asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(w), "r"(c));
+    return d;
+}
+
+template <bool A_SIGNED, int M>
+__global__ void __launch_bounds__(kGemvWarps * 32)
+gemv_kernel(const uint8_t *__restrict__ a, const int8_t *__restrict__ w, const ColParam *__restrict__ cols, uint8_t *__restrict__ out,
+            int N, int K, int k_pad, int bn_rows, int bn_data, int zw_eff, int out_zp, int act_min, int act_max) {
+    extern __shared__ uint4 gemv_smem[];            // M rows of K bytes
+    const int k16 = K >> 4;
+    for (int i = threadIdx.x; i < M * k16; i += blockDim.x) gemv_smem[i] = __ldg(reinterpret_cast<const uint4 *>(a) + i);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * kGemvWarps + warp;
+    if (n >= N) return;
+    const int tn = n / bn_data, r = n - tn * bn_data;
+    const uint4 *wrow = reinterpret_cast<const uint4 *>(w + (static_cast<size_t>(tn) * bn_rows + r) * k_pad);
+    int32_t acc[M], asum[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = asum[m] = 0;
+#pragma unroll 4
+    for (int i = lane; i < k16; i += 32) {
+        const uint4 wv = __ldg(wrow + i);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const uint4 av = gemv_smem[m * k16 + i];
+            acc[m] = dp4a_as<A_SIGNED>(av.x, wv.x, acc[m]);
+            acc[m] = dp4a_as<A_SIGNED>(av.y, wv.y, acc[m]);
+            acc[m] = dp4a_as<A_SIGNED>(av.z, wv.z, acc[m]);
+            acc[m] = dp4a_as<A_SIGNED>(av.w, wv.w, acc[m]);
+            if (zw_eff != 0) {
+                asum[m] = dp4a_as<A_SIGNED>(av.x, 0x01010101u, asum[m]);
+                asum[m] = dp4a_as<A_SIGNED>(av.y, 0x01010101u, asum[m]);
+                asum[m] = dp4a_as<A_SIGNED>(av.z, 0x01010101u, asum[m]);
+                asum[m] = dp4a_as<A_SIGNED>(av.w, 0x01010101u, asum[m]);
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], off);
+            asum[m] += __shfl_xor_sync(0xffffffffu, asum[m], off);
+        }
+    if (lane == 0) {
+        const ColParam c = cols[static_cast<size_t>(tn) * bn_rows + r];
+        const int4 cv = make_int4(c.mult, c.addend, c.esh, c.bias);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const int32_t v = acc[m] - zw_eff * asum[m] + c.bias;
+            out[static_cast<size_t>(m) * N + n] = static_cast<uint8_t>(tc_requant<true>(v, cv, act_max - act_min, out_zp, act_min, act_max) + act_min);
+        }
+    }
+}
+
+template <bool A_SIGNED>
+void launch_gemv(int M, const void *a, const void *w, const ColParam *cols, void *out, const TcParams &p, int k_pad, cudaStream_t s) {
+    const int blocks = (p.N + kGemvWarps - 1) / kGemvWarps;
+    const size_t smem = static_cast<size_t>(M) * p.K;
+#define ENN_GEMV(MM)                                                                                                          \
+    gemv_kernel<A_SIGNED, MM><<<blocks, kGemvWarps * 32, smem, s>>>(static_cast<const uint8_t *>(a), static_cast<const int8_t *>(w), cols, \
+                                                                   static_cast<uint8_t *>(out), p.N, p.K, k_pad, p.bn_rows, p.bn_data,     \
+                                                                   p.zw_eff, p.out_zp, p.act_min, p.act_max)
+    switch (M) {
+        case 1: ENN_GEMV(1); break;
+        case 2: ENN_GEMV(2); break;
+        case 3: ENN_GEMV(3); break;
+        case 4: ENN_GEMV(4); break;
+        case 5: ENN_GEMV(5); break;
+        case 6: ENN_GEMV(6); break;
+        case 7: ENN_GEMV(7); break;
+        default: ENN_GEMV(8); break;
+    }
+#undef ENN_GEMV
+}
+
+// ------------------------------------------------------------------------------------------------------
 // im2col: gathers the A operand of a convolution that the kernel above cannot read in place (taps, strides,
 // dilation, channel counts that are not a multiple of 16) into a [M][Kp] byte matrix in scratch memory.
 // Positions outside the image are written as the input zero point (the reference's pad kernels do the same,
@@ -535,6 +628,7 @@ struct TcGemm {
     size_t smem_bytes = 0;
     int grid = 0;
     bool gather = false;               // A is gathered into scratch by im2col first
+    bool use_gemv = false;             // M <= 8 read in place: weight-streaming GEMV instead of the tensor-core kernel
     Im2colGeom ig{};
     CUtensorMap map_a_static{};        // A map over the library's static scratch array (no-allocation entry point)
     const void *map_a_static_ptr = nullptr;
@@ -720,6 +814,8 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         gm.prm.qh = 1; gm.prm.qw = static_cast<int32_t>(M64);
         gm.prm.out_base = 0; gm.prm.out_sn = 0; gm.prm.out_sy = 0; gm.prm.out_sx = N;
         gm.gather = !in_place;
+        gm.use_gemv = in_place && M64 <= kGemvMaxM && (K & 15) == 0 && static_cast<size_t>(M64) * K <= 48 * 1024 && !getenv("ENN_B200_NO_GEMV");
+        if (gm.use_gemv) op->info.impl = ENN_B200_IMPL_GEMV;
         if (gm.gather) {
             Im2colGeom &ig = gm.ig;
             ig.n = g.n; ig.h = g.h; ig.w = g.w; ig.cin = cin;
@@ -856,6 +952,18 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
             if ((reinterpret_cast<uintptr_t>(in) & 15) != 0) {
                 ctx->last_error = "tensor-core path needs a 16-byte aligned input pointer";
                 return ENN_B200_INVALID_PARAMS;
+            }
+            if (gm.use_gemv) {
+                // few rows: HBM-bound on the weights, CUDA-core GEMV over the same packed weights and constants
+                const int k_pad = p.k_blocks * kBK;
+                if (p.a_signed) launch_gemv<true>(p.M, in, gm.w_dev, p.cols, out, p, k_pad, ctx->stream);
+                else launch_gemv<false>(p.M, in, gm.w_dev, p.cols, out, p, k_pad, ctx->stream);
+                cudaError_t ge = cudaGetLastError();
+                if (ge != cudaSuccess) {
+                    ctx->last_error = std::string("gemv_kernel launch: ") + cudaGetErrorString(ge);
+                    return ENN_B200_CUDA_FAILURE;
+                }
+                continue;
             }
             if (gm.map_a_ptr != in) {
                 int hit = -1;

@@ -170,6 +170,9 @@ FC_CASES = {
     "mixed_shift": dict(m=150, k=64, n=80, out_scale=0.0015),      # multipliers 0.013 .. 1.33: e >= 1, e == 0 and left shifts
     "mixed_shift_per_tensor": dict(m=150, k=32, n=40, per_channel=False, w_scale=0.05, out_scale=0.0012),
     "n24": dict(m=300, k=96, n=24),
+    "gemv_m1_k4096": dict(m=1, k=4096, n=1000),
+    "gemv_m3_per_tensor": dict(m=3, k=1280, n=77, per_channel=False),
+    "gemv_m8_mixed_shift": dict(m=8, k=64, n=80, out_scale=0.0015),
 }
 
 
