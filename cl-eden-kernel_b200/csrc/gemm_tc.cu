@@ -72,6 +72,13 @@ struct TcParams {
     // out + out_base + img * out_sn + qy * out_sy + qx * out_sx.  A plain [M][N] result uses qh = 1, qw = M.
     int32_t qh, qw;
     int64_t out_base, out_sn, out_sy, out_sx;
+    // Implicit-convolution mode (taps > 0): an M tile is a patch of conv_ht x conv_wt output positions of one image;
+    // k-block kb = (tap, channel chunk) and its A tile is the 4-D box {span channels, conv_wt, conv_ht, 1} of the
+    // (zero-point padded) NHWC input at (chunk * span, tx * conv_wt + tap_dx, ty * conv_ht + tap_dy, image).
+    int32_t taps, cchunks;
+    int32_t conv_ht, conv_wt, conv_ty, conv_tx;
+    int32_t span;           // bytes of K per k-block = swizzle span of both operand tiles: 128, 64 or 32
+    int16_t tap_dx[64], tap_dy[64];
     int32_t *err;           // host-mapped error word
     long long *dbg;         // optional per-CTA cycle counters [grid][8] (null in normal use)
     int32_t dbg_mode;       // development switches (0 in normal use)
@@ -116,6 +123,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
                  : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t c0, int32_t c1, int32_t c2, int32_t c3) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -154,13 +167,15 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 // K-major operand tile in shared memory, 128-byte rows, 128B swizzle: rows are 128 bytes apart, groups of 8
 // rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+// `span` = bytes per row = swizzle span (128 / 64 / 32): groups of 8 rows are 8 * span bytes apart and the layout
+// type is SWIZZLE_128B (2), SWIZZLE_64B (4) or SWIZZLE_32B (6).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t span = 128) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);        // start address, 16-byte units
     d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (unused for swizzled K-major)
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset
+    d |= static_cast<uint64_t>((8 * span) >> 4) << 32;              // stride byte offset
     d |= static_cast<uint64_t>(1) << 46;                            // descriptor version
-    d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B
+    d |= static_cast<uint64_t>(span == 128 ? 2 : (span == 64 ? 4 : 6)) << 61;
     return d;
 }
 
@@ -191,8 +206,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles.
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    const uint32_t a_bytes = kBM * kBK;
-    const uint32_t b_bytes = static_cast<uint32_t>(p.bn_rows) * kBK;
+    const uint32_t span = p.taps > 0 ? static_cast<uint32_t>(p.span) : kBK;
+    const uint32_t a_bytes = kBM * span;
+    const uint32_t b_bytes = static_cast<uint32_t>(p.bn_rows) * span;
     const uint32_t stage_bytes = a_bytes + b_bytes;     // both multiples of 1024
     uint8_t *tiles = smem;
     // Per-epilogue-warp copies of the N tile's column constants (kEpiWarps x 256 x 16 bytes): private to a warp, so
@@ -246,9 +262,21 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.err, 1)) { ok = false; break; }
                         t_wait += clock64() - t0;
                         const uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
-                        mbar_expect_tx(full0 + 8 * stage, stage_bytes);
-                        tma_load_2d(sa, &map_a, full0 + 8 * stage, kb * kBK, tm * kBM);
-                        tma_load_2d(sa + a_bytes, &map_b, full0 + 8 * stage, kb * kBK, tn * p.bn_rows);
+                        if (p.taps > 0) {
+                            // patch (img, ty, tx) of the output grid, tap and channel chunk of this k-block
+                            const int per_img = p.conv_ty * p.conv_tx;
+                            const int img = tm / per_img, rem = tm - img * per_img;
+                            const int ty = rem / p.conv_tx, tx = rem - ty * p.conv_tx;
+                            const int tap = kb / p.cchunks, cc = kb - tap * p.cchunks;
+                            mbar_expect_tx(full0 + 8 * stage, static_cast<uint32_t>(p.conv_ht * p.conv_wt) * span + b_bytes);
+                            tma_load_4d(sa, &map_a, full0 + 8 * stage, cc * static_cast<int>(span), tx * p.conv_wt + p.tap_dx[tap],
+                                        ty * p.conv_ht + p.tap_dy[tap], img);
+                            tma_load_2d(sa + a_bytes, &map_b, full0 + 8 * stage, kb * static_cast<int>(span), tn * p.bn_rows);
+                        } else {
+                            mbar_expect_tx(full0 + 8 * stage, stage_bytes);
+                            tma_load_2d(sa, &map_a, full0 + 8 * stage, kb * kBK, tm * kBM);
+                            tma_load_2d(sa + a_bytes, &map_b, full0 + 8 * stage, kb * kBK, tn * p.bn_rows);
+                        }
                         if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
                     }
                 }
@@ -285,8 +313,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         t_full += clock64() - t1;
                         tc_fence_after();
                         const uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
-                        const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + a_bytes);
-                        const int ksteps = min(4, (p.K - kb * kBK + 31) >> 5);
+                        const uint64_t da = make_smem_desc(sa, span), db = make_smem_desc(sa + a_bytes, span);
+                        const int ksteps = p.taps > 0 ? static_cast<int>(span >> 5) : min(4, (p.K - kb * kBK + 31) >> 5);
                         for (int k = 0; k < ksteps; ++k)
                             umma_i8(d_tmem, da + 2 * k, db + 2 * k, p.idesc, (kb | k) != 0);
                         umma_commit(empty0 + 8 * stage);      // frees the stage when these MMAs have read it
@@ -357,7 +385,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int m = (tg * p.group + j) * kBM + row_in_tile;
                     row_ok = m < p.M;
                     const int mq = row_ok ? m : 0;
-                    if (p.qh == 1) {
+                    if (p.taps > 0) {
+                        const int tm = tg * p.group + j;
+                        const int per_img = p.conv_ty * p.conv_tx;
+                        const int img = tm / per_img, rem = tm - img * per_img;
+                        const int ty = rem / p.conv_tx, tx = rem - ty * p.conv_tx;
+                        const int hy = row_in_tile / p.conv_wt, wx = row_in_tile - hy * p.conv_wt;
+                        const int qy = ty * p.conv_ht + hy, qx = tx * p.conv_wt + wx;
+                        row_ok = hy < p.conv_ht && qy < p.qh && qx < p.qw;
+                        orow = p.out + p.out_base + img * p.out_sn + (row_ok ? qy : 0) * p.out_sy + (row_ok ? qx : 0) * p.out_sx + n_base;
+                    } else if (p.qh == 1) {
                         orow = p.out + p.out_base + static_cast<int64_t>(mq) * p.out_sx + n_base;
                     } else {
                         const int img = mq / (p.qh * p.qw), rem = mq - img * (p.qh * p.qw);
@@ -598,6 +635,26 @@ __global__ void im2col_kernel(Im2colGeom g, const uint8_t *__restrict__ in, uint
 // ------------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------------
+// Copies an NHWC tensor into a larger one with `lo_y` / `lo_x` extra rows / columns before and extra ones after, filled
+// with the input zero point: what the reference's pad kernels produce (PadConvertKernels.cpp:241-373), so that the
+// tap boxes of the implicit convolution never meet a border.  One thread writes 16 bytes (C % 16 == 0).
+__global__ void pad_nhwc_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int n, int h, int w, int c, int hp, int wp, int lo_y,
+                                int lo_x, uint32_t fill, int64_t total16) {
+    const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= total16) return;
+    const int c16 = c >> 4;
+    const int cc = static_cast<int>(t % c16);
+    int64_t r = t / c16;
+    const int x = static_cast<int>(r % wp);
+    r /= wp;
+    const int y = static_cast<int>(r % hp);
+    const int img = static_cast<int>(r / hp);
+    const int iy = y - lo_y, ix = x - lo_x;
+    uint4 v = make_uint4(fill, fill, fill, fill);
+    if (iy >= 0 && iy < h && ix >= 0 && ix < w) v = __ldg(reinterpret_cast<const uint4 *>(in + ((static_cast<int64_t>(img) * h + iy) * w + ix) * c) + cc);
+    reinterpret_cast<uint4 *>(out)[t] = v;
+}
+
 void launch_im2col(const Im2colGeom &ig, const void *in, uint8_t *dst, int64_t total16, unsigned blocks, cudaStream_t s) {
     const uint8_t *src = static_cast<const uint8_t *>(in);
     const uintptr_t a = reinterpret_cast<uintptr_t>(in);
@@ -629,6 +686,11 @@ struct TcGemm {
     int grid = 0;
     bool gather = false;               // A is gathered into scratch by im2col first
     bool use_gemv = false;             // M <= 8 read in place: weight-streaming GEMV instead of the tensor-core kernel
+    // Implicit convolution (stride-1 taps read as TMA boxes, no gathered matrix): the source is either the caller's
+    // tensor (input zero point 0: the zero OOB fill is already right) or a zero-point padded copy in scratch.
+    bool implicit = false;
+    bool padded = false;
+    int32_t pad_lo_y = 0, pad_lo_x = 0, hp = 0, wp = 0;
     Im2colGeom ig{};
     CUtensorMap map_a_static{};        // A map over the library's static scratch array (no-allocation entry point)
     const void *map_a_static_ptr = nullptr;
@@ -642,6 +704,10 @@ struct TcPlan {
     int32_t *err_dev = nullptr;
 };
 
+CUtensorMapSwizzle swizzle_of(uint32_t span) {
+    return span == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (span == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
 bool encode_2d(enn_b200_context *ctx, CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint64_t pitch,
                uint32_t box_inner, uint32_t box_outer) {
     EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
@@ -651,8 +717,22 @@ bool encode_2d(enn_b200_context *ctx, CUtensorMap *map, const void *base, uint64
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_of(box_inner), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// NHWC activation tensor {C, W, H, N} with a box of {span channels, box_w, box_h, 1}.
+bool encode_nhwc(enn_b200_context *ctx, CUtensorMap *map, const void *base, uint64_t c, uint64_t w, uint64_t h, uint64_t n, uint32_t span,
+                 uint32_t box_w, uint32_t box_h) {
+    EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+    if (!fn) return false;
+    cuuint64_t dims[4] = {c, w, h, n};
+    cuuint64_t strides[3] = {c, w * c, h * w * c};
+    cuuint32_t box[4] = {span, box_w, box_h, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle_of(span), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 
@@ -664,7 +744,7 @@ struct QuantHost {   // host copies of what setup_quant uploaded
 // weight(n, k) returns the raw weight byte of output column n at reduction index k (k < K).
 template <typename WeightFn>
 int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh, int32_t M, int32_t N, int32_t K, WeightFn weight,
-                   TcGemm *gm) {
+                   TcGemm *gm, uint32_t span = kBK) {
     TcParams &p = gm->prm;
     p.M = M; p.N = N; p.K = K;
     const int32_t zw_eff = g.w_signed ? g.w_zp : g.w_zp - 128;   // weights as signed bytes: int8 stays, u8 becomes w - 128
@@ -743,11 +823,12 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         return ENN_B200_CUDA_FAILURE;
     }
     p.cols = static_cast<const ColParam *>(gm->cols_dev);
-    if (!encode_2d(ctx, &gm->map_b, gm->w_dev, k_pad, static_cast<uint64_t>(tiles_n) * p.bn_rows, k_pad, kBK, p.bn_rows)) {
+    if (!encode_2d(ctx, &gm->map_b, gm->w_dev, k_pad, static_cast<uint64_t>(tiles_n) * p.bn_rows, k_pad, span, p.bn_rows)) {
         ctx->last_error = "cuTensorMapEncodeTiled failed for the weight tensor";
         return ENN_B200_CUDA_FAILURE;
     }
-    const size_t stage_bytes = static_cast<size_t>(kBM) * kBK + static_cast<size_t>(p.bn_rows) * kBK;
+    if (span != kBK) p.k_blocks = K / static_cast<int32_t>(span);      // implicit convolution: one (tap, channel chunk) per k-block
+    const size_t stage_bytes = (static_cast<size_t>(kBM) + p.bn_rows) * span;
     const size_t fixed = static_cast<size_t>(kEpiWarps) * kChunksPerWarp * 16 * sizeof(ColParam) + 256 + 1024;   // column constants, barriers, slack
     int stages = static_cast<int>((227 * 1024 - fixed) / stage_bytes);
     if (stages > 8) stages = 8;
@@ -801,6 +882,64 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
     const uint32_t fill = (static_cast<uint32_t>(g.in_zp) & 0xff) * 0x01010101u;
     int32_t st = ENN_B200_SUCCESS;
 
+    // Decides how a GEMM whose A operand is described by `ig` (grid oh x ow per image, taps kh x kw) gets that operand and
+    // builds it: implicit convolution (stride-1 taps, Cin % 32 == 0) or gathered matrix.  `weight(n, k)` uses k = tap * cin + c.
+    auto make_conv_gemm = [&](TcGemm &gm, const Im2colGeom &ig, auto weight) -> int32_t {
+        const int32_t K = ig.kh * ig.kw * cin;
+        const int32_t taps = ig.kh * ig.kw;
+        uint32_t span = 0;
+        if (ig.sy == 1 && ig.sx == 1 && (cin & 31) == 0 && taps <= 64 && !getenv("ENN_B200_NO_IMPLICIT"))
+            span = (cin % 128 == 0) ? 128 : ((cin % 64 == 0) ? 64 : 32);
+        const int64_t M64 = static_cast<int64_t>(ig.n) * ig.oh * ig.ow;
+        if (M64 <= 0 || M64 > INT32_MAX) return ENN_B200_INVALID_PARAMS;
+        gm.ig = ig;
+        if (!span) {
+            int32_t st2 = build_gemm(ctx, g, qh, static_cast<int32_t>(M64), N, K, weight, &gm);
+            if (st2 != ENN_B200_SUCCESS) return st2;
+            gm.gather = true;
+            gm.ig.K = K; gm.ig.Kp = (K + 15) & ~15;
+            const size_t need = static_cast<size_t>(M64) * gm.ig.Kp;
+            if (need > plan->scratch_bytes) plan->scratch_bytes = need;
+            return ENN_B200_SUCCESS;
+        }
+        // patch of the output grid per M tile: as wide as the grid allows, rows to fill 128 accumulator rows
+        const int32_t wt = ig.ow < kBM ? ig.ow : kBM;
+        int32_t ht = kBM / wt;
+        if (ht > ig.oh) ht = ig.oh;
+        const int32_t tx = (ig.ow + wt - 1) / wt, ty = (ig.oh + ht - 1) / ht;
+        const int64_t tiles = static_cast<int64_t>(ig.n) * tx * ty;
+        if (tiles * kBM > INT32_MAX) return ENN_B200_INVALID_PARAMS;
+        int32_t st2 = build_gemm(ctx, g, qh, static_cast<int32_t>(tiles * kBM), N, K, weight, &gm, span);
+        if (st2 != ENN_B200_SUCCESS) return st2;
+        TcParams &p = gm.prm;
+        p.taps = taps; p.cchunks = cin / static_cast<int32_t>(span); p.span = static_cast<int32_t>(span);
+        p.conv_ht = ht; p.conv_wt = wt; p.conv_ty = ty; p.conv_tx = tx;
+        int32_t min_dy = 0, max_dy = 0, min_dx = 0, max_dx = 0;
+        for (int32_t ky = 0; ky < ig.kh; ++ky)
+            for (int32_t kx = 0; kx < ig.kw; ++kx) {
+                const int32_t dy = ky * ig.dy + ig.y0, dx = kx * ig.dx + ig.x0;
+                min_dy = dy < min_dy ? dy : min_dy; max_dy = dy > max_dy ? dy : max_dy;
+                min_dx = dx < min_dx ? dx : min_dx; max_dx = dx > max_dx ? dx : max_dx;
+            }
+        gm.implicit = true;
+        gm.padded = g.in_zp != 0;            // zero OOB fill already equals the zero point otherwise
+        gm.pad_lo_y = gm.padded ? -min_dy : 0;
+        gm.pad_lo_x = gm.padded ? -min_dx : 0;
+        const int32_t hi_y = ig.oh - 1 + max_dy - (ig.h - 1), hi_x = ig.ow - 1 + max_dx - (ig.w - 1);
+        gm.hp = gm.padded ? gm.pad_lo_y + ig.h + (hi_y > 0 ? hi_y : 0) : ig.h;
+        gm.wp = gm.padded ? gm.pad_lo_x + ig.w + (hi_x > 0 ? hi_x : 0) : ig.w;
+        for (int32_t ky = 0; ky < ig.kh; ++ky)
+            for (int32_t kx = 0; kx < ig.kw; ++kx) {
+                p.tap_dy[ky * ig.kw + kx] = static_cast<int16_t>(ky * ig.dy + ig.y0 + gm.pad_lo_y);
+                p.tap_dx[ky * ig.kw + kx] = static_cast<int16_t>(kx * ig.dx + ig.x0 + gm.pad_lo_x);
+            }
+        if (gm.padded) {
+            const size_t need = static_cast<size_t>(ig.n) * gm.hp * gm.wp * cin;
+            if (need > plan->scratch_bytes) plan->scratch_bytes = need;
+        }
+        return ENN_B200_SUCCESS;
+    };
+
     if (op->kind != OP_DECONV) {
         const int64_t M64 = static_cast<int64_t>(g.n) * g.oh * g.ow;
         if (M64 <= 0 || M64 > INT32_MAX) return bail(ENN_B200_INVALID_PARAMS);
@@ -809,26 +948,39 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
                               g.ow == g.w && (cin & 15) == 0;
         plan->gemms.resize(1);
         TcGemm &gm = plan->gemms[0];
-        st = build_gemm(ctx, g, qh, static_cast<int32_t>(M64), N, K, [&](int32_t n, int32_t k) { return w[static_cast<size_t>(k) * N + n]; }, &gm);
-        if (st != ENN_B200_SUCCESS) return bail(st);
-        gm.prm.qh = 1; gm.prm.qw = static_cast<int32_t>(M64);
-        gm.prm.out_base = 0; gm.prm.out_sn = 0; gm.prm.out_sy = 0; gm.prm.out_sx = N;
-        gm.gather = !in_place;
-        gm.use_gemv = in_place && M64 <= kGemvMaxM && (K & 15) == 0 && static_cast<size_t>(M64) * K <= 48 * 1024 && !getenv("ENN_B200_NO_GEMV");
-        if (gm.use_gemv) op->info.impl = ENN_B200_IMPL_GEMV;
-        if (gm.gather) {
-            Im2colGeom &ig = gm.ig;
+        auto weight = [&](int32_t n, int32_t k) { return w[static_cast<size_t>(k) * N + n]; };
+        if (in_place) {
+            st = build_gemm(ctx, g, qh, static_cast<int32_t>(M64), N, K, weight, &gm);
+            if (st != ENN_B200_SUCCESS) return bail(st);
+            gm.use_gemv = M64 <= kGemvMaxM && (K & 15) == 0 && static_cast<size_t>(M64) * K <= 48 * 1024 && !getenv("ENN_B200_NO_GEMV");
+            if (gm.use_gemv) op->info.impl = ENN_B200_IMPL_GEMV;
+            gm.prm.qh = 1; gm.prm.qw = static_cast<int32_t>(M64);
+            gm.prm.out_base = 0; gm.prm.out_sn = 0; gm.prm.out_sy = 0; gm.prm.out_sx = N;
+        } else {
+            Im2colGeom ig{};
             ig.n = g.n; ig.h = g.h; ig.w = g.w; ig.cin = cin;
             ig.oh = g.oh; ig.ow = g.ow; ig.kh = g.kh; ig.kw = g.kw;
             ig.sy = g.sh; ig.sx = g.sw; ig.dy = g.dh; ig.dx = g.dw; ig.y0 = -g.pt; ig.x0 = -g.pl;
-            ig.K = K; ig.Kp = (K + 15) & ~15; ig.fill = fill;
-            plan->scratch_bytes = static_cast<size_t>(M64) * ig.Kp;
+            ig.fill = fill;
+            st = make_conv_gemm(gm, ig, weight);
+            if (st != ENN_B200_SUCCESS) return bail(st);
+            if (gm.implicit) {
+                gm.prm.qh = g.oh; gm.prm.qw = g.ow;
+                gm.prm.out_base = 0;
+                gm.prm.out_sn = static_cast<int64_t>(g.oh) * g.ow * N;
+                gm.prm.out_sy = static_cast<int64_t>(g.ow) * N;
+                gm.prm.out_sx = N;
+            } else {
+                gm.prm.qh = 1; gm.prm.qw = static_cast<int32_t>(M64);
+                gm.prm.out_base = 0; gm.prm.out_sn = 0; gm.prm.out_sy = 0; gm.prm.out_sx = N;
+            }
         }
     } else {
         // Transposed convolution (DeconvolutionKernels.cpp:24-198) split by output parity: outputs with
         // (oy + pad_t) % sh == py only ever meet kernel rows ky = py + sh * jy, so each class (py, px) is a
         // stride-1 correlation over the input with its own small filter:
         //   out[n, sh*q - pad_t + py, ...] = sum_{jy,jx,c} in[n, q - jy, r - jx, c] * w[c][co][py + sh*jy][px + sw*jx].
+        plan->gemms.reserve(static_cast<size_t>(g.sh) * g.sw);
         for (int32_t py = 0; py < g.sh; ++py) {
             for (int32_t px = 0; px < g.sw; ++px) {
                 const int32_t jy_n = py < g.kh ? (g.kh - py + g.sh - 1) / g.sh : 0;
@@ -840,24 +992,24 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
                 const int32_t r_hi = (g.ow - 1 + g.pl - px) >= 0 ? (g.ow - 1 + g.pl - px) / g.sw : -1;
                 const int32_t qh_n = q_hi - q_lo + 1, qw_n = r_hi - r_lo + 1;
                 if (qh_n <= 0 || qw_n <= 0) continue;
-                const int64_t M64 = static_cast<int64_t>(g.n) * qh_n * qw_n;
-                if (M64 > INT32_MAX) return bail(ENN_B200_INVALID_PARAMS);
                 // A class without taps (stride larger than the kernel) still has outputs: requant(bias).  One
                 // zero-weight dummy tap keeps it on the same code path.
                 const int32_t jy_e = jy_n > 0 ? jy_n : 1, jx_e = jx_n > 0 ? jx_n : 1;
                 const bool empty = jy_n == 0 || jx_n == 0;
-                const int32_t K = jy_e * jx_e * cin;
                 plan->gemms.emplace_back();
                 TcGemm &gm = plan->gemms.back();
-                st = build_gemm(ctx, g, qh, static_cast<int32_t>(M64), N, K,
-                                [&](int32_t n, int32_t k) -> uint8_t {
-                                    const int32_t tap = k / cin, c = k - tap * cin;
-                                    const int32_t jy = tap / jx_e, jx = tap - jy * jx_e;
-                                    if (empty) return g.w_signed ? static_cast<uint8_t>(g.w_zp) : static_cast<uint8_t>(g.w_zp);
-                                    const int32_t ky = py + g.sh * jy, kx = px + g.sw * jx;
-                                    return w[((static_cast<size_t>(ky) * g.kw + kx) * cin + c) * N + n];
-                                },
-                                &gm);
+                Im2colGeom ig{};
+                ig.n = g.n; ig.h = g.h; ig.w = g.w; ig.cin = cin;
+                ig.oh = qh_n; ig.ow = qw_n; ig.kh = jy_e; ig.kw = jx_e;
+                ig.sy = 1; ig.sx = 1; ig.dy = -1; ig.dx = -1; ig.y0 = q_lo; ig.x0 = r_lo;
+                ig.fill = fill;
+                st = make_conv_gemm(gm, ig, [&](int32_t n, int32_t k) -> uint8_t {
+                    const int32_t tap = k / cin, c = k - tap * cin;
+                    const int32_t jy = tap / jx_e, jx = tap - jy * jx_e;
+                    if (empty) return static_cast<uint8_t>(g.w_zp);
+                    const int32_t ky = py + g.sh * jy, kx = px + g.sw * jx;
+                    return w[((static_cast<size_t>(ky) * g.kw + kx) * cin + c) * N + n];
+                });
                 if (st != ENN_B200_SUCCESS) return bail(st);
                 gm.prm.qh = qh_n; gm.prm.qw = qw_n;
                 const int32_t oy0 = g.sh * q_lo - g.pt + py, ox0 = g.sw * r_lo - g.pl + px;
@@ -865,14 +1017,6 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
                 gm.prm.out_sn = static_cast<int64_t>(g.oh) * g.ow * N;
                 gm.prm.out_sy = static_cast<int64_t>(g.sh) * g.ow * N;
                 gm.prm.out_sx = static_cast<int64_t>(g.sw) * N;
-                gm.gather = true;
-                Im2colGeom &ig = gm.ig;
-                ig.n = g.n; ig.h = g.h; ig.w = g.w; ig.cin = cin;
-                ig.oh = qh_n; ig.ow = qw_n; ig.kh = jy_e; ig.kw = jx_e;
-                ig.sy = 1; ig.sx = 1; ig.dy = -1; ig.dx = -1; ig.y0 = q_lo; ig.x0 = r_lo;
-                ig.K = K; ig.Kp = (K + 15) & ~15; ig.fill = fill;
-                const size_t need = static_cast<size_t>(M64) * ig.Kp;
-                if (need > plan->scratch_bytes) plan->scratch_bytes = need;
             }
         }
         if (plan->gemms.empty()) return bail(ENN_B200_INVALID_PARAMS);
@@ -890,7 +1034,14 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
     int launches = 0;
     for (auto &gm : plan->gemms) {
         gm.prm.err = plan->err_dev;
-        launches += gm.gather ? 2 : 1;
+        launches += (gm.gather || (gm.implicit && gm.padded)) ? 2 : 1;
+        if (gm.implicit && gm.padded) {
+            if (!encode_nhwc(ctx, &gm.map_a, plan->scratch, cin, gm.wp, gm.hp, g.n, gm.prm.span, gm.prm.conv_wt, gm.prm.conv_ht)) {
+                ctx->last_error = "cuTensorMapEncodeTiled failed for the padded activation tensor";
+                return bail(ENN_B200_CUDA_FAILURE);
+            }
+            gm.map_a_ptr = plan->scratch;
+        }
         if (gm.gather) {   // the offset table also serves as the fallback for misaligned input pointers
             // Byte-granular gather: per reduction index, the byte offset of (ky, kx, c) from the tap-(0,0) pixel
             // and the tap's pixel displacement.
@@ -948,6 +1099,24 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
             const int64_t total16 = static_cast<int64_t>(p.M) * (gm.ig.Kp >> 4);
             const unsigned blocks = static_cast<unsigned>((total16 + 255) / 256);
             launch_im2col(gm.ig, in, static_cast<uint8_t *>(plan->scratch), total16, blocks, ctx->stream);
+        } else if (gm.implicit) {
+            if ((reinterpret_cast<uintptr_t>(in) & 15) != 0) {
+                ctx->last_error = "tensor-core path needs a 16-byte aligned input pointer";
+                return ENN_B200_INVALID_PARAMS;
+            }
+            const Im2colGeom &ig = gm.ig;
+            if (gm.padded) {
+                const int64_t total16 = static_cast<int64_t>(ig.n) * gm.hp * gm.wp * (ig.cin >> 4);
+                pad_nhwc_kernel<<<static_cast<unsigned>((total16 + 255) / 256), 256, 0, ctx->stream>>>(
+                    static_cast<const uint8_t *>(in), static_cast<uint8_t *>(plan->scratch), ig.n, ig.h, ig.w, ig.cin, gm.hp, gm.wp, gm.pad_lo_y,
+                    gm.pad_lo_x, ig.fill, total16);
+            } else if (gm.map_a_ptr != in) {
+                if (!encode_nhwc(ctx, &gm.map_a, in, ig.cin, ig.w, ig.h, ig.n, p.span, p.conv_wt, p.conv_ht)) {
+                    ctx->last_error = "cuTensorMapEncodeTiled failed for the activation tensor";
+                    return ENN_B200_CUDA_FAILURE;
+                }
+                gm.map_a_ptr = in;
+            }
         } else {
             if ((reinterpret_cast<uintptr_t>(in) & 15) != 0) {
                 ctx->last_error = "tensor-core path needs a 16-byte aligned input pointer";
@@ -1025,7 +1194,7 @@ int32_t tc_execute_static(enn_b200_op *op, const void *in, void *out) {
     size_t need = 0;
     for (auto &gm : plan->gemms) {
         if (!gm.gather) {
-            ctx->last_error = "enn_b200_op_execute_noalloc: this operator reads its input in place and uses no scratch; call enn_b200_op_execute";
+            ctx->last_error = "enn_b200_op_execute_noalloc: this operator has no gathered input matrix; call enn_b200_op_execute";
             return ENN_B200_INVALID_PARAMS;
         }
         const size_t bytes = static_cast<size_t>(gm.prm.M) * gm.ig.Kp;

@@ -47,6 +47,14 @@ CONV_CASES = {
     "signed_act": dict(n=1, h=8, w=8, cin=8, cout=8, k=3, act_dtype=cases.enn.S8, in_zp=-3, out_zp=5, per_channel=True, out_scale=0.2),
     "big_multiplier": dict(n=1, h=6, w=6, cin=4, cout=4, k=1, in_scale=0.5, w_scale=0.5, out_scale=0.05, w_zp=3),
     "batch_stem_like": dict(n=2, h=32, w=32, cin=3, cout=32, k=3, stride=2, per_channel=True, out_scale=0.1),
+    # implicit (tap-box) convolutions: swizzle spans 128 / 64 / 32, ragged grids, dilation, zero and non-zero input zero point
+    "implicit_c128": dict(n=2, h=20, w=17, cin=128, cout=48, k=3),
+    "implicit_c64_56": dict(n=2, h=56, w=56, cin=64, cout=64, k=3),
+    "implicit_c32_dil": dict(n=1, h=19, w=23, cin=32, cout=16, k=3, dil=2),
+    "implicit_zp0": dict(n=1, h=15, w=15, cin=64, cout=32, k=3, in_zp=0, per_channel=True, out_scale=0.4),
+    "implicit_wide": dict(n=1, h=5, w=150, cin=32, cout=32, k=3),
+    "implicit_5x5_valid": dict(n=1, h=12, w=12, cin=32, cout=24, k=5, pad="valid"),
+    "implicit_c96": dict(n=1, h=9, w=9, cin=96, cout=40, k=3),
 }
 
 
@@ -139,6 +147,9 @@ DECONV_CASES = {
     "k2_s2": dict(n=1, h=7, w=9, cin=8, cout=4, k=2, stride=2, pad=0),
     "s1": dict(n=1, h=6, w=6, cin=8, cout=8, k=3, stride=1, pad=1),
     "relu6": dict(n=1, h=5, w=5, cin=4, cout=4, act=cases.enn.ACT_RELU6),
+    "implicit_config4_small": dict(n=2, h=16, w=16, cin=128, cout=64),
+    "implicit_c32_k3": dict(n=1, h=9, w=7, cin=32, cout=16, k=3, stride=2, pad=0),
+    "implicit_c64_s3": dict(n=1, h=6, w=6, cin=64, cout=16, k=4, stride=3, pad=1),
 }
 
 
