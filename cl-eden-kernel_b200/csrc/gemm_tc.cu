@@ -60,6 +60,7 @@ struct TcParams {
     int32_t bn_rows;        // B rows per N tile in shared memory (= UMMA N), multiple of 16
     int32_t bn_data;        // real output columns per N tile
     int32_t stages;
+    int32_t kpack;          // k-blocks that share one pipeline stage (one barrier round trip per kpack k-blocks)
     int32_t need_asum;      // 1: column bn_data of each accumulator tile holds sum_k a
     int32_t zw_eff;         // zw'
     int32_t a_signed;
@@ -209,7 +210,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t span = p.taps > 0 ? static_cast<uint32_t>(p.span) : kBK;
     const uint32_t a_bytes = kBM * span;
     const uint32_t b_bytes = static_cast<uint32_t>(p.bn_rows) * span;
-    const uint32_t stage_bytes = a_bytes + b_bytes;     // both multiples of 1024
+    const uint32_t kb_bytes = a_bytes + b_bytes;                      // one k-block: A tile then B tile
+    const uint32_t stage_bytes = kb_bytes * static_cast<uint32_t>(p.kpack);
     uint8_t *tiles = smem;
     // Per-epilogue-warp copies of the N tile's column constants (kEpiWarps x 256 x 16 bytes): private to a warp, so
     // refreshing them needs only a warp-level sync.
@@ -257,25 +259,35 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int nsub = min(p.group, p.tiles_m - tg * p.group);
                 for (int j = 0; j < nsub && ok; ++j) {
                     const int tm = tg * p.group + j;
-                    for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    int img = 0, ty = 0, tx = 0;
+                    if (p.taps > 0) {       // patch (img, ty, tx) of the output grid
+                        const int per_img = p.conv_ty * p.conv_tx;
+                        img = tm / per_img;
+                        const int rem = tm - img * per_img;
+                        ty = rem / p.conv_tx;
+                        tx = rem - ty * p.conv_tx;
+                    }
+                    int tap = 0, cc = 0;
+                    for (int kb0 = 0; kb0 < p.k_blocks; kb0 += p.kpack) {
+                        const int nkb = min(p.kpack, p.k_blocks - kb0);
                         const long long t0 = clock64();
                         if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.err, 1)) { ok = false; break; }
                         t_wait += clock64() - t0;
-                        const uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
+                        const uint32_t bar = full0 + 8 * stage;
+                        uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
                         if (p.taps > 0) {
-                            // patch (img, ty, tx) of the output grid, tap and channel chunk of this k-block
-                            const int per_img = p.conv_ty * p.conv_tx;
-                            const int img = tm / per_img, rem = tm - img * per_img;
-                            const int ty = rem / p.conv_tx, tx = rem - ty * p.conv_tx;
-                            const int tap = kb / p.cchunks, cc = kb - tap * p.cchunks;
-                            mbar_expect_tx(full0 + 8 * stage, static_cast<uint32_t>(p.conv_ht * p.conv_wt) * span + b_bytes);
-                            tma_load_4d(sa, &map_a, full0 + 8 * stage, cc * static_cast<int>(span), tx * p.conv_wt + p.tap_dx[tap],
-                                        ty * p.conv_ht + p.tap_dy[tap], img);
-                            tma_load_2d(sa + a_bytes, &map_b, full0 + 8 * stage, kb * static_cast<int>(span), tn * p.bn_rows);
+                            mbar_expect_tx(bar, (static_cast<uint32_t>(p.conv_ht * p.conv_wt) * span + b_bytes) * nkb);
+                            for (int q = 0; q < nkb; ++q, sa += kb_bytes) {
+                                tma_load_4d(sa, &map_a, bar, cc * static_cast<int>(span), tx * p.conv_wt + p.tap_dx[tap], ty * p.conv_ht + p.tap_dy[tap], img);
+                                tma_load_2d(sa + a_bytes, &map_b, bar, (kb0 + q) * static_cast<int>(span), tn * p.bn_rows);
+                                if (++cc == p.cchunks) { cc = 0; ++tap; }
+                            }
                         } else {
-                            mbar_expect_tx(full0 + 8 * stage, stage_bytes);
-                            tma_load_2d(sa, &map_a, full0 + 8 * stage, kb * kBK, tm * kBM);
-                            tma_load_2d(sa + a_bytes, &map_b, full0 + 8 * stage, kb * kBK, tn * p.bn_rows);
+                            mbar_expect_tx(bar, kb_bytes * nkb);
+                            for (int q = 0; q < nkb; ++q, sa += kb_bytes) {
+                                tma_load_2d(sa, &map_a, bar, (kb0 + q) * kBK, tm * kBM);
+                                tma_load_2d(sa + a_bytes, &map_b, bar, (kb0 + q) * kBK, tn * p.bn_rows);
+                            }
                         }
                         if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
                     }
@@ -307,16 +319,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int nsub = min(p.group, p.tiles_m - tg * p.group);
                 for (int j = 0; j < nsub && ok; ++j) {
                     const uint32_t d_tmem = tmem_base + ab * kMaxBN + j * p.bn_rows;
-                    for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    for (int kb0 = 0; kb0 < p.k_blocks; kb0 += p.kpack) {
+                        const int nkb = min(p.kpack, p.k_blocks - kb0);
                         const long long t1 = clock64();
                         if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.err, 3)) { ok = false; break; }
                         t_full += clock64() - t1;
                         tc_fence_after();
-                        const uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
-                        const uint64_t da = make_smem_desc(sa, span), db = make_smem_desc(sa + a_bytes, span);
-                        const int ksteps = p.taps > 0 ? static_cast<int>(span >> 5) : min(4, (p.K - kb * kBK + 31) >> 5);
-                        for (int k = 0; k < ksteps; ++k)
-                            umma_i8(d_tmem, da + 2 * k, db + 2 * k, p.idesc, (kb | k) != 0);
+                        uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
+                        for (int q = 0; q < nkb; ++q, sa += kb_bytes) {
+                            const uint64_t da = make_smem_desc(sa, span), db = make_smem_desc(sa + a_bytes, span);
+                            const int kb = kb0 + q;
+                            const int ksteps = p.taps > 0 ? static_cast<int>(span >> 5) : min(4, (p.K - kb * kBK + 31) >> 5);
+                            for (int k = 0; k < ksteps; ++k)
+                                umma_i8(d_tmem, da + 2 * k, db + 2 * k, p.idesc, (kb | k) != 0);
+                        }
                         umma_commit(empty0 + 8 * stage);      // frees the stage when these MMAs have read it
                         if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
                     }
@@ -690,6 +706,7 @@ struct TcGemm {
     // tensor (input zero point 0: the zero OOB fill is already right) or a zero-point padded copy in scratch.
     bool implicit = false;
     bool padded = false;
+    bool runs_pad = false;             // this GEMM launches the pad pass (the first padded GEMM of the operator)
     int32_t pad_lo_y = 0, pad_lo_x = 0, hp = 0, wp = 0;
     Im2colGeom ig{};
     CUtensorMap map_a_static{};        // A map over the library's static scratch array (no-allocation entry point)
@@ -828,7 +845,13 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         return ENN_B200_CUDA_FAILURE;
     }
     if (span != kBK) p.k_blocks = K / static_cast<int32_t>(span);      // implicit convolution: one (tap, channel chunk) per k-block
-    const size_t stage_bytes = (static_cast<size_t>(kBM) + p.bn_rows) * span;
+    // Several small k-blocks share a pipeline stage so that a barrier round trip covers ~32 KB of operands.
+    const size_t kb_bytes = (static_cast<size_t>(kBM) + p.bn_rows) * span;
+    p.kpack = static_cast<int32_t>((32 * 1024) / kb_bytes);
+    if (p.kpack < 1) p.kpack = 1;
+    if (p.kpack > p.k_blocks) p.kpack = p.k_blocks;
+    if (p.kpack > 8) p.kpack = 8;
+    const size_t stage_bytes = kb_bytes * p.kpack;
     const size_t fixed = static_cast<size_t>(kEpiWarps) * kChunksPerWarp * 16 * sizeof(ColParam) + 256 + 1024;   // column constants, barriers, slack
     int stages = static_cast<int>((227 * 1024 - fixed) / stage_bytes);
     if (stages > 8) stages = 8;
@@ -1022,6 +1045,35 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         if (plan->gemms.empty()) return bail(ENN_B200_INVALID_PARAMS);
     }
 
+    {   // All implicit GEMMs of an operator read the same input: one padded copy with the union of their margins.
+        int32_t lo_y = 0, lo_x = 0, hi_y = 0, hi_x = 0;
+        bool any = false;
+        for (auto &gm : plan->gemms)
+            if (gm.implicit && gm.padded) {
+                any = true;
+                lo_y = gm.pad_lo_y > lo_y ? gm.pad_lo_y : lo_y;
+                lo_x = gm.pad_lo_x > lo_x ? gm.pad_lo_x : lo_x;
+                const int32_t hy = gm.hp - gm.pad_lo_y - g.h, hx = gm.wp - gm.pad_lo_x - g.w;
+                hi_y = hy > hi_y ? hy : hi_y;
+                hi_x = hx > hi_x ? hx : hi_x;
+            }
+        if (any) {
+            bool first = true;
+            for (auto &gm : plan->gemms)
+                if (gm.implicit && gm.padded) {
+                    for (int32_t t = 0; t < gm.prm.taps; ++t) {
+                        gm.prm.tap_dy[t] = static_cast<int16_t>(gm.prm.tap_dy[t] + lo_y - gm.pad_lo_y);
+                        gm.prm.tap_dx[t] = static_cast<int16_t>(gm.prm.tap_dx[t] + lo_x - gm.pad_lo_x);
+                    }
+                    gm.pad_lo_y = lo_y; gm.pad_lo_x = lo_x;
+                    gm.hp = lo_y + g.h + hi_y; gm.wp = lo_x + g.w + hi_x;
+                    gm.runs_pad = first;
+                    first = false;
+                    const size_t need = static_cast<size_t>(g.n) * gm.hp * gm.wp * cin;
+                    if (need > plan->scratch_bytes) plan->scratch_bytes = need;
+                }
+        }
+    }
     if (plan->scratch_bytes > (static_cast<size_t>(8) << 30)) return bail(ENN_B200_INVALID_PARAMS);   // keep the direct kernel
     cudaError_t e;
     if ((plan->scratch_bytes && (e = cudaMalloc(&plan->scratch, plan->scratch_bytes)) != cudaSuccess) ||
@@ -1034,7 +1086,7 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
     int launches = 0;
     for (auto &gm : plan->gemms) {
         gm.prm.err = plan->err_dev;
-        launches += (gm.gather || (gm.implicit && gm.padded)) ? 2 : 1;
+        launches += (gm.gather || (gm.implicit && gm.runs_pad)) ? 2 : 1;
         if (gm.implicit && gm.padded) {
             if (!encode_nhwc(ctx, &gm.map_a, plan->scratch, cin, gm.wp, gm.hp, g.n, gm.prm.span, gm.prm.conv_wt, gm.prm.conv_ht)) {
                 ctx->last_error = "cuTensorMapEncodeTiled failed for the padded activation tensor";
@@ -1105,7 +1157,9 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
                 return ENN_B200_INVALID_PARAMS;
             }
             const Im2colGeom &ig = gm.ig;
-            if (gm.padded) {
+            if (gm.padded && !gm.runs_pad) {
+                // the padded copy was written by an earlier GEMM of this operator in the same execute
+            } else if (gm.padded) {
                 const int64_t total16 = static_cast<int64_t>(ig.n) * gm.hp * gm.wp * (ig.cin >> 4);
                 pad_nhwc_kernel<<<static_cast<unsigned>((total16 + 255) / 256), 256, 0, ctx->stream>>>(
                     static_cast<const uint8_t *>(in), static_cast<uint8_t *>(plan->scratch), ig.n, ig.h, ig.w, ig.cin, gm.hp, gm.wp, gm.pad_lo_y,
@@ -1153,12 +1207,25 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
         }
         p.out = static_cast<uint8_t *>(out);
         p.dbg_mode = getenv("ENN_B200_TC_MODE") ? atoi(getenv("ENN_B200_TC_MODE")) : 0;
+        static long long *dbg_buf = nullptr;
+        const bool dbg = getenv("ENN_B200_TC_DEBUG") != nullptr;     // development aid: role wait-cycle counters of CTA 0
+        if (dbg) {
+            if (!dbg_buf) cudaMallocManaged(&dbg_buf, sizeof(long long) * 8 * 1024);
+            p.dbg = dbg_buf;
+        }
         if (p.need_asum) {
             if (p.general) tc_gemm_kernel<true, true><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a, gm.map_b, p);
             else tc_gemm_kernel<true, false><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a, gm.map_b, p);
         } else {
             if (p.general) tc_gemm_kernel<false, true><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a, gm.map_b, p);
             else tc_gemm_kernel<false, false><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a, gm.map_b, p);
+        }
+        if (dbg) {
+            cudaStreamSynchronize(ctx->stream);
+            const long long *d = p.dbg;
+            std::fprintf(stderr, "tc dbg cta0: tiles %d x %d (group %d) k_blocks %d stages %d | producer wait %lld / %lld | mma full-wait %lld tempty-wait %lld / %lld | epi tfull-wait %lld / %lld\n",
+                         p.tiles_m, p.tiles_n, p.group, p.k_blocks, p.stages, d[0], d[1], d[2], d[3], d[4], d[5], d[6]);
+            p.dbg = nullptr;
         }
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) {
