@@ -778,6 +778,19 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     while (static_cast<int64_t>(p.tiles_m) * tiles_n < ctx->sm_count && (N + tiles_n) / (tiles_n + 1) >= 32) ++tiles_n;
     int32_t bn_data = (((N + tiles_n - 1) / tiles_n) + 15) & ~15;
     tiles_n = (N + bn_data - 1) / bn_data;
+    if (static_cast<int64_t>(p.tiles_m) * tiles_n > ctx->sm_count && bn_data >= 128) {
+        // Several waves of tiles: a slightly narrower tile can save a whole wave (time ~ waves x tile width).
+        int64_t best = ((static_cast<int64_t>(p.tiles_m) * tiles_n + ctx->sm_count - 1) / ctx->sm_count) * bn_data;
+        for (int32_t cand = bn_data - 16; cand >= bn_data - 64 && cand >= 128; cand -= 16) {
+            const int32_t tn = (N + cand - 1) / cand;
+            const int64_t cost = ((static_cast<int64_t>(p.tiles_m) * tn + ctx->sm_count - 1) / ctx->sm_count) * cand;
+            if (cost < best) {
+                best = cost;
+                bn_data = cand;
+                tiles_n = tn;
+            }
+        }
+    }
     p.tiles_n = tiles_n;
     p.bn_data = bn_data;
     p.bn_rows = bn_data + extra;
