@@ -106,6 +106,8 @@ PROTOTYPES = {
     "enn_b200_oplist_finalize": (C.c_int32, [_P]),
     "enn_b200_oplist_execute": (C.c_int32, [_P, C.POINTER(_P), C.POINTER(_P)]),
     "enn_b200_oplist_execute_device": (C.c_int32, [_P]),
+    "enn_b200_oplist_submit": (C.c_int32, [_P, C.POINTER(_P), C.POINTER(_P)]),
+    "enn_b200_oplist_wait": (C.c_int32, [_P]),
     "enn_b200_oplist_tensor_ptr": (C.c_int32, [_P, C.c_int32, C.POINTER(_P)]),
     "enn_b200_oplist_stats": (C.c_int32, [_P, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "enn_b200_oplist_destroy": (C.c_int32, [_P]),
@@ -332,6 +334,14 @@ class OpList:
         a = (C.c_void_p * len(in_ptrs))(*in_ptrs)
         b = (C.c_void_p * len(out_ptrs))(*out_ptrs)
         self.ctx.check(lib.enn_b200_oplist_execute(self.h, a, b))
+
+    def submit_host_ptrs(self, in_ptrs, out_ptrs):
+        a = (C.c_void_p * len(in_ptrs))(*in_ptrs)
+        b = (C.c_void_p * len(out_ptrs))(*out_ptrs)
+        self.ctx.check(lib.enn_b200_oplist_submit(self.h, a, b))
+
+    def wait(self):
+        self.ctx.check(lib.enn_b200_oplist_wait(self.h))
 
     def execute(self, inputs):
         """inputs: list of numpy arrays; returns list of uint8 arrays (flat)."""

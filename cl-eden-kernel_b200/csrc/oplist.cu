@@ -21,6 +21,7 @@ struct enn_b200_oplist {
     struct Tensor {
         int64_t bytes = 0;
         void *dev = nullptr;
+        void *dev_alt = nullptr;       // second copy of a graph input / output, for pipelined submission
         int first_def = -1, last_use = -1;
         bool is_input = false, is_output = false;
         int pool_slot = -1;
@@ -36,6 +37,14 @@ struct enn_b200_oplist {
     std::vector<int64_t> pool_bytes;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
+    // Pipelined submission (enn_b200_oplist_submit): a second graph bound to the alternate input / output buffers,
+    // a copy stream for the host-to-device transfers, and events that hand the two buffer sets back and forth.
+    cudaGraph_t graph_alt = nullptr;
+    cudaGraphExec_t exec_alt = nullptr;
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_in_ready[2] = {nullptr, nullptr}, ev_slot_free[2] = {nullptr, nullptr};
+    bool slot_used[2] = {false, false};
+    uint64_t seq = 0;
     bool finalized = false;
     int64_t device_bytes = 0;
     int32_t kernel_launches = 0;
@@ -46,13 +55,17 @@ int32_t lfail(enn_b200_oplist *l, int32_t st, const char *msg) {
     if (l && l->ctx) l->ctx->last_error = msg;
     return st;
 }
-int32_t run_nodes(enn_b200_oplist *l) {
+int32_t run_nodes(enn_b200_oplist *l, int slot = 0) {
+    auto ptr = [&](int t) {
+        auto &T = l->tensors[t];
+        return (slot == 1 && T.dev_alt) ? T.dev_alt : T.dev;
+    };
     for (auto &n : l->nodes) {
         int32_t st;
         if (n.in1 >= 0)
-            st = enn_b200_op_execute2(n.op, l->tensors[n.in0].dev, l->tensors[n.in1].dev, l->tensors[n.out].dev);
+            st = enn_b200_op_execute2(n.op, ptr(n.in0), ptr(n.in1), ptr(n.out));
         else
-            st = enn_b200_op_execute(n.op, l->tensors[n.in0].dev, l->tensors[n.out].dev);
+            st = enn_b200_op_execute(n.op, ptr(n.in0), ptr(n.out));
         if (st != ENN_B200_SUCCESS) return st;
     }
     return ENN_B200_SUCCESS;
@@ -188,6 +201,28 @@ int32_t enn_b200_oplist_finalize(enn_b200_oplist *l) {
         if (st != ENN_B200_SUCCESS) return st;
         if (e != cudaSuccess || !l->graph) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: stream capture failed");
         if (cudaGraphInstantiate(&l->exec, l->graph, 0) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: graph instantiation failed");
+        // Second buffer set + graph for pipelined submission.
+        for (auto &T : l->tensors)
+            if (T.is_input || T.is_output) {
+                const size_t bytes = static_cast<size_t>(T.bytes > 0 ? T.bytes : 1);
+                if (cudaMalloc(&T.dev_alt, (bytes + 255) & ~static_cast<size_t>(255)) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: device allocation failed");
+                l->device_bytes += static_cast<int64_t>(bytes);
+            }
+        st = run_nodes(l, 1);      // eager pass on the alternate pointers (operators cache per-pointer state)
+        if (st != ENN_B200_SUCCESS) return st;
+        if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: warm-up pass failed");
+        if (cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess)
+            return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: stream capture could not start");
+        st = run_nodes(l, 1);
+        e = cudaStreamEndCapture(ctx->stream, &l->graph_alt);
+        if (st != ENN_B200_SUCCESS) return st;
+        if (e != cudaSuccess || !l->graph_alt) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: stream capture failed");
+        if (cudaGraphInstantiate(&l->exec_alt, l->graph_alt, 0) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: graph instantiation failed");
+        if (cudaStreamCreateWithFlags(&l->copy_stream, cudaStreamNonBlocking) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: copy stream creation failed");
+        for (int i = 0; i < 2; ++i)
+            if (cudaEventCreateWithFlags(&l->ev_in_ready[i], cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&l->ev_slot_free[i], cudaEventDisableTiming) != cudaSuccess)
+                return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: event creation failed");
     }
     l->finalized = true;
     return ENN_B200_SUCCESS;
@@ -222,6 +257,48 @@ int32_t enn_b200_oplist_execute(enn_b200_oplist *l, const void *const *host_inpu
     return ENN_B200_SUCCESS;
 }
 
+// Pipelined ExecuteSubGraph: returns as soon as the work is queued.  The host-to-device copy of this submission runs
+// on a copy stream and overlaps the operators of the previous one (two device copies of every graph input / output
+// alternate); results are valid in host_outputs after enn_b200_oplist_wait.  Host buffers must stay alive and untouched
+// until then and should be pinned.
+int32_t enn_b200_oplist_submit(enn_b200_oplist *l, const void *const *host_inputs, void *const *host_outputs) {
+    if (!l || !l->finalized) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist not finalized");
+    if ((!l->inputs.empty() && !host_inputs) || (!l->outputs.empty() && !host_outputs)) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_submit: null buffer table");
+    if (!l->exec || !l->exec_alt) return enn_b200_oplist_execute(l, host_inputs, host_outputs);
+    const int slot = static_cast<int>(l->seq & 1);
+    cudaStream_t cs = l->copy_stream, s = l->ctx->stream;
+    // the previous user of this buffer set must have finished reading its inputs and copying out its outputs
+    if (l->slot_used[slot] && cudaStreamWaitEvent(cs, l->ev_slot_free[slot], 0) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: event wait failed");
+    for (size_t i = 0; i < l->inputs.size(); ++i) {
+        auto &T = l->tensors[l->inputs[i]];
+        if (!host_inputs[i]) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_submit: null input buffer");
+        void *dst = slot ? T.dev_alt : T.dev;
+        if (T.bytes && cudaMemcpyAsync(dst, host_inputs[i], static_cast<size_t>(T.bytes), cudaMemcpyHostToDevice, cs) != cudaSuccess)
+            return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: input copy failed");
+    }
+    if (cudaEventRecord(l->ev_in_ready[slot], cs) != cudaSuccess || cudaStreamWaitEvent(s, l->ev_in_ready[slot], 0) != cudaSuccess)
+        return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: event hand-over failed");
+    if (cudaGraphLaunch(slot ? l->exec_alt : l->exec, s) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: graph launch failed");
+    for (size_t i = 0; i < l->outputs.size(); ++i) {
+        auto &T = l->tensors[l->outputs[i]];
+        if (!host_outputs[i]) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_submit: null output buffer");
+        const void *src = slot ? T.dev_alt : T.dev;
+        if (T.bytes && cudaMemcpyAsync(host_outputs[i], src, static_cast<size_t>(T.bytes), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+            return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: output copy failed");
+    }
+    if (cudaEventRecord(l->ev_slot_free[slot], s) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: event record failed");
+    l->slot_used[slot] = true;
+    ++l->seq;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_oplist_wait(enn_b200_oplist *l) {
+    if (!l || !l->finalized) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist not finalized");
+    if (l->copy_stream && cudaStreamSynchronize(l->copy_stream) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_wait: copy stream failed");
+    if (cudaStreamSynchronize(l->ctx->stream) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_wait: stream synchronisation failed");
+    return ENN_B200_SUCCESS;
+}
+
 int32_t enn_b200_oplist_tensor_ptr(enn_b200_oplist *l, int32_t tensor_id, void **dev_ptr) {
     if (!l || !dev_ptr || tensor_id < 0 || tensor_id >= static_cast<int32_t>(l->tensors.size())) return ENN_B200_INVALID_PARAMS;
     if (!l->finalized) return lfail(l, ENN_B200_FAILURE, "oplist not finalized");
@@ -243,8 +320,20 @@ int32_t enn_b200_oplist_destroy(enn_b200_oplist *l) {
         cudaSetDevice(l->ctx->device);
         cudaStreamSynchronize(l->ctx->stream);
     }
+    if (l->copy_stream) {
+        cudaStreamSynchronize(l->copy_stream);
+        cudaStreamDestroy(l->copy_stream);
+    }
+    for (int i = 0; i < 2; ++i) {
+        if (l->ev_in_ready[i]) cudaEventDestroy(l->ev_in_ready[i]);
+        if (l->ev_slot_free[i]) cudaEventDestroy(l->ev_slot_free[i]);
+    }
     if (l->exec) cudaGraphExecDestroy(l->exec);
     if (l->graph) cudaGraphDestroy(l->graph);
+    if (l->exec_alt) cudaGraphExecDestroy(l->exec_alt);
+    if (l->graph_alt) cudaGraphDestroy(l->graph_alt);
+    for (auto &T : l->tensors)
+        if (T.dev_alt) cudaFree(T.dev_alt);
     for (auto &n : l->nodes) enn_b200_op_release(n.op);
     for (void *p : l->pool)
         if (p) cudaFree(p);

@@ -197,6 +197,11 @@ int32_t enn_b200_oplist_set_io(enn_b200_oplist *list, const int32_t *input_ids, 
 int32_t enn_b200_oplist_finalize(enn_b200_oplist *list);
 /* ExecuteSubGraph: host_inputs[i] / host_outputs[i] follow the order given to set_io; copies in, runs, copies out, blocks. */
 int32_t enn_b200_oplist_execute(enn_b200_oplist *list, const void *const *host_inputs, void *const *host_outputs);
+/* Pipelined ExecuteSubGraph (the async H2D / D2H overlap the reference's set_input_data / set_output_data do not have):
+ * queues copy-in, graph and copy-out and returns; the copy-in of one submission overlaps the operators of the previous
+ * one.  Outputs are valid after enn_b200_oplist_wait.  Host buffers must stay untouched until then (pin them). */
+int32_t enn_b200_oplist_submit(enn_b200_oplist *list, const void *const *host_inputs, void *const *host_outputs);
+int32_t enn_b200_oplist_wait(enn_b200_oplist *list);
 /* Operators only, on device-resident tensors, asynchronous on the context stream. */
 int32_t enn_b200_oplist_execute_device(enn_b200_oplist *list);
 int32_t enn_b200_oplist_tensor_ptr(enn_b200_oplist *list, int32_t tensor_id, void **dev_ptr);

@@ -295,6 +295,27 @@ def test_oplist_mobilenet_small(enn, orc, ctx):
         ol.destroy()
 
 
+def test_oplist_pipelined_submit(enn, ctx):
+    """enn_b200_oplist_submit / wait (copy-in overlapped with the previous graph) gives the blocking call's results."""
+    import importlib
+    mn = importlib.import_module("cl_eden_kernel_b200.mobilenet")
+    layers, _ = mn.build_model(seed=4, calib_images=1, resolution=64, num_classes=50)
+    ol, info = mn.make_oplist(enn, ctx, layers, batch=2, resolution=64)
+    try:
+        rng = np.random.default_rng(11)
+        xs = [rng.integers(0, 256, (2, 64, 64, 3), dtype=np.int64).astype(np.uint8) for _ in range(5)]
+        want = [ol.execute([x])[0].copy() for x in xs]
+        outs = [np.zeros(100, np.uint8) for _ in xs]
+        for x, o in zip(xs, outs):
+            ol.submit_host_ptrs([x.ctypes.data], [o.ctypes.data])
+        ol.wait()
+        for w, o in zip(want, outs):
+            assert np.array_equal(w, o)
+        assert len({w.tobytes() for w in want}) == len(want)      # the five inputs really gave five different results
+    finally:
+        ol.destroy()
+
+
 def test_mobilenet_layers_individually(enn, orc, ctx):
     """Each distinct MobileNetV2 layer shape at 224x224, batch 2, fed with the oracle's own activations."""
     import importlib
