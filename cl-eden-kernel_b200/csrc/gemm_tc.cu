@@ -3,9 +3,10 @@
 // fused bias / zero-point / fixed-point requantisation / clamp epilogue -> NHWC bytes.
 //
 // One persistent CTA per SM, warp-specialised:
-//   warp 0      TMA producer (one lane)
+//   warp 0      TMA producer of the A tiles (one lane)
 //   warp 1      TMEM allocation, MMA issue (one lane)
-//   warps 2..25 epilogue: each thread owns one accumulator row (= one output pixel) and a quarter of its columns
+//   warps 2..25 epilogue: each thread owns one accumulator row (= one output pixel) and a share of its columns
+//   warp 26     TMA producer of the B tiles (one lane)
 // Two accumulator buffers in TMEM let the epilogue of tile i overlap the MMAs of tile i+1.
 //
 // Value computed (ConvolutionKernels.cpp:956-1274 / :1317-1375): for output row m, column n
@@ -23,6 +24,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <type_traits>
 
 #include "internal.h"
 #include "requant.h"
@@ -42,7 +44,8 @@ constexpr int kMaxBN = 256;         // UMMA N limit
 constexpr int kEpiWarps = 24;         // epilogue warps: 6 per TMEM lane quarter, splitting the 16-column chunks
 constexpr int kColGroups = kEpiWarps / 4;
 constexpr int kChunksPerWarp = (kMaxBN / 16 + kColGroups - 1) / kColGroups;   // chunks one warp can own
-constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int kThreads = 64 + 32 * kEpiWarps + 32;   // A producer, MMA issuer, epilogue warps, B producer
+constexpr int kThreadsOneProducer = kThreads - 32;    // small problems: warp 0 loads both operands
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 struct ColParam {   // per output column, 16 bytes
@@ -57,6 +60,7 @@ struct TcParams {
     int32_t tiles_m, tiles_n, k_blocks;
     int32_t group;          // M tiles computed side by side in one accumulator buffer (group * bn_rows <= 256 columns)
     int32_t tiles_mg;       // ceil(tiles_m / group)
+    int32_t raster;         // M groups per rasterisation band (see tile_coords)
     int32_t bn_rows;        // B rows per N tile in shared memory (= UMMA N), multiple of 16
     int32_t bn_data;        // real output columns per N tile
     int32_t stages;
@@ -65,6 +69,7 @@ struct TcParams {
     int32_t zw_eff;         // zw'
     int32_t a_signed;
     int32_t act_min, act_max, out_zp;
+    int32_t two;            // 1: CTA-pair mode (tiles_mg counts pairs of M tiles, group == 1, kpack == 1)
     int32_t general;        // 1: some column needs the general (left shift / wide) requantisation
     uint32_t idesc;
     const ColParam *cols;   // [tiles_n][bn_rows]
@@ -107,6 +112,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait of the single-thread roles (producers, MMA issuer).  Callers look at the barrier with the non-blocking
+// test_wait first (the common case: already complete); what is left waits with try_wait, which parks the thread in
+// hardware between looks instead of spinning through issue slots that the epilogue warps of the same scheduler need.
+__device__ __forceinline__ bool mbar_wait_fast(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *err, int code) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (err) *reinterpret_cast<volatile int32_t *>(err) = code;
+    return false;
+}
 // Bounded wait.  Returns false after the limit (or when another thread already aborted the CTA).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *err, int code) {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
@@ -140,17 +168,83 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 // Arrives on the mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- CTA-pair (cta_group::2) forms: two CTAs of a cluster compute one 256-row tile, each holding its own 128 rows of
+// A, half of the B rows and its 128 accumulator lanes.  The MMA is issued by the rank-0 CTA only.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The tile lands in this CTA's shared memory; the bytes are counted on the rank-0 CTA's barrier (cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster, int32_t c0, int32_t c1) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// Arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask) : "memory");
+}
+
+// One k-block: KS (1, 2 or 4) MMAs over consecutive 32-byte K slices of the A tile at descriptor address `lo_a` and the
+// B tile at `lo_b` (16-byte units; `desc_hi` = the constant upper descriptor word).  All descriptors are formed first, then
+// the MMAs follow each other as one uninterrupted instruction run.  The first MMA overwrites the accumulator when
+// `accumulate_first` is 0.
+template <bool TWO, int KS>
+__device__ __forceinline__ void umma_i8_run(uint32_t d_tmem, uint32_t desc_hi, uint32_t lo_a, uint32_t lo_b, uint32_t idesc,
+                                            uint32_t accumulate_first) {
+#define ENN_MMA_PAIR "tcgen05.mma.cta_group::2.kind::i8"
+#define ENN_MMA_ONE "tcgen05.mma.cta_group::1.kind::i8"
+#define ENN_DESC(I, OFF)                                                       \
+    "add.u32 t, %2, " #OFF ";\n\tmov.b64 a" #I ", {t, %1};\n\t"                 \
+    "add.u32 t, %3, " #OFF ";\n\tmov.b64 b" #I ", {t, %1};\n\t"
+#define ENN_RUN_HEAD                                                                                  \
+    "{\n\t.reg .pred p, q;\n\t.reg .b64 a0, a1, a2, a3, b0, b1, b2, b3;\n\t.reg .b32 t;\n\t"           \
+    "setp.ne.b32 p, %5, 0;\n\t"                                                                       \
+    "setp.eq.b32 q, %5, %5;\n\t"
+#define ENN_RUN_ARGS ::"r"(d_tmem), "r"(desc_hi), "r"(lo_a), "r"(lo_b), "r"(idesc), "r"(accumulate_first) : "memory"
+#define ENN_RUN(MMA)                                                                                                   \
+    if (KS == 4)                                                                                                       \
+        asm volatile(ENN_RUN_HEAD ENN_DESC(0, 0) ENN_DESC(1, 2) ENN_DESC(2, 4) ENN_DESC(3, 6)                         \
+                     MMA " [%0], a0, b0, %4, p;\n\t" MMA " [%0], a1, b1, %4, q;\n\t" MMA " [%0], a2, b2, %4, q;\n\t" \
+                     MMA " [%0], a3, b3, %4, q;\n\t}" ENN_RUN_ARGS);                                                   \
+    else if (KS == 2)                                                                                                  \
+        asm volatile(ENN_RUN_HEAD ENN_DESC(0, 0) ENN_DESC(1, 2)                                                       \
+                     MMA " [%0], a0, b0, %4, p;\n\t" MMA " [%0], a1, b1, %4, q;\n\t}" ENN_RUN_ARGS);                   \
+    else                                                                                                               \
+        asm volatile(ENN_RUN_HEAD ENN_DESC(0, 0) MMA " [%0], a0, b0, %4, p;\n\t}" ENN_RUN_ARGS);
+    if (TWO) { ENN_RUN(ENN_MMA_PAIR) } else { ENN_RUN(ENN_MMA_ONE) }
+#undef ENN_RUN
+#undef ENN_RUN_ARGS
+#undef ENN_RUN_HEAD
+#undef ENN_DESC
+#undef ENN_MMA_ONE
+#undef ENN_MMA_PAIR
 }
 
 __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
@@ -186,6 +280,32 @@ __device__ __forceinline__ uint32_t pack_sat_u8_tc(int32_t hi, int32_t lo, uint3
     return d;
 }
 
+// Work unit `tile` -> (M tile group tg, N tile tn).  Units are numbered band by band: a band is `raster` consecutive M
+// groups, and inside a band the M index runs fastest.  The units in flight at one time (one per SM) then share few A and
+// few B tiles, so that both operands stay L2 resident for large problems.
+__device__ __forceinline__ void tile_coords(const TcParams &p, int tile, int &tg, int &tn) {
+    if (p.tiles_n == 1) {       // the usual convolution case: no division (every epilogue thread runs this per tile)
+        tg = tile;
+        tn = 0;
+        return;
+    }
+    if (p.raster == p.tiles_mg && p.tiles_n <= 4) {     // one band, few N tiles: subtract instead of dividing
+        tg = tile;
+        tn = 0;
+        while (tg >= p.tiles_mg) {
+            tg -= p.tiles_mg;
+            ++tn;
+        }
+        return;
+    }
+    const int band = p.raster * p.tiles_n;
+    const int b = tile / band, r = tile - b * band;
+    const int g0 = b * p.raster;
+    const int gw = min(p.raster, p.tiles_mg - g0);      // the last band may be narrower
+    tn = r / gw;
+    tg = g0 + (r - tn * gw);
+}
+
 // Requantise one accumulator to (value - act_min) in [0, act_max - act_min].
 // Fast form (esh = right shift e >= 1): stage 1 is one 32x32->64 multiply-add and a funnel shift, stage 2 is
 // (x + addend - [x < 0]) >> e with addend = 2^(e-1) + ((out_zp - act_min) << e), i.e. RoundingDivideByPOT
@@ -201,7 +321,49 @@ __device__ __forceinline__ int32_t tc_requant(int32_t acc, const int4 &c, int32_
     return __vimin_s32_relu(v, hi_clamp);
 }
 
-template <bool ASUM, bool GENERAL>
+// The k loop of one accumulator tile for the common big-GEMM shape (four K slices per k-block, one k-block per stage),
+// unrolled over the D stages of the ring: stage addresses, barrier addresses and descriptors are then loop invariants
+// held in registers, and a k-block costs the MMA thread a barrier look-up, the four MMAs, a commit and a counter.
+// The ring position carries over from tile to tile, so the unrolled sequence is entered at the current stage.
+#define ENN_KB(S)                                                                                                        \
+    {                                                                                                                    \
+        const uint32_t bar = full0 + 8 * (S);                                                                            \
+        if (!mbar_test_wait(bar, phase) && !mbar_wait_fast(bar, phase, abort_flag, err, 3)) return false;                \
+        umma_i8_run<TWO, 4>(d_tmem, desc_hi, lo0 + (S) * stage16, lo0 + (S) * stage16 + a16, idesc, acc);                \
+        acc = 1;                                                                                                         \
+        if (TWO) umma_commit_pair(empty0 + 8 * (S));                                                                     \
+        else umma_commit(empty0 + 8 * (S));                                                                              \
+        if (--n == 0) {                                                                                                  \
+            stage = (S) + 1;                                                                                             \
+            break;                                                                                                       \
+        }                                                                                                                \
+    }
+#define ENN_TILE_FN(NAME, D, CASES)                                                                                      \
+    template <bool TWO>                                                                                                  \
+    __device__ __forceinline__ bool NAME(uint32_t d_tmem, int n, uint32_t &stage, uint32_t &phase, uint32_t full0,       \
+                                         uint32_t empty0, uint32_t desc_hi, uint32_t lo0, uint32_t stage16, uint32_t a16, \
+                                         uint32_t idesc, volatile int *abort_flag, int32_t *err) {                      \
+        uint32_t acc = 0;                                                                                                \
+        for (;;) {                                                                                                       \
+            switch (stage) { CASES }                                                                                     \
+            if (n == 0) break;                                                                                           \
+            stage = 0;                                                                                                   \
+            phase ^= 1;                                                                                                  \
+        }                                                                                                                \
+        if (stage == (D)) {                                                                                              \
+            stage = 0;                                                                                                   \
+            phase ^= 1;                                                                                                  \
+        }                                                                                                                \
+        return true;                                                                                                     \
+    }
+ENN_TILE_FN(mma_tile_d4, 4, case 0: ENN_KB(0) case 1: ENN_KB(1) case 2: ENN_KB(2) case 3: ENN_KB(3))
+ENN_TILE_FN(mma_tile_d6, 6, case 0: ENN_KB(0) case 1: ENN_KB(1) case 2: ENN_KB(2) case 3: ENN_KB(3) case 4: ENN_KB(4) case 5: ENN_KB(5))
+#undef ENN_TILE_FN
+#undef ENN_KB
+
+// TWO: CTA-pair mode (launched as clusters of 2; plain GEMM operands only, group == 1, kpack == 1): the pair owns M
+// tiles 2t and 2t + 1 of one N tile, every B byte is read from L2 once per pair, and a stage per CTA is A plus half of B.
+template <bool ASUM, bool GENERAL, bool TWO>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -209,8 +371,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     const uint32_t span = p.taps > 0 ? static_cast<uint32_t>(p.span) : kBK;
     const uint32_t a_bytes = kBM * span;
-    const uint32_t b_bytes = static_cast<uint32_t>(p.bn_rows) * span;
+    const uint32_t b_bytes = static_cast<uint32_t>(TWO ? p.bn_rows >> 1 : p.bn_rows) * span;
     const uint32_t kb_bytes = a_bytes + b_bytes;                      // one k-block: A tile then B tile
+    const uint32_t rank = TWO ? cluster_ctarank() : 0;
+    const int tile_first = TWO ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int tile_step = TWO ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
     const uint32_t stage_bytes = kb_bytes * static_cast<uint32_t>(p.kpack);
     uint8_t *tiles = smem;
     // Per-epilogue-warp copies of the N tile's column constants (kEpiWarps x 256 x 16 bytes): private to a warp, so
@@ -219,28 +384,35 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t s_cols_u32 = smem_u32(s_cols);
     uint64_t *bars = reinterpret_cast<uint64_t *>(s_cols + kEpiWarps * kChunksPerWarp * 16);
     // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * p.stages + 4);
+    const int nst = p.stages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * nst + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + p.stages);
-    const uint32_t tfull0 = smem_u32(bars + 2 * p.stages), tempty0 = smem_u32(bars + 2 * p.stages + 2);
+    const bool dbg = p.dbg != nullptr;
+    const bool split = blockDim.x == kThreads;      // launched with the separate B producer warp
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + nst);
+    const uint32_t tfull0 = smem_u32(bars + 2 * nst), tempty0 = smem_u32(bars + 2 * nst + 2);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(full0 + 8 * s, 1);
+        for (int s = 0; s < nst; ++s) {
+            mbar_init(full0 + 8 * s, split ? 2 : 1);        // one expect-tx arrival per producer
             mbar_init(empty0 + 8 * s, 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull0 + 8 * b, 1);
-            mbar_init(tempty0 + 8 * b, kEpiWarps);      // one arrival per epilogue warp
+            mbar_init(tempty0 + 8 * b, TWO ? 2 * kEpiWarps : kEpiWarps);      // one arrival per epilogue warp (of both CTAs)
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    if (warp == 1) {
+        if (TWO) tmem_alloc_pair(smem_u32(tmem_slot), 512);
+        else tmem_alloc(smem_u32(tmem_slot), 512);
+    }
     tc_fence_before();
     __syncthreads();
+    if (TWO) cluster_sync_all();        // the peer's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -248,98 +420,175 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // buffer, so that every epilogue warp has columns to work on.
     const int total_tiles = p.tiles_mg * p.tiles_n;
 
-    if (warp == 0) {
-        // ---------------- TMA producer ----------------
+    if (warp == 0 || warp == kEpiWarps + 2) {
+        // ---------------- TMA producers: warp 0 loads the A tiles, the last warp the B tiles ----------------
+        // (one thread issuing both operands of every k-block cannot keep up with the tensor pipe)
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            bool ok = true;
-            long long t_wait = 0, t_begin = clock64();
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int tg = tile % p.tiles_mg, tn = tile / p.tiles_mg;
-                const int nsub = min(p.group, p.tiles_m - tg * p.group);
-                for (int j = 0; j < nsub && ok; ++j) {
-                    const int tm = tg * p.group + j;
-                    int img = 0, ty = 0, tx = 0;
-                    if (p.taps > 0) {       // patch (img, ty, tx) of the output grid
-                        const int per_img = p.conv_ty * p.conv_tx;
-                        img = tm / per_img;
-                        const int rem = tm - img * per_img;
-                        ty = rem / p.conv_tx;
-                        tx = rem - ty * p.conv_tx;
-                    }
-                    int tap = 0, cc = 0;
-                    for (int kb0 = 0; kb0 < p.k_blocks; kb0 += p.kpack) {
-                        const int nkb = min(p.kpack, p.k_blocks - kb0);
-                        const long long t0 = clock64();
-                        if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.err, 1)) { ok = false; break; }
-                        t_wait += clock64() - t0;
-                        const uint32_t bar = full0 + 8 * stage;
-                        uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
-                        if (p.taps > 0) {
-                            mbar_expect_tx(bar, (static_cast<uint32_t>(p.conv_ht * p.conv_wt) * span + b_bytes) * nkb);
-                            for (int q = 0; q < nkb; ++q, sa += kb_bytes) {
-                                tma_load_4d(sa, &map_a, bar, cc * static_cast<int>(span), tx * p.conv_wt + p.tap_dx[tap], ty * p.conv_ht + p.tap_dy[tap], img);
-                                tma_load_2d(sa + a_bytes, &map_b, bar, (kb0 + q) * static_cast<int>(span), tn * p.bn_rows);
-                                if (++cc == p.cchunks) { cc = 0; ++tap; }
-                            }
-                        } else {
-                            mbar_expect_tx(bar, kb_bytes * nkb);
-                            for (int q = 0; q < nkb; ++q, sa += kb_bytes) {
-                                tma_load_2d(sa, &map_a, bar, (kb0 + q) * kBK, tm * kBM);
-                                tma_load_2d(sa + a_bytes, &map_b, bar, (kb0 + q) * kBK, tn * p.bn_rows);
-                            }
+            // WHICH: 0 = the A tiles, 1 = the B tiles, 2 = both (launches without the separate B producer warp)
+            auto produce = [&](auto which) {
+                constexpr int WHICH = decltype(which)::value;
+                constexpr bool DO_A = WHICH != 1, DO_B = WHICH != 0;
+                uint32_t stage = 0, phase = 0, filled = 0;
+                const uint32_t sa_stage0 = smem_u32(tiles);
+                uint32_t sa_stage = sa_stage0;
+                // bytes this producer's loads add to a k-block (pairs: of both CTAs, counted on rank 0's barrier)
+                const uint32_t a_tx = p.taps > 0 ? static_cast<uint32_t>(p.conv_ht * p.conv_wt) * span : a_bytes;
+                const uint32_t kb_tx = ((DO_A ? a_tx : 0u) + (DO_B ? b_bytes : 0u)) * (TWO ? 2u : 1u);
+                bool ok = true;
+                long long t_wait = 0;
+                for (int tile = tile_first; tile < total_tiles && ok; tile += tile_step) {
+                    int tg, tn;
+                    tile_coords(p, tile, tg, tn);
+                    const int nsub = min(p.group, p.tiles_m - tg * p.group);
+                    for (int j = 0; j < nsub && ok; ++j) {
+                        const int tm = TWO ? tg * 2 + static_cast<int>(rank) : tg * p.group + j;
+                        int img = 0, ty = 0, tx = 0;
+                        if (DO_A && p.taps > 0) {       // patch (img, ty, tx) of the output grid
+                            const int per_img = p.conv_ty * p.conv_tx;
+                            img = tm / per_img;
+                            const int rem = tm - img * per_img;
+                            ty = rem / p.conv_tx;
+                            tx = rem - ty * p.conv_tx;
                         }
-                        if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+                        int tap = 0, cc = 0;
+                        const int row_a = tm * kBM;
+                        const int row_b = tn * p.bn_rows + (TWO ? static_cast<int>(rank) * (p.bn_rows >> 1) : 0);
+                        const int kstep_b = p.taps > 0 ? static_cast<int>(span) : kBK;
+                        for (int kb0 = 0; kb0 < p.k_blocks; kb0 += p.kpack) {
+                            const int nkb = min(p.kpack, p.k_blocks - kb0);
+                            const uint32_t ebar = empty0 + 8 * stage;
+                            const long long t0 = dbg ? clock64() : 0;
+                            if (!mbar_test_wait(ebar, phase ^ 1) && !mbar_wait_fast(ebar, phase ^ 1, abort_flag, p.err, 1)) { ok = false; break; }
+                            if (dbg) t_wait += clock64() - t0;
+                            const uint32_t bar = full0 + 8 * stage;
+                            uint32_t sa = sa_stage;
+                            if ((p.dbg_mode & 1) && filled >= static_cast<uint32_t>(p.stages)) {
+                                // development switch: operands stay as first loaded (measures the MMA side alone; results are wrong)
+                                if (rank == 0) mbar_arrive(bar);
+                            } else if (TWO) {
+                                // rank 0 expects the bytes of both CTAs; every load reports to rank 0's barrier
+                                if (rank == 0) mbar_expect_tx(bar, kb_tx * nkb);
+                                const uint32_t bar0 = mapa_rank(bar, 0);
+                                for (int q = 0; q < nkb; ++q, sa += kb_bytes) {
+                                    if (DO_A) tma_load_2d_pair(sa, &map_a, bar0, (kb0 + q) * kBK, row_a);
+                                    if (DO_B) tma_load_2d_pair(sa + a_bytes, &map_b, bar0, (kb0 + q) * kBK, row_b);
+                                }
+                            } else {
+                                mbar_expect_tx(bar, kb_tx * nkb);
+                                for (int q = 0; q < nkb; ++q, sa += kb_bytes) {
+                                    if (DO_A) {
+                                        if (p.taps > 0) {
+                                            tma_load_4d(sa, &map_a, bar, cc * static_cast<int>(span), tx * p.conv_wt + p.tap_dx[tap], ty * p.conv_ht + p.tap_dy[tap], img);
+                                            if (++cc == p.cchunks) { cc = 0; ++tap; }
+                                        } else {
+                                            tma_load_2d(sa, &map_a, bar, (kb0 + q) * kBK, row_a);
+                                        }
+                                    }
+                                    if (DO_B) tma_load_2d(sa + a_bytes, &map_b, bar, (kb0 + q) * kstep_b, row_b);
+                                }
+                            }
+                            ++filled;
+                            sa_stage += stage_bytes;
+                            if (++stage == static_cast<uint32_t>(nst)) { stage = 0; phase ^= 1; sa_stage = sa_stage0; }
+                        }
                     }
                 }
-            }
-            if (p.dbg) { p.dbg[blockIdx.x * 8 + 0] = t_wait; p.dbg[blockIdx.x * 8 + 1] = clock64() - t_begin; }
-            if (!ok) {
-                // Give copies already in flight a bounded chance to land before shared memory is released.
-                for (int s = 0; s < p.stages; ++s)
-                    for (uint32_t i = 0; i < (1u << 16); ++i)
-                        if (mbar_try_wait(full0 + 8 * s, 0) || mbar_try_wait(full0 + 8 * s, 1)) break;
-            }
+                if (dbg && DO_A) p.dbg[blockIdx.x * 8 + 0] = t_wait;
+                if (!ok) {
+                    // Give copies already in flight a bounded chance to land before shared memory is released.
+                    for (int s = 0; s < nst; ++s)
+                        for (uint32_t i = 0; i < (1u << 16); ++i)
+                            if (mbar_try_wait(full0 + 8 * s, 0) || mbar_try_wait(full0 + 8 * s, 1)) break;
+                }
+            };
+            if (!split) produce(std::integral_constant<int, 2>{});
+            else if (warp == 0) produce(std::integral_constant<int, 0>{});
+            else produce(std::integral_constant<int, 1>{});
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // The tensor pipe has next to no queue in front of it: whatever this thread executes between two MMAs is
+        // time the pipe idles.  So the MMAs of a k-block go out as one uninterrupted run with every operand already in
+        // a register, and the bookkeeping between k-blocks (commit, ring advance, barrier look-up, descriptor
+        // addresses) is kept to a few instructions.
+        if (lane == 0 && rank == 0) {
             uint32_t stage = 0, phase = 0;
             uint32_t it = 0;
             bool ok = true;
-            long long t_full = 0, t_tempty = 0, t_begin = clock64();
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+            const uint32_t idesc = p.idesc;
+            const uint32_t desc_hi = static_cast<uint32_t>(make_smem_desc(0, span) >> 32);
+            const uint32_t lo0 = smem_u32(tiles) >> 4;                 // descriptor address field of stage 0 (16-byte units)
+            const uint32_t stage16 = stage_bytes >> 4, kb16 = kb_bytes >> 4, a16 = a_bytes >> 4;
+            // K slices per k-block: the whole span, except that the last k-block of a plain GEMM stops after the slices
+            // that hold real K (rounded up to 1, 2 or 4: the operands are zero beyond K, so a surplus slice adds nothing).
+            const int ks = static_cast<int>(span >> 5);
+            int ks_last = ks;
+            if (p.taps == 0) {
+                const int real = (p.K - (p.k_blocks - 1) * kBK + 31) >> 5;
+                ks_last = real <= 1 ? 1 : (real == 2 ? 2 : 4);
+            }
+            uint32_t lo_stage = lo0;
+            long long t_tempty = 0, t_begin = dbg ? clock64() : 0;
+            unsigned long long ns_begin = 0;
+            if (dbg) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_begin));
+            for (int tile = tile_first; tile < total_tiles && ok; tile += tile_step, ++it) {
                 const uint32_t ab = it & 1, use = it >> 1;
                 // wait until the epilogue has drained this accumulator buffer
-                const long long t0 = clock64();
-                if (!mbar_wait(tempty0 + 8 * ab, (use & 1) ^ 1, abort_flag, p.err, 2)) { ok = false; break; }
-                t_tempty += clock64() - t0;
+                const long long t0 = dbg ? clock64() : 0;
+                if (!mbar_wait_fast(tempty0 + 8 * ab, (use & 1) ^ 1, abort_flag, p.err, 2)) { ok = false; break; }
+                if (dbg) t_tempty += clock64() - t0;
+                if (TWO) asm volatile("fence.acq_rel.cluster;" ::: "memory");   // half of the arrivals came from the peer CTA
                 tc_fence_after();
-                const int tg = tile % p.tiles_mg;
+                int tg, tn_unused;
+                tile_coords(p, tile, tg, tn_unused);
                 const int nsub = min(p.group, p.tiles_m - tg * p.group);
                 for (int j = 0; j < nsub && ok; ++j) {
                     const uint32_t d_tmem = tmem_base + ab * kMaxBN + j * p.bn_rows;
-                    for (int kb0 = 0; kb0 < p.k_blocks; kb0 += p.kpack) {
-                        const int nkb = min(p.kpack, p.k_blocks - kb0);
-                        const long long t1 = clock64();
-                        if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.err, 3)) { ok = false; break; }
-                        t_full += clock64() - t1;
-                        tc_fence_after();
-                        uint32_t sa = smem_u32(tiles + static_cast<size_t>(stage) * stage_bytes);
-                        for (int q = 0; q < nkb; ++q, sa += kb_bytes) {
-                            const uint64_t da = make_smem_desc(sa, span), db = make_smem_desc(sa + a_bytes, span);
-                            const int kb = kb0 + q;
-                            const int ksteps = p.taps > 0 ? static_cast<int>(span >> 5) : min(4, (p.K - kb * kBK + 31) >> 5);
-                            for (int k = 0; k < ksteps; ++k)
-                                umma_i8(d_tmem, da + 2 * k, db + 2 * k, p.idesc, (kb | k) != 0);
-                        }
-                        umma_commit(empty0 + 8 * stage);      // frees the stage when these MMAs have read it
-                        if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+                    if (ks == 4 && ks_last == 4 && p.kpack == 1 && p.stages == (TWO ? 6 : 4)) {
+                        // big-GEMM shape: 256-wide tiles give four stages per CTA, six per CTA of a pair
+                        if constexpr (TWO) ok = mma_tile_d6<true>(d_tmem, p.k_blocks, stage, phase, full0, empty0, desc_hi, lo0, stage16, a16, idesc, abort_flag, p.err);
+                        else ok = mma_tile_d4<false>(d_tmem, p.k_blocks, stage, phase, full0, empty0, desc_hi, lo0, stage16, a16, idesc, abort_flag, p.err);
+                        lo_stage = lo0 + stage * stage16;
+                        continue;
                     }
+                    auto k_loop = [&](auto ks_tag) {
+                        constexpr int KS = decltype(ks_tag)::value;
+                        int kb = 0;
+                        while (kb < p.k_blocks) {
+                            const uint32_t bar = full0 + 8 * stage;
+                            if (!mbar_test_wait(bar, phase) && !mbar_wait_fast(bar, phase, abort_flag, p.err, 3)) { ok = false; break; }
+                            uint32_t lo = lo_stage;
+                            const int kb_end = min(kb + p.kpack, p.k_blocks);
+                            for (; kb < kb_end; ++kb, lo += kb16) {
+                                if (KS == 4 && kb == p.k_blocks - 1 && ks_last != 4) {
+                                    if (ks_last == 1) umma_i8_run<TWO, 1>(d_tmem, desc_hi, lo, lo + a16, idesc, kb != 0);
+                                    else umma_i8_run<TWO, 2>(d_tmem, desc_hi, lo, lo + a16, idesc, kb != 0);
+                                } else {
+                                    umma_i8_run<TWO, KS>(d_tmem, desc_hi, lo, lo + a16, idesc, kb != 0);
+                                }
+                            }
+                            // frees the stage (in both CTAs of a pair) when these MMAs have read it
+                            if (TWO) umma_commit_pair(empty0 + 8 * stage);
+                            else umma_commit(empty0 + 8 * stage);
+                            lo_stage += stage16;
+                            if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; lo_stage = lo0; }
+                        }
+                    };
+                    if (ks == 4) k_loop(std::integral_constant<int, 4>{});
+                    else if (ks == 2) k_loop(std::integral_constant<int, 2>{});
+                    else k_loop(std::integral_constant<int, 1>{});
                 }
-                if (ok) umma_commit(tfull0 + 8 * ab);     // accumulator complete
+                if (ok) {                                  // accumulator complete
+                    if (TWO) umma_commit_pair(tfull0 + 8 * ab);
+                    else umma_commit(tfull0 + 8 * ab);
+                }
             }
-            if (p.dbg) { p.dbg[blockIdx.x * 8 + 2] = t_full; p.dbg[blockIdx.x * 8 + 3] = t_tempty; p.dbg[blockIdx.x * 8 + 4] = clock64() - t_begin; }
+            if (dbg) {
+                unsigned long long ns_end;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_end));
+                p.dbg[blockIdx.x * 8 + 3] = t_tempty; p.dbg[blockIdx.x * 8 + 4] = clock64() - t_begin;
+                p.dbg[blockIdx.x * 8 + 7] = static_cast<long long>(ns_end - ns_begin);
+            }
         }
     } else {
         // ---------------- epilogue: thread = accumulator row, warp = (lane quarter, column share) ----------------
@@ -354,11 +603,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         int loaded_tn = -1;
         long long t_tfull = 0, t_begin = clock64();
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-            const int tg = tile % p.tiles_mg, tn = tile / p.tiles_mg;
+        for (int tile = tile_first; tile < total_tiles && ok; tile += tile_step, ++it) {
+            int tg, tn;
+            tile_coords(p, tile, tg, tn);
             const int nsub = min(p.group, p.tiles_m - tg * p.group);
             const uint32_t ab = it & 1, use = it >> 1;
-            const long long t0 = clock64();
+            const long long t0 = dbg ? clock64() : 0;
             // Chunk c of the buffer = 16 columns cc of M tile j: c = j * cps + cc.  This warp owns chunks
             // cgrp, cgrp + kColGroups, ...; it keeps private copies of the constants of the columns it meets.
             const int cps = p.bn_data >> 4;
@@ -377,7 +627,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 loaded_tn = tn;
             }
             if (!mbar_wait(tfull0 + 8 * ab, use & 1, abort_flag, p.err, 4)) { ok = false; break; }
-            t_tfull += clock64() - t0;
+            if (dbg) t_tfull += clock64() - t0;
             tc_fence_after();
             const uint32_t t_row = tmem_base + ab * kMaxBN + (static_cast<uint32_t>(q * 32) << 16);
             const int n_base = tn * p.bn_data;
@@ -393,12 +643,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             bool row_ok = false;
             int32_t asum_term = 0;
             uint32_t lc = my_cols;
-            for (int c = cgrp; c < nchunks; c += kColGroups, lc += 256) {
+            for (int c = cgrp; c < nchunks && !(p.dbg_mode & 2); c += kColGroups, lc += 256) {
                 uint32_t r[16];
                 tmem_ld_x16(t_row + j * p.bn_rows + (cc << 4), r);     // warp-collective
                 if (j != cur_j) {
                     cur_j = j;
-                    const int m = (tg * p.group + j) * kBM + row_in_tile;
+                    const int m = (TWO ? tg * 2 + static_cast<int>(rank) : tg * p.group + j) * kBM + row_in_tile;
                     row_ok = m < p.M;
                     const int mq = row_ok ? m : 0;
                     if (p.taps > 0) {
@@ -465,15 +715,22 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty0 + 8 * ab);
+            if (lane == 0) {
+                if (TWO) mbar_arrive_cluster(mapa_rank(tempty0 + 8 * ab, 0));
+                else mbar_arrive(tempty0 + 8 * ab);
+            }
         }
         if (p.dbg && threadIdx.x == 64) { p.dbg[blockIdx.x * 8 + 5] = t_tfull; p.dbg[blockIdx.x * 8 + 6] = clock64() - t_begin; }
     }
 
     tc_fence_before();
     __syncthreads();
+    if (TWO) cluster_sync_all();        // no signal may reach a CTA that has left
     tc_fence_after();
-    if (warp == 1) tmem_dealloc(tmem_base, 512);
+    if (warp == 1) {
+        if (TWO) tmem_dealloc_pair(tmem_base, 512);
+        else tmem_dealloc(tmem_base, 512);
+    }
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -700,6 +957,7 @@ struct TcGemm {
     void *ktab_dev = nullptr;          // im2col offset table (byte-granular gather only)
     size_t smem_bytes = 0;
     int grid = 0;
+    int threads = 0;                   // kThreads (separate B producer warp) for long-K GEMMs, else kThreadsOneProducer
     bool gather = false;               // A is gathered into scratch by im2col first
     bool use_gemv = false;             // M <= 8 read in place: weight-streaming GEMV instead of the tensor-core kernel
     // Implicit convolution (stride-1 taps read as TMA boxes, no gathered matrix): the source is either the caller's
@@ -791,18 +1049,44 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
             }
         }
     }
+    // CTA pairs (cta_group::2): two SMs share one 256-row tile and every B byte is fetched once per pair.  Measured on
+    // 4096^3 and 8192^3 it runs within 2 % of the one-CTA kernel (both are bound by operand delivery, not by B traffic),
+    // so it is opt-in: ENN_B200_TC_PAIR=1 selects it for plain GEMMs with several waves of 256-wide tiles and long K.
+    bool two = false;
+    int32_t forced_rows = 0;
+    if (const char *ev = getenv("ENN_B200_TC_PAIR")) {
+        two = atoi(ev) != 0 && span == kBK && p.tiles_m >= 2 && (K + kBK - 1) / kBK >= 8 && bn_data >= 128 &&
+              static_cast<int64_t>(p.tiles_m) * tiles_n >= 2ll * ctx->sm_count;
+        if (atoi(ev) >= 128) forced_rows = atoi(ev) & ~31;      // tuning: that UMMA N instead of 256
+    }
+    if (two) {
+        const int32_t rows = forced_rows >= 128 && forced_rows <= kMaxBN ? forced_rows : kMaxBN;   // the pair's UMMA N
+        if (rows - extra <= max_data) {
+            bn_data = rows - extra;
+            tiles_n = (N + bn_data - 1) / bn_data;
+        } else {
+            two = false;
+        }
+    }
+    p.two = two ? 1 : 0;
     p.tiles_n = tiles_n;
     p.bn_data = bn_data;
     p.bn_rows = bn_data + extra;
     p.k_blocks = (K + kBK - 1) / kBK;
-    p.group = kMaxBN / p.bn_rows;
+    p.group = two ? 1 : kMaxBN / p.bn_rows;
     if (p.group > p.tiles_m) p.group = p.tiles_m;
     // keep at least ~2 work units per SM before widening the groups
     while (p.group > 1 && static_cast<int64_t>((p.tiles_m + p.group - 1) / p.group) * tiles_n < 2ll * ctx->sm_count) --p.group;
-    p.tiles_mg = (p.tiles_m + p.group - 1) / p.group;
+    p.tiles_mg = two ? (p.tiles_m + 1) / 2 : (p.tiles_m + p.group - 1) / p.group;
+    // Bands only pay when the operands do not stay L2 resident by themselves (their coordinates cost two divisions per
+    // tile in every epilogue thread).
+    const bool big_operands = (static_cast<int64_t>(M) + N) * K > (48ll << 20);
+    p.raster = !big_operands ? p.tiles_mg : (two ? 8 : 16);
+    if (const char *ev = getenv("ENN_B200_TC_RASTER")) p.raster = atoi(ev) > 0 ? atoi(ev) : p.raster;   // tuning override
+    if (p.raster > p.tiles_mg) p.raster = p.tiles_mg;
     const int32_t k_pad = p.k_blocks * kBK;
     p.idesc = (2u << 4) | (static_cast<uint32_t>(g.a_signed ? 1 : 0) << 7) | (1u << 10) |
-              (static_cast<uint32_t>(p.bn_rows >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+              (static_cast<uint32_t>(p.bn_rows >> 3) << 17) | (static_cast<uint32_t>((p.two ? 2 * kBM : kBM) >> 4) << 24);
 
     // Packed B: [tiles_n][bn_rows][k_pad] int8, zero padded; row bn_data of each tile is all ones (sum_k a).
     std::vector<int8_t> wb(static_cast<size_t>(tiles_n) * p.bn_rows * k_pad, 0);
@@ -853,19 +1137,19 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         return ENN_B200_CUDA_FAILURE;
     }
     p.cols = static_cast<const ColParam *>(gm->cols_dev);
-    if (!encode_2d(ctx, &gm->map_b, gm->w_dev, k_pad, static_cast<uint64_t>(tiles_n) * p.bn_rows, k_pad, span, p.bn_rows)) {
+    if (!encode_2d(ctx, &gm->map_b, gm->w_dev, k_pad, static_cast<uint64_t>(tiles_n) * p.bn_rows, k_pad, span, p.two ? p.bn_rows / 2 : p.bn_rows)) {
         ctx->last_error = "cuTensorMapEncodeTiled failed for the weight tensor";
         return ENN_B200_CUDA_FAILURE;
     }
     if (span != kBK) p.k_blocks = K / static_cast<int32_t>(span);      // implicit convolution: one (tap, channel chunk) per k-block
     // Several small k-blocks share a pipeline stage so that a barrier round trip covers ~32 KB of operands.
-    const size_t kb_bytes = (static_cast<size_t>(kBM) + p.bn_rows) * span;
+    const size_t kb_bytes = (static_cast<size_t>(kBM) + (p.two ? p.bn_rows / 2 : p.bn_rows)) * span;
     p.kpack = static_cast<int32_t>((32 * 1024) / kb_bytes);
-    if (p.kpack < 1) p.kpack = 1;
+    if (p.kpack < 1 || p.two) p.kpack = 1;
     if (p.kpack > p.k_blocks) p.kpack = p.k_blocks;
     if (p.kpack > 8) p.kpack = 8;
     const size_t stage_bytes = kb_bytes * p.kpack;
-    const size_t fixed = static_cast<size_t>(kEpiWarps) * kChunksPerWarp * 16 * sizeof(ColParam) + 256 + 1024;   // column constants, barriers, slack
+    const size_t fixed = static_cast<size_t>(kEpiWarps) * kChunksPerWarp * 16 * sizeof(ColParam) + 1024 + 1024;   // column constants, barriers, slack
     int stages = static_cast<int>((227 * 1024 - fixed) / stage_bytes);
     if (stages > 8) stages = 8;
     if (stages < 2) return ENN_B200_INVALID_PARAMS;
@@ -873,6 +1157,10 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     gm->smem_bytes = stages * stage_bytes + fixed;
     const int total_tiles = p.tiles_mg * p.tiles_n;
     gm->grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
+    if (p.two) gm->grid = 2 * (total_tiles < ctx->sm_count / 2 ? total_tiles : ctx->sm_count / 2);
+    // One thread cannot issue both operands of every k-block fast enough for a long MMA-bound k loop; short, epilogue-
+    // bound problems are better off without the extra warp.
+    gm->threads = (p.kpack == 1 && p.k_blocks >= 8) ? kThreads : kThreadsOneProducer;
     return ENN_B200_SUCCESS;
 }
 
@@ -886,6 +1174,43 @@ void free_plan(TcPlan *plan) {
     if (plan->scratch) cudaFree(plan->scratch);
     if (plan->err_host) cudaFreeHost(plan->err_host);
     delete plan;
+}
+
+template <bool ASUM, bool GENERAL>
+void launch_tc_gemm_variant(const TcGemm &gm, const CUtensorMap &map_a, const TcParams &p, cudaStream_t stream) {
+    if (!p.two) {
+        tc_gemm_kernel<ASUM, GENERAL, false><<<gm.grid, gm.threads, gm.smem_bytes, stream>>>(map_a, gm.map_b, p);
+        return;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(gm.grid));
+    cfg.blockDim = dim3(static_cast<unsigned>(gm.threads));
+    cfg.dynamicSmemBytes = gm.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, tc_gemm_kernel<ASUM, GENERAL, true>, map_a, gm.map_b, p);
+}
+
+void launch_tc_gemm(const TcGemm &gm, const CUtensorMap &map_a, const TcParams &p, cudaStream_t stream) {
+    if (p.need_asum) {
+        if (p.general) launch_tc_gemm_variant<true, true>(gm, map_a, p, stream);
+        else launch_tc_gemm_variant<true, false>(gm, map_a, p, stream);
+    } else {
+        if (p.general) launch_tc_gemm_variant<false, true>(gm, map_a, p, stream);
+        else launch_tc_gemm_variant<false, false>(gm, map_a, p, stream);
+    }
+}
+
+template <bool ASUM, bool GENERAL>
+void set_tc_gemm_smem_attr() {
+    cudaFuncSetAttribute(tc_gemm_kernel<ASUM, GENERAL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(tc_gemm_kernel<ASUM, GENERAL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
 
 }  // namespace
@@ -1137,10 +1462,10 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
     op->info.kernel_launches = launches;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(tc_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        cudaFuncSetAttribute(tc_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        cudaFuncSetAttribute(tc_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        cudaFuncSetAttribute(tc_gemm_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        set_tc_gemm_smem_attr<false, false>();
+        set_tc_gemm_smem_attr<false, true>();
+        set_tc_gemm_smem_attr<true, false>();
+        set_tc_gemm_smem_attr<true, true>();
         attr_set = true;
     }
     op->tc = plan;
@@ -1226,18 +1551,12 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
             if (!dbg_buf) cudaMallocManaged(&dbg_buf, sizeof(long long) * 8 * 1024);
             p.dbg = dbg_buf;
         }
-        if (p.need_asum) {
-            if (p.general) tc_gemm_kernel<true, true><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a, gm.map_b, p);
-            else tc_gemm_kernel<true, false><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a, gm.map_b, p);
-        } else {
-            if (p.general) tc_gemm_kernel<false, true><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a, gm.map_b, p);
-            else tc_gemm_kernel<false, false><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a, gm.map_b, p);
-        }
+        launch_tc_gemm(gm, gm.map_a, p, ctx->stream);
         if (dbg) {
             cudaStreamSynchronize(ctx->stream);
             const long long *d = p.dbg;
-            std::fprintf(stderr, "tc dbg cta0: tiles %d x %d (group %d) k_blocks %d stages %d | producer wait %lld / %lld | mma full-wait %lld tempty-wait %lld / %lld | epi tfull-wait %lld / %lld\n",
-                         p.tiles_m, p.tiles_n, p.group, p.k_blocks, p.stages, d[0], d[1], d[2], d[3], d[4], d[5], d[6]);
+            std::fprintf(stderr, "tc dbg cta0: tiles %d x %d (group %d) k_blocks %d stages %d | producer wait %lld | mma tempty-wait %lld / %lld | epi tfull-wait %lld / %lld | mma thread %lld ns\n",
+                         p.tiles_m, p.tiles_n, p.group, p.k_blocks, p.stages, d[0], d[3], d[4], d[5], d[6], d[7]);
             p.dbg = nullptr;
         }
         cudaError_t e = cudaGetLastError();
@@ -1319,13 +1638,7 @@ int32_t tc_execute_static(enn_b200_op *op, const void *in, void *out) {
         p.out = static_cast<uint8_t *>(out);
         p.dbg = nullptr;
         p.dbg_mode = 0;
-        if (p.need_asum) {
-            if (p.general) tc_gemm_kernel<true, true><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a_static, gm.map_b, p);
-            else tc_gemm_kernel<true, false><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a_static, gm.map_b, p);
-        } else {
-            if (p.general) tc_gemm_kernel<false, true><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a_static, gm.map_b, p);
-            else tc_gemm_kernel<false, false><<<gm.grid, kThreads, gm.smem_bytes, ctx->stream>>>(gm.map_a_static, gm.map_b, p);
-        }
+        launch_tc_gemm(gm, gm.map_a_static, p, ctx->stream);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) {
             ctx->last_error = std::string("enn_b200_op_execute_noalloc launch: ") + cudaGetErrorString(e);

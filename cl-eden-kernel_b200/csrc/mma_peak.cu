@@ -1,7 +1,8 @@
 // Measures the sustained rate of tcgen05.mma on this device: every SM runs one CTA that issues a long chain
 // of 128 x N x K-step MMAs on resident shared-memory tiles (no global traffic), so the result is the
 // tensor-pipe ceiling the implicit-GEMM kernel is compared against.  kind 0: kind::i8 (u8 x s8 -> s32, K
-// step 32), kind 1: kind::f16 with bf16 operands (-> f32, K step 16).
+// step 32), kind 1: kind::f16 with bf16 operands (-> f32, K step 16); kinds 2 and 3: the same on pseudo-random
+// operand bytes instead of zeros.
 #include <cuda_runtime.h>
 
 #include "internal.h"
@@ -11,13 +12,25 @@ namespace {
 
 __device__ __forceinline__ uint32_t pk_smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
-__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int kind, int n, int iters, int *err) {
+template <int KIND>
+__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int n, int iters, int random_fill, int *err) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     __shared__ uint64_t bar;
     __shared__ uint32_t tmem_slot;
-    // A: 128 rows x 128 bytes, B: 256 rows x 128 bytes, zero filled.
-    for (int i = threadIdx.x; i < (128 + 256) * 128 / 16; i += blockDim.x) reinterpret_cast<uint4 *>(smem)[i] = make_uint4(0, 0, 0, 0);
+    // A: 128 rows x 128 bytes, B: 256 rows x 128 bytes; zero filled, or pseudo-random bytes (the operand bit toggling of
+    // real data, which is what the power management sees in a real GEMM).
+    for (int i = threadIdx.x; i < (128 + 256) * 128 / 16; i += blockDim.x) {
+        uint32_t h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t x = (static_cast<uint32_t>(i) * 4u + j) * 2654435761u + blockIdx.x * 40503u;
+            x ^= x >> 15; x *= 2246822519u; x ^= x >> 13;
+            if (KIND == 1) x &= 0x3FFF3FFFu;      // bf16: keep the exponents small (finite values)
+            h[j] = random_fill ? x : 0u;
+        }
+        reinterpret_cast<uint4 *>(smem)[i] = make_uint4(h[0], h[1], h[2], h[3]);
+    }
     const uint32_t bar_a = pk_smem_u32(&bar);
     if (threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a) : "memory");
@@ -40,23 +53,27 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int kind, int n, int i
         d |= static_cast<uint64_t>(1) << 46;
         d |= static_cast<uint64_t>(2) << 61;
         const uint64_t da = d | ((sa & 0x3FFFF) >> 4), db = d | (((sa + 128 * 128) & 0x3FFFF) >> 4);
-        uint32_t idesc;
-        if (kind == 0)
-            idesc = (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (8u << 24);
-        else
-            idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (8u << 24);
+        const uint32_t idesc = KIND == 0 ? (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (8u << 24)
+                                         : (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (8u << 24);
+        // The tensor pipe only reaches its full rate when the MMAs follow each other without other instructions in
+        // between (there is next to no queue in front of it), so the four K slices go out as one instruction run with
+        // loop-invariant operands.
+        const uint64_t a0 = da, a1 = da + 2, a2 = da + 4, a3 = da + 6, b0 = db, b1 = db + 2, b2 = db + 4, b3 = db + 6;
         for (int it = 0; it < iters; ++it) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const uint32_t acc = (it | k) != 0;
-                const uint32_t dt = tmem_base + ((it & 1) ? 256 : 0);
-                if (kind == 0)
-                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                                 ::"r"(dt), "l"(da + 2 * k), "l"(db + 2 * k), "r"(idesc), "r"(acc) : "memory");
-                else
-                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                                 ::"r"(dt), "l"(da + 2 * k), "l"(db + 2 * k), "r"(idesc), "r"(acc) : "memory");
-            }
+            if (KIND == 0)
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %10, 0;\n\tsetp.eq.b32 q, %10, %10;\n\t"
+                             "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %5, %9, p;\n\t"
+                             "tcgen05.mma.cta_group::1.kind::i8 [%0], %2, %6, %9, q;\n\t"
+                             "tcgen05.mma.cta_group::1.kind::i8 [%0], %3, %7, %9, q;\n\t"
+                             "tcgen05.mma.cta_group::1.kind::i8 [%0], %4, %8, %9, q;\n\t}"
+                             ::"r"(tmem_base), "l"(a0), "l"(a1), "l"(a2), "l"(a3), "l"(b0), "l"(b1), "l"(b2), "l"(b3), "r"(idesc), "r"(it) : "memory");
+            else
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %10, 0;\n\tsetp.eq.b32 q, %10, %10;\n\t"
+                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %5, %9, p;\n\t"
+                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %6, %9, q;\n\t"
+                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %7, %9, q;\n\t"
+                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %8, %9, q;\n\t}"
+                             ::"r"(tmem_base), "l"(a0), "l"(a1), "l"(a2), "l"(a3), "l"(b0), "l"(b1), "l"(b2), "l"(b3), "r"(idesc), "r"(it) : "memory");
         }
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_a) : "memory");
         bool done = false;
@@ -78,18 +95,24 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int kind, int n, int i
 
 // Returns achieved tera-operations per second (2 * MACs) over the whole device, or a negative value on error.
 double measure_mma_peak(enn_b200_context *ctx, int kind, int n, int iters) {
-    if (!ctx || ctx->cc_major != 10 || n < 16 || n > 256 || (n & 15) || iters < 1) return -1.0;
+    if (!ctx || ctx->cc_major != 10 || kind < 0 || kind > 3 || n < 16 || n > 256 || (n & 15) || iters < 1) return -1.0;
     int *err = nullptr;
     if (cudaMalloc(&err, sizeof(int)) != cudaSuccess) return -1.0;
     cudaMemsetAsync(err, 0, sizeof(int), ctx->stream);
     const size_t smem = (128 + 256) * 128 + 1024;
-    cudaFuncSetAttribute(mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaFuncSetAttribute(mma_peak_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaFuncSetAttribute(mma_peak_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    const int random_fill = kind >> 1;
+    auto launch = [&](int its) {
+        if ((kind & 1) == 0) mma_peak_kernel<0><<<ctx->sm_count, 128, smem, ctx->stream>>>(n, its, random_fill, err);
+        else mma_peak_kernel<1><<<ctx->sm_count, 128, smem, ctx->stream>>>(n, its, random_fill, err);
+    };
     cudaEvent_t e0, e1;
     cudaEventCreate(&e0);
     cudaEventCreate(&e1);
-    mma_peak_kernel<<<ctx->sm_count, 128, smem, ctx->stream>>>(kind, n, iters / 4 + 1, err);   // warm-up
+    launch(iters / 4 + 1);   // warm-up
     cudaEventRecord(e0, ctx->stream);
-    mma_peak_kernel<<<ctx->sm_count, 128, smem, ctx->stream>>>(kind, n, iters, err);
+    launch(iters);
     cudaEventRecord(e1, ctx->stream);
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     float ms = 0.f;
@@ -100,7 +123,7 @@ double measure_mma_peak(enn_b200_context *ctx, int kind, int n, int iters) {
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     if (e != cudaSuccess || herr != 0 || ms <= 0.f) return -1.0;
-    const double kstep = kind == 0 ? 32.0 : 16.0;
+    const double kstep = (kind & 1) == 0 ? 32.0 : 16.0;
     const double ops = 2.0 * 128.0 * n * kstep * 4.0 * iters * ctx->sm_count;
     return ops / (ms * 1e-3) / 1e12;
 }

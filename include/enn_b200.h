@@ -230,7 +230,7 @@ int32_t enn_b200_requant_host(int32_t acc, int32_t multiplier, int32_t shift, in
 
 /* Measures the sustained tcgen05.mma rate of the device (no reference counterpart: it provides the measured
  * tensor-pipe ceiling that GEMM-shaped operators are reported against).  kind 0: kind::i8 (u8 x s8 -> s32),
- * kind 1: kind::f16 with bf16 operands.  n: MMA N (16..256, multiple of 16); iters: MMA groups of 4 per SM.
+ * kind 1: kind::f16 with bf16 operands; kinds 2 and 3: the same on pseudo-random operand bytes.  n: MMA N (16..256, multiple of 16); iters: MMA groups of 4 per SM.
  * Writes tera-operations (2 x MAC) per second summed over all SMs. */
 int32_t enn_b200_measure_mma_peak(enn_b200_context *ctx, int32_t kind, int32_t n, int32_t iters, double *tera_ops);
 

@@ -216,6 +216,26 @@ def test_fc_full_size_sampled_rows(enn, orc, ctx):
         op.release()
 
 
+@pytest.mark.parametrize("m,k,n,w_zp", [(4096, 4096, 4096, None), (4230, 1024, 2500, 131)])
+def test_fc_cta_pair_mode(enn, orc, ctx, monkeypatch, m, k, n, w_zp):
+    """The opt-in CTA-pair (cta_group::2) GEMM: same bytes as the oracle on sampled rows; the second shape has an odd
+    number of M tiles (the last pair's second half lies outside the matrix), ragged N and the row-sum correction."""
+    monkeypatch.setenv("ENN_B200_TC_PAIR", "1")
+    kw = {} if w_zp is None else dict(w_zp=w_zp, per_channel=False)     # per-tensor u8 weights: zw' != 0
+    d, x, w, b, sc = cases.fc_case(seed=9, m=m, k=k, n=n, **kw)
+    op = enn.fully_connected(ctx, d, w, b, sc)
+    try:
+        assert op.info.impl == enn.IMPL_TCGEN05
+        y = op.run(x).reshape(m, n)
+        rows = np.r_[0:3, 126:131, 255:258, m - 260:m - 254, m - 3:m, np.random.default_rng(1).integers(0, m, 12)]
+        ds = type(d).from_buffer_copy(d)
+        ds.m = len(rows)
+        y_ref = orc.fully_connected(ds, np.ascontiguousarray(x[rows]), w, b, sc)
+        assert np.array_equal(y[rows], y_ref)
+    finally:
+        op.release()
+
+
 @pytest.mark.parametrize("count,act", [(1, 0), (15, 0), (4097, 3), (1 << 20, 0), (56 * 56 * 24 * 3, 0)])
 def test_add_parity(enn, orc, ctx, count, act):
     rng = np.random.default_rng(count)
