@@ -599,6 +599,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t lo_word = (static_cast<uint32_t>(p.act_min) & 0xff) * 0x01010101u;
         const int64_t st_bits = p.out_base | p.out_sn | p.out_sy | p.out_sx | p.bn_data | static_cast<int64_t>(reinterpret_cast<uintptr_t>(p.out));
         const int st_align = (st_bits & 15) == 0 ? 16 : ((st_bits & 7) == 0 ? 8 : 1);   // widest store every row start allows
+        const bool st_fast = st_align == 16 && (p.N & 15) == 0;      // every chunk is one aligned 16-byte store
+        const int patch_y = p.taps > 0 ? row_in_tile / p.conv_wt : 0;   // this thread's position in the output patch
+        const int patch_x = p.taps > 0 ? row_in_tile - patch_y * p.conv_wt : 0;
+        const int cps_mod = (p.bn_data >> 4) % kColGroups;
         uint32_t it = 0;
         bool ok = true;
         int loaded_tn = -1;
@@ -632,86 +636,89 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t t_row = tmem_base + ab * kMaxBN + (static_cast<uint32_t>(q * 32) << 16);
             const int n_base = tn * p.bn_data;
             const int n_cols = min(p.bn_data, p.N - n_base);
-            const int nchunks = nsub * cps;
 
-            // Walk this warp's chunks; (j, cc) follow c = j * cps + cc incrementally (no divisions in the loop),
-            // and the output row pointer is recomputed only when the M tile j changes.
-            int j = 0, cc = cgrp;
-            while (cc >= cps) { cc -= cps; ++j; }
-            int cur_j = -1;
-            uint8_t *orow = nullptr;
-            bool row_ok = false;
-            int32_t asum_term = 0;
+            // Walk this warp's chunks M tile by M tile: chunk c = j * cps + cc belongs to this warp when c = cgrp (mod
+            // kColGroups); `first` is the first such cc of M tile j and moves by -cps (mod kColGroups) from one M tile to
+            // the next.  Everything that depends only on the M tile (row pointer, row sum) is computed once per j.
+            int first = cgrp;
             uint32_t lc = my_cols;
-            for (int c = cgrp; c < nchunks && !(p.dbg_mode & 2); c += kColGroups, lc += 256) {
-                uint32_t r[16];
-                tmem_ld_x16(t_row + j * p.bn_rows + (cc << 4), r);     // warp-collective
-                if (j != cur_j) {
-                    cur_j = j;
-                    const int m = (TWO ? tg * 2 + static_cast<int>(rank) : tg * p.group + j) * kBM + row_in_tile;
-                    row_ok = m < p.M;
-                    const int mq = row_ok ? m : 0;
+            const uint8_t *out_tile = p.out + p.out_base + n_base;
+            for (int j = 0; j < nsub && !(p.dbg_mode & 2); ++j) {
+                if (first < cps) {
+                    const int tm = TWO ? tg * 2 + static_cast<int>(rank) : tg * p.group + j;
+                    const int m = tm * kBM + row_in_tile;
+                    bool row_ok = m < p.M;
+                    uint8_t *orow;
                     if (p.taps > 0) {
-                        const int tm = tg * p.group + j;
                         const int per_img = p.conv_ty * p.conv_tx;
                         const int img = tm / per_img, rem = tm - img * per_img;
                         const int ty = rem / p.conv_tx, tx = rem - ty * p.conv_tx;
-                        const int hy = row_in_tile / p.conv_wt, wx = row_in_tile - hy * p.conv_wt;
-                        const int qy = ty * p.conv_ht + hy, qx = tx * p.conv_wt + wx;
-                        row_ok = hy < p.conv_ht && qy < p.qh && qx < p.qw;
-                        orow = p.out + p.out_base + img * p.out_sn + (row_ok ? qy : 0) * p.out_sy + (row_ok ? qx : 0) * p.out_sx + n_base;
+                        const int qy = ty * p.conv_ht + patch_y, qx = tx * p.conv_wt + patch_x;
+                        row_ok = patch_y < p.conv_ht && qy < p.qh && qx < p.qw;
+                        orow = const_cast<uint8_t *>(out_tile) + img * p.out_sn + (row_ok ? qy : 0) * p.out_sy + (row_ok ? qx : 0) * p.out_sx;
                     } else if (p.qh == 1) {
-                        orow = p.out + p.out_base + static_cast<int64_t>(mq) * p.out_sx + n_base;
+                        orow = const_cast<uint8_t *>(out_tile) + static_cast<int64_t>(row_ok ? m : 0) * p.out_sx;
                     } else {
+                        const int mq = row_ok ? m : 0;
                         const int img = mq / (p.qh * p.qw), rem = mq - img * (p.qh * p.qw);
                         const int qy = rem / p.qw, qx = rem - qy * p.qw;
-                        orow = p.out + p.out_base + img * p.out_sn + qy * p.out_sy + qx * p.out_sx + n_base;
+                        orow = const_cast<uint8_t *>(out_tile) + img * p.out_sn + qy * p.out_sy + qx * p.out_sx;
                     }
+                    const uint32_t t_tile = t_row + j * p.bn_rows;
+                    int32_t asum_term = 0;
                     if (ASUM) {
                         uint32_t rs;
-                        tmem_ld_x1(t_row + j * p.bn_rows + p.bn_data, rs);
+                        tmem_ld_x1(t_tile + p.bn_data, rs);       // warp-collective
                         tmem_ld_wait();
                         asum_term = p.zw_eff * static_cast<int32_t>(rs);
                     }
-                }
-                tmem_ld_wait();
-                const int c0 = cc << 4;
-                if (row_ok && c0 < n_cols) {
-                    uint32_t w[4];
+                    for (int c0 = first << 4; c0 < (cps << 4); c0 += kColGroups * 16, lc += 256) {
+                        uint32_t r[16];
+                        tmem_ld_x16(t_tile + c0, r);              // warp-collective
+                        tmem_ld_wait();
+                        if (row_ok && c0 < n_cols) {
+                            uint32_t w[4];
 #pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) {
-                        int32_t y[4];
+                            for (int jj = 0; jj < 4; ++jj) {
+                                int32_t y[4];
 #pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            int4 cv;
-                            asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(lc + (jj * 4 + b) * 16));
-                            int32_t acc = static_cast<int32_t>(r[jj * 4 + b]) + cv.w;
-                            if (ASUM) acc -= asum_term;
-                            y[b] = tc_requant<GENERAL>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
+                                for (int b = 0; b < 4; ++b) {
+                                    int4 cv;
+                                    asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(lc + (jj * 4 + b) * 16));
+                                    int32_t acc = static_cast<int32_t>(r[jj * 4 + b]) + cv.w;
+                                    if (ASUM) acc -= asum_term;
+                                    y[b] = tc_requant<GENERAL>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
+                                }
+                                const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
+                                w[jj] = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
+                            }
+                            if (st_fast) {
+                                *reinterpret_cast<uint4 *>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                            } else {
+                                const int left = n_cols - c0;
+                                if (st_align == 16 && left >= 16) {
+                                    *reinterpret_cast<uint4 *>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                                } else if (st_align >= 8 && left >= 8) {
+                                    *reinterpret_cast<uint2 *>(orow + c0) = make_uint2(w[0], w[1]);
+                                    if (left >= 16) {
+                                        *reinterpret_cast<uint2 *>(orow + c0 + 8) = make_uint2(w[2], w[3]);
+                                    } else {
+#pragma unroll
+                                        for (int b = 8; b < 16; ++b)
+                                            if (b < left) orow[c0 + b] = static_cast<uint8_t>(w[b >> 2] >> (8 * (b & 3)));
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int b = 0; b < 16; ++b)
+                                        if (b < left) orow[c0 + b] = static_cast<uint8_t>(w[b >> 2] >> (8 * (b & 3)));
+                                }
+                            }
                         }
-                        const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
-                        w[jj] = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
-                    }
-                    const int left = n_cols - c0;
-                    if (st_align == 16 && left >= 16) {
-                        *reinterpret_cast<uint4 *>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
-                    } else if (st_align >= 8 && left >= 8) {
-                        *reinterpret_cast<uint2 *>(orow + c0) = make_uint2(w[0], w[1]);
-                        if (left >= 16) {
-                            *reinterpret_cast<uint2 *>(orow + c0 + 8) = make_uint2(w[2], w[3]);
-                        } else {
-#pragma unroll
-                            for (int b = 8; b < 16; ++b)
-                                if (b < left) orow[c0 + b] = static_cast<uint8_t>(w[b >> 2] >> (8 * (b & 3)));
-                        }
-                    } else {
-#pragma unroll
-                        for (int b = 0; b < 16; ++b)
-                            if (b < left) orow[c0 + b] = static_cast<uint8_t>(w[b >> 2] >> (8 * (b & 3)));
                     }
                 }
-                cc += kColGroups;
-                while (cc >= cps) { cc -= cps; ++j; }
+                // first chunk of this warp in the next M tile
+                first -= cps_mod;
+                if (first < 0) first += kColGroups;
             }
             tc_fence_before();
             __syncwarp();
