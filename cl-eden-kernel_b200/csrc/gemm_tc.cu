@@ -943,6 +943,139 @@ void launch_im2col(const Im2colGeom &ig, const void *in, uint8_t *dst, int64_t t
     else if (ig.ktab) im2col_kernel<1><<<blocks, 256, 0, s>>>(ig, src, dst, total16);
 }
 
+// ------------------------------------------------------------------------------------------------------
+// First-layer convolution: 3x3 taps over 3 input channels (K = 27), any stride, Cout a multiple of 16.  Gathering
+// 27-byte rows into a matrix and running the GEMM costs two extra passes over a matrix three times the size of the
+// image, for almost no MMA work; here a thread owns one output pixel, builds its 27 window bytes in registers
+// (three 9-byte row segments, read with aligned words and funnel shifts), and walks the output channels with the
+// packed int8 weights and epilogue constants of the tensor-core plan broadcast from shared memory: 7 dp4a and the
+// same exact requantisation per output byte.  Border pixels take a bytewise path with the input zero point as fill.
+// ------------------------------------------------------------------------------------------------------
+template <bool A_SIGNED>
+__device__ __forceinline__ int32_t dp4a_aw(uint32_t a, uint32_t w, int32_t c) {
+    int32_t d;
+    if (A_SIGNED) asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(w), "r"(c));
+    else asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(w), "r"(c));
+    return d;
+}
+
+// Byte k of the 27-byte window stream = byte (k % 9) of row segment k / 9; a row segment sits in three words.
+template <int D>
+__device__ __forceinline__ uint32_t window_word(const uint32_t (&src)[9]) {
+    uint32_t v = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int k = 4 * D + i;
+        if (k < 27) {
+            const int sb = (k / 9) * 12 + (k % 9);      // byte index in src viewed as 36 bytes
+            // place byte sb % 4 of src[sb / 4] at position i of v, keep v's other bytes
+            const uint32_t sel = (i == 0 ? 0x3214u : i == 1 ? 0x3240u : i == 2 ? 0x3410u : 0x4210u) + (static_cast<uint32_t>(sb % 4) << (4 * i));
+            v = __byte_perm(v, src[sb / 4], sel);
+        }
+    }
+    return v;
+}
+
+struct Conv3x3c3Params {
+    int32_t n, h, w, oh, ow, sy, sx, y0, x0;
+    int32_t M, N, k_pad;
+    int32_t zw_eff, act_min, act_max, out_zp;
+    uint32_t fill;
+    int64_t in_bytes;
+};
+
+template <bool A_SIGNED, bool ASUM, bool GENERAL>
+__global__ void __launch_bounds__(256) conv3x3c3_kernel(Conv3x3c3Params g, const uint8_t *__restrict__ in, const int8_t *__restrict__ wq,
+                                                        const ColParam *__restrict__ cols, uint8_t *__restrict__ out) {
+    extern __shared__ uint4 smem_q[];
+    uint4 *s_w = smem_q;                 // [N][2] : 32 weight bytes per output channel (27 real, 5 zero)
+    uint4 *s_c = smem_q + 2 * g.N;       // [N]    : epilogue constants
+    for (int i = threadIdx.x; i < 2 * g.N; i += blockDim.x)
+        s_w[i] = *reinterpret_cast<const uint4 *>(wq + static_cast<size_t>(i >> 1) * g.k_pad + (i & 1) * 16);
+    for (int i = threadIdx.x; i < g.N; i += blockDim.x) s_c[i] = *reinterpret_cast<const uint4 *>(cols + i);
+    __syncthreads();
+    const uint32_t sw_u32 = smem_u32(s_w), sc_u32 = smem_u32(s_c);
+    const int32_t hi_clamp = g.act_max - g.act_min;
+    const uint32_t lo_word = (static_cast<uint32_t>(g.act_min) & 0xff) * 0x01010101u;
+
+    for (int m = blockIdx.x * blockDim.x + threadIdx.x; m < g.M; m += gridDim.x * blockDim.x) {
+        const int ox = m % g.ow, t = m / g.ow;
+        const int oy = t % g.oh, img = t / g.oh;
+        const int iy0 = oy * g.sy + g.y0, ix0 = ox * g.sx + g.x0;
+        uint32_t src[9];
+        const int64_t row0 = ((static_cast<int64_t>(img) * g.h + iy0) * g.w + ix0) * 3;
+        const bool interior = iy0 >= 0 && iy0 + 3 <= g.h && ix0 >= 0 && ix0 + 3 <= g.w &&
+                              row0 + 2ll * g.w * 3 + 12 <= g.in_bytes;      // the aligned words of the last row stay inside the tensor
+        if (interior) {
+#pragma unroll
+            for (int r = 0; r < 3; ++r) {
+                const uint8_t *pr = in + row0 + static_cast<int64_t>(r) * g.w * 3;
+                const uintptr_t a = reinterpret_cast<uintptr_t>(pr);
+                const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~static_cast<uintptr_t>(3));
+                const uint32_t sh = static_cast<uint32_t>(a & 3) * 8;
+                const uint32_t q0 = __ldg(q), q1 = __ldg(q + 1), q2 = __ldg(q + 2);
+                src[3 * r] = __funnelshift_r(q0, q1, sh);
+                src[3 * r + 1] = __funnelshift_r(q1, q2, sh);
+                src[3 * r + 2] = q2 >> sh;
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < 3; ++r) {
+                const int iy = iy0 + r;
+                uint32_t wd[3] = {0, 0, 0};
+#pragma unroll
+                for (int b = 0; b < 9; ++b) {
+                    const int ix = ix0 + b / 3;
+                    uint32_t v = g.fill & 0xff;
+                    if (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w) v = in[((static_cast<int64_t>(img) * g.h + iy) * g.w + ix) * 3 + b % 3];
+                    wd[b / 4] |= v << (8 * (b % 4));
+                }
+                src[3 * r] = wd[0]; src[3 * r + 1] = wd[1]; src[3 * r + 2] = wd[2];
+            }
+        }
+        uint32_t a[7];
+        a[0] = window_word<0>(src); a[1] = window_word<1>(src); a[2] = window_word<2>(src); a[3] = window_word<3>(src);
+        a[4] = window_word<4>(src); a[5] = window_word<5>(src); a[6] = window_word<6>(src);
+        int32_t asum_term = 0;
+        if (ASUM) {
+            int32_t sa = 0;
+#pragma unroll
+            for (int d = 0; d < 7; ++d) sa = dp4a_aw<A_SIGNED>(a[d], d == 6 ? 0x00010101u : 0x01010101u, sa);
+            asum_term = g.zw_eff * sa;
+        }
+        uint8_t *orow = out + static_cast<int64_t>(m) * g.N;
+        for (int n0 = 0; n0 < g.N; n0 += 16) {
+            uint32_t wout[4];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                int32_t y[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int nn = n0 + jj * 4 + b;
+                    uint4 w0, w1;
+                    int4 cv;
+                    asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "r"(sw_u32 + nn * 32));
+                    asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w) : "r"(sw_u32 + nn * 32 + 16));
+                    asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(sc_u32 + nn * 16));
+                    int32_t acc = cv.w;
+                    acc = dp4a_aw<A_SIGNED>(a[0], w0.x, acc);
+                    acc = dp4a_aw<A_SIGNED>(a[1], w0.y, acc);
+                    acc = dp4a_aw<A_SIGNED>(a[2], w0.z, acc);
+                    acc = dp4a_aw<A_SIGNED>(a[3], w0.w, acc);
+                    acc = dp4a_aw<A_SIGNED>(a[4], w1.x, acc);
+                    acc = dp4a_aw<A_SIGNED>(a[5], w1.y, acc);
+                    acc = dp4a_aw<A_SIGNED>(a[6], w1.z, acc);
+                    if (ASUM) acc -= asum_term;
+                    y[b] = tc_requant<GENERAL>(acc, cv, hi_clamp, g.out_zp, g.act_min, g.act_max);
+                }
+                const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
+                wout[jj] = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
+            }
+            *reinterpret_cast<uint4 *>(orow + n0) = make_uint4(wout[0], wout[1], wout[2], wout[3]);
+        }
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -966,6 +1099,7 @@ struct TcGemm {
     int grid = 0;
     int threads = 0;                   // kThreads (separate B producer warp) for long-K GEMMs, else kThreadsOneProducer
     bool gather = false;               // A is gathered into scratch by im2col first
+    bool first_layer = false;          // 3x3 taps over 3 channels: conv3x3c3_kernel instead of gather + GEMM
     bool use_gemv = false;             // M <= 8 read in place: weight-streaming GEMV instead of the tensor-core kernel
     // Implicit convolution (stride-1 taps read as TMA boxes, no gathered matrix): the source is either the caller's
     // tensor (input zero point 0: the zero OOB fill is already right) or a zero-point padded copy in scratch.
@@ -1204,6 +1338,32 @@ void launch_tc_gemm_variant(const TcGemm &gm, const CUtensorMap &map_a, const Tc
     cudaLaunchKernelEx(&cfg, tc_gemm_kernel<ASUM, GENERAL, true>, map_a, gm.map_b, p);
 }
 
+void launch_first_layer(enn_b200_context *ctx, const TcGemm &gm, const void *in, void *out) {
+    const TcParams &p = gm.prm;
+    const Im2colGeom &ig = gm.ig;
+    Conv3x3c3Params g{};
+    g.n = ig.n; g.h = ig.h; g.w = ig.w; g.oh = ig.oh; g.ow = ig.ow; g.sy = ig.sy; g.sx = ig.sx; g.y0 = ig.y0; g.x0 = ig.x0;
+    g.M = p.M; g.N = p.N; g.k_pad = p.k_blocks * kBK;
+    g.zw_eff = p.zw_eff; g.act_min = p.act_min; g.act_max = p.act_max; g.out_zp = p.out_zp;
+    g.fill = ig.fill;
+    g.in_bytes = static_cast<int64_t>(ig.n) * ig.h * ig.w * 3;
+    const size_t smem = static_cast<size_t>(p.N) * 48;
+    const int64_t want = (static_cast<int64_t>(p.M) + 255) / 256;
+    const unsigned blocks = static_cast<unsigned>(want < 8ll * ctx->sm_count ? want : 8ll * ctx->sm_count);
+    const uint8_t *src = static_cast<const uint8_t *>(in);
+    const int8_t *wq = static_cast<const int8_t *>(gm.w_dev);
+    uint8_t *dst = static_cast<uint8_t *>(out);
+#define ENN_FL(S, A, G) conv3x3c3_kernel<S, A, G><<<blocks, 256, smem, ctx->stream>>>(g, src, wq, p.cols, dst)
+    if (p.a_signed) {
+        if (p.need_asum) { if (p.general) ENN_FL(true, true, true); else ENN_FL(true, true, false); }
+        else { if (p.general) ENN_FL(true, false, true); else ENN_FL(true, false, false); }
+    } else {
+        if (p.need_asum) { if (p.general) ENN_FL(false, true, true); else ENN_FL(false, true, false); }
+        else { if (p.general) ENN_FL(false, false, true); else ENN_FL(false, false, false); }
+    }
+#undef ENN_FL
+}
+
 void launch_tc_gemm(const TcGemm &gm, const CUtensorMap &map_a, const TcParams &p, cudaStream_t stream) {
     if (p.need_asum) {
         if (p.general) launch_tc_gemm_variant<true, true>(gm, map_a, p, stream);
@@ -1266,6 +1426,8 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
             if (st2 != ENN_B200_SUCCESS) return st2;
             gm.gather = true;
             gm.ig.K = K; gm.ig.Kp = (K + 15) & ~15;
+            gm.first_layer = ig.kh == 3 && ig.kw == 3 && cin == 3 && ig.dy == 1 && ig.dx == 1 && (N & 15) == 0 && gm.prm.tiles_n == 1 &&
+                             M64 >= 4096 && !getenv("ENN_B200_NO_FIRST_LAYER");
             const size_t need = static_cast<size_t>(M64) * gm.ig.Kp;
             if (need > plan->scratch_bytes) plan->scratch_bytes = need;
             return ENN_B200_SUCCESS;
@@ -1431,7 +1593,7 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
     int launches = 0;
     for (auto &gm : plan->gemms) {
         gm.prm.err = plan->err_dev;
-        launches += (gm.gather || (gm.implicit && gm.runs_pad)) ? 2 : 1;
+        launches += ((gm.gather && !gm.first_layer) || (gm.implicit && gm.runs_pad)) ? 2 : 1;
         if (gm.implicit && gm.padded) {
             if (!encode_nhwc(ctx, &gm.map_a, plan->scratch, cin, gm.wp, gm.hp, g.n, gm.prm.span, gm.prm.conv_wt, gm.prm.conv_ht)) {
                 ctx->last_error = "cuTensorMapEncodeTiled failed for the padded activation tensor";
@@ -1492,6 +1654,15 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
     for (auto &gm : plan->gemms) {
         TcParams &p = gm.prm;
         if (p.M == 0) continue;
+        if (gm.first_layer && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+            launch_first_layer(ctx, gm, in, out);
+            cudaError_t fe = cudaGetLastError();
+            if (fe != cudaSuccess) {
+                ctx->last_error = std::string("conv3x3c3_kernel launch: ") + cudaGetErrorString(fe);
+                return ENN_B200_CUDA_FAILURE;
+            }
+            continue;
+        }
         if (gm.gather) {
             const int64_t total16 = static_cast<int64_t>(p.M) * (gm.ig.Kp >> 4);
             const unsigned blocks = static_cast<unsigned>((total16 + 255) / 256);

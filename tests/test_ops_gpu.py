@@ -55,6 +55,12 @@ CONV_CASES = {
     "implicit_wide": dict(n=1, h=5, w=150, cin=32, cout=32, k=3),
     "implicit_5x5_valid": dict(n=1, h=12, w=12, cin=32, cout=24, k=5, pad="valid"),
     "implicit_c96": dict(n=1, h=9, w=9, cin=96, cout=40, k=3),
+    # first-layer kernel (3x3 taps over 3 channels, >= 4096 output pixels): stride 2 per-channel, stride 1 with u8
+    # per-tensor weights (row-sum correction), signed activations, VALID padding, odd widths (unaligned row starts)
+    "first_layer_s2": dict(n=4, h=66, w=71, cin=3, cout=32, k=3, stride=2, per_channel=True, out_scale=0.1),
+    "first_layer_s1_u8w": dict(n=2, h=47, w=53, cin=3, cout=16, k=3, w_zp=121, out_scale=0.05),
+    "first_layer_signed": dict(n=1, h=70, w=69, cin=3, cout=48, k=3, act_dtype=cases.enn.S8, in_zp=-7, out_zp=3, per_channel=True, out_scale=0.2),
+    "first_layer_valid": dict(n=3, h=41, w=43, cin=3, cout=32, k=3, pad="valid", per_channel=True, out_scale=0.15, act=cases.enn.ACT_NONE),
 }
 
 
