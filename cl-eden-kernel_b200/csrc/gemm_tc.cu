@@ -410,6 +410,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (TWO) tmem_alloc_pair(smem_u32(tmem_slot), 512);
         else tmem_alloc(smem_u32(tmem_slot), 512);
     }
+    // Column constants: when those of all N tiles fit the staging area they are loaded here once, shared by every
+    // epilogue warp (any warp can then take any chunk); otherwise each epilogue warp keeps private copies of the
+    // columns it owns and refreshes them when the N tile changes.
+    const bool cols_shared = p.tiles_n * p.bn_rows <= kEpiWarps * kChunksPerWarp * 16;
+    if (cols_shared)
+        for (int i = threadIdx.x; i < p.tiles_n * p.bn_rows; i += blockDim.x) s_cols[i] = __ldg(reinterpret_cast<const int4 *>(p.cols) + i);
     tc_fence_before();
     __syncthreads();
     if (TWO) cluster_sync_all();        // the peer's barriers exist before anything signals them
@@ -603,6 +609,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int patch_y = p.taps > 0 ? row_in_tile / p.conv_wt : 0;   // this thread's position in the output patch
         const int patch_x = p.taps > 0 ? row_in_tile - patch_y * p.conv_wt : 0;
         const int cps_mod = (p.bn_data >> 4) % kColGroups;
+        const uint32_t rot_step = static_cast<uint32_t>((p.group * (p.bn_data >> 4)) % kColGroups);
         uint32_t it = 0;
         bool ok = true;
         int loaded_tn = -1;
@@ -617,7 +624,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // cgrp, cgrp + kColGroups, ...; it keeps private copies of the constants of the columns it meets.
             const int cps = p.bn_data >> 4;
             const uint32_t my_cols = s_cols_u32 + (warp - 2) * (kChunksPerWarp * 16 * 16);
-            if (tn != loaded_tn) {
+            if (!cols_shared && tn != loaded_tn) {
                 const int4 *src = reinterpret_cast<const int4 *>(p.cols + static_cast<size_t>(tn) * p.bn_rows);
                 __syncwarp();
                 for (int i = lane; i < kChunksPerWarp * 16; i += 32) {
@@ -640,8 +647,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // Walk this warp's chunks M tile by M tile: chunk c = j * cps + cc belongs to this warp when c = cgrp (mod
             // kColGroups); `first` is the first such cc of M tile j and moves by -cps (mod kColGroups) from one M tile to
             // the next.  Everything that depends only on the M tile (row pointer, row sum) is computed once per j.
+            // With shared constants the column groups that get one chunk more than the others change from tile to tile
+            // (the chunks of a buffer rarely divide evenly over the groups).
             int first = cgrp;
-            uint32_t lc = my_cols;
+            if (cols_shared) {
+                first += static_cast<int>((it * rot_step) % kColGroups);
+                if (first >= kColGroups) first -= kColGroups;
+            }
+            uint32_t lc_private = my_cols;
+            const uint32_t lc_shared = s_cols_u32 + static_cast<uint32_t>(tn * p.bn_rows) * 16;
             const uint8_t *out_tile = p.out + p.out_base + n_base;
             for (int j = 0; j < nsub && !(p.dbg_mode & 2); ++j) {
                 if (first < cps) {
@@ -672,7 +686,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         tmem_ld_wait();
                         asum_term = p.zw_eff * static_cast<int32_t>(rs);
                     }
-                    for (int c0 = first << 4; c0 < (cps << 4); c0 += kColGroups * 16, lc += 256) {
+                    for (int c0 = first << 4; c0 < (cps << 4); c0 += kColGroups * 16, lc_private += 256) {
+                        const uint32_t lc = cols_shared ? lc_shared + c0 * 16 : lc_private;
                         uint32_t r[16];
                         tmem_ld_x16(t_tile + c0, r);              // warp-collective
                         tmem_ld_wait();
