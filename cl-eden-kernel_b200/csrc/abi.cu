@@ -91,6 +91,12 @@ void fill_info(enn_b200_op *op, int64_t in_elems, int64_t out_elems, int64_t mac
 }  // namespace
 
 namespace enn_b200 {
+
+bool pdl_enabled() {
+    static const bool on = getenv("ENN_B200_NO_PDL") == nullptr;
+    return on;
+}
+
 // mma_peak.cu
 double measure_mma_peak(enn_b200_context *ctx, int kind, int n, int iters);
 // gemm_tc.cu

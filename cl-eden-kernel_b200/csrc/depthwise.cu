@@ -202,6 +202,8 @@ template <int STRIDE, bool W_SIGNED, bool NEED_ASUM>
 __global__ void __launch_bounds__(256, 2)
 dw3x3_kernel(ConvGeom g, const DwChan *__restrict__ chan, const uint32_t *__restrict__ w_packed,
              const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int th, int nyt, int nstrip, int64_t total) {
+    pdl_wait();         // the tensors of the kernel before this one are complete from here on
+    pdl_trigger();
     const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (tid >= total) return;
     const int cqn = g.cin >> 2;
@@ -688,7 +690,7 @@ cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, const void *w_pack
     const uint8_t *i = static_cast<const uint8_t *>(in);
     uint8_t *o = static_cast<uint8_t *>(out);
     const bool need_asum = g.w_zp != 0;
-#define ENN_DW_LAUNCH(ST, WS, AS) dw3x3_kernel<ST, WS, AS><<<blocks, threads, 0, s>>>(g, c, w, i, o, th, nyt, nstrip, total)
+#define ENN_DW_LAUNCH(ST, WS, AS) launch_pdl(dw3x3_kernel<ST, WS, AS>, dim3(blocks), dim3(threads), 0, s, g, c, w, i, o, th, nyt, nstrip, total)
     if (g.sh == 1) {
         if (g.w_signed) { if (need_asum) ENN_DW_LAUNCH(1, true, true); else ENN_DW_LAUNCH(1, true, false); }
         else            { if (need_asum) ENN_DW_LAUNCH(1, false, true); else ENN_DW_LAUNCH(1, false, false); }

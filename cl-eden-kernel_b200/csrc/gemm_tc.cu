@@ -421,6 +421,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (TWO) cluster_sync_all();        // the peer's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched only this launch's own resources and constants; the activations of the kernel before
+    // this one are complete (and the tensor this one writes is no longer read) from here on.
+    pdl_wait();
+    pdl_trigger();
 
     // Work unit = (N tile, group of `group` consecutive M tiles).  For narrow N several M tiles share one accumulator
     // buffer, so that every epilogue warp has columns to work on.
@@ -1009,6 +1013,8 @@ __global__ void __launch_bounds__(256) conv3x3c3_kernel(Conv3x3c3Params g, const
         s_w[i] = *reinterpret_cast<const uint4 *>(wq + static_cast<size_t>(i >> 1) * g.k_pad + (i & 1) * 16);
     for (int i = threadIdx.x; i < g.N; i += blockDim.x) s_c[i] = *reinterpret_cast<const uint4 *>(cols + i);
     __syncthreads();
+    pdl_wait();         // weights and constants above belong to the plan; the image may come from the kernel before
+    pdl_trigger();
     const uint32_t sw_u32 = smem_u32(s_w), sc_u32 = smem_u32(s_c);
     const int32_t hi_clamp = g.act_max - g.act_min;
     const uint32_t lo_word = (static_cast<uint32_t>(g.act_min) & 0xff) * 0x01010101u;
@@ -1335,7 +1341,7 @@ void free_plan(TcPlan *plan) {
 template <bool ASUM, bool GENERAL>
 void launch_tc_gemm_variant(const TcGemm &gm, const CUtensorMap &map_a, const TcParams &p, cudaStream_t stream) {
     if (!p.two) {
-        tc_gemm_kernel<ASUM, GENERAL, false><<<gm.grid, gm.threads, gm.smem_bytes, stream>>>(map_a, gm.map_b, p);
+        launch_pdl(tc_gemm_kernel<ASUM, GENERAL, false>, dim3(static_cast<unsigned>(gm.grid)), dim3(static_cast<unsigned>(gm.threads)), gm.smem_bytes, stream, map_a, gm.map_b, p);
         return;
     }
     cudaLaunchConfig_t cfg{};
@@ -1368,7 +1374,7 @@ void launch_first_layer(enn_b200_context *ctx, const TcGemm &gm, const void *in,
     const uint8_t *src = static_cast<const uint8_t *>(in);
     const int8_t *wq = static_cast<const int8_t *>(gm.w_dev);
     uint8_t *dst = static_cast<uint8_t *>(out);
-#define ENN_FL(S, A, G) conv3x3c3_kernel<S, A, G><<<blocks, 256, smem, ctx->stream>>>(g, src, wq, p.cols, dst)
+#define ENN_FL(S, A, G) launch_pdl(conv3x3c3_kernel<S, A, G>, dim3(blocks), dim3(256), smem, ctx->stream, g, src, wq, p.cols, dst)
     if (p.a_signed) {
         if (p.need_asum) { if (p.general) ENN_FL(true, true, true); else ENN_FL(true, true, false); }
         else { if (p.general) ENN_FL(true, false, true); else ENN_FL(true, false, false); }

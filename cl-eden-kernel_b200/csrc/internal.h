@@ -74,6 +74,8 @@ struct enn_b200_op {
 
 namespace enn_b200 {
 
+bool pdl_enabled();     // abi.cu: false when ENN_B200_NO_PDL is set (development switch)
+
 // kernels_direct.cu
 cudaError_t launch_conv_direct(const ConvGeom &g, const Requant &rq, const void *in, const void *w, void *out,
                                cudaStream_t s);
@@ -92,5 +94,31 @@ cudaError_t launch_add(const AddParams &p, int64_t count, const void *a, const v
 cudaError_t launch_avgpool(const PoolGeom &p, const void *in, void *out, cudaStream_t s);
 cudaError_t launch_transpose_nchw_nhwc(const void *src, void *dst, int n, int c, int h, int w, bool to_nhwc,
                                        cudaStream_t s);
+
+
+// ---- programmatic dependent launch ------------------------------------------------------------------------
+// Kernels launched with launch_pdl may start (block scheduling, their own set-up code) while the kernel before them in
+// the stream is still draining; they call pdl_wait() before they read or write any tensor, which blocks until that
+// kernel has completed and its writes are visible, and pdl_trigger() to let their own successor start early.  A kernel
+// that is launched the ordinary way keeps the ordinary stream order, whatever its neighbours do.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 
 }  // namespace enn_b200

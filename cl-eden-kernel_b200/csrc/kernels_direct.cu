@@ -102,6 +102,8 @@ cudaError_t launch_deconv_direct(const ConvGeom &g, const Requant &rq, const voi
 // Quantized add: AddKernelsQauntized.cpp:135-219 (left shift 20, three SRDHM + rounding-shift stages).
 __global__ void add_kernel(AddParams p, int64_t count, const uint8_t *__restrict__ a, const uint8_t *__restrict__ b,
                            uint8_t *__restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride) {
         const int32_t v0 = p.in0_off + load_byte(a, i, p.is_signed);
@@ -118,6 +120,8 @@ __global__ void add_kernel(AddParams p, int64_t count, const uint8_t *__restrict
 // 16 bytes per thread per step; used when count and pointers allow.
 __global__ void add_kernel_vec(AddParams p, int64_t count16, const uint4 *__restrict__ a, const uint4 *__restrict__ b,
                                uint4 *__restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count16; i += stride) {
         const uint4 va = a[i], vb = b[i];
@@ -154,24 +158,26 @@ cudaError_t launch_add(const AddParams &p, int64_t count, const void *a, const v
         const int64_t n16 = count / 16;
         const int64_t want = (n16 + threads - 1) / threads;
         const int blocks = static_cast<int>(want < static_cast<int64_t>(sm_count) * 8 ? want : static_cast<int64_t>(sm_count) * 8);
-        add_kernel_vec<<<blocks, threads, 0, s>>>(p, n16, static_cast<const uint4 *>(a), static_cast<const uint4 *>(b),
-                                                  static_cast<uint4 *>(out));
+        launch_pdl(add_kernel_vec, dim3(blocks), dim3(threads), 0, s, p, n16, static_cast<const uint4 *>(a), static_cast<const uint4 *>(b),
+                   static_cast<uint4 *>(out));
         const int64_t tail = count - n16 * 16;
         if (tail > 0) {
-            add_kernel<<<1, 32, 0, s>>>(p, tail, static_cast<const uint8_t *>(a) + n16 * 16,
-                                        static_cast<const uint8_t *>(b) + n16 * 16, static_cast<uint8_t *>(out) + n16 * 16);
+            launch_pdl(add_kernel, dim3(1), dim3(32), 0, s, p, tail, static_cast<const uint8_t *>(a) + n16 * 16,
+                       static_cast<const uint8_t *>(b) + n16 * 16, static_cast<uint8_t *>(out) + n16 * 16);
         }
     } else {
         const int64_t want = (count + threads - 1) / threads;
         const int blocks = static_cast<int>(want < static_cast<int64_t>(sm_count) * 8 ? want : static_cast<int64_t>(sm_count) * 8);
-        add_kernel<<<blocks, threads, 0, s>>>(p, count, static_cast<const uint8_t *>(a), static_cast<const uint8_t *>(b),
-                                              static_cast<uint8_t *>(out));
+        launch_pdl(add_kernel, dim3(blocks), dim3(threads), 0, s, p, count, static_cast<const uint8_t *>(a), static_cast<const uint8_t *>(b),
+                   static_cast<uint8_t *>(out));
     }
     return cudaGetLastError();
 }
 
 // Average pool: AveragepoolKernels.cpp:8-54.  One thread per (pixel, channel), channel fastest (NHWC).
 __global__ void avgpool_kernel(PoolGeom p, const void *__restrict__ in, uint8_t *__restrict__ out, int64_t total) {
+    pdl_wait();
+    pdl_trigger();
     const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const int32_t c = static_cast<int32_t>(idx % p.c);
@@ -199,8 +205,8 @@ cudaError_t launch_avgpool(const PoolGeom &p, const void *in, void *out, cudaStr
     const int64_t total = static_cast<int64_t>(p.n) * p.oh * p.ow * p.c;
     if (total == 0) return cudaSuccess;
     const int threads = 256;
-    avgpool_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, s>>>(
-        p, in, static_cast<uint8_t *>(out), total);
+    launch_pdl(avgpool_kernel, dim3(static_cast<unsigned>((total + threads - 1) / threads)), dim3(threads), 0, s, p, in,
+               static_cast<uint8_t *>(out), total);
     return cudaGetLastError();
 }
 
