@@ -70,7 +70,7 @@ struct TcParams {
     int32_t a_signed;
     int32_t act_min, act_max, out_zp;
     int32_t two;            // 1: CTA-pair mode (tiles_mg counts pairs of M tiles, group == 1, kpack == 1)
-    int32_t general;        // 1: some column needs the general (left shift / wide) requantisation
+    int32_t mode;           // epilogue mode (kModeNudge ...), see tc_requant
     uint32_t idesc;
     const ColParam *cols;   // [tiles_n][bn_rows]
     uint8_t *out;           // output tensor base
@@ -247,13 +247,11 @@ __device__ __forceinline__ void umma_i8_run(uint32_t d_tmem, uint32_t desc_hi, u
 #undef ENN_MMA_PAIR
 }
 
-__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
+__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld_x1(uint32_t taddr, uint32_t &r) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
@@ -306,15 +304,45 @@ __device__ __forceinline__ void tile_coords(const TcParams &p, int tile, int &tg
     tg = g0 + (r - tn * gw);
 }
 
-// Requantise one accumulator to (value - act_min) in [0, act_max - act_min].
+// Epilogue modes (one kernel variant each; the planner picks the cheapest one every column of the operator allows):
+//   kModeNudge   fused two-stage form below, every column a right shift e >= 1;
+//   kModeGeneral as kModeNudge, but columns flagged esh < 0 take the general code (left shifts, e == 0, wide ranges);
+//   kModeReluTwo lower clamp == output zero point (ReLU-type outputs): a negative stage-1 value ends at the clamp with or
+//                without the tie correction, so the correction is dropped and the bias, both rounding terms and a left
+//                shift ls fold into one 64-bit addend: q = acc * M0 + C, C = bias * M0 + 2^(30-ls) (+ 2^(e-1+31-ls) when
+//                e >= 1); result = (q >> (31 - ls)) >> e.  Covers e == 0 and left shifts, which otherwise need the
+//                general code.
+//   kModeReluHi  the same with one shift, hi32(q) >> (e - 1), for operators whose columns all have e >= 1 and ls == 0:
+//                implemented, but its shorter chains make the compiler keep more constants in flight than the epilogue's
+//                72 registers hold; it spilled and measured slower, so the planner does not select it.
+// ColParam words: {mult, addend, esh, bias} for the first two modes, {C low, C high, mult, shifts} for the ReLU modes
+// (shifts = e - 1 for kModeReluHi, (31 - ls) | e << 8 for kModeReluTwo).
+constexpr int kModeNudge = 0, kModeGeneral = 1, kModeReluHi = 2, kModeReluTwo = 3;
+
+// Requantise one accumulator (bias not yet added) to (value - act_min) in [0, act_max - act_min].
 // Fast form (esh = right shift e >= 1): stage 1 is one 32x32->64 multiply-add and a funnel shift, stage 2 is
 // (x + addend - [x < 0]) >> e with addend = 2^(e-1) + ((out_zp - act_min) << e), i.e. RoundingDivideByPOT
-// (ties away from zero) with the zero point and the lower clamp folded in.  Columns that need a left shift,
-// e == 0, or whose accumulator range could overflow the fused form carry esh < 0 and take the general code.
-template <bool GENERAL>
+// (ties away from zero) with the zero point and the lower clamp folded in.
+template <int MODE>
 __device__ __forceinline__ int32_t tc_requant(int32_t acc, const int4 &c, int32_t hi_clamp, int32_t out_zp, int32_t act_min,
                                               int32_t act_max) {
-    if (GENERAL && c.z < 0) return enn_requant(acc, c.x, c.y, out_zp, act_min, act_max) - act_min;   // c.y = raw shift
+    if (MODE == kModeReluHi || MODE == kModeReluTwo) {
+        int64_t cc;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(cc) : "r"(c.x), "r"(c.y));
+        const int64_t q = static_cast<int64_t>(acc) * c.z + cc;
+        int32_t lo, hi;
+        asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(q));
+        int32_t v;
+        if (MODE == kModeReluHi) {
+            v = hi >> c.w;
+        } else {
+            const int32_t xa = static_cast<int32_t>(__funnelshift_r(static_cast<uint32_t>(lo), static_cast<uint32_t>(hi), static_cast<uint32_t>(c.w)));
+            v = xa >> (c.w >> 8);
+        }
+        return __vimin_s32_relu(v, hi_clamp);
+    }
+    acc += c.w;
+    if (MODE == kModeGeneral && c.z < 0) return enn_requant(acc, c.x, c.y, out_zp, act_min, act_max) - act_min;   // c.y = raw shift
     const int64_t p = static_cast<int64_t>(acc) * c.x + (1ll << 30);
     const int32_t x = static_cast<int32_t>(p >> 31);
     const int32_t v = (x + c.y - static_cast<int32_t>(static_cast<uint32_t>(x) >> 31)) >> c.z;
@@ -363,7 +391,7 @@ ENN_TILE_FN(mma_tile_d6, 6, case 0: ENN_KB(0) case 1: ENN_KB(1) case 2: ENN_KB(2
 
 // TWO: CTA-pair mode (launched as clusters of 2; plain GEMM operands only, group == 1, kpack == 1): the pair owns M
 // tiles 2t and 2t + 1 of one N tile, every B byte is read from L2 once per pair, and a stage per CTA is A plus half of B.
-template <bool ASUM, bool GENERAL, bool TWO>
+template <bool ASUM, int MODE, bool TWO>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -692,25 +720,31 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                     for (int c0 = first << 4; c0 < (cps << 4); c0 += kColGroups * 16, lc_private += 256) {
                         const uint32_t lc = cols_shared ? lc_shared + c0 * 16 : lc_private;
-                        uint32_t r[16];
-                        tmem_ld_x16(t_tile + c0, r);              // warp-collective
-                        tmem_ld_wait();
-                        if (row_ok && c0 < n_cols) {
-                            uint32_t w[4];
+                        // two 8-column loads per chunk: half the accumulator registers live at a time
+                        uint32_t w[4];
 #pragma unroll
-                            for (int jj = 0; jj < 4; ++jj) {
-                                int32_t y[4];
+                        for (int half = 0; half < 2; ++half) {
+                            uint32_t r[8];
+                            tmem_ld_x8(t_tile + c0 + 8 * half, r);      // warp-collective
+                            tmem_ld_wait();
+                            if (row_ok && c0 < n_cols) {
 #pragma unroll
-                                for (int b = 0; b < 4; ++b) {
-                                    int4 cv;
-                                    asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(lc + (jj * 4 + b) * 16));
-                                    int32_t acc = static_cast<int32_t>(r[jj * 4 + b]) + cv.w;
-                                    if (ASUM) acc -= asum_term;
-                                    y[b] = tc_requant<GENERAL>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
+                                for (int jj = 0; jj < 2; ++jj) {
+                                    int32_t y[4];
+#pragma unroll
+                                    for (int b = 0; b < 4; ++b) {
+                                        int4 cv;
+                                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(lc + (half * 8 + jj * 4 + b) * 16));
+                                        int32_t acc = static_cast<int32_t>(r[jj * 4 + b]);
+                                        if (ASUM) acc -= asum_term;
+                                        y[b] = tc_requant<MODE>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
+                                    }
+                                    const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
+                                    w[half * 2 + jj] = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
                                 }
-                                const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
-                                w[jj] = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
                             }
+                        }
+                        if (row_ok && c0 < n_cols) {
                             if (st_fast) {
                                 *reinterpret_cast<uint4 *>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
                             } else {
@@ -825,8 +859,8 @@ gemv_kernel(const uint8_t *__restrict__ a, const int8_t *__restrict__ w, const C
         const int4 cv = make_int4(c.mult, c.addend, c.esh, c.bias);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-            const int32_t v = acc[m] - zw_eff * asum[m] + c.bias;
-            out[static_cast<size_t>(m) * N + n] = static_cast<uint8_t>(tc_requant<true>(v, cv, act_max - act_min, out_zp, act_min, act_max) + act_min);
+            const int32_t v = acc[m] - zw_eff * asum[m];
+            out[static_cast<size_t>(m) * N + n] = static_cast<uint8_t>(tc_requant<kModeGeneral>(v, cv, act_max - act_min, out_zp, act_min, act_max) + act_min);
         }
     }
 }
@@ -1003,7 +1037,7 @@ struct Conv3x3c3Params {
     int64_t in_bytes;
 };
 
-template <bool A_SIGNED, bool ASUM, bool GENERAL>
+template <bool A_SIGNED, bool ASUM, int MODE>
 __global__ void __launch_bounds__(256) conv3x3c3_kernel(Conv3x3c3Params g, const uint8_t *__restrict__ in, const int8_t *__restrict__ wq,
                                                         const ColParam *__restrict__ cols, uint8_t *__restrict__ out) {
     extern __shared__ uint4 smem_q[];
@@ -1078,7 +1112,7 @@ __global__ void __launch_bounds__(256) conv3x3c3_kernel(Conv3x3c3Params g, const
                     asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "r"(sw_u32 + nn * 32));
                     asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w) : "r"(sw_u32 + nn * 32 + 16));
                     asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(sc_u32 + nn * 16));
-                    int32_t acc = cv.w;
+                    int32_t acc = 0;
                     acc = dp4a_aw<A_SIGNED>(a[0], w0.x, acc);
                     acc = dp4a_aw<A_SIGNED>(a[1], w0.y, acc);
                     acc = dp4a_aw<A_SIGNED>(a[2], w0.z, acc);
@@ -1087,7 +1121,7 @@ __global__ void __launch_bounds__(256) conv3x3c3_kernel(Conv3x3c3Params g, const
                     acc = dp4a_aw<A_SIGNED>(a[5], w1.y, acc);
                     acc = dp4a_aw<A_SIGNED>(a[6], w1.z, acc);
                     if (ASUM) acc -= asum_term;
-                    y[b] = tc_requant<GENERAL>(acc, cv, hi_clamp, g.out_zp, g.act_min, g.act_max);
+                    y[b] = tc_requant<MODE>(acc, cv, hi_clamp, g.out_zp, g.act_min, g.act_max);
                 }
                 const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
                 wout[jj] = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
@@ -1254,8 +1288,9 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     std::vector<int8_t> wb(static_cast<size_t>(tiles_n) * p.bn_rows * k_pad, 0);
     std::vector<ColParam> cols(static_cast<size_t>(tiles_n) * p.bn_rows);
     std::memset(cols.data(), 0, cols.size() * sizeof(ColParam));
-    p.general = 0;
     const int64_t amax = g.a_signed ? 128 : 255;
+    const int64_t zo_eff = static_cast<int64_t>(g.out_zp) - g.act_min;
+    std::vector<int64_t> folded_v(N), bound_v(N);
     for (int32_t n = 0; n < N; ++n) {
         const int32_t tn = n / bn_data, r = n % bn_data;
         int8_t *dst = wb.data() + (static_cast<size_t>(tn) * p.bn_rows + r) * k_pad;
@@ -1269,18 +1304,55 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         }
         const int64_t folded = static_cast<int64_t>(qh.bias[n]) - static_cast<int64_t>(g.in_zp) * wsum +
                                static_cast<int64_t>(K) * g.in_zp * zw_eff;
+        folded_v[n] = folded;
+        // bound on |accumulator + folded bias|
+        bound_v[n] = amax * wabs + static_cast<int64_t>(K) * amax * (zw_eff < 0 ? -zw_eff : zw_eff) + (folded < 0 ? -folded : folded);
+    }
+    // ReLU-type outputs (lower clamp == output zero point): can every column use the merged form?
+    bool relu_hi = zo_eff == 0 && M > kGemvMaxM && !getenv("ENN_B200_NO_RELU_MODE"), relu_two = relu_hi;
+    for (int32_t n = 0; n < N && relu_two; ++n) {
+        const int32_t sh = qh.shift[n];
+        const int32_t ls = sh > 0 ? sh : 0, e = sh > 0 ? 0 : -sh;
+        const bool in_range = folded_v[n] <= INT32_MAX && folded_v[n] >= INT32_MIN && bound_v[n] < (1ll << 31) && qh.mult[n] >= 0;
+        if (!in_range || ls > 30 || e > 31) relu_hi = relu_two = false;
+        if (ls > 0 || e < 1) relu_hi = false;
+        // two-shift form: the left-shifted accumulator must not wrap (the reference multiplies in int32) and the
+        // stage-1 value plus the rounding term must fit 32 bits
+        if ((bound_v[n] << ls) + (e >= 1 ? (1ll << (e - 1)) : 0) + 1 >= (1ll << 31)) relu_two = false;
+    }
+    (void)relu_hi;      // the one-shift form needs more registers than the 72 the epilogue has and spills: measured slower
+    p.mode = relu_two ? kModeReluTwo : kModeNudge;
+    for (int32_t n = 0; n < N; ++n) {
+        const int32_t tn = n / bn_data, r = n % bn_data;
+        const int64_t folded = folded_v[n];
         ColParam &c = cols[static_cast<size_t>(tn) * p.bn_rows + r];
+        if (p.mode == kModeReluHi || p.mode == kModeReluTwo) {
+            const int32_t sh = qh.shift[n];
+            const int32_t ls = sh > 0 ? sh : 0, e = sh > 0 ? 0 : -sh;
+            int64_t cc = folded * qh.mult[n];
+            int32_t word;
+            if (p.mode == kModeReluHi) {
+                cc += (1ll << 30) + (1ll << (30 + e));
+                word = e - 1;
+            } else {
+                const int32_t s1 = 31 - ls;
+                cc += (1ll << (30 - ls)) + (e >= 1 ? (1ll << (e - 1 + s1)) : 0);
+                word = s1 | (e << 8);
+            }
+            c.mult = static_cast<int32_t>(static_cast<uint32_t>(static_cast<uint64_t>(cc) & 0xffffffffu));   // word 0: C low
+            c.addend = static_cast<int32_t>(static_cast<uint32_t>(static_cast<uint64_t>(cc) >> 32));            // word 1: C high
+            c.esh = qh.mult[n];                                                                                // word 2: M0
+            c.bias = word;                                                                                     // word 3: shifts
+            continue;
+        }
         c.mult = qh.mult[n];
         c.bias = static_cast<int32_t>(folded);     // wraps like the reference's int32 accumulation
         const int32_t e = qh.shift[n] > 0 ? -1 : -qh.shift[n];
-        const int64_t zo_eff = static_cast<int64_t>(g.out_zp) - g.act_min;
         const int64_t addend = e > 0 ? (1ll << (e - 1)) + zo_eff * (1ll << e) : zo_eff;
-        const int64_t acc_bound = amax * wabs + static_cast<int64_t>(K) * amax * (zw_eff < 0 ? -zw_eff : zw_eff) +
-                                  (folded < 0 ? -folded : folded);
-        if (e < 1 || folded > INT32_MAX || folded < INT32_MIN || acc_bound + 2 + (addend < 0 ? -addend : addend) >= (1ll << 31)) {
+        if (e < 1 || folded > INT32_MAX || folded < INT32_MIN || bound_v[n] + 2 + (addend < 0 ? -addend : addend) >= (1ll << 31)) {
             c.addend = qh.shift[n];                // general path keeps the raw signed shift
             c.esh = INT32_MIN;
-            p.general = 1;
+            p.mode = kModeGeneral;
         } else {
             c.addend = static_cast<int32_t>(addend);
             c.esh = e;
@@ -1338,10 +1410,10 @@ void free_plan(TcPlan *plan) {
     delete plan;
 }
 
-template <bool ASUM, bool GENERAL>
+template <bool ASUM, int MODE>
 void launch_tc_gemm_variant(const TcGemm &gm, const CUtensorMap &map_a, const TcParams &p, cudaStream_t stream) {
     if (!p.two) {
-        launch_pdl(tc_gemm_kernel<ASUM, GENERAL, false>, dim3(static_cast<unsigned>(gm.grid)), dim3(static_cast<unsigned>(gm.threads)), gm.smem_bytes, stream, map_a, gm.map_b, p);
+        launch_pdl(tc_gemm_kernel<ASUM, MODE, false>, dim3(static_cast<unsigned>(gm.grid)), dim3(static_cast<unsigned>(gm.threads)), gm.smem_bytes, stream, map_a, gm.map_b, p);
         return;
     }
     cudaLaunchConfig_t cfg{};
@@ -1356,7 +1428,7 @@ void launch_tc_gemm_variant(const TcGemm &gm, const CUtensorMap &map_a, const Tc
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, tc_gemm_kernel<ASUM, GENERAL, true>, map_a, gm.map_b, p);
+    cudaLaunchKernelEx(&cfg, tc_gemm_kernel<ASUM, MODE, true>, map_a, gm.map_b, p);
 }
 
 void launch_first_layer(enn_b200_context *ctx, const TcGemm &gm, const void *in, void *out) {
@@ -1375,30 +1447,39 @@ void launch_first_layer(enn_b200_context *ctx, const TcGemm &gm, const void *in,
     const int8_t *wq = static_cast<const int8_t *>(gm.w_dev);
     uint8_t *dst = static_cast<uint8_t *>(out);
 #define ENN_FL(S, A, G) launch_pdl(conv3x3c3_kernel<S, A, G>, dim3(blocks), dim3(256), smem, ctx->stream, g, src, wq, p.cols, dst)
-    if (p.a_signed) {
-        if (p.need_asum) { if (p.general) ENN_FL(true, true, true); else ENN_FL(true, true, false); }
-        else { if (p.general) ENN_FL(true, false, true); else ENN_FL(true, false, false); }
-    } else {
-        if (p.need_asum) { if (p.general) ENN_FL(false, true, true); else ENN_FL(false, true, false); }
-        else { if (p.general) ENN_FL(false, false, true); else ENN_FL(false, false, false); }
+#define ENN_FL_MODE(S, A)                                           \
+    switch (p.mode) {                                               \
+        case kModeNudge: ENN_FL(S, A, kModeNudge); break;           \
+        case kModeGeneral: ENN_FL(S, A, kModeGeneral); break;       \
+        default: ENN_FL(S, A, kModeReluTwo); break;                 \
     }
+    if (p.a_signed) {
+        if (p.need_asum) { ENN_FL_MODE(true, true) } else { ENN_FL_MODE(true, false) }
+    } else {
+        if (p.need_asum) { ENN_FL_MODE(false, true) } else { ENN_FL_MODE(false, false) }
+    }
+#undef ENN_FL_MODE
 #undef ENN_FL
 }
 
-void launch_tc_gemm(const TcGemm &gm, const CUtensorMap &map_a, const TcParams &p, cudaStream_t stream) {
-    if (p.need_asum) {
-        if (p.general) launch_tc_gemm_variant<true, true>(gm, map_a, p, stream);
-        else launch_tc_gemm_variant<true, false>(gm, map_a, p, stream);
-    } else {
-        if (p.general) launch_tc_gemm_variant<false, true>(gm, map_a, p, stream);
-        else launch_tc_gemm_variant<false, false>(gm, map_a, p, stream);
+template <bool ASUM>
+void launch_tc_gemm_mode(const TcGemm &gm, const CUtensorMap &map_a, const TcParams &p, cudaStream_t stream) {
+    switch (p.mode) {
+        case kModeNudge: launch_tc_gemm_variant<ASUM, kModeNudge>(gm, map_a, p, stream); break;
+        case kModeGeneral: launch_tc_gemm_variant<ASUM, kModeGeneral>(gm, map_a, p, stream); break;
+        default: launch_tc_gemm_variant<ASUM, kModeReluTwo>(gm, map_a, p, stream); break;
     }
 }
 
-template <bool ASUM, bool GENERAL>
+void launch_tc_gemm(const TcGemm &gm, const CUtensorMap &map_a, const TcParams &p, cudaStream_t stream) {
+    if (p.need_asum) launch_tc_gemm_mode<true>(gm, map_a, p, stream);
+    else launch_tc_gemm_mode<false>(gm, map_a, p, stream);
+}
+
+template <bool ASUM, int MODE>
 void set_tc_gemm_smem_attr() {
-    cudaFuncSetAttribute(tc_gemm_kernel<ASUM, GENERAL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    cudaFuncSetAttribute(tc_gemm_kernel<ASUM, GENERAL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(tc_gemm_kernel<ASUM, MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(tc_gemm_kernel<ASUM, MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
 }
 
 }  // namespace
@@ -1652,10 +1733,12 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
     op->info.kernel_launches = launches;
     static bool attr_set = false;
     if (!attr_set) {
-        set_tc_gemm_smem_attr<false, false>();
-        set_tc_gemm_smem_attr<false, true>();
-        set_tc_gemm_smem_attr<true, false>();
-        set_tc_gemm_smem_attr<true, true>();
+        set_tc_gemm_smem_attr<false, kModeNudge>();
+        set_tc_gemm_smem_attr<false, kModeGeneral>();
+        set_tc_gemm_smem_attr<false, kModeReluTwo>();
+        set_tc_gemm_smem_attr<true, kModeNudge>();
+        set_tc_gemm_smem_attr<true, kModeGeneral>();
+        set_tc_gemm_smem_attr<true, kModeReluTwo>();
         attr_set = true;
     }
     op->tc = plan;
