@@ -354,6 +354,21 @@ static int32_t conv_like_prepare(enn_b200_context *ctx, const enn_b200_conv_desc
             chan[c * 4 + 2] = e | ((e > 0 ? 31 : 32) << 8);
             chan[c * 4 + 3] = static_cast<int32_t>(folded);
         }
+        // ReLU-type output (lower clamp == output zero point) with right shifts only: merged one-shift form.
+        bool relu = ok && g.out_zp == g.act_min && !getenv("ENN_B200_DW_TMA") && !getenv("ENN_B200_NO_RELU_MODE");
+        for (int32_t c = 0; c < cout && relu; ++c)
+            if ((chan[c * 4 + 2] & 0xff) < 1 || chan[c * 4 + 0] < 0) relu = false;
+        if (relu) {
+            for (int32_t c = 0; c < cout; ++c) {
+                const int32_t m0 = chan[c * 4 + 0], e = chan[c * 4 + 2] & 0xff;
+                const int64_t cc = static_cast<int64_t>(chan[c * 4 + 3]) * m0 + (1ll << 30) + (1ll << (30 + e));
+                chan[c * 4 + 0] = static_cast<int32_t>(static_cast<uint32_t>(static_cast<uint64_t>(cc) & 0xffffffffu));
+                chan[c * 4 + 1] = static_cast<int32_t>(static_cast<uint32_t>(static_cast<uint64_t>(cc) >> 32));
+                chan[c * 4 + 2] = m0;
+                chan[c * 4 + 3] = e - 1;
+            }
+            op->dw_relu = true;
+        }
         if (ok) {
             int32_t *dc = nullptr;
             uint32_t *dwp = nullptr;
@@ -530,7 +545,7 @@ int32_t enn_b200_op_execute(enn_b200_op *op, const void *in, void *out) {
                 if (e != cudaErrorNotSupported) break;
             }
             if (op->dw_chan && op->impl == ENN_B200_IMPL_DEPTHWISE) {
-                e = launch_dw3x3(op->g, op->dw_chan, op->dw_w, in, out, ctx->sm_count, ctx->stream);
+                e = launch_dw3x3(op->g, op->dw_chan, op->dw_relu, op->dw_w, in, out, ctx->sm_count, ctx->stream);
                 break;
             }
             e = launch_depthwise(op->g, op->rq, in, op->w_direct, out, ctx->sm_count, ctx->stream);

@@ -198,7 +198,11 @@ __device__ __forceinline__ void dw_accumulate(int32_t (&acc)[4][4], int32_t (&as
 // w_packed: [C][3] words, bytes (w[ky][0], w[ky][1], w[ky][2], 0) of channel c.
 // The lower clamp is folded into the stage-2 addend (addend -= act_min << e), so the epilogue clamps
 // (v - act_min) to [0, act_max - act_min] with one min-with-relu and adds act_min back per packed word.
-template <int STRIDE, bool W_SIGNED, bool NEED_ASUM>
+// RELU: the operator's lower clamp equals its output zero point and every channel shifts right by e >= 1: the tie
+// correction cannot change a clamped result, so bias and both rounding terms fold into one 64-bit addend per channel,
+// q = acc * M0 + C with C = bias * M0 + 2^30 + 2^(30+e), result = hi32(q) >> (e - 1); DwChan then holds
+// {C low, C high, M0, e - 1}.
+template <int STRIDE, bool W_SIGNED, bool NEED_ASUM, bool RELU>
 __global__ void __launch_bounds__(256, 2)
 dw3x3_kernel(ConvGeom g, const DwChan *__restrict__ chan, const uint32_t *__restrict__ w_packed,
              const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int th, int nyt, int nstrip, int64_t total) {
@@ -219,7 +223,11 @@ dw3x3_kernel(ConvGeom g, const DwChan *__restrict__ chan, const uint32_t *__rest
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
         const DwChan ch = chan[cq * 4 + c];
-        mult[c] = ch.mult; addend[c] = ch.addend; esh[c] = ch.e; bias[c] = ch.bias;
+        if (RELU) {
+            mult[c] = ch.e; addend[c] = ch.mult; esh[c] = ch.bias; bias[c] = ch.addend;    // M0, C low, e - 1, C high
+        } else {
+            mult[c] = ch.mult; addend[c] = ch.addend; esh[c] = ch.e; bias[c] = ch.bias;
+        }
 #pragma unroll
         for (int ky = 0; ky < 3; ++ky) {
             wlo[ky][c] = w_packed[(cq * 4 + c) * 3 + ky];
@@ -251,11 +259,13 @@ dw3x3_kernel(ConvGeom g, const DwChan *__restrict__ chan, const uint32_t *__rest
     for (int j = 0; j < 4; ++j)
         if (ox0 + j < g.ow) omask |= 1u << j;
 
+    const int32_t zero4[4] = {0, 0, 0, 0};
     // One output row: accumulate three input rows, requantise, store 4 pixels x 4 channels.
     auto emit = [&](const DwRow<STRIDE> &r0, const DwRow<STRIDE> &r1, const DwRow<STRIDE> &r2) {
         int32_t acc[4][4];
         int32_t asum[NEED_ASUM ? 4 : 1][4];
-        dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, true>(acc, asum, r0, wlo[0], whi[0], bias);
+        if constexpr (RELU) dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, true>(acc, asum, r0, wlo[0], whi[0], zero4);
+        else dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, true>(acc, asum, r0, wlo[0], whi[0], bias);
         dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r1, wlo[1], whi[1], bias);
         dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r2, wlo[2], whi[2], bias);
 #pragma unroll
@@ -265,9 +275,17 @@ dw3x3_kernel(ConvGeom g, const DwChan *__restrict__ chan, const uint32_t *__rest
             for (int c = 0; c < 4; ++c) {
                 int32_t a = acc[c][j];
                 if (NEED_ASUM) a -= g.w_zp * asum[c][j];
-                const int64_t p = static_cast<int64_t>(a) * mult[c] + (1ll << 30);
-                const int32_t x = static_cast<int32_t>(p >> 31);
-                const int32_t v = (x + addend[c] - static_cast<int32_t>(shr_clamp(static_cast<uint32_t>(x), esh[c] >> 8))) >> (esh[c] & 0xff);
+                int32_t v;
+                if (RELU) {
+                    int64_t cc;
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(cc) : "r"(addend[c]), "r"(bias[c]));
+                    const int64_t q = static_cast<int64_t>(a) * mult[c] + cc;
+                    v = static_cast<int32_t>(q >> 32) >> esh[c];
+                } else {
+                    const int64_t p = static_cast<int64_t>(a) * mult[c] + (1ll << 30);
+                    const int32_t x = static_cast<int32_t>(p >> 31);
+                    v = (x + addend[c] - static_cast<int32_t>(shr_clamp(static_cast<uint32_t>(x), esh[c] >> 8))) >> (esh[c] & 0xff);
+                }
                 y[c] = __vimin_s32_relu(v, hi_clamp);
             }
             if (omask & (1u << j)) {
@@ -671,7 +689,7 @@ cudaError_t dw_tma_launch(enn_b200_op *op, const void *in, void *out) {
 }
 
 
-cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, const void *w_packed, const void *in, void *out,
+cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, bool relu_form, const void *w_packed, const void *in, void *out,
                          int sm_count, cudaStream_t s) {
     const int nstrip = (g.ow + 3) / 4;
     const int cqn = g.cin / 4;
@@ -690,7 +708,9 @@ cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, const void *w_pack
     const uint8_t *i = static_cast<const uint8_t *>(in);
     uint8_t *o = static_cast<uint8_t *>(out);
     const bool need_asum = g.w_zp != 0;
-#define ENN_DW_LAUNCH(ST, WS, AS) launch_pdl(dw3x3_kernel<ST, WS, AS>, dim3(blocks), dim3(threads), 0, s, g, c, w, i, o, th, nyt, nstrip, total)
+#define ENN_DW_LAUNCH(ST, WS, AS)                                                                                                          \
+    (relu_form ? launch_pdl(dw3x3_kernel<ST, WS, AS, true>, dim3(blocks), dim3(threads), 0, s, g, c, w, i, o, th, nyt, nstrip, total)     \
+               : launch_pdl(dw3x3_kernel<ST, WS, AS, false>, dim3(blocks), dim3(threads), 0, s, g, c, w, i, o, th, nyt, nstrip, total))
     if (g.sh == 1) {
         if (g.w_signed) { if (need_asum) ENN_DW_LAUNCH(1, true, true); else ENN_DW_LAUNCH(1, true, false); }
         else            { if (need_asum) ENN_DW_LAUNCH(1, false, true); else ENN_DW_LAUNCH(1, false, false); }

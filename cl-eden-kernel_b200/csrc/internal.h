@@ -67,6 +67,7 @@ struct enn_b200_op {
     std::vector<void *> owned;         // device allocations released with the op
     enn_b200_op_info_t info{};
     void *dw_chan = nullptr;           // depthwise 3x3 fast path: per-channel constants (in `owned`)
+    bool dw_relu = false;              // dw_chan holds the merged ReLU form {C low, C high, M0, e - 1}
     void *dw_w = nullptr;              // depthwise 3x3 fast path: packed 3-tap weight words (in `owned`)
     void *dw_tma = nullptr;            // depthwise TMA-tile plan (depthwise.cu), owned
     void *tc = nullptr;                // tensor-core plan (gemm_tc.cu), owned
@@ -84,7 +85,7 @@ cudaError_t launch_deconv_direct(const ConvGeom &g, const Requant &rq, const voi
 cudaError_t launch_depthwise(const ConvGeom &g, const Requant &rq, const void *in, const void *w, void *out,
                              int sm_count, cudaStream_t s);
 bool dw3x3_eligible(const ConvGeom &g);
-cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, const void *w_packed, const void *in, void *out,
+cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, bool relu_form, const void *w_packed, const void *in, void *out,
                          int sm_count, cudaStream_t s);
 bool dw_tma_plan(enn_b200_op *op);
 cudaError_t dw_tma_launch(enn_b200_op *op, const void *in, void *out);
