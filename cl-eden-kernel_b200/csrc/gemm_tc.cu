@@ -84,6 +84,7 @@ struct TcParams {
     int32_t taps, cchunks;
     int32_t conv_ht, conv_wt, conv_ty, conv_tx;
     int32_t span;           // bytes of K per k-block = swizzle span of both operand tiles: 128, 64 or 32
+    int32_t k_pad;          // row pitch of the packed B matrix (K rounded up to 128)
     int16_t tap_dx[64], tap_dy[64];
     int32_t *err;           // host-mapped error word
     long long *dbg;         // optional per-CTA cycle counters [grid][8] (null in normal use)
@@ -397,7 +398,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles.
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    const uint32_t span = p.taps > 0 ? static_cast<uint32_t>(p.span) : kBK;
+    const uint32_t span = static_cast<uint32_t>(p.span);
     const uint32_t a_bytes = kBM * span;
     const uint32_t b_bytes = static_cast<uint32_t>(TWO ? p.bn_rows >> 1 : p.bn_rows) * span;
     const uint32_t kb_bytes = a_bytes + b_bytes;                      // one k-block: A tile then B tile
@@ -491,7 +492,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         int tap = 0, cc = 0;
                         const int row_a = tm * kBM;
                         const int row_b = tn * p.bn_rows + (TWO ? static_cast<int>(rank) * (p.bn_rows >> 1) : 0);
-                        const int kstep_b = p.taps > 0 ? static_cast<int>(span) : kBK;
+                        const int kstep_b = static_cast<int>(span);
                         for (int kb0 = 0; kb0 < p.k_blocks; kb0 += p.kpack) {
                             const int nkb = min(p.kpack, p.k_blocks - kb0);
                             const uint32_t ebar = empty0 + 8 * stage;
@@ -508,8 +509,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 if (rank == 0) mbar_expect_tx(bar, kb_tx * nkb);
                                 const uint32_t bar0 = mapa_rank(bar, 0);
                                 for (int q = 0; q < nkb; ++q, sa += kb_bytes) {
-                                    if (DO_A) tma_load_2d_pair(sa, &map_a, bar0, (kb0 + q) * kBK, row_a);
-                                    if (DO_B) tma_load_2d_pair(sa + a_bytes, &map_b, bar0, (kb0 + q) * kBK, row_b);
+                                    if (DO_A) tma_load_2d_pair(sa, &map_a, bar0, (kb0 + q) * kstep_b, row_a);
+                                    if (DO_B) tma_load_2d_pair(sa + a_bytes, &map_b, bar0, (kb0 + q) * kstep_b, row_b);
                                 }
                             } else {
                                 mbar_expect_tx(bar, kb_tx * nkb);
@@ -519,7 +520,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                             tma_load_4d(sa, &map_a, bar, cc * static_cast<int>(span), tx * p.conv_wt + p.tap_dx[tap], ty * p.conv_ht + p.tap_dy[tap], img);
                                             if (++cc == p.cchunks) { cc = 0; ++tap; }
                                         } else {
-                                            tma_load_2d(sa, &map_a, bar, (kb0 + q) * kBK, row_a);
+                                            tma_load_2d(sa, &map_a, bar, (kb0 + q) * kstep_b, row_a);
                                         }
                                     }
                                     if (DO_B) tma_load_2d(sa + a_bytes, &map_b, bar, (kb0 + q) * kstep_b, row_b);
@@ -562,7 +563,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int ks = static_cast<int>(span >> 5);
             int ks_last = ks;
             if (p.taps == 0) {
-                const int real = (p.K - (p.k_blocks - 1) * kBK + 31) >> 5;
+                const int real = (p.K - (p.k_blocks - 1) * static_cast<int>(span) + 31) >> 5;
                 ks_last = real <= 1 ? 1 : (real == 2 ? 2 : 4);
             }
             uint32_t lo_stage = lo0;
@@ -1215,9 +1216,14 @@ struct QuantHost {   // host copies of what setup_quant uploaded
 // weight(n, k) returns the raw weight byte of output column n at reduction index k (k < K).
 template <typename WeightFn>
 int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh, int32_t M, int32_t N, int32_t K, WeightFn weight,
-                   TcGemm *gm, uint32_t span = kBK) {
+                   TcGemm *gm, uint32_t implicit_span = 0) {
     TcParams &p = gm->prm;
     p.M = M; p.N = N; p.K = K;
+    // K bytes per k-block.  Implicit convolutions bring theirs (the channel chunk); plain GEMMs with a short K use 32-
+    // or 64-byte rows, so that the TMA does not spend its time zero-filling 128-byte rows that are mostly padding.
+    uint32_t span = implicit_span ? implicit_span : (K <= 32 ? 32u : (K <= 64 ? 64u : static_cast<uint32_t>(kBK)));
+    if (getenv("ENN_B200_NO_NARROW_SPAN") && !implicit_span) span = kBK;
+    p.span = static_cast<int32_t>(span);
     const int32_t zw_eff = g.w_signed ? g.w_zp : g.w_zp - 128;   // weights as signed bytes: int8 stays, u8 becomes w - 128
     p.zw_eff = zw_eff;
     p.need_asum = zw_eff != 0;
@@ -1268,7 +1274,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     p.tiles_n = tiles_n;
     p.bn_data = bn_data;
     p.bn_rows = bn_data + extra;
-    p.k_blocks = (K + kBK - 1) / kBK;
+    p.k_blocks = (K + static_cast<int32_t>(span) - 1) / static_cast<int32_t>(span);
     p.group = two ? 1 : kMaxBN / p.bn_rows;
     if (p.group > p.tiles_m) p.group = p.tiles_m;
     // keep at least ~2 work units per SM before widening the groups
@@ -1280,7 +1286,8 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     p.raster = !big_operands ? p.tiles_mg : (two ? 8 : 16);
     if (const char *ev = getenv("ENN_B200_TC_RASTER")) p.raster = atoi(ev) > 0 ? atoi(ev) : p.raster;   // tuning override
     if (p.raster > p.tiles_mg) p.raster = p.tiles_mg;
-    const int32_t k_pad = p.k_blocks * kBK;
+    const int32_t k_pad = ((K + kBK - 1) / kBK) * kBK;
+    p.k_pad = k_pad;
     p.idesc = (2u << 4) | (static_cast<uint32_t>(g.a_signed ? 1 : 0) << 7) | (1u << 10) |
               (static_cast<uint32_t>(p.bn_rows >> 3) << 17) | (static_cast<uint32_t>((p.two ? 2 * kBM : kBM) >> 4) << 24);
 
@@ -1375,7 +1382,6 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         ctx->last_error = "cuTensorMapEncodeTiled failed for the weight tensor";
         return ENN_B200_CUDA_FAILURE;
     }
-    if (span != kBK) p.k_blocks = K / static_cast<int32_t>(span);      // implicit convolution: one (tap, channel chunk) per k-block
     // Several small k-blocks share a pipeline stage so that a barrier round trip covers ~32 KB of operands.
     const size_t kb_bytes = (static_cast<size_t>(kBM) + (p.two ? p.bn_rows / 2 : p.bn_rows)) * span;
     p.kpack = static_cast<int32_t>((32 * 1024) / kb_bytes);
@@ -1436,7 +1442,7 @@ void launch_first_layer(enn_b200_context *ctx, const TcGemm &gm, const void *in,
     const Im2colGeom &ig = gm.ig;
     Conv3x3c3Params g{};
     g.n = ig.n; g.h = ig.h; g.w = ig.w; g.oh = ig.oh; g.ow = ig.ow; g.sy = ig.sy; g.sx = ig.sx; g.y0 = ig.y0; g.x0 = ig.x0;
-    g.M = p.M; g.N = p.N; g.k_pad = p.k_blocks * kBK;
+    g.M = p.M; g.N = p.N; g.k_pad = p.k_pad;
     g.zw_eff = p.zw_eff; g.act_min = p.act_min; g.act_max = p.act_max; g.out_zp = p.out_zp;
     g.fill = ig.fill;
     g.in_bytes = static_cast<int64_t>(ig.n) * ig.h * ig.w * 3;
@@ -1723,7 +1729,7 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
             gm.ig.ktab = static_cast<const int2 *>(gm.ktab_dev);
         }
         if (gm.gather) {
-            if (!encode_2d(ctx, &gm.map_a, plan->scratch, gm.ig.Kp, gm.prm.M, gm.ig.Kp, kBK, kBM)) {
+            if (!encode_2d(ctx, &gm.map_a, plan->scratch, gm.ig.Kp, gm.prm.M, gm.ig.Kp, static_cast<uint32_t>(gm.prm.span), kBM)) {
                 ctx->last_error = "cuTensorMapEncodeTiled failed for the gathered activation matrix";
                 return bail(ENN_B200_CUDA_FAILURE);
             }
@@ -1798,7 +1804,7 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
             }
             if (gm.use_gemv) {
                 // few rows: HBM-bound on the weights, CUDA-core GEMV over the same packed weights and constants
-                const int k_pad = p.k_blocks * kBK;
+                const int k_pad = p.k_pad;
                 if (p.a_signed) launch_gemv<true>(p.M, in, gm.w_dev, p.cols, out, p, k_pad, ctx->stream);
                 else launch_gemv<false>(p.M, in, gm.w_dev, p.cols, out, p, k_pad, ctx->stream);
                 cudaError_t ge = cudaGetLastError();
@@ -1815,7 +1821,7 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
                 if (hit < 0) {
                     hit = gm.map_cache_next;
                     gm.map_cache_next = (gm.map_cache_next + 1) % TcGemm::kMapCache;
-                    if (!encode_2d(ctx, &gm.map_cache[hit], in, p.K, p.M, p.K, kBK, kBM)) {
+                    if (!encode_2d(ctx, &gm.map_cache[hit], in, p.K, p.M, p.K, static_cast<uint32_t>(p.span), kBM)) {
                         ctx->last_error = "cuTensorMapEncodeTiled failed for the activation tensor";
                         return ENN_B200_CUDA_FAILURE;
                     }
@@ -1908,7 +1914,7 @@ int32_t tc_execute_static(enn_b200_op *op, const void *in, void *out) {
         TcParams p = gm.prm;     // private copy: the handle's own launch state is left untouched
         if (p.M == 0) continue;
         if (gm.map_a_static_ptr != scratch) {
-            if (!encode_2d(ctx, &gm.map_a_static, scratch, gm.ig.Kp, p.M, gm.ig.Kp, kBK, kBM)) {
+            if (!encode_2d(ctx, &gm.map_a_static, scratch, gm.ig.Kp, p.M, gm.ig.Kp, static_cast<uint32_t>(p.span), kBM)) {
                 ctx->last_error = "cuTensorMapEncodeTiled failed for the static scratch";
                 return ENN_B200_CUDA_FAILURE;
             }
