@@ -57,6 +57,10 @@ CONV_CASES = {
     "implicit_c96": dict(n=1, h=9, w=9, cin=96, cout=40, k=3),
     # first-layer kernel (3x3 taps over 3 channels, >= 4096 output pixels): stride 2 per-channel, stride 1 with u8
     # per-tensor weights (row-sum correction), signed activations, VALID padding, odd widths (unaligned row starts)
+    # ReLU-type outputs with multipliers from 0.03 to 3 (right shifts, e == 0, left shifts) in 1x1, implicit 3x3 and gathered form
+    "relu_wide_mult_1x1": dict(n=2, h=14, w=14, cin=32, cout=48, k=1, per_channel=True, out_scale=0.0006, out_zp=0),
+    "relu_wide_mult_3x3": dict(n=1, h=12, w=13, cin=32, cout=32, k=3, per_channel=True, out_scale=0.0006, act=cases.enn.ACT_RELU, out_zp=0),
+    "relu_wide_mult_gather": dict(n=2, h=15, w=14, cin=8, cout=16, k=3, stride=2, per_channel=True, out_scale=0.0004, out_zp=0),
     "first_layer_s2": dict(n=4, h=66, w=71, cin=3, cout=32, k=3, stride=2, per_channel=True, out_scale=0.1),
     "first_layer_s1_u8w": dict(n=2, h=47, w=53, cin=3, cout=16, k=3, w_zp=121, out_scale=0.05),
     "first_layer_signed": dict(n=1, h=70, w=69, cin=3, cout=48, k=3, act_dtype=cases.enn.S8, in_zp=-7, out_zp=3, per_channel=True, out_scale=0.2),
@@ -110,6 +114,8 @@ DW_CASES = {
     "signed": dict(n=1, h=9, w=9, c=8, act_dtype=cases.enn.S8, in_zp=-5, out_zp=-128),
     "tiny": dict(n=1, h=1, w=1, c=4),
     "per_tensor_s2": dict(n=2, h=15, w=13, c=12, stride=2, per_channel=False, out_scale=0.08, out_zp=3),
+    "relu_small_out_scale": dict(n=1, h=20, w=21, c=32, out_scale=0.004),           # multipliers up to 0.5: shifts down to e = 1
+    "relu_s2_zp5": dict(n=2, h=21, w=20, c=48, stride=2, out_zp=5, out_scale=0.02),
     "s2_even": dict(n=1, h=16, w=16, c=8, stride=2),
     "ragged_rows": dict(n=3, h=10, w=6, c=4),
     "single_row": dict(n=1, h=1, w=9, c=8),
@@ -190,6 +196,11 @@ FC_CASES = {
     "gemv_m1_k4096": dict(m=1, k=4096, n=1000),
     "gemv_m3_per_tensor": dict(m=3, k=1280, n=77, per_channel=False),
     "gemv_m8_mixed_shift": dict(m=8, k=64, n=80, out_scale=0.0015),
+    # ReLU-type outputs (lower clamp == output zero point: merged 64-bit epilogue) across right shifts, e == 0 and left shifts
+    "relu_mixed_shift": dict(m=150, k=64, n=80, out_scale=0.0015, act=cases.enn.ACT_RELU, out_zp=0),
+    "relu6_mixed_shift_zp7": dict(m=260, k=160, n=144, out_scale=0.003, act=cases.enn.ACT_RELU6, out_zp=7),
+    "relu_per_tensor_mixed": dict(m=150, k=32, n=48, per_channel=False, w_scale=0.05, out_scale=0.0012, act=cases.enn.ACT_RELU, out_zp=0),
+    "relu_small_mult": dict(m=300, k=96, n=96, act=cases.enn.ACT_RELU6, out_zp=0),
 }
 
 
