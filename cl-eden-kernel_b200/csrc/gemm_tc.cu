@@ -128,9 +128,18 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // test_wait first (the common case: already complete); what is left waits with try_wait, which parks the thread in
 // hardware between looks instead of spinning through issue slots that the epilogue warps of the same scheduler need.
 __device__ __forceinline__ bool mbar_wait_fast(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *err, int code) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    for (uint32_t i = 0; i < (kSpinLimit >> 4); ++i) {
+        // suspend-time hint (ns): stay parked until the phase completes instead of coming back every few hundred cycles
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity), "r"(10000u)
+            : "memory");
+        if (ok) return true;
+        if ((i & 63u) == 63u && *abort_flag) return false;
     }
     *abort_flag = 1;
     if (err) *reinterpret_cast<volatile int32_t *>(err) = code;
