@@ -463,6 +463,21 @@ int32_t enn_b200_add_prepare(enn_b200_context *ctx, const enn_b200_add_desc *d, 
         p.act_min = p.is_signed ? -128 : 0;
         p.act_max = p.is_signed ? 127 : 255;
     }
+    {
+        std::vector<int32_t> lut(512);
+        for (int32_t b = 0; b < 256; ++b) {
+            const int32_t v = p.is_signed ? static_cast<int32_t>(static_cast<int8_t>(b)) : b;
+            lut[b] = enn_rdivpot(enn_srdhm((p.in0_off + v) * (1 << 20), p.m0), -p.s0);
+            lut[256 + b] = enn_rdivpot(enn_srdhm((p.in1_off + v) * (1 << 20), p.m1), -p.s1);
+        }
+        int32_t *dl = nullptr;
+        const int32_t st = upload_vec(op, lut, &dl);
+        if (st != ENN_B200_SUCCESS) {
+            enn_b200_op_release(op);
+            return st;
+        }
+        p.lut = dl;
+    }
     op->info.impl = op->impl;
     op->info.in_bytes = 2 * d->count; op->info.out_bytes = d->count;
     op->info.algorithmic_bytes = 3 * d->count;

@@ -128,7 +128,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // test_wait first (the common case: already complete); what is left waits with try_wait, which parks the thread in
 // hardware between looks instead of spinning through issue slots that the epilogue warps of the same scheduler need.
 __device__ __forceinline__ bool mbar_wait_fast(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *err, int code) {
-    for (uint32_t i = 0; i < (kSpinLimit >> 4); ++i) {
+    for (uint32_t i = 0; i < (kSpinLimit >> 7); ++i) {       // 2^17 looks of up to 10 us: gives up after about a second
         // suspend-time hint (ns): stay parked until the phase completes instead of coming back every few hundred cycles
         uint32_t ok;
         asm volatile(

@@ -45,6 +45,9 @@ struct AddParams {
     int32_t m0, s0, m1, s1, mo, so;   // multipliers and (non-positive) shifts
     int32_t act_min, act_max;
     int32_t is_signed;
+    // Stage-1 values of both inputs by input byte (device array of 2 x 256 words: in0 table, in1 table), so that the
+    // vector kernel spends its instructions on the last stage only.  Built at prepare time with the same functions.
+    const int32_t *lut;
 };
 
 struct PoolGeom {

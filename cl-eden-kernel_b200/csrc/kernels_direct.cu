@@ -117,9 +117,13 @@ __global__ void add_kernel(AddParams p, int64_t count, const uint8_t *__restrict
     }
 }
 
-// 16 bytes per thread per step; used when count and pointers allow.
+// 16 bytes per thread per step; used when count and pointers allow.  The first two stages depend on one input byte
+// each and come from the operator's tables (staged in shared memory); the last stage is computed.
 __global__ void add_kernel_vec(AddParams p, int64_t count16, const uint4 *__restrict__ a, const uint4 *__restrict__ b,
                                uint4 *__restrict__ out) {
+    __shared__ int32_t s_lut[512];
+    for (int i = threadIdx.x; i < 512; i += blockDim.x) s_lut[i] = p.lut[i];      // operator constants, not a tensor
+    __syncthreads();
     pdl_wait();
     pdl_trigger();
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -134,10 +138,7 @@ __global__ void add_kernel_vec(AddParams p, int64_t count16, const uint4 *__rest
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const uint32_t ba = (wa[j] >> (8 * k)) & 0xff, bb = (wb[j] >> (8 * k)) & 0xff;
-                const int32_t ia = p.is_signed ? static_cast<int32_t>(static_cast<int8_t>(ba)) : static_cast<int32_t>(ba);
-                const int32_t ib = p.is_signed ? static_cast<int32_t>(static_cast<int8_t>(bb)) : static_cast<int32_t>(bb);
-                const int32_t x0 = enn_rdivpot(enn_srdhm((p.in0_off + ia) * (1 << 20), p.m0), -p.s0);
-                const int32_t x1 = enn_rdivpot(enn_srdhm((p.in1_off + ib) * (1 << 20), p.m1), -p.s1);
+                const int32_t x0 = s_lut[ba], x1 = s_lut[256 + bb];
                 int32_t o = enn_rdivpot(enn_srdhm(x0 + x1, p.mo), -p.so) + p.out_off;
                 o = max(p.act_min, o);
                 o = min(p.act_max, o);
