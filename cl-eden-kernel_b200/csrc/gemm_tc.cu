@@ -1596,7 +1596,33 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         plan->gemms.resize(1);
         TcGemm &gm = plan->gemms[0];
         auto weight = [&](int32_t n, int32_t k) { return w[static_cast<size_t>(k) * N + n]; };
-        if (in_place) {
+        // Pixel packing: with K of 16, 32 or 64 bytes and few output channels, f = 128 / K consecutive pixels are one
+        // 128-byte row of the activation tensor.  The GEMM [M/f][fK] x blockdiag(W, ..., W) -> [M/f][fN] is the same
+        // memory as [M][K] x W -> [M][N] when the off-diagonal weights equal the weight zero point (their terms vanish
+        // in the zero-point algebra), and the TMA then fetches one full line per row instead of f short ones, which is
+        // what bounds these layers.  The extra MMA work (f times) is free: the tensor pipe idles in them.
+        int32_t pack = 1;
+        if (in_place && M64 >= 4096 && (K == 16 || K == 32 || K == 64) && !getenv("ENN_B200_NO_PACK")) {
+            const int32_t f = 128 / K;
+            const int32_t zw_eff = g.w_signed ? g.w_zp : g.w_zp - 128;
+            if (M64 % f == 0 && f * N <= kMaxBN - (zw_eff != 0 ? 16 : 0)) pack = f;
+        }
+        if (in_place && pack > 1) {
+            QuantHost qp;
+            for (int32_t r = 0; r < pack; ++r) {
+                qp.mult.insert(qp.mult.end(), qh.mult.begin(), qh.mult.end());
+                qp.shift.insert(qp.shift.end(), qh.shift.begin(), qh.shift.end());
+                qp.bias.insert(qp.bias.end(), qh.bias.begin(), qh.bias.end());
+            }
+            const uint8_t zero_raw = static_cast<uint8_t>(g.w_zp);
+            auto packed_weight = [&](int32_t n, int32_t k) -> uint8_t {
+                return n / N == k / K ? w[static_cast<size_t>(k % K) * N + (n % N)] : zero_raw;
+            };
+            st = build_gemm(ctx, g, qp, static_cast<int32_t>(M64 / pack), pack * N, pack * K, packed_weight, &gm);
+            if (st != ENN_B200_SUCCESS) return bail(st);
+            gm.prm.qh = 1; gm.prm.qw = static_cast<int32_t>(M64 / pack);
+            gm.prm.out_base = 0; gm.prm.out_sn = 0; gm.prm.out_sy = 0; gm.prm.out_sx = pack * N;
+        } else if (in_place) {
             st = build_gemm(ctx, g, qh, static_cast<int32_t>(M64), N, K, weight, &gm);
             if (st != ENN_B200_SUCCESS) return bail(st);
             gm.use_gemv = M64 <= kGemvMaxM && (K & 15) == 0 && static_cast<size_t>(M64) * K <= 48 * 1024 && !getenv("ENN_B200_NO_GEMV");

@@ -61,6 +61,7 @@ CONV_CASES = {
     "relu_wide_mult_1x1": dict(n=2, h=14, w=14, cin=32, cout=48, k=1, per_channel=True, out_scale=0.0006, out_zp=0),
     "relu_wide_mult_3x3": dict(n=1, h=12, w=13, cin=32, cout=32, k=3, per_channel=True, out_scale=0.0006, act=cases.enn.ACT_RELU, out_zp=0),
     "relu_wide_mult_gather": dict(n=2, h=15, w=14, cin=8, cout=16, k=3, stride=2, per_channel=True, out_scale=0.0004, out_zp=0),
+    "pack_1x1_c32_to_16": dict(n=2, h=48, w=50, cin=32, cout=16, k=1, per_channel=True, out_scale=0.3, act=cases.enn.ACT_NONE),
     "first_layer_s2": dict(n=4, h=66, w=71, cin=3, cout=32, k=3, stride=2, per_channel=True, out_scale=0.1),
     "first_layer_s1_u8w": dict(n=2, h=47, w=53, cin=3, cout=16, k=3, w_zp=121, out_scale=0.05),
     "first_layer_signed": dict(n=1, h=70, w=69, cin=3, cout=48, k=3, act_dtype=cases.enn.S8, in_zp=-7, out_zp=3, per_channel=True, out_scale=0.2),
@@ -201,6 +202,11 @@ FC_CASES = {
     "relu6_mixed_shift_zp7": dict(m=260, k=160, n=144, out_scale=0.003, act=cases.enn.ACT_RELU6, out_zp=7),
     "relu_per_tensor_mixed": dict(m=150, k=32, n=48, per_channel=False, w_scale=0.05, out_scale=0.0012, act=cases.enn.ACT_RELU, out_zp=0),
     "relu_small_mult": dict(m=300, k=96, n=96, act=cases.enn.ACT_RELU6, out_zp=0),
+    # pixel packing (K of 16 / 32 / 64 bytes, few output channels, >= 4096 rows): block-diagonal weights, f rows per 128-byte line
+    "pack_k32_n16": dict(m=4104, k=32, n=16),
+    "pack_k16_n24_per_tensor": dict(m=4104, k=16, n=24, per_channel=False, w_zp=119),
+    "pack_k64_n96_relu": dict(m=4098, k=64, n=96, act=cases.enn.ACT_RELU, out_zp=0, out_scale=0.004),
+    "pack_k32_n48_mixed_shift": dict(m=4100, k=32, n=48, out_scale=0.0012),
 }
 
 
