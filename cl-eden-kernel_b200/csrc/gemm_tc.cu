@@ -1591,8 +1591,8 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         const int64_t M64 = static_cast<int64_t>(g.n) * g.oh * g.ow;
         if (M64 <= 0 || M64 > INT32_MAX) return bail(ENN_B200_INVALID_PARAMS);
         const int32_t K = g.kh * g.kw * cin;
-        const bool in_place = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.pt == 0 && g.pl == 0 && g.oh == g.h &&
-                              g.ow == g.w && (cin & 15) == 0;
+        const bool pointwise = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.pt == 0 && g.pl == 0 && g.oh == g.h && g.ow == g.w;
+        bool in_place = pointwise && (cin & 15) == 0;
         plan->gemms.resize(1);
         TcGemm &gm = plan->gemms[0];
         auto weight = [&](int32_t n, int32_t k) { return w[static_cast<size_t>(k) * N + n]; };
@@ -1601,11 +1601,16 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         // memory as [M][K] x W -> [M][N] when the off-diagonal weights equal the weight zero point (their terms vanish
         // in the zero-point algebra), and the TMA then fetches one full line per row instead of f short ones, which is
         // what bounds these layers.  The extra MMA work (f times) is free: the tensor pipe idles in them.
+        // A channel count that is not a multiple of 16 (24) cannot be read in place at all (TMA row pitch); packed rows of
+        // f * K bytes can, which removes the gather pass; several N tiles are accepted in that case.
         int32_t pack = 1;
-        if (in_place && M64 >= 4096 && (K == 16 || K == 32 || K == 64) && !getenv("ENN_B200_NO_PACK")) {
-            const int32_t f = 128 / K;
+        if (pointwise && M64 >= 4096 && K <= 64 && !getenv("ENN_B200_NO_PACK")) {
             const int32_t zw_eff = g.w_signed ? g.w_zp : g.w_zp - 128;
-            if (M64 % f == 0 && f * N <= kMaxBN - (zw_eff != 0 ? 16 : 0)) pack = f;
+            for (int32_t f = 8; f >= 2 && pack == 1; f >>= 1) {
+                if (f * K > 128 || (f * K) % 16 != 0 || M64 % f != 0) continue;
+                if (f * N <= kMaxBN - (zw_eff != 0 ? 16 : 0) || (K & 15) != 0) pack = f;
+            }
+            if (pack > 1) in_place = true;
         }
         if (in_place && pack > 1) {
             QuantHost qp;

@@ -61,6 +61,8 @@ CONV_CASES = {
     "relu_wide_mult_1x1": dict(n=2, h=14, w=14, cin=32, cout=48, k=1, per_channel=True, out_scale=0.0006, out_zp=0),
     "relu_wide_mult_3x3": dict(n=1, h=12, w=13, cin=32, cout=32, k=3, per_channel=True, out_scale=0.0006, act=cases.enn.ACT_RELU, out_zp=0),
     "relu_wide_mult_gather": dict(n=2, h=15, w=14, cin=8, cout=16, k=3, stride=2, per_channel=True, out_scale=0.0004, out_zp=0),
+    "pack_1x1_c24_to_144_relu": dict(n=2, h=48, w=50, cin=24, cout=144, k=1, per_channel=True, out_scale=0.002, out_zp=0),
+    "pack_1x1_c24_to_40_u8w": dict(n=1, h=64, w=66, cin=24, cout=40, k=1, w_zp=130, out_scale=0.03),
     "pack_1x1_c32_to_16": dict(n=2, h=48, w=50, cin=32, cout=16, k=1, per_channel=True, out_scale=0.3, act=cases.enn.ACT_NONE),
     "first_layer_s2": dict(n=4, h=66, w=71, cin=3, cout=32, k=3, stride=2, per_channel=True, out_scale=0.1),
     "first_layer_s1_u8w": dict(n=2, h=47, w=53, cin=3, cout=16, k=3, w_zp=121, out_scale=0.05),
