@@ -323,8 +323,8 @@ __device__ __forceinline__ void tile_coords(const TcParams &p, int tile, int &tg
 //                e >= 1); result = (q >> (31 - ls)) >> e.  Covers e == 0 and left shifts, which otherwise need the
 //                general code.
 //   kModeReluHi  the same with one shift, hi32(q) >> (e - 1), for operators whose columns all have e >= 1 and ls == 0:
-//                implemented, but its shorter chains make the compiler keep more constants in flight than the epilogue's
-//                72 registers hold; it spilled and measured slower, so the planner does not select it.
+//                implemented, but it spills a little under the epilogue's 72-register cap and measured within noise of
+//                the two-shift form, so the planner selects it only with ENN_B200_RELU_HI=1.
 // ColParam words: {mult, addend, esh, bias} for the first two modes, {C low, C high, mult, shifts} for the ReLU modes
 // (shifts = e - 1 for kModeReluHi, (31 - ls) | e << 8 for kModeReluTwo).
 constexpr int kModeNudge = 0, kModeGeneral = 1, kModeReluHi = 2, kModeReluTwo = 3;
@@ -755,7 +755,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             }
                         }
                         if (row_ok && c0 < n_cols) {
-                            if (st_fast) {
+                            if (p.dbg_mode & 4) {
+                                // development switch: no stores (isolates the store path; only one lane keeps the values alive)
+                                if ((w[0] ^ w[1] ^ w[2] ^ w[3]) == 0x12345678u && lane == 33) orow[0] = 1;
+                            } else if (st_fast) {
                                 *reinterpret_cast<uint4 *>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
                             } else {
                                 const int left = n_cols - c0;
@@ -1336,8 +1339,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         // stage-1 value plus the rounding term must fit 32 bits
         if ((bound_v[n] << ls) + (e >= 1 ? (1ll << (e - 1)) : 0) + 1 >= (1ll << 31)) relu_two = false;
     }
-    (void)relu_hi;      // the one-shift form needs more registers than the 72 the epilogue has and spills: measured slower
-    p.mode = relu_two ? kModeReluTwo : kModeNudge;
+    p.mode = relu_hi && getenv("ENN_B200_RELU_HI") ? kModeReluHi : (relu_two ? kModeReluTwo : kModeNudge);
     for (int32_t n = 0; n < N; ++n) {
         const int32_t tn = n / bn_data, r = n % bn_data;
         const int64_t folded = folded_v[n];
@@ -1466,6 +1468,7 @@ void launch_first_layer(enn_b200_context *ctx, const TcGemm &gm, const void *in,
     switch (p.mode) {                                               \
         case kModeNudge: ENN_FL(S, A, kModeNudge); break;           \
         case kModeGeneral: ENN_FL(S, A, kModeGeneral); break;       \
+        case kModeReluHi: ENN_FL(S, A, kModeReluHi); break;         \
         default: ENN_FL(S, A, kModeReluTwo); break;                 \
     }
     if (p.a_signed) {
@@ -1482,6 +1485,7 @@ void launch_tc_gemm_mode(const TcGemm &gm, const CUtensorMap &map_a, const TcPar
     switch (p.mode) {
         case kModeNudge: launch_tc_gemm_variant<ASUM, kModeNudge>(gm, map_a, p, stream); break;
         case kModeGeneral: launch_tc_gemm_variant<ASUM, kModeGeneral>(gm, map_a, p, stream); break;
+        case kModeReluHi: launch_tc_gemm_variant<ASUM, kModeReluHi>(gm, map_a, p, stream); break;
         default: launch_tc_gemm_variant<ASUM, kModeReluTwo>(gm, map_a, p, stream); break;
     }
 }
@@ -1781,9 +1785,11 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
     if (!attr_set) {
         set_tc_gemm_smem_attr<false, kModeNudge>();
         set_tc_gemm_smem_attr<false, kModeGeneral>();
+        set_tc_gemm_smem_attr<false, kModeReluHi>();
         set_tc_gemm_smem_attr<false, kModeReluTwo>();
         set_tc_gemm_smem_attr<true, kModeNudge>();
         set_tc_gemm_smem_attr<true, kModeGeneral>();
+        set_tc_gemm_smem_attr<true, kModeReluHi>();
         set_tc_gemm_smem_attr<true, kModeReluTwo>();
         attr_set = true;
     }
