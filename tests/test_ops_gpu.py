@@ -84,6 +84,41 @@ def test_conv2d_parity(enn, orc, ctx, name):
         op.release()
 
 
+def _sweep_params(seed):
+    """One pseudo-random convolution / activation / quantisation combination (fixed by `seed`)."""
+    rng = np.random.default_rng(1000 + seed)
+    k = int(rng.choice([1, 1, 1, 3]))
+    cin = int(rng.choice([3, 8, 16, 24, 32, 48, 64, 96]))
+    cout = int(rng.choice([16, 24, 32, 48, 96, 144]))
+    stride = int(rng.choice([1, 1, 2])) if k == 3 else 1
+    per_channel = bool(rng.integers(0, 2))
+    act = int(rng.choice([cases.enn.ACT_NONE, cases.enn.ACT_RELU, cases.enn.ACT_RELU6]))
+    out_zp = int(rng.choice([0, 0, 5, 128])) if act != cases.enn.ACT_NONE else int(rng.integers(0, 256))
+    h, w = int(rng.integers(33, 50)), int(rng.integers(33, 50))
+    n = 4
+    while (n * h * w) % 8:          # keep the row count divisible by every packing factor
+        w += 1
+    out_scale = float(np.exp(rng.uniform(np.log(3e-4), np.log(0.3))))
+    kw = dict(n=n, h=h, w=w, cin=cin, cout=cout, k=k, stride=stride, per_channel=per_channel, act=act, out_zp=out_zp, out_scale=out_scale)
+    if not per_channel:
+        kw["w_zp"] = int(rng.integers(100, 156))
+    return kw
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_conv2d_parity_sweep(enn, orc, ctx, seed):
+    """Pseudo-random geometry x activation x quantisation combinations (>= 4096 output pixels, so that the packed,
+    first-layer and ReLU-merged paths are all eligible) against the oracle, default implementation."""
+    kw = _sweep_params(seed)
+    d, x, w, b, sc = cases.conv_case(seed=seed, **kw)
+    y_ref = orc.conv2d(d, x, w, b, sc)
+    op = enn.conv2d(ctx, d, w, b, sc)
+    try:
+        _check(op, y_ref, x)
+    finally:
+        op.release()
+
+
 def test_kat_perchannel_conv_gpu(enn, ctx):
     """Reference known-answer test gpu_userdriver_test.cc:474-575 through NCHW upload + layout conversion."""
     k = json.load(open(os.path.join(HERE, "golden", "kat_perchannel_conv.json")))
@@ -138,6 +173,47 @@ def test_depthwise_parity(enn, orc, ctx, name):
         for impl in (enn.IMPL_DEPTHWISE, enn.IMPL_DIRECT):     # 3x3 fast path (when eligible) and general kernel
             op.set_impl(impl)
             _check(op, y_ref, x)
+    finally:
+        op.release()
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_depthwise_parity_sweep(enn, orc, ctx, seed):
+    """Pseudo-random 3x3 depthwise layers (channels, stride, activation, zero points, output scale over three decades,
+    so that right shifts down to 1 and both requantisation forms occur) against the oracle."""
+    rng = np.random.default_rng(2000 + seed)
+    act = int(rng.choice([cases.enn.ACT_NONE, cases.enn.ACT_RELU, cases.enn.ACT_RELU6]))
+    kw = dict(n=2, h=int(rng.integers(9, 40)), w=int(rng.integers(9, 40)), c=int(rng.choice([4, 8, 12, 32, 48, 96, 144])),
+              stride=int(rng.choice([1, 2])), per_channel=bool(rng.integers(0, 2)), act=act,
+              out_zp=int(rng.choice([0, 0, 3, 128])) if act != cases.enn.ACT_NONE else int(rng.integers(0, 256)),
+              out_scale=float(np.exp(rng.uniform(np.log(2e-3), np.log(0.2)))), in_zp=int(rng.choice([0, 17, 128])))
+    if not kw["per_channel"]:
+        kw["w_zp"] = int(rng.integers(100, 156))
+    d, x, w, b, sc = cases.depthwise_case(seed=seed, **kw)
+    y_ref = orc.depthwise(d, x, w, b, sc)
+    op = enn.depthwise(ctx, d, w, b, sc)
+    try:
+        _check(op, y_ref, x)
+    finally:
+        op.release()
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_fc_parity_sweep(enn, orc, ctx, seed):
+    """Pseudo-random FullyConnected shapes (packed, narrow-span, GEMV and plain paths) x activation x quantisation."""
+    rng = np.random.default_rng(3000 + seed)
+    act = int(rng.choice([cases.enn.ACT_NONE, cases.enn.ACT_RELU, cases.enn.ACT_RELU6]))
+    kw = dict(m=int(rng.choice([3, 8, 200, 4104, 4112])), k=int(rng.choice([16, 32, 48, 64, 96, 160, 512])),
+              n=int(rng.choice([16, 24, 40, 96, 272])), per_channel=bool(rng.integers(0, 2)), act=act,
+              out_zp=int(rng.choice([0, 0, 9, 128])) if act != cases.enn.ACT_NONE else int(rng.integers(0, 256)))
+    kw["out_scale"] = cases.fc_out_scale(kw["k"]) * float(np.exp(rng.uniform(np.log(0.02), np.log(2.0))))
+    if not kw["per_channel"]:
+        kw["w_zp"] = int(rng.integers(100, 156))
+    d, x, w, b, sc = cases.fc_case(seed=seed, **kw)
+    y_ref = orc.fully_connected(d, x, w, b, sc)
+    op = enn.fully_connected(ctx, d, w, b, sc)
+    try:
+        _check(op, y_ref, x)
     finally:
         op.release()
 
