@@ -139,6 +139,14 @@ int32_t enn_b200_context_destroy(enn_b200_context *ctx) {
     if (!ctx) return ENN_B200_INVALID_PARAMS;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    if (ctx->aux_ready) {
+        for (int i = 0; i < enn_b200_context::kAuxStreams; ++i) {
+            cudaStreamSynchronize(ctx->aux_streams[i]);
+            cudaStreamDestroy(ctx->aux_streams[i]);
+            cudaEventDestroy(ctx->ev_join[i]);
+        }
+        cudaEventDestroy(ctx->ev_fork);
+    }
     cudaStreamDestroy(ctx->stream);
     delete ctx;
     return ENN_B200_SUCCESS;

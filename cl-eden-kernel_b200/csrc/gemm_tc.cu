@@ -1184,6 +1184,7 @@ struct TcPlan {
     std::vector<TcGemm> gemms;
     void *scratch = nullptr;           // im2col matrix, shared by the GEMMs of the op (they run in stream order)
     size_t scratch_bytes = 0;
+    bool fan_out = false;              // the GEMMs are independent (deconvolution classes): run them side by side
     int32_t *err_host = nullptr;       // pinned + mapped
     int32_t *err_dev = nullptr;
 };
@@ -1702,6 +1703,17 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
             }
         }
         if (plan->gemms.empty()) return bail(ENN_B200_INVALID_PARAMS);
+        // The classes write disjoint outputs and only read the (padded) input: give each a share of the SMs and launch
+        // them on side streams, so that their launch and pipeline latencies overlap instead of adding up.
+        const int ncls = static_cast<int>(plan->gemms.size());
+        bool all_implicit = true;
+        for (auto &gm : plan->gemms) all_implicit = all_implicit && gm.implicit;
+        if (ncls > 1 && ncls <= enn_b200_context::kAuxStreams + 1 && all_implicit && !getenv("ENN_B200_NO_FAN_OUT")) {
+            plan->fan_out = true;
+            const int share = ctx->sm_count / ncls > 0 ? ctx->sm_count / ncls : 1;
+            for (auto &gm : plan->gemms)
+                if (gm.grid > share) gm.grid = share;
+        }
     }
 
     {   // All implicit GEMMs of an operator read the same input: one padded copy with the union of their margins.
@@ -1807,6 +1819,20 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
         ctx->last_error = buf;
         return ENN_B200_CUDA_FAILURE;
     }
+    const bool fan_out = plan->fan_out && !getenv("ENN_B200_TC_DEBUG");
+    if (fan_out && !ctx->aux_ready) {
+        bool ok = cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; i < enn_b200_context::kAuxStreams && ok; ++i)
+            ok = cudaStreamCreateWithFlags(&ctx->aux_streams[i], cudaStreamNonBlocking) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&ctx->ev_join[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) {
+            ctx->last_error = "could not create the side streams";
+            return ENN_B200_CUDA_FAILURE;
+        }
+        ctx->aux_ready = true;
+    }
+    int cls = 0;             // index of the GEMM among those launched (fan-out: 0 runs on the main stream)
+    bool forked = false;
     for (auto &gm : plan->gemms) {
         TcParams &p = gm.prm;
         if (p.M == 0) continue;
@@ -1885,7 +1911,23 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
             if (!dbg_buf) cudaMallocManaged(&dbg_buf, sizeof(long long) * 8 * 1024);
             p.dbg = dbg_buf;
         }
-        launch_tc_gemm(gm, gm.map_a, p, ctx->stream);
+        cudaStream_t gs = ctx->stream;
+        if (fan_out) {
+            if (!forked) {       // everything the classes read (input, padded copy) is ordered before this point
+                cudaEventRecord(ctx->ev_fork, ctx->stream);
+                forked = true;
+            }
+            if (cls > 0) {
+                gs = ctx->aux_streams[cls - 1];
+                cudaStreamWaitEvent(gs, ctx->ev_fork, 0);
+            }
+        }
+        launch_tc_gemm(gm, gm.map_a, p, gs);
+        if (fan_out && cls > 0) {
+            cudaEventRecord(ctx->ev_join[cls - 1], gs);
+            cudaStreamWaitEvent(ctx->stream, ctx->ev_join[cls - 1], 0);
+        }
+        ++cls;
         if (dbg) {
             cudaStreamSynchronize(ctx->stream);
             const long long *d = p.dbg;

@@ -15,6 +15,12 @@ struct enn_b200_context {
     int cc_major = 0, cc_minor = 0;
     std::string last_error;
     void *encode_tiled = nullptr;   // cuTensorMapEncodeTiled, resolved through the runtime
+    // Side streams for operators made of independent launches (the parity classes of a transposed convolution): forked
+    // from and joined back into `stream` with events, created on first use.
+    static constexpr int kAuxStreams = 8;
+    cudaStream_t aux_streams[kAuxStreams] = {};
+    cudaEvent_t ev_fork = nullptr, ev_join[kAuxStreams] = {};
+    bool aux_ready = false;
 };
 
 namespace enn_b200 {
