@@ -416,6 +416,34 @@ def test_oplist_mobilenet_small(enn, orc, ctx):
         ol.destroy()
 
 
+def test_oplist_with_deconvolution(enn, orc, ctx):
+    """conv -> transposed conv -> conv in one operator list: the deconvolution's parity-class launches fork onto side
+    streams inside the captured graph and join again; results equal the oracle chain, twice (graph replay)."""
+    d1, x, w1, b1, s1 = cases.conv_case(seed=21, n=2, h=12, w=12, cin=16, cout=32, k=3, per_channel=True, out_scale=0.2)
+    y1 = orc.conv2d(d1, x, w1, b1, s1)
+    d2, _, w2, b2, s2 = cases.deconv_case(seed=22, n=2, h=12, w=12, cin=32, cout=16, in_zp=int(d1.out_zp), in_scale=float(d1.out_scale))
+    y2 = orc.deconv(d2, y1, w2, b2, s2)
+    oh, ow = y2.shape[1], y2.shape[2]
+    d3, _, w3, b3, s3 = cases.conv_case(seed=23, n=2, h=oh, w=ow, cin=16, cout=16, k=1, per_channel=True, out_scale=0.1,
+                                        in_zp=int(d2.out_zp), in_scale=float(d2.out_scale))
+    y3 = orc.conv2d(d3, y2, w3, b3, s3)
+    ol = enn.OpList(ctx)
+    ops = [enn.conv2d(ctx, d1, w1, b1, s1), enn.deconv(ctx, d2, w2, b2, s2), enn.conv2d(ctx, d3, w3, b3, s3)]
+    try:
+        t0 = ol.tensor(x.nbytes)
+        t1, t2, t3 = ol.tensor(y1.nbytes), ol.tensor(y2.nbytes), ol.tensor(y3.nbytes)
+        ol.add(ops[0], [t0], t1)
+        ol.add(ops[1], [t1], t2)
+        ol.add(ops[2], [t2], t3)
+        ol.set_io([t0], [t3], [y3.nbytes])
+        ol.finalize()
+        for _ in range(2):
+            (y,) = ol.execute([x])
+            assert np.array_equal(y.reshape(y3.shape), y3)
+    finally:
+        ol.destroy()
+
+
 def test_oplist_pipelined_submit(enn, ctx):
     """enn_b200_oplist_submit / wait (copy-in overlapped with the previous graph) gives the blocking call's results."""
     import importlib
