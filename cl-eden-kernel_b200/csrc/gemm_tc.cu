@@ -475,7 +475,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // thread issues about one tensor copy per 420 cycles, which is also about what the tensor pipe needs per
         // k-block, so two lanes of each producer warp take the k-blocks in turn (two lanes issuing in step reach
         // 1.7 x the rate of one).  A stage always belongs to the same lane, so each lane meets its stages' phases in order.
-        const bool pair_lanes = split && !TWO && p.taps == 0 && p.group == 1 && p.kpack == 1 && (nst & 1) == 0 && p.k_blocks >= 8 &&
+        const bool pair_lanes = split && p.taps == 0 && p.group == 1 && p.kpack == 1 && (nst & 1) == 0 && p.k_blocks >= 8 &&
                                 !(p.dbg_mode & 9);
         if (pair_lanes) {
             const int nl = 2;      // lanes that share the issue (four measured slightly worse than two)
@@ -493,13 +493,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         t_cur = t;
                         int tg, tn;
                         tile_coords(p, tile_first + t * tile_step, tg, tn);
-                        row = is_a ? tg * kBM : tn * p.bn_rows;
+                        if (TWO) row = is_a ? (tg * 2 + static_cast<int>(rank)) * kBM : tn * p.bn_rows + static_cast<int>(rank) * (p.bn_rows >> 1);
+                        else row = is_a ? tg * kBM : tn * p.bn_rows;
                     }
                     const uint32_t ebar = empty0 + 8 * stage;
                     if (!mbar_test_wait(ebar, phase ^ 1) && !mbar_wait_fast(ebar, phase ^ 1, abort_flag, p.err, 1)) { ok = false; break; }
                     const uint32_t bar = full0 + 8 * stage;
-                    mbar_expect_tx(bar, tx);
-                    tma_load_2d(sa0 + stage * stage_bytes, map, bar, kb * static_cast<int>(span), row);
+                    if (TWO) {      // rank 0 expects the bytes of both CTAs; every load reports to rank 0's barrier
+                        if (rank == 0) mbar_expect_tx(bar, 2 * tx);
+                        tma_load_2d_pair(sa0 + stage * stage_bytes, map, mapa_rank(bar, 0), kb * static_cast<int>(span), row);
+                    } else {
+                        mbar_expect_tx(bar, tx);
+                        tma_load_2d(sa0 + stage * stage_bytes, map, bar, kb * static_cast<int>(span), row);
+                    }
                     stage += nl;
                     if (stage >= static_cast<uint32_t>(nst)) { stage -= nst; phase ^= 1; }
                     kb += nl;
@@ -1304,14 +1310,15 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
             }
         }
     }
-    // CTA pairs (cta_group::2): two SMs share one 256-row tile and every B byte is fetched once per pair.  Measured on
-    // 4096^3 and 8192^3 it runs within 2 % of the one-CTA kernel (both are bound by operand delivery, not by B traffic),
-    // so it is opt-in: ENN_B200_TC_PAIR=1 selects it for plain GEMMs with several waves of 256-wide tiles and long K.
-    bool two = false;
+    // CTA pairs (cta_group::2): two SMs share one 256-row tile and every B byte is fetched once per pair.  Used for plain
+    // GEMMs with several waves of 256-wide tiles, long K and operands too large to stay L2 resident ((M+N) K > 48 MB):
+    // 8192^3 runs 7 % faster than on the one-CTA kernel, 4096^3 3 % slower.  ENN_B200_TC_PAIR=0 / 1 overrides the size rule.
+    const bool pair_ok = span == kBK && !implicit_span && p.tiles_m >= 2 && (K + kBK - 1) / kBK >= 8 && bn_data >= 128 &&
+                         static_cast<int64_t>(p.tiles_m) * tiles_n >= 2ll * ctx->sm_count;
+    bool two = pair_ok && (static_cast<int64_t>(M) + N) * K > (48ll << 20);
     int32_t forced_rows = 0;
     if (const char *ev = getenv("ENN_B200_TC_PAIR")) {
-        two = atoi(ev) != 0 && span == kBK && p.tiles_m >= 2 && (K + kBK - 1) / kBK >= 8 && bn_data >= 128 &&
-              static_cast<int64_t>(p.tiles_m) * tiles_n >= 2ll * ctx->sm_count;
+        two = pair_ok && atoi(ev) != 0;
         if (atoi(ev) >= 128) forced_rows = atoi(ev) & ~31;      // tuning: that UMMA N instead of 256
     }
     if (two) {
