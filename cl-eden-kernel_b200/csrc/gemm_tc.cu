@@ -65,6 +65,7 @@ struct TcParams {
     int32_t bn_data;        // real output columns per N tile
     int32_t stages;
     int32_t kpack;          // k-blocks that share one pipeline stage (one barrier round trip per kpack k-blocks)
+    int32_t b_res;          // implicit convolutions: the whole B operand (one N tile, every tap) is loaded once and stays in shared memory
     int32_t need_asum;      // 1: column bn_data of each accumulator tile holds sum_k a
     int32_t zw_eff;         // zw'
     int32_t a_signed;
@@ -410,7 +411,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t span = static_cast<uint32_t>(p.span);
     const uint32_t a_bytes = kBM * span;
     const uint32_t b_bytes = static_cast<uint32_t>(TWO ? p.bn_rows >> 1 : p.bn_rows) * span;
-    const uint32_t kb_bytes = a_bytes + b_bytes;                      // one k-block: A tile then B tile
+    const bool bres = !TWO && p.b_res != 0;
+    const uint32_t b_stride = (b_bytes + 1023u) & ~1023u;             // resident B: distance between its k-blocks
+    const uint32_t kb_bytes = a_bytes + (bres ? 0u : b_bytes);        // one k-block of a stage: A tile, then B tile unless B is resident
     const uint32_t rank = TWO ? cluster_ctarank() : 0;
     const int tile_first = TWO ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
     const int tile_step = TWO ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
@@ -418,12 +421,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint8_t *tiles = smem;
     // Per-epilogue-warp copies of the N tile's column constants (kEpiWarps x 256 x 16 bytes): private to a warp, so
     // refreshing them needs only a warp-level sync.
-    int4 *s_cols = reinterpret_cast<int4 *>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+    uint8_t *b_resident = smem + static_cast<size_t>(p.stages) * stage_bytes;
+    int4 *s_cols = reinterpret_cast<int4 *>(b_resident + (bres ? static_cast<size_t>(p.k_blocks) * b_stride : 0));
     const uint32_t s_cols_u32 = smem_u32(s_cols);
     uint64_t *bars = reinterpret_cast<uint64_t *>(s_cols + kEpiWarps * kChunksPerWarp * 16);
     // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2]
     const int nst = p.stages;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * nst + 4);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * nst + 5);      // bars[2 * nst + 4]: resident B loaded
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -437,6 +441,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(full0 + 8 * s, split ? 2 : 1);        // one expect-tx arrival per producer
             mbar_init(empty0 + 8 * s, 1);
         }
+        mbar_init(tempty0 + 16, 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull0 + 8 * b, 1);
             mbar_init(tempty0 + 8 * b, TWO ? 2 * kEpiWarps : kEpiWarps);      // one arrival per epilogue warp (of both CTAs)
@@ -527,7 +532,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t sa_stage = sa_stage0;
                 // bytes this producer's loads add to a k-block (pairs: of both CTAs, counted on rank 0's barrier)
                 const uint32_t a_tx = p.taps > 0 ? static_cast<uint32_t>(p.conv_ht * p.conv_wt) * span : a_bytes;
-                const uint32_t kb_tx = ((DO_A ? a_tx : 0u) + (DO_B ? b_bytes : 0u)) * (TWO ? 2u : 1u);
+                const uint32_t kb_tx = ((DO_A ? a_tx : 0u) + (DO_B && !bres ? b_bytes : 0u)) * (TWO ? 2u : 1u);
+                if (DO_B && bres) {       // the operator's only N tile: every k-block of B, once
+                    const uint32_t bb = tempty0 + 16;
+                    mbar_expect_tx(bb, b_bytes * static_cast<uint32_t>(p.k_blocks));
+                    for (int kb = 0; kb < p.k_blocks; ++kb)
+                        tma_load_2d(smem_u32(b_resident) + kb * b_stride, &map_b, bb, kb * static_cast<int>(span), 0);
+                }
                 bool ok = true;
                 long long t_wait = 0;
                 for (int tile = tile_first; tile < total_tiles && ok; tile += tile_step) {
@@ -578,7 +589,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                             tma_load_2d(sa, &map_a, bar, (kb0 + q) * kstep_b, row_a);
                                         }
                                     }
-                                    if (DO_B) tma_load_2d(sa + a_bytes, &map_b, bar, (kb0 + q) * kstep_b, row_b);
+                                    if (DO_B && !bres) tma_load_2d(sa + a_bytes, &map_b, bar, (kb0 + q) * kstep_b, row_b);
                                 }
                             }
                             ++filled;
@@ -622,6 +633,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 ks_last = real <= 1 ? 1 : (real == 2 ? 2 : 4);
             }
             uint32_t lo_stage = lo0;
+            const uint32_t bres_lo = smem_u32(b_resident) >> 4, bstride16 = b_stride >> 4;
+            if (bres && !mbar_wait_fast(tempty0 + 16, 0, abort_flag, p.err, 5)) ok = false;
             long long t_tempty = 0, t_begin = dbg ? clock64() : 0;
             unsigned long long ns_begin = 0;
             if (dbg) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_begin));
@@ -638,7 +651,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int nsub = min(p.group, p.tiles_m - tg * p.group);
                 for (int j = 0; j < nsub && ok; ++j) {
                     const uint32_t d_tmem = tmem_base + ab * kMaxBN + j * p.bn_rows;
-                    if (ks == 4 && ks_last == 4 && p.kpack == 1 && p.stages == (TWO ? 6 : 4)) {
+                    if (ks == 4 && ks_last == 4 && p.kpack == 1 && !bres && p.stages == (TWO ? 6 : 4)) {
                         // big-GEMM shape: 256-wide tiles give four stages per CTA, six per CTA of a pair
                         if constexpr (TWO) ok = mma_tile_d6<true>(d_tmem, p.k_blocks, stage, phase, full0, empty0, desc_hi, lo0, stage16, a16, idesc, abort_flag, p.err);
                         else ok = mma_tile_d4<false>(d_tmem, p.k_blocks, stage, phase, full0, empty0, desc_hi, lo0, stage16, a16, idesc, abort_flag, p.err);
@@ -654,11 +667,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             uint32_t lo = lo_stage;
                             const int kb_end = min(kb + p.kpack, p.k_blocks);
                             for (; kb < kb_end; ++kb, lo += kb16) {
+                                const uint32_t lo_b = bres ? bres_lo + kb * bstride16 : lo + a16;
                                 if (KS == 4 && kb == p.k_blocks - 1 && ks_last != 4) {
-                                    if (ks_last == 1) umma_i8_run<TWO, 1>(d_tmem, desc_hi, lo, lo + a16, idesc, kb != 0);
-                                    else umma_i8_run<TWO, 2>(d_tmem, desc_hi, lo, lo + a16, idesc, kb != 0);
+                                    if (ks_last == 1) umma_i8_run<TWO, 1>(d_tmem, desc_hi, lo, lo_b, idesc, kb != 0);
+                                    else umma_i8_run<TWO, 2>(d_tmem, desc_hi, lo, lo_b, idesc, kb != 0);
                                 } else {
-                                    umma_i8_run<TWO, KS>(d_tmem, desc_hi, lo, lo + a16, idesc, kb != 0);
+                                    umma_i8_run<TWO, KS>(d_tmem, desc_hi, lo, lo_b, idesc, kb != 0);
                                 }
                             }
                             // frees the stage (in both CTAs of a pair) when these MMAs have read it
@@ -1442,18 +1456,24 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         return ENN_B200_CUDA_FAILURE;
     }
     // Several small k-blocks share a pipeline stage so that a barrier round trip covers ~32 KB of operands.
-    const size_t kb_bytes = (static_cast<size_t>(kBM) + (p.two ? p.bn_rows / 2 : p.bn_rows)) * span;
+    // Implicit convolutions are bound by the producer's copy issue (a thread issues one tensor copy per ~420 cycles and a
+    // tile needs one A and one B copy per tap): when the weights of the only N tile fit, they are loaded once per CTA
+    // and stay resident, the stages hold A only, and the producer issues half as many copies.
+    const size_t b_tile = (static_cast<size_t>(p.bn_rows) * span + 1023) & ~static_cast<size_t>(1023);
+    p.b_res = (implicit_span != 0 && !p.two && tiles_n == 1 && b_tile * p.k_blocks <= 72 * 1024 && !getenv("ENN_B200_NO_BRES")) ? 1 : 0;
+    const size_t kb_bytes = p.b_res ? static_cast<size_t>(kBM) * span : (static_cast<size_t>(kBM) + (p.two ? p.bn_rows / 2 : p.bn_rows)) * span;
     p.kpack = static_cast<int32_t>((32 * 1024) / kb_bytes);
     if (p.kpack < 1 || p.two) p.kpack = 1;
     if (p.kpack > p.k_blocks) p.kpack = p.k_blocks;
     if (p.kpack > 8) p.kpack = 8;
     const size_t stage_bytes = kb_bytes * p.kpack;
     const size_t fixed = static_cast<size_t>(kEpiWarps) * kChunksPerWarp * 16 * sizeof(ColParam) + 1024 + 1024;   // column constants, barriers, slack
-    int stages = static_cast<int>((227 * 1024 - fixed) / stage_bytes);
+    const size_t resident = p.b_res ? b_tile * p.k_blocks : 0;
+    int stages = static_cast<int>((227 * 1024 - fixed - resident) / stage_bytes);
     if (stages > 8) stages = 8;
     if (stages < 2) return ENN_B200_INVALID_PARAMS;
     p.stages = stages;
-    gm->smem_bytes = stages * stage_bytes + fixed;
+    gm->smem_bytes = stages * stage_bytes + fixed + resident;
     const int total_tiles = p.tiles_mg * p.tiles_n;
     gm->grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
     if (p.two) gm->grid = 2 * (total_tiles < ctx->sm_count / 2 ? total_tiles : ctx->sm_count / 2);
