@@ -522,6 +522,73 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             if (mbar_try_wait(full0 + 8 * s2, 0) || mbar_try_wait(full0 + 8 * s2, 1)) break;
                 }
             }
+        } else if (!TWO && !split && p.taps > 0 && bres && (nst & 1) == 0 && !(p.dbg_mode & 9)) {
+            // Implicit convolution with resident weights: only A tap boxes are left to load, and the copy issue rate of
+            // one thread still bounds the kernel, so lanes 0 and 1 fill alternate stages (a stage keeps its lane).
+            if (lane == 0) {       // the operator's only N tile: every k-block of B, once
+                const uint32_t bb = tempty0 + 16;
+                mbar_expect_tx(bb, b_bytes * static_cast<uint32_t>(p.k_blocks));
+                for (int kb = 0; kb < p.k_blocks; ++kb) tma_load_2d(smem_u32(b_resident) + kb * b_stride, &map_b, bb, kb * static_cast<int>(span), 0);
+            }
+            if (lane < 2) {
+                const uint32_t a_tx = static_cast<uint32_t>(p.conv_ht * p.conv_wt) * span;
+                const uint32_t sa0 = smem_u32(tiles);
+                const int gpt = (p.k_blocks + p.kpack - 1) / p.kpack;      // stages per M tile
+                const int per_img = p.conv_ty * p.conv_tx;
+                int tile = tile_first, j = 0, g = 0, tg = 0, tn = 0, nsub = 0;
+                bool done = tile >= total_tiles, ok = true;
+                if (!done) {
+                    tile_coords(p, tile, tg, tn);
+                    nsub = min(p.group, p.tiles_m - tg * p.group);
+                }
+                auto advance = [&](int n) {
+                    for (int s2 = 0; s2 < n && !done; ++s2) {
+                        if (++g < gpt) continue;
+                        g = 0;
+                        if (++j < nsub) continue;
+                        j = 0;
+                        tile += tile_step;
+                        if (tile >= total_tiles) {
+                            done = true;
+                        } else {
+                            tile_coords(p, tile, tg, tn);
+                            nsub = min(p.group, p.tiles_m - tg * p.group);
+                        }
+                    }
+                };
+                advance(lane);
+                uint32_t stage = static_cast<uint32_t>(lane), phase = 0;
+                int tm_cur = -1, img = 0, ty = 0, tx = 0;
+                while (!done) {
+                    const int tm = tg * p.group + j;
+                    if (tm != tm_cur) {          // patch (img, ty, tx) of the output grid
+                        tm_cur = tm;
+                        img = tm / per_img;
+                        const int rem = tm - img * per_img;
+                        ty = rem / p.conv_tx;
+                        tx = rem - ty * p.conv_tx;
+                    }
+                    const int kb0 = g * p.kpack, nkb = min(p.kpack, p.k_blocks - kb0);
+                    const uint32_t ebar = empty0 + 8 * stage;
+                    if (!mbar_test_wait(ebar, phase ^ 1) && !mbar_wait_fast(ebar, phase ^ 1, abort_flag, p.err, 1)) { ok = false; break; }
+                    const uint32_t bar = full0 + 8 * stage;
+                    mbar_expect_tx(bar, a_tx * nkb);
+                    int tap = kb0 / p.cchunks, cc = kb0 - tap * p.cchunks;
+                    uint32_t sa = sa0 + stage * stage_bytes;
+                    for (int q = 0; q < nkb; ++q, sa += kb_bytes) {
+                        tma_load_4d(sa, &map_a, bar, cc * static_cast<int>(span), tx * p.conv_wt + p.tap_dx[tap], ty * p.conv_ht + p.tap_dy[tap], img);
+                        if (++cc == p.cchunks) { cc = 0; ++tap; }
+                    }
+                    stage += 2;
+                    if (stage >= static_cast<uint32_t>(nst)) { stage -= nst; phase ^= 1; }
+                    advance(2);
+                }
+                if (!ok) {
+                    for (int s2 = 0; s2 < nst; ++s2)
+                        for (uint32_t i = 0; i < (1u << 16); ++i)
+                            if (mbar_try_wait(full0 + 8 * s2, 0) || mbar_try_wait(full0 + 8 * s2, 1)) break;
+                }
+            }
         } else if (lane == 0) {
             // WHICH: 0 = the A tiles, 1 = the B tiles, 2 = both (launches without the separate B producer warp)
             auto produce = [&](auto which) {
@@ -1471,6 +1538,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     const size_t resident = p.b_res ? b_tile * p.k_blocks : 0;
     int stages = static_cast<int>((227 * 1024 - fixed - resident) / stage_bytes);
     if (stages > 8) stages = 8;
+    if (p.b_res && stages >= 3 && (stages & 1)) --stages;      // two producer lanes on alternate stages need an even ring
     if (stages < 2) return ENN_B200_INVALID_PARAMS;
     p.stages = stages;
     gm->smem_bytes = stages * stage_bytes + fixed + resident;
