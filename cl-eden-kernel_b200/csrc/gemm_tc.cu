@@ -522,19 +522,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             if (mbar_try_wait(full0 + 8 * s2, 0) || mbar_try_wait(full0 + 8 * s2, 1)) break;
                 }
             }
-        } else if (!TWO && !split && p.taps > 0 && bres && (nst & 1) == 0 && !(p.dbg_mode & 9)) {
-            // Implicit convolution with resident weights: only A tap boxes are left to load, and the copy issue rate of
-            // one thread still bounds the kernel, so lanes 0 and 1 fill alternate stages (a stage keeps its lane).
+        } else if (!TWO && !split && bres && (nst & 1) == 0 && !(p.dbg_mode & 9)) {
+            // Resident weights (implicit convolutions, narrow pointwise layers): only A tiles are left to load, and the copy
+            // issue rate of one thread still bounds the kernel, so lanes 0 and 1 fill alternate stages (a stage keeps its lane).
             if (lane == 0) {       // the operator's only N tile: every k-block of B, once
                 const uint32_t bb = tempty0 + 16;
                 mbar_expect_tx(bb, b_bytes * static_cast<uint32_t>(p.k_blocks));
                 for (int kb = 0; kb < p.k_blocks; ++kb) tma_load_2d(smem_u32(b_resident) + kb * b_stride, &map_b, bb, kb * static_cast<int>(span), 0);
             }
             if (lane < 2) {
-                const uint32_t a_tx = static_cast<uint32_t>(p.conv_ht * p.conv_wt) * span;
+                const uint32_t a_tx = p.taps > 0 ? static_cast<uint32_t>(p.conv_ht * p.conv_wt) * span : a_bytes;
                 const uint32_t sa0 = smem_u32(tiles);
                 const int gpt = (p.k_blocks + p.kpack - 1) / p.kpack;      // stages per M tile
-                const int per_img = p.conv_ty * p.conv_tx;
+                const int per_img = p.taps > 0 ? p.conv_ty * p.conv_tx : 1;
                 int tile = tile_first, j = 0, g = 0, tg = 0, tn = 0, nsub = 0;
                 bool done = tile >= total_tiles, ok = true;
                 if (!done) {
@@ -561,23 +561,27 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 int tm_cur = -1, img = 0, ty = 0, tx = 0;
                 while (!done) {
                     const int tm = tg * p.group + j;
-                    if (tm != tm_cur) {          // patch (img, ty, tx) of the output grid
-                        tm_cur = tm;
+                    if (tm != tm_cur && p.taps > 0) {          // patch (img, ty, tx) of the output grid
                         img = tm / per_img;
                         const int rem = tm - img * per_img;
                         ty = rem / p.conv_tx;
                         tx = rem - ty * p.conv_tx;
                     }
+                    tm_cur = tm;
                     const int kb0 = g * p.kpack, nkb = min(p.kpack, p.k_blocks - kb0);
                     const uint32_t ebar = empty0 + 8 * stage;
                     if (!mbar_test_wait(ebar, phase ^ 1) && !mbar_wait_fast(ebar, phase ^ 1, abort_flag, p.err, 1)) { ok = false; break; }
                     const uint32_t bar = full0 + 8 * stage;
                     mbar_expect_tx(bar, a_tx * nkb);
-                    int tap = kb0 / p.cchunks, cc = kb0 - tap * p.cchunks;
                     uint32_t sa = sa0 + stage * stage_bytes;
-                    for (int q = 0; q < nkb; ++q, sa += kb_bytes) {
-                        tma_load_4d(sa, &map_a, bar, cc * static_cast<int>(span), tx * p.conv_wt + p.tap_dx[tap], ty * p.conv_ht + p.tap_dy[tap], img);
-                        if (++cc == p.cchunks) { cc = 0; ++tap; }
+                    if (p.taps > 0) {
+                        int tap = kb0 / p.cchunks, cc = kb0 - tap * p.cchunks;
+                        for (int q = 0; q < nkb; ++q, sa += kb_bytes) {
+                            tma_load_4d(sa, &map_a, bar, cc * static_cast<int>(span), tx * p.conv_wt + p.tap_dx[tap], ty * p.conv_ht + p.tap_dy[tap], img);
+                            if (++cc == p.cchunks) { cc = 0; ++tap; }
+                        }
+                    } else {
+                        for (int q = 0; q < nkb; ++q, sa += kb_bytes) tma_load_2d(sa, &map_a, bar, (kb0 + q) * static_cast<int>(span), tm * kBM);
                     }
                     stage += 2;
                     if (stage >= static_cast<uint32_t>(nst)) { stage -= nst; phase ^= 1; }
@@ -1523,11 +1527,12 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         return ENN_B200_CUDA_FAILURE;
     }
     // Several small k-blocks share a pipeline stage so that a barrier round trip covers ~32 KB of operands.
-    // Implicit convolutions are bound by the producer's copy issue (a thread issues one tensor copy per ~420 cycles and a
-    // tile needs one A and one B copy per tap): when the weights of the only N tile fit, they are loaded once per CTA
-    // and stay resident, the stages hold A only, and the producer issues half as many copies.
+    // Implicit convolutions and narrow pointwise layers are bound by the producer's copy issue (a thread issues one tensor
+    // copy per ~420 cycles and a tile needs one A and one B copy per k-block): when the weights of the only N tile fit,
+    // they are loaded once per CTA and stay resident, the stages hold A only, and the producer issues half as many copies.
     const size_t b_tile = (static_cast<size_t>(p.bn_rows) * span + 1023) & ~static_cast<size_t>(1023);
-    p.b_res = (implicit_span != 0 && !p.two && tiles_n == 1 && b_tile * p.k_blocks <= 72 * 1024 && !getenv("ENN_B200_NO_BRES")) ? 1 : 0;
+    p.b_res = ((implicit_span != 0 || p.bn_rows <= 64) && !p.two && tiles_n == 1 && M > kGemvMaxM && b_tile * p.k_blocks <= 72 * 1024 &&
+               !getenv("ENN_B200_NO_BRES")) ? 1 : 0;
     const size_t kb_bytes = p.b_res ? static_cast<size_t>(kBM) * span : (static_cast<size_t>(kBM) + (p.two ? p.bn_rows / 2 : p.bn_rows)) * span;
     p.kpack = static_cast<int32_t>((32 * 1024) / kb_bytes);
     if (p.kpack < 1 || p.two) p.kpack = 1;
