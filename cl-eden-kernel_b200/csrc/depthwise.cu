@@ -154,6 +154,11 @@ __device__ __forceinline__ void dw_transpose_row(DwRow<STRIDE> &r, const DwRaw<S
     }
 }
 
+// 128-thread blocks, four per SM (16 warps at the 128-register budget the kernel needs to stay spill-free). Five
+// blocks at 96 registers spill and lose more in a chain of layers than the extra warps gain; 256-thread blocks at
+// the same occupancy drain more slowly before the next layer's GEMM CTA, which needs the whole SM, can start.
+constexpr int kDwThreads = 128;
+
 template <int STRIDE, bool W_SIGNED, bool NEED_ASUM, bool FIRST>
 __device__ __forceinline__ void dw_accumulate(int32_t (&acc)[4][4], int32_t (&asum)[NEED_ASUM ? 4 : 1][4],
                                               const DwRow<STRIDE> &r, const uint32_t (&wlo)[4], const uint32_t (&whi)[4],
@@ -203,7 +208,7 @@ __device__ __forceinline__ void dw_accumulate(int32_t (&acc)[4][4], int32_t (&as
 // q = acc * M0 + C with C = bias * M0 + 2^30 + 2^(30+e), result = hi32(q) >> (e - 1); DwChan then holds
 // {C low, C high, M0, e - 1}.
 template <int STRIDE, bool W_SIGNED, bool NEED_ASUM, bool RELU>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(kDwThreads, 4)
 dw3x3_kernel(ConvGeom g, const DwChan *__restrict__ chan, const uint32_t *__restrict__ w_packed,
              const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int th, int nyt, int nstrip, int64_t total) {
     pdl_wait();         // the tensors of the kernel before this one are complete from here on
@@ -701,7 +706,7 @@ cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, bool relu_form, co
     const int nyt = (g.oh + th - 1) / th;
     const int64_t total = static_cast<int64_t>(g.n) * nyt * nstrip * cqn;
     if (total == 0) return cudaSuccess;
-    const int threads = 256;
+    const int threads = kDwThreads;
     const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
     const DwChan *c = static_cast<const DwChan *>(chan);
     const uint32_t *w = static_cast<const uint32_t *>(w_packed);
