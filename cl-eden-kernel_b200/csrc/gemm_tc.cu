@@ -328,6 +328,7 @@ __device__ __forceinline__ void tile_coords(const TcParams &p, int tile, int &tg
 //                the two-shift form, so the planner selects it only with ENN_B200_RELU_HI=1.
 // ColParam words: {mult, addend, esh, bias} for the first two modes, {C low, C high, mult, shifts} for the ReLU modes
 // (shifts = e - 1 for kModeReluHi, (31 - ls) | e << 8 for kModeReluTwo).
+constexpr size_t kWidePackWeightBytes = 100 * 1024;    // resident block-diagonal weights of a wide-row pixel packing
 constexpr int kModeNudge = 0, kModeGeneral = 1, kModeReluHi = 2, kModeReluTwo = 3;
 
 // Requantise one accumulator (bias not yet added) to (value - act_min) in [0, act_max - act_min].
@@ -779,6 +780,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int64_t st_bits = p.out_base | p.out_sn | p.out_sy | p.out_sx | p.bn_data | static_cast<int64_t>(reinterpret_cast<uintptr_t>(p.out));
         const int st_align = (st_bits & 15) == 0 ? 16 : ((st_bits & 7) == 0 ? 8 : 1);   // widest store every row start allows
         const bool st_fast = st_align == 16 && (p.N & 15) == 0;      // every chunk is one aligned 16-byte store
+        const bool whole_rows = st_fast && p.taps == 0 && !(p.dbg_mode & 4);   // rows of a full M tile are all real: see the chunk loop
         const int patch_y = p.taps > 0 ? row_in_tile / p.conv_wt : 0;   // this thread's position in the output patch
         const int patch_x = p.taps > 0 ? row_in_tile - patch_y * p.conv_wt : 0;
         const int cps_mod = (p.bn_data >> 4) % kColGroups;
@@ -859,6 +861,39 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         tmem_ld_wait();
                         asum_term = p.zw_eff * static_cast<int32_t>(rs);
                     }
+                    // Requantises the 8 accumulators of one half chunk into two packed words.
+                    auto half_chunk = [&](const uint32_t (&r)[8], uint32_t lc_half, uint32_t &w0, uint32_t &w1) {
+#pragma unroll
+                        for (int jj = 0; jj < 2; ++jj) {
+                            int32_t y[4];
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                int4 cv;
+                                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(lc_half + (jj * 4 + b) * 16));
+                                int32_t acc = static_cast<int32_t>(r[jj * 4 + b]);
+                                if (ASUM) acc -= asum_term;
+                                y[b] = tc_requant<MODE>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
+                            }
+                            const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
+                            (jj == 0 ? w0 : w1) = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
+                        }
+                    };
+                    if (whole_rows && n_cols == (cps << 4) && m + (kBM - 1 - row_in_tile) < p.M) {
+                        // The usual case, decided per warp: the M tile lies inside the matrix, every chunk is 16 real columns and
+                        // one aligned 16-byte store.  No per-thread conditions, so nothing here diverges.
+                        for (int c0 = first << 4; c0 < (cps << 4); c0 += kColGroups * 16, lc_private += 256) {
+                            const uint32_t lc = cols_shared ? lc_shared + c0 * 16 : lc_private;
+                            uint32_t w[4];
+#pragma unroll
+                            for (int half = 0; half < 2; ++half) {
+                                uint32_t r[8];
+                                tmem_ld_x8(t_tile + c0 + 8 * half, r);      // warp-collective
+                                tmem_ld_wait();
+                                half_chunk(r, lc + half * 128, w[half * 2], w[half * 2 + 1]);
+                            }
+                            *reinterpret_cast<uint4 *>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
                     for (int c0 = first << 4; c0 < (cps << 4); c0 += kColGroups * 16, lc_private += 256) {
                         const uint32_t lc = cols_shared ? lc_shared + c0 * 16 : lc_private;
                         // two 8-column loads per chunk: half the accumulator registers live at a time
@@ -868,22 +903,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             uint32_t r[8];
                             tmem_ld_x8(t_tile + c0 + 8 * half, r);      // warp-collective
                             tmem_ld_wait();
-                            if (row_ok && c0 < n_cols) {
-#pragma unroll
-                                for (int jj = 0; jj < 2; ++jj) {
-                                    int32_t y[4];
-#pragma unroll
-                                    for (int b = 0; b < 4; ++b) {
-                                        int4 cv;
-                                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(lc + (half * 8 + jj * 4 + b) * 16));
-                                        int32_t acc = static_cast<int32_t>(r[jj * 4 + b]);
-                                        if (ASUM) acc -= asum_term;
-                                        y[b] = tc_requant<MODE>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
-                                    }
-                                    const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
-                                    w[half * 2 + jj] = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
-                                }
-                            }
+                            if (row_ok && c0 < n_cols) half_chunk(r, lc + half * 128, w[half * 2], w[half * 2 + 1]);
                         }
                         if (row_ok && c0 < n_cols) {
                             if (p.dbg_mode & 4) {
@@ -912,6 +932,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             }
                         }
                     }
+                }
                 }
                 // first chunk of this warp in the next M tile
                 first -= cps_mod;
@@ -1360,7 +1381,7 @@ struct QuantHost {   // host copies of what setup_quant uploaded
 // weight(n, k) returns the raw weight byte of output column n at reduction index k (k < K).
 template <typename WeightFn>
 int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh, int32_t M, int32_t N, int32_t K, WeightFn weight,
-                   TcGemm *gm, uint32_t implicit_span = 0) {
+                   TcGemm *gm, uint32_t implicit_span = 0, bool want_resident = false) {
     TcParams &p = gm->prm;
     p.M = M; p.N = N; p.K = K;
     // K bytes per k-block.  Implicit convolutions bring theirs (the channel chunk); plain GEMMs with a short K use 32-
@@ -1531,16 +1552,16 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     // copy per ~420 cycles and a tile needs one A and one B copy per k-block): when the weights of the only N tile fit,
     // they are loaded once per CTA and stay resident, the stages hold A only, and the producer issues half as many copies.
     const size_t b_tile = (static_cast<size_t>(p.bn_rows) * span + 1023) & ~static_cast<size_t>(1023);
-    p.b_res = ((implicit_span != 0 || p.bn_rows <= 64) && !p.two && tiles_n == 1 && M > kGemvMaxM && b_tile * p.k_blocks <= 72 * 1024 &&
+    p.b_res = ((implicit_span != 0 || p.bn_rows <= 64 || want_resident) && !p.two && tiles_n == 1 && M > kGemvMaxM && b_tile * p.k_blocks <= (want_resident ? kWidePackWeightBytes : 72 * 1024) &&
                !getenv("ENN_B200_NO_BRES")) ? 1 : 0;
     const size_t kb_bytes = p.b_res ? static_cast<size_t>(kBM) * span : (static_cast<size_t>(kBM) + (p.two ? p.bn_rows / 2 : p.bn_rows)) * span;
     p.kpack = static_cast<int32_t>((32 * 1024) / kb_bytes);
     if (p.kpack < 1 || p.two) p.kpack = 1;
     if (p.kpack > p.k_blocks) p.kpack = p.k_blocks;
     if (p.kpack > 8) p.kpack = 8;
-    const size_t stage_bytes = kb_bytes * p.kpack;
     const size_t fixed = static_cast<size_t>(kEpiWarps) * kChunksPerWarp * 16 * sizeof(ColParam) + 1024 + 1024;   // column constants, barriers, slack
     const size_t resident = p.b_res ? b_tile * p.k_blocks : 0;
+    const size_t stage_bytes = kb_bytes * p.kpack;
     int stages = static_cast<int>((227 * 1024 - fixed - resident) / stage_bytes);
     if (stages > 8) stages = 8;
     if (p.b_res && stages >= 3 && (stages & 1)) --stages;      // two producer lanes on alternate stages need an even ring
@@ -1757,6 +1778,23 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
             }
             if (pack > 1) in_place = true;
         }
+        // Wider rows that are not whole 128-byte lines (K = 96, 144, 192 ...: the MobileNetV2 project layers).  In place,
+        // every 128-byte box row of such a tensor straddles two lines and the last k-block is mostly padding; with f pixels
+        // per row of f * K bytes the k-blocks are (mostly) aligned full lines and the f * N output bytes of a row are whole
+        // 16-byte stores.  The block-diagonal weights (f^2 times the layer's) must stay resident in shared memory, and the
+        // layer must keep two waves of M tiles, or the packing costs more than it saves.
+        bool wide_pack = false;
+        if (pointwise && pack == 1 && M64 >= 4096 && K > 64 && (K & 127) != 0 && (K & 15) == 0 && !getenv("ENN_B200_NO_PACK")) {
+            const int32_t zw_eff = g.w_signed ? g.w_zp : g.w_zp - 128;
+            const int32_t extra = zw_eff != 0 ? 16 : 0;
+            const int32_t forced = getenv("ENN_B200_PACK_WIDE") ? atoi(getenv("ENN_B200_PACK_WIDE")) : 0;   // tuning override (1 = off)
+            for (int32_t f = 8; f >= 2 && pack == 1 && forced != 1; f >>= 1) {
+                if ((forced > 1 && f != forced) || M64 % f != 0 || f * N > kMaxBN - extra) continue;
+                const size_t kp = (static_cast<size_t>(f) * K + 127) & ~static_cast<size_t>(127);
+                const size_t rows = ((static_cast<size_t>(f) * N + 15) & ~static_cast<size_t>(15)) + extra;
+                if (rows * kp <= kWidePackWeightBytes && M64 / f >= 2ll * kBM * ctx->sm_count) { pack = f; wide_pack = true; in_place = true; }
+            }
+        }
         if (in_place && pack > 1) {
             QuantHost qp;
             for (int32_t r = 0; r < pack; ++r) {
@@ -1768,7 +1806,7 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
             auto packed_weight = [&](int32_t n, int32_t k) -> uint8_t {
                 return n / N == k / K ? w[static_cast<size_t>(k % K) * N + (n % N)] : zero_raw;
             };
-            st = build_gemm(ctx, g, qp, static_cast<int32_t>(M64 / pack), pack * N, pack * K, packed_weight, &gm);
+            st = build_gemm(ctx, g, qp, static_cast<int32_t>(M64 / pack), pack * N, pack * K, packed_weight, &gm, 0, wide_pack);
             if (st != ENN_B200_SUCCESS) return bail(st);
             gm.prm.qh = 1; gm.prm.qw = static_cast<int32_t>(M64 / pack);
             gm.prm.out_base = 0; gm.prm.out_sn = 0; gm.prm.out_sy = 0; gm.prm.out_sx = pack * N;

@@ -64,6 +64,10 @@ CONV_CASES = {
     "pack_1x1_c24_to_144_relu": dict(n=2, h=48, w=50, cin=24, cout=144, k=1, per_channel=True, out_scale=0.002, out_zp=0),
     "pack_1x1_c24_to_40_u8w": dict(n=1, h=64, w=66, cin=24, cout=40, k=1, w_zp=130, out_scale=0.03),
     "pack_1x1_c32_to_16": dict(n=2, h=48, w=50, cin=32, cout=16, k=1, per_channel=True, out_scale=0.3, act=cases.enn.ACT_NONE),
+    # rows of 96 / 144 / 192 bytes (not whole 128-byte lines), few output channels: the shapes of the MobileNetV2 project layers
+    "pack_wide_1x1_c96_to_24": dict(n=2, h=48, w=50, cin=96, cout=24, k=1, per_channel=True, out_scale=0.4, act=cases.enn.ACT_NONE),
+    "pack_wide_1x1_c144_to_32_u8w": dict(n=1, h=64, w=66, cin=144, cout=32, k=1, w_zp=130, out_scale=0.08, act=cases.enn.ACT_NONE),
+    "pack_wide_1x1_c192_to_64_relu": dict(n=2, h=46, w=50, cin=192, cout=64, k=1, per_channel=True, out_scale=0.004, out_zp=0),
     "first_layer_s2": dict(n=4, h=66, w=71, cin=3, cout=32, k=3, stride=2, per_channel=True, out_scale=0.1),
     "first_layer_s1_u8w": dict(n=2, h=47, w=53, cin=3, cout=16, k=3, w_zp=121, out_scale=0.05),
     "first_layer_signed": dict(n=1, h=70, w=69, cin=3, cout=48, k=3, act_dtype=cases.enn.S8, in_zp=-7, out_zp=3, per_channel=True, out_scale=0.2),
@@ -285,6 +289,9 @@ FC_CASES = {
     "pack_k16_n24_per_tensor": dict(m=4104, k=16, n=24, per_channel=False, w_zp=119),
     "pack_k64_n96_relu": dict(m=4098, k=64, n=96, act=cases.enn.ACT_RELU, out_zp=0, out_scale=0.004),
     "pack_k32_n48_mixed_shift": dict(m=4100, k=32, n=48, out_scale=0.0012),
+    "pack_wide_k96_n24": dict(m=4104, k=96, n=24, act=cases.enn.ACT_NONE),
+    "pack_wide_k144_n24_per_tensor": dict(m=4100, k=144, n=24, per_channel=False, w_zp=119, act=cases.enn.ACT_NONE),
+    "pack_wide_k192_n32": dict(m=4098, k=192, n=32, act=cases.enn.ACT_NONE, out_scale=0.3),
 }
 
 
