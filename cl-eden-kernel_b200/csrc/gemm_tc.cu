@@ -326,9 +326,8 @@ __device__ __forceinline__ void tile_coords(const TcParams &p, int tile, int &tg
 //                shift ls fold into one 64-bit addend: q = acc * M0 + C, C = bias * M0 + 2^(30-ls) (+ 2^(e-1+31-ls) when
 //                e >= 1); result = (q >> (31 - ls)) >> e.  Covers e == 0 and left shifts, which otherwise need the
 //                general code.
-//   kModeReluHi  the same with one shift, hi32(q) >> (e - 1), for operators whose columns all have e >= 1 and ls == 0:
-//                implemented, but it spills a little under the epilogue's 72-register cap and measured within noise of
-//                the two-shift form, so the planner selects it only with ENN_B200_RELU_HI=1.
+//   kModeReluHi  the same with one shift, hi32(q) >> (e - 1), for operators whose columns all have e >= 1 and ls == 0
+//                (two ALU instructions per output fewer; ENN_B200_NO_RELU_HI=1 keeps the two-shift form).
 // ColParam words: {mult, addend, esh, bias} for the first two modes, {C low, C high, mult, shifts} for the ReLU modes
 // (shifts = e - 1 for kModeReluHi, (31 - ls) | e << 8 for kModeReluTwo).
 constexpr size_t kWidePackWeightBytes = 100 * 1024;    // resident block-diagonal weights of a wide-row pixel packing
@@ -1496,7 +1495,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         // stage-1 value plus the rounding term must fit 32 bits
         if ((bound_v[n] << ls) + (e >= 1 ? (1ll << (e - 1)) : 0) + 1 >= (1ll << 31)) relu_two = false;
     }
-    p.mode = relu_hi && getenv("ENN_B200_RELU_HI") ? kModeReluHi : (relu_two ? kModeReluTwo : kModeNudge);
+    p.mode = relu_hi && !getenv("ENN_B200_NO_RELU_HI") ? kModeReluHi : (relu_two ? kModeReluTwo : kModeNudge);
     for (int32_t n = 0; n < N; ++n) {
         const int32_t tn = n / bn_data, r = n % bn_data;
         const int64_t folded = folded_v[n];
