@@ -485,6 +485,26 @@ int32_t enn_b200_add_prepare(enn_b200_context *ctx, const enn_b200_add_desc *d, 
             return st;
         }
         p.lut = dl;
+        std::vector<uint8_t> lut2(65536);
+        for (uint32_t a = 0; a < 256; ++a)
+            for (uint32_t b = 0; b < 256; ++b) {
+                int32_t o = enn_rdivpot(enn_srdhm(lut[a] + lut[256 + b], p.mo), -p.so) + p.out_off;
+                o = o < p.act_min ? p.act_min : o;
+                o = o > p.act_max ? p.act_max : o;
+                lut2[add_lut2_index(a, b)] = static_cast<uint8_t>(o);
+            }
+        uint8_t *dl2 = nullptr;
+        const int32_t st2 = upload_vec(op, lut2, &dl2);
+        if (st2 != ENN_B200_SUCCESS) {
+            enn_b200_op_release(op);
+            return st2;
+        }
+        p.lut2 = dl2;
+        const cudaError_t ae = add_kernel_init();
+        if (ae != cudaSuccess) {
+            enn_b200_op_release(op);
+            return cuda_fail(ctx, ae, "add_kernel_init");
+        }
     }
     op->info.impl = op->impl;
     op->info.in_bytes = 2 * d->count; op->info.out_bytes = d->count;

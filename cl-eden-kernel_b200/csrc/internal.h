@@ -54,7 +54,18 @@ struct AddParams {
     // Stage-1 values of both inputs by input byte (device array of 2 x 256 words: in0 table, in1 table), so that the
     // vector kernel spends its instructions on the last stage only.  Built at prepare time with the same functions.
     const int32_t *lut;
+    // The whole operator as one table: output byte for every pair of input bytes, at index
+    // add_lut2_index(a, b) (65536 bytes, built from the same three stages at prepare time).  Large tensors use it
+    // from shared memory: a lookup replaces the 64-bit multiply and both rounding shifts of the last stage.
+    const uint8_t *lut2;
 };
+
+// Position of pair (a, b) in the 64 KB table: row a, column b with the low bits of a folded into the word index, so
+// that lanes whose b bytes agree (flat image regions) still spread over the shared-memory banks.
+__host__ __device__ inline uint32_t add_lut2_index(uint32_t a, uint32_t b) {
+    const uint32_t idx = (a << 8) | b;
+    return idx ^ ((idx >> 6) & 0x7cu);
+}
 
 struct PoolGeom {
     int32_t n, h, w, c, kh, kw, sh, sw, pt, pl, oh, ow;
@@ -99,6 +110,7 @@ cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, bool relu_form, co
 bool dw_tma_plan(enn_b200_op *op);
 cudaError_t dw_tma_launch(enn_b200_op *op, const void *in, void *out);
 void dw_tma_release(enn_b200_op *op);
+cudaError_t add_kernel_init();
 cudaError_t launch_add(const AddParams &p, int64_t count, const void *a, const void *b, void *out, int sm_count,
                        cudaStream_t s);
 cudaError_t launch_avgpool(const PoolGeom &p, const void *in, void *out, cudaStream_t s);

@@ -150,9 +150,62 @@ __global__ void add_kernel_vec(AddParams p, int64_t count16, const uint4 *__rest
     }
 }
 
+// Large tensors: the operator's 64 KB pair table in shared memory, 16 bytes per thread per step, one byte lookup per
+// output.  The table belongs to the operator, so it is staged before the wait on the kernel that produces the inputs.
+constexpr int kAddLut2Threads = 256;
+constexpr int64_t kAddLut2MinCount = 1 << 20;      // below this the table staging costs more than the arithmetic it saves
+
+__global__ void __launch_bounds__(kAddLut2Threads) add_kernel_lut2(AddParams p, int64_t count16, const uint4 *__restrict__ a,
+                                                                  const uint4 *__restrict__ b, uint4 *__restrict__ out) {
+    extern __shared__ uint4 s_lut2_q[];
+    const uint4 *src = reinterpret_cast<const uint4 *>(p.lut2);
+    for (int i = threadIdx.x; i < 4096; i += blockDim.x) s_lut2_q[i] = __ldg(src + i);
+    __syncthreads();
+    pdl_wait();
+    pdl_trigger();
+    const uint8_t *lut = reinterpret_cast<const uint8_t *>(s_lut2_q);
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count16; i += stride) {
+        const uint4 va = a[i], vb = b[i];
+        const uint32_t wa[4] = {va.x, va.y, va.z, va.w};
+        const uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w};
+        uint32_t wo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t o[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                // (a byte k) << 8 | (b byte k): bytes {b.k, a.k, zero, zero}
+                const uint32_t idx = __byte_perm(wb[j], wa[j], 0x7700u | (static_cast<uint32_t>(4 + k) << 4) | static_cast<uint32_t>(k)) & 0xffffu;
+                o[k] = lut[idx ^ ((idx >> 6) & 0x7cu)];
+            }
+            wo[j] = o[0] | (o[1] << 8) | (o[2] << 16) | (o[3] << 24);
+        }
+        out[i] = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+    }
+}
+
+// Called once per prepared add operator (with its device current): the pair-table kernel needs 64 KB of dynamic shared memory.
+cudaError_t add_kernel_init() {
+    return cudaFuncSetAttribute(add_kernel_lut2, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+}
+
 cudaError_t launch_add(const AddParams &p, int64_t count, const void *a, const void *b, void *out, int sm_count,
                        cudaStream_t s) {
     if (count == 0) return cudaSuccess;
+    if (count >= kAddLut2MinCount && p.lut2 && !getenv("ENN_B200_NO_ADD_LUT2") &&
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        const int64_t n16 = count / 16;
+        const int64_t want = (n16 + kAddLut2Threads * 4 - 1) / (kAddLut2Threads * 4);      // at least four steps per thread
+        const int blocks = static_cast<int>(want < static_cast<int64_t>(sm_count) * 3 ? want : static_cast<int64_t>(sm_count) * 3);
+        launch_pdl(add_kernel_lut2, dim3(blocks), dim3(kAddLut2Threads), 65536, s, p, n16, static_cast<const uint4 *>(a),
+                   static_cast<const uint4 *>(b), static_cast<uint4 *>(out));
+        const int64_t tail = count - n16 * 16;
+        if (tail > 0)
+            launch_pdl(add_kernel, dim3(1), dim3(32), 0, s, p, tail, static_cast<const uint8_t *>(a) + n16 * 16,
+                       static_cast<const uint8_t *>(b) + n16 * 16, static_cast<uint8_t *>(out) + n16 * 16);
+        return cudaGetLastError();
+    }
     const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
     const int threads = 256;
     if (aligned && count >= 16) {
@@ -202,10 +255,61 @@ __global__ void avgpool_kernel(PoolGeom p, const void *__restrict__ in, uint8_t 
     out[idx] = static_cast<uint8_t>(v);
 }
 
+// Four channels per thread (C % 4 == 0, windows of at most 256 taps): one 32-bit load per tap, the four byte sums kept
+// as two words of two 16-bit lanes.  Signed bytes are flipped to unsigned on load and the bias taken out of the sum.
+__global__ void avgpool_vec4_kernel(PoolGeom p, const uint32_t *__restrict__ in, uint32_t *__restrict__ out, int64_t total4) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total4) return;
+    const int32_t c4n = p.c >> 2;
+    const int32_t c4 = static_cast<int32_t>(idx % c4n);
+    int64_t q = idx / c4n;
+    const int32_t ox = static_cast<int32_t>(q % p.ow);
+    q /= p.ow;
+    const int32_t oy = static_cast<int32_t>(q % p.oh);
+    const int32_t b = static_cast<int32_t>(q / p.oh);
+    int32_t si = oy * p.sh - p.pt, sj = ox * p.sw - p.pl;
+    const int32_t ei = min(si + p.kh, p.h), ej = min(sj + p.kw, p.w);
+    si = max(si, 0);
+    sj = max(sj, 0);
+    const int32_t pool = (ei - si) * (ej - sj);
+    const uint32_t flip = p.is_signed ? 0x80808080u : 0u;
+    uint32_t even = 0, odd = 0;          // bytes 0, 2 and bytes 1, 3 as 16-bit lanes
+    for (int32_t i = si; i < ei; ++i) {
+        const uint32_t *row = in + (static_cast<int64_t>(b) * p.h + i) * p.w * c4n + c4;
+#pragma unroll 7
+        for (int32_t j = sj; j < ej; ++j) {
+            const uint32_t v = __ldg(row + static_cast<int64_t>(j) * c4n) ^ flip;
+            even += v & 0x00ff00ffu;
+            odd += (v >> 8) & 0x00ff00ffu;
+        }
+    }
+    const int32_t bias = p.is_signed ? 128 * pool : 0;
+    const int32_t sums[4] = {static_cast<int32_t>(even & 0xffff) - bias, static_cast<int32_t>(odd & 0xffff) - bias,
+                             static_cast<int32_t>(even >> 16) - bias, static_cast<int32_t>(odd >> 16) - bias};
+    uint32_t r = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        int32_t v = (sums[k] + pool / 2) / pool;
+        v = max(v, p.act_min);
+        v = min(v, p.act_max);
+        r |= (static_cast<uint32_t>(v) & 0xff) << (8 * k);
+    }
+    out[idx] = r;
+}
+
 cudaError_t launch_avgpool(const PoolGeom &p, const void *in, void *out, cudaStream_t s) {
     const int64_t total = static_cast<int64_t>(p.n) * p.oh * p.ow * p.c;
     if (total == 0) return cudaSuccess;
     const int threads = 256;
+    if ((p.c & 3) == 0 && p.kh * p.kw <= 256 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 3) == 0) {
+        const int64_t total4 = total / 4;
+        const int th = 128;
+        launch_pdl(avgpool_vec4_kernel, dim3(static_cast<unsigned>((total4 + th - 1) / th)), dim3(th), 0, s, p,
+                   static_cast<const uint32_t *>(in), static_cast<uint32_t *>(out), total4);
+        return cudaGetLastError();
+    }
     launch_pdl(avgpool_kernel, dim3(static_cast<unsigned>((total + threads - 1) / threads)), dim3(threads), 0, s, p, in,
                static_cast<uint8_t *>(out), total);
     return cudaGetLastError();

@@ -358,6 +358,45 @@ def test_add_parity(enn, orc, ctx, count, act):
         op.release()
 
 
+# four-channels-per-thread kernel: padded windows (ragged at the borders), signed bytes, a clamp that bites
+@pytest.mark.parametrize("shape", [(2, 9, 10, 24, 3, 2, 1, "u8", 0), (2, 7, 7, 64, 7, 1, 0, "s8", 0), (3, 8, 8, 12, 3, 1, 1, "s8", 1),
+                                   (1, 12, 12, 8, 5, 3, 2, "u8", 3)])
+def test_avgpool_vec4_parity(enn, orc, ctx, shape):
+    n, h, w, c, k, s, pad, dt, act = shape
+    rng = np.random.default_rng(h * w + c)
+    signed = dt == "s8"
+    x = rng.integers(-128 if signed else 0, 128 if signed else 256, (n, h, w, c), dtype=np.int64).astype(np.int8 if signed else np.uint8)
+    oh, ow = (h + 2 * pad - k) // s + 1, (w + 2 * pad - k) // s + 1
+    d = enn.PoolDesc(n=n, h=h, w=w, c=c, kh=k, kw=k, stride_h=s, stride_w=s, pad_t=pad, pad_l=pad, out_h=oh, out_w=ow,
+                     activation=act, act_dtype=enn.S8 if signed else enn.U8, out_scale=0.5, out_zp=-3 if signed else 100)
+    op = enn.avgpool(ctx, d)
+    try:
+        _check(op, orc.avgpool(d, x), x)
+    finally:
+        op.release()
+
+
+# pair-table kernel (>= 2^20 elements): a tail after the 16-byte groups, a clamp that bites, signed bytes, flat inputs
+@pytest.mark.parametrize("count,act,dt,flat", [((1 << 21) + 5, 3, "u8", False), ((1 << 20) + 16, 0, "s8", False),
+                                               (1 << 20, 1, "u8", True)])
+def test_add_pair_table_parity(enn, orc, ctx, count, act, dt, flat):
+    rng = np.random.default_rng(count + act)
+    signed = dt == "s8"
+    lo, hi, npdt = (-128, 128, np.int8) if signed else (0, 256, np.uint8)
+    a = rng.integers(lo, hi, count, dtype=np.int64).astype(npdt)
+    b = rng.integers(lo, hi, count, dtype=np.int64).astype(npdt)
+    if flat:
+        b[:] = 131
+    d = enn.AddDesc(count=count, activation=act, act_dtype=enn.S8 if signed else enn.U8, in0_scale=0.031,
+                    in0_zp=-8 if signed else 120, in1_scale=0.047, in1_zp=3 if signed else 131, out_scale=0.06,
+                    out_zp=-2 if signed else 126)
+    op = enn.add(ctx, d)
+    try:
+        _check(op, orc.add(d, a, b), a, b)
+    finally:
+        op.release()
+
+
 @pytest.mark.parametrize("shape", [(2, 7, 7, 1280, 7, 1), (1, 9, 9, 16, 3, 2), (3, 5, 6, 7, 2, 2)])
 def test_avgpool_parity(enn, orc, ctx, shape):
     n, h, w, c, k, s = shape
