@@ -93,6 +93,7 @@ struct TcParams {
     int32_t *err;           // host-mapped error word
     long long *dbg;         // optional per-CTA cycle counters [grid][8] (null in normal use)
     int32_t dbg_mode;       // development switches (0 in normal use)
+    int32_t epi_g;          // M tiles of a work unit the epilogue requantises together per column (1, 2 or 4)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -786,7 +787,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int patch_y = p.taps > 0 ? row_in_tile / p.conv_wt : 0;   // this thread's position in the output patch
         const int patch_x = p.taps > 0 ? row_in_tile - patch_y * p.conv_wt : 0;
         const int cps_mod = (p.bn_data >> 4) % kColGroups;
-        const uint32_t rot_step = static_cast<uint32_t>((p.group * (p.bn_data >> 4)) % kColGroups);
+        // Several M tiles of a unit requantised together (shared column constants): flat row-major outputs with aligned rows only.
+        const int epi_g = (!TWO && p.epi_g > 1 && st_fast && p.taps == 0 && p.qh == 1 && p.dbg_mode == 0) ? p.epi_g : 1;
+        const uint32_t rot_step = static_cast<uint32_t>((((p.group + epi_g - 1) / epi_g) * (p.bn_data >> 4)) % kColGroups);
         uint32_t it = 0;
         bool ok = true;
         int loaded_tn = -1;
@@ -834,7 +837,74 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t lc_private = my_cols;
             const uint32_t lc_shared = s_cols_u32 + static_cast<uint32_t>(tn * p.bn_rows) * 16;
             const uint8_t *out_tile = p.out + p.out_base + n_base;
-            for (int j = 0; j < nsub && !(p.dbg_mode & 2); ++j) {
+            // G M tiles at a time: the 16 bytes of constants a column needs are loaded from shared memory once and serve G
+            // outputs (those loads are what saturates first in the one-tile form: two LSU wavefronts per output and warp).
+            auto multi_tiles = [&](auto gtag) {
+                constexpr int G = decltype(gtag)::value;
+                for (int j0 = 0; j0 < nsub; j0 += G) {
+                    if (first < cps) {
+                        const int gn = min(G, nsub - j0);
+                        uint8_t *orow[G];
+                        bool live[G];
+                        int32_t asum_term[G];
+#pragma unroll
+                        for (int i = 0; i < G; ++i) {
+                            const int m = (tg * p.group + j0 + i) * kBM + row_in_tile;
+                            live[i] = i < gn && m < p.M;
+                            orow[i] = const_cast<uint8_t *>(out_tile) + static_cast<int64_t>(live[i] ? m : 0) * p.out_sx;
+                            asum_term[i] = 0;
+                            if (ASUM) {
+                                uint32_t rs;
+                                tmem_ld_x1(t_row + (j0 + i < p.group ? j0 + i : j0) * p.bn_rows + p.bn_data, rs);       // warp-collective
+                                tmem_ld_wait();
+                                asum_term[i] = p.zw_eff * static_cast<int32_t>(rs);
+                            }
+                        }
+                        for (int c0 = first << 4; c0 < (cps << 4); c0 += kColGroups * 16, lc_private += 256) {
+                            const uint32_t lc = cols_shared ? lc_shared + c0 * 16 : lc_private;
+                            uint32_t w[G][4];
+#pragma unroll
+                            for (int half = 0; half < 2; ++half) {
+                                uint32_t r[G][8];
+#pragma unroll
+                                for (int i = 0; i < G; ++i)      // warp-collective; a slot the unit does not have re-reads the first one (unused)
+                                    tmem_ld_x8(t_row + (j0 + i < p.group ? j0 + i : j0) * p.bn_rows + c0 + 8 * half, r[i]);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int jj = 0; jj < 2; ++jj) {
+                                    int32_t y[G][4];
+#pragma unroll
+                                    for (int b = 0; b < 4; ++b) {
+                                        int4 cv;
+                                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(lc + (half * 8 + jj * 4 + b) * 16));
+#pragma unroll
+                                        for (int i = 0; i < G; ++i) {
+                                            int32_t acc = static_cast<int32_t>(r[i][jj * 4 + b]);
+                                            if (ASUM) acc -= asum_term[i];
+                                            y[i][b] = tc_requant<MODE>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
+                                        }
+                                    }
+#pragma unroll
+                                    for (int i = 0; i < G; ++i) {
+                                        const uint32_t hi = pack_sat_u8_tc(y[i][3], y[i][2], 0);
+                                        w[i][half * 2 + jj] = pack_sat_u8_tc(y[i][1], y[i][0], hi) + lo_word;
+                                    }
+                                }
+                            }
+                            if (c0 < n_cols) {
+#pragma unroll
+                                for (int i = 0; i < G; ++i)
+                                    if (live[i]) *reinterpret_cast<uint4 *>(orow[i] + c0) = make_uint4(w[i][0], w[i][1], w[i][2], w[i][3]);
+                            }
+                        }
+                    }
+                    first -= cps_mod;
+                    if (first < 0) first += kColGroups;
+                }
+            };
+            if (epi_g == 4) multi_tiles(std::integral_constant<int, 4>{});
+            else if (epi_g == 2) multi_tiles(std::integral_constant<int, 2>{});
+            for (int j = 0; j < nsub && epi_g == 1 && !(p.dbg_mode & 2); ++j) {
                 if (first < cps) {
                     const int tm = TWO ? tg * 2 + static_cast<int>(rank) : tg * p.group + j;
                     const int m = tm * kBM + row_in_tile;
@@ -1418,7 +1488,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     p.act_min = g.act_min; p.act_max = g.act_max; p.out_zp = g.out_zp;
     const int32_t extra = p.need_asum ? 16 : 0;
     int32_t max_data = kMaxBN - extra;
-    if (const char *ev = getenv("ENN_B200_TC_BN")) max_data = atoi(ev) >= 16 && atoi(ev) <= max_data ? (atoi(ev) & ~15) : max_data;   // tuning override
+    if (const char *ev = getenv("ENN_B200_TC_BN")) max_data = atoi(ev) >= 96 && atoi(ev) <= max_data ? (atoi(ev) & ~15) : max_data;   // tuning override
     p.tiles_m = (M + kBM - 1) / kBM;
     // N tiling: as few tiles as possible, but split further while the grid would leave SMs idle.
     int32_t tiles_n = (N + max_data - 1) / max_data;
@@ -1596,6 +1666,8 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     // One thread cannot issue both operands of every k-block fast enough for a long MMA-bound k loop; short, epilogue-
     // bound problems are better off without the extra warp.
     gm->threads = (p.kpack == 1 && p.k_blocks >= 8) ? kThreads : kThreadsOneProducer;
+    p.epi_g = p.two ? 1 : (p.group >= 4 ? 4 : (p.group >= 2 ? 2 : 1));
+    if (const char *ev = getenv("ENN_B200_EPI_G")) p.epi_g = atoi(ev) == 4 || atoi(ev) == 2 ? (atoi(ev) <= p.group ? atoi(ev) : p.epi_g) : 1;   // tuning override
     return ENN_B200_SUCCESS;
 }
 

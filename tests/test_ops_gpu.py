@@ -289,6 +289,11 @@ FC_CASES = {
     "pack_k16_n24_per_tensor": dict(m=4104, k=16, n=24, per_channel=False, w_zp=119),
     "pack_k64_n96_relu": dict(m=4098, k=64, n=96, act=cases.enn.ACT_RELU, out_zp=0, out_scale=0.004),
     "pack_k32_n48_mixed_shift": dict(m=4100, k=32, n=48, out_scale=0.0012),
+    # several M tiles requantised together per column: 3 tiles per unit taken 2 at a time (row-sum column, u8 weights),
+    # 4 at a time with a last unit of 3 tiles and a ragged last tile, 2 at a time with two N tiles
+    "group3_rowsum_k128_n64": dict(m=120000, k=128, n=64, per_channel=False, w_zp=119),
+    "group4_ragged_k128_n64": dict(m=128 * 4 * 300 + 128 * 2 + 5, k=128, n=64),
+    "group2_two_n_tiles_k256_n256_relu": dict(m=40000, k=256, n=256, act=cases.enn.ACT_RELU6, out_zp=0, out_scale=0.01),
     "pack_wide_k96_n24": dict(m=4104, k=96, n=24, act=cases.enn.ACT_NONE),
     "pack_wide_k144_n24_per_tensor": dict(m=4100, k=144, n=24, per_channel=False, w_zp=119, act=cases.enn.ACT_NONE),
     "pack_wide_k192_n32": dict(m=4098, k=192, n=32, act=cases.enn.ACT_NONE, out_scale=0.3),
