@@ -1864,7 +1864,11 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         // A channel count that is not a multiple of 16 (24) cannot be read in place at all (TMA row pitch); packed rows of
         // f * K bytes can, which removes the gather pass; several N tiles are accepted in that case.
         int32_t pack = 1;
-        if (pointwise && M64 >= 4096 && K <= 64 && !getenv("ENN_B200_NO_PACK")) {
+        // Not for layers with 96 or more output channels whose rows can be read in place: their time is the epilogue's, not
+        // the row fetches', and unpacked they keep two M tiles per work unit, which halves the epilogue's loads of the
+        // column constants (112 x 112 x 16 -> 96: 161 us packed, 152 us in place).
+        const bool epilogue_heavy = N >= 96 && (K & 15) == 0;
+        if (pointwise && M64 >= 4096 && K <= 64 && !epilogue_heavy && !getenv("ENN_B200_NO_PACK")) {
             const int32_t zw_eff = g.w_signed ? g.w_zp : g.w_zp - 128;
             for (int32_t f = 8; f >= 2 && pack == 1; f >>= 1) {
                 if (f * K > 128 || (f * K) % 16 != 0 || M64 % f != 0) continue;
