@@ -1039,6 +1039,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ------------------------------------------------------------------------------------------------------
 constexpr int kGemvMaxM = 8;
 constexpr int kGemvWarps = 8;
+constexpr int kGemvAhead = 8;       // 16-byte weight loads per lane issued before anything else
 
 template <bool A_SIGNED>
 __device__ __forceinline__ int32_t dp4a_as(uint32_t a, uint32_t w, int32_t c) {
@@ -1056,19 +1057,29 @@ gemv_kernel(const uint8_t *__restrict__ a, const int8_t *__restrict__ w, const C
             int N, int K, int k_pad, int bn_rows, int bn_data, int zw_eff, int out_zp, int act_min, int act_max) {
     extern __shared__ uint4 gemv_smem[];            // M rows of K bytes
     const int k16 = K >> 4;
-    for (int i = threadIdx.x; i < M * k16; i += blockDim.x) gemv_smem[i] = __ldg(reinterpret_cast<const uint4 *>(a) + i);
-    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * kGemvWarps + warp;
-    if (n >= N) return;
-    const int tn = n / bn_data, r = n - tn * bn_data;
+    const bool active = n < N;
+    const int tn = active ? n / bn_data : 0, r = active ? n - tn * bn_data : 0;
     const uint4 *wrow = reinterpret_cast<const uint4 *>(w + (static_cast<size_t>(tn) * bn_rows + r) * k_pad);
+    // The weights are the operator's constants: the first kGemvAhead 512-byte pieces of this warp's column (all of it up
+    // to K = 4096) are requested before the wait on the kernel that produces the activations and before the
+    // activations are staged, so that the whole weight stream is in flight from the first instruction on.
+    pdl_trigger();
+    uint4 wpre[kGemvAhead];
+#pragma unroll
+    for (int u = 0; u < kGemvAhead; ++u) {
+        const int i = lane + 32 * u;
+        wpre[u] = active && i < k16 ? __ldg(wrow + i) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    pdl_wait();
+    for (int i = threadIdx.x; i < M * k16; i += blockDim.x) gemv_smem[i] = __ldg(reinterpret_cast<const uint4 *>(a) + i);
+    __syncthreads();
+    if (!active) return;
     int32_t acc[M], asum[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[m] = asum[m] = 0;
-#pragma unroll 4
-    for (int i = lane; i < k16; i += 32) {
-        const uint4 wv = __ldg(wrow + i);
+    auto mac = [&](int i, const uint4 &wv) {
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             const uint4 av = gemv_smem[m * k16 + i];
@@ -1083,7 +1094,14 @@ gemv_kernel(const uint8_t *__restrict__ a, const int8_t *__restrict__ w, const C
                 asum[m] = dp4a_as<A_SIGNED>(av.w, 0x01010101u, asum[m]);
             }
         }
+    };
+#pragma unroll
+    for (int u = 0; u < kGemvAhead; ++u) {
+        const int i = lane + 32 * u;
+        if (i < k16) mac(i, wpre[u]);
     }
+#pragma unroll 4
+    for (int i = lane + 32 * kGemvAhead; i < k16; i += 32) mac(i, __ldg(wrow + i));
 #pragma unroll
     for (int m = 0; m < M; ++m)
 #pragma unroll
@@ -1107,9 +1125,9 @@ void launch_gemv(int M, const void *a, const void *w, const ColParam *cols, void
     const int blocks = (p.N + kGemvWarps - 1) / kGemvWarps;
     const size_t smem = static_cast<size_t>(M) * p.K;
 #define ENN_GEMV(MM)                                                                                                          \
-    gemv_kernel<A_SIGNED, MM><<<blocks, kGemvWarps * 32, smem, s>>>(static_cast<const uint8_t *>(a), static_cast<const int8_t *>(w), cols, \
-                                                                   static_cast<uint8_t *>(out), p.N, p.K, k_pad, p.bn_rows, p.bn_data,     \
-                                                                   p.zw_eff, p.out_zp, p.act_min, p.act_max)
+    launch_pdl(gemv_kernel<A_SIGNED, MM>, dim3(blocks), dim3(kGemvWarps * 32), smem, s, static_cast<const uint8_t *>(a),      \
+               static_cast<const int8_t *>(w), cols, static_cast<uint8_t *>(out), p.N, p.K, k_pad, p.bn_rows, p.bn_data, p.zw_eff,  \
+               p.out_zp, p.act_min, p.act_max)
     switch (M) {
         case 1: ENN_GEMV(1); break;
         case 2: ENN_GEMV(2); break;
