@@ -211,7 +211,6 @@ template <int STRIDE, bool W_SIGNED, bool NEED_ASUM, bool RELU>
 __global__ void __launch_bounds__(kDwThreads, 4)
 dw3x3_kernel(ConvGeom g, const DwChan *__restrict__ chan, const uint32_t *__restrict__ w_packed,
              const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int th, int nyt, int nstrip, int64_t total) {
-    pdl_wait();         // the tensors of the kernel before this one are complete from here on
     pdl_trigger();
     const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (tid >= total) return;
@@ -301,6 +300,9 @@ dw3x3_kernel(ConvGeom g, const DwChan *__restrict__ chan, const uint32_t *__rest
         orow += out_pitch;
     };
 
+    // Everything above read only the operator's own constants (weights, per-channel words) and overlaps the tail of the
+    // kernel before this one; its tensors are complete from here on.
+    pdl_wait();
     // Ring of three transposed rows; the loop is unrolled over the ring so no register copies are needed.
     // The raw loads of the next input row(s) are issued before the current output row is computed, so
     // their latency overlaps the dp4a / requantisation work.
