@@ -468,6 +468,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (TWO) cluster_sync_all();        // the peer's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Resident weights (the operator's only N tile: every k-block of B, once) are constants of the plan: their copy
+    // starts here, ahead of the wait below, and the MMA issuer picks it up on its barrier.
+    if (bres && threadIdx.x == 0) {
+        const uint32_t bb = tempty0 + 16;
+        mbar_expect_tx(bb, b_bytes * static_cast<uint32_t>(p.k_blocks));
+        for (int kb = 0; kb < p.k_blocks; ++kb) tma_load_2d(smem_u32(b_resident) + kb * b_stride, &map_b, bb, kb * static_cast<int>(span), 0);
+    }
     // Everything above touched only this launch's own resources and constants; the activations of the kernel before
     // this one are complete (and the tensor this one writes is no longer read) from here on.
     pdl_wait();
@@ -529,11 +536,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         } else if (!TWO && !split && bres && (nst & 1) == 0 && !(p.dbg_mode & 9)) {
             // Resident weights (implicit convolutions, narrow pointwise layers): only A tiles are left to load, and the copy
             // issue rate of one thread still bounds the kernel, so lanes 0 and 1 fill alternate stages (a stage keeps its lane).
-            if (lane == 0) {       // the operator's only N tile: every k-block of B, once
-                const uint32_t bb = tempty0 + 16;
-                mbar_expect_tx(bb, b_bytes * static_cast<uint32_t>(p.k_blocks));
-                for (int kb = 0; kb < p.k_blocks; ++kb) tma_load_2d(smem_u32(b_resident) + kb * b_stride, &map_b, bb, kb * static_cast<int>(span), 0);
-            }
             if (lane < 2) {
                 const uint32_t a_tx = p.taps > 0 ? static_cast<uint32_t>(p.conv_ht * p.conv_wt) * span : a_bytes;
                 const uint32_t sa0 = smem_u32(tiles);
@@ -608,12 +610,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 // bytes this producer's loads add to a k-block (pairs: of both CTAs, counted on rank 0's barrier)
                 const uint32_t a_tx = p.taps > 0 ? static_cast<uint32_t>(p.conv_ht * p.conv_wt) * span : a_bytes;
                 const uint32_t kb_tx = ((DO_A ? a_tx : 0u) + (DO_B && !bres ? b_bytes : 0u)) * (TWO ? 2u : 1u);
-                if (DO_B && bres) {       // the operator's only N tile: every k-block of B, once
-                    const uint32_t bb = tempty0 + 16;
-                    mbar_expect_tx(bb, b_bytes * static_cast<uint32_t>(p.k_blocks));
-                    for (int kb = 0; kb < p.k_blocks; ++kb)
-                        tma_load_2d(smem_u32(b_resident) + kb * b_stride, &map_b, bb, kb * static_cast<int>(span), 0);
-                }
                 bool ok = true;
                 long long t_wait = 0;
                 for (int tile = tile_first; tile < total_tiles && ok; tile += tile_step) {
