@@ -1658,7 +1658,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     // copy per ~420 cycles and a tile needs one A and one B copy per k-block): when the weights of the only N tile fit,
     // they are loaded once per CTA and stay resident, the stages hold A only, and the producer issues half as many copies.
     const size_t b_tile = (static_cast<size_t>(p.bn_rows) * span + 1023) & ~static_cast<size_t>(1023);
-    p.b_res = ((implicit_span != 0 || p.bn_rows <= 64 || want_resident) && !p.two && tiles_n == 1 && M > kGemvMaxM && b_tile * p.k_blocks <= (want_resident ? kWidePackWeightBytes : 72 * 1024) &&
+    p.b_res = ((implicit_span != 0 || p.bn_rows <= 64 || want_resident || (p.k_blocks == 1 && !getenv("ENN_B200_NO_BRES_K1"))) && !p.two && tiles_n == 1 && M > kGemvMaxM && b_tile * p.k_blocks <= (want_resident ? kWidePackWeightBytes : 72 * 1024) &&
                !getenv("ENN_B200_NO_BRES")) ? 1 : 0;
     const size_t kb_bytes = p.b_res ? static_cast<size_t>(kBM) * span : (static_cast<size_t>(kBM) + (p.two ? p.bn_rows / 2 : p.bn_rows)) * span;
     p.kpack = static_cast<int32_t>((32 * 1024) / kb_bytes);
