@@ -87,6 +87,7 @@ PROTOTYPES = {
     "enn_b200_host_free": (C.c_int32, [_P]),
     "enn_b200_last_error": (C.c_int32, [_P, C.c_char_p, C.c_size_t]),
     "enn_b200_stream": (_P, [_P]),
+    "enn_b200_context_set_option": (C.c_int32, [_P, C.c_char_p, C.c_int32]),
     "enn_b200_conv2d_prepare": (C.c_int32, [_P, C.POINTER(ConvDesc), _P, _P, _P, C.POINTER(_P)]),
     "enn_b200_depthwise_prepare": (C.c_int32, [_P, C.POINTER(ConvDesc), _P, _P, _P, C.POINTER(_P)]),
     "enn_b200_deconv_prepare": (C.c_int32, [_P, C.POINTER(ConvDesc), _P, _P, _P, C.POINTER(_P)]),
@@ -98,6 +99,8 @@ PROTOTYPES = {
     "enn_b200_op_execute2": (C.c_int32, [_P, _P, _P, _P]),
     "enn_b200_op_execute_noalloc": (C.c_int32, [_P, _P, _P]),
     "enn_b200_op_info": (C.c_int32, [_P, C.POINTER(OpInfo)]),
+    "enn_b200_op_test_starve_next": (C.c_int32, [_P]),
+    "enn_b200_op_clear_error": (C.c_int32, [_P]),
     "enn_b200_op_release": (C.c_int32, [_P]),
     "enn_b200_oplist_create": (C.c_int32, [_P, C.POINTER(_P)]),
     "enn_b200_oplist_add_tensor": (C.c_int32, [_P, C.c_int64, C.POINTER(C.c_int32)]),
@@ -203,6 +206,10 @@ class Context:
     def stream(self):
         return lib.enn_b200_stream(self.h)
 
+    def set_option(self, name, value):
+        """Planner override for operators prepared afterwards (tests and tuning)."""
+        self.check(lib.enn_b200_context_set_option(self.h, name.encode(), int(value)))
+
     def mma_peak(self, kind=0, n=256, iters=4096):
         """Measured tcgen05.mma rate in tera-ops/s (kind 0: int8, kind 1: bf16)."""
         v = C.c_double()
@@ -232,6 +239,12 @@ class Op:
 
     def execute2(self, a_dev, b_dev, out_dev):
         self.ctx.check(lib.enn_b200_op_execute2(self.h, a_dev, b_dev, out_dev))
+
+    def test_starve_next(self):
+        self.ctx.check(lib.enn_b200_op_test_starve_next(self.h))
+
+    def clear_error(self):
+        self.ctx.check(lib.enn_b200_op_clear_error(self.h))
 
     @property
     def out_shape(self):

@@ -92,10 +92,8 @@ void fill_info(enn_b200_op *op, int64_t in_elems, int64_t out_elems, int64_t mac
 
 namespace enn_b200 {
 
-bool pdl_enabled() {
-    static const bool on = getenv("ENN_B200_NO_PDL") == nullptr;
-    return on;
-}
+static bool g_pdl_on = true;     // process-wide; option "no_pdl" of any context turns it off
+bool pdl_enabled() { return g_pdl_on; }
 
 // mma_peak.cu
 double measure_mma_peak(enn_b200_context *ctx, int kind, int n, int iters);
@@ -104,6 +102,8 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *weights_hwio_host);
 int32_t tc_execute(enn_b200_op *op, const void *in, void *out);
 void tc_release(enn_b200_op *op);
 bool tc_available(const enn_b200_context *ctx);
+int32_t tc_test_starve_next(enn_b200_op *op);
+void tc_clear_error(enn_b200_op *op);
 }  // namespace enn_b200
 
 extern "C" {
@@ -207,6 +207,20 @@ int32_t enn_b200_last_error(enn_b200_context *ctx, char *buf, size_t buf_len) {
 
 void *enn_b200_stream(enn_b200_context *ctx) { return ctx ? static_cast<void *>(ctx->stream) : nullptr; }
 
+int32_t enn_b200_context_set_option(enn_b200_context *ctx, const char *name, int32_t value) {
+    if (!ctx || !name) return ENN_B200_INVALID_PARAMS;
+    static const char *const known[] = {"no_pdl", "no_relu_mode", "no_relu_hi", "no_first_layer", "no_implicit", "no_gemv",
+                                        "no_narrow_span", "no_pack", "pack_wide", "no_bres", "no_bres_k1", "no_fan_out", "tc_bn",
+                                        "tc_pair", "tc_raster", "epi_g", "dw_legacy", "no_fuse", "dw_rows"};
+    bool ok = false;
+    for (const char *k : known) ok = ok || std::strcmp(k, name) == 0;
+    if (!ok) return fail(ctx, ENN_B200_INVALID_PARAMS, std::string("unknown option: ") + name);
+    if (std::strcmp(name, "tc_bn") == 0 && value != 0 && value < 96) return fail(ctx, ENN_B200_INVALID_PARAMS, "tc_bn must be 0 or at least 96");
+    ctx->options[name] = value;
+    if (std::strcmp(name, "no_pdl") == 0) g_pdl_on = value == 0;
+    return ENN_B200_SUCCESS;
+}
+
 void enn_b200_quantize_multiplier(double real_multiplier, int32_t *quantized_multiplier, int32_t *shift) {
     quantize_multiplier(real_multiplier, quantized_multiplier, shift);
 }
@@ -222,6 +236,8 @@ void enn_b200_activation_range(int32_t activation, int32_t act_dtype, float scal
 
 int32_t enn_b200_measure_mma_peak(enn_b200_context *ctx, int32_t kind, int32_t n, int32_t iters, double *tera_ops) {
     if (!ctx || !tera_ops) return ENN_B200_INVALID_PARAMS;
+    // 2^16 groups keep every SM busy for a few milliseconds; more would hold a shared GPU for no better figure.
+    if (iters < 1 || iters > (1 << 16)) return fail(ctx, ENN_B200_INVALID_PARAMS, "iters must be within 1 .. 65536");
     const double v = measure_mma_peak(ctx, kind, n, iters);
     if (v < 0) return fail(ctx, ENN_B200_FAILURE, "tensor-pipe peak measurement failed");
     *tera_ops = v;
@@ -363,7 +379,7 @@ static int32_t conv_like_prepare(enn_b200_context *ctx, const enn_b200_conv_desc
             chan[c * 4 + 3] = static_cast<int32_t>(folded);
         }
         // ReLU-type output (lower clamp == output zero point) with right shifts only: merged one-shift form.
-        bool relu = ok && g.out_zp == g.act_min && !getenv("ENN_B200_DW_TMA") && !getenv("ENN_B200_NO_RELU_MODE");
+        bool relu = ok && g.out_zp == g.act_min && !ctx->opt("no_relu_mode");
         for (int32_t c = 0; c < cout && relu; ++c)
             if ((chan[c * 4 + 2] & 0xff) < 1 || chan[c * 4 + 0] < 0) relu = false;
         if (relu) {
@@ -386,9 +402,8 @@ static int32_t conv_like_prepare(enn_b200_context *ctx, const enn_b200_conv_desc
             }
             op->dw_chan = dc;
             op->dw_w = dwp;
-            // TMA-staged variant (C % 16 == 0).  Measured on B200 it does not beat the register-streamed kernel (the
-            // depthwise path is bound by integer issue, not by load latency), so it is opt-in for experiments.
-            if (getenv("ENN_B200_DW_TMA")) dw_tma_plan(op);
+            // Row-ring variant (C % 16 == 0): input rows staged in shared memory by bulk copies; the default where it applies.
+            dw_ring_plan(op);
         }
     }
     if (kind != OP_DEPTHWISE && tc_available(ctx)) {
@@ -582,12 +597,14 @@ int32_t enn_b200_op_execute(enn_b200_op *op, const void *in, void *out) {
             e = launch_deconv_direct(op->g, op->rq, in, op->w_direct, out, ctx->stream);
             break;
         case OP_DEPTHWISE:
-            if (op->dw_tma && op->impl == ENN_B200_IMPL_DEPTHWISE) {
-                e = dw_tma_launch(op, in, out);
+            if (op->dw_ring && op->impl == ENN_B200_IMPL_DEPTHWISE) {
+                e = dw_ring_launch(op, in, out);
                 if (e == cudaErrorLaunchFailure) return fail(ctx, ENN_B200_CUDA_FAILURE, "depthwise kernel gave up on a barrier wait earlier");
                 if (e != cudaErrorNotSupported) break;
             }
-            if (op->dw_chan && op->impl == ENN_B200_IMPL_DEPTHWISE) {
+            // The register-streamed kernel reads and writes 32-bit words: other alignments take the general kernel.
+            if (op->dw_chan && op->impl == ENN_B200_IMPL_DEPTHWISE &&
+                ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 3) == 0) {
                 e = launch_dw3x3(op->g, op->dw_chan, op->dw_relu, op->dw_w, in, out, ctx->sm_count, ctx->stream);
                 break;
             }
@@ -618,11 +635,25 @@ int32_t enn_b200_op_info(const enn_b200_op *op, enn_b200_op_info_t *info) {
     return ENN_B200_SUCCESS;
 }
 
+int32_t enn_b200_op_test_starve_next(enn_b200_op *op) {
+    if (!op) return ENN_B200_INVALID_PARAMS;
+    if (op->impl != ENN_B200_IMPL_TCGEN05 || !op->tc) return fail(op->ctx, ENN_B200_INVALID_PARAMS, "the self-test needs an operator on the tensor-core kernel");
+    return tc_test_starve_next(op) == ENN_B200_SUCCESS ? ENN_B200_SUCCESS
+                                                       : fail(op->ctx, ENN_B200_INVALID_PARAMS, "this plan has no starved form (GEMV, first layer or CTA pairs)");
+}
+
+int32_t enn_b200_op_clear_error(enn_b200_op *op) {
+    if (!op) return ENN_B200_INVALID_PARAMS;
+    if (op->tc) tc_clear_error(op);
+    if (op->dw_ring) dw_ring_clear_error(op);
+    return ENN_B200_SUCCESS;
+}
+
 int32_t enn_b200_op_release(enn_b200_op *op) {
     if (!op) return ENN_B200_INVALID_PARAMS;
     if (op->ctx) cudaSetDevice(op->ctx->device);
     if (op->tc) tc_release(op);
-    if (op->dw_tma) dw_tma_release(op);
+    if (op->dw_ring) dw_ring_release(op);
     for (void *p : op->owned) cudaFree(p);
     delete op;
     return ENN_B200_SUCCESS;

@@ -356,29 +356,6 @@ dw3x3_kernel(ConvGeom g, const DwChan *__restrict__ chan, const uint32_t *__rest
     }
 }
 
-// ------------------------------------------------------------------------------------------------------
-// 3x3 fast path with TMA-staged input tiles (C % 16 == 0).
-//
-// A persistent CTA walks tiles of TH x (4 * NS) output pixels x CT channels.  The input window of a tile
-// (with its one-pixel halo) is fetched by ONE 4-D tensor-map copy into shared memory, double buffered, so the
-// copy of tile i+1 runs while tile i is computed; out-of-image positions arrive as zeros and are overwritten
-// with the input zero point before use.  Threads then run the same transposed-row / dp4a / fused requantisation
-// code as dw3x3_kernel, but every load is a shared-memory load at a compile-time offset: no per-load address
-// arithmetic, no border predicates, no global-load latency in the math loop.
-// Thread = (channel quad, strip of 4 output columns, row group); a row group owns R consecutive output rows.
-// ------------------------------------------------------------------------------------------------------
-struct DwTmaParams {
-    int32_t n, h, w, c, oh, ow, pt, pl;
-    int32_t ns, rg, r;            // strips per tile, row groups per tile, output rows per row group
-    int32_t th, wt;               // output rows / columns per tile (rg * r, 4 * ns)
-    int32_t win, hin;             // input window per tile (box extents in W and H)
-    int32_t tiles_x, tiles_y, cblks, total_tiles;
-    int32_t in_zp, w_zp, act_min, act_max;
-    uint32_t tile_bytes;          // bytes one tensor-map copy delivers (win * hin * CT)
-    uint32_t buf_pitch;           // distance between the two shared-memory buffers (tile_bytes rounded up to 128)
-    int32_t *err;                 // host-mapped error word
-};
-
 __device__ __forceinline__ uint32_t dw_smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ uint32_t dw_lds32(uint32_t addr) {
     uint32_t v;
@@ -386,183 +363,301 @@ __device__ __forceinline__ uint32_t dw_lds32(uint32_t addr) {
     return v;
 }
 
-template <int STRIDE, int CT, bool W_SIGNED, bool NEED_ASUM>
-__global__ void __launch_bounds__(256, 2)
-dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, DwTmaParams p, const DwChan *__restrict__ chan,
-                 const uint32_t *__restrict__ w_packed, uint8_t *__restrict__ out) {
-    extern __shared__ uint8_t dw_smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dw_smem_raw) + 127) & ~static_cast<uintptr_t>(127));
-    __shared__ uint64_t full_bar[2];
-    __shared__ int s_ok;
-    constexpr int QN = CT / 4;
+// ------------------------------------------------------------------------------------------------------
+// 3x3 fast path, row-ring form (C % 16 == 0, at most 224 channel quads): the default for the MobileNetV2-style layers.
+//
+// The register-streamed kernel above keeps about 12 KB of loads in flight per SM, a third of what the HBM latency
+// needs, and spends instructions on per-load predicates and addresses.  Here the input reaches shared memory through
+// the bulk-copy engine instead: a CTA owns one x tile (4 * ns output columns, all C channels) and a contiguous range
+// of output rows; a producer thread streams the input rows of that tile into a ring of row slots with one
+// `cp.async.bulk` per row (the (4 ns - 1) s + 3 pixels of a row are contiguous in NHWC because the tile spans all
+// channels), up to the whole ring ahead of the consumers, so tens of KB per SM are in flight whatever the register
+// budget.  Consumer threads (4 channels x 4 output pixels each, as above) wait on the slot's mbarrier, read their six
+// (stride 1) or nine (stride 2) words with shared-memory loads at fixed offsets, release the slot as soon as the row
+// sits transposed in registers, and run the same dp4a / fused requantisation code.  No border predicate is left in
+// the loop: pixels left and right of the image are slot positions that no copy ever writes and that hold the input
+// zero point from the start (a CTA keeps its x tile for its whole life), rows above and below the image are read
+// from a constant row of zero points.
+// Every wait is bounded; a thread that gives up records a code, raises the CTA's abort flag and all roles leave.
+// ------------------------------------------------------------------------------------------------------
+struct DwRingParams {
+    int32_t n, h, w, c, oh, ow, pt, pl;
+    int32_t q;              // channel quads per pixel (C / 4)
+    int32_t ns;             // strips of 4 output columns per x tile
+    int32_t tx_n;           // x tiles per row
+    int32_t ctas_per_tx;    // CTAs that share the rows of one x tile (grid = tx_n * ctas_per_tx)
+    int32_t slot_px;        // pixels per ring slot: (4 ns - 1) s + 3
+    int32_t nr;             // ring slots
+    uint32_t pitch;         // bytes per slot (multiple of 128)
+    int32_t in_zp, w_zp, act_min, act_max;
+    int32_t *err;           // host-mapped error word
+};
+
+constexpr int kDwRingConsumers = 224;                   // consumer threads per CTA at most (7 warps)
+constexpr int kDwRingThreads = kDwRingConsumers + 32;   // + the producer warp
+constexpr uint32_t kDwSpinLimit = 1u << 22;
+
+__device__ __forceinline__ bool dw_mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; false after the limit or once another thread has raised the abort flag.
+__device__ __forceinline__ bool dw_mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *err, int code) {
+    for (uint32_t i = 0; i < kDwSpinLimit; ++i) {
+        if (dw_mbar_try(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (err) *reinterpret_cast<volatile int32_t *>(err) = code;
+    return false;
+}
+
+template <int STRIDE, bool W_SIGNED, bool NEED_ASUM, bool RELU>
+__global__ void __launch_bounds__(kDwRingThreads, 2)
+dw3x3_ring_kernel(const DwRingParams p, const DwChan *__restrict__ chan, const uint32_t *__restrict__ w_packed,
+                  const uint8_t *__restrict__ in, uint8_t *__restrict__ out) {
+    extern __shared__ uint8_t dw_ring_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dw_ring_raw) + 127) & ~static_cast<uintptr_t>(127));
     constexpr int NP = STRIDE == 1 ? 6 : 9;
-    const int tid = threadIdx.x;
-    const int cq = tid % QN;
-    const int strip = (tid / QN) % p.ns;
-    const int rgi = tid / (QN * p.ns);
-    const uint32_t buf0 = dw_smem_u32(smem);
-    const uint32_t bar0 = dw_smem_u32(&full_bar[0]);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int ncw = (static_cast<int>(blockDim.x) >> 5) - 1;        // consumer warps; the last warp produces
+    const uint32_t zrow = dw_smem_u32(smem);                        // constant row of input zero points
+    const uint32_t ring = zrow + p.pitch;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + static_cast<size_t>(p.nr + 1) * p.pitch);
+    const uint32_t full0 = dw_smem_u32(bars), empty0 = full0 + 8u * p.nr;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * p.nr);
+    pdl_trigger();
     if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + 8) : "memory");
+        for (int i = 0; i < p.nr; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full0 + 8 * i) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty0 + 8 * i), "r"(ncw) : "memory");
+        }
+        *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const uint32_t zaw = (static_cast<uint32_t>(p.in_zp) & 0xff) * 0x01010101u;
+    {   // every slot and the constant row start as zero points; copies later overwrite the in-image pixels only
+        const uint32_t n16 = (static_cast<uint32_t>(p.nr) + 1u) * (p.pitch >> 4);
+        for (uint32_t i = tid; i < n16; i += blockDim.x)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(zrow + i * 16), "r"(zaw) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // ordered before the bulk copies into the same bytes
     }
     __syncthreads();
 
-    auto tile_coords = [&](int tile, int &cb, int &img, int &ty, int &tx) {
-        tx = tile % p.tiles_x;
-        int t = tile / p.tiles_x;
-        ty = t % p.tiles_y;
-        t /= p.tiles_y;
-        img = t % p.n;
-        cb = t / p.n;              // channel block is the slowest index: a CTA keeps its weights for many tiles
-    };
-    auto issue = [&](int tile, int buf) {
-        int cb, img, ty, tx;
-        tile_coords(tile, cb, img, ty, tx);
-        const uint32_t bar = bar0 + 8 * buf;
-        const uint32_t dst = buf0 + buf * p.buf_pitch;
-        const int x = tx * p.wt * STRIDE - p.pl, y = ty * p.th * STRIDE - p.pt;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(p.tile_bytes) : "memory");
-        asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-                     ::"r"(dst), "l"(&map_in), "r"(bar), "r"(cb * CT), "r"(x), "r"(y), "r"(img)
-                     : "memory");
-    };
+    // This CTA: x tile `tx`, output rows [u0, u1) of the N * OH rows of that tile column (row u = image * OH + oy).
+    const int tx = static_cast<int>(blockIdx.x) / p.ctas_per_tx, part = static_cast<int>(blockIdx.x) - tx * p.ctas_per_tx;
+    const int64_t units = static_cast<int64_t>(p.n) * p.oh;
+    const int u0 = static_cast<int>(units * part / p.ctas_per_tx), u1 = static_cast<int>(units * (part + 1) / p.ctas_per_tx);
+    const int ox0 = tx * p.ns * 4;
+    const int ix_start = ox0 * STRIDE - p.pl;
+    const int ix_lo = ix_start < 0 ? 0 : ix_start;
+    const int ix_hi = ix_start + p.slot_px < p.w ? ix_start + p.slot_px : p.w;
 
-    uint32_t wlo[3][4], whi[3][4];
+    if (warp == ncw) {
+        // ---------------- producer: one bulk copy per in-image input row, in the order the consumers take them ----------------
+        if (lane == 0 && ix_hi > ix_lo) {
+            pdl_wait();         // the input tensor is complete from here on
+            const uint32_t bytes = static_cast<uint32_t>(ix_hi - ix_lo) * p.c;
+            const uint32_t dst_off = static_cast<uint32_t>(ix_lo - ix_start) * p.c;
+            const int64_t row_bytes = static_cast<int64_t>(p.w) * p.c;
+            uint32_t slot = 0, phase = 0;
+            bool ok = true;
+            for (int u = u0; u < u1 && ok;) {
+                const int img = u / p.oh, oy0 = u - img * p.oh;
+                const int cnt = min(p.oh - oy0, u1 - u);
+                int iy_a = oy0 * STRIDE - p.pt, iy_b = (oy0 + cnt - 1) * STRIDE - p.pt + 2;
+                iy_a = iy_a < 0 ? 0 : iy_a;
+                iy_b = iy_b > p.h - 1 ? p.h - 1 : iy_b;
+                const uint8_t *src = in + (static_cast<int64_t>(img) * p.h + iy_a) * row_bytes + static_cast<int64_t>(ix_lo) * p.c;
+                for (int iy = iy_a; iy <= iy_b; ++iy, src += row_bytes) {
+                    if (!dw_mbar_try(empty0 + 8 * slot, phase ^ 1) && !dw_mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag, p.err, 11)) { ok = false; break; }
+                    const uint32_t bar = full0 + 8 * slot;
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(ring + slot * p.pitch + dst_off), "l"(src), "r"(bytes), "r"(bar) : "memory");
+                    if (++slot == static_cast<uint32_t>(p.nr)) { slot = 0; phase ^= 1; }
+                }
+                u += cnt;
+            }
+            if (!ok) {      // copies still in flight get a bounded chance to land before the shared memory is given back
+                for (int s2 = 0; s2 < p.nr; ++s2)
+                    for (uint32_t i = 0; i < (1u << 16); ++i)
+                        if (dw_mbar_try(full0 + 8 * s2, 0) || dw_mbar_try(full0 + 8 * s2, 1)) break;
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    const int nthr = p.ns * p.q;                      // real tasks; the last warp's surplus lanes shadow the last task
+    const int task = tid < nthr ? tid : nthr - 1;
+    const int strip = task / p.q, cq = task - strip * p.q;
+    uint32_t wlo[3][4], whi[STRIDE == 1 ? 3 : 1][4];
     int32_t mult[4], addend[4], esh[4], bias[4];
-    int loaded_cb = -1;
-    const uint32_t zaw = (static_cast<uint32_t>(p.in_zp) & 0xff) * 0x01010101u;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int4 ch = __ldg(reinterpret_cast<const int4 *>(chan) + cq * 4 + c);
+        if (RELU) {
+            mult[c] = ch.z; addend[c] = ch.x; esh[c] = ch.w; bias[c] = ch.y;    // M0, C low, e - 1, C high
+        } else {
+            mult[c] = ch.x; addend[c] = ch.y; esh[c] = ch.z; bias[c] = ch.w;
+        }
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky) {
+            wlo[ky][c] = __ldg(w_packed + (cq * 4 + c) * 3 + ky);
+            if (STRIDE == 1) whi[ky][c] = wlo[ky][c] << 8;
+        }
+    }
+    const uint32_t cpix = static_cast<uint32_t>(p.c);
+    const uint32_t toff = static_cast<uint32_t>(strip * 4 * STRIDE) * cpix + static_cast<uint32_t>(cq) * 4;
     const int32_t hi_clamp = p.act_max - p.act_min;
     const uint32_t lo_word = (static_cast<uint32_t>(p.act_min) & 0xff) * 0x01010101u;
-    const uint32_t row_pitch = static_cast<uint32_t>(p.win) * CT;
-
-    int it = 0;
-    if (tid == 0 && static_cast<int>(blockIdx.x) < p.total_tiles) issue(blockIdx.x, 0);
-    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
-        const int buf = it & 1;
-        int cb, img, ty, tx;
-        tile_coords(tile, cb, img, ty, tx);
-        // Prefetch the next tile into the other buffer (its last readers finished before the barrier that ended
-        // the previous iteration), then wait, bounded, for this tile.
-        if (tid == 0) {
-            const int next = tile + gridDim.x;
-            if (next < p.total_tiles) issue(next, buf ^ 1);
-            const uint32_t bar = bar0 + 8 * buf, parity = (it >> 1) & 1;
-            int ok = 0;
-            for (uint32_t i = 0; i < (1u << 24) && !ok; ++i) {
-                uint32_t done;
-                asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-                             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-                ok = done != 0;
-            }
-            if (!ok && p.err) *reinterpret_cast<volatile int32_t *>(p.err) = 7;
-            s_ok = ok;
-        }
-        __syncthreads();
-        if (!s_ok) break;            // uniform: every thread reads the same flag
-        {   // every thread observes the completed phase itself before touching the tile
-            uint32_t done;
-            asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-                         : "=r"(done) : "r"(bar0 + 8 * buf), "r"((it >> 1) & 1) : "memory");
-            (void)done;
-        }
-        const uint32_t tbase = buf0 + buf * p.buf_pitch;
-        const int ix0 = tx * p.wt * STRIDE - p.pl, iy0 = ty * p.th * STRIDE - p.pt;
-        // Zero-filled positions outside the image become the input zero point (what the reference's pad kernel writes).
-        if (zaw != 0 && (ix0 < 0 || iy0 < 0 || ix0 + p.win > p.w || iy0 + p.hin > p.h)) {
-            for (int px = tid; px < p.win * p.hin; px += 256) {
-                const int ry = px / p.win, rx = px - ry * p.win;
-                if (iy0 + ry < 0 || iy0 + ry >= p.h || ix0 + rx < 0 || ix0 + rx >= p.w) {
-                    const uint32_t a = tbase + static_cast<uint32_t>(px) * CT;
+    uint32_t omask = 0;
 #pragma unroll
-                    for (int k = 0; k < CT; k += 16)
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(a + k), "r"(zaw) : "memory");
-                }
-            }
-            __syncthreads();
+    for (int j = 0; j < 4; ++j)
+        if (tid < nthr && ox0 + strip * 4 + j < p.ow) omask |= 1u << j;
+    const uint32_t out_pitch = static_cast<uint32_t>(p.ow) * cpix;
+    const int32_t zero4[4] = {0, 0, 0, 0};
+
+    uint32_t slot_a = 0, phase_a = 0;       // next slot to take a row from
+    uint32_t slot_r = 0;                    // next slot to hand back
+    bool ok = true;
+    uint8_t *orow = out;
+
+    // Reads this thread's words of input row iy (from its ring slot, or from the constant row outside the image).
+    auto issue = [&](DwRaw<STRIDE> &raw, int iy) {
+        uint32_t base = zrow;
+        if (static_cast<unsigned>(iy) < static_cast<unsigned>(p.h)) {
+            // Every lane looks once (the usual case: the row landed long ago); otherwise the lanes wait, bounded, and
+            // agree on the outcome, so that a warp always leaves the row loop as a whole.
+            const uint32_t bar = full0 + 8 * slot_a;
+            if (!__all_sync(0xffffffffu, dw_mbar_try(bar, phase_a)))
+                ok = __all_sync(0xffffffffu, dw_mbar_wait(bar, phase_a, abort_flag, p.err, 12));
+            base = ring + slot_a * p.pitch;
+            if (++slot_a == static_cast<uint32_t>(p.nr)) { slot_a = 0; phase_a ^= 1; }
         }
-        if (cb != loaded_cb) {
-            loaded_cb = cb;
+        base += toff;
+#pragma unroll
+        for (int i = 0; i < NP; ++i) raw.p[i] = dw_lds32(base + static_cast<uint32_t>(i) * cpix);
+    };
+    // Hands the slot of input row iy back to the producer; the row's words are in registers by now.
+    auto release = [&](int iy) {
+        if (static_cast<unsigned>(iy) < static_cast<unsigned>(p.h)) {
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * slot_r) : "memory");
+            if (++slot_r == static_cast<uint32_t>(p.nr)) slot_r = 0;
+        }
+    };
+    auto emit = [&](const DwRow<STRIDE> &r0, const DwRow<STRIDE> &r1, const DwRow<STRIDE> &r2) {
+        int32_t acc[4][4];
+        int32_t asum[NEED_ASUM ? 4 : 1][4];
+        if constexpr (RELU) dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, true>(acc, asum, r0, wlo[0], whi[0], zero4);
+        else dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, true>(acc, asum, r0, wlo[0], whi[0], bias);
+        dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r1, wlo[1], whi[STRIDE == 1 ? 1 : 0], bias);
+        dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r2, wlo[2], whi[STRIDE == 1 ? 2 : 0], bias);
+        uint32_t word[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int32_t y[4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const int ch = cb * CT + cq * 4 + c;
-                const DwChan v = chan[ch];
-                mult[c] = v.mult; addend[c] = v.addend; esh[c] = v.e; bias[c] = v.bias;
-#pragma unroll
-                for (int ky = 0; ky < 3; ++ky) {
-                    wlo[ky][c] = w_packed[ch * 3 + ky];
-                    whi[ky][c] = wlo[ky][c] << 8;
+                int32_t a = acc[c][j];
+                if (NEED_ASUM) a -= p.w_zp * asum[c][j];
+                int32_t v;
+                if (RELU) {
+                    int64_t cc;
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(cc) : "r"(addend[c]), "r"(bias[c]));
+                    const int64_t qv = static_cast<int64_t>(a) * mult[c] + cc;
+                    v = static_cast<int32_t>(qv >> 32) >> esh[c];
+                } else {
+                    const int64_t pr = static_cast<int64_t>(a) * mult[c] + (1ll << 30);
+                    const int32_t x = static_cast<int32_t>(pr >> 31);
+                    v = (x + addend[c] - static_cast<int32_t>(shr_clamp(static_cast<uint32_t>(x), esh[c] >> 8))) >> (esh[c] & 0xff);
                 }
+                y[c] = __vimin_s32_relu(v, hi_clamp);
             }
+            const uint32_t hi = pack_sat_u8(y[3], y[2], 0);
+            word[j] = pack_sat_u8(y[1], y[0], hi) + lo_word;      // u8 outputs: byte + act_min <= act_max, no carry between bytes
         }
-        // This thread: output rows oy0 .. oy0 + r - 1 of the tile, columns ox0 .. ox0 + 3, channels cb*CT + cq*4 ..
-        const int oy0 = ty * p.th + rgi * p.r;
-        const int ox0 = tx * p.wt + strip * 4;
-        const int rows = min(p.r, p.oh - oy0);
-        if (rows > 0 && ox0 < p.ow) {
-            uint32_t omask = 0;
+        if (omask == 15u) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint32_t *>(orow + static_cast<uint32_t>(j) * cpix) = word[j];
+        } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                if (ox0 + j < p.ow) omask |= 1u << j;
-            // shared address of (local input row rgi*r*STRIDE, local pixel strip*4*STRIDE, channel quad)
-            uint32_t srow = tbase + (static_cast<uint32_t>(rgi * p.r * STRIDE) * p.win + static_cast<uint32_t>(strip * 4 * STRIDE)) * CT + cq * 4;
-            uint8_t *orow = out + ((static_cast<int64_t>(img) * p.oh + oy0) * p.ow + ox0) * static_cast<int64_t>(p.c) + cb * CT + cq * 4;
-            const uint32_t out_pitch = static_cast<uint32_t>(p.ow) * p.c;
-            const uint32_t cpix = static_cast<uint32_t>(p.c);
+                if (omask & (1u << j)) *reinterpret_cast<uint32_t *>(orow + static_cast<uint32_t>(j) * cpix) = word[j];
+        }
+        orow += out_pitch;
+    };
 
-            auto load_row = [&](DwRow<STRIDE> &r) {
-                DwRaw<STRIDE> raw;
-#pragma unroll
-                for (int i = 0; i < NP; ++i) raw.p[i] = dw_lds32(srow + i * CT);
-                srow += row_pitch;
-                dw_transpose_row<STRIDE>(r, raw);
-            };
-            auto emit = [&](const DwRow<STRIDE> &r0, const DwRow<STRIDE> &r1, const DwRow<STRIDE> &r2) {
-                int32_t acc[4][4];
-                int32_t asum[NEED_ASUM ? 4 : 1][4];
-                dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, true>(acc, asum, r0, wlo[0], whi[0], bias);
-                dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r1, wlo[1], whi[1], bias);
-                dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r2, wlo[2], whi[2], bias);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    int32_t y[4];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        int32_t a = acc[c][j];
-                        if (NEED_ASUM) a -= p.w_zp * asum[c][j];
-                        const int64_t pr = static_cast<int64_t>(a) * mult[c] + (1ll << 30);
-                        const int32_t x = static_cast<int32_t>(pr >> 31);
-                        const int32_t v = (x + addend[c] - static_cast<int32_t>(shr_clamp(static_cast<uint32_t>(x), esh[c] >> 8))) >> (esh[c] & 0xff);
-                        y[c] = __vimin_s32_relu(v, hi_clamp);
-                    }
-                    if (omask & (1u << j)) {
-                        const uint32_t hi = pack_sat_u8(y[3], y[2], 0);
-                        *reinterpret_cast<uint32_t *>(orow + static_cast<uint32_t>(j) * cpix) = pack_sat_u8(y[1], y[0], hi) + lo_word;
-                    }
+    pdl_wait();     // the tensor this kernel writes is no longer read by the kernel before it
+    for (int u = u0; u < u1 && ok;) {
+        const int img = u / p.oh, oy0 = u - img * p.oh;
+        const int cnt = min(p.oh - oy0, u1 - u);
+        u += cnt;
+        orow = out + ((static_cast<int64_t>(img) * p.oh + oy0) * p.ow + ox0 + strip * 4) * static_cast<int64_t>(cpix) + cq * 4;
+        const int iy0 = oy0 * STRIDE - p.pt;
+        DwRow<STRIDE> ra, rb, rc;
+        if constexpr (STRIDE == 1) {
+            DwRaw<STRIDE> nx;
+            issue(nx, iy0);
+            dw_transpose_row<STRIDE>(ra, nx);
+            release(iy0);
+            issue(nx, iy0 + 1);
+            dw_transpose_row<STRIDE>(rb, nx);
+            release(iy0 + 1);
+            issue(nx, iy0 + 2);
+            for (int r = 0; r < cnt && ok; r += 3) {
+                dw_transpose_row<STRIDE>(rc, nx);
+                release(iy0 + 2 + r);
+                if (r + 1 < cnt) issue(nx, iy0 + 3 + r);
+                emit(ra, rb, rc);
+                if (r + 1 < cnt) {
+                    dw_transpose_row<STRIDE>(ra, nx);
+                    release(iy0 + 3 + r);
+                    if (r + 2 < cnt) issue(nx, iy0 + 4 + r);
+                    emit(rb, rc, ra);
                 }
-                orow += out_pitch;
-            };
-            DwRow<STRIDE> ra, rb, rc;
-            load_row(ra);
-            if constexpr (STRIDE == 1) {
-                load_row(rb);
-                for (int oy = 0; oy < rows; oy += 3) {
-                    load_row(rc);
-                    emit(ra, rb, rc);
-                    if (oy + 1 < rows) { load_row(ra); emit(rb, rc, ra); }
-                    if (oy + 2 < rows) { load_row(rb); emit(rc, ra, rb); }
+                if (r + 2 < cnt) {
+                    dw_transpose_row<STRIDE>(rb, nx);
+                    release(iy0 + 4 + r);
+                    if (r + 3 < cnt) issue(nx, iy0 + 5 + r);
+                    emit(rc, ra, rb);
                 }
-            } else {
-                for (int oy = 0; oy < rows; oy += 2) {
-                    load_row(rb);
-                    load_row(rc);
-                    emit(ra, rb, rc);
-                    if (oy + 1 < rows) { load_row(rb); load_row(ra); emit(rc, rb, ra); }
+            }
+        } else {
+            DwRaw<STRIDE> n1, n2;
+            issue(n1, iy0);
+            dw_transpose_row<STRIDE>(ra, n1);
+            release(iy0);
+            issue(n1, iy0 + 1);
+            issue(n2, iy0 + 2);
+            for (int r = 0; r < cnt && ok; r += 2) {
+                const int iy = iy0 + 2 * r;
+                dw_transpose_row<STRIDE>(rb, n1);
+                release(iy + 1);
+                dw_transpose_row<STRIDE>(rc, n2);
+                release(iy + 2);
+                if (r + 1 < cnt) {
+                    issue(n1, iy + 3);
+                    issue(n2, iy + 4);
+                }
+                emit(ra, rb, rc);
+                if (r + 1 < cnt) {
+                    dw_transpose_row<STRIDE>(rb, n1);
+                    release(iy + 3);
+                    dw_transpose_row<STRIDE>(ra, n2);
+                    release(iy + 4);
+                    if (r + 2 < cnt) {
+                        issue(n1, iy + 5);
+                        issue(n2, iy + 6);
+                    }
+                    emit(rc, rb, ra);
                 }
             }
         }
-        __syncthreads();             // all reads of this buffer are done before it is refilled two tiles later
     }
 }
 
@@ -571,64 +666,55 @@ bool dw3x3_eligible(const ConvGeom &g) {
            (g.cin % 4) == 0 && !g.a_signed;
 }
 
-typedef CUresult (*DwEncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-struct DwTmaPlan {
-    DwTmaParams prm{};
-    int ct = 0;
-    int grid = 0;
+// Launch shape of the row-ring kernel for one geometry.
+struct DwRingPlan {
+    DwRingParams prm{};
+    int grid = 0, threads = 0;
     size_t smem = 0;
-    CUtensorMap map{};
-    const void *map_ptr = nullptr;
-    int32_t *err_host = nullptr;
+    int32_t *err_host = nullptr;       // pinned + mapped
     int32_t *err_dev = nullptr;
 };
 
-// Chooses the tile shape; returns false when the geometry is outside this kernel's domain.
-bool dw_tma_plan(enn_b200_op *op) {
+// Chooses tile width, ring depth and grid; returns false when the geometry is outside the kernel's domain.
+bool dw_ring_plan(enn_b200_op *op) {
     const ConvGeom &g = op->g;
     enn_b200_context *ctx = op->ctx;
-    if (!dw3x3_eligible(g) || (g.cin & 15) != 0 || !ctx->encode_tiled || ctx->cc_major != 10 || !op->dw_chan) return false;
-    if (g.n <= 0) return false;
-    DwTmaPlan *pl = new (std::nothrow) DwTmaPlan();
+    if (!dw3x3_eligible(g) || (g.cin & 15) != 0 || !op->dw_chan || ctx->cc_major < 9 || ctx->opt("dw_legacy")) return false;
+    const int q = g.cin / 4, s = g.sh;
+    if (q > kDwRingConsumers || g.n <= 0) return false;
+    const int strips = (g.ow + 3) / 4;
+    int ns_max = kDwRingConsumers / q;
+    if (ns_max > strips) ns_max = strips;
+    const int tx_n = (strips + ns_max - 1) / ns_max;
+    const int ns = (strips + tx_n - 1) / tx_n;
+    DwRingPlan *pl = new (std::nothrow) DwRingPlan();
     if (!pl) return false;
-    DwTmaParams &p = pl->prm;
-    const int s = g.sh;
-    pl->ct = (g.cin % 64 == 0) ? 64 : ((g.cin % 32 == 0) ? 32 : 16);
-    const int qn = pl->ct / 4;
-    int ns = 1;
-    while (ns < 8 && ns * 4 < g.ow) ns *= 2;
-    while (qn * ns > 256) ns /= 2;
-    const int rg = 256 / (qn * ns);
-    int r = (g.oh + rg - 1) / rg;
-    if (r > 8) r = 8;
-    if (r < 1) r = 1;
-    auto bytes_for = [&](int rr) {
-        const int th = rg * rr, wt = 4 * ns;
-        return static_cast<size_t>(wt * s + 3 - s) * (th * s + 3 - s) * pl->ct;
-    };
-    while (r > 1 && bytes_for(r) > 48 * 1024) --r;
-    if (bytes_for(r) > 100 * 1024) {
-        delete pl;
-        return false;
-    }
+    DwRingParams &p = pl->prm;
     p.n = g.n; p.h = g.h; p.w = g.w; p.c = g.cin; p.oh = g.oh; p.ow = g.ow; p.pt = g.pt; p.pl = g.pl;
-    p.ns = ns; p.rg = rg; p.r = r; p.th = rg * r; p.wt = 4 * ns;
-    p.win = p.wt * s + 3 - s; p.hin = p.th * s + 3 - s;
-    p.tiles_x = (g.ow + p.wt - 1) / p.wt; p.tiles_y = (g.oh + p.th - 1) / p.th; p.cblks = g.cin / pl->ct;
-    const int64_t total = static_cast<int64_t>(p.tiles_x) * p.tiles_y * p.cblks * g.n;
-    if (total > INT32_MAX) {
+    p.q = q; p.ns = ns; p.tx_n = tx_n;
+    p.slot_px = (4 * ns - 1) * s + 3;
+    p.pitch = (static_cast<uint32_t>(p.slot_px) * g.cin + 127u) & ~127u;
+    // Two CTAs per SM share the shared memory; a ring of up to 16 rows each keeps 50-100 KB per SM in flight.
+    const size_t budget = 108 * 1024;
+    int nr = static_cast<int>((budget - 512) / p.pitch) - 1;
+    if (ctx->opt("dw_rows") > 0 && ctx->opt("dw_rows") < nr) nr = ctx->opt("dw_rows");   // tuning override
+    if (nr > 16) nr = 16;
+    if (nr < 4) {
         delete pl;
         return false;
     }
-    p.total_tiles = static_cast<int32_t>(total);
+    p.nr = nr;
     p.in_zp = g.in_zp; p.w_zp = g.w_zp; p.act_min = g.act_min; p.act_max = g.act_max;
-    p.tile_bytes = static_cast<uint32_t>(bytes_for(r));
-    p.buf_pitch = (p.tile_bytes + 127u) & ~127u;
-    pl->smem = 2 * static_cast<size_t>(p.buf_pitch) + 128;
-    pl->grid = p.total_tiles < 2 * ctx->sm_count ? p.total_tiles : 2 * ctx->sm_count;
+    // One wave of CTAs (two per SM), each with at least a few output rows so that the two halo rows stay cheap.
+    const int64_t units = static_cast<int64_t>(g.n) * g.oh;
+    int per_tx = (2 * ctx->sm_count) / tx_n;
+    if (per_tx < 1) per_tx = 1;
+    const int64_t min_rows = 6;
+    if (per_tx > (units + min_rows - 1) / min_rows) per_tx = static_cast<int>((units + min_rows - 1) / min_rows);
+    p.ctas_per_tx = per_tx;
+    pl->grid = per_tx * tx_n;
+    pl->threads = 32 * ((ns * q + 31) / 32 + 1);
+    pl->smem = static_cast<size_t>(nr + 1) * p.pitch + static_cast<size_t>(nr) * 16 + 64 + 128;
     if (cudaHostAlloc(reinterpret_cast<void **>(&pl->err_host), sizeof(int32_t), cudaHostAllocMapped) != cudaSuccess ||
         cudaHostGetDevicePointer(reinterpret_cast<void **>(&pl->err_dev), pl->err_host, 0) != cudaSuccess) {
         if (pl->err_host) cudaFreeHost(pl->err_host);
@@ -637,64 +723,59 @@ bool dw_tma_plan(enn_b200_op *op) {
     }
     *pl->err_host = 0;
     p.err = pl->err_dev;
-    op->dw_tma = pl;
+    op->dw_ring = pl;
     return true;
 }
 
-void dw_tma_release(enn_b200_op *op) {
-    DwTmaPlan *pl = static_cast<DwTmaPlan *>(op->dw_tma);
+void dw_ring_release(enn_b200_op *op) {
+    DwRingPlan *pl = static_cast<DwRingPlan *>(op->dw_ring);
     if (!pl) return;
     if (pl->err_host) cudaFreeHost(pl->err_host);
     delete pl;
-    op->dw_tma = nullptr;
+    op->dw_ring = nullptr;
 }
 
-template <int STRIDE, int CT>
-static cudaError_t dw_tma_launch_t(const DwTmaPlan *pl, const ConvGeom &g, const void *chan, const void *wp, void *out, cudaStream_t s) {
-    const DwChan *c = static_cast<const DwChan *>(chan);
-    const uint32_t *w = static_cast<const uint32_t *>(wp);
-    uint8_t *o = static_cast<uint8_t *>(out);
-    const bool asum = g.w_zp != 0;
-#define ENN_DWT(WS, AS)                                                                                                      \
-    do {                                                                                                                     \
-        cudaFuncSetAttribute(dw3x3_tma_kernel<STRIDE, CT, WS, AS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024); \
-        dw3x3_tma_kernel<STRIDE, CT, WS, AS><<<pl->grid, 256, pl->smem, s>>>(pl->map, pl->prm, c, w, o);                     \
-    } while (0)
-    if (g.w_signed) { if (asum) ENN_DWT(true, true); else ENN_DWT(true, false); }
-    else            { if (asum) ENN_DWT(false, true); else ENN_DWT(false, false); }
-#undef ENN_DWT
-    return cudaGetLastError();
+void dw_ring_clear_error(enn_b200_op *op) {
+    DwRingPlan *pl = static_cast<DwRingPlan *>(op->dw_ring);
+    if (pl && pl->err_host) *pl->err_host = 0;
 }
 
-// Returns cudaErrorNotSupported when the plan cannot be used for this call (misaligned input pointer).
-cudaError_t dw_tma_launch(enn_b200_op *op, const void *in, void *out) {
-    DwTmaPlan *pl = static_cast<DwTmaPlan *>(op->dw_tma);
-    enn_b200_context *ctx = op->ctx;
-    if (!pl || (reinterpret_cast<uintptr_t>(in) & 15) != 0) return cudaErrorNotSupported;
+// Returns cudaErrorNotSupported when the plan cannot serve this call (pointers not aligned for the bulk copies and the
+// 32-bit stores), cudaErrorLaunchFailure when an earlier launch gave up on a barrier wait.
+cudaError_t dw_ring_launch(enn_b200_op *op, const void *in, void *out) {
+    DwRingPlan *pl = static_cast<DwRingPlan *>(op->dw_ring);
+    if (!pl || (reinterpret_cast<uintptr_t>(in) & 15) != 0 || (reinterpret_cast<uintptr_t>(out) & 3) != 0) return cudaErrorNotSupported;
     if (*pl->err_host != 0) return cudaErrorLaunchFailure;
     const ConvGeom &g = op->g;
-    if (pl->map_ptr != in) {
-        DwEncodeTiledFn fn = reinterpret_cast<DwEncodeTiledFn>(ctx->encode_tiled);
-        cuuint64_t dims[4] = {static_cast<cuuint64_t>(g.cin), static_cast<cuuint64_t>(g.w), static_cast<cuuint64_t>(g.h), static_cast<cuuint64_t>(g.n)};
-        cuuint64_t strides[3] = {static_cast<cuuint64_t>(g.cin), static_cast<cuuint64_t>(g.w) * g.cin, static_cast<cuuint64_t>(g.h) * g.w * g.cin};
-        cuuint32_t box[4] = {static_cast<cuuint32_t>(pl->ct), static_cast<cuuint32_t>(pl->prm.win), static_cast<cuuint32_t>(pl->prm.hin), 1};
-        cuuint32_t estr[4] = {1, 1, 1, 1};
-        if (fn(&pl->map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(in), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return cudaErrorNotSupported;
-        pl->map_ptr = in;
+    const DwChan *c = static_cast<const DwChan *>(op->dw_chan);
+    const uint32_t *w = static_cast<const uint32_t *>(op->dw_w);
+    const uint8_t *i = static_cast<const uint8_t *>(in);
+    uint8_t *o = static_cast<uint8_t *>(out);
+    cudaStream_t s = op->ctx->stream;
+    const bool asum = g.w_zp != 0, relu = op->dw_relu;
+    static bool attr_set = false;
+#define ENN_DWR_ATTR(ST, WS, AS, RL) cudaFuncSetAttribute(dw3x3_ring_kernel<ST, WS, AS, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024)
+    if (!attr_set) {
+        ENN_DWR_ATTR(1, true, true, true); ENN_DWR_ATTR(1, true, true, false); ENN_DWR_ATTR(1, true, false, true); ENN_DWR_ATTR(1, true, false, false);
+        ENN_DWR_ATTR(1, false, true, true); ENN_DWR_ATTR(1, false, true, false); ENN_DWR_ATTR(1, false, false, true); ENN_DWR_ATTR(1, false, false, false);
+        ENN_DWR_ATTR(2, true, true, true); ENN_DWR_ATTR(2, true, true, false); ENN_DWR_ATTR(2, true, false, true); ENN_DWR_ATTR(2, true, false, false);
+        ENN_DWR_ATTR(2, false, true, true); ENN_DWR_ATTR(2, false, true, false); ENN_DWR_ATTR(2, false, false, true); ENN_DWR_ATTR(2, false, false, false);
+        attr_set = true;
     }
-    cudaStream_t s = ctx->stream;
+#undef ENN_DWR_ATTR
+#define ENN_DWR(ST, WS, AS, RL) launch_pdl(dw3x3_ring_kernel<ST, WS, AS, RL>, dim3(pl->grid), dim3(pl->threads), pl->smem, s, pl->prm, c, w, i, o)
+#define ENN_DWR_R(ST, WS, AS) (relu ? ENN_DWR(ST, WS, AS, true) : ENN_DWR(ST, WS, AS, false))
     if (g.sh == 1) {
-        if (pl->ct == 64) return dw_tma_launch_t<1, 64>(pl, g, op->dw_chan, op->dw_w, out, s);
-        if (pl->ct == 32) return dw_tma_launch_t<1, 32>(pl, g, op->dw_chan, op->dw_w, out, s);
-        return dw_tma_launch_t<1, 16>(pl, g, op->dw_chan, op->dw_w, out, s);
+        if (g.w_signed) { if (asum) ENN_DWR_R(1, true, true); else ENN_DWR_R(1, true, false); }
+        else            { if (asum) ENN_DWR_R(1, false, true); else ENN_DWR_R(1, false, false); }
+    } else {
+        if (g.w_signed) { if (asum) ENN_DWR_R(2, true, true); else ENN_DWR_R(2, true, false); }
+        else            { if (asum) ENN_DWR_R(2, false, true); else ENN_DWR_R(2, false, false); }
     }
-    if (pl->ct == 64) return dw_tma_launch_t<2, 64>(pl, g, op->dw_chan, op->dw_w, out, s);
-    if (pl->ct == 32) return dw_tma_launch_t<2, 32>(pl, g, op->dw_chan, op->dw_w, out, s);
-    return dw_tma_launch_t<2, 16>(pl, g, op->dw_chan, op->dw_w, out, s);
+#undef ENN_DWR_R
+#undef ENN_DWR
+    return cudaGetLastError();
 }
-
 
 cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, bool relu_form, const void *w_packed, const void *in, void *out,
                          int sm_count, cudaStream_t s) {
@@ -704,7 +785,6 @@ cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, bool relu_form, co
     const int64_t want_threads = static_cast<int64_t>(sm_count) * 512 * 2;
     int th = g.oh;
     while (th > 8 && static_cast<int64_t>(g.n) * ((g.oh + th - 1) / th) * nstrip * cqn < want_threads) th = (th + 1) / 2;
-    if (const char *ev = getenv("ENN_B200_DW_TH")) th = atoi(ev) > 0 ? atoi(ev) : th;   // tuning override
     const int nyt = (g.oh + th - 1) / th;
     const int64_t total = static_cast<int64_t>(g.n) * nyt * nstrip * cqn;
     if (total == 0) return cudaSuccess;

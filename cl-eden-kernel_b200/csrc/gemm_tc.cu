@@ -35,8 +35,20 @@ bool tc_available(const enn_b200_context *ctx);
 int32_t tc_plan_conv(enn_b200_op *op, const void *weights_hwio_host);
 int32_t tc_execute(enn_b200_op *op, const void *in, void *out);
 void tc_release(enn_b200_op *op);
+int32_t tc_test_starve_next(enn_b200_op *op);
+void tc_clear_error(enn_b200_op *op);
 
 namespace {
+
+// Measurement aids (operands loaded once, epilogue or stores skipped, per-role wait counters) change results or add
+// host synchronisation; they exist only in development builds (-DENN_B200_DEV) and compile to nothing otherwise.
+#ifdef ENN_B200_DEV
+#define ENN_DBG_MODE(p) ((p).dbg_mode)
+#define ENN_DBG_PTR(p) ((p).dbg)
+#else
+#define ENN_DBG_MODE(p) 0
+#define ENN_DBG_PTR(p) static_cast<long long *>(nullptr)
+#endif
 
 constexpr int kBM = 128;            // rows per tile = UMMA M
 constexpr int kBK = 128;            // bytes of K per stage = one 128B swizzle atom = 4 UMMA K steps
@@ -94,6 +106,7 @@ struct TcParams {
     long long *dbg;         // optional per-CTA cycle counters [grid][8] (null in normal use)
     int32_t dbg_mode;       // development switches (0 in normal use)
     int32_t epi_g;          // M tiles of a work unit the epilogue requantises together per column (1, 2 or 4)
+    int32_t test_starve;    // self-test of the bounded waits: no operand copy is issued and the waits give up early
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -132,8 +145,9 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait of the single-thread roles (producers, MMA issuer).  Callers look at the barrier with the non-blocking
 // test_wait first (the common case: already complete); what is left waits with try_wait, which parks the thread in
 // hardware between looks instead of spinning through issue slots that the epilogue warps of the same scheduler need.
-__device__ __forceinline__ bool mbar_wait_fast(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *err, int code) {
-    for (uint32_t i = 0; i < (kSpinLimit >> 7); ++i) {       // 2^17 looks of up to 10 us: gives up after about a second
+__device__ __forceinline__ bool mbar_wait_fast(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *err, int code,
+                                               uint32_t looks = kSpinLimit >> 7) {
+    for (uint32_t i = 0; i < looks; ++i) {       // by default 2^17 looks of up to 10 us: gives up after about a second
         // suspend-time hint (ns): stay parked until the phase completes instead of coming back every few hundred cycles
         uint32_t ok;
         asm volatile(
@@ -435,7 +449,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool dbg = p.dbg != nullptr;
+    const bool dbg = ENN_DBG_PTR(p) != nullptr;
     const bool split = blockDim.x == kThreads;      // launched with the separate B producer warp
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + nst);
     const uint32_t tfull0 = smem_u32(bars + 2 * nst), tempty0 = smem_u32(bars + 2 * nst + 2);
@@ -470,7 +484,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
     // Resident weights (the operator's only N tile: every k-block of B, once) are constants of the plan: their copy
     // starts here, ahead of the wait below, and the MMA issuer picks it up on its barrier.
-    if (bres && threadIdx.x == 0) {
+    const bool starve = p.test_starve != 0;      // self-test: nothing is copied, so the first wait of the MMA issuer runs out
+    if (bres && threadIdx.x == 0 && !starve) {
         const uint32_t bb = tempty0 + 16;
         mbar_expect_tx(bb, b_bytes * static_cast<uint32_t>(p.k_blocks));
         for (int kb = 0; kb < p.k_blocks; ++kb) tma_load_2d(smem_u32(b_resident) + kb * b_stride, &map_b, bb, kb * static_cast<int>(span), 0);
@@ -491,8 +506,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // thread issues about one tensor copy per 420 cycles, which is also about what the tensor pipe needs per
         // k-block, so two lanes of each producer warp take the k-blocks in turn (two lanes issuing in step reach
         // 1.7 x the rate of one).  A stage always belongs to the same lane, so each lane meets its stages' phases in order.
-        const bool pair_lanes = split && p.taps == 0 && p.group == 1 && p.kpack == 1 && (nst & 1) == 0 && p.k_blocks >= 8 &&
-                                !(p.dbg_mode & 9);
+        const bool pair_lanes = !starve && split && p.taps == 0 && p.group == 1 && p.kpack == 1 && (nst & 1) == 0 && p.k_blocks >= 8 &&
+                                !(ENN_DBG_MODE(p) & 9);
         if (pair_lanes) {
             const int nl = 2;      // lanes that share the issue (four measured slightly worse than two)
             if (lane < nl) {
@@ -533,7 +548,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             if (mbar_try_wait(full0 + 8 * s2, 0) || mbar_try_wait(full0 + 8 * s2, 1)) break;
                 }
             }
-        } else if (!TWO && !split && bres && (nst & 1) == 0 && !(p.dbg_mode & 9)) {
+        } else if (!starve && !TWO && !split && bres && (nst & 1) == 0 && !(ENN_DBG_MODE(p) & 9)) {
             // Resident weights (implicit convolutions, narrow pointwise layers): only A tiles are left to load, and the copy
             // issue rate of one thread still bounds the kernel, so lanes 0 and 1 fill alternate stages (a stage keeps its lane).
             if (lane < 2) {
@@ -599,7 +614,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             if (mbar_try_wait(full0 + 8 * s2, 0) || mbar_try_wait(full0 + 8 * s2, 1)) break;
                 }
             }
-        } else if (lane == 0) {
+        } else if (lane == 0 && !starve) {
             // WHICH: 0 = the A tiles, 1 = the B tiles, 2 = both (launches without the separate B producer warp)
             auto produce = [&](auto which) {
                 constexpr int WHICH = decltype(which)::value;
@@ -638,7 +653,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             if (dbg) t_wait += clock64() - t0;
                             const uint32_t bar = full0 + 8 * stage;
                             uint32_t sa = sa_stage;
-                            if ((p.dbg_mode & 1) && filled >= static_cast<uint32_t>(p.stages)) {
+                            if ((ENN_DBG_MODE(p) & 1) && filled >= static_cast<uint32_t>(p.stages)) {
                                 // development switch: operands stay as first loaded (measures the MMA side alone; results are wrong)
                                 if (rank == 0) mbar_arrive(bar);
                             } else if (TWO) {
@@ -669,7 +684,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                     }
                 }
-                if (dbg && DO_A) p.dbg[blockIdx.x * 8 + 0] = t_wait;
+                if (dbg && DO_A) ENN_DBG_PTR(p)[blockIdx.x * 8 + 0] = t_wait;
                 if (!ok) {
                     // Give copies already in flight a bounded chance to land before shared memory is released.
                     for (int s = 0; s < nst; ++s)
@@ -705,7 +720,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             uint32_t lo_stage = lo0;
             const uint32_t bres_lo = smem_u32(b_resident) >> 4, bstride16 = b_stride >> 4;
-            if (bres && !mbar_wait_fast(tempty0 + 16, 0, abort_flag, p.err, 5)) ok = false;
+            const uint32_t looks = starve ? 64u : (kSpinLimit >> 7);
+            if (bres && !mbar_wait_fast(tempty0 + 16, 0, abort_flag, p.err, 5, looks)) ok = false;
             long long t_tempty = 0, t_begin = dbg ? clock64() : 0;
             unsigned long long ns_begin = 0;
             if (dbg) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_begin));
@@ -713,7 +729,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t ab = it & 1, use = it >> 1;
                 // wait until the epilogue has drained this accumulator buffer
                 const long long t0 = dbg ? clock64() : 0;
-                if (!mbar_wait_fast(tempty0 + 8 * ab, (use & 1) ^ 1, abort_flag, p.err, 2)) { ok = false; break; }
+                if (!mbar_wait_fast(tempty0 + 8 * ab, (use & 1) ^ 1, abort_flag, p.err, 2, looks)) { ok = false; break; }
                 if (dbg) t_tempty += clock64() - t0;
                 if (TWO) asm volatile("fence.acq_rel.cluster;" ::: "memory");   // half of the arrivals came from the peer CTA
                 tc_fence_after();
@@ -722,7 +738,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int nsub = min(p.group, p.tiles_m - tg * p.group);
                 for (int j = 0; j < nsub && ok; ++j) {
                     const uint32_t d_tmem = tmem_base + ab * kMaxBN + j * p.bn_rows;
-                    if (ks == 4 && ks_last == 4 && p.kpack == 1 && !bres && p.stages == (TWO ? 6 : 4)) {
+                    if (ks == 4 && ks_last == 4 && p.kpack == 1 && !bres && p.stages == (TWO ? 6 : 4) && !starve) {
                         // big-GEMM shape: 256-wide tiles give four stages per CTA, six per CTA of a pair
                         if constexpr (TWO) ok = mma_tile_d6<true>(d_tmem, p.k_blocks, stage, phase, full0, empty0, desc_hi, lo0, stage16, a16, idesc, abort_flag, p.err);
                         else ok = mma_tile_d4<false>(d_tmem, p.k_blocks, stage, phase, full0, empty0, desc_hi, lo0, stage16, a16, idesc, abort_flag, p.err);
@@ -734,7 +750,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         int kb = 0;
                         while (kb < p.k_blocks) {
                             const uint32_t bar = full0 + 8 * stage;
-                            if (!mbar_test_wait(bar, phase) && !mbar_wait_fast(bar, phase, abort_flag, p.err, 3)) { ok = false; break; }
+                            if (!mbar_test_wait(bar, phase) && !mbar_wait_fast(bar, phase, abort_flag, p.err, 3, looks)) { ok = false; break; }
                             uint32_t lo = lo_stage;
                             const int kb_end = min(kb + p.kpack, p.k_blocks);
                             for (; kb < kb_end; ++kb, lo += kb16) {
@@ -765,8 +781,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (dbg) {
                 unsigned long long ns_end;
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_end));
-                p.dbg[blockIdx.x * 8 + 3] = t_tempty; p.dbg[blockIdx.x * 8 + 4] = clock64() - t_begin;
-                p.dbg[blockIdx.x * 8 + 7] = static_cast<long long>(ns_end - ns_begin);
+                ENN_DBG_PTR(p)[blockIdx.x * 8 + 3] = t_tempty; ENN_DBG_PTR(p)[blockIdx.x * 8 + 4] = clock64() - t_begin;
+                ENN_DBG_PTR(p)[blockIdx.x * 8 + 7] = static_cast<long long>(ns_end - ns_begin);
             }
         }
     } else {
@@ -775,21 +791,25 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int cgrp = (warp - 2) >> 2;                  // which share of the 16-column chunks this warp takes
         const int row_in_tile = q * 32 + lane;
         const int32_t hi_clamp = p.act_max - p.act_min;
-        const uint32_t lo_word = (static_cast<uint32_t>(p.act_min) & 0xff) * 0x01010101u;
+        // The lower clamp is added back to the packed bytes.  Unsigned outputs: byte + act_min <= act_max <= 255, so a
+        // plain 32-bit add never carries between bytes.  Signed outputs (act_min may be negative): the bytes get
+        // act_min + 128 (0..127, sums again <= 255) and the sign bit of every byte is flipped afterwards.
+        const uint32_t sign_word = p.a_signed ? 0x80808080u : 0u;
+        const uint32_t lo_word = (static_cast<uint32_t>(p.act_min + (p.a_signed ? 128 : 0)) & 0xff) * 0x01010101u;
         const int64_t st_bits = p.out_base | p.out_sn | p.out_sy | p.out_sx | p.bn_data | static_cast<int64_t>(reinterpret_cast<uintptr_t>(p.out));
         const int st_align = (st_bits & 15) == 0 ? 16 : ((st_bits & 7) == 0 ? 8 : 1);   // widest store every row start allows
         const bool st_fast = st_align == 16 && (p.N & 15) == 0;      // every chunk is one aligned 16-byte store
-        const bool whole_rows = st_fast && p.taps == 0 && !(p.dbg_mode & 4);   // rows of a full M tile are all real: see the chunk loop
+        const bool whole_rows = st_fast && p.taps == 0 && !(ENN_DBG_MODE(p) & 4);   // rows of a full M tile are all real: see the chunk loop
         const int patch_y = p.taps > 0 ? row_in_tile / p.conv_wt : 0;   // this thread's position in the output patch
         const int patch_x = p.taps > 0 ? row_in_tile - patch_y * p.conv_wt : 0;
         const int cps_mod = (p.bn_data >> 4) % kColGroups;
         // Several M tiles of a unit requantised together (shared column constants): flat row-major outputs with aligned rows only.
-        const int epi_g = (!TWO && p.epi_g > 1 && st_fast && p.taps == 0 && p.qh == 1 && p.dbg_mode == 0) ? p.epi_g : 1;
+        const int epi_g = (!TWO && p.epi_g > 1 && st_fast && p.taps == 0 && p.qh == 1 && ENN_DBG_MODE(p) == 0) ? p.epi_g : 1;
         const uint32_t rot_step = static_cast<uint32_t>((((p.group + epi_g - 1) / epi_g) * (p.bn_data >> 4)) % kColGroups);
         uint32_t it = 0;
         bool ok = true;
         int loaded_tn = -1;
-        long long t_tfull = 0, t_begin = clock64();
+        long long t_tfull = 0, t_begin = dbg ? clock64() : 0;
         for (int tile = tile_first; tile < total_tiles && ok; tile += tile_step, ++it) {
             int tg, tn;
             tile_coords(p, tile, tg, tn);
@@ -883,7 +903,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                                     for (int i = 0; i < G; ++i) {
                                         const uint32_t hi = pack_sat_u8_tc(y[i][3], y[i][2], 0);
-                                        w[i][half * 2 + jj] = pack_sat_u8_tc(y[i][1], y[i][0], hi) + lo_word;
+                                        w[i][half * 2 + jj] = (pack_sat_u8_tc(y[i][1], y[i][0], hi) + lo_word) ^ sign_word;
                                     }
                                 }
                             }
@@ -900,7 +920,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             };
             if (epi_g == 4) multi_tiles(std::integral_constant<int, 4>{});
             else if (epi_g == 2) multi_tiles(std::integral_constant<int, 2>{});
-            for (int j = 0; j < nsub && epi_g == 1 && !(p.dbg_mode & 2); ++j) {
+            for (int j = 0; j < nsub && epi_g == 1 && !(ENN_DBG_MODE(p) & 2); ++j) {
                 if (first < cps) {
                     const int tm = TWO ? tg * 2 + static_cast<int>(rank) : tg * p.group + j;
                     const int m = tm * kBM + row_in_tile;
@@ -943,7 +963,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 y[b] = tc_requant<MODE>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
                             }
                             const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
-                            (jj == 0 ? w0 : w1) = pack_sat_u8_tc(y[1], y[0], hi) + lo_word;
+                            (jj == 0 ? w0 : w1) = (pack_sat_u8_tc(y[1], y[0], hi) + lo_word) ^ sign_word;
                         }
                     };
                     if (whole_rows && n_cols == (cps << 4) && m + (kBM - 1 - row_in_tile) < p.M) {
@@ -974,7 +994,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             if (row_ok && c0 < n_cols) half_chunk(r, lc + half * 128, w[half * 2], w[half * 2 + 1]);
                         }
                         if (row_ok && c0 < n_cols) {
-                            if (p.dbg_mode & 4) {
+                            if (ENN_DBG_MODE(p) & 4) {
                                 // development switch: no stores (isolates the store path; only one lane keeps the values alive)
                                 if ((w[0] ^ w[1] ^ w[2] ^ w[3]) == 0x12345678u && lane == 33) orow[0] = 1;
                             } else if (st_fast) {
@@ -1013,7 +1033,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 else mbar_arrive(tempty0 + 8 * ab);
             }
         }
-        if (p.dbg && threadIdx.x == 64) { p.dbg[blockIdx.x * 8 + 5] = t_tfull; p.dbg[blockIdx.x * 8 + 6] = clock64() - t_begin; }
+        if (dbg && threadIdx.x == 64) { ENN_DBG_PTR(p)[blockIdx.x * 8 + 5] = t_tfull; ENN_DBG_PTR(p)[blockIdx.x * 8 + 6] = clock64() - t_begin; }
     }
 
     tc_fence_before();
@@ -1304,7 +1324,9 @@ __global__ void __launch_bounds__(256) conv3x3c3_kernel(Conv3x3c3Params g, const
     pdl_trigger();
     const uint32_t sw_u32 = smem_u32(s_w), sc_u32 = smem_u32(s_c);
     const int32_t hi_clamp = g.act_max - g.act_min;
-    const uint32_t lo_word = (static_cast<uint32_t>(g.act_min) & 0xff) * 0x01010101u;
+    // lower clamp added back per byte; signed outputs go through act_min + 128 and a sign-bit flip (no carries between bytes)
+    const uint32_t sign_word = A_SIGNED ? 0x80808080u : 0u;
+    const uint32_t lo_word = (static_cast<uint32_t>(g.act_min + (A_SIGNED ? 128 : 0)) & 0xff) * 0x01010101u;
 
     // Window of output pixel m as 7 words (27 bytes + 1 zero) and its row-sum term.
     auto load_window = [&](int m, uint32_t (&a)[7], int32_t &asum_term) {
@@ -1392,7 +1414,7 @@ __global__ void __launch_bounds__(256) conv3x3c3_kernel(Conv3x3c3Params g, const
 #pragma unroll
                 for (int i = 0; i < P; ++i) {
                     const uint32_t hi = pack_sat_u8_tc(y[i][3], y[i][2], 0);
-                    wout[i][jj] = pack_sat_u8_tc(y[i][1], y[i][0], hi) + lo_word;
+                    wout[i][jj] = (pack_sat_u8_tc(y[i][1], y[i][0], hi) + lo_word) ^ sign_word;
                 }
             }
 #pragma unroll
@@ -1445,6 +1467,7 @@ struct TcPlan {
     bool fan_out = false;              // the GEMMs are independent (deconvolution classes): run them side by side
     int32_t *err_host = nullptr;       // pinned + mapped
     int32_t *err_dev = nullptr;
+    bool starve_next = false;          // the next execute runs the bounded-wait self-test (tc_test_starve_next)
 };
 
 CUtensorMapSwizzle swizzle_of(uint32_t span) {
@@ -1493,7 +1516,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     // K bytes per k-block.  Implicit convolutions bring theirs (the channel chunk); plain GEMMs with a short K use 32-
     // or 64-byte rows, so that the TMA does not spend its time zero-filling 128-byte rows that are mostly padding.
     uint32_t span = implicit_span ? implicit_span : (K <= 32 ? 32u : (K <= 64 ? 64u : static_cast<uint32_t>(kBK)));
-    if (getenv("ENN_B200_NO_NARROW_SPAN") && !implicit_span) span = kBK;
+    if (ctx->opt("no_narrow_span") && !implicit_span) span = kBK;
     p.span = static_cast<int32_t>(span);
     const int32_t zw_eff = g.w_signed ? g.w_zp : g.w_zp - 128;   // weights as signed bytes: int8 stays, u8 becomes w - 128
     p.zw_eff = zw_eff;
@@ -1502,7 +1525,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     p.act_min = g.act_min; p.act_max = g.act_max; p.out_zp = g.out_zp;
     const int32_t extra = p.need_asum ? 16 : 0;
     int32_t max_data = kMaxBN - extra;
-    if (const char *ev = getenv("ENN_B200_TC_BN")) max_data = atoi(ev) >= 96 && atoi(ev) <= max_data ? (atoi(ev) & ~15) : max_data;   // tuning override
+    if (ctx->has_opt("tc_bn")) max_data = ctx->opt("tc_bn") >= 96 && ctx->opt("tc_bn") <= max_data ? (ctx->opt("tc_bn") & ~15) : max_data;   // tuning override, 96 columns at least
     p.tiles_m = (M + kBM - 1) / kBM;
     // N tiling: as few tiles as possible, but split further while the grid would leave SMs idle.
     int32_t tiles_n = (N + max_data - 1) / max_data;
@@ -1529,9 +1552,10 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
                          static_cast<int64_t>(p.tiles_m) * tiles_n >= 2ll * ctx->sm_count;
     bool two = pair_ok && (static_cast<int64_t>(M) + N) * K > (48ll << 20);
     int32_t forced_rows = 0;
-    if (const char *ev = getenv("ENN_B200_TC_PAIR")) {
-        two = pair_ok && atoi(ev) != 0;
-        if (atoi(ev) >= 128) forced_rows = atoi(ev) & ~31;      // tuning: that UMMA N instead of 256
+    if (ctx->has_opt("tc_pair")) {
+        const int ev = ctx->opt("tc_pair");
+        two = pair_ok && ev != 0;
+        if (ev >= 128) forced_rows = ev & ~31;      // tuning: that UMMA N instead of 256
     }
     if (two) {
         const int32_t rows = forced_rows >= 128 && forced_rows <= kMaxBN ? forced_rows : kMaxBN;   // the pair's UMMA N
@@ -1556,7 +1580,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     // tile in every epilogue thread).
     const bool big_operands = (static_cast<int64_t>(M) + N) * K > (48ll << 20);
     p.raster = !big_operands ? p.tiles_mg : (two ? 8 : 16);
-    if (const char *ev = getenv("ENN_B200_TC_RASTER")) p.raster = atoi(ev) > 0 ? atoi(ev) : p.raster;   // tuning override
+    if (ctx->opt("tc_raster") > 0) p.raster = ctx->opt("tc_raster");   // tuning override
     if (p.raster > p.tiles_mg) p.raster = p.tiles_mg;
     const int32_t k_pad = ((K + kBK - 1) / kBK) * kBK;
     p.k_pad = k_pad;
@@ -1588,7 +1612,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         bound_v[n] = amax * wabs + static_cast<int64_t>(K) * amax * (zw_eff < 0 ? -zw_eff : zw_eff) + (folded < 0 ? -folded : folded);
     }
     // ReLU-type outputs (lower clamp == output zero point): can every column use the merged form?
-    bool relu_hi = zo_eff == 0 && M > kGemvMaxM && !getenv("ENN_B200_NO_RELU_MODE"), relu_two = relu_hi;
+    bool relu_hi = zo_eff == 0 && M > kGemvMaxM && !ctx->opt("no_relu_mode"), relu_two = relu_hi;
     for (int32_t n = 0; n < N && relu_two; ++n) {
         const int32_t sh = qh.shift[n];
         const int32_t ls = sh > 0 ? sh : 0, e = sh > 0 ? 0 : -sh;
@@ -1599,7 +1623,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         // stage-1 value plus the rounding term must fit 32 bits
         if ((bound_v[n] << ls) + (e >= 1 ? (1ll << (e - 1)) : 0) + 1 >= (1ll << 31)) relu_two = false;
     }
-    p.mode = relu_hi && !getenv("ENN_B200_NO_RELU_HI") ? kModeReluHi : (relu_two ? kModeReluTwo : kModeNudge);
+    p.mode = relu_hi && !ctx->opt("no_relu_hi") ? kModeReluHi : (relu_two ? kModeReluTwo : kModeNudge);
     for (int32_t n = 0; n < N; ++n) {
         const int32_t tn = n / bn_data, r = n % bn_data;
         const int64_t folded = folded_v[n];
@@ -1658,8 +1682,8 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     // copy per ~420 cycles and a tile needs one A and one B copy per k-block): when the weights of the only N tile fit,
     // they are loaded once per CTA and stay resident, the stages hold A only, and the producer issues half as many copies.
     const size_t b_tile = (static_cast<size_t>(p.bn_rows) * span + 1023) & ~static_cast<size_t>(1023);
-    p.b_res = ((implicit_span != 0 || p.bn_rows <= 64 || want_resident || (p.k_blocks == 1 && !getenv("ENN_B200_NO_BRES_K1"))) && !p.two && tiles_n == 1 && M > kGemvMaxM && b_tile * p.k_blocks <= (want_resident ? kWidePackWeightBytes : 72 * 1024) &&
-               !getenv("ENN_B200_NO_BRES")) ? 1 : 0;
+    p.b_res = ((implicit_span != 0 || p.bn_rows <= 64 || want_resident || (p.k_blocks == 1 && !ctx->opt("no_bres_k1"))) && !p.two && tiles_n == 1 && M > kGemvMaxM && b_tile * p.k_blocks <= (want_resident ? kWidePackWeightBytes : 72 * 1024) &&
+               !ctx->opt("no_bres")) ? 1 : 0;
     const size_t kb_bytes = p.b_res ? static_cast<size_t>(kBM) * span : (static_cast<size_t>(kBM) + (p.two ? p.bn_rows / 2 : p.bn_rows)) * span;
     p.kpack = static_cast<int32_t>((32 * 1024) / kb_bytes);
     if (p.kpack < 1 || p.two) p.kpack = 1;
@@ -1681,7 +1705,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     // bound problems are better off without the extra warp.
     gm->threads = (p.kpack == 1 && p.k_blocks >= 8) ? kThreads : kThreadsOneProducer;
     p.epi_g = p.two ? 1 : (p.group >= 4 ? 4 : (p.group >= 2 ? 2 : 1));
-    if (const char *ev = getenv("ENN_B200_EPI_G")) p.epi_g = atoi(ev) == 4 || atoi(ev) == 2 ? (atoi(ev) <= p.group ? atoi(ev) : p.epi_g) : 1;   // tuning override
+    if (ctx->has_opt("epi_g")) { const int ev = ctx->opt("epi_g"); p.epi_g = ev == 4 || ev == 2 ? (ev <= p.group ? ev : p.epi_g) : 1; }   // tuning override
     return ENN_B200_SUCCESS;
 }
 
@@ -1807,7 +1831,7 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         const int32_t K = ig.kh * ig.kw * cin;
         const int32_t taps = ig.kh * ig.kw;
         uint32_t span = 0;
-        if (ig.sy == 1 && ig.sx == 1 && (cin & 31) == 0 && taps <= 64 && !getenv("ENN_B200_NO_IMPLICIT"))
+        if (ig.sy == 1 && ig.sx == 1 && (cin & 31) == 0 && taps <= 64 && !ctx->opt("no_implicit"))
             span = (cin % 128 == 0) ? 128 : ((cin % 64 == 0) ? 64 : 32);
         const int64_t M64 = static_cast<int64_t>(ig.n) * ig.oh * ig.ow;
         if (M64 <= 0 || M64 > INT32_MAX) return ENN_B200_INVALID_PARAMS;
@@ -1818,7 +1842,7 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
             gm.gather = true;
             gm.ig.K = K; gm.ig.Kp = (K + 15) & ~15;
             gm.first_layer = ig.kh == 3 && ig.kw == 3 && cin == 3 && ig.dy == 1 && ig.dx == 1 && (N & 15) == 0 && gm.prm.tiles_n == 1 &&
-                             M64 >= 4096 && !getenv("ENN_B200_NO_FIRST_LAYER");
+                             M64 >= 4096 && !ctx->opt("no_first_layer");
             const size_t need = static_cast<size_t>(M64) * gm.ig.Kp;
             if (need > plan->scratch_bytes) plan->scratch_bytes = need;
             return ENN_B200_SUCCESS;
@@ -1882,7 +1906,7 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         // the row fetches', and unpacked they keep two M tiles per work unit, which halves the epilogue's loads of the
         // column constants (112 x 112 x 16 -> 96: 161 us packed, 152 us in place).
         const bool epilogue_heavy = N >= 96 && (K & 15) == 0;
-        if (pointwise && M64 >= 4096 && K <= 64 && !epilogue_heavy && !getenv("ENN_B200_NO_PACK")) {
+        if (pointwise && M64 >= 4096 && K <= 64 && !epilogue_heavy && !ctx->opt("no_pack")) {
             const int32_t zw_eff = g.w_signed ? g.w_zp : g.w_zp - 128;
             for (int32_t f = 8; f >= 2 && pack == 1; f >>= 1) {
                 if (f * K > 128 || (f * K) % 16 != 0 || M64 % f != 0) continue;
@@ -1896,10 +1920,10 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         // 16-byte stores.  The block-diagonal weights (f^2 times the layer's) must stay resident in shared memory, and the
         // layer must keep two waves of M tiles, or the packing costs more than it saves.
         bool wide_pack = false;
-        if (pointwise && pack == 1 && M64 >= 4096 && K > 64 && (K & 127) != 0 && (K & 15) == 0 && !getenv("ENN_B200_NO_PACK")) {
+        if (pointwise && pack == 1 && M64 >= 4096 && K > 64 && (K & 127) != 0 && (K & 15) == 0 && !ctx->opt("no_pack")) {
             const int32_t zw_eff = g.w_signed ? g.w_zp : g.w_zp - 128;
             const int32_t extra = zw_eff != 0 ? 16 : 0;
-            const int32_t forced = getenv("ENN_B200_PACK_WIDE") ? atoi(getenv("ENN_B200_PACK_WIDE")) : 0;   // tuning override (1 = off)
+            const int32_t forced = ctx->opt("pack_wide");   // tuning override (1 = off)
             for (int32_t f = 8; f >= 2 && pack == 1 && forced != 1; f >>= 1) {
                 if ((forced > 1 && f != forced) || M64 % f != 0 || f * N > kMaxBN - extra) continue;
                 const size_t kp = (static_cast<size_t>(f) * K + 127) & ~static_cast<size_t>(127);
@@ -1925,7 +1949,7 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         } else if (in_place) {
             st = build_gemm(ctx, g, qh, static_cast<int32_t>(M64), N, K, weight, &gm);
             if (st != ENN_B200_SUCCESS) return bail(st);
-            gm.use_gemv = M64 <= kGemvMaxM && (K & 15) == 0 && static_cast<size_t>(M64) * K <= 48 * 1024 && !getenv("ENN_B200_NO_GEMV");
+            gm.use_gemv = M64 <= kGemvMaxM && (K & 15) == 0 && static_cast<size_t>(M64) * K <= 48 * 1024 && !ctx->opt("no_gemv");
             if (gm.use_gemv) op->info.impl = ENN_B200_IMPL_GEMV;
             gm.prm.qh = 1; gm.prm.qw = static_cast<int32_t>(M64);
             gm.prm.out_base = 0; gm.prm.out_sn = 0; gm.prm.out_sy = 0; gm.prm.out_sx = N;
@@ -1998,7 +2022,7 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         const int ncls = static_cast<int>(plan->gemms.size());
         bool all_implicit = true;
         for (auto &gm : plan->gemms) all_implicit = all_implicit && gm.implicit;
-        if (ncls > 1 && ncls <= enn_b200_context::kAuxStreams + 1 && all_implicit && !getenv("ENN_B200_NO_FAN_OUT")) {
+        if (ncls > 1 && ncls <= enn_b200_context::kAuxStreams + 1 && all_implicit && !ctx->opt("no_fan_out")) {
             plan->fan_out = true;
             const int share = ctx->sm_count / ncls > 0 ? ctx->sm_count / ncls : 1;
             for (auto &gm : plan->gemms)
@@ -2109,7 +2133,11 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
         ctx->last_error = buf;
         return ENN_B200_CUDA_FAILURE;
     }
+    #ifdef ENN_B200_DEV
     const bool fan_out = plan->fan_out && !getenv("ENN_B200_TC_DEBUG");
+#else
+    const bool fan_out = plan->fan_out;
+#endif
     if (fan_out && !ctx->aux_ready) {
         bool ok = cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming) == cudaSuccess;
         for (int i = 0; i < enn_b200_context::kAuxStreams && ok; ++i)
@@ -2121,6 +2149,8 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
         }
         ctx->aux_ready = true;
     }
+    const bool starve = plan->starve_next;
+    plan->starve_next = false;
     int cls = 0;             // index of the GEMM among those launched (fan-out: 0 runs on the main stream)
     bool forked = false;
     for (auto &gm : plan->gemms) {
@@ -2194,6 +2224,8 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
             }
         }
         p.out = static_cast<uint8_t *>(out);
+        p.test_starve = starve ? 1 : 0;
+#ifdef ENN_B200_DEV
         p.dbg_mode = getenv("ENN_B200_TC_MODE") ? atoi(getenv("ENN_B200_TC_MODE")) : 0;
         static long long *dbg_buf = nullptr;
         const bool dbg = getenv("ENN_B200_TC_DEBUG") != nullptr;     // development aid: role wait-cycle counters of CTA 0
@@ -2201,6 +2233,7 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
             if (!dbg_buf) cudaMallocManaged(&dbg_buf, sizeof(long long) * 8 * 1024);
             p.dbg = dbg_buf;
         }
+#endif
         cudaStream_t gs = ctx->stream;
         if (fan_out) {
             if (!forked) {       // everything the classes read (input, padded copy) is ordered before this point
@@ -2218,6 +2251,7 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
             cudaStreamWaitEvent(ctx->stream, ctx->ev_join[cls - 1], 0);
         }
         ++cls;
+#ifdef ENN_B200_DEV
         if (dbg) {
             cudaStreamSynchronize(ctx->stream);
             const long long *d = p.dbg;
@@ -2225,6 +2259,7 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
                          p.tiles_m, p.tiles_n, p.group, p.k_blocks, p.stages, d[0], d[3], d[4], d[5], d[6], d[7]);
             p.dbg = nullptr;
         }
+#endif
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) {
             ctx->last_error = std::string("tc_gemm_kernel launch: ") + cudaGetErrorString(e);
@@ -2232,6 +2267,24 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
         }
     }
     return ENN_B200_SUCCESS;
+}
+
+// Self-test hook for the bounded waits: the next tc_execute of this operator issues no operand copies, so the MMA
+// issuer's first wait (shortened to a fraction of a millisecond) runs out, the CTA-wide abort flag ends every other role,
+// TMEM is released and the error code reaches the host.  Nothing is in flight when the kernel gives up.
+int32_t tc_test_starve_next(enn_b200_op *op) {
+    TcPlan *plan = static_cast<TcPlan *>(op->tc);
+    if (!plan) return ENN_B200_INVALID_PARAMS;
+    for (auto &gm : plan->gemms)
+        if (gm.use_gemv || gm.first_layer || gm.prm.two) return ENN_B200_INVALID_PARAMS;   // pairs: the peer CTA would only see its own, long limit
+    plan->starve_next = true;
+    return ENN_B200_SUCCESS;
+}
+
+// Forgets a recorded barrier time-out so that the operator can be executed again.
+void tc_clear_error(enn_b200_op *op) {
+    TcPlan *plan = static_cast<TcPlan *>(op->tc);
+    if (plan && plan->err_host) *plan->err_host = 0;
 }
 
 void tc_release(enn_b200_op *op) {
@@ -2248,6 +2301,7 @@ static __device__ __align__(256) uint8_t g_static_scratch[kStaticScratchBytes];
 // The array's name is only a host-side handle; the device address differs per device and is looked up once per
 // device with that device current.
 static uint8_t *g_static_scratch_addr[64] = {nullptr};
+static std::mutex g_static_scratch_mutex;      // guards the table above (first calls from several host threads)
 
 int32_t tc_execute_static(enn_b200_op *op, const void *in, void *out) {
     enn_b200_context *ctx = op->ctx;
@@ -2273,17 +2327,26 @@ int32_t tc_execute_static(enn_b200_op *op, const void *in, void *out) {
         return ENN_B200_INVALID_PARAMS;
     }
     if (ctx->device < 0 || ctx->device >= 64) return ENN_B200_INVALID_PARAMS;
-    if (cudaSetDevice(ctx->device) != cudaSuccess) return ENN_B200_CUDA_FAILURE;
-    if (!g_static_scratch_addr[ctx->device]) {
-        void *addr = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&addr, g_static_scratch);
-        if (e != cudaSuccess || !addr) {
-            ctx->last_error = std::string("enn_b200_op_execute_noalloc: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e);
-            return ENN_B200_CUDA_FAILURE;
+    uint8_t *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        scratch = g_static_scratch_addr[ctx->device];
+        if (!scratch) {
+            // The symbol's address belongs to the device that is current during the lookup; the caller's own current
+            // device is put back afterwards.
+            int prev = -1;
+            cudaGetDevice(&prev);
+            if (cudaSetDevice(ctx->device) != cudaSuccess) return ENN_B200_CUDA_FAILURE;
+            void *addr = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&addr, g_static_scratch);
+            if (prev >= 0 && prev != ctx->device) cudaSetDevice(prev);
+            if (e != cudaSuccess || !addr) {
+                ctx->last_error = std::string("enn_b200_op_execute_noalloc: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e);
+                return ENN_B200_CUDA_FAILURE;
+            }
+            scratch = g_static_scratch_addr[ctx->device] = static_cast<uint8_t *>(addr);
         }
-        g_static_scratch_addr[ctx->device] = static_cast<uint8_t *>(addr);
     }
-    uint8_t *scratch = g_static_scratch_addr[ctx->device];
     if (*plan->err_host != 0) {
         ctx->last_error = "tensor-core kernel gave up on a barrier wait earlier";
         return ENN_B200_CUDA_FAILURE;
@@ -2304,6 +2367,7 @@ int32_t tc_execute_static(enn_b200_op *op, const void *in, void *out) {
         p.out = static_cast<uint8_t *>(out);
         p.dbg = nullptr;
         p.dbg_mode = 0;
+        p.test_starve = 0;
         launch_tc_gemm(gm, gm.map_a_static, p, ctx->stream);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) {

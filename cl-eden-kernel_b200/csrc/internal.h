@@ -3,6 +3,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstring>
+#include <map>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -21,6 +24,14 @@ struct enn_b200_context {
     cudaStream_t aux_streams[kAuxStreams] = {};
     cudaEvent_t ev_fork = nullptr, ev_join[kAuxStreams] = {};
     bool aux_ready = false;
+    // Planner overrides set with enn_b200_context_set_option (tests and tuning).  They are read when an operator is
+    // prepared, never on the execute path, and never from the environment.
+    std::map<std::string, int> options;
+    bool has_opt(const char *name) const { return options.find(name) != options.end(); }
+    int opt(const char *name, int dflt = 0) const {
+        auto it = options.find(name);
+        return it == options.end() ? dflt : it->second;
+    }
 };
 
 namespace enn_b200 {
@@ -89,7 +100,7 @@ struct enn_b200_op {
     void *dw_chan = nullptr;           // depthwise 3x3 fast path: per-channel constants (in `owned`)
     bool dw_relu = false;              // dw_chan holds the merged ReLU form {C low, C high, M0, e - 1}
     void *dw_w = nullptr;              // depthwise 3x3 fast path: packed 3-tap weight words (in `owned`)
-    void *dw_tma = nullptr;            // depthwise TMA-tile plan (depthwise.cu), owned
+    void *dw_ring = nullptr;           // depthwise row-ring plan (depthwise.cu), owned
     void *tc = nullptr;                // tensor-core plan (gemm_tc.cu), owned
 };
 
@@ -107,9 +118,10 @@ cudaError_t launch_depthwise(const ConvGeom &g, const Requant &rq, const void *i
 bool dw3x3_eligible(const ConvGeom &g);
 cudaError_t launch_dw3x3(const ConvGeom &g, const void *chan, bool relu_form, const void *w_packed, const void *in, void *out,
                          int sm_count, cudaStream_t s);
-bool dw_tma_plan(enn_b200_op *op);
-cudaError_t dw_tma_launch(enn_b200_op *op, const void *in, void *out);
-void dw_tma_release(enn_b200_op *op);
+bool dw_ring_plan(enn_b200_op *op);
+cudaError_t dw_ring_launch(enn_b200_op *op, const void *in, void *out);
+void dw_ring_release(enn_b200_op *op);
+void dw_ring_clear_error(enn_b200_op *op);
 cudaError_t add_kernel_init();
 cudaError_t launch_add(const AddParams &p, int64_t count, const void *a, const void *b, void *out, int sm_count,
                        cudaStream_t s);

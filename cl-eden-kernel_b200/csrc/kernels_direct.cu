@@ -193,7 +193,7 @@ cudaError_t add_kernel_init() {
 cudaError_t launch_add(const AddParams &p, int64_t count, const void *a, const void *b, void *out, int sm_count,
                        cudaStream_t s) {
     if (count == 0) return cudaSuccess;
-    if (count >= kAddLut2MinCount && p.lut2 && !getenv("ENN_B200_NO_ADD_LUT2") &&
+    if (count >= kAddLut2MinCount && p.lut2 &&
         ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
         const int64_t n16 = count / 16;
         const int64_t want = (n16 + kAddLut2Threads * 4 - 1) / (kAddLut2Threads * 4);      // at least four steps per thread

@@ -140,6 +140,12 @@ int32_t enn_b200_host_free(void *host_ptr);
 int32_t enn_b200_last_error(enn_b200_context *ctx, char *buf, size_t buf_len);
 /* cudaStream_t of the context, as void*, so a caller can order its own work against it. */
 void *enn_b200_stream(enn_b200_context *ctx);
+/* Planner overrides for tests and tuning, read when an operator is prepared (the library reads no environment
+ * variable).  Names: no_pdl, no_relu_mode, no_relu_hi, no_first_layer, no_implicit, no_gemv, no_narrow_span, no_pack,
+ * pack_wide, no_bres, no_bres_k1, no_fan_out, tc_bn (>= 96), tc_pair, tc_raster, epi_g, dw_legacy, dw_rows, no_fuse.
+ * Stands where the reference reads its build-time device switches (CLRuntime.cpp:174-213).  Unknown names are
+ * rejected with INVALID_PARAMS; none of them changes a result. */
+int32_t enn_b200_context_set_option(enn_b200_context *ctx, const char *name, int32_t value);
 
 /* ---- operators.  *_prepare uploads + re-packs constant tensors once (the reference does this in
  *      initialize(): alignQuantizedWeightGEMM, align_weight_direct, matrixTrans ...) and derives the
@@ -181,6 +187,14 @@ int32_t enn_b200_op_execute2(enn_b200_op *op, const void *in0_dev, const void *i
  * shared array; the first call per device does a one-time address lookup and should precede any stream capture. */
 int32_t enn_b200_op_execute_noalloc(enn_b200_op *op, const void *in_dev, void *out_dev);
 int32_t enn_b200_op_info(const enn_b200_op *op, enn_b200_op_info_t *info);
+/* Failure handling (Common.hpp:113-119 CL_FAILURE; the reference has no device-side waits to bound).  A kernel whose
+ * bounded barrier wait ran out leaves a code in host-visible memory and every later execute of that operator returns
+ * CUDA_FAILURE until enn_b200_op_clear_error.  enn_b200_op_test_starve_next arms a self-test of exactly that path for
+ * a tensor-core operator: its next execute issues no operand copy and uses a wait limit of under a millisecond, so the
+ * kernel gives up with nothing in flight, releases its tensor memory and returns; outputs of that execute are
+ * undefined. */
+int32_t enn_b200_op_test_starve_next(enn_b200_op *op);
+int32_t enn_b200_op_clear_error(enn_b200_op *op);
 int32_t enn_b200_op_release(enn_b200_op *op);
 
 /* ---- operator list: GpuUserDriver::OpenSubGraph / ExecuteSubGraph / CloseSubGraph (gpu_userdriver.cc) and

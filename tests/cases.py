@@ -81,9 +81,12 @@ def depthwise_case(seed=0, n=2, h=112, w=112, c=32, k=3, stride=1, dm=1, per_cha
 
 def deconv_case(seed=0, n=1, h=16, w=16, cin=128, cout=64, k=4, stride=2, pad=1, per_channel=False,
                 layout=enn.W_IOHW, in_scale=0.02, in_zp=128, w_scale=0.004, w_zp=120, out_scale=0.05, out_zp=128,
-                act=enn.ACT_NONE):
+                act=enn.ACT_NONE, act_dtype=enn.U8):
     rng = np.random.default_rng(seed)
-    x = rng.integers(0, 256, (n, h, w, cin), dtype=np.int64).astype(np.uint8)
+    if act_dtype == enn.S8:
+        x = rng.integers(-128, 128, (n, h, w, cin), dtype=np.int64).astype(np.int8)
+    else:
+        x = rng.integers(0, 256, (n, h, w, cin), dtype=np.int64).astype(np.uint8)
     wshape = (cin, cout, k, k) if layout == enn.W_IOHW else (cout, k, k, cin)
     if per_channel:
         wt = rng.integers(-127, 128, wshape, dtype=np.int64).astype(np.int8)
@@ -92,7 +95,7 @@ def deconv_case(seed=0, n=1, h=16, w=16, cin=128, cout=64, k=4, stride=2, pad=1,
     bias = rng.integers(-1000, 1001, (cout,), dtype=np.int64).astype(np.int32)
     scales = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), cout)).astype(np.float32) if per_channel else None
     d = enn.conv_desc(n=n, h=h, w=w, cin=cin, cout=cout, kh=k, kw=k, stride_h=stride, stride_w=stride, pad_t=pad,
-                      pad_r=pad, pad_b=pad, pad_l=pad, groups=1, activation=act,
+                      pad_r=pad, pad_b=pad, pad_l=pad, groups=1, activation=act, act_dtype=act_dtype,
                       weight_dtype=enn.S8 if per_channel else enn.U8, weight_layout=layout,
                       per_channel=int(per_channel), in_scale=in_scale, in_zp=in_zp, w_scale=w_scale,
                       w_zp=0 if per_channel else w_zp, out_scale=out_scale, out_zp=out_zp)
@@ -106,9 +109,12 @@ def fc_out_scale(k, in_scale=0.02, w_scale_typ=0.01):
 
 
 def fc_case(seed=0, m=4, k=256, n=64, per_channel=True, act=enn.ACT_NONE, in_scale=0.02, in_zp=128, out_zp=128,
-            w_scale=0.01, w_zp=0, out_scale=None):
+            w_scale=0.01, w_zp=0, out_scale=None, act_dtype=enn.U8):
     rng = np.random.default_rng(seed)
-    x = rng.integers(0, 256, (m, k), dtype=np.int64).astype(np.uint8)
+    if act_dtype == enn.S8:
+        x = rng.integers(-128, 128, (m, k), dtype=np.int64).astype(np.int8)
+    else:
+        x = rng.integers(0, 256, (m, k), dtype=np.int64).astype(np.uint8)
     if per_channel:
         wt = rng.integers(-127, 128, (n, k), dtype=np.int64).astype(np.int8)
     else:
@@ -116,7 +122,7 @@ def fc_case(seed=0, m=4, k=256, n=64, per_channel=True, act=enn.ACT_NONE, in_sca
         w_zp = w_zp or 127
     bias = rng.integers(-1000, 1001, (n,), dtype=np.int64).astype(np.int32)
     scales = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), n)).astype(np.float32) if per_channel else None
-    d = enn.FcDesc(m=m, k=k, n=n, activation=act, act_dtype=enn.U8, weight_dtype=enn.S8 if per_channel else enn.U8,
+    d = enn.FcDesc(m=m, k=k, n=n, activation=act, act_dtype=act_dtype, weight_dtype=enn.S8 if per_channel else enn.U8,
                    per_channel=int(per_channel), in_scale=in_scale, in_zp=in_zp, w_scale=w_scale, w_zp=w_zp,
                    bias_scale=float(np.float32(in_scale) * np.float32(w_scale)), out_scale=out_scale or fc_out_scale(k),
                    out_zp=out_zp)

@@ -1,6 +1,7 @@
 """GPU parity tests: every operator through the C ABI against the CPU oracle, bit for bit."""
 import json
 import os
+import zlib
 
 import numpy as np
 import pytest
@@ -9,6 +10,11 @@ import cases
 
 pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _seed(name):
+    """Case seed from the case name, the same in every process (str hashes are randomised per process)."""
+    return zlib.crc32(name.encode()) % 1000
 
 
 def _check(op, y_ref, x, x2=None):
@@ -72,13 +78,24 @@ CONV_CASES = {
     "first_layer_s1_u8w": dict(n=2, h=47, w=53, cin=3, cout=16, k=3, w_zp=121, out_scale=0.05),
     "first_layer_signed": dict(n=1, h=70, w=69, cin=3, cout=48, k=3, act_dtype=cases.enn.S8, in_zp=-7, out_zp=3, per_channel=True, out_scale=0.2),
     "first_layer_valid": dict(n=3, h=41, w=43, cin=3, cout=32, k=3, pad="valid", per_channel=True, out_scale=0.15, act=cases.enn.ACT_NONE),
+    # signed activations with a negative lower clamp and outputs on both sides of zero (the packed epilogue adds the clamp
+    # back per byte): in-place 1x1 with N a multiple of 16 and not, implicit 3x3, gathered, first layer, u8 weights
+    "s8_none_1x1_n48": dict(n=2, h=14, w=14, cin=32, cout=48, k=1, act_dtype=cases.enn.S8, in_zp=-3, out_zp=-5, act=cases.enn.ACT_NONE, per_channel=True, out_scale=0.6),
+    "s8_relu_zpm128_1x1_n40": dict(n=2, h=14, w=14, cin=32, cout=40, k=1, act_dtype=cases.enn.S8, in_zp=4, out_zp=-128, act=cases.enn.ACT_RELU, per_channel=True, out_scale=0.3),
+    "s8_none_implicit_3x3": dict(n=1, h=12, w=13, cin=32, cout=32, k=3, act_dtype=cases.enn.S8, in_zp=-1, out_zp=7, act=cases.enn.ACT_NONE, per_channel=True, out_scale=1.5),
+    "s8_relu6_zpm128_implicit": dict(n=2, h=9, w=9, cin=64, cout=24, k=3, act_dtype=cases.enn.S8, in_zp=0, out_zp=-128, per_channel=True, out_scale=0.03),
+    "s8_none_gather_s2": dict(n=2, h=15, w=14, cin=8, cout=16, k=3, stride=2, act_dtype=cases.enn.S8, in_zp=-9, out_zp=0, act=cases.enn.ACT_NONE, per_channel=True, out_scale=0.5),
+    "s8_none_first_layer": dict(n=1, h=70, w=69, cin=3, cout=32, k=3, act_dtype=cases.enn.S8, in_zp=-7, out_zp=-10, act=cases.enn.ACT_NONE, per_channel=True, out_scale=0.3),
+    "s8_none_u8_weights": dict(n=2, h=10, w=10, cin=16, cout=32, k=1, act_dtype=cases.enn.S8, in_zp=5, out_zp=-3, act=cases.enn.ACT_NONE, w_zp=121, out_scale=0.08),
 }
 
 
 @pytest.mark.parametrize("name", list(CONV_CASES))
 def test_conv2d_parity(enn, orc, ctx, name):
-    d, x, w, b, sc = cases.conv_case(seed=hash(name) % 1000, **CONV_CASES[name])
+    d, x, w, b, sc = cases.conv_case(seed=_seed(name), **CONV_CASES[name])
     y_ref = orc.conv2d(d, x, w, b, sc)
+    if name.startswith("s8_"):      # the case is only worth its name with outputs on both sides of zero
+        assert (y_ref < 0).mean() > 0.05 and (y_ref >= 0).mean() > 0.05, ((y_ref < 0).mean(), name)
     op = enn.conv2d(ctx, d, w, b, sc)
     try:
         for impl in _impls(enn, op):
@@ -165,12 +182,27 @@ DW_CASES = {
     "relu": dict(n=1, h=8, w=8, c=8, act=cases.enn.ACT_RELU, out_zp=20),
     "none_act_zp128": dict(n=1, h=8, w=11, c=16, act=cases.enn.ACT_NONE, out_zp=128, out_scale=0.1),
     "tall": dict(n=1, h=70, w=5, c=4),
+    # row-ring kernel (C % 16 == 0): several x tiles, ragged last strip, row ranges that cross image boundaries, one- and
+    # two-row images, borders with a non-zero input zero point, both SAME-padding parities of stride 2, u8 weights
+    "ring_c144_w56": dict(n=3, h=56, w=56, c=144),
+    "ring_c144_s2_odd": dict(n=2, h=57, w=55, c=144, stride=2),
+    "ring_c192_w28": dict(n=5, h=28, w=28, c=192, in_zp=3),
+    "ring_c384_w14": dict(n=7, h=14, w=14, c=384),
+    "ring_c576_s2": dict(n=3, h=14, w=14, c=576, stride=2, in_zp=0),
+    "ring_c16_wide": dict(n=1, h=5, w=230, c=16),
+    "ring_h1": dict(n=4, h=1, w=33, c=32),
+    "ring_h2_s2": dict(n=4, h=2, w=9, c=64, stride=2),
+    "ring_many_images": dict(n=40, h=7, w=10, c=32),
+    "ring_many_images_s2": dict(n=37, h=9, w=11, c=48, stride=2, out_scale=0.02),
+    "ring_per_tensor": dict(n=2, h=20, w=21, c=32, per_channel=False, out_scale=0.08, out_zp=3),
+    "ring_per_tensor_s2_relu": dict(n=2, h=22, w=19, c=64, stride=2, per_channel=False, out_scale=0.03, out_zp=0),
+    "ring_none_act": dict(n=2, h=13, w=17, c=96, act=cases.enn.ACT_NONE, out_zp=131, out_scale=0.1),
 }
 
 
 @pytest.mark.parametrize("name", list(DW_CASES))
 def test_depthwise_parity(enn, orc, ctx, name):
-    d, x, w, b, sc = cases.depthwise_case(seed=hash(name) % 1000, **DW_CASES[name])
+    d, x, w, b, sc = cases.depthwise_case(seed=_seed(name), **DW_CASES[name])
     y_ref = orc.depthwise(d, x, w, b, sc)
     op = enn.depthwise(ctx, d, w, b, sc)
     try:
@@ -222,15 +254,39 @@ def test_fc_parity_sweep(enn, orc, ctx, seed):
         op.release()
 
 
-@pytest.mark.parametrize("name", ["config2_s1", "config2_s2", "wide_c", "c960_7x7", "none_act_zp128", "s2_even"])
-def test_depthwise_tma_variant(enn, orc, ctx, name, monkeypatch):
-    """The opt-in TMA-staged depthwise kernel (ENN_B200_DW_TMA=1) on the cases with C % 16 == 0."""
-    monkeypatch.setenv("ENN_B200_DW_TMA", "1")
-    d, x, w, b, sc = cases.depthwise_case(seed=hash(name) % 1000, **DW_CASES[name])
-    op = enn.depthwise(ctx, d, w, b, sc)
+@pytest.mark.parametrize("name", ["config2_s1", "config2_s2", "wide_c", "ring_c144_s2_odd", "none_act_zp128", "ring_per_tensor"])
+def test_depthwise_register_streamed_kernel(enn, orc, name):
+    """The register-streamed 3x3 kernel (what channel counts that are not a multiple of 16, or more than 896, use) on
+    shapes the row-ring kernel normally takes, selected with the planner option `dw_legacy`."""
+    c2 = enn.Context(0)
     try:
-        _check(op, orc.depthwise(d, x, w, b, sc), x)
+        c2.set_option("dw_legacy", 1)
+        d, x, w, b, sc = cases.depthwise_case(seed=_seed(name), **DW_CASES[name])
+        op = enn.depthwise(c2, d, w, b, sc)
+        try:
+            _check(op, orc.depthwise(d, x, w, b, sc), x)
+        finally:
+            op.release()
     finally:
+        c2.close()
+
+
+def test_depthwise_unaligned_pointers(enn, orc, ctx):
+    """Device pointers at odd offsets (sub-buffers): the 16-byte and 4-byte aligned fast paths step aside."""
+    d, x, w, b, sc = cases.depthwise_case(seed=11, n=2, h=12, w=13, c=32)
+    y_ref = orc.depthwise(d, x, w, b, sc).reshape(-1)
+    op = enn.depthwise(ctx, d, w, b, sc)
+    buf_in, buf_out = ctx.malloc(x.nbytes + 64), ctx.malloc(y_ref.size + 64)
+    try:
+        for off_in, off_out in ((1, 0), (4, 0), (0, 3), (5, 7), (16, 4)):
+            pin = type(buf_in)(buf_in.value + off_in)
+            pout = type(buf_out)(buf_out.value + off_out)
+            ctx.upload(pin, x)
+            op.execute(pin, pout)
+            assert np.array_equal(ctx.download(pout, (y_ref.size,)), y_ref), (off_in, off_out)
+    finally:
+        ctx.free(buf_in)
+        ctx.free(buf_out)
         op.release()
 
 
@@ -245,12 +301,14 @@ DECONV_CASES = {
     "implicit_config4_small": dict(n=2, h=16, w=16, cin=128, cout=64),
     "implicit_c32_k3": dict(n=1, h=9, w=7, cin=32, cout=16, k=3, stride=2, pad=0),
     "implicit_c64_s3": dict(n=1, h=6, w=6, cin=64, cout=16, k=4, stride=3, pad=1),
+    "s8_none_implicit": dict(n=2, h=8, w=8, cin=32, cout=16, per_channel=True, out_scale=1.2, act_dtype=cases.enn.S8, in_zp=-4, out_zp=-6),
+    "s8_relu_zpm128_u8w": dict(n=1, h=7, w=9, cin=16, cout=24, act_dtype=cases.enn.S8, in_zp=3, out_zp=-128, act=cases.enn.ACT_RELU, out_scale=0.1),
 }
 
 
 @pytest.mark.parametrize("name", list(DECONV_CASES))
 def test_deconv_parity(enn, orc, ctx, name):
-    d, x, w, b, sc = cases.deconv_case(seed=hash(name) % 1000, **DECONV_CASES[name])
+    d, x, w, b, sc = cases.deconv_case(seed=_seed(name), **DECONV_CASES[name])
     y_ref = orc.deconv(d, x, w, b, sc)
     op = enn.deconv(ctx, d, w, b, sc)
     try:
@@ -297,12 +355,17 @@ FC_CASES = {
     "pack_wide_k96_n24": dict(m=4104, k=96, n=24, act=cases.enn.ACT_NONE),
     "pack_wide_k144_n24_per_tensor": dict(m=4100, k=144, n=24, per_channel=False, w_zp=119, act=cases.enn.ACT_NONE),
     "pack_wide_k192_n32": dict(m=4098, k=192, n=32, act=cases.enn.ACT_NONE, out_scale=0.3),
+    # signed activations, negative lower clamp, outputs on both sides of zero
+    "s8_none_n64": dict(m=300, k=256, n=64, act_dtype=cases.enn.S8, in_zp=-5, out_zp=3),
+    "s8_none_n29_gemv": dict(m=5, k=128, n=29, act_dtype=cases.enn.S8, in_zp=6, out_zp=-20),
+    "s8_relu_zpm128_n40": dict(m=200, k=96, n=40, act_dtype=cases.enn.S8, in_zp=0, out_zp=-128, act=cases.enn.ACT_RELU),
+    "s8_none_pack_k32_n16": dict(m=4104, k=32, n=16, act_dtype=cases.enn.S8, in_zp=-2, out_zp=1),
 }
 
 
 @pytest.mark.parametrize("name", list(FC_CASES))
 def test_fc_parity(enn, orc, ctx, name):
-    d, x, w, b, sc = cases.fc_case(seed=hash(name) % 1000, **FC_CASES[name])
+    d, x, w, b, sc = cases.fc_case(seed=_seed(name), **FC_CASES[name])
     y_ref = orc.fully_connected(d, x, w, b, sc)
     op = enn.fully_connected(ctx, d, w, b, sc)
     try:
@@ -330,10 +393,11 @@ def test_fc_full_size_sampled_rows(enn, orc, ctx):
 
 
 @pytest.mark.parametrize("m,k,n,w_zp", [(4096, 4096, 4096, None), (4230, 1024, 2500, 131)])
-def test_fc_cta_pair_mode(enn, orc, ctx, monkeypatch, m, k, n, w_zp):
+def test_fc_cta_pair_mode(enn, orc, m, k, n, w_zp):
     """The opt-in CTA-pair (cta_group::2) GEMM: same bytes as the oracle on sampled rows; the second shape has an odd
     number of M tiles (the last pair's second half lies outside the matrix), ragged N and the row-sum correction."""
-    monkeypatch.setenv("ENN_B200_TC_PAIR", "1")
+    ctx = enn.Context(0)
+    ctx.set_option("tc_pair", 1)
     kw = {} if w_zp is None else dict(w_zp=w_zp, per_channel=False)     # per-tensor u8 weights: zw' != 0
     d, x, w, b, sc = cases.fc_case(seed=9, m=m, k=k, n=n, **kw)
     op = enn.fully_connected(ctx, d, w, b, sc)
@@ -347,6 +411,7 @@ def test_fc_cta_pair_mode(enn, orc, ctx, monkeypatch, m, k, n, w_zp):
         assert np.array_equal(y[rows], y_ref)
     finally:
         op.release()
+        ctx.close()
 
 
 @pytest.mark.parametrize("count,act", [(1, 0), (15, 0), (4097, 3), (1 << 20, 0), (56 * 56 * 24 * 3, 0)])
@@ -415,6 +480,46 @@ def test_avgpool_parity(enn, orc, ctx, shape):
         _check(op, orc.avgpool(d, x), x)
     finally:
         op.release()
+
+
+def test_bounded_wait_gives_up_and_reports(enn, orc, ctx):
+    """Failure detection on the device without a fault: one execute of a tensor-core operator is starved of its operand
+    copies (nothing is issued, the wait limit is a fraction of a millisecond), the kernel gives up with nothing in
+    flight, frees its tensor memory and returns; the host then reads the code, the operator refuses to run until the
+    error is cleared, and afterwards it (and a freshly prepared one) computes the right bytes again."""
+    d, x, w, b, sc = cases.conv_case(seed=5, n=2, h=16, w=16, cin=64, cout=64, k=1, per_channel=True, out_scale=0.3)
+    y_ref = orc.conv2d(d, x, w, b, sc).reshape(-1)
+    op = enn.conv2d(ctx, d, w, b, sc)
+    try:
+        assert op.info.impl == enn.IMPL_TCGEN05
+        assert np.array_equal(op.run(x), y_ref)
+        op.test_starve_next()
+        op.run(x)                                   # the starved launch itself is enqueued without an error
+        ctx.sync()
+        with pytest.raises(enn.EnnError) as e:
+            op.run(x)
+        assert e.value.status == enn.CUDA_FAILURE and "barrier wait" in str(e.value)
+        op.clear_error()
+        assert np.array_equal(op.run(x), y_ref)
+        op2 = enn.conv2d(ctx, d, w, b, sc)
+        assert np.array_equal(op2.run(x), y_ref)
+        op2.release()
+    finally:
+        op.release()
+
+
+def test_options_and_limits(enn, ctx):
+    c2 = enn.Context(0)
+    try:
+        with pytest.raises(enn.EnnError):
+            c2.set_option("no_such_option", 1)
+        with pytest.raises(enn.EnnError):
+            c2.set_option("tc_bn", 64)              # narrower tiles than the epilogue supports are refused
+        c2.set_option("no_gemv", 1)
+        with pytest.raises(enn.EnnError):
+            c2.mma_peak(0, 256, 1 << 20)            # would keep every SM busy for a long time
+    finally:
+        c2.close()
 
 
 def test_error_paths(enn, ctx):
