@@ -137,7 +137,7 @@ __device__ __forceinline__ void dw_transpose_row(DwRow<STRIDE> &r, const DwRaw<S
         r.lo[2] = prmt(t1, t3, 0x5410); r.lo[3] = prmt(t1, t3, 0x7632);
     }
     if (STRIDE == 1) {
-        // hi = pixels 2..5
+        // hi = pixels 2..5 (its first two intermediate words are the second two of lo; the compiler merges them)
         const uint32_t t0 = prmt(p[2], p[3], 0x5140), t1 = prmt(p[2], p[3], 0x7362);
         const uint32_t t2 = prmt(p[4], p[5], 0x5140), t3 = prmt(p[4], p[5], 0x7362);
         r.hi[0] = prmt(t0, t2, 0x5410); r.hi[1] = prmt(t0, t2, 0x7632);
@@ -390,6 +390,7 @@ struct DwRingParams {
     int32_t nr;             // ring slots
     uint32_t pitch;         // bytes per slot (multiple of 128)
     int32_t in_zp, w_zp, act_min, act_max;
+    const uint8_t *zrow;    // one slot's worth of input zero points in global memory (source of the rows outside the image)
     int32_t *err;           // host-mapped error word
 };
 
@@ -414,18 +415,20 @@ __device__ __forceinline__ bool dw_mbar_wait(uint32_t bar, uint32_t parity, vola
     return false;
 }
 
-template <int STRIDE, bool W_SIGNED, bool NEED_ASUM, bool RELU>
+// RQ: 0 two-stage requantisation, 1 merged ReLU form, 2 merged ReLU form whose clamp is the saturation of the byte pack
+// itself (lower clamp 0, upper clamp 255: no min / max and no offset to add back).
+template <int STRIDE, bool W_SIGNED, bool NEED_ASUM, int RQ>
 __global__ void __launch_bounds__(kDwRingThreads, 2)
 dw3x3_ring_kernel(const DwRingParams p, const DwChan *__restrict__ chan, const uint32_t *__restrict__ w_packed,
                   const uint8_t *__restrict__ in, uint8_t *__restrict__ out) {
     extern __shared__ uint8_t dw_ring_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(dw_ring_raw) + 127) & ~static_cast<uintptr_t>(127));
     constexpr int NP = STRIDE == 1 ? 6 : 9;
+    constexpr bool RELU = RQ != 0;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ncw = (static_cast<int>(blockDim.x) >> 5) - 1;        // consumer warps; the last warp produces
-    const uint32_t zrow = dw_smem_u32(smem);                        // constant row of input zero points
-    const uint32_t ring = zrow + p.pitch;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + static_cast<size_t>(p.nr + 1) * p.pitch);
+    const uint32_t ring = dw_smem_u32(smem);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + static_cast<size_t>(p.nr) * p.pitch);
     const uint32_t full0 = dw_smem_u32(bars), empty0 = full0 + 8u * p.nr;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * p.nr);
     pdl_trigger();
@@ -437,11 +440,11 @@ dw3x3_ring_kernel(const DwRingParams p, const DwChan *__restrict__ chan, const u
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    const uint32_t zaw = (static_cast<uint32_t>(p.in_zp) & 0xff) * 0x01010101u;
-    {   // every slot and the constant row start as zero points; copies later overwrite the in-image pixels only
-        const uint32_t n16 = (static_cast<uint32_t>(p.nr) + 1u) * (p.pitch >> 4);
+    {   // every slot starts as zero points; the copies overwrite the in-image pixel range only
+        const uint32_t zaw = (static_cast<uint32_t>(p.in_zp) & 0xff) * 0x01010101u;
+        const uint32_t n16 = static_cast<uint32_t>(p.nr) * (p.pitch >> 4);
         for (uint32_t i = tid; i < n16; i += blockDim.x)
-            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(zrow + i * 16), "r"(zaw) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(ring + i * 16), "r"(zaw) : "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // ordered before the bulk copies into the same bytes
     }
     __syncthreads();
@@ -456,7 +459,9 @@ dw3x3_ring_kernel(const DwRingParams p, const DwChan *__restrict__ chan, const u
     const int ix_hi = ix_start + p.slot_px < p.w ? ix_start + p.slot_px : p.w;
 
     if (warp == ncw) {
-        // ---------------- producer: one bulk copy per in-image input row, in the order the consumers take them ----------------
+        // ---------------- producer: one bulk copy per input row, in the order the consumers take them ----------------
+        // Rows above and below the image are copied from a row of zero points in global memory, so that the consumers
+        // treat every row alike.
         if (lane == 0 && ix_hi > ix_lo) {
             pdl_wait();         // the input tensor is complete from here on
             const uint32_t bytes = static_cast<uint32_t>(ix_hi - ix_lo) * p.c;
@@ -467,11 +472,10 @@ dw3x3_ring_kernel(const DwRingParams p, const DwChan *__restrict__ chan, const u
             for (int u = u0; u < u1 && ok;) {
                 const int img = u / p.oh, oy0 = u - img * p.oh;
                 const int cnt = min(p.oh - oy0, u1 - u);
-                int iy_a = oy0 * STRIDE - p.pt, iy_b = (oy0 + cnt - 1) * STRIDE - p.pt + 2;
-                iy_a = iy_a < 0 ? 0 : iy_a;
-                iy_b = iy_b > p.h - 1 ? p.h - 1 : iy_b;
-                const uint8_t *src = in + (static_cast<int64_t>(img) * p.h + iy_a) * row_bytes + static_cast<int64_t>(ix_lo) * p.c;
-                for (int iy = iy_a; iy <= iy_b; ++iy, src += row_bytes) {
+                const int iy_a = oy0 * STRIDE - p.pt, iy_b = (oy0 + cnt - 1) * STRIDE - p.pt + 2;
+                const uint8_t *img_base = in + static_cast<int64_t>(img) * p.h * row_bytes + static_cast<int64_t>(ix_lo) * p.c;
+                for (int iy = iy_a; iy <= iy_b; ++iy) {
+                    const uint8_t *src = static_cast<unsigned>(iy) < static_cast<unsigned>(p.h) ? img_base + iy * row_bytes : p.zrow;
                     if (!dw_mbar_try(empty0 + 8 * slot, phase ^ 1) && !dw_mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag, p.err, 11)) { ok = false; break; }
                     const uint32_t bar = full0 + 8 * slot;
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -495,12 +499,15 @@ dw3x3_ring_kernel(const DwRingParams p, const DwChan *__restrict__ chan, const u
     const int task = tid < nthr ? tid : nthr - 1;
     const int strip = task / p.q, cq = task - strip * p.q;
     uint32_t wlo[3][4], whi[STRIDE == 1 ? 3 : 1][4];
-    int32_t mult[4], addend[4], esh[4], bias[4];
+    int32_t mult[4], esh[4];
+    int32_t addend[RELU ? 1 : 4], bias[RELU ? 1 : 4];
+    int64_t cc[RELU ? 4 : 1];       // merged form: the 64-bit addend, held as a register pair from the start
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
         const int4 ch = __ldg(reinterpret_cast<const int4 *>(chan) + cq * 4 + c);
-        if (RELU) {
-            mult[c] = ch.z; addend[c] = ch.x; esh[c] = ch.w; bias[c] = ch.y;    // M0, C low, e - 1, C high
+        if constexpr (RELU) {       // {C low, C high, M0, e - 1}
+            mult[c] = ch.z; esh[c] = ch.w;
+            cc[c] = static_cast<int64_t>((static_cast<uint64_t>(static_cast<uint32_t>(ch.y)) << 32) | static_cast<uint32_t>(ch.x));
         } else {
             mult[c] = ch.x; addend[c] = ch.y; esh[c] = ch.z; bias[c] = ch.w;
         }
@@ -511,52 +518,53 @@ dw3x3_ring_kernel(const DwRingParams p, const DwChan *__restrict__ chan, const u
         }
     }
     const uint32_t cpix = static_cast<uint32_t>(p.c);
-    const uint32_t toff = static_cast<uint32_t>(strip * 4 * STRIDE) * cpix + static_cast<uint32_t>(cq) * 4;
     const int32_t hi_clamp = p.act_max - p.act_min;
     const uint32_t lo_word = (static_cast<uint32_t>(p.act_min) & 0xff) * 0x01010101u;
-    uint32_t omask = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-        if (tid < nthr && ox0 + strip * 4 + j < p.ow) omask |= 1u << j;
+    const bool live = tid < nthr;
+    const bool st0 = live && ox0 + strip * 4 + 0 < p.ow, st1 = live && ox0 + strip * 4 + 1 < p.ow;
+    const bool st2 = live && ox0 + strip * 4 + 2 < p.ow, st3 = live && ox0 + strip * 4 + 3 < p.ow;
     const uint32_t out_pitch = static_cast<uint32_t>(p.ow) * cpix;
     const int32_t zero4[4] = {0, 0, 0, 0};
 
-    uint32_t slot_a = 0, phase_a = 0;       // next slot to take a row from
-    uint32_t slot_r = 0;                    // next slot to hand back
+    // Ring position of the next row to take: its slot's read address for this thread, its barrier and the phase.
+    const uint32_t rd0 = ring + static_cast<uint32_t>(strip * 4 * STRIDE) * cpix + static_cast<uint32_t>(cq) * 4;
+    const uint32_t rd_end = rd0 + static_cast<uint32_t>(p.nr) * p.pitch;
+    uint32_t rd = rd0, bar_a = full0, phase_a = 0;
+    const uint32_t rel_off = 8u * p.nr;         // empty barrier of a slot = its full barrier + rel_off
     bool ok = true;
     uint8_t *orow = out;
 
-    // Reads this thread's words of input row iy (from its ring slot, or from the constant row outside the image).
-    auto issue = [&](DwRaw<STRIDE> &raw, int iy) {
-        uint32_t base = zrow;
-        if (static_cast<unsigned>(iy) < static_cast<unsigned>(p.h)) {
-            // Every lane looks once (the usual case: the row landed long ago); otherwise the lanes wait, bounded, and
-            // agree on the outcome, so that a warp always leaves the row loop as a whole.
-            const uint32_t bar = full0 + 8 * slot_a;
-            if (!__all_sync(0xffffffffu, dw_mbar_try(bar, phase_a)))
-                ok = __all_sync(0xffffffffu, dw_mbar_wait(bar, phase_a, abort_flag, p.err, 12));
-            base = ring + slot_a * p.pitch;
-            if (++slot_a == static_cast<uint32_t>(p.nr)) { slot_a = 0; phase_a ^= 1; }
-        }
-        base += toff;
+    // Reads this thread's words of the next input row; returns the barrier to signal once they have been used.
+    auto issue = [&](DwRaw<STRIDE> &raw) -> uint32_t {
+        // Every lane looks once (the usual case: the row landed long ago); otherwise the lanes wait, bounded, and agree
+        // on the outcome, so that a warp always leaves the row loop as a whole.
+        if (!__all_sync(0xffffffffu, dw_mbar_try(bar_a, phase_a)))
+            ok = __all_sync(0xffffffffu, dw_mbar_wait(bar_a, phase_a, abort_flag, p.err, 12));
 #pragma unroll
-        for (int i = 0; i < NP; ++i) raw.p[i] = dw_lds32(base + static_cast<uint32_t>(i) * cpix);
+        for (int i = 0; i < NP; ++i) raw.p[i] = dw_lds32(rd + static_cast<uint32_t>(i) * cpix);
+        const uint32_t rel = bar_a + rel_off;
+        rd += p.pitch;
+        bar_a += 8;
+        if (rd == rd_end) { rd = rd0; bar_a = full0; phase_a ^= 1; }
+        return rel;
     };
-    // Hands the slot of input row iy back to the producer; the row's words are in registers by now.
-    auto release = [&](int iy) {
-        if (static_cast<unsigned>(iy) < static_cast<unsigned>(p.h)) {
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * slot_r) : "memory");
-            if (++slot_r == static_cast<uint32_t>(p.nr)) slot_r = 0;
-        }
+    // Hands a slot back to the producer; the row's words are in registers by now.
+    auto release = [&](uint32_t rel) {
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(rel) : "memory");
     };
     auto emit = [&](const DwRow<STRIDE> &r0, const DwRow<STRIDE> &r1, const DwRow<STRIDE> &r2) {
         int32_t acc[4][4];
         int32_t asum[NEED_ASUM ? 4 : 1][4];
-        if constexpr (RELU) dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, true>(acc, asum, r0, wlo[0], whi[0], zero4);
-        else dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, true>(acc, asum, r0, wlo[0], whi[0], bias);
-        dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r1, wlo[1], whi[STRIDE == 1 ? 1 : 0], bias);
-        dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r2, wlo[2], whi[STRIDE == 1 ? 2 : 0], bias);
+        if constexpr (RELU) {
+            dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, true>(acc, asum, r0, wlo[0], whi[0], zero4);
+            dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r1, wlo[1], whi[STRIDE == 1 ? 1 : 0], zero4);
+            dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r2, wlo[2], whi[STRIDE == 1 ? 2 : 0], zero4);
+        } else {
+            dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, true>(acc, asum, r0, wlo[0], whi[0], bias);
+            dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r1, wlo[1], whi[STRIDE == 1 ? 1 : 0], bias);
+            dw_accumulate<STRIDE, W_SIGNED, NEED_ASUM, false>(acc, asum, r2, wlo[2], whi[STRIDE == 1 ? 2 : 0], bias);
+        }
         uint32_t word[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -566,29 +574,24 @@ dw3x3_ring_kernel(const DwRingParams p, const DwChan *__restrict__ chan, const u
                 int32_t a = acc[c][j];
                 if (NEED_ASUM) a -= p.w_zp * asum[c][j];
                 int32_t v;
-                if (RELU) {
-                    int64_t cc;
-                    asm("mov.b64 %0, {%1, %2};" : "=l"(cc) : "r"(addend[c]), "r"(bias[c]));
-                    const int64_t qv = static_cast<int64_t>(a) * mult[c] + cc;
+                if constexpr (RELU) {
+                    const int64_t qv = static_cast<int64_t>(a) * mult[c] + cc[c];
                     v = static_cast<int32_t>(qv >> 32) >> esh[c];
                 } else {
                     const int64_t pr = static_cast<int64_t>(a) * mult[c] + (1ll << 30);
                     const int32_t x = static_cast<int32_t>(pr >> 31);
                     v = (x + addend[c] - static_cast<int32_t>(shr_clamp(static_cast<uint32_t>(x), esh[c] >> 8))) >> (esh[c] & 0xff);
                 }
-                y[c] = __vimin_s32_relu(v, hi_clamp);
+                y[c] = RQ == 2 ? v : __vimin_s32_relu(v, hi_clamp);
             }
             const uint32_t hi = pack_sat_u8(y[3], y[2], 0);
-            word[j] = pack_sat_u8(y[1], y[0], hi) + lo_word;      // u8 outputs: byte + act_min <= act_max, no carry between bytes
+            word[j] = pack_sat_u8(y[1], y[0], hi);
+            if (RQ != 2) word[j] += lo_word;      // u8 outputs: byte + act_min <= act_max, no carry between bytes
         }
-        if (omask == 15u) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint32_t *>(orow + static_cast<uint32_t>(j) * cpix) = word[j];
-        } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (omask & (1u << j)) *reinterpret_cast<uint32_t *>(orow + static_cast<uint32_t>(j) * cpix) = word[j];
-        }
+        if (st0) *reinterpret_cast<uint32_t *>(orow) = word[0];
+        if (st1) *reinterpret_cast<uint32_t *>(orow + cpix) = word[1];
+        if (st2) *reinterpret_cast<uint32_t *>(orow + 2 * cpix) = word[2];
+        if (st3) *reinterpret_cast<uint32_t *>(orow + 3 * cpix) = word[3];
         orow += out_pitch;
     };
 
@@ -598,61 +601,61 @@ dw3x3_ring_kernel(const DwRingParams p, const DwChan *__restrict__ chan, const u
         const int cnt = min(p.oh - oy0, u1 - u);
         u += cnt;
         orow = out + ((static_cast<int64_t>(img) * p.oh + oy0) * p.ow + ox0 + strip * 4) * static_cast<int64_t>(cpix) + cq * 4;
-        const int iy0 = oy0 * STRIDE - p.pt;
         DwRow<STRIDE> ra, rb, rc;
         if constexpr (STRIDE == 1) {
+            // input rows oy0 - pt ... oy0 - pt + cnt + 1, one per output row after the first three
             DwRaw<STRIDE> nx;
-            issue(nx, iy0);
+            uint32_t rel = issue(nx);
             dw_transpose_row<STRIDE>(ra, nx);
-            release(iy0);
-            issue(nx, iy0 + 1);
+            release(rel);
+            rel = issue(nx);
             dw_transpose_row<STRIDE>(rb, nx);
-            release(iy0 + 1);
-            issue(nx, iy0 + 2);
+            release(rel);
+            rel = issue(nx);
             for (int r = 0; r < cnt && ok; r += 3) {
                 dw_transpose_row<STRIDE>(rc, nx);
-                release(iy0 + 2 + r);
-                if (r + 1 < cnt) issue(nx, iy0 + 3 + r);
+                release(rel);
+                if (r + 1 < cnt) rel = issue(nx);
                 emit(ra, rb, rc);
                 if (r + 1 < cnt) {
                     dw_transpose_row<STRIDE>(ra, nx);
-                    release(iy0 + 3 + r);
-                    if (r + 2 < cnt) issue(nx, iy0 + 4 + r);
+                    release(rel);
+                    if (r + 2 < cnt) rel = issue(nx);
                     emit(rb, rc, ra);
                 }
                 if (r + 2 < cnt) {
                     dw_transpose_row<STRIDE>(rb, nx);
-                    release(iy0 + 4 + r);
-                    if (r + 3 < cnt) issue(nx, iy0 + 5 + r);
+                    release(rel);
+                    if (r + 3 < cnt) rel = issue(nx);
                     emit(rc, ra, rb);
                 }
             }
         } else {
+            // input rows 2 oy0 - pt ... 2 oy0 - pt + 2 cnt, two per output row after the first
             DwRaw<STRIDE> n1, n2;
-            issue(n1, iy0);
+            uint32_t rel1 = issue(n1), rel2;
             dw_transpose_row<STRIDE>(ra, n1);
-            release(iy0);
-            issue(n1, iy0 + 1);
-            issue(n2, iy0 + 2);
+            release(rel1);
+            rel1 = issue(n1);
+            rel2 = issue(n2);
             for (int r = 0; r < cnt && ok; r += 2) {
-                const int iy = iy0 + 2 * r;
                 dw_transpose_row<STRIDE>(rb, n1);
-                release(iy + 1);
+                release(rel1);
                 dw_transpose_row<STRIDE>(rc, n2);
-                release(iy + 2);
+                release(rel2);
                 if (r + 1 < cnt) {
-                    issue(n1, iy + 3);
-                    issue(n2, iy + 4);
+                    rel1 = issue(n1);
+                    rel2 = issue(n2);
                 }
                 emit(ra, rb, rc);
                 if (r + 1 < cnt) {
                     dw_transpose_row<STRIDE>(rb, n1);
-                    release(iy + 3);
+                    release(rel1);
                     dw_transpose_row<STRIDE>(ra, n2);
-                    release(iy + 4);
+                    release(rel2);
                     if (r + 2 < cnt) {
-                        issue(n1, iy + 5);
-                        issue(n2, iy + 6);
+                        rel1 = issue(n1);
+                        rel2 = issue(n2);
                     }
                     emit(rc, rb, ra);
                 }
@@ -673,6 +676,7 @@ struct DwRingPlan {
     size_t smem = 0;
     int32_t *err_host = nullptr;       // pinned + mapped
     int32_t *err_dev = nullptr;
+    void *zrow_dev = nullptr;          // row of input zero points
 };
 
 // Chooses tile width, ring depth and grid; returns false when the geometry is outside the kernel's domain.
@@ -694,9 +698,13 @@ bool dw_ring_plan(enn_b200_op *op) {
     p.q = q; p.ns = ns; p.tx_n = tx_n;
     p.slot_px = (4 * ns - 1) * s + 3;
     p.pitch = (static_cast<uint32_t>(p.slot_px) * g.cin + 127u) & ~127u;
-    // Two CTAs per SM share the shared memory; a ring of up to 16 rows each keeps 50-100 KB per SM in flight.
-    const size_t budget = 108 * 1024;
-    int nr = static_cast<int>((budget - 512) / p.pitch) - 1;
+    // CTAs per SM: what the 128-register budget allows for this block size (at most four); they share the shared memory,
+    // and a ring of up to 16 rows each keeps 50-100 KB per SM in flight.
+    const int threads = 32 * ((ns * q + 31) / 32 + 1);
+    int per_sm = 65536 / (threads * 128);
+    per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+    const size_t budget = static_cast<size_t>(216 * 1024) / per_sm;
+    int nr = static_cast<int>((budget - 512) / p.pitch);
     if (ctx->opt("dw_rows") > 0 && ctx->opt("dw_rows") < nr) nr = ctx->opt("dw_rows");   // tuning override
     if (nr > 16) nr = 16;
     if (nr < 4) {
@@ -705,19 +713,26 @@ bool dw_ring_plan(enn_b200_op *op) {
     }
     p.nr = nr;
     p.in_zp = g.in_zp; p.w_zp = g.w_zp; p.act_min = g.act_min; p.act_max = g.act_max;
-    // One wave of CTAs (two per SM), each with at least a few output rows so that the two halo rows stay cheap.
+    // One wave of CTAs, each with at least a few output rows so that the two halo rows stay cheap.
     const int64_t units = static_cast<int64_t>(g.n) * g.oh;
-    int per_tx = (2 * ctx->sm_count) / tx_n;
+    int per_tx = (per_sm * ctx->sm_count) / tx_n;
     if (per_tx < 1) per_tx = 1;
     const int64_t min_rows = 6;
     if (per_tx > (units + min_rows - 1) / min_rows) per_tx = static_cast<int>((units + min_rows - 1) / min_rows);
     p.ctas_per_tx = per_tx;
     pl->grid = per_tx * tx_n;
-    pl->threads = 32 * ((ns * q + 31) / 32 + 1);
-    pl->smem = static_cast<size_t>(nr + 1) * p.pitch + static_cast<size_t>(nr) * 16 + 64 + 128;
+    pl->threads = threads;
+    pl->smem = static_cast<size_t>(nr) * p.pitch + static_cast<size_t>(nr) * 16 + 64 + 128;
+    if (cudaMalloc(&pl->zrow_dev, p.pitch) != cudaSuccess || cudaMemset(pl->zrow_dev, g.in_zp & 0xff, p.pitch) != cudaSuccess) {
+        if (pl->zrow_dev) cudaFree(pl->zrow_dev);
+        delete pl;
+        return false;
+    }
+    p.zrow = static_cast<const uint8_t *>(pl->zrow_dev);
     if (cudaHostAlloc(reinterpret_cast<void **>(&pl->err_host), sizeof(int32_t), cudaHostAllocMapped) != cudaSuccess ||
         cudaHostGetDevicePointer(reinterpret_cast<void **>(&pl->err_dev), pl->err_host, 0) != cudaSuccess) {
         if (pl->err_host) cudaFreeHost(pl->err_host);
+        cudaFree(pl->zrow_dev);
         delete pl;
         return false;
     }
@@ -731,6 +746,7 @@ void dw_ring_release(enn_b200_op *op) {
     DwRingPlan *pl = static_cast<DwRingPlan *>(op->dw_ring);
     if (!pl) return;
     if (pl->err_host) cudaFreeHost(pl->err_host);
+    if (pl->zrow_dev) cudaFree(pl->zrow_dev);
     delete pl;
     op->dw_ring = nullptr;
 }
@@ -752,19 +768,21 @@ cudaError_t dw_ring_launch(enn_b200_op *op, const void *in, void *out) {
     const uint8_t *i = static_cast<const uint8_t *>(in);
     uint8_t *o = static_cast<uint8_t *>(out);
     cudaStream_t s = op->ctx->stream;
-    const bool asum = g.w_zp != 0, relu = op->dw_relu;
+    const bool asum = g.w_zp != 0;
+    const int rq = !op->dw_relu ? 0 : ((g.act_min == 0 && g.act_max >= 255) ? 2 : 1);
     static bool attr_set = false;
-#define ENN_DWR_ATTR(ST, WS, AS, RL) cudaFuncSetAttribute(dw3x3_ring_kernel<ST, WS, AS, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024)
+#define ENN_DWR_ATTR(ST, WS, AS) \
+    cudaFuncSetAttribute(dw3x3_ring_kernel<ST, WS, AS, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024); \
+    cudaFuncSetAttribute(dw3x3_ring_kernel<ST, WS, AS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024); \
+    cudaFuncSetAttribute(dw3x3_ring_kernel<ST, WS, AS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024)
     if (!attr_set) {
-        ENN_DWR_ATTR(1, true, true, true); ENN_DWR_ATTR(1, true, true, false); ENN_DWR_ATTR(1, true, false, true); ENN_DWR_ATTR(1, true, false, false);
-        ENN_DWR_ATTR(1, false, true, true); ENN_DWR_ATTR(1, false, true, false); ENN_DWR_ATTR(1, false, false, true); ENN_DWR_ATTR(1, false, false, false);
-        ENN_DWR_ATTR(2, true, true, true); ENN_DWR_ATTR(2, true, true, false); ENN_DWR_ATTR(2, true, false, true); ENN_DWR_ATTR(2, true, false, false);
-        ENN_DWR_ATTR(2, false, true, true); ENN_DWR_ATTR(2, false, true, false); ENN_DWR_ATTR(2, false, false, true); ENN_DWR_ATTR(2, false, false, false);
+        ENN_DWR_ATTR(1, true, true); ENN_DWR_ATTR(1, true, false); ENN_DWR_ATTR(1, false, true); ENN_DWR_ATTR(1, false, false);
+        ENN_DWR_ATTR(2, true, true); ENN_DWR_ATTR(2, true, false); ENN_DWR_ATTR(2, false, true); ENN_DWR_ATTR(2, false, false);
         attr_set = true;
     }
 #undef ENN_DWR_ATTR
-#define ENN_DWR(ST, WS, AS, RL) launch_pdl(dw3x3_ring_kernel<ST, WS, AS, RL>, dim3(pl->grid), dim3(pl->threads), pl->smem, s, pl->prm, c, w, i, o)
-#define ENN_DWR_R(ST, WS, AS) (relu ? ENN_DWR(ST, WS, AS, true) : ENN_DWR(ST, WS, AS, false))
+#define ENN_DWR(ST, WS, AS, RQ) launch_pdl(dw3x3_ring_kernel<ST, WS, AS, RQ>, dim3(pl->grid), dim3(pl->threads), pl->smem, s, pl->prm, c, w, i, o)
+#define ENN_DWR_R(ST, WS, AS) (rq == 0 ? ENN_DWR(ST, WS, AS, 0) : (rq == 1 ? ENN_DWR(ST, WS, AS, 1) : ENN_DWR(ST, WS, AS, 2)))
     if (g.sh == 1) {
         if (g.w_signed) { if (asum) ENN_DWR_R(1, true, true); else ENN_DWR_R(1, true, false); }
         else            { if (asum) ENN_DWR_R(1, false, true); else ENN_DWR_R(1, false, false); }
