@@ -1,18 +1,22 @@
 #!/usr/bin/env python
 """Benchmark of the quantized operator hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--lanes S]
 
-One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of seeded synthetic
-input.  The default workload is the whole MobileNetV2-1.0 224x224 uint8 graph at batch 256 per GPU
-(metric: images/s, summed over GPUs; every rank runs its own 256 images, no collective on the data path).
-Single-operator workloads (--workload depthwise3x3_s1 ... ) report HBM GB/s or int8 TOPS of that operator.
+One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of seeded synthetic input.
+The default workload is the whole MobileNetV2-1.0 224x224 uint8 graph on ONE batch of 256 images: at N GPUs
+(torchrun, one process per GPU) the batch is partitioned into contiguous slices of 256 / N images, every rank runs
+its slice, there is no collective on the data path, and only the 256 x 1000 logits are gathered on rank 0
+(metric: images/s of the whole job; "scaling": "strong").  Single-operator workloads (--workload depthwise3x3_s1 ...)
+report HBM GB/s or int8 TOPS of that operator.
 
-`value` is measured with inputs resident in HBM (CUDA events on the library's stream); `e2e` is the same
-metric through the operator-list C ABI with HOST buffers: host->device copy of the batch, the graph, and the
-device->host copy of the result inside the timed region.  `--impl reference` times the CPU oracle (the
-reference has no CPU implementation of these operators and its OpenCL path cannot run on this machine) on a
-bounded sample of the same workload, with all host threads.
+`value` is measured with inputs resident in HBM (CUDA events on the library's streams); `e2e` is the same metric
+through the operator-list C ABI with HOST buffers: host->device copy of every step's images, the graph, the
+device->host copy of the logits and, at N > 1, the gather of all ranks' logits on rank 0 inside the timed region.
+A rank may run several operator lists ("lanes", each with its own stream, buffers and CUDA graph) and hand
+successive steps to them in turn, so that the kernels of neighbouring steps fill SMs a small slice leaves idle.
+`--impl reference` times the CPU oracle (the reference has no CPU implementation of these operators and its OpenCL
+path cannot run on this machine) on a bounded sample of the same workload, with all host threads.
 """
 import argparse
 import ctypes as C
@@ -28,22 +32,35 @@ import time
 import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "cl-eden-kernel_b200")
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 DEFAULT_WORKLOAD = "mobilenetv2_u8_b256"
+GLOBAL_BATCH = 256
+WORKLOAD_TEXT = "MobileNetV2-1.0 224x224 uint8 graph (per-channel int8 weights), one batch of 256 images partitioned over the GPUs"
+
+# DRAM traffic of the graph's kernels from one ncu pass over a batch-32 graph replay (profiles/mobilenetv2_graph_dram.md),
+# as measured bytes / algorithmic bytes per kernel family; activations dominate, so traffic grows in proportion to the batch.
+NCU_TRAFFIC_RATIO = {}
 
 
 def load_package():
     name = "cl_eden_kernel_b200"
     if name in sys.modules:
         return sys.modules[name]
-    pkg = os.path.join(ROOT, "cl-eden-kernel_b200")
-    spec = importlib.util.spec_from_file_location(name, os.path.join(pkg, "__init__.py"), submodule_search_locations=[pkg])
+    spec = importlib.util.spec_from_file_location(name, os.path.join(PKG, "__init__.py"), submodule_search_locations=[PKG])
     mod = importlib.util.module_from_spec(spec)
     sys.modules[name] = mod
     spec.loader.exec_module(mod)
     return mod
+
+
+def load_plain(modname):
+    """A module of the package directory loaded on its own (descriptors, workloads, graph builder): the CPU arm uses
+    these without importing the package, i.e. without loading the CUDA library."""
+    if PKG not in sys.path:
+        sys.path.insert(0, PKG)
+    return importlib.import_module(modname)
 
 
 def measured_peaks():
@@ -53,6 +70,13 @@ def measured_peaks():
             d = json.load(f)
         return {"hbm_gbs": d.get("hbm_gbs", 6650.0), "bf16_tflops": d.get("bf16_tflops", 1590.0), "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 class ClockSampler:
@@ -106,7 +130,7 @@ class ClockSampler:
 
 
 class Cuda:
-    """The few runtime calls the benchmark needs on the library's own stream (events, memset)."""
+    """The few runtime calls the benchmark needs on the library's own streams (events, graph capture)."""
 
     def __init__(self):
         rt = C.CDLL("libcudart.so")
@@ -114,7 +138,7 @@ class Cuda:
         rt.cudaEventRecord.argtypes = [C.c_void_p, C.c_void_p]
         rt.cudaEventSynchronize.argtypes = [C.c_void_p]
         rt.cudaEventElapsedTime.argtypes = [C.POINTER(C.c_float), C.c_void_p, C.c_void_p]
-        rt.cudaMemsetAsync.argtypes = [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]
+        rt.cudaStreamWaitEvent.argtypes = [C.c_void_p, C.c_void_p, C.c_uint]
         self.rt = rt
 
     def event(self):
@@ -125,8 +149,12 @@ class Cuda:
     def record(self, e, stream):
         assert self.rt.cudaEventRecord(e, stream) == 0
 
+    def stream_wait(self, stream, e):
+        assert self.rt.cudaStreamWaitEvent(stream, e, 0) == 0
+
     def elapsed_ms(self, e0, e1):
         ms = C.c_float()
+        assert self.rt.cudaEventSynchronize(e1) == 0
         assert self.rt.cudaEventElapsedTime(C.byref(ms), e0, e1) == 0
         return ms.value
 
@@ -167,8 +195,7 @@ def dist_env():
 # ---------------------------------------------------------------------------------------------------
 # Single-operator configurations (BASELINE configs 1-4), timed over rotating buffer sets larger than L2
 # ---------------------------------------------------------------------------------------------------
-def op_configs(enn):
-    import cases
+def op_configs(cases):
     return {
         "conv3x3_1x56x56x64": ("conv2d", lambda: cases.conv_case(seed=0), "tensor"),
         "conv3x3_256x56x56x64": ("conv2d", lambda: cases.conv_case(seed=0, n=256), "tensor"),
@@ -183,39 +210,76 @@ def op_configs(enn):
         "mnv2_project_256x56x56x144to24": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=56, w=56, cin=144, cout=24, k=1, per_channel=True, out_scale=0.3, act=0, out_zp=128), "hbm"),
         "mnv2_project_256x112x112x32to16": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=112, w=112, cin=32, cout=16, k=1, per_channel=True, out_scale=0.3, act=0, out_zp=128), "hbm"),
         "mnv2_stem_256x224x224x3to32": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=224, w=224, cin=3, cout=32, k=3, stride=2, per_channel=True, out_scale=0.0235, out_zp=0), "hbm"),
+        "mnv2_dw_256x56x56x144_s1": ("depthwise", lambda: cases.depthwise_case(seed=0, n=256, h=56, w=56, c=144, in_zp=0, out_scale=0.0235), "hbm"),
+        "mnv2_dw_256x112x112x96_s2": ("depthwise", lambda: cases.depthwise_case(seed=0, n=256, h=112, w=112, c=96, stride=2, in_zp=0, out_scale=0.0235), "hbm"),
+        "mnv2_add_256x56x56x24": ("add", None, "hbm"),
+        "mnv2_pool_256x7x7x1280": ("avgpool", None, "hbm"),
     }
 
 
-def time_op(enn, ctx, cu, name, reps=20, warmup=3):
+KERNEL_OF_IMPL = {0: "conv_direct_kernel", 1: "tc_gemm_kernel", 2: "gemv_kernel", 3: "dw3x3_ring_kernel", 4: "eltwise"}
+
+
+def make_op(enn, ctx, cases, name):
+    """Prepared operator + its host inputs for one named configuration."""
+    kind, mk, bound = op_configs(cases)[name]
+    if kind == "add":
+        count = 256 * 56 * 56 * 24
+        rng = np.random.default_rng(0)
+        x = rng.integers(0, 256, count, dtype=np.int64).astype(np.uint8)
+        x2 = rng.integers(0, 256, count, dtype=np.int64).astype(np.uint8)
+        d = enn.AddDesc(count=count, activation=0, act_dtype=enn.U8, in0_scale=0.031, in0_zp=120, in1_scale=0.047, in1_zp=131,
+                        out_scale=0.06, out_zp=126)
+        return kind, bound, (d, x, x2), (lambda: enn.add(ctx, d))
+    if kind == "avgpool":
+        x = np.random.default_rng(0).integers(0, 256, (256, 7, 7, 1280), dtype=np.int64).astype(np.uint8)
+        d = enn.PoolDesc(n=256, h=7, w=7, c=1280, kh=7, kw=7, stride_h=1, stride_w=1, pad_t=0, pad_l=0, out_h=1, out_w=1,
+                         activation=0, act_dtype=enn.U8, out_scale=0.02, out_zp=0)
+        return kind, bound, (d, x, None), (lambda: enn.avgpool(ctx, d))
+    d, x, w, b, sc = mk()
+    return kind, bound, (d, x, w, b, sc), (lambda: getattr(enn, kind)(ctx, d, w, b, sc))
+
+
+def time_op(enn, ctx, cu, cases, name, reps=20, warmup=3):
     """Device-resident timing of one operator: `reps` back-to-back launches over rotating input/output
     buffer sets whose total size exceeds twice the L2, bracketed by CUDA events."""
-    kind, mk, bound = op_configs(enn)[name]
-    d, x, w, b, sc = mk()
-    op = getattr(enn, kind)(ctx, d, w, b, sc)
+    kind, bound, cfg, mk = make_op(enn, ctx, cases, name)
+    x = cfg[1]
+    x2 = cfg[2] if kind == "add" else None
+    wbytes = cfg[2].nbytes if kind not in ("add", "avgpool") else 0
+    op = mk()
     info = op.info
     # Operators whose traffic is mostly weights (FullyConnected) rotate over several prepared instances as well, so that
     # the weights of one launch have left the L2 before they are read again.
-    nops = int(min(24, -(-(280 << 20) // w.nbytes))) if w.nbytes >= (4 << 20) else 1
-    ops = [op] + [getattr(enn, kind)(ctx, d, w, b, sc) for _ in range(nops - 1)]
-    per_set = x.nbytes + info.out_bytes
+    nops = int(min(24, -(-(280 << 20) // wbytes))) if wbytes >= (4 << 20) else 1
+    ops = [op] + [mk() for _ in range(nops - 1)]
+    per_set = x.nbytes * (2 if x2 is not None else 1) + info.out_bytes
     nsets = int(max(2, min(64, -(-(280 << 20) // per_set))))
     xs = [ctx.to_device(x) for _ in range(nsets)]
+    x2s = [ctx.to_device(x2) for _ in range(nsets)] if x2 is not None else None
     ys = [ctx.malloc(max(1, info.out_bytes)) for _ in range(nsets)]
     reps = max(reps, nops)
+
+    def run(i):
+        if x2s is not None:
+            ops[i % nops].execute2(xs[i % nsets], x2s[i % nsets], ys[i % nsets])
+        else:
+            ops[i % nops].execute(xs[i % nsets], ys[i % nsets])
+
     for i in range(max(warmup, nops)):
-        ops[i % nops].execute(xs[i % nsets], ys[i % nsets])
+        run(i)
     ctx.sync()
     e0, e1 = cu.event(), cu.event()
     cu.record(e0, ctx.stream)
     for i in range(reps):
-        ops[i % nops].execute(xs[i % nsets], ys[i % nsets])
+        run(i)
     cu.record(e1, ctx.stream)
     ctx.sync()
     ms_eager = cu.elapsed_ms(e0, e1) / reps
     # The same `reps` launches captured once into a CUDA graph and replayed: operators of a few microseconds are bound by
     # the host's launch rate when every call comes from the Python loop above, and the graph shows the device's time.
     ms, timing = ms_eager, "eager launches"
-    exe = cu.capture(ctx.stream, lambda: [ops[i % nops].execute(xs[i % nsets], ys[i % nsets]) for i in range(reps)])
+    exe = cu.capture(ctx.stream, lambda: [run(i) for i in range(reps)])
     if exe is not None:
         cu.launch_graph(exe, ctx.stream)
         ctx.sync()
@@ -228,7 +292,7 @@ def time_op(enn, ctx, cu, name, reps=20, warmup=3):
         cu.destroy_graph(exe)
         if ms_graph < ms_eager:
             ms, timing = ms_graph, "CUDA graph of the same launches"
-    for p in xs + ys:
+    for p in xs + ys + (x2s or []):
         ctx.free(p)
     res = dict(workload=name, impl=int(info.impl), bound=bound, ms=ms, launches_per_step=int(info.kernel_launches),
                tops=2 * info.macs / (ms * 1e-3) / 1e12, gbs=info.algorithmic_bytes / (ms * 1e-3) / 1e9,
@@ -236,77 +300,206 @@ def time_op(enn, ctx, cu, name, reps=20, warmup=3):
                ms_eager=ms_eager)
     for o in ops:
         o.release()
-    return res, (d, x, w, b, sc, kind)
+    return res, (kind, cfg)
+
+
+def cpu_baseline_op(kind, cfg, max_seconds=3.0):
+    """The oracle's version of one operator on a bounded slice of its batch: (seconds per call, rows taken, rows)."""
+    from oracle import orc
+    orc.set_num_threads(host_threads())
+    if kind == "add":
+        d, x, x2 = cfg
+        total = int(d.count)
+        ns = min(total, 1 << 22)
+        ds = type(d).from_buffer_copy(d)
+        ds.count = ns
+        fn = lambda: orc.add(ds, x[:ns], x2[:ns])
+    elif kind == "avgpool":
+        d, x, _ = cfg
+        total, ns = d.n, min(d.n, 64)
+        ds = type(d).from_buffer_copy(d)
+        ds.n = ns
+        xs = np.ascontiguousarray(x[:ns])
+        fn = lambda: orc.avgpool(ds, xs)
+    else:
+        d, x, w, b, sc = cfg
+        f = getattr(orc, kind)
+        ds = type(d).from_buffer_copy(d)
+        if kind == "fully_connected":
+            ns, total = min(d.m, 64), d.m
+            ds.m = ns
+        else:
+            ns, total = min(d.n, 8), d.n
+            ds.n = ns
+        xs = np.ascontiguousarray(x[:ns])
+        fn = lambda: f(ds, xs, w, b, sc)
+    fn()
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        fn()
+        reps += 1
+        if time.perf_counter() - t0 > max_seconds or reps >= 20:
+            break
+    return (time.perf_counter() - t0) / reps, ns, total, reps
 
 
 # ---------------------------------------------------------------------------------------------------
 # MobileNetV2 graph
 # ---------------------------------------------------------------------------------------------------
-KERNEL_OF_IMPL = {0: "conv_direct_kernel", 1: "tc_gemm_kernel", 2: "gemv", 3: "dw3x3_kernel", 4: "eltwise"}
+def kernel_of_layer(L, impl):
+    if L["kind"] == "conv" and L["cin"] == 3:
+        return "conv3x3c3_kernel"
+    if L["kind"] == "add":
+        return "add_kernel_lut2"
+    if L["kind"] == "pool":
+        return "avgpool_vec4_kernel"
+    return KERNEL_OF_IMPL.get(impl, "other")
 
 
-def run_mobilenet(args, enn, ctx, cu, rank, world, local, barrier, batch=256):
+class Lane:
+    """One operator list with its own context (stream), buffers, CUDA graph and pinned host buffers."""
+
+    def __init__(self, enn, mn, device, layers, batch, x, out_bytes):
+        self.enn = enn
+        self.ctx = enn.Context(device)
+        self.ol, self.info = mn.make_oplist(enn, self.ctx, layers, batch)
+        self.ctx.upload(self.ol.tensor_ptr(self.info["tensor_ids"]["input"]), x)
+        self.host = []
+        for _ in range(2):
+            hin, hout = C.c_void_p(), C.c_void_p()
+            assert enn.lib.enn_b200_host_alloc(x.nbytes, C.byref(hin)) == 0
+            assert enn.lib.enn_b200_host_alloc(out_bytes, C.byref(hout)) == 0
+            C.memmove(hin, x.ctypes.data, x.nbytes)
+            self.host.append((hin.value, hout.value))
+        self.out_bytes = out_bytes
+        self.n = 0
+
+    def submit(self):
+        hin, hout = self.host[self.n & 1]
+        self.ol.submit_host_ptrs([hin], [hout])
+        self.n += 1
+        return hout
+
+    def logits(self, which):
+        return np.ctypeslib.as_array((C.c_uint8 * self.out_bytes).from_address(self.host[which][1])).copy()
+
+
+class DevView:
+    """Zero-copy view of device bytes for torch (CUDA array interface)."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+
+
+def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist):
     mn = importlib.import_module("cl_eden_kernel_b200.mobilenet")
     layers, _ = mn.build_model(seed=0, calib_images=1)
-    x = np.random.default_rng(1000 + rank).integers(0, 256, (batch, 224, 224, 3), dtype=np.int64).astype(np.uint8)
-    ol, info = mn.make_oplist(enn, ctx, layers, batch)
-    stats = ol.stats()
-    in_ptr = ol.tensor_ptr(info["tensor_ids"]["input"])
-    ctx.upload(in_ptr, x)
-    stream = ctx.stream
+    if GLOBAL_BATCH % world:
+        raise SystemExit(f"the {GLOBAL_BATCH}-image batch does not split over {world} GPUs")
+    per_rank = GLOBAL_BATCH // world
+    x_full = np.random.default_rng(1000).integers(0, 256, (GLOBAL_BATCH, 224, 224, 3), dtype=np.int64).astype(np.uint8)
+    x = np.ascontiguousarray(x_full[rank * per_rank:(rank + 1) * per_rank])
+    classes = layers[-1]["cout"]
+    out_bytes = per_rank * classes
+    multi = world > 1
+
+    # ---- lanes: how many operator lists share this GPU.  "auto" times 1, 2 and 3 on a few steps and keeps the best. ----
+    max_lanes = args.lanes if args.lanes > 0 else 3
+    lanes = [Lane(enn, mn, local, layers, per_rank, x, out_bytes) for _ in range(max_lanes)]
+    info = lanes[0].info
+    stats = lanes[0].ol.stats()
+
+    def device_steps(use, steps):
+        """`steps` graph launches handed to the first `use` lanes in turn; device time between the first launch and
+        the completion of the last, measured on lane 0's stream."""
+        e0, e1 = cu.event(), cu.event()
+        tails = [cu.event() for _ in range(use)]
+        for l in lanes[:use]:
+            l.ctx.sync()
+        cu.record(e0, lanes[0].ctx.stream)
+        for i in range(steps):
+            lanes[i % use].ol.execute_device()
+        for k in range(1, use):
+            cu.record(tails[k], lanes[k].ctx.stream)
+            cu.stream_wait(lanes[0].ctx.stream, tails[k])
+        cu.record(e1, lanes[0].ctx.stream)
+        return cu.elapsed_ms(e0, e1)
+
+    for l in lanes:
+        for _ in range(args.warmup):
+            l.ol.execute_device()
+        l.ctx.sync()
+    if args.lanes > 0:
+        use = args.lanes
+        lane_trials = None
+    else:
+        lane_trials = {}
+        for s in range(1, max_lanes + 1):
+            device_steps(s, 2 * s)
+            lane_trials[s] = device_steps(s, 6 * s) / (6 * s)
+        if multi:      # every rank must make the same choice: take rank 0's
+            t = torch.tensor([lane_trials[s] for s in sorted(lane_trials)], device="cuda", dtype=torch.float64)
+            dist.broadcast(t, 0)
+            lane_trials = {s: v for s, v in zip(sorted(lane_trials), t.tolist())}
+        use = min(lane_trials, key=lane_trials.get)
 
     # ---- device-resident: K graph launches between two events ----
-    for _ in range(args.warmup):
-        ol.execute_device()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     barrier()
-    e0, e1 = cu.event(), cu.event()
-    cu.record(e0, stream)
-    for _ in range(args.steps):
-        ol.execute_device()
-    cu.record(e1, stream)
+    total_ms = device_steps(use, args.steps)
     barrier()
-    total_ms = cu.elapsed_ms(e0, e1)
 
-    # ---- end to end: host buffers (pinned) through enn_b200_oplist_execute ----
-    hin, hout = C.c_void_p(), C.c_void_p()
-    out_bytes = batch * layers[-1]["cout"]
-    enn.lib.enn_b200_host_alloc(x.nbytes, C.byref(hin))
-    enn.lib.enn_b200_host_alloc(out_bytes, C.byref(hout))
-    C.memmove(hin, x.ctypes.data, x.nbytes)
-    # Two pinned input / output buffer pairs alternate, as a caller streaming batches would; every step copies its
-    # 38.5 MB batch host->device and its logits device->host (enn_b200_oplist_submit overlaps the copy-in of step
-    # i+1 with the operators of step i); the region ends when the last result has landed (enn_b200_oplist_wait).
-    hin2, hout2 = C.c_void_p(), C.c_void_p()
-    enn.lib.enn_b200_host_alloc(x.nbytes, C.byref(hin2))
-    enn.lib.enn_b200_host_alloc(out_bytes, C.byref(hout2))
-    C.memmove(hin2, x.ctypes.data, x.nbytes)
-    host_pairs = [(hin.value, hout.value), (hin2.value, hout2.value)]
-    for i in range(2):
-        ol.submit_host_ptrs([host_pairs[i][0]], [host_pairs[i][1]])
-    ol.wait()
+    # ---- end to end: host buffers (pinned) through enn_b200_oplist_submit / _wait, logits gathered on rank 0 ----
+    # Every step copies its images host->device and its logits device->host (the copy-in of a step overlaps the
+    # operators of the step before); at N > 1 every step's logits also travel to rank 0 (NCCL gather of the device
+    # copy, ordered on the lane's stream, then device->host there).  The region ends when the last result has landed.
+    ext, src_views, gath, gath_host = None, None, None, None
+    if multi:
+        ext = [torch.cuda.ExternalStream(l.ctx.stream.value if hasattr(l.ctx.stream, "value") else int(l.ctx.stream)) for l in lanes[:use]]
+        if rank == 0:
+            gath = [torch.empty((world, out_bytes), dtype=torch.uint8, device="cuda") for _ in range(use)]
+            gath_host = [torch.empty((world, out_bytes), dtype=torch.uint8).pin_memory() for _ in range(use)]
+
+    def e2e_steps(steps):
+        for i in range(steps):
+            k = i % use
+            lanes[k].submit()
+            if multi:
+                with torch.cuda.stream(ext[k]):
+                    src = torch.as_tensor(DevView(lanes[k].ol.last_output_ptr(0).value, out_bytes), device="cuda")
+                    dist.gather(src, list(gath[k].unbind(0)) if rank == 0 else None, dst=0)
+                    if rank == 0:
+                        gath_host[k].copy_(gath[k], non_blocking=True)
+        for l in lanes[:use]:
+            l.ol.wait()
+
+    e2e_steps(2 * use)
     barrier()
-    t0 = cu.event()
-    t1 = cu.event()
-    cu.record(t0, stream)
-    for i in range(args.steps):
-        ol.submit_host_ptrs([host_pairs[i & 1][0]], [host_pairs[i & 1][1]])
-    ol.wait()
-    cu.record(t1, stream)
+    t0, t1 = cu.event(), cu.event()
+    tails = [cu.event() for _ in range(use)]
+    cu.record(t0, lanes[0].ctx.stream)
+    e2e_steps(args.steps)
+    for k in range(1, use):
+        cu.record(tails[k], lanes[k].ctx.stream)
+        cu.stream_wait(lanes[0].ctx.stream, tails[k])
+    cu.record(t1, lanes[0].ctx.stream)
     barrier()
     e2e_ms = cu.elapsed_ms(t0, t1)
     clocks = sampler.stop() if rank == 0 else None
-    logits = np.ctypeslib.as_array((C.c_uint8 * out_bytes).from_address(hout.value)).copy()
+    logits = lanes[0].logits(1 if (lanes[0].n & 1) == 0 else 0).reshape(per_rank, classes)   # the buffer of lane 0's latest step
+    gathered = gath_host[0].numpy().reshape(GLOBAL_BATCH, classes).copy() if multi and rank == 0 else None
 
     # ---- per-layer timing (rank 0): which kernel dominates, and its achieved bandwidth ----
     per_kernel = {}
     if rank == 0:
+        ctx, ol = lanes[0].ctx, lanes[0].ol
         tid = info["tensor_ids"]
-        # eager per-layer timing uses fresh operator handles on private buffers (graph nodes are owned by the list)
+        # eager per-layer timing uses fresh operator handles on the list's buffers (graph nodes are owned by the list)
         for L, pl in zip(layers, info["per_layer"]):
-            d = mn.layer_descs(enn, L, batch)
+            d = mn.layer_descs(enn, L, per_rank)
             if L["kind"] == "conv":
                 op = enn.conv2d(ctx, d, L["w"], L["bias"], L["scales"])
             elif L["kind"] == "dw":
@@ -323,13 +516,13 @@ def run_mobilenet(args, enn, ctx, cu, rank, world, local, barrier, batch=256):
             run = (lambda: op.execute2(a, b2, o)) if b2 is not None else (lambda: op.execute(a, o))
             run()
             ea, eb = cu.event(), cu.event()
-            cu.record(ea, stream)
+            cu.record(ea, ctx.stream)
             for _ in range(5):
                 run()
-            cu.record(eb, stream)
+            cu.record(eb, ctx.stream)
             ctx.sync()
             ms = cu.elapsed_ms(ea, eb) / 5
-            k = KERNEL_OF_IMPL.get(pl["impl"], "other")
+            k = kernel_of_layer(L, pl["impl"])
             acc = per_kernel.setdefault(k, dict(ms=0.0, bytes=0, macs=0, launches=0))
             acc["ms"] += ms
             acc["bytes"] += pl["bytes"]
@@ -337,57 +530,45 @@ def run_mobilenet(args, enn, ctx, cu, rank, world, local, barrier, batch=256):
             acc["launches"] += pl["launches"]
             op.release()
     ol_info = dict(macs=info["macs"], bytes=info["bytes"], launches=info["launches"], stats=stats, layers=len(layers))
-    return dict(total_ms=total_ms, e2e_ms=e2e_ms, clocks=clocks, units_per_step=batch, h2d=int(x.nbytes), d2h=int(out_bytes),
-                per_kernel=per_kernel, info=ol_info, logits_checksum=int(logits.astype(np.int64).sum()), layers=layers, x=x)
+    return dict(total_ms=total_ms, e2e_ms=e2e_ms, clocks=clocks, per_rank=per_rank, h2d=int(x.nbytes), d2h=int(out_bytes),
+                per_kernel=per_kernel, info=ol_info, logits=logits, gathered=gathered, layers=layers, x=x, x_full=x_full,
+                lanes=use, lane_trials=lane_trials, mn=mn, lane_objs=lanes)
 
 
 def cpu_baseline_mobilenet(layers, x, max_images=8):
-    """The oracle graph timed on the host cores over a bounded sample of the batch."""
-    import mobilenet_ref
-    from oracle import orc
+    """The oracle graph timed on the host cores over a bounded sample of the batch; also returns its logits."""
+    from oracle import mobilenet_ref, orc
+    orc.set_num_threads(host_threads())
+    types, mn = load_plain("abi_types"), load_plain("mobilenet")
     xs = np.ascontiguousarray(x[:max_images])
-    mobilenet_ref.run_oracle(layers, xs[:1])
+    y = mobilenet_ref.run_oracle(layers, xs, types=types, mobilenet=mn)
     t0 = time.perf_counter()
     reps = 0
     while True:
-        mobilenet_ref.run_oracle(layers, xs)
+        mobilenet_ref.run_oracle(layers, xs, types=types, mobilenet=mn)
         reps += 1
         if time.perf_counter() - t0 > 8.0 or reps >= 10:
             break
     dt = (time.perf_counter() - t0) / reps
     return {"value": len(xs) / dt, "unit": "images/s", "cores": orc.num_threads(), "kind": "port",
-            "sample": f"{len(xs)} of {x.shape[0]} images of the same MobileNetV2-u8 graph, {reps} repetitions, {dt * 1e3:.0f} ms each"}
+            "sample": f"{len(xs)} of {x.shape[0]} images of the same MobileNetV2-u8 graph, {reps} repetitions, {dt * 1e3:.0f} ms each"}, y
 
 
-def cpu_baseline_op(cfg, max_seconds=8.0):
-    from oracle import orc
-    d, x, w, b, sc, kind = cfg
-    fn = getattr(orc, kind)
-    if kind == "fully_connected":
-        ns, total = min(d.m, 64), d.m
-        ds = type(d).from_buffer_copy(d)
-        ds.m = ns
-    else:
-        ns, total = min(d.n, 8), d.n
-        ds = type(d).from_buffer_copy(d)
-        ds.n = ns
-    xs = np.ascontiguousarray(x[:ns])
-    fn(ds, xs, w, b, sc)
-    t0 = time.perf_counter()
-    reps = 0
-    while True:
-        fn(ds, xs, w, b, sc)
-        reps += 1
-        if time.perf_counter() - t0 > max_seconds or reps >= 20:
-            break
-    dt = (time.perf_counter() - t0) / reps
-    return dt, ns, total, reps
+def graph_config(mn, layers, world):
+    """The `config` object of the default workload; the same for both arms."""
+    per_rank = GLOBAL_BATCH // max(1, world)
+    macs, nbytes = mn.graph_work(layers, GLOBAL_BATCH)
+    return {"workload": WORKLOAD_TEXT, "global_batch": GLOBAL_BATCH, "images_per_gpu": per_rank,
+            "l2": "no flush needed: the activations a step streams (several hundred MB per GPU) exceed the 126 MB L2",
+            "sharding": f"contiguous slices of {per_rank} images per rank; no collective on the data path; the {GLOBAL_BATCH} x 1000 logits are gathered on rank 0",
+            "ops_per_step": len(layers), "gmacs_per_step": macs / 1e9, "algorithmic_gbytes_per_step": nbytes / 1e9}
 
 
 def run_ours(args):
     import torch
     import torch.distributed as dist
     enn = load_package()
+    cases = importlib.import_module("cl_eden_kernel_b200.workloads")
     rank, world, local = dist_env()
     if world > 1 and args.gpus != world:
         raise SystemExit("--gpus must equal WORLD_SIZE under torchrun")
@@ -408,14 +589,14 @@ def run_ours(args):
     peaks = measured_peaks()
     result = None
     if args.workload == DEFAULT_WORKLOAD:
-        r = run_mobilenet(args, enn, ctx, cu, rank, world, local, barrier)
+        r = run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist)
         total_ms, e2e_ms = r["total_ms"], r["e2e_ms"]
         if multi:
             t = torch.tensor([total_ms, e2e_ms], device="cuda", dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             total_ms, e2e_ms = t.tolist()
         if rank == 0:
-            units = r["units_per_step"] * world * args.steps
+            units = GLOBAL_BATCH * args.steps
             pk = r["per_kernel"]
             dom = max(pk, key=lambda k: pk[k]["ms"]) if pk else None
             roof = None
@@ -423,68 +604,101 @@ def run_ours(args):
                 launches = max(1, pk[dom]["launches"])
                 avg_ms = pk[dom]["ms"] / launches
                 ach = pk[dom]["bytes"] / (pk[dom]["ms"] * 1e-3) / 1e9
+                ratio = NCU_TRAFFIC_RATIO.get(dom)
                 roof = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                        "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                        "frac": ach / peaks["hbm_gbs"],
+                        "traffic": pk[dom]["bytes"] / launches * ratio if ratio else None,
+                        "algorithmic_bytes_per_launch": pk[dom]["bytes"] / launches,
+                        "peak_source": peaks["source"],
                         "avg_launch_ms": avg_ms, "launches_per_step": launches,
                         "share_of_step": pk[dom]["ms"] / sum(v["ms"] for v in pk.values()),
-                        "per_kernel_ms": {k: round(v["ms"], 4) for k, v in pk.items()}}
+                        "per_kernel_ms": {k: round(v["ms"], 4) for k, v in pk.items()},
+                        "per_kernel_frac_of_hbm": {k: round(v["bytes"] / (v["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 3) for k, v in pk.items()}}
             result = {
                 "metric": "mobilenetv2_u8_images_per_s", "value": units / (total_ms * 1e-3), "unit": "images/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-                "config": {"workload": "MobileNetV2-1.0 224x224 uint8 graph (per-channel int8 weights), batch 256 per GPU",
-                           "l2": f"working set {r['info']['stats']['device_bytes'] >> 20} MiB of activations per step exceeds the 126 MB L2",
-                           "sharding": "each rank runs its own 256 images; no collective on the data path",
-                           "ops_per_step": r["info"]["layers"], "gmacs_per_step": r["info"]["macs"] / 1e9,
-                           "algorithmic_gbytes_per_step": r["info"]["bytes"] / 1e9},
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+                "config": graph_config(r["mn"], r["layers"], world),
                 "roofline": roof,
-                "e2e": {"value": units / (e2e_ms * 1e-3), "unit": "images/s", "h2d_bytes_per_step": r["h2d"],
-                        "d2h_bytes_per_step": r["d2h"]},
+                "e2e": {"value": units / (e2e_ms * 1e-3), "unit": "images/s", "h2d_bytes_per_step": r["h2d"] * world,
+                        "d2h_bytes_per_step": r["d2h"] * world},
                 "gpu_launches": int(r["info"]["launches"] * args.steps),
                 "clocks": r["clocks"],
-                "logits_checksum": r["logits_checksum"],
+                "logits_checksum": int(r["logits"].astype(np.int64).sum()),
             }
+            result["lanes_per_gpu"] = r["lanes"]
+            result["device_bytes_per_lane"] = r["info"]["stats"]["device_bytes"]
+            if r["lane_trials"]:
+                result["lane_trial_ms_per_step"] = {str(k): round(v, 4) for k, v in r["lane_trials"].items()}
+            if multi:
+                # The gathered logits of the partitioned run against the same 256 images on this GPU alone.
+                lane = Lane(enn, r["mn"], local, r["layers"], GLOBAL_BATCH, r["x_full"], GLOBAL_BATCH * r["layers"][-1]["cout"])
+                lane.submit()
+                lane.ol.wait()
+                full = lane.logits(0).reshape(GLOBAL_BATCH, -1)
+                if not np.array_equal(full, r["gathered"]):
+                    raise SystemExit("gathered logits of the partitioned batch differ from the single-GPU result")
+                result["gathered_equals_single_gpu"] = True
+                lane.ol.destroy()
             if world == 1 and not args.skip_cpu_baseline:
-                result["cpu_baseline"] = cpu_baseline_mobilenet(r["layers"], r["x"])
+                result["cpu_baseline"], y_ref = cpu_baseline_mobilenet(r["layers"], r["x"])
+                if not np.array_equal(r["logits"][:len(y_ref)], y_ref.reshape(len(y_ref), -1)):
+                    raise SystemExit("logits of the timed graph differ from the CPU oracle")
+                result["parity_checked_images"] = int(len(y_ref))
             if world == 1 and not args.skip_per_op:
                 per_op = []
                 i8_peak = ctx.mma_peak(2, 256, 16384)      # kind::i8 on pseudo-random operand bytes
-                for name in op_configs(enn):
+                for name in op_configs(cases):
                     if name.startswith("mnv2_"):
                         continue
-                    res, _ = time_op(enn, ctx, cu, name)
+                    res, (kind, cfg) = time_op(enn, ctx, cu, cases, name)
                     res["frac_of_hbm_measured"] = res["gbs"] / peaks["hbm_gbs"]
                     res["frac_of_int8_tensor_measured"] = res["tops"] / i8_peak
                     res["frac_of_int8_tensor_nominal_4500"] = res["tops"] / 4500.0
+                    if not args.skip_cpu_baseline:
+                        dt, ns, total, reps = cpu_baseline_op(kind, cfg, max_seconds=1.5)
+                        res["cpu_baseline"] = {"ms_full_op_extrapolated": dt * 1e3 * total / ns, "cores": host_threads(), "kind": "port",
+                                               "sample": f"{ns} of {total} batch rows, {reps} repetitions, {dt * 1e3:.1f} ms each"}
                     per_op.append(res)
                 result["per_op"] = per_op
                 result["int8_tensor_peak_measured_tops"] = i8_peak
                 result["int8_tensor_peak_zero_operands_tops"] = ctx.mma_peak(0, 256, 16384)
     else:
-        res, cfg = time_op(enn, ctx, cu, args.workload, reps=args.steps, warmup=args.warmup)
-        d, x, w, b, sc, kind = cfg
+        res, (kind, cfg) = time_op(enn, ctx, cu, cases, args.workload, reps=args.steps, warmup=args.warmup)
         # end to end: one operator through upload / execute / download with pinned host buffers
-        op = getattr(enn, kind)(ctx, d, w, b, sc)
+        _, _, _, mk = make_op(enn, ctx, cases, args.workload)
+        op = mk()
         info = op.info
-        hin, hout = C.c_void_p(), C.c_void_p()
+        x = cfg[1]
+        x2 = cfg[2] if kind == "add" else None
+        hin, hin2, hout = C.c_void_p(), C.c_void_p(), C.c_void_p()
         enn.lib.enn_b200_host_alloc(x.nbytes, C.byref(hin))
+        enn.lib.enn_b200_host_alloc(x.nbytes, C.byref(hin2))
         enn.lib.enn_b200_host_alloc(max(1, info.out_bytes), C.byref(hout))
         C.memmove(hin, x.ctypes.data, x.nbytes)
-        xd, yd = ctx.malloc(x.nbytes), ctx.malloc(max(1, info.out_bytes))
+        if x2 is not None:
+            C.memmove(hin2, x2.ctypes.data, x2.nbytes)
+        xd, x2d, yd = ctx.malloc(x.nbytes), ctx.malloc(x.nbytes), ctx.malloc(max(1, info.out_bytes))
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        for _ in range(2):
+
+        def e2e_once():
             enn.lib.enn_b200_upload(ctx.h, xd, hin, x.nbytes)
-            op.execute(xd, yd)
+            if x2 is not None:
+                enn.lib.enn_b200_upload(ctx.h, x2d, hin2, x.nbytes)
+                op.execute2(xd, x2d, yd)
+            else:
+                op.execute(xd, yd)
             enn.lib.enn_b200_download(ctx.h, hout, yd, info.out_bytes)
+
+        for _ in range(2):
+            e2e_once()
         barrier()
         e0, e1 = cu.event(), cu.event()
         cu.record(e0, ctx.stream)
         for _ in range(args.steps):
-            enn.lib.enn_b200_upload(ctx.h, xd, hin, x.nbytes)
-            op.execute(xd, yd)
-            enn.lib.enn_b200_download(ctx.h, hout, yd, info.out_bytes)
+            e2e_once()
         cu.record(e1, ctx.stream)
         barrier()
         e2e_ms = cu.elapsed_ms(e0, e1) / args.steps
@@ -501,26 +715,26 @@ def run_ours(args):
             i8_peak = ctx.mma_peak(2, 256, 16384)      # kind::i8 on pseudo-random operand bytes
             peak = peaks["hbm_gbs"] if hbm else i8_peak
             ach = per_step / (res["ms"] * 1e-3)
+            kname = {"depthwise": "dw3x3_ring_kernel", "add": "add_kernel_lut2", "avgpool": "avgpool_vec4_kernel"}.get(kind, KERNEL_OF_IMPL.get(res["impl"]))
             result = {
                 "metric": ("hbm_gbs_" if hbm else "int8_tops_") + args.workload, "value": world * per_step / (ms * 1e-3),
                 "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
                 "config": {"workload": args.workload, "l2": f"{res['buffer_sets']} rotating input/output buffer sets, together larger than twice the L2",
                            "sharding": "independent replicas per rank, no collective"},
-                "roofline": {"bound": "hbm" if hbm else "tensor", "kernel": KERNEL_OF_IMPL.get(res["impl"]), "achieved": ach, "peak": peak,
+                "roofline": {"bound": "hbm" if hbm else "tensor", "kernel": kname, "achieved": ach, "peak": peak,
                              "unit": unit, "frac": ach / peak, "traffic": None,
                              "peak_source": peaks["source"] if hbm else "measured tcgen05.mma kind::i8 rate on random operand bytes (enn_b200_measure_mma_peak)",
                              "frac_of_nominal_4500_tops": None if hbm else ach / 4500.0},
-                "e2e": {"value": world * per_step / (e2e_ms * 1e-3), "unit": unit, "h2d_bytes_per_step": int(x.nbytes),
+                "e2e": {"value": world * per_step / (e2e_ms * 1e-3), "unit": unit, "h2d_bytes_per_step": int(x.nbytes * (2 if x2 is not None else 1)),
                         "d2h_bytes_per_step": int(info.out_bytes)},
                 "gpu_launches": int(res["launches_per_step"] * args.steps),
                 "clocks": clocks,
             }
             if world == 1 and not args.skip_cpu_baseline:
-                dt, ns, total, reps = cpu_baseline_op(cfg)
+                dt, ns, total, reps = cpu_baseline_op(kind, cfg, max_seconds=8.0)
                 frac = ns / total
-                from oracle import orc
-                result["cpu_baseline"] = {"value": per_step * frac / dt, "unit": unit, "cores": orc.num_threads(), "kind": "port",
+                result["cpu_baseline"] = {"value": per_step * frac / dt, "unit": unit, "cores": host_threads(), "kind": "port",
                                           "sample": f"{ns} of {total} batch rows of {args.workload}, {reps} repetitions, {dt * 1e3:.1f} ms each"}
     if rank == 0 and result is not None:
         print(json.dumps(result), flush=True)
@@ -529,38 +743,50 @@ def run_ours(args):
 
 
 def run_reference(args):
-    """The CPU oracle on the host cores: K steps, each a bounded sample of the workload."""
+    """The CPU oracle on the host cores: K steps, each a bounded sample of the workload.  Loads the descriptors, the
+    workload generators and the oracle only; the CUDA library is not touched."""
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    enn = load_package()
-    from oracle import orc
+    from oracle import mobilenet_ref, orc
+    orc.set_num_threads(host_threads())          # a launcher may have set OMP_NUM_THREADS=1 for its ranks
+    types, cases = load_plain("abi_types"), load_plain("workloads")
     if args.workload == DEFAULT_WORKLOAD:
-        import mobilenet_ref
-        mn = importlib.import_module("cl_eden_kernel_b200.mobilenet")
+        mn = load_plain("mobilenet")
         layers, _ = mn.build_model(seed=0, calib_images=1)
         n = 8
         x = np.random.default_rng(1000).integers(0, 256, (n, 224, 224, 3), dtype=np.int64).astype(np.uint8)
         for _ in range(args.warmup):
-            mobilenet_ref.run_oracle(layers, x[:2])
+            mobilenet_ref.run_oracle(layers, x[:2], types=types, mobilenet=mn)
         t0 = time.perf_counter()
         for _ in range(args.steps):
-            mobilenet_ref.run_oracle(layers, x)
+            mobilenet_ref.run_oracle(layers, x, types=types, mobilenet=mn)
         dt = (time.perf_counter() - t0) / args.steps
         v, unit, metric = n / dt, "images/s", "mobilenetv2_u8_images_per_s"
-        sample = f"each step = {n} images (of the 256-image batch) through the CPU oracle graph"
-        cfg = {"workload": "MobileNetV2-1.0 224x224 uint8 graph (per-channel int8 weights), batch 256 per GPU"}
+        sample = f"each step = the first {n} images of the {GLOBAL_BATCH}-image batch through the CPU oracle graph"
+        cfg = graph_config(mn, layers, args.gpus)
+        scaling = "strong"
     else:
-        kind, mk, bound = op_configs(enn)[args.workload]
+        kind, mk, bound = op_configs(cases)[args.workload]
+        if mk is None:
+            print(json.dumps({"impl": "reference", "unavailable": "this profiling workload has no CPU arm"}), flush=True)
+            return
         d, x, w, b, sc = mk()
-        dt, ns, total, reps = cpu_baseline_op((d, x, w, b, sc, kind), max_seconds=3.0)
-        op_bytes = x.nbytes * ns / total
-        v, unit, metric = op_bytes / dt / 1e9, "GB/s (input bytes only)", "cpu_" + args.workload
+        dt, ns, total, reps = cpu_baseline_op(kind, (d, x, w, b, sc), max_seconds=3.0)
+        hbm = bound == "hbm"
+        if kind == "fully_connected":
+            macs, abytes = d.m * d.k * d.n, d.m * d.k + d.k * d.n + d.m * d.n + 12 * d.n
+        else:
+            abytes = x.nbytes + w.nbytes + 12 * d.cout
+            macs = 0
+        per_step = (abytes / 1e9 if hbm else 2 * macs / 1e12) * ns / total
+        v, unit, metric = per_step / dt, ("GB/s" if hbm else "TOP/s"), ("hbm_gbs_" if hbm else "int8_tops_") + args.workload
         sample = f"{ns} of {total} batch rows"
         cfg = {"workload": args.workload}
+        scaling = "weak"
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
         "dtype": "u8", "data": "synthetic", "config": cfg,
         "cpu_baseline": {"value": v, "unit": unit, "cores": orc.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -574,6 +800,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--lanes", type=int, default=0, help="operator lists per GPU that take the steps in turn (0: time 1..3 and keep the best)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU leg (profiling runs)")
     ap.add_argument("--skip-per-op", action="store_true", help="omit the single-operator table (profiling runs)")
     args = ap.parse_args()

@@ -14,64 +14,12 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libenn_b200.so")
 
-SUCCESS, FAILURE, CUDA_FAILURE, INVALID_PARAMS = 0, 1, 2, 3
-ACT_NONE, ACT_RELU, ACT_RELU1, ACT_RELU6 = 0, 1, 2, 3
-U8, S8 = 0, 1
-W_OIHW, W_OHWI, W_IOHW = 0, 1, 2
-IMPL_DIRECT, IMPL_TCGEN05, IMPL_GEMV, IMPL_DEPTHWISE, IMPL_ELTWISE = 0, 1, 2, 3, 4
-
-
-class ConvDesc(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in (
-        "n", "h", "w", "cin", "cout", "kh", "kw", "stride_h", "stride_w", "dil_h", "dil_w",
-        "pad_t", "pad_r", "pad_b", "pad_l", "groups", "activation", "act_dtype", "weight_dtype",
-        "weight_layout", "per_channel")] + [
-        ("in_scale", C.c_float), ("in_zp", C.c_int32), ("w_scale", C.c_float), ("w_zp", C.c_int32),
-        ("bias_scale", C.c_float), ("out_scale", C.c_float), ("out_zp", C.c_int32),
-        ("out_h", C.c_int32), ("out_w", C.c_int32)]
-
-
-class FcDesc(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("m", "k", "n", "activation", "act_dtype", "weight_dtype", "per_channel")] + [
-        ("in_scale", C.c_float), ("in_zp", C.c_int32), ("w_scale", C.c_float), ("w_zp", C.c_int32),
-        ("bias_scale", C.c_float), ("out_scale", C.c_float), ("out_zp", C.c_int32)]
-
-
-class AddDesc(C.Structure):
-    _fields_ = [("count", C.c_int64), ("activation", C.c_int32), ("act_dtype", C.c_int32),
-                ("in0_scale", C.c_float), ("in0_zp", C.c_int32), ("in1_scale", C.c_float), ("in1_zp", C.c_int32),
-                ("out_scale", C.c_float), ("out_zp", C.c_int32)]
-
-
-class PoolDesc(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("n", "h", "w", "c", "kh", "kw", "stride_h", "stride_w", "pad_t", "pad_l",
-                                          "out_h", "out_w", "activation", "act_dtype")] + [
-        ("out_scale", C.c_float), ("out_zp", C.c_int32)]
-
-
-class OpInfo(C.Structure):
-    _fields_ = [("impl", C.c_int32), ("out_n", C.c_int32), ("out_h", C.c_int32), ("out_w", C.c_int32),
-                ("out_c", C.c_int32), ("in_bytes", C.c_int64), ("out_bytes", C.c_int64), ("macs", C.c_int64),
-                ("algorithmic_bytes", C.c_int64), ("act_min", C.c_int32), ("act_max", C.c_int32),
-                ("kernel_launches", C.c_int32)]
-
-
-def conv_desc(**kw):
-    """ConvDesc with the reference's defaults (stride/dilation 1, one group, no activation, u8/u8, OHWI)."""
-    d = ConvDesc()
-    d.stride_h = d.stride_w = d.dil_h = d.dil_w = 1
-    d.groups = 1
-    d.weight_layout = W_OHWI
-    d.in_scale = d.w_scale = d.out_scale = 1.0
-    d.bias_scale = 1.0
-    for k, v in kw.items():
-        if not hasattr(d, k):
-            raise AttributeError(k)
-        setattr(d, k, v)
-    if "bias_scale" not in kw:
-        d.bias_scale = np.float32(d.in_scale) * np.float32(d.w_scale)
-    return d
-
+try:
+    from .abi_types import *          # noqa: F401,F403  (constants, descriptors, conv_desc)
+    from .abi_types import ConvDesc, FcDesc, AddDesc, PoolDesc, OpInfo
+except ImportError:                   # loaded as a plain module
+    from abi_types import *           # noqa: F401,F403
+    from abi_types import ConvDesc, FcDesc, AddDesc, PoolDesc, OpInfo
 
 # Every symbol include/enn_b200.h declares, with its prototype: (restype, argtypes).
 _P = C.c_void_p
@@ -112,8 +60,15 @@ PROTOTYPES = {
     "enn_b200_oplist_submit": (C.c_int32, [_P, C.POINTER(_P), C.POINTER(_P)]),
     "enn_b200_oplist_wait": (C.c_int32, [_P]),
     "enn_b200_oplist_tensor_ptr": (C.c_int32, [_P, C.c_int32, C.POINTER(_P)]),
+    "enn_b200_oplist_last_output_ptr": (C.c_int32, [_P, C.c_int32, C.POINTER(_P)]),
     "enn_b200_oplist_stats": (C.c_int32, [_P, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "enn_b200_oplist_destroy": (C.c_int32, [_P]),
+    "enn_b200_group_create": (C.c_int32, [C.POINTER(_P), C.c_int32, C.POINTER(_P)]),
+    "enn_b200_group_execute": (C.c_int32, [_P, C.POINTER(_P), C.POINTER(_P)]),
+    "enn_b200_group_submit": (C.c_int32, [_P, C.POINTER(_P), C.POINTER(_P)]),
+    "enn_b200_group_wait": (C.c_int32, [_P]),
+    "enn_b200_group_last_error": (C.c_int32, [_P, C.c_char_p, C.c_size_t]),
+    "enn_b200_group_destroy": (C.c_int32, [_P, C.c_int32]),
     "enn_b200_nchw_to_nhwc": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "enn_b200_nhwc_to_nchw": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "enn_b200_quantize_multiplier": (None, [C.c_double, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
@@ -371,6 +326,11 @@ class OpList:
         self.ctx.check(lib.enn_b200_oplist_tensor_ptr(self.h, tid, C.byref(p)))
         return p
 
+    def last_output_ptr(self, index=0):
+        p = C.c_void_p()
+        self.ctx.check(lib.enn_b200_oplist_last_output_ptr(self.h, index, C.byref(p)))
+        return p
+
     def stats(self):
         a, b, c = C.c_int64(), C.c_int32(), C.c_int32()
         self.ctx.check(lib.enn_b200_oplist_stats(self.h, C.byref(a), C.byref(b), C.byref(c)))
@@ -380,3 +340,47 @@ class OpList:
         if self.h:
             lib.enn_b200_oplist_destroy(self.h)
             self.h = None
+
+
+class Group:
+    """One ExecuteSubGraph call over several operator lists (one per device, or several per device): the batch is split
+    along its outermost dimension in member order, members run side by side, results land in one host buffer."""
+
+    def __init__(self, lists):
+        self.lists = list(lists)
+        arr = (C.c_void_p * len(self.lists))(*[l.h for l in self.lists])
+        h = C.c_void_p()
+        st = lib.enn_b200_group_create(arr, len(self.lists), C.byref(h))
+        if st != SUCCESS:
+            raise EnnError(st, "enn_b200_group_create failed")
+        self.h = h
+        self.out_bytes = [sum(l.out_bytes[i] for l in self.lists) for i in range(self.lists[0].n_out)]
+
+    def _check(self, st):
+        if st != SUCCESS:
+            buf = C.create_string_buffer(512)
+            lib.enn_b200_group_last_error(self.h, buf, 512)
+            raise EnnError(st, buf.value.decode())
+
+    def execute_host_ptrs(self, in_ptrs, out_ptrs):
+        self._check(lib.enn_b200_group_execute(self.h, (C.c_void_p * len(in_ptrs))(*in_ptrs), (C.c_void_p * len(out_ptrs))(*out_ptrs)))
+
+    def submit_host_ptrs(self, in_ptrs, out_ptrs):
+        self._check(lib.enn_b200_group_submit(self.h, (C.c_void_p * len(in_ptrs))(*in_ptrs), (C.c_void_p * len(out_ptrs))(*out_ptrs)))
+
+    def wait(self):
+        self._check(lib.enn_b200_group_wait(self.h))
+
+    def execute(self, inputs):
+        ins = [np.ascontiguousarray(x) for x in inputs]
+        outs = [np.empty(n, np.uint8) for n in self.out_bytes]
+        self.execute_host_ptrs([x.ctypes.data for x in ins], [o.ctypes.data for o in outs])
+        return outs
+
+    def destroy(self, destroy_lists=True):
+        if self.h:
+            lib.enn_b200_group_destroy(self.h, 1 if destroy_lists else 0)
+            self.h = None
+            if destroy_lists:
+                for l in self.lists:
+                    l.h = None

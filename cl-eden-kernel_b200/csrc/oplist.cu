@@ -12,6 +12,7 @@
 // The operator sequence is captured once into a CUDA graph, so an inference is one graph launch instead of
 // one enqueue per operator.
 #include <algorithm>
+#include <cstdio>
 #include <new>
 
 #include "internal.h"
@@ -306,6 +307,17 @@ int32_t enn_b200_oplist_tensor_ptr(enn_b200_oplist *l, int32_t tensor_id, void *
     return ENN_B200_SUCCESS;
 }
 
+// Device address of graph output `output_index` as written by the most recent submit / execute (pipelined submissions
+// alternate between two device copies of every graph input and output).
+int32_t enn_b200_oplist_last_output_ptr(enn_b200_oplist *l, int32_t output_index, void **dev_ptr) {
+    if (!l || !dev_ptr || output_index < 0 || output_index >= static_cast<int32_t>(l->outputs.size())) return ENN_B200_INVALID_PARAMS;
+    if (!l->finalized) return lfail(l, ENN_B200_FAILURE, "oplist not finalized");
+    auto &T = l->tensors[l->outputs[output_index]];
+    const bool alt = l->seq > 0 && ((l->seq - 1) & 1) && T.dev_alt;
+    *dev_ptr = alt ? T.dev_alt : T.dev;
+    return ENN_B200_SUCCESS;
+}
+
 int32_t enn_b200_oplist_stats(enn_b200_oplist *l, int64_t *device_bytes, int32_t *n_buffers, int32_t *kernel_launches) {
     if (!l || !l->finalized) return ENN_B200_INVALID_PARAMS;
     if (device_bytes) *device_bytes = l->device_bytes;
@@ -338,6 +350,161 @@ int32_t enn_b200_oplist_destroy(enn_b200_oplist *l) {
     for (void *p : l->pool)
         if (p) cudaFree(p);
     delete l;
+    return ENN_B200_SUCCESS;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------------
+// Operator-list group: one ExecuteSubGraph call over several devices.
+//
+// The reference's GpuUserDriver::ExecuteSubGraph (gpu_userdriver.cc) takes the whole batch in one call.  A group holds
+// one finalized operator list per device (or several per device), each built for its share of the batch; one call
+// splits every graph input along its outermost dimension into contiguous slices (member i takes the next
+// bytes-of-its-input-tensor bytes), runs the members side by side, one host worker thread per member, and lands every
+// member's outputs at the matching offsets of the caller's output buffers.  There is no collective: batch slices are
+// independent, only the results meet again, in host memory.
+// ------------------------------------------------------------------------------------------------------
+#include <condition_variable>
+#include <mutex>
+#include <thread>
+
+struct enn_b200_group {
+    struct Member {
+        enn_b200_oplist *list = nullptr;
+        std::thread worker;
+        std::vector<const void *> ins;
+        std::vector<void *> outs;
+        int job = 0;            // 0 idle, 1 execute (blocking), 2 submit, 3 wait, -1 quit
+        int32_t status = ENN_B200_SUCCESS;
+        bool done = true;
+    };
+    std::vector<Member> members;
+    std::mutex m;
+    std::condition_variable cv_job, cv_done;
+    std::string last_error;
+};
+
+namespace {
+void group_worker(enn_b200_group *g, int idx) {
+    enn_b200_group::Member &me = g->members[idx];
+    cudaSetDevice(me.list->ctx->device);       // the worker's current device for its whole life
+    for (;;) {
+        int job;
+        {
+            std::unique_lock<std::mutex> lk(g->m);
+            g->cv_job.wait(lk, [&] { return me.job != 0; });
+            job = me.job;
+        }
+        int32_t st = ENN_B200_SUCCESS;
+        if (job == 1) st = enn_b200_oplist_execute(me.list, me.ins.data(), me.outs.data());
+        else if (job == 2) st = enn_b200_oplist_submit(me.list, me.ins.data(), me.outs.data());
+        else if (job == 3) st = enn_b200_oplist_wait(me.list);
+        {
+            std::lock_guard<std::mutex> lk(g->m);
+            me.status = st;
+            me.job = 0;
+            me.done = true;
+        }
+        g->cv_done.notify_all();
+        if (job < 0) return;
+    }
+}
+
+// Hands `job` to every member (with its slices of the caller's buffers for jobs 1 and 2) and waits for all of them.
+int32_t group_run(enn_b200_group *g, int job, const void *const *host_inputs, void *const *host_outputs) {
+    if (!g) return ENN_B200_INVALID_PARAMS;
+    if (job == 1 || job == 2) {
+        const size_t n_in = g->members[0].list->inputs.size(), n_out = g->members[0].list->outputs.size();
+        if ((n_in && !host_inputs) || (n_out && !host_outputs)) return ENN_B200_INVALID_PARAMS;
+        std::vector<size_t> in_off(n_in, 0), out_off(n_out, 0);
+        for (auto &me : g->members) {
+            me.ins.resize(n_in);
+            me.outs.resize(n_out);
+            for (size_t i = 0; i < n_in; ++i) {
+                if (!host_inputs[i]) return ENN_B200_INVALID_PARAMS;
+                me.ins[i] = static_cast<const uint8_t *>(host_inputs[i]) + in_off[i];
+                in_off[i] += static_cast<size_t>(me.list->tensors[me.list->inputs[i]].bytes);
+            }
+            for (size_t i = 0; i < n_out; ++i) {
+                if (!host_outputs[i]) return ENN_B200_INVALID_PARAMS;
+                me.outs[i] = static_cast<uint8_t *>(host_outputs[i]) + out_off[i];
+                out_off[i] += static_cast<size_t>(me.list->tensors[me.list->outputs[i]].bytes);
+            }
+        }
+    }
+    {
+        std::lock_guard<std::mutex> lk(g->m);
+        for (auto &me : g->members) {
+            me.done = false;
+            me.job = job;
+        }
+    }
+    g->cv_job.notify_all();
+    int32_t st = ENN_B200_SUCCESS;
+    {
+        std::unique_lock<std::mutex> lk(g->m);
+        g->cv_done.wait(lk, [&] {
+            for (auto &me : g->members)
+                if (!me.done) return false;
+            return true;
+        });
+        for (auto &me : g->members)
+            if (me.status != ENN_B200_SUCCESS && st == ENN_B200_SUCCESS) {
+                st = me.status;
+                g->last_error = me.list->ctx->last_error;
+            }
+    }
+    return st;
+}
+}  // namespace
+
+extern "C" {
+
+int32_t enn_b200_group_create(enn_b200_oplist *const *lists, int32_t n_lists, enn_b200_group **out) {
+    if (!lists || n_lists < 1 || !out) return ENN_B200_INVALID_PARAMS;
+    *out = nullptr;
+    for (int i = 0; i < n_lists; ++i) {
+        if (!lists[i] || !lists[i]->finalized) return ENN_B200_INVALID_PARAMS;
+        if (lists[i]->inputs.size() != lists[0]->inputs.size() || lists[i]->outputs.size() != lists[0]->outputs.size())
+            return lfail(lists[i], ENN_B200_INVALID_PARAMS, "group: members differ in their number of graph inputs / outputs");
+        for (int k = 0; k < i; ++k)
+            if (lists[k] == lists[i] || lists[k]->ctx == lists[i]->ctx)
+                return lfail(lists[i], ENN_B200_INVALID_PARAMS, "group: every member needs its own list and context");
+    }
+    enn_b200_group *g = new (std::nothrow) enn_b200_group();
+    if (!g) return ENN_B200_FAILURE;
+    g->members.resize(n_lists);
+    for (int i = 0; i < n_lists; ++i) g->members[i].list = lists[i];
+    for (int i = 0; i < n_lists; ++i) g->members[i].worker = std::thread(group_worker, g, i);
+    *out = g;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_group_execute(enn_b200_group *g, const void *const *host_inputs, void *const *host_outputs) {
+    return group_run(g, 1, host_inputs, host_outputs);
+}
+
+int32_t enn_b200_group_submit(enn_b200_group *g, const void *const *host_inputs, void *const *host_outputs) {
+    return group_run(g, 2, host_inputs, host_outputs);
+}
+
+int32_t enn_b200_group_wait(enn_b200_group *g) { return group_run(g, 3, nullptr, nullptr); }
+
+int32_t enn_b200_group_last_error(enn_b200_group *g, char *buf, size_t buf_len) {
+    if (!buf || !buf_len) return ENN_B200_SUCCESS;
+    std::snprintf(buf, buf_len, "%s", g ? g->last_error.c_str() : "null group");
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_group_destroy(enn_b200_group *g, int32_t destroy_lists) {
+    if (!g) return ENN_B200_INVALID_PARAMS;
+    group_run(g, -1, nullptr, nullptr);
+    for (auto &me : g->members)
+        if (me.worker.joinable()) me.worker.join();
+    if (destroy_lists)
+        for (auto &me : g->members) enn_b200_oplist_destroy(me.list);
+    delete g;
     return ENN_B200_SUCCESS;
 }
 

@@ -198,6 +198,28 @@ def layer_descs(enn, L, batch):
     raise ValueError(L["kind"])
 
 
+def graph_work(layers, batch):
+    """(multiply-accumulates, algorithmic bytes) of one pass over `batch` images, counted as the library counts them per
+    operator: input + output + weights + 12 bytes of per-channel constants per output channel, each once."""
+    macs = nbytes = 0
+    for L in layers:
+        h = L["h"]
+        if L["kind"] in ("conv", "dw"):
+            pt, pb = L["pad"]
+            oh = (h + pt + pb - L["k"]) // L["stride"] + 1
+            cin_g = 1 if L["kind"] == "dw" else L["cin"]
+            macs += batch * oh * oh * L["cout"] * L["k"] * L["k"] * cin_g
+            nbytes += batch * h * h * L["cin"] + batch * oh * oh * L["cout"] + L["k"] * L["k"] * cin_g * L["cout"] + 12 * L["cout"]
+        elif L["kind"] == "fc":
+            macs += batch * L["cin"] * L["cout"]
+            nbytes += batch * L["cin"] + batch * L["cout"] + L["cin"] * L["cout"] + 12 * L["cout"]
+        elif L["kind"] == "add":
+            nbytes += 3 * batch * h * h * L["cout"]
+        else:
+            nbytes += batch * h * h * L["cin"] + batch * L["cin"]
+    return macs, nbytes
+
+
 def make_oplist(enn, ctx, layers, batch, resolution=224):
     """Prepares every layer through the C ABI and wires them into an operator list.
     Returns (oplist, info) where info carries per-layer work figures for reporting."""

@@ -219,9 +219,28 @@ int32_t enn_b200_oplist_wait(enn_b200_oplist *list);
 /* Operators only, on device-resident tensors, asynchronous on the context stream. */
 int32_t enn_b200_oplist_execute_device(enn_b200_oplist *list);
 int32_t enn_b200_oplist_tensor_ptr(enn_b200_oplist *list, int32_t tensor_id, void **dev_ptr);
+/* Device address of graph output `output_index` as written by the latest enn_b200_oplist_submit (submissions alternate
+ * between two device copies of every graph input / output), for callers that pass results on device-side
+ * (CLTensor::getDataPtr on an output tensor). */
+int32_t enn_b200_oplist_last_output_ptr(enn_b200_oplist *list, int32_t output_index, void **dev_ptr);
 int32_t enn_b200_oplist_stats(enn_b200_oplist *list, int64_t *device_bytes, int32_t *n_buffers, int32_t *kernel_launches);
 /* CloseSubGraph: releases the operators, the buffers and the graph. */
 int32_t enn_b200_oplist_destroy(enn_b200_oplist *list);
+
+/* ---- operator-list group: one ExecuteSubGraph call (gpu_userdriver.cc, whole batch per call) spread over several
+ *      devices.  Every member is a finalized list built for its slice of the batch, on its own context (one per device,
+ *      or several per device).  A call splits each graph input along its outermost dimension into contiguous slices in
+ *      member order (member i takes as many bytes as its own input tensor holds), runs the members side by side with one
+ *      host worker thread each, and writes each member's outputs at the matching offsets of host_outputs.  No collective
+ *      is involved: the slices are independent and only the results meet again, in host memory.  submit / wait are the
+ *      pipelined forms (enn_b200_oplist_submit / _wait on every member).  destroy_lists != 0 also destroys the lists. ---- */
+typedef struct enn_b200_group enn_b200_group;
+int32_t enn_b200_group_create(enn_b200_oplist *const *lists, int32_t n_lists, enn_b200_group **group);
+int32_t enn_b200_group_execute(enn_b200_group *group, const void *const *host_inputs, void *const *host_outputs);
+int32_t enn_b200_group_submit(enn_b200_group *group, const void *const *host_inputs, void *const *host_outputs);
+int32_t enn_b200_group_wait(enn_b200_group *group);
+int32_t enn_b200_group_last_error(enn_b200_group *group, char *buf, size_t buf_len);
+int32_t enn_b200_group_destroy(enn_b200_group *group, int32_t destroy_lists);
 
 /* Layout converters for NCHW models (CLRuntime.cpp:1477-1620 NHWC2NCHW_* / NCHW2NHWC_*), 1-byte elements. */
 int32_t enn_b200_nchw_to_nhwc(enn_b200_context *ctx, const void *src_dev, void *dst_dev, int32_t n, int32_t c,

@@ -492,6 +492,15 @@ int32_t orc_avgpool(const enn_b200_pool_desc *d, const void *in, void *out) {
     return 0;
 }
 
+// Worker threads of the following calls (a launcher may have exported OMP_NUM_THREADS=1 for its ranks).
+void orc_set_num_threads(int32_t n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int32_t orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

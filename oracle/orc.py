@@ -136,6 +136,10 @@ def num_threads():
     return lib.orc_num_threads()
 
 
+def set_num_threads(n):
+    lib.orc_set_num_threads(int(n))
+
+
 # ---- the reference's own kernel text compiled as C++ (oracle/ref_kernels_shim.cpp), when built ----
 def has_ref_kernels():
     return ref is not None and hasattr(ref, "ref_has_kernels")

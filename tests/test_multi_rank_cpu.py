@@ -1,5 +1,6 @@
-"""World-size-2 gloo test of the multi-rank plumbing the benchmark uses: every rank takes its own batch of
-independent images (no collective on the data path), times are reduced with MAX, rank 0 aggregates units."""
+"""World-size-2 gloo test of the multi-rank plumbing the benchmark uses: ONE global batch is partitioned into
+contiguous slices, one per rank (no collective on the data path), times are reduced with MAX, and only the logits are
+gathered on rank 0, where they must equal the whole batch run in one piece."""
 import os
 import socket
 import subprocess
@@ -21,15 +22,20 @@ WORKER = textwrap.dedent("""
     import mobilenet_ref
     mn = importlib.import_module("cl_eden_kernel_b200.mobilenet")
     layers, _ = mn.build_model(seed=0, calib_images=1, resolution=32, num_classes=10)
-    # each rank owns a contiguous slice of the global batch, seeded by rank as the benchmark does
-    x = np.random.default_rng(1000 + rank).integers(0, 256, (2, 32, 32, 3), dtype=np.int64).astype(np.uint8)
+    # every rank draws the same global batch and owns a contiguous slice of it, as the benchmark does
+    batch = 4
+    per_rank = batch // world
+    x_full = np.random.default_rng(1000).integers(0, 256, (batch, 32, 32, 3), dtype=np.int64).astype(np.uint8)
+    x = np.ascontiguousarray(x_full[rank * per_rank:(rank + 1) * per_rank])
     y = mobilenet_ref.run_oracle(layers, x)                 # CPU stand-in for the per-rank device graph
     t = torch.tensor([1.0 + rank, 2.0 + 0.5 * rank], dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)                # timing rule: max over ranks
-    gathered = [torch.zeros(2, 10, dtype=torch.uint8) for _ in range(world)]
-    dist.all_gather(gathered, torch.from_numpy(y.copy()))   # only the final logits are gathered
+    gathered = [torch.zeros(per_rank, 10, dtype=torch.uint8) for _ in range(world)] if rank == 0 else None
+    dist.gather(torch.from_numpy(y.copy()), gathered, dst=0)   # only the final logits travel
     if rank == 0:
-        print(json.dumps({"max_ms": t.tolist(), "units": 2 * world, "rows": int(torch.cat(gathered).shape[0]),
+        whole = mobilenet_ref.run_oracle(layers, x_full)
+        print(json.dumps({"max_ms": t.tolist(), "units": batch, "rows": int(torch.cat(gathered).shape[0]),
+                          "equal": bool(np.array_equal(torch.cat(gathered).numpy(), whole)),
                           "distinct": bool((gathered[0] != gathered[1]).any())}))
     dist.destroy_process_group()
 """)
@@ -53,7 +59,7 @@ def test_two_rank_gloo_sharding(tmp_path):
     line = [ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1]
     out = json.loads(line)
     assert out["max_ms"] == [2.0, 2.5]
-    assert out["units"] == 4 and out["rows"] == 4 and out["distinct"]
+    assert out["units"] == 4 and out["rows"] == 4 and out["distinct"] and out["equal"]
 
 
 def test_reference_arm_runs_on_rank0_only():

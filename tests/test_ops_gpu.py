@@ -621,6 +621,36 @@ def test_oplist_pipelined_submit(enn, ctx):
         ol.destroy()
 
 
+def test_oplist_group_splits_one_batch(enn, orc):
+    """enn_b200_group_*: one host batch in, one host buffer out, over three operator lists with slices of 3 + 2 + 1
+    images (their own contexts; on a one-GPU machine all on device 0): blocking and pipelined calls equal the oracle on
+    the whole batch."""
+    import importlib
+    import mobilenet_ref
+    mn = importlib.import_module("cl_eden_kernel_b200.mobilenet")
+    layers, _ = mn.build_model(seed=6, calib_images=1, resolution=64, num_classes=40)
+    rng = np.random.default_rng(12)
+    xs = [rng.integers(0, 256, (6, 64, 64, 3), dtype=np.int64).astype(np.uint8) for _ in range(3)]
+    want = [mobilenet_ref.run_oracle(layers, x).reshape(-1) for x in xs]
+    ctxs = [enn.Context(0) for _ in range(3)]
+    lists = [mn.make_oplist(enn, c, layers, batch=b, resolution=64)[0] for c, b in zip(ctxs, (3, 2, 1))]
+    grp = enn.Group(lists)
+    try:
+        for x, w in zip(xs, want):
+            (y,) = grp.execute([x])
+            assert np.array_equal(y, w)
+        outs = [np.zeros(6 * 40, np.uint8) for _ in xs]
+        for x, o in zip(xs, outs):
+            grp.submit_host_ptrs([x.ctypes.data], [o.ctypes.data])
+        grp.wait()
+        for o, w in zip(outs, want):
+            assert np.array_equal(o, w)
+    finally:
+        grp.destroy()
+        for c in ctxs:
+            c.close()
+
+
 def test_mobilenet_layers_individually(enn, orc, ctx):
     """Each distinct MobileNetV2 layer shape at 224x224, batch 2, fed with the oracle's own activations."""
     import importlib
