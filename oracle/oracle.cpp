@@ -19,12 +19,13 @@
 //     extracts the registered source strings at build time and oracle/ref_kernels_shim.cpp compiles them as C++ and
 //     replays the operators' host launch sequence.  Covered: conv_per_channel_quantized, depthwise_conv,
 //     depthwise_conv_per_channel, matrixTrans / weightAlign / convBackGemmRXR / PERCHANNELconvBackGemmRXR /
-//     convertBottomDiff2[_per_channel], avepooling_tflite, eltwiseAddQuantized_opt (live comparison where the reference
-//     tree is mounted, tests/golden/ref_kernels.npz elsewhere).
-//   * Not executed: the vectorised per-tensor conv kernels (quantizedGemmBlocked, direct3x3_8x4, gemm_block4x4: OpenCL
-//     vector types and ARM dot-product built-ins).  Per-tensor Conv2D is the same formula as the per-channel kernel
-//     with one multiplier and a weight zero point (ConvolutionKernels.cpp:956-1274 vs :1317-1375) and is pinned by the
-//     restated source only.  FullyConnected: see orc_fc / orc_fc_float below.
+//     convertBottomDiff2[_per_channel], avepooling_tflite, eltwiseAddQuantized_opt, and the per-tensor u8 convolution of
+//     CLGEMMConvolutionQuantized: pad_opt, convert_optimized / convertBlocked2, alignQuantizedWeight_gemm,
+//     quantizedGemmBlocked (live comparison where the reference tree is mounted, tests/golden/ref_kernels.npz elsewhere).
+//   * Not executed: the other per-tensor conv variants (direct3x3_8x4, gemm_block4x4: ARM dot-product built-ins and
+//     texture-style layouts).  They compute the value of quantizedGemmBlocked with the zero-point terms folded into the
+//     bias (DirectConvolutionKernel.cpp:4871-4884, ConvolutionGEMM1xXkernels.cpp:2003-2013).  FullyConnected: see orc_fc /
+//     orc_fc_float below.
 #include <algorithm>
 #include <cmath>
 #include <cstdint>

@@ -163,6 +163,12 @@ def ref_conv_per_channel(desc, x, w, bias, scales):
     return _ref_conv_like(ref.ref_conv_per_channel, lib.orc_conv_out_dims, desc, x, w, bias, scales)
 
 
+def ref_conv_per_tensor(desc, x, w, bias):
+    """Per-tensor u8 convolution through the reference's own GEMM path (pad_opt, convert_optimized / convertBlocked2,
+    alignQuantizedWeight_gemm, quantizedGemmBlocked)."""
+    return _ref_conv_like(lambda d, a, b, c, _s, o: ref.ref_conv_per_tensor(d, a, b, c, o), lib.orc_conv_out_dims, desc, x, w, bias, None)
+
+
 def ref_depthwise(desc, x, w, bias, scales=None):
     return _ref_conv_like(ref.ref_depthwise, lib.orc_conv_out_dims, desc, x, w, bias, scales)
 

@@ -32,23 +32,94 @@ static inline size_t get_global_size(int i) { return g_size[i]; }
 #define max(a, b) ((a) > (b) ? (a) : (b))
 #define min(a, b) ((a) < (b) ? (a) : (b))
 
+// OpenCL vector types: named components (.s0 ... .sf, .lo / .hi on 16-vectors) over the same storage as an array.
+template <typename T, int N>
+struct vecn;
 template <typename T>
-struct vec4 {
-    T s0, s1, s2, s3;
-    vec4() = default;
-    vec4(T v) : s0(v), s1(v), s2(v), s3(v) {}
-    vec4(T a, T b, T c, T d) : s0(a), s1(b), s2(c), s3(d) {}
+struct vecn<T, 2> {
+    union { T v[2]; struct { T s0, s1; }; };
+    vecn() = default;
+    explicit vecn(T a) { v[0] = v[1] = a; }
 };
-typedef vec4<int> int4;
-typedef vec4<uchar> uchar4;
-typedef vec4<char> char4;
-static inline int4 operator+(const int4 &a, const int4 &b) { return int4(a.s0 + b.s0, a.s1 + b.s1, a.s2 + b.s2, a.s3 + b.s3); }
-static inline int4 operator*(const int4 &a, const int4 &b) { return int4(a.s0 * b.s0, a.s1 * b.s1, a.s2 * b.s2, a.s3 * b.s3); }
-static inline int4 &operator+=(int4 &a, const int4 &b) { a = a + b; return a; }
 template <typename T>
-static inline vec4<T> vload4(size_t off, const T *p) { return vec4<T>(p[4 * off], p[4 * off + 1], p[4 * off + 2], p[4 * off + 3]); }
+struct vecn<T, 3> {
+    union { T v[3]; struct { T s0, s1, s2; }; };
+    vecn() = default;
+    explicit vecn(T a) { v[0] = v[1] = v[2] = a; }
+};
 template <typename T>
-static inline int4 convert_int4(const vec4<T> &v) { return int4(v.s0, v.s1, v.s2, v.s3); }
+struct vecn<T, 4> {
+    union { T v[4]; struct { T s0, s1, s2, s3; }; };
+    vecn() = default;
+    vecn(T a) { v[0] = v[1] = v[2] = v[3] = a; }
+    vecn(T a, T b, T c, T d) { v[0] = a; v[1] = b; v[2] = c; v[3] = d; }
+};
+template <typename T>
+struct vecn<T, 8> {
+    union { T v[8]; struct { T s0, s1, s2, s3, s4, s5, s6, s7; }; };
+    vecn() = default;
+    explicit vecn(T a) { for (int i = 0; i < 8; ++i) v[i] = a; }
+    template <int M> vecn<T, M> sub(int first) const { vecn<T, M> r; for (int i = 0; i < M; ++i) r.v[i] = v[first + i]; return r; }
+};
+template <typename T>
+struct vecn<T, 16> {
+    union {
+        T v[16];
+        struct { T s0, s1, s2, s3, s4, s5, s6, s7, s8, s9, sa, sb, sc, sd, se, sf; };
+        struct { vecn<T, 8> lo, hi; };
+    };
+    vecn() = default;
+    explicit vecn(T a) { for (int i = 0; i < 16; ++i) v[i] = a; }
+    template <typename U> explicit vecn(U a) { for (int i = 0; i < 16; ++i) v[i] = static_cast<T>(a); }   // (uchar16)int_value
+    template <int M> vecn<T, M> sub(int first) const { vecn<T, M> r; for (int i = 0; i < M; ++i) r.v[i] = v[first + i]; return r; }
+};
+template <typename T> using vec4 = vecn<T, 4>;
+typedef vecn<int, 2> int2;
+typedef vecn<int, 3> int3;
+typedef vecn<int, 4> int4;
+typedef vecn<int, 8> int8;
+typedef vecn<int, 16> int16;
+typedef vecn<uchar, 3> uchar3;
+typedef vecn<uchar, 4> uchar4;
+typedef vecn<uchar, 8> uchar8;
+typedef vecn<uchar, 16> uchar16;
+typedef vecn<char, 4> char4;
+typedef vecn<short, 2> short2;
+typedef vecn<short, 3> short3;
+typedef vecn<short, 4> short4;
+typedef vecn<short, 8> short8;
+typedef vecn<short, 16> short16;
+template <typename T, int N>
+static inline vecn<T, N> operator+(const vecn<T, N> &a, const vecn<T, N> &b) { vecn<T, N> r; for (int i = 0; i < N; ++i) r.v[i] = static_cast<T>(a.v[i] + b.v[i]); return r; }
+template <typename T, int N>
+static inline vecn<T, N> operator*(const vecn<T, N> &a, const vecn<T, N> &b) { vecn<T, N> r; for (int i = 0; i < N; ++i) r.v[i] = static_cast<T>(a.v[i] * b.v[i]); return r; }
+template <typename T, int N, typename S>
+static inline vecn<T, N> operator+(const vecn<T, N> &a, S b) { vecn<T, N> r; for (int i = 0; i < N; ++i) r.v[i] = static_cast<T>(a.v[i] + b); return r; }
+template <typename T, int N>
+static inline vecn<T, N> &operator+=(vecn<T, N> &a, const vecn<T, N> &b) { a = a + b; return a; }
+template <int N, typename T>
+static inline vecn<T, N> vloadn(size_t off, const T *p) { vecn<T, N> r; for (int i = 0; i < N; ++i) r.v[i] = p[N * off + i]; return r; }
+template <typename T> static inline vecn<T, 2> vload2(size_t off, const T *p) { return vloadn<2>(off, p); }
+template <typename T> static inline vecn<T, 3> vload3(size_t off, const T *p) { return vloadn<3>(off, p); }
+template <typename T> static inline vecn<T, 4> vload4(size_t off, const T *p) { return vloadn<4>(off, p); }
+template <typename T> static inline vecn<T, 8> vload8(size_t off, const T *p) { return vloadn<8>(off, p); }
+template <typename T> static inline vecn<T, 16> vload16(size_t off, const T *p) { return vloadn<16>(off, p); }
+template <typename T, int N>
+static inline void vstoren(const vecn<T, N> &v, size_t off, T *p) { for (int i = 0; i < N; ++i) p[N * off + i] = v.v[i]; }
+template <typename T> static inline void vstore2(const vecn<T, 2> &v, size_t off, T *p) { vstoren(v, off, p); }
+template <typename T> static inline void vstore3(const vecn<T, 3> &v, size_t off, T *p) { vstoren(v, off, p); }
+template <typename T> static inline void vstore4(const vecn<T, 4> &v, size_t off, T *p) { vstoren(v, off, p); }
+template <typename T> static inline void vstore8(const vecn<T, 8> &v, size_t off, T *p) { vstoren(v, off, p); }
+template <typename T> static inline void vstore16(const vecn<T, 16> &v, size_t off, T *p) { vstoren(v, off, p); }
+template <typename D, typename T, int N>
+static inline vecn<D, N> convert_vec(const vecn<T, N> &v) { vecn<D, N> r; for (int i = 0; i < N; ++i) r.v[i] = static_cast<D>(v.v[i]); return r; }
+template <typename T> static inline int4 convert_int4(const vecn<T, 4> &v) { return convert_vec<int>(v); }
+template <typename T> static inline int8 convert_int8(const vecn<T, 8> &v) { return convert_vec<int>(v); }
+template <typename T> static inline int16 convert_int16(const vecn<T, 16> &v) { return convert_vec<int>(v); }
+template <typename T> static inline short2 convert_short2(const vecn<T, 2> &v) { return convert_vec<short>(v); }
+template <typename T> static inline short3 convert_short3(const vecn<T, 3> &v) { return convert_vec<short>(v); }
+template <typename T> static inline short4 convert_short4(const vecn<T, 4> &v) { return convert_vec<short>(v); }
+template <typename T> static inline short8 convert_short8(const vecn<T, 8> &v) { return convert_vec<short>(v); }
 
 #include "_ref/ref_kernels_gen.inc"
 
@@ -296,6 +367,86 @@ int32_t ref_add(const enn_b200_add_desc *d, const uint8_t *a, const uint8_t *b, 
     ocl::run3(1, static_cast<size_t>(d->count), 1, [&] {
         ocl::eltwiseAddQuantized_opt_INT8(ta.data(), tb.data(), out, left_shift, -d->in0_zp, -d->in1_zp, d->out_zp, s0, s1, so, q0, q1, qo, lo, hi);
     });
+    return 0;
+}
+
+// CLGEMMConvolutionQuantized (per-tensor u8 convolution; cl_optimized_impls/CLGEMMConvolutionQuantized.cpp): weights to
+// int16 with the zero point removed and interleaved four rows at a time (alignQuantizedWeight_gemm, once at
+// initialize), then per execute: CLPadConvert (pad_opt with the input zero point, then convert_optimized for one group
+// or convertBlocked2 per group) and quantizedGemmBlocked per group.  Buffer sizes, argument order and global sizes
+// follow the host code.  Padding entries beyond the real reduction length are never written by the reference and meet
+// padding weights; here both buffers start zeroed, so those products are zero.
+int32_t ref_conv_per_tensor(const enn_b200_conv_desc *d, const uint8_t *in, const uint8_t *w, const int32_t *bias, uint8_t *out) {
+    if (d->per_channel || d->act_dtype != ENN_B200_U8 || d->weight_dtype != ENN_B200_U8 || d->dil_h > 1 || d->dil_w > 1) return 3;
+    const uint32_t g = d->groups > 0 ? d->groups : 1, cig = d->cin / g, cog = d->cout / g;
+    const int oh = out_dim(d->h, d->pad_t, d->pad_b, d->kh, 1, d->stride_h), ow = out_dim(d->w, d->pad_l, d->pad_r, d->kw, 1, d->stride_w);
+    // weights as OIHW (ANDROID_NN models are converted first, CLGEMMConvolutionQuantized.cpp initialize)
+    std::vector<uint8_t> wo(static_cast<size_t>(d->cout) * cig * d->kh * d->kw);
+    for (int o = 0; o < d->cout; ++o)
+        for (uint32_t i = 0; i < cig; ++i)
+            for (int ky = 0; ky < d->kh; ++ky)
+                for (int kx = 0; kx < d->kw; ++kx) {
+                    const size_t dst = ((static_cast<size_t>(o) * cig + i) * d->kh + ky) * d->kw + kx;
+                    wo[dst] = d->weight_layout == ENN_B200_W_OHWI ? w[((static_cast<size_t>(o) * d->kh + ky) * d->kw + kx) * cig + i] : w[dst];
+                }
+    // alignQuantizedWeightGEMM
+    const uint32_t src_unit_count = cig * d->kh * d->kw, dst_align_count = align_to(src_unit_count, 16);
+    const uint32_t group_top_channel = cog, aligned_group_top_channel = align_to(cog, 16);
+    const uint32_t align_weight_height = dst_align_count, align_weight_width = aligned_group_top_channel * g;
+    std::vector<short> wq(static_cast<size_t>(align_weight_height) * align_weight_width + 64, 0);
+    wo.resize(wo.size() + 16, 0);     // the 8-wide loads of the last row may read a few bytes past the tensor
+    ocl::run3(d->cout, align_to((src_unit_count + 7) / 8, 12), 1, [&] {
+        ocl::alignQuantizedWeight_gemm_INT8(wo.data(), wq.data(), src_unit_count, dst_align_count, group_top_channel, aligned_group_top_channel,
+                                            -d->w_zp);
+    });
+    // CLPadConvert::execute
+    const int ph = d->h + d->pad_t + d->pad_b, pw = d->w + d->pad_l + d->pad_r;
+    std::vector<uint8_t> x = nhwc_to_nchw(in, d->n, d->h, d->w, d->cin);
+    const size_t slack = 64;          // pad_opt loads 16 bytes around every row start, also left of the tensor
+    std::vector<uint8_t> xs(x.size() + 2 * slack, 0);
+    std::memcpy(xs.data() + slack, x.data(), x.size());
+    const uint8_t *x0 = xs.data() + slack;
+    std::vector<uint8_t> xp;
+    const uint8_t *padded = x0;
+    if (d->pad_t || d->pad_b || d->pad_l || d->pad_r) {
+        xp.assign(static_cast<size_t>(d->n) * d->cin * ph * pw + slack, 0);
+        ocl::run3(static_cast<size_t>(d->n) * d->cin, align_to(ph, 4), align_to((pw + 15) / 16, 64), [&] {
+            ocl::pad_opt_INT8(x0, xp.data(), d->in_zp, d->pad_t, d->pad_l, d->h, d->w, ph, pw);
+        });
+        padded = xp.data();
+    }
+    const uint32_t align_input_height = align_to(static_cast<size_t>(oh) * ow, 12) * g, align_input_width = dst_align_count;
+    std::vector<uint8_t> col(static_cast<size_t>(d->n) * align_input_height * align_input_width + slack, 0);
+    const uint32_t add_pad_height = d->pad_t || d->pad_b || d->pad_l || d->pad_r ? ph : d->h;
+    const uint32_t add_pad_width = d->pad_t || d->pad_b || d->pad_l || d->pad_r ? pw : d->w;
+    const uint32_t group_height = align_input_height / g;
+    if (g == 1) {
+        ocl::run3(d->n, static_cast<size_t>(oh) * ow, align_to(static_cast<size_t>(d->cin) * d->kh, 16), [&] {
+            ocl::convert_optimized_INT8(padded, col.data(), d->kw, d->kh, d->stride_w, d->stride_h, add_pad_height, add_pad_width, cig, group_height,
+                                        align_input_width, ow, oh);
+        });
+    } else {
+        for (uint32_t i = 0; i < g; ++i)
+            ocl::run3(d->n, align_to(static_cast<size_t>(oh) * ow, 16), align_to(static_cast<size_t>(d->cin) * d->kh * d->kw / g, 16), [&] {
+                ocl::convertBlocked2_INT8(padded, col.data(), d->kw, d->kh, d->stride_w, d->stride_h, add_pad_height, add_pad_width, cig, group_height,
+                                          align_input_width, i, ow, g, oh);
+            });
+    }
+    // execute(): multiplier, then quantizedGEMMRun per group
+    int32_t m;
+    int s;
+    per_tensor_params(d, &m, &s);
+    s *= -1;                          // CLGEMMConvolutionQuantized::execute; undone inside the kernel
+    int32_t lo, hi;
+    act_range(d, true, &lo, &hi);
+    std::vector<uint8_t> y(static_cast<size_t>(d->n) * d->cout * oh * ow + slack, 0);
+    for (uint32_t i = 0; i < g; ++i)
+        ocl::run3(d->n, align_weight_width / g / 4, align_input_height / g, [&] {
+            ocl::quantizedGemmBlocked_INT8(col.data(), wq.data(), bias, y.data(), align_input_width, d->cout, oh * ow, g, i, -d->in_zp, d->out_zp, m,
+                                           s, lo, hi);
+        });
+    y.resize(static_cast<size_t>(d->n) * d->cout * oh * ow);
+    nchw_to_nhwc(y, out, d->n, oh, ow, d->cout);
     return 0;
 }
 

@@ -4,7 +4,8 @@ and run on the CPU (oracle/ref_kernels_shim.cpp -> oracle/_ref/libennref.so), on
     make -C oracle && python tests/golden/gen_ref_kernels.py
 
 Each entry stores only the expected output; inputs are regenerated from the seed by tests/cases.py, so the file
-stays small.  Kernels covered: conv_per_channel_quantized, depthwise_conv (per-tensor u8), depthwise_conv_per_channel,
+stays small.  Kernels covered: pad_opt + convert_optimized / convertBlocked2 + alignQuantizedWeight_gemm +
+quantizedGemmBlocked (per-tensor u8 convolution), conv_per_channel_quantized, depthwise_conv (per-tensor u8), depthwise_conv_per_channel,
 matrixTrans + convBackGemmRXR + convertBottomDiff2 (deconvolution, per-tensor and per-channel),
 avepooling_tflite, eltwiseAddQuantized_opt.
 """

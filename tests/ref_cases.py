@@ -27,6 +27,14 @@ CASES = {
     "conv_pc_1x1_relu6": ("conv_pc", lambda: cases.conv_case(seed=102, n=1, h=7, w=7, cin=32, cout=16, k=1, per_channel=True, out_scale=0.1, out_zp=0)),
     "conv_pc_s2_group": ("conv_pc", lambda: cases.conv_case(seed=103, n=1, h=11, w=9, cin=8, cout=8, k=3, stride=2, groups=2, per_channel=True,
                                                                out_scale=0.15, layout=enn.W_OIHW, act=enn.ACT_NONE)),
+    # per-tensor u8 convolution through the reference's GEMM path (pad_opt, convert_optimized / convertBlocked2,
+    # alignQuantizedWeight_gemm, quantizedGemmBlocked): the configuration-1 geometry at reduced size, groups, stride 2 with
+    # a reduction length that is not a multiple of 16, 1x1 with a small weight zero point, a 7x7 first layer
+    "conv_pt_config1_14": ("conv_pt", lambda: cases.conv_case(seed=120, n=1, h=14, w=14, cin=64, cout=64, k=3)),
+    "conv_pt_groups": ("conv_pt", lambda: cases.conv_case(seed=121, n=2, h=9, w=9, cin=8, cout=12, k=3, groups=4, layout=enn.W_OIHW)),
+    "conv_pt_s2_ragged": ("conv_pt", lambda: cases.conv_case(seed=122, n=2, h=9, w=11, cin=5, cout=7, k=3, stride=2, w_zp=140, act=enn.ACT_RELU)),
+    "conv_pt_1x1_zp3": ("conv_pt", lambda: cases.conv_case(seed=123, n=1, h=7, w=7, cin=24, cout=10, k=1, w_zp=3, act=enn.ACT_NONE)),
+    "conv_pt_7x7_s2": ("conv_pt", lambda: cases.conv_case(seed=124, n=1, h=33, w=35, cin=3, cout=5, k=7, stride=2, w_zp=200)),
     "dw_pc_s1": ("dw", lambda: cases.depthwise_case(seed=104, n=2, h=12, w=12, c=8)),
     "dw_pc_s2": ("dw", lambda: cases.depthwise_case(seed=105, n=1, h=13, w=11, c=12, stride=2)),
     "dw_pt_s1": ("dw", lambda: cases.depthwise_case(seed=106, n=1, h=10, w=10, c=8, per_channel=False, out_scale=0.08, out_zp=3)),
@@ -47,6 +55,9 @@ def run_reference(orc, kind, case):
     if kind == "conv_pc":
         d, x, w, b, sc = case
         return orc.ref_conv_per_channel(d, x, w, b, sc)
+    if kind == "conv_pt":
+        d, x, w, b, sc = case
+        return orc.ref_conv_per_tensor(d, x, w, b)
     if kind == "dw":
         d, x, w, b, sc = case
         return orc.ref_depthwise(d, x, w, b, sc)
@@ -61,7 +72,7 @@ def run_reference(orc, kind, case):
 
 
 def run_oracle(orc, kind, case):
-    if kind == "conv_pc":
+    if kind in ("conv_pc", "conv_pt"):
         d, x, w, b, sc = case
         return orc.conv2d(d, x, w, b, sc)
     if kind == "dw":

@@ -376,6 +376,78 @@ def test_fc_parity(enn, orc, ctx, name):
         op.release()
 
 
+def _sub_batch(d, x, idx):
+    """Descriptor and input restricted to the images `idx` of the batch (for the oracle on sampled images)."""
+    ds = type(d).from_buffer_copy(d)
+    ds.n = len(idx)
+    return ds, np.ascontiguousarray(x[idx])
+
+
+@pytest.mark.parametrize("stride", [1, 2])
+def test_depthwise_config2_benchmark_size(enn, orc, ctx, stride):
+    """Benchmark configuration 2 at its full size (64 x 112 x 112 x 32): first, middle and last images against the oracle,
+    and every image against the first (all 64 are computed independently from a repeated input)."""
+    d, x, w, b, sc = cases.depthwise_case(seed=0, n=64, stride=stride)
+    op = enn.depthwise(ctx, d, w, b, sc)
+    try:
+        y = op.run(x).reshape(op.out_shape)
+        idx = [0, 31, 63]
+        ds, xs = _sub_batch(d, x, idx)
+        assert np.array_equal(y[idx], orc.depthwise(ds, xs, w, b, sc))
+        x_rep = np.ascontiguousarray(np.broadcast_to(x[5], x.shape))
+        y_rep = op.run(x_rep).reshape(op.out_shape)
+        assert np.array_equal(y_rep, np.broadcast_to(y[5], y.shape))
+    finally:
+        op.release()
+
+
+def test_deconv_config4_benchmark_size(enn, orc, ctx):
+    """Benchmark configuration 4 at its full size (8 x 64 x 64 x 128 -> 8 x 128 x 128 x 64): first and last images
+    against the oracle, every image against image 3 on a repeated input."""
+    d, x, w, b, sc = cases.deconv_case(seed=0, n=8, h=64, w=64)
+    op = enn.deconv(ctx, d, w, b, sc)
+    try:
+        y = op.run(x).reshape(op.out_shape)
+        idx = [0, 7]
+        ds, xs = _sub_batch(d, x, idx)
+        assert np.array_equal(y[idx], orc.deconv(ds, xs, w, b, sc))
+        x_rep = np.ascontiguousarray(np.broadcast_to(x[3], x.shape))
+        y_rep = op.run(x_rep).reshape(op.out_shape)
+        assert np.array_equal(y_rep, np.broadcast_to(y[3], y.shape))
+    finally:
+        op.release()
+
+
+def test_conv_config1_batched_benchmark_size(enn, orc, ctx):
+    """Configuration 1 (per-tensor u8 3x3 convolution, 56 x 56 x 64) at batch 1 whole and at batch 256 on sampled images."""
+    d, x, w, b, sc = cases.conv_case(seed=0)
+    op = enn.conv2d(ctx, d, w, b, sc)
+    try:
+        assert np.array_equal(op.run(x).reshape(op.out_shape), orc.conv2d(d, x, w, b, sc))
+    finally:
+        op.release()
+    d, x, w, b, sc = cases.conv_case(seed=0, n=256)
+    op = enn.conv2d(ctx, d, w, b, sc)
+    try:
+        y = op.run(x).reshape(op.out_shape)
+        idx = [0, 128, 255]
+        ds, xs = _sub_batch(d, x, idx)
+        assert np.array_equal(y[idx], orc.conv2d(ds, xs, w, b, sc))
+    finally:
+        op.release()
+
+
+def test_fc_config3_gemv_benchmark_size(enn, orc, ctx):
+    """Benchmark configuration 3, M = 1 (1 x 4096 x 4096): every output against the oracle."""
+    d, x, w, b, sc = cases.fc_case(seed=0, m=1, k=4096, n=4096)
+    op = enn.fully_connected(ctx, d, w, b, sc)
+    try:
+        assert op.info.impl == enn.IMPL_GEMV
+        assert np.array_equal(op.run(x).reshape(1, 4096), orc.fully_connected(d, x, w, b, sc))
+    finally:
+        op.release()
+
+
 def test_fc_full_size_sampled_rows(enn, orc, ctx):
     """4096 x 4096 x 4096 (the largest benchmark GEMM): rows sampled across all M tiles against the oracle."""
     d, x, w, b, sc = cases.fc_case(seed=5, m=4096, k=4096, n=4096)
@@ -702,9 +774,9 @@ def test_library_matches_reference_kernel_text_golden(enn, ctx, name):
     golden = np.load(os.path.join(HERE, "golden", "ref_kernels.npz"))[name]
     kind, mk = ref_cases.CASES[name]
     case = mk()
-    if kind in ("conv_pc", "dw", "deconv"):
+    if kind in ("conv_pc", "conv_pt", "dw", "deconv"):
         d, x, w, b, sc = case
-        op = {"conv_pc": enn.conv2d, "dw": enn.depthwise, "deconv": enn.deconv}[kind](ctx, d, w, b, sc)
+        op = {"conv_pc": enn.conv2d, "conv_pt": enn.conv2d, "dw": enn.depthwise, "deconv": enn.deconv}[kind](ctx, d, w, b, sc)
         x2 = None
     elif kind == "pool":
         d, x = case
@@ -713,7 +785,7 @@ def test_library_matches_reference_kernel_text_golden(enn, ctx, name):
         d, x, x2 = case
         op = enn.add(ctx, d)
     try:
-        for impl in _impls(enn, op) if kind in ("conv_pc", "deconv") else [op.info.impl]:
+        for impl in _impls(enn, op) if kind in ("conv_pc", "conv_pt", "deconv") else [op.info.impl]:
             op.set_impl(impl)
             assert np.array_equal(op.run(x, x2), golden.reshape(-1)), (name, impl)
     finally:

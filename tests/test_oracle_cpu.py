@@ -219,6 +219,13 @@ def test_oracle_matches_reference_kernel_text_live(orc):
                             k=int(rng.choice([1, 3])), stride=stride, per_channel=True, out_scale=float(rng.uniform(0.05, 0.5)),
                             out_zp=int(rng.integers(0, 256)), act=int(rng.integers(0, 4)))
         assert np.array_equal(orc.conv2d(*c), orc.ref_conv_per_channel(*c))
+        groups = int(rng.choice([1, 1, 2]))
+        t = cases.conv_case(seed=250 + i, n=int(rng.integers(1, 3)), h=h + 1, w=w + 1, cin=groups * int(rng.integers(1, 7)),
+                            cout=groups * int(rng.integers(1, 10)), kh=int(rng.choice([1, 3, 5])), kw=int(rng.choice([1, 3, 5, 7])), stride=stride,
+                            groups=groups, layout=int(rng.choice([cases.enn.W_OIHW, cases.enn.W_OHWI])), w_zp=int(rng.integers(0, 256)),
+                            in_zp=int(rng.integers(0, 256)), out_scale=float(rng.uniform(0.02, 0.3)), out_zp=int(rng.integers(0, 256)),
+                            act=int(rng.integers(0, 4)), pad=str(rng.choice(["same", "valid"])) if h > 6 and w > 8 else "same")
+        assert np.array_equal(orc.conv2d(*t), orc.ref_conv_per_tensor(*t[:4]))
         for pc in (True, False):
             dcase = cases.depthwise_case(seed=300 + i, n=1, h=h + 2, w=w + 2, c=int(rng.integers(1, 7)), stride=stride, per_channel=pc,
                                          out_scale=float(rng.uniform(0.02, 0.2)), out_zp=int(rng.integers(0, 200)), act=int(rng.integers(0, 4)),
