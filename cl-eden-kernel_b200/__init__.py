@@ -16,10 +16,10 @@ LIB_PATH = os.path.join(_HERE, "libenn_b200.so")
 
 try:
     from .abi_types import *          # noqa: F401,F403  (constants, descriptors, conv_desc)
-    from .abi_types import ConvDesc, FcDesc, AddDesc, PoolDesc, OpInfo
+    from .abi_types import ConvDesc, FcDesc, AddDesc, PoolDesc, OpInfo, MeanDesc, ConcatDesc, SoftmaxDesc, ResizeDesc
 except ImportError:                   # loaded as a plain module
     from abi_types import *           # noqa: F401,F403
-    from abi_types import ConvDesc, FcDesc, AddDesc, PoolDesc, OpInfo
+    from abi_types import ConvDesc, FcDesc, AddDesc, PoolDesc, OpInfo, MeanDesc, ConcatDesc, SoftmaxDesc, ResizeDesc
 
 # Every symbol include/enn_b200.h declares, with its prototype: (restype, argtypes).
 _P = C.c_void_p
@@ -42,9 +42,15 @@ PROTOTYPES = {
     "enn_b200_fc_prepare": (C.c_int32, [_P, C.POINTER(FcDesc), _P, _P, _P, C.POINTER(_P)]),
     "enn_b200_add_prepare": (C.c_int32, [_P, C.POINTER(AddDesc), C.POINTER(_P)]),
     "enn_b200_avgpool_prepare": (C.c_int32, [_P, C.POINTER(PoolDesc), C.POINTER(_P)]),
+    "enn_b200_maxpool_prepare": (C.c_int32, [_P, C.POINTER(PoolDesc), C.POINTER(_P)]),
+    "enn_b200_mean_prepare": (C.c_int32, [_P, C.POINTER(MeanDesc), C.POINTER(_P)]),
+    "enn_b200_concat_prepare": (C.c_int32, [_P, C.POINTER(ConcatDesc), C.POINTER(_P)]),
+    "enn_b200_softmax_prepare": (C.c_int32, [_P, C.POINTER(SoftmaxDesc), C.POINTER(_P)]),
+    "enn_b200_resize_bilinear_prepare": (C.c_int32, [_P, C.POINTER(ResizeDesc), C.POINTER(_P)]),
     "enn_b200_op_set_impl": (C.c_int32, [_P, C.c_int32]),
     "enn_b200_op_execute": (C.c_int32, [_P, _P, _P]),
     "enn_b200_op_execute2": (C.c_int32, [_P, _P, _P, _P]),
+    "enn_b200_op_execute_n": (C.c_int32, [_P, C.POINTER(_P), C.c_int32, _P]),
     "enn_b200_op_execute_noalloc": (C.c_int32, [_P, _P, _P]),
     "enn_b200_op_info": (C.c_int32, [_P, C.POINTER(OpInfo)]),
     "enn_b200_op_test_starve_next": (C.c_int32, [_P]),
@@ -195,6 +201,21 @@ class Op:
     def execute2(self, a_dev, b_dev, out_dev):
         self.ctx.check(lib.enn_b200_op_execute2(self.h, a_dev, b_dev, out_dev))
 
+    def execute_n(self, in_devs, out_dev):
+        arr = (C.c_void_p * len(in_devs))(*[p.value if hasattr(p, "value") else p for p in in_devs])
+        self.ctx.check(lib.enn_b200_op_execute_n(self.h, arr, len(in_devs), out_dev))
+
+    def run_n(self, xs):
+        """Upload several host arrays, execute the n-input form, download."""
+        devs = [self.ctx.to_device(x) for x in xs]
+        o = self.ctx.malloc(max(1, self.info.out_bytes))
+        try:
+            self.execute_n(devs, o)
+            return self.ctx.download(o, (self.info.out_bytes,), np.int8 if xs[0].dtype == np.int8 else np.uint8)
+        finally:
+            for p in devs + [o]:
+                self.ctx.free(p)
+
     def test_starve_next(self):
         self.ctx.check(lib.enn_b200_op_test_starve_next(self.h))
 
@@ -266,6 +287,32 @@ def avgpool(ctx, desc):
     h = C.c_void_p()
     ctx.check(lib.enn_b200_avgpool_prepare(ctx.h, C.byref(desc), C.byref(h)))
     return Op(ctx, h)
+
+
+def _prepare_simple(ctx, fn, desc):
+    h = C.c_void_p()
+    ctx.check(fn(ctx.h, C.byref(desc), C.byref(h)))
+    return Op(ctx, h)
+
+
+def maxpool(ctx, desc):
+    return _prepare_simple(ctx, lib.enn_b200_maxpool_prepare, desc)
+
+
+def mean(ctx, desc):
+    return _prepare_simple(ctx, lib.enn_b200_mean_prepare, desc)
+
+
+def concat(ctx, desc):
+    return _prepare_simple(ctx, lib.enn_b200_concat_prepare, desc)
+
+
+def softmax(ctx, desc):
+    return _prepare_simple(ctx, lib.enn_b200_softmax_prepare, desc)
+
+
+def resize_bilinear(ctx, desc):
+    return _prepare_simple(ctx, lib.enn_b200_resize_bilinear_prepare, desc)
 
 
 class OpList:

@@ -42,6 +42,45 @@ class PoolDesc(C.Structure):
         ("out_scale", C.c_float), ("out_zp", C.c_int32)]
 
 
+class MeanDesc(C.Structure):
+    _fields_ = [("dims", C.c_int32 * 4), ("axis_mask", C.c_int32), ("act_dtype", C.c_int32)]
+
+
+CONCAT_MAX_INPUTS = 8
+
+
+class ConcatDesc(C.Structure):
+    _fields_ = [("n_inputs", C.c_int32), ("act_dtype", C.c_int32), ("outer", C.c_int64), ("inner", C.c_int64 * CONCAT_MAX_INPUTS),
+                ("in_scale", C.c_float * CONCAT_MAX_INPUTS), ("in_zp", C.c_int32 * CONCAT_MAX_INPUTS), ("out_scale", C.c_float),
+                ("out_zp", C.c_int32)]
+
+
+class SoftmaxDesc(C.Structure):
+    _fields_ = [("outer", C.c_int64), ("channels", C.c_int32), ("inner", C.c_int64), ("beta", C.c_float), ("act_dtype", C.c_int32),
+                ("in_scale", C.c_float), ("in_zp", C.c_int32), ("out_scale", C.c_float), ("out_zp", C.c_int32)]
+
+
+class ResizeDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n", "h", "w", "c", "out_h", "out_w", "align_corners", "half_pixel_centers", "act_dtype")]
+
+
+def mean_desc(dims, axes, act_dtype=U8):
+    d = MeanDesc()
+    for i, v in enumerate(dims):
+        d.dims[i] = v
+    d.axis_mask = sum(1 << a for a in axes)
+    d.act_dtype = act_dtype
+    return d
+
+
+def concat_desc(outer, inner, in_scale, in_zp, out_scale, out_zp, act_dtype=U8):
+    d = ConcatDesc()
+    d.n_inputs, d.act_dtype, d.outer, d.out_scale, d.out_zp = len(inner), act_dtype, outer, out_scale, out_zp
+    for i in range(len(inner)):
+        d.inner[i], d.in_scale[i], d.in_zp[i] = inner[i], in_scale[i], in_zp[i]
+    return d
+
+
 class OpInfo(C.Structure):
     _fields_ = [("impl", C.c_int32), ("out_n", C.c_int32), ("out_h", C.c_int32), ("out_w", C.c_int32),
                 ("out_c", C.c_int32), ("in_bytes", C.c_int64), ("out_bytes", C.c_int64), ("macs", C.c_int64),

@@ -613,6 +613,19 @@ int32_t enn_b200_op_execute(enn_b200_op *op, const void *in, void *out) {
         case OP_AVGPOOL:
             e = launch_avgpool(op->pool, in, out, ctx->stream);
             break;
+        case OP_MAXPOOL:
+            e = launch_maxpool(op->pool, in, out, ctx->stream);
+            break;
+        case OP_MEAN:
+        case OP_SOFTMAX:
+        case OP_RESIZE:
+            e = launch_graph_op(op, &in, 1, out);
+            break;
+        case OP_CONCAT:
+            if (op->info.in_bytes != op->info.out_bytes || !op->graph_state) return fail(ctx, ENN_B200_FAILURE, "bad concat state");
+            e = launch_graph_op(op, &in, 1, out);       // a one-input concatenation
+            if (e == cudaErrorInvalidValue) return fail(ctx, ENN_B200_INVALID_PARAMS, "this concatenation needs enn_b200_op_execute_n");
+            break;
         default:
             return fail(ctx, ENN_B200_INVALID_PARAMS, "op needs enn_b200_op_execute2");
     }
@@ -627,6 +640,21 @@ int32_t enn_b200_op_execute2(enn_b200_op *op, const void *in0, const void *in1, 
     cudaError_t e = launch_add(op->add, op->count, in0, in1, out, op->ctx->sm_count, op->ctx->stream);
     if (e != cudaSuccess) return cuda_fail(op->ctx, e, "add launch");
     return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_op_execute_n(enn_b200_op *op, const void *const *ins, int32_t n_in, void *out) {
+    if (!op) return ENN_B200_INVALID_PARAMS;
+    if (!ins || !out || n_in < 1) return fail(op->ctx, ENN_B200_INVALID_PARAMS, "null device pointer");
+    for (int i = 0; i < n_in; ++i)
+        if (!ins[i]) return fail(op->ctx, ENN_B200_INVALID_PARAMS, "null device pointer");
+    if (op->kind == OP_CONCAT) {
+        cudaError_t e = launch_graph_op(op, ins, n_in, out);
+        if (e == cudaErrorInvalidValue) return fail(op->ctx, ENN_B200_INVALID_PARAMS, "wrong number of inputs for this concatenation");
+        if (e != cudaSuccess) return cuda_fail(op->ctx, e, "concat launch");
+        return ENN_B200_SUCCESS;
+    }
+    if (op->kind == OP_ADD) return n_in == 2 ? enn_b200_op_execute2(op, ins[0], ins[1], out) : fail(op->ctx, ENN_B200_INVALID_PARAMS, "add takes two inputs");
+    return n_in == 1 ? enn_b200_op_execute(op, ins[0], out) : fail(op->ctx, ENN_B200_INVALID_PARAMS, "this operator takes one input");
 }
 
 int32_t enn_b200_op_info(const enn_b200_op *op, enn_b200_op_info_t *info) {
@@ -654,6 +682,7 @@ int32_t enn_b200_op_release(enn_b200_op *op) {
     if (op->ctx) cudaSetDevice(op->ctx->device);
     if (op->tc) tc_release(op);
     if (op->dw_ring) dw_ring_release(op);
+    if (op->graph_state) graph_op_release(op);
     for (void *p : op->owned) cudaFree(p);
     delete op;
     return ENN_B200_SUCCESS;

@@ -36,7 +36,7 @@ struct enn_b200_context {
 
 namespace enn_b200 {
 
-enum OpKind { OP_CONV = 0, OP_DEPTHWISE = 1, OP_DECONV = 2, OP_FC = 3, OP_ADD = 4, OP_AVGPOOL = 5 };
+enum OpKind { OP_CONV = 0, OP_DEPTHWISE = 1, OP_DECONV = 2, OP_FC = 3, OP_ADD = 4, OP_AVGPOOL = 5, OP_MAXPOOL = 6, OP_MEAN = 7, OP_CONCAT = 8, OP_SOFTMAX = 9, OP_RESIZE = 10 };
 
 // Geometry + quantisation handed to kernels by value.
 struct ConvGeom {
@@ -102,6 +102,7 @@ struct enn_b200_op {
     void *dw_w = nullptr;              // depthwise 3x3 fast path: packed 3-tap weight words (in `owned`)
     void *dw_ring = nullptr;           // depthwise row-ring plan (depthwise.cu), owned
     void *tc = nullptr;                // tensor-core plan (gemm_tc.cu), owned
+    void *graph_state = nullptr;       // state of Mean / Concat / Softmax / Resize (graph_ops.cu), owned
 };
 
 namespace enn_b200 {
@@ -126,6 +127,9 @@ cudaError_t add_kernel_init();
 cudaError_t launch_add(const AddParams &p, int64_t count, const void *a, const void *b, void *out, int sm_count,
                        cudaStream_t s);
 cudaError_t launch_avgpool(const PoolGeom &p, const void *in, void *out, cudaStream_t s);
+cudaError_t launch_maxpool(const PoolGeom &p, const void *in, void *out, cudaStream_t s);
+cudaError_t launch_graph_op(enn_b200_op *op, const void *const *ins, int n_in, void *out);     // Mean, Concat, Softmax, Resize
+void graph_op_release(enn_b200_op *op);
 cudaError_t launch_transpose_nchw_nhwc(const void *src, void *dst, int n, int c, int h, int w, bool to_nhwc,
                                        cudaStream_t s);
 

@@ -29,7 +29,8 @@ struct enn_b200_oplist {
     };
     struct Node {
         enn_b200_op *op = nullptr;
-        int in0 = -1, in1 = -1, out = -1;
+        std::vector<int> ins;
+        int out = -1;
     };
     std::vector<Tensor> tensors;
     std::vector<Node> nodes;
@@ -62,11 +63,9 @@ int32_t run_nodes(enn_b200_oplist *l, int slot = 0) {
         return (slot == 1 && T.dev_alt) ? T.dev_alt : T.dev;
     };
     for (auto &n : l->nodes) {
-        int32_t st;
-        if (n.in1 >= 0)
-            st = enn_b200_op_execute2(n.op, ptr(n.in0), ptr(n.in1), ptr(n.out));
-        else
-            st = enn_b200_op_execute(n.op, ptr(n.in0), ptr(n.out));
+        const void *ins[ENN_B200_CONCAT_MAX_INPUTS];
+        for (size_t i = 0; i < n.ins.size(); ++i) ins[i] = ptr(n.ins[i]);
+        const int32_t st = enn_b200_op_execute_n(n.op, ins, static_cast<int32_t>(n.ins.size()), ptr(n.out));
         if (st != ENN_B200_SUCCESS) return st;
     }
     return ENN_B200_SUCCESS;
@@ -95,21 +94,27 @@ int32_t enn_b200_oplist_add_tensor(enn_b200_oplist *l, int64_t bytes, int32_t *t
 }
 
 int32_t enn_b200_oplist_add_op(enn_b200_oplist *l, enn_b200_op *op, const int32_t *in_ids, int32_t n_in, int32_t out_id) {
-    if (!l || !op || !in_ids || n_in < 1 || n_in > 2) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: bad argument");
+    if (!l || !op || !in_ids || n_in < 1 || n_in > ENN_B200_CONCAT_MAX_INPUTS) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: bad argument");
     if (l->finalized) return lfail(l, ENN_B200_FAILURE, "oplist already finalized");
     const int nt = static_cast<int>(l->tensors.size());
     if (out_id < 0 || out_id >= nt) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: bad output tensor id");
     for (int i = 0; i < n_in; ++i)
         if (in_ids[i] < 0 || in_ids[i] >= nt) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: bad input tensor id");
-    if ((op->kind == enn_b200::OP_ADD) != (n_in == 2)) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: wrong input count for this operator");
+    const int want_in = op->kind == enn_b200::OP_ADD ? 2 : (op->kind == enn_b200::OP_CONCAT ? n_in : 1);
+    if (n_in != want_in) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: wrong input count for this operator");
     if (l->tensors[out_id].bytes < op->info.out_bytes) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: output tensor too small");
-    const int64_t need_in = n_in == 2 ? op->info.in_bytes / 2 : op->info.in_bytes;
-    for (int i = 0; i < n_in; ++i)
-        if (l->tensors[in_ids[i]].bytes < need_in) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: input tensor too small");
+    if (op->kind == enn_b200::OP_CONCAT) {
+        int64_t have = 0;
+        for (int i = 0; i < n_in; ++i) have += l->tensors[in_ids[i]].bytes;
+        if (have < op->info.in_bytes) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: input tensors too small");
+    } else {
+        const int64_t need_in = n_in == 2 ? op->info.in_bytes / 2 : op->info.in_bytes;
+        for (int i = 0; i < n_in; ++i)
+            if (l->tensors[in_ids[i]].bytes < need_in) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: input tensor too small");
+    }
     enn_b200_oplist::Node n;
     n.op = op;
-    n.in0 = in_ids[0];
-    n.in1 = n_in == 2 ? in_ids[1] : -1;
+    n.ins.assign(in_ids, in_ids + n_in);
     n.out = out_id;
     l->nodes.push_back(n);
     return ENN_B200_SUCCESS;
@@ -140,8 +145,7 @@ int32_t enn_b200_oplist_finalize(enn_b200_oplist *l) {
     for (int id : l->outputs) l->tensors[id].is_output = true;
     for (int i = 0; i < n_nodes; ++i) {
         auto &n = l->nodes[i];
-        for (int t : {n.in0, n.in1}) {
-            if (t < 0) continue;
+        for (int t : n.ins) {
             auto &T = l->tensors[t];
             if (T.first_def < 0 && !T.is_input) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist: tensor read before it is written");
             T.last_use = i;

@@ -79,4 +79,40 @@ bool derive_requant(int32_t cout, bool per_channel, float in_scale, float w_scal
     return ok;
 }
 
+uint8_t concat_requant_byte(uint8_t byte, bool is_signed, float in_scale, int32_t in_zp, float out_scale, int32_t out_zp) {
+    const int32_t x = is_signed ? static_cast<int32_t>(static_cast<int8_t>(byte)) : static_cast<int32_t>(byte);
+    const volatile float inverse_output_scale = 1.f / out_scale;
+    const volatile float scale = in_scale * inverse_output_scale;
+    const volatile float bias = static_cast<float>(-in_zp) * scale;
+    const volatile float prod = static_cast<float>(x) * scale;
+    const volatile float sum = prod + bias;
+    int32_t value = static_cast<int32_t>(std::round(sum)) + out_zp;
+    const int32_t qmin = is_signed ? -128 : 0, qmax = is_signed ? 127 : 255;
+    value = value > qmin ? value : qmin;
+    value = value < qmax ? value : qmax;
+    return static_cast<uint8_t>(value);
+}
+
+void softmax_exp_table(bool is_signed, float in_scale, int32_t in_zp, float beta, float *table) {
+    float deq[256];
+    for (int b = 0; b < 256; ++b) {
+        const int32_t x = is_signed ? static_cast<int32_t>(static_cast<int8_t>(b)) : b;
+        const volatile float centred = static_cast<float>(x) - static_cast<float>(in_zp);
+        deq[b] = in_scale * centred;
+    }
+    for (int m = 0; m < 256; ++m)
+        for (int b = 0; b < 256; ++b) {
+            const volatile float diff = deq[b] - deq[m];
+            const volatile float arg = diff * beta;
+            table[m * 256 + b] = std::exp(static_cast<float>(arg));
+        }
+}
+
+void resize_scales(int32_t in_h, int32_t in_w, int32_t out_h, int32_t out_w, bool align_corners, float *height_scale, float *width_scale) {
+    *height_scale = static_cast<float>(in_h) / out_h;
+    *width_scale = static_cast<float>(in_w) / out_w;
+    if (align_corners && out_h > 1) *height_scale = static_cast<float>(in_h - 1) / (out_h - 1);
+    if (align_corners && out_w > 1) *width_scale = static_cast<float>(in_w - 1) / (out_w - 1);
+}
+
 }  // namespace enn_b200

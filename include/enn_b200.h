@@ -111,6 +111,52 @@ typedef struct enn_b200_pool_desc {
     float out_scale;  int32_t out_zp;
 } enn_b200_pool_desc;
 
+/* Remaining quantized graph operators of the reference's u8 models.  Tensors are described by their memory order, so
+ * the same descriptors serve NHWC and NCHW callers.
+ * Mean (CLMean.cpp:72-297, MeanKernels.cpp): integer sum over the axes in axis_mask (bit i = dims[i]) divided by the
+ * element count with C truncation; no rescaling (the reference assumes equal input and output quantisation). */
+typedef struct enn_b200_mean_desc {
+    int32_t dims[4];                /* in memory order, outermost first (NHWC: n, h, w, c) */
+    int32_t axis_mask;
+    int32_t act_dtype;
+} enn_b200_mean_desc;
+
+/* Concatenation (CLConcat.cpp:224-256, ConcatKernels.cpp:399-470): input i is viewed as [outer][inner[i]] and lands at
+ * column offset sum(inner[0..i)) of the output [outer][sum inner]; an input whose scale differs from the output's is
+ * requantised in float, round((x - zp_i) * s_i / s_o) + zp_o, one whose scale is equal is copied as it is. */
+#define ENN_B200_CONCAT_MAX_INPUTS 8
+typedef struct enn_b200_concat_desc {
+    int32_t n_inputs;
+    int32_t act_dtype;
+    int64_t outer;
+    int64_t inner[ENN_B200_CONCAT_MAX_INPUTS];
+    float in_scale[ENN_B200_CONCAT_MAX_INPUTS];
+    int32_t in_zp[ENN_B200_CONCAT_MAX_INPUTS];
+    float out_scale;
+    int32_t out_zp;
+} enn_b200_concat_desc;
+
+/* Softmax over `channels` of a tensor viewed as [outer][channels][inner] (CLSoftmax.cpp:81-150: dequantise, float
+ * softmax_axis2 with beta, quantise with round(x / s_o + zp_o) and saturation). */
+typedef struct enn_b200_softmax_desc {
+    int64_t outer;
+    int32_t channels;
+    int64_t inner;
+    float beta;
+    int32_t act_dtype;
+    float in_scale;   int32_t in_zp;
+    float out_scale;  int32_t out_zp;
+} enn_b200_softmax_desc;
+
+/* Bilinear resize of NHWC bytes (CLResizeBilinear.cpp, ResizeBilinearKernels.cpp:41-83): float interpolation of the raw
+ * bytes, truncated; no rescaling. */
+typedef struct enn_b200_resize_desc {
+    int32_t n, h, w, c;
+    int32_t out_h, out_w;
+    int32_t align_corners, half_pixel_centers;
+    int32_t act_dtype;
+} enn_b200_resize_desc;
+
 /* Derived per-op facts, for callers that size buffers or report work. */
 typedef struct enn_b200_op_info_t {
     int32_t impl;                   /* ENN_B200_IMPL_* */
@@ -170,6 +216,17 @@ int32_t enn_b200_add_prepare(enn_b200_context *ctx, const enn_b200_add_desc *des
 /* CLAveragepool::initialize (CLAveragepool.cpp). */
 int32_t enn_b200_avgpool_prepare(enn_b200_context *ctx, const enn_b200_pool_desc *desc, enn_b200_op **op);
 
+/* CLMaxpool::initialize (CLMaxpool.cpp:21-118; kernel MaxpoolKernels.cpp:33-58: window clipped to the image, clamp). */
+int32_t enn_b200_maxpool_prepare(enn_b200_context *ctx, const enn_b200_pool_desc *desc, enn_b200_op **op);
+/* CLMean::initialize (CLMean.cpp:30-107). */
+int32_t enn_b200_mean_prepare(enn_b200_context *ctx, const enn_b200_mean_desc *desc, enn_b200_op **op);
+/* CLConcat::initialize (CLConcat.cpp:126-205); executed with enn_b200_op_execute_n. */
+int32_t enn_b200_concat_prepare(enn_b200_context *ctx, const enn_b200_concat_desc *desc, enn_b200_op **op);
+/* CLSoftmax::initialize (CLSoftmax.cpp:28-121). */
+int32_t enn_b200_softmax_prepare(enn_b200_context *ctx, const enn_b200_softmax_desc *desc, enn_b200_op **op);
+/* CLResizeBilinear::initialize (CLResizeBilinear.cpp:120-218). */
+int32_t enn_b200_resize_bilinear_prepare(enn_b200_context *ctx, const enn_b200_resize_desc *desc, enn_b200_op **op);
+
 /* Force the kernel family of a prepared conv / fc / deconv handle (ENN_B200_IMPL_DIRECT or
  * ENN_B200_IMPL_TCGEN05 ...); INVALID_PARAMS if that family cannot run the geometry.  For tests and benches. */
 int32_t enn_b200_op_set_impl(enn_b200_op *op, int32_t impl);
@@ -180,6 +237,8 @@ int32_t enn_b200_op_set_impl(enn_b200_op *op, int32_t impl);
 int32_t enn_b200_op_execute(enn_b200_op *op, const void *in_dev, void *out_dev);
 /* Two-input form for the quantized add (inputs = {a, b}). */
 int32_t enn_b200_op_execute2(enn_b200_op *op, const void *in0_dev, const void *in1_dev, void *out_dev);
+/* n-input form (concatenation; also accepts the one- and two-input operators). */
+int32_t enn_b200_op_execute_n(enn_b200_op *op, const void *const *ins_dev, int32_t n_in, void *out_dev);
 /* No counterpart in the reference.  Runs a prepared Conv2D / Deconvolution whose input is gathered into a scratch
  * matrix without allocating anything: the matrix goes into a 32 MiB device array that is part of the library image.
  * For callers that may not call cudaMalloc at run time.  Limits: the operator must be on the tensor-core path and

@@ -132,6 +132,44 @@ def avgpool(desc, x):
     return out
 
 
+def maxpool(desc, x):
+    x = np.ascontiguousarray(x)
+    out = np.empty((desc.n, desc.out_h, desc.out_w, desc.c), dtype=x.dtype)
+    assert lib.orc_maxpool(C.byref(desc), _ptr(x), _ptr(out)) == 0
+    return out
+
+
+def mean(desc, x):
+    x = np.ascontiguousarray(x)
+    shape = [1 if desc.axis_mask & (1 << a) else desc.dims[a] for a in range(4)]
+    out = np.empty(shape, dtype=x.dtype)
+    assert lib.orc_mean(C.byref(desc), _ptr(x), _ptr(out)) == 0
+    return out
+
+
+def concat(desc, xs):
+    xs = [np.ascontiguousarray(x) for x in xs]
+    total = sum(desc.inner[i] for i in range(desc.n_inputs))
+    out = np.empty((desc.outer, total), dtype=xs[0].dtype)
+    arr = (C.c_void_p * len(xs))(*[x.ctypes.data for x in xs])
+    assert lib.orc_concat(C.byref(desc), arr, _ptr(out)) == 0
+    return out
+
+
+def softmax(desc, x):
+    x = np.ascontiguousarray(x)
+    out = np.empty(x.shape, dtype=x.dtype)
+    assert lib.orc_softmax(C.byref(desc), _ptr(x), _ptr(out)) == 0
+    return out
+
+
+def resize_bilinear(desc, x):
+    x = np.ascontiguousarray(x)
+    out = np.empty((desc.n, desc.out_h, desc.out_w, desc.c), dtype=x.dtype)
+    assert lib.orc_resize_bilinear(C.byref(desc), _ptr(x), _ptr(out)) == 0
+    return out
+
+
 def num_threads():
     return lib.orc_num_threads()
 
@@ -188,4 +226,43 @@ def ref_add(desc, a, b):
     a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
     out = np.empty(a.shape, dtype=np.uint8)
     assert ref.ref_add(C.byref(desc), _ptr(a), _ptr(b), _ptr(out)) == 0
+    return out
+
+
+def ref_maxpool(desc, x):
+    x = np.ascontiguousarray(x)
+    out = np.empty((desc.n, desc.out_h, desc.out_w, desc.c), dtype=np.uint8)
+    assert ref.ref_maxpool(C.byref(desc), _ptr(x), _ptr(out)) == 0
+    return out
+
+
+def ref_mean(desc, x):
+    """The reference's CLMean on the same dims and axes (its kernels index dims as N, C, H, W; the arithmetic does not
+    depend on the names)."""
+    x = np.ascontiguousarray(x)
+    shape = [1 if desc.axis_mask & (1 << a) else desc.dims[a] for a in range(4)]
+    out = np.zeros(shape, dtype=np.uint8)
+    assert ref.ref_mean(desc.dims, C.c_int32(desc.axis_mask), _ptr(x), _ptr(out)) == 0
+    return out
+
+
+def ref_concat_channels_nchw(xs, in_scale, in_zp, out_scale, out_zp):
+    """Reference concat_axis1 on NCHW inputs [N][C_i][H*W]; returns [N][sum C][H*W]."""
+    xs = [np.ascontiguousarray(x) for x in xs]
+    n, hw = xs[0].shape[0], xs[0].shape[2]
+    ch = (C.c_int32 * len(xs))(*[x.shape[1] for x in xs])
+    sc = (C.c_float * len(xs))(*in_scale)
+    zp = (C.c_int32 * len(xs))(*in_zp)
+    arr = (C.c_void_p * len(xs))(*[x.ctypes.data for x in xs])
+    out = np.zeros((n, sum(x.shape[1] for x in xs), hw), np.uint8)
+    ref.ref_concat_axis1.argtypes = [C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_int32),
+                                     C.c_float, C.c_int32, C.POINTER(C.c_void_p), C.c_void_p]
+    assert ref.ref_concat_axis1(len(xs), n, ch, hw, sc, zp, out_scale, out_zp, arr, _ptr(out)) == 0
+    return out
+
+
+def ref_resize_bilinear(desc, x):
+    x = np.ascontiguousarray(x)
+    out = np.empty((desc.n, desc.out_h, desc.out_w, desc.c), dtype=np.uint8)
+    assert ref.ref_resize_bilinear(C.byref(desc), _ptr(x), _ptr(out)) == 0
     return out

@@ -21,6 +21,8 @@ int main(int argc, char **argv) {
         "eltwiseAddQuantized_opt_INT8",
         // per-tensor GEMM convolution (CLGEMMConvolutionQuantized + CLPadConvert)
         "pad_opt_INT8", "convert_optimized_INT8", "convertBlocked2_INT8", "alignQuantizedWeight_gemm_INT8", "quantizedGemmBlocked_INT8",
+        // remaining quantized graph operators
+        "maxpooling_INT8", "mean_feature_opt_INT8", "sum_axis_INT8", "mean_INT8", "concat_axis1_INT8", "resize_bilinear_INT8",
     };
     FILE *f = std::fopen(argv[1], "w");
     if (!f) return 3;

@@ -22,6 +22,30 @@ def _add(seed, count, act=0):
     return d, a, b
 
 
+def _maxpool(seed, n, h, w, c, k, s, pad, act=0):
+    x = np.random.default_rng(seed).integers(0, 256, (n, h, w, c), dtype=np.int64).astype(np.uint8)
+    oh, ow = (h - k + s + 2 * pad) // s, (w - k + s + 2 * pad) // s          # CLMaxpool.cpp:62-67
+    d = enn.PoolDesc(n=n, h=h, w=w, c=c, kh=k, kw=k, stride_h=s, stride_w=s, pad_t=pad, pad_l=pad, out_h=oh, out_w=ow, activation=act,
+                     act_dtype=enn.U8, out_scale=0.05, out_zp=10)
+    return d, x
+
+
+def _mean(seed, dims, axes):
+    x = np.random.default_rng(seed).integers(0, 256, dims, dtype=np.int64).astype(np.uint8)
+    return enn.mean_desc(dims, axes), x
+
+
+def _concat(seed, outer, inner, scales, zps, out_scale, out_zp):
+    rng = np.random.default_rng(seed)
+    xs = [rng.integers(0, 256, (outer, k), dtype=np.int64).astype(np.uint8) for k in inner]
+    return enn.concat_desc(outer, inner, scales, zps, out_scale, out_zp), xs
+
+
+def _resize(seed, n, h, w, c, oh, ow, align=0, half=0):
+    x = np.random.default_rng(seed).integers(0, 256, (n, h, w, c), dtype=np.int64).astype(np.uint8)
+    return enn.ResizeDesc(n=n, h=h, w=w, c=c, out_h=oh, out_w=ow, align_corners=align, half_pixel_centers=half, act_dtype=enn.U8), x
+
+
 CASES = {
     "conv_pc_3x3": ("conv_pc", lambda: cases.conv_case(seed=101, n=2, h=9, w=10, cin=8, cout=12, k=3, per_channel=True, out_scale=0.2)),
     "conv_pc_1x1_relu6": ("conv_pc", lambda: cases.conv_case(seed=102, n=1, h=7, w=7, cin=32, cout=16, k=1, per_channel=True, out_scale=0.1, out_zp=0)),
@@ -48,6 +72,17 @@ CASES = {
     "avgpool_3x3s2": ("pool", lambda: _pool(112, 1, 9, 9, 8, 3, 2, act=enn.ACT_RELU6)),
     "add": ("add", lambda: _add(113, 4099)),
     "add_relu6": ("add", lambda: _add(114, 1000, act=enn.ACT_RELU6)),
+    # remaining graph operators: maxpooling, mean (global-pool form and the halving sum_axis form), concat_axis1 with equal and
+    # different scales, resize_bilinear in its three coordinate conventions
+    "maxpool_3x3s2_pad": ("maxpool", lambda: _maxpool(130, 2, 9, 11, 6, 3, 2, 1)),
+    "maxpool_2x2_relu6": ("maxpool", lambda: _maxpool(131, 1, 8, 8, 16, 2, 2, 0, act=enn.ACT_RELU6)),
+    "mean_hw_nhwc": ("mean", lambda: _mean(132, (2, 7, 7, 12), (1, 2))),
+    "mean_trailing": ("mean", lambda: _mean(133, (3, 5, 6, 9), (2, 3))),
+    "mean_single_axis": ("mean", lambda: _mean(134, (2, 4, 10, 3), (2,))),
+    "concat_mixed_scales": ("concat", lambda: _concat(135, 30, (5, 8, 3), (0.02, 0.031, 0.02), (3, 120, 7), 0.02, 11)),
+    "resize_up": ("resize", lambda: _resize(136, 2, 5, 6, 4, 10, 13)),
+    "resize_align_corners": ("resize", lambda: _resize(137, 1, 7, 7, 3, 13, 9, align=1)),
+    "resize_half_pixel_down": ("resize", lambda: _resize(138, 1, 9, 8, 2, 4, 5, half=1)),
 }
 
 
@@ -67,6 +102,19 @@ def run_reference(orc, kind, case):
     if kind == "pool":
         d, x = case
         return orc.ref_avgpool(d, x)
+    if kind == "maxpool":
+        return orc.ref_maxpool(*case)
+    if kind == "mean":
+        return orc.ref_mean(*case)
+    if kind == "resize":
+        return orc.ref_resize_bilinear(*case)
+    if kind == "concat":
+        # the reference concatenates NCHW tensors along C: present the [outer][inner_i] inputs as [1][inner_i][outer]
+        d, xs = case
+        n = d.n_inputs
+        out = orc.ref_concat_channels_nchw([np.ascontiguousarray(x.T[None]) for x in xs], [d.in_scale[i] for i in range(n)],
+                                           [d.in_zp[i] for i in range(n)], d.out_scale, d.out_zp)
+        return np.ascontiguousarray(out[0].T)
     d, a, b = case
     return orc.ref_add(d, a, b)
 
@@ -84,5 +132,13 @@ def run_oracle(orc, kind, case):
     if kind == "pool":
         d, x = case
         return orc.avgpool(d, x)
+    if kind == "maxpool":
+        return orc.maxpool(*case)
+    if kind == "mean":
+        return orc.mean(*case)
+    if kind == "resize":
+        return orc.resize_bilinear(*case)
+    if kind == "concat":
+        return orc.concat(*case)
     d, a, b = case
     return orc.add(d, a, b)

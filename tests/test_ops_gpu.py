@@ -774,6 +774,15 @@ def test_library_matches_reference_kernel_text_golden(enn, ctx, name):
     golden = np.load(os.path.join(HERE, "golden", "ref_kernels.npz"))[name]
     kind, mk = ref_cases.CASES[name]
     case = mk()
+    if kind in ("maxpool", "mean", "resize", "concat"):
+        d, x = case
+        op = {"maxpool": enn.maxpool, "mean": enn.mean, "resize": enn.resize_bilinear, "concat": enn.concat}[kind](ctx, d)
+        try:
+            y = op.run_n(x) if kind == "concat" else op.run(x)
+            assert np.array_equal(y, golden.reshape(-1)), name
+        finally:
+            op.release()
+        return
     if kind in ("conv_pc", "conv_pt", "dw", "deconv"):
         d, x, w, b, sc = case
         op = {"conv_pc": enn.conv2d, "conv_pt": enn.conv2d, "dw": enn.depthwise, "deconv": enn.deconv}[kind](ctx, d, w, b, sc)
@@ -790,3 +799,115 @@ def test_library_matches_reference_kernel_text_golden(enn, ctx, name):
             assert np.array_equal(op.run(x, x2), golden.reshape(-1)), (name, impl)
     finally:
         op.release()
+
+
+# ---- remaining graph operators (MaxPool, Mean, Concat, Softmax, Resize) against the oracle ----
+@pytest.mark.parametrize("shape", [(2, 9, 11, 6, 3, 2, 1, "u8", 0), (1, 112, 112, 24, 3, 2, 0, "u8", 3), (3, 7, 7, 40, 2, 1, 0, "s8", 0),
+                                   (1, 5, 6, 3, 5, 1, 2, "s8", 1)])
+def test_maxpool_parity(enn, orc, ctx, shape):
+    n, h, w, c, k, s, pad, dt, act = shape
+    signed = dt == "s8"
+    x = np.random.default_rng(h * w + c).integers(-128 if signed else 0, 128 if signed else 256, (n, h, w, c), dtype=np.int64).astype(np.int8 if signed else np.uint8)
+    oh, ow = (h - k + s + 2 * pad) // s, (w - k + s + 2 * pad) // s
+    d = enn.PoolDesc(n=n, h=h, w=w, c=c, kh=k, kw=k, stride_h=s, stride_w=s, pad_t=pad, pad_l=pad, out_h=oh, out_w=ow, activation=act,
+                     act_dtype=enn.S8 if signed else enn.U8, out_scale=0.04, out_zp=-20 if signed else 7)
+    op = enn.maxpool(ctx, d)
+    try:
+        _check(op, orc.maxpool(d, x), x)
+    finally:
+        op.release()
+
+
+@pytest.mark.parametrize("dims,axes,dt", [((4, 7, 7, 1280), (1, 2), "u8"), ((2, 9, 5, 33), (3,), "u8"), ((3, 4, 6, 8), (0, 2), "s8"),
+                                          ((2, 3, 5, 7), (0, 1, 2, 3), "s8"), ((1, 1, 40, 17), (2,), "u8")])
+def test_mean_parity(enn, orc, ctx, dims, axes, dt):
+    signed = dt == "s8"
+    x = np.random.default_rng(sum(dims)).integers(-128 if signed else 0, 128 if signed else 256, dims, dtype=np.int64).astype(np.int8 if signed else np.uint8)
+    d = enn.mean_desc(dims, axes, enn.S8 if signed else enn.U8)
+    op = enn.mean(ctx, d)
+    try:
+        _check(op, orc.mean(d, x), x)
+    finally:
+        op.release()
+
+
+@pytest.mark.parametrize("outer,inner,dt", [(56 * 56 * 2, (24, 24, 48), "u8"), (3, (1000, 7), "u8"), (17, (5, 3, 9, 2, 8, 1, 4, 6), "s8"), (1, (33,), "u8")])
+def test_concat_parity(enn, orc, ctx, outer, inner, dt):
+    signed = dt == "s8"
+    rng = np.random.default_rng(outer + len(inner))
+    xs = [rng.integers(-128 if signed else 0, 128 if signed else 256, (outer, k), dtype=np.int64).astype(np.int8 if signed else np.uint8) for k in inner]
+    scales = [0.02 if i % 3 == 0 else float(rng.uniform(0.005, 0.08)) for i in range(len(inner))]      # every third input: plain copy
+    zps = [int(rng.integers(-20, 20) if signed else rng.integers(0, 256)) for _ in inner]
+    d = enn.concat_desc(outer, inner, scales, zps, 0.02, -3 if signed else 120, enn.S8 if signed else enn.U8)
+    op = enn.concat(ctx, d)
+    try:
+        y = op.run_n(xs).reshape(outer, sum(inner))
+        assert np.array_equal(y, orc.concat(d, xs))
+    finally:
+        op.release()
+
+
+@pytest.mark.parametrize("outer,channels,inner,beta,dt", [(256, 1000, 1, 1.0, "u8"), (2, 21, 65, 1.0, "u8"), (7, 10, 1, 0.5, "s8"), (1, 1, 9, 2.0, "u8")])
+def test_softmax_parity(enn, orc, ctx, outer, channels, inner, beta, dt):
+    """Quantized softmax = dequantise, float softmax, quantise.  The library and the oracle take exp() from the same host
+    libm and keep every float operation separate, so the bytes are equal; against the reference's OpenCL exp() a last-
+    bit difference of the exponential can move an output by one step."""
+    signed = dt == "s8"
+    x = np.random.default_rng(channels).integers(-128 if signed else 0, 128 if signed else 256, (outer, channels, inner), dtype=np.int64).astype(np.int8 if signed else np.uint8)
+    d = enn.SoftmaxDesc(outer=outer, channels=channels, inner=inner, beta=beta, act_dtype=enn.S8 if signed else enn.U8, in_scale=0.05,
+                        in_zp=-3 if signed else 121, out_scale=1.0 / 256, out_zp=-128 if signed else 0)
+    op = enn.softmax(ctx, d)
+    try:
+        y = op.run(x).reshape(x.shape)
+        y_ref = orc.softmax(d, x)
+        assert np.array_equal(y, y_ref)
+        assert len(np.unique(y_ref)) > (3 if channels > 1 else 0)
+    finally:
+        op.release()
+
+
+@pytest.mark.parametrize("shape", [(2, 5, 6, 4, 10, 13, 0, 0, "u8"), (1, 33, 33, 21, 129, 129, 1, 0, "u8"), (2, 9, 8, 16, 4, 5, 0, 1, "s8"),
+                                   (1, 1, 1, 8, 7, 3, 1, 0, "u8"), (1, 16, 16, 32, 32, 32, 0, 1, "u8")])
+def test_resize_bilinear_parity(enn, orc, ctx, shape):
+    n, h, w, c, oh, ow, align, half, dt = shape
+    signed = dt == "s8"
+    x = np.random.default_rng(h * ow).integers(-128 if signed else 0, 128 if signed else 256, (n, h, w, c), dtype=np.int64).astype(np.int8 if signed else np.uint8)
+    d = enn.ResizeDesc(n=n, h=h, w=w, c=c, out_h=oh, out_w=ow, align_corners=align, half_pixel_centers=half, act_dtype=enn.S8 if signed else enn.U8)
+    op = enn.resize_bilinear(ctx, d)
+    try:
+        _check(op, orc.resize_bilinear(d, x), x)
+    finally:
+        op.release()
+
+
+def test_oplist_with_graph_operators(enn, orc, ctx):
+    """conv -> {maxpool, resize} -> concat -> mean -> softmax in one operator list (a concatenation node with two inputs)."""
+    d1, x, w1, b1, s1 = cases.conv_case(seed=31, n=2, h=16, w=16, cin=8, cout=16, k=3, per_channel=True, out_scale=0.2)
+    y1 = orc.conv2d(d1, x, w1, b1, s1)
+    dp = enn.PoolDesc(n=2, h=16, w=16, c=16, kh=2, kw=2, stride_h=2, stride_w=2, pad_t=0, pad_l=0, out_h=8, out_w=8, activation=0, act_dtype=enn.U8,
+                      out_scale=float(d1.out_scale), out_zp=int(d1.out_zp))
+    y2 = orc.maxpool(dp, y1)
+    dr = enn.ResizeDesc(n=2, h=16, w=16, c=16, out_h=8, out_w=8, align_corners=0, half_pixel_centers=1, act_dtype=enn.U8)
+    y3 = orc.resize_bilinear(dr, y1)
+    dc = enn.concat_desc(2 * 8 * 8, (16, 16), (float(d1.out_scale), float(d1.out_scale)), (int(d1.out_zp), int(d1.out_zp)), 0.3, 100)
+    y4 = orc.concat(dc, [y2.reshape(-1, 16), y3.reshape(-1, 16)])
+    dm = enn.mean_desc((2, 8, 8, 32), (1, 2))
+    y5 = orc.mean(dm, y4.reshape(2, 8, 8, 32))
+    ds = enn.SoftmaxDesc(outer=2, channels=32, inner=1, beta=1.0, act_dtype=enn.U8, in_scale=0.3, in_zp=100, out_scale=1.0 / 256, out_zp=0)
+    y6 = orc.softmax(ds, y5.reshape(2, 32, 1))
+    ol = enn.OpList(ctx)
+    try:
+        t = [ol.tensor(v.size) for v in (x, y1, y2, y3, y4, y5, y6)]
+        ol.add(enn.conv2d(ctx, d1, w1, b1, s1), [t[0]], t[1])
+        ol.add(enn.maxpool(ctx, dp), [t[1]], t[2])
+        ol.add(enn.resize_bilinear(ctx, dr), [t[1]], t[3])
+        ol.add(enn.concat(ctx, dc), [t[2], t[3]], t[4])
+        ol.add(enn.mean(ctx, dm), [t[4]], t[5])
+        ol.add(enn.softmax(ctx, ds), [t[5]], t[6])
+        ol.set_io([t[0]], [t[6]], [y6.size])
+        ol.finalize()
+        for _ in range(2):
+            (y,) = ol.execute([x])
+            assert np.array_equal(y, y6.reshape(-1))
+    finally:
+        ol.destroy()

@@ -207,6 +207,18 @@ def test_oracle_matches_reference_kernel_text_golden(orc, ref_golden, name):
     assert np.array_equal(got, ref_golden[name]), name
 
 
+def test_oracle_softmax_against_float64_model(orc, enn):
+    """Softmax has no integer definition; the oracle's float path stays within one output step of a float64 model."""
+    rng = np.random.default_rng(5)
+    x = rng.integers(0, 256, (6, 37, 3), dtype=np.int64).astype(np.uint8)
+    d = enn.SoftmaxDesc(outer=6, channels=37, inner=3, beta=1.0, act_dtype=enn.U8, in_scale=0.04, in_zp=100, out_scale=1.0 / 256, out_zp=0)
+    y = orc.softmax(d, x).astype(np.int64)
+    real = (x.astype(np.float64) - 100) * np.float64(np.float32(0.04))
+    e = np.exp(real - real.max(axis=1, keepdims=True))
+    model = np.clip(np.round(e / e.sum(axis=1, keepdims=True) * 256), 0, 255)
+    assert np.abs(y - model).max() <= 1 and (y != model).mean() < 0.02
+
+
 def test_oracle_matches_reference_kernel_text_live(orc):
     """Fresh random geometry against the live build of the reference kernels (this container only)."""
     if not orc.has_ref_kernels():
@@ -236,3 +248,19 @@ def test_oracle_matches_reference_kernel_text_live(orc):
                                       stride=int(rng.integers(1, 3)), pad=int(rng.integers(0, 2)), per_channel=pc,
                                       layout=int(rng.choice([cases.enn.W_IOHW, cases.enn.W_OHWI])), out_scale=float(rng.uniform(0.05, 0.6)))
             assert np.array_equal(orc.deconv(*tcase), orc.ref_deconv(*tcase))
+        # remaining graph operators against the reference's maxpooling, mean_feature_opt / sum_axis / mean, concat_axis1, resize_bilinear
+        import ref_cases
+        k, st = int(rng.integers(1, 4)), int(rng.integers(1, 3))
+        mp = ref_cases._maxpool(500 + i, 1, h + 2, w + 3, int(rng.integers(1, 6)), k, st, int(rng.integers(0, k)), act=int(rng.integers(0, 4)))
+        assert np.array_equal(orc.maxpool(*mp), orc.ref_maxpool(*mp))
+        dims = tuple(int(v) for v in rng.integers(1, 8, 4))
+        axes = tuple(a for a in range(4) if rng.integers(0, 2)) or (3,)
+        mc = ref_cases._mean(600 + i, dims, axes)
+        assert np.array_equal(orc.mean(*mc), orc.ref_mean(*mc)), (dims, axes)
+        inner = tuple(int(v) for v in rng.integers(1, 9, int(rng.integers(1, 5))))
+        cc = ref_cases._concat(700 + i, int(rng.integers(1, 20)), inner, [float(rng.choice([0.02, rng.uniform(0.004, 0.09)])) for _ in inner],
+                               [int(v) for v in rng.integers(0, 256, len(inner))], 0.02, int(rng.integers(0, 256)))
+        assert np.array_equal(ref_cases.run_oracle(orc, "concat", cc), ref_cases.run_reference(orc, "concat", cc))
+        rc = ref_cases._resize(800 + i, 1, h, w, int(rng.integers(1, 5)), int(rng.integers(1, 20)), int(rng.integers(1, 20)), align=int(rng.integers(0, 2)),
+                               half=int(rng.integers(0, 2)))
+        assert np.array_equal(orc.resize_bilinear(*rc), orc.ref_resize_bilinear(*rc))
