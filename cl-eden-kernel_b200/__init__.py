@@ -75,6 +75,12 @@ PROTOTYPES = {
     "enn_b200_group_wait": (C.c_int32, [_P]),
     "enn_b200_group_last_error": (C.c_int32, [_P, C.c_char_p, C.c_size_t]),
     "enn_b200_group_destroy": (C.c_int32, [_P, C.c_int32]),
+    "enn_b200_model_open": (C.c_int32, [_P, _P, C.c_size_t, C.c_int32, C.POINTER(_P)]),
+    "enn_b200_model_info": (C.c_int32, [_P, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "enn_b200_model_io_bytes": (C.c_int32, [_P, C.c_int32, C.c_int32, C.POINTER(C.c_int64)]),
+    "enn_b200_model_oplist": (C.c_int32, [_P, C.POINTER(_P)]),
+    "enn_b200_model_execute": (C.c_int32, [_P, C.POINTER(_P), C.POINTER(_P)]),
+    "enn_b200_model_close": (C.c_int32, [_P]),
     "enn_b200_nchw_to_nhwc": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "enn_b200_nhwc_to_nchw": (C.c_int32, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "enn_b200_quantize_multiplier": (None, [C.c_double, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
@@ -431,3 +437,35 @@ class Group:
             if destroy_lists:
                 for l in self.lists:
                     l.h = None
+
+
+class Model:
+    """An NNC (v2) model file opened through the front end: parsed, operators prepared, operator list finalized."""
+
+    def __init__(self, ctx, nnc_bytes, batch=0):
+        self.ctx = ctx
+        h = C.c_void_p()
+        buf = (C.c_uint8 * len(nnc_bytes)).from_buffer_copy(nnc_bytes)
+        ctx.check(lib.enn_b200_model_open(ctx.h, buf, len(nnc_bytes), batch, C.byref(h)))
+        self.h = h
+        a, b, c = C.c_int32(), C.c_int32(), C.c_int32()
+        lib.enn_b200_model_info(h, C.byref(a), C.byref(b), C.byref(c))
+        self.n_inputs, self.n_outputs, self.n_operators = a.value, b.value, c.value
+
+    def io_bytes(self, is_output, index):
+        v = C.c_int64()
+        self.ctx.check(lib.enn_b200_model_io_bytes(self.h, int(is_output), index, C.byref(v)))
+        return v.value
+
+    def execute(self, inputs):
+        ins = [np.ascontiguousarray(x) for x in inputs]
+        outs = [np.empty(self.io_bytes(True, i), np.uint8) for i in range(self.n_outputs)]
+        a = (C.c_void_p * len(ins))(*[x.ctypes.data for x in ins])
+        b = (C.c_void_p * len(outs))(*[o.ctypes.data for o in outs])
+        self.ctx.check(lib.enn_b200_model_execute(self.h, a, b))
+        return outs
+
+    def close(self):
+        if self.h:
+            lib.enn_b200_model_close(self.h)
+            self.h = None

@@ -301,6 +301,22 @@ int32_t enn_b200_group_wait(enn_b200_group *group);
 int32_t enn_b200_group_last_error(enn_b200_group *group, char *buf, size_t buf_len);
 int32_t enn_b200_group_destroy(enn_b200_group *group, int32_t destroy_lists);
 
+/* ---- NNC model front end: the model-to-operators half of GpuUserDriver::OpenSubGraph (OperationConstructor::open_oplist
+ *      and create_ud_operator<...>, gpu_op_constructor.cc:63-383, 789-863, 1797-2046) over the NNC v2 flatbuffer
+ *      (src/model/schema/nnc/v2/schema.fbs).  Parses the first subgraph, derives padding / precision / per-channel
+ *      information with the reference's rules, prepares every operator and finalizes an operator list.  `batch` > 0
+ *      replaces the outermost dimension of every activation tensor.  Models whose activations are NHWC in memory only
+ *      (TENSORFLOW_NHWC, CAFFE_NHWC, ANDROID_NN without use_nchw); UINT8 / INT8 tensors only. ---- */
+typedef struct enn_b200_model enn_b200_model;
+int32_t enn_b200_model_open(enn_b200_context *ctx, const void *nnc_bytes, size_t nbytes, int32_t batch, enn_b200_model **model);
+int32_t enn_b200_model_info(enn_b200_model *model, int32_t *n_inputs, int32_t *n_outputs, int32_t *n_operators);
+int32_t enn_b200_model_io_bytes(enn_b200_model *model, int32_t is_output, int32_t index, int64_t *bytes);
+/* The model's operator list (owned by the model), for the pipelined / device-resident calls. */
+int32_t enn_b200_model_oplist(enn_b200_model *model, enn_b200_oplist **list);
+/* ExecuteSubGraph on the model: host buffers in graph input / output order. */
+int32_t enn_b200_model_execute(enn_b200_model *model, const void *const *host_inputs, void *const *host_outputs);
+int32_t enn_b200_model_close(enn_b200_model *model);
+
 /* Layout converters for NCHW models (CLRuntime.cpp:1477-1620 NHWC2NCHW_* / NCHW2NHWC_*), 1-byte elements. */
 int32_t enn_b200_nchw_to_nhwc(enn_b200_context *ctx, const void *src_dev, void *dst_dev, int32_t n, int32_t c,
                               int32_t h, int32_t w);
