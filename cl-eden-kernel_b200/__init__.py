@@ -30,6 +30,7 @@ PROTOTYPES = {
     "enn_b200_free": (C.c_int32, [_P, _P]),
     "enn_b200_upload": (C.c_int32, [_P, _P, _P, C.c_size_t]),
     "enn_b200_download": (C.c_int32, [_P, _P, _P, C.c_size_t]),
+    "enn_b200_copy_device": (C.c_int32, [_P, _P, _P, C.c_size_t]),
     "enn_b200_stream_sync": (C.c_int32, [_P]),
     "enn_b200_host_alloc": (C.c_int32, [C.c_size_t, C.POINTER(_P)]),
     "enn_b200_host_free": (C.c_int32, [_P]),
@@ -52,6 +53,7 @@ PROTOTYPES = {
     "enn_b200_op_execute2": (C.c_int32, [_P, _P, _P, _P]),
     "enn_b200_op_execute_n": (C.c_int32, [_P, C.POINTER(_P), C.c_int32, _P]),
     "enn_b200_op_execute_noalloc": (C.c_int32, [_P, _P, _P]),
+    "enn_b200_op_rebind_constants": (C.c_int32, [_P, _P, _P]),
     "enn_b200_op_info": (C.c_int32, [_P, C.POINTER(OpInfo)]),
     "enn_b200_op_test_starve_next": (C.c_int32, [_P]),
     "enn_b200_op_clear_error": (C.c_int32, [_P]),
@@ -207,6 +209,10 @@ class Op:
     def execute2(self, a_dev, b_dev, out_dev):
         self.ctx.check(lib.enn_b200_op_execute2(self.h, a_dev, b_dev, out_dev))
 
+    def rebind_constants(self, weights_dev=None, bias_dev=None):
+        """Operators prepared with weights_as_input / bias_as_input: take the tensors' current device contents."""
+        self.ctx.check(lib.enn_b200_op_rebind_constants(self.h, weights_dev, bias_dev))
+
     def execute_n(self, in_devs, out_dev):
         arr = (C.c_void_p * len(in_devs))(*[p.value if hasattr(p, "value") else p for p in in_devs])
         self.ctx.check(lib.enn_b200_op_execute_n(self.h, arr, len(in_devs), out_dev))
@@ -260,8 +266,8 @@ class Op:
 
 def _prepare(ctx, fn, desc, w, bias, scales):
     h = C.c_void_p()
-    w = np.ascontiguousarray(w)
-    bias = np.ascontiguousarray(bias, dtype=np.int32)
+    w = np.ascontiguousarray(w) if w is not None else None                      # None: weights_as_input
+    bias = np.ascontiguousarray(bias, dtype=np.int32) if bias is not None else None  # None: bias_as_input
     sc = np.ascontiguousarray(scales, dtype=np.float32) if scales is not None else None
     ctx.check(fn(ctx.h, C.byref(desc), _np_ptr(w), _np_ptr(bias), _np_ptr(sc), C.byref(h)))
     return Op(ctx, h)

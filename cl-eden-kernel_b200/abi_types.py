@@ -21,13 +21,14 @@ class ConvDesc(C.Structure):
         "weight_layout", "per_channel")] + [
         ("in_scale", C.c_float), ("in_zp", C.c_int32), ("w_scale", C.c_float), ("w_zp", C.c_int32),
         ("bias_scale", C.c_float), ("out_scale", C.c_float), ("out_zp", C.c_int32),
-        ("out_h", C.c_int32), ("out_w", C.c_int32)]
+        ("out_h", C.c_int32), ("out_w", C.c_int32), ("weights_as_input", C.c_int32), ("bias_as_input", C.c_int32)]
 
 
 class FcDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("m", "k", "n", "activation", "act_dtype", "weight_dtype", "per_channel")] + [
         ("in_scale", C.c_float), ("in_zp", C.c_int32), ("w_scale", C.c_float), ("w_zp", C.c_int32),
-        ("bias_scale", C.c_float), ("out_scale", C.c_float), ("out_zp", C.c_int32)]
+        ("bias_scale", C.c_float), ("out_scale", C.c_float), ("out_zp", C.c_int32),
+        ("weights_as_input", C.c_int32), ("bias_as_input", C.c_int32)]
 
 
 class AddDesc(C.Structure):

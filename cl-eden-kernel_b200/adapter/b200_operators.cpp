@@ -48,23 +48,36 @@ Status B200OperatorBase::ensure_nhwc_staging(bool nchw) {
 
 Status B200OperatorBase::prepare_conv_like(int kind, const enn_b200_conv_desc &desc, const std::shared_ptr<ITensor> &weight,
                                            const std::shared_ptr<ITensor> &bias, const std::vector<float> &scales) {
+    // A filter or bias that is not a constant tensor is read from its device buffer at every execute()
+    // (CLConvolution.cpp:75-76, CLDepthwiseConvolution.cpp:121; the deconvolution says so in its parameters).
+    enn_b200_conv_desc d = desc;
+    runtime_weights_ = d.weights_as_input != 0 || !weight->is_const();
+    runtime_bias_ = !bias->is_const();
+    d.weights_as_input = runtime_weights_;
+    d.bias_as_input = runtime_bias_;
     std::vector<uint8_t> wt, bt;
-    const void *w = host_bytes(weight, &wt);
-    const int32_t *b = static_cast<const int32_t *>(host_bytes(bias, &bt));
-    const float *sc = desc.per_channel ? scales.data() : nullptr;
+    const void *w = runtime_weights_ ? nullptr : host_bytes(weight, &wt);
+    const int32_t *b = runtime_bias_ ? nullptr : static_cast<const int32_t *>(host_bytes(bias, &bt));
+    const float *sc = d.per_channel ? scales.data() : nullptr;
+    if (d.per_channel && static_cast<int64_t>(scales.size()) < d.cout) return Status::INVALID_PARAMS;
     int32_t st;
-    if (kind == 0) st = enn_b200_conv2d_prepare(runtime_->context(), &desc, w, b, sc, &op_);
-    else if (kind == 1) st = enn_b200_depthwise_prepare(runtime_->context(), &desc, w, b, sc, &op_);
-    else st = enn_b200_deconv_prepare(runtime_->context(), &desc, w, b, sc, &op_);
+    if (kind == 0) st = enn_b200_conv2d_prepare(runtime_->context(), &d, w, b, sc, &op_);
+    else if (kind == 1) st = enn_b200_depthwise_prepare(runtime_->context(), &d, w, b, sc, &op_);
+    else st = enn_b200_deconv_prepare(runtime_->context(), &d, w, b, sc, &op_);
     return to_status(st);
 }
 
 Status B200OperatorBase::execute() {
     if (!op_) return Status::FAILURE;
     enn_b200_context *ctx = runtime_->context();
-    const void *in = inputs_[0]->getDataPtr();
-    void *out = outputs_[0]->getDataPtr();
+    const void *in = device_ptr(inputs_[0]);
+    void *out = device_ptr(outputs_[0]);
+    if (!in || !out) return Status::INVALID_PARAMS;      // not a tensor of this driver, or no buffer assigned yet
     int32_t st;
+    if (runtime_weights_ || runtime_bias_) {
+        st = enn_b200_op_rebind_constants(op_, device_ptr(inputs_[1]), static_cast<const int32_t *>(device_ptr(inputs_[2])));
+        if (st != ENN_B200_SUCCESS) return to_status(st);
+    }
     if (nchw_) {
         st = enn_b200_nchw_to_nhwc(ctx, in, in_nhwc_, in_dim_.n, in_dim_.c, in_dim_.h, in_dim_.w);
         if (st != ENN_B200_SUCCESS) return to_status(st);
@@ -72,7 +85,7 @@ Status B200OperatorBase::execute() {
         if (st != ENN_B200_SUCCESS) return to_status(st);
         return to_status(enn_b200_nhwc_to_nchw(ctx, out_nhwc_, out, out_dim_.n, out_dim_.c, out_dim_.h, out_dim_.w));
     }
-    if (two_inputs_) return to_status(enn_b200_op_execute2(op_, in, inputs_[1]->getDataPtr(), out));
+    if (two_inputs_) return to_status(enn_b200_op_execute2(op_, in, device_ptr(inputs_[1]), out));
     return to_status(enn_b200_op_execute(op_, in, out));
 }
 
@@ -171,6 +184,7 @@ Status B200Deconvolution::initialize(std::vector<std::shared_ptr<ITensor>> input
     d.stride_h = p->stride.h; d.stride_w = p->stride.w;
     d.pad_t = p->padding.t; d.pad_r = p->padding.r; d.pad_b = p->padding.b; d.pad_l = p->padding.l;
     d.groups = p->group_size;
+    d.weights_as_input = p->weights_as_input;
     d.activation = act_code(*p->activation_info);
     Status s = ensure_nhwc_staging(nchw);
     if (s != Status::SUCCESS) return s;
@@ -197,9 +211,13 @@ Status B200FullyConnected::initialize(const std::vector<std::shared_ptr<ITensor>
     d.w_scale = input_tensors[1]->getScale(); d.w_zp = input_tensors[1]->getZeroPoint();
     d.bias_scale = input_tensors[2]->getScale();
     d.out_scale = output_tensors[0]->getScale(); d.out_zp = output_tensors[0]->getZeroPoint();
+    runtime_weights_ = !input_tensors[1]->is_const();     // CLFullyConnected.cpp:36
+    runtime_bias_ = !input_tensors[2]->is_const();
+    d.weights_as_input = runtime_weights_;
+    d.bias_as_input = runtime_bias_;
     std::vector<uint8_t> wt, bt;
-    const void *w = host_bytes(input_tensors[1], &wt);
-    const int32_t *b = static_cast<const int32_t *>(host_bytes(input_tensors[2], &bt));
+    const void *w = runtime_weights_ ? nullptr : host_bytes(input_tensors[1], &wt);
+    const int32_t *b = runtime_bias_ ? nullptr : static_cast<const int32_t *>(host_bytes(input_tensors[2], &bt));
     return to_status(enn_b200_fc_prepare(runtime_->context(), &d, w, b, nullptr, &op_));
 }
 

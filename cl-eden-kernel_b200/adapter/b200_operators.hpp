@@ -32,6 +32,7 @@ protected:
     Dim4 in_dim_{}, out_dim_{};          // logical NCHW-named dims (n, c, h, w)
     void *in_nhwc_ = nullptr, *out_nhwc_ = nullptr;
     bool two_inputs_ = false;
+    bool runtime_weights_ = false, runtime_bias_ = false;   // filter / bias are not constant tensors
 };
 
 class B200Convolution : public B200OperatorBase {
@@ -87,7 +88,7 @@ public:
     std::shared_ptr<ITensor> create_and_copy_tensor(DataType type, const void *data, const Dim4 &dim, DataOrder order, float scale,
                                                     int32_t zero_point) {
         auto t = std::make_shared<B200Tensor>(runtime_, type, dim, order, scale, zero_point, true);
-        t->writeData(data);
+        t->writeData(const_cast<void *>(data));   // DataPtr is void * (Common.hpp:12); the bytes are only read
         return t;
     }
     std::shared_ptr<B200Convolution> createConvolution(const PrecisionType &p) { return std::make_shared<B200Convolution>(runtime_, p); }

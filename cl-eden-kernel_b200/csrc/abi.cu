@@ -182,6 +182,12 @@ int32_t enn_b200_download(enn_b200_context *ctx, void *host_dst, const void *dev
     return ENN_B200_SUCCESS;
 }
 
+int32_t enn_b200_copy_device(enn_b200_context *ctx, void *dev_dst, const void *dev_src, size_t bytes) {
+    if (!ctx || (bytes && (!dev_dst || !dev_src))) return fail(ctx, ENN_B200_INVALID_PARAMS, "bad copy arguments");
+    if (bytes) ENN_CUDA(ctx, cudaMemcpyAsync(dev_dst, dev_src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return ENN_B200_SUCCESS;
+}
+
 int32_t enn_b200_stream_sync(enn_b200_context *ctx) {
     if (!ctx) return ENN_B200_INVALID_PARAMS;
     ENN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -251,8 +257,8 @@ int32_t enn_b200_requant_host(int32_t acc, int32_t mult, int32_t shift, int32_t 
 // ------------------------------------------------------------------------------------------------------
 // Conv2D
 // ------------------------------------------------------------------------------------------------------
-static int32_t conv_like_prepare(enn_b200_context *ctx, const enn_b200_conv_desc *d, const void *w_host,
-                                 const int32_t *bias_host, const float *pc_scales, int kind, enn_b200_op **out) {
+static int32_t conv_like_prepare_const(enn_b200_context *ctx, const enn_b200_conv_desc *d, const void *w_host,
+                                       const int32_t *bias_host, const float *pc_scales, int kind, enn_b200_op **out) {
     if (!ctx || !d || !w_host || !bias_host || !out) return fail(ctx, ENN_B200_INVALID_PARAMS, "null argument");
     *out = nullptr;
     if (!valid_common(d)) return fail(ctx, ENN_B200_INVALID_PARAMS, "bad descriptor");
@@ -420,6 +426,38 @@ static int32_t conv_like_prepare(enn_b200_context *ctx, const enn_b200_conv_desc
     return ENN_B200_SUCCESS;
 }
 
+// Filter and / or bias as runtime tensors: plan with whatever is constant (zeros stand in for the rest), remember
+// what a rebind needs.
+static int32_t conv_like_prepare(enn_b200_context *ctx, const enn_b200_conv_desc *d, const void *w_host,
+                                 const int32_t *bias_host, const float *pc_scales, int kind, enn_b200_op **out) {
+    if (!d || (!d->weights_as_input && !d->bias_as_input)) return conv_like_prepare_const(ctx, d, w_host, bias_host, pc_scales, kind, out);
+    if (!ctx || !out) return fail(ctx, ENN_B200_INVALID_PARAMS, "null argument");
+    *out = nullptr;
+    if (!valid_common(d)) return fail(ctx, ENN_B200_INVALID_PARAMS, "bad descriptor");
+    if ((!d->weights_as_input && !w_host) || (!d->bias_as_input && !bias_host)) return fail(ctx, ENN_B200_INVALID_PARAMS, "constant tensor missing");
+    if (d->per_channel && !pc_scales) return fail(ctx, ENN_B200_INVALID_PARAMS, "per-channel scales missing");
+    const int64_t groups = d->groups > 0 ? d->groups : 1;
+    int64_t w_elems = static_cast<int64_t>(d->cout) * d->kh * d->kw;
+    if (kind == OP_CONV) w_elems *= d->cin / groups;
+    else if (kind == OP_DECONV) w_elems *= d->cin;
+    std::unique_ptr<RuntimeConstants> dyn(new (std::nothrow) RuntimeConstants());
+    if (!dyn) return fail(ctx, ENN_B200_FAILURE, "out of host memory");
+    dyn->weights = d->weights_as_input != 0;
+    dyn->bias = d->bias_as_input != 0;
+    dyn->desc = *d;
+    dyn->desc.weights_as_input = dyn->desc.bias_as_input = 0;
+    dyn->prepare_kind = kind;
+    if (d->per_channel) dyn->scales.assign(pc_scales, pc_scales + d->cout);
+    dyn->w_host.assign(static_cast<size_t>(w_elems), 0);
+    if (w_host) std::memcpy(dyn->w_host.data(), w_host, dyn->w_host.size());
+    dyn->b_host.assign(static_cast<size_t>(d->cout), 0);
+    if (bias_host) std::memcpy(dyn->b_host.data(), bias_host, dyn->b_host.size() * sizeof(int32_t));
+    const int32_t st = conv_like_prepare_const(ctx, &dyn->desc, dyn->w_host.data(), dyn->b_host.data(),
+                                               d->per_channel ? dyn->scales.data() : nullptr, kind, out);
+    if (st == ENN_B200_SUCCESS) (*out)->dyn = std::move(dyn);
+    return st;
+}
+
 int32_t enn_b200_conv2d_prepare(enn_b200_context *ctx, const enn_b200_conv_desc *desc, const void *weights_host,
                                 const int32_t *bias_host, const float *per_channel_scales, enn_b200_op **op) {
     return conv_like_prepare(ctx, desc, weights_host, bias_host, per_channel_scales, OP_CONV, op);
@@ -451,6 +489,7 @@ int32_t enn_b200_fc_prepare(enn_b200_context *ctx, const enn_b200_fc_desc *d, co
     c.per_channel = d->per_channel;
     c.in_scale = d->in_scale; c.in_zp = d->in_zp; c.w_scale = d->w_scale; c.w_zp = d->w_zp;
     c.bias_scale = d->bias_scale; c.out_scale = d->out_scale; c.out_zp = d->out_zp;
+    c.weights_as_input = d->weights_as_input; c.bias_as_input = d->bias_as_input;
     int32_t st = conv_like_prepare(ctx, &c, weights_host, bias_host, per_channel_scales, OP_CONV, op);
     if (st == ENN_B200_SUCCESS) (*op)->kind = OP_FC;
     return st;
@@ -585,6 +624,7 @@ int32_t enn_b200_op_execute(enn_b200_op *op, const void *in, void *out) {
     if (!op) return ENN_B200_INVALID_PARAMS;
     enn_b200_context *ctx = op->ctx;
     if (!in || !out) return fail(ctx, ENN_B200_INVALID_PARAMS, "null device pointer");
+    if (op->dyn && !op->dyn->bound) return fail(ctx, ENN_B200_FAILURE, "filter / bias are runtime tensors: call enn_b200_op_rebind_constants first");
     cudaError_t e = cudaSuccess;
     switch (op->kind) {
         case OP_CONV:
@@ -674,6 +714,30 @@ int32_t enn_b200_op_clear_error(enn_b200_op *op) {
     if (!op) return ENN_B200_INVALID_PARAMS;
     if (op->tc) tc_clear_error(op);
     if (op->dw_ring) dw_ring_clear_error(op);
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_op_rebind_constants(enn_b200_op *op, const void *weights_dev, const int32_t *bias_dev) {
+    if (!op || !op->ctx) return ENN_B200_INVALID_PARAMS;
+    enn_b200_context *ctx = op->ctx;
+    if (!op->dyn) return fail(ctx, ENN_B200_INVALID_PARAMS, "operator was prepared with constant filter and bias");
+    RuntimeConstants &dyn = *op->dyn;
+    if ((dyn.weights && !weights_dev) || (dyn.bias && !bias_dev)) return fail(ctx, ENN_B200_INVALID_PARAMS, "null runtime tensor");
+    ENN_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (dyn.weights) ENN_CUDA(ctx, cudaMemcpyAsync(dyn.w_host.data(), weights_dev, dyn.w_host.size(), cudaMemcpyDeviceToHost, ctx->stream));
+    if (dyn.bias)
+        ENN_CUDA(ctx, cudaMemcpyAsync(dyn.b_host.data(), bias_dev, dyn.b_host.size() * sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    // Also orders the swap below after every launch of this operator that is still in flight on the stream.
+    ENN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    enn_b200_op *fresh = nullptr;
+    const int32_t st = conv_like_prepare_const(ctx, &dyn.desc, dyn.w_host.data(), dyn.b_host.data(),
+                                               dyn.desc.per_channel ? dyn.scales.data() : nullptr, dyn.prepare_kind, &fresh);
+    if (st != ENN_B200_SUCCESS) return st;
+    fresh->kind = op->kind;                // FullyConnected keeps its kind
+    fresh->dyn = std::move(op->dyn);
+    fresh->dyn->bound = true;
+    std::swap(*op, *fresh);
+    enn_b200_op_release(fresh);            // the previous plan and its device constants
     return ENN_B200_SUCCESS;
 }
 

@@ -2398,5 +2398,9 @@ extern "C" int32_t enn_b200_op_execute_noalloc(enn_b200_op *op, const void *in_d
         op->ctx->last_error = "null device pointer";
         return ENN_B200_INVALID_PARAMS;
     }
+    if (op->dyn && !op->dyn->bound) {
+        op->ctx->last_error = "filter / bias are runtime tensors: call enn_b200_op_rebind_constants first";
+        return ENN_B200_FAILURE;
+    }
     return enn_b200::tc_execute_static(op, in_dev, out_dev);
 }

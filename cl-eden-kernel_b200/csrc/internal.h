@@ -5,6 +5,7 @@
 
 #include <cstring>
 #include <map>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -85,6 +86,16 @@ struct PoolGeom {
 
 }  // namespace enn_b200
 
+// Operators whose filter and / or bias are runtime tensors: what prepare needs again at every rebind.
+struct RuntimeConstants {
+    bool weights = false, bias = false, bound = false;
+    enn_b200_conv_desc desc{};         // flags cleared
+    int prepare_kind = 0;              // OP_CONV / OP_DEPTHWISE / OP_DECONV handed to the prepare routine
+    std::vector<float> scales;
+    std::vector<uint8_t> w_host;       // caller's layout
+    std::vector<int32_t> b_host;
+};
+
 struct enn_b200_op {
     enn_b200_context *ctx = nullptr;
     int kind = 0;
@@ -103,6 +114,7 @@ struct enn_b200_op {
     void *dw_ring = nullptr;           // depthwise row-ring plan (depthwise.cu), owned
     void *tc = nullptr;                // tensor-core plan (gemm_tc.cu), owned
     void *graph_state = nullptr;       // state of Mean / Concat / Softmax / Resize (graph_ops.cu), owned
+    std::unique_ptr<RuntimeConstants> dyn;   // set when the descriptor said weights_as_input / bias_as_input
 };
 
 namespace enn_b200 {

@@ -96,6 +96,7 @@ int32_t enn_b200_oplist_add_tensor(enn_b200_oplist *l, int64_t bytes, int32_t *t
 int32_t enn_b200_oplist_add_op(enn_b200_oplist *l, enn_b200_op *op, const int32_t *in_ids, int32_t n_in, int32_t out_id) {
     if (!l || !op || !in_ids || n_in < 1 || n_in > ENN_B200_CONCAT_MAX_INPUTS) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: bad argument");
     if (l->finalized) return lfail(l, ENN_B200_FAILURE, "oplist already finalized");
+    if (op->dyn) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: operators with runtime filter / bias run outside operator lists");
     const int nt = static_cast<int>(l->tensors.size());
     if (out_id < 0 || out_id >= nt) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_add_op: bad output tensor id");
     for (int i = 0; i < n_in; ++i)

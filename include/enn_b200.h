@@ -81,6 +81,8 @@ typedef struct enn_b200_conv_desc {
     float bias_scale;                    /* must equal in_scale*w_scale (KernelUtil.cpp:14-16) or multiplier is 0 */
     float out_scale;  int32_t out_zp;
     int32_t out_h, out_w;           /* 0 = derive; deconvolution may pass explicit output size */
+    int32_t weights_as_input;       /* 1: the filter is a runtime tensor (CLConvolution.cpp:75 !weight->is_const()) */
+    int32_t bias_as_input;          /* 1: the bias is a runtime tensor (CLConvolution.cpp:76, :496-501) */
 } enn_b200_conv_desc;
 
 /* FullyConnected: out[m][n] = requant(bias[n] + sum_k (a[m][k]-in_zp)(w[n][k]-w_zp)), the integer
@@ -92,6 +94,8 @@ typedef struct enn_b200_fc_desc {
     float w_scale;    int32_t w_zp;
     float bias_scale;
     float out_scale;  int32_t out_zp;
+    int32_t weights_as_input;       /* CLFullyConnected.cpp:36 */
+    int32_t bias_as_input;
 } enn_b200_fc_desc;
 
 /* Quantized elementwise add (CLAddQuantized.cpp:70-165) and average pool (CLAveragepool.cpp:175-224). */
@@ -179,6 +183,8 @@ int32_t enn_b200_free(enn_b200_context *ctx, void *dev_ptr);
 int32_t enn_b200_upload(enn_b200_context *ctx, void *dev_dst, const void *host_src, size_t bytes);
 /* Copies device->host on the stream and blocks until done, like the blocking readData in set_output_data. */
 int32_t enn_b200_download(enn_b200_context *ctx, void *host_dst, const void *dev_src, size_t bytes);
+/* Device->device on the stream (CLRuntime::copyBuffer, as used by CLConvolution.cpp:151 for the bias). */
+int32_t enn_b200_copy_device(enn_b200_context *ctx, void *dev_dst, const void *dev_src, size_t bytes);
 int32_t enn_b200_stream_sync(enn_b200_context *ctx);            /* CLComputeLibrary::synchronize */
 int32_t enn_b200_host_alloc(size_t bytes, void **host_ptr);      /* pinned host staging */
 int32_t enn_b200_host_free(void *host_ptr);
@@ -239,6 +245,15 @@ int32_t enn_b200_op_execute(enn_b200_op *op, const void *in_dev, void *out_dev);
 int32_t enn_b200_op_execute2(enn_b200_op *op, const void *in0_dev, const void *in1_dev, void *out_dev);
 /* n-input form (concatenation; also accepts the one- and two-input operators). */
 int32_t enn_b200_op_execute_n(enn_b200_op *op, const void *const *ins_dev, int32_t n_in, void *out_dev);
+/* Operators prepared with weights_as_input / bias_as_input take those tensors at run time.  The reference re-runs
+ * its weight conversion and bias copy inside every execute() of such an operator
+ * (CLGEMMConvolutionQuantized.cpp:142-160, CLConvolution.cpp:496-501); here the caller states when the tensors have
+ * changed: rebind reads the flagged tensor(s) from device memory in the layout the descriptor names (the other one,
+ * if constant, is the copy kept from prepare), re-derives every packed constant of the operator in place and returns
+ * when they are on the device.  execute() of such an operator fails with FAILURE until the first rebind.  A pointer
+ * whose tensor is not flagged is ignored (may be NULL).  Such operators cannot be added to an operator list, whose
+ * captured launch sequence holds the constants' addresses. */
+int32_t enn_b200_op_rebind_constants(enn_b200_op *op, const void *weights_dev, const int32_t *bias_dev);
 /* No counterpart in the reference.  Runs a prepared Conv2D / Deconvolution whose input is gathered into a scratch
  * matrix without allocating anything: the matrix goes into a 32 MiB device array that is part of the library image.
  * For callers that may not call cudaMalloc at run time.  Limits: the operator must be on the tensor-core path and

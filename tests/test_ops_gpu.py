@@ -594,6 +594,75 @@ def test_options_and_limits(enn, ctx):
         c2.close()
 
 
+def _rebind_check(enn, orc, ctx, prepare, oracle, d, x, w, b, sc, dyn_w, dyn_b, rounds=2):
+    """Operators whose filter / bias are runtime tensors: every rebind takes the tensors' current device contents."""
+    d.weights_as_input, d.bias_as_input = int(dyn_w), int(dyn_b)
+    op = prepare(ctx, d, None if dyn_w else w, None if dyn_b else b, sc)
+    wd, bd = ctx.to_device(w), ctx.to_device(b)
+    xd = ctx.to_device(x)
+    od = ctx.malloc(op.info.out_bytes)
+    try:
+        with pytest.raises(enn.EnnError) as e:
+            op.execute(xd, od)                      # nothing bound yet
+        assert e.value.status == enn.FAILURE
+        rng = np.random.default_rng(11)
+        for r in range(rounds):
+            if r:                                   # new contents in the same device buffers
+                if dyn_w:
+                    w = rng.integers(np.iinfo(w.dtype).min, int(np.iinfo(w.dtype).max) + 1, w.shape, dtype=np.int64).astype(w.dtype)
+                    ctx.upload(wd, w)
+                if dyn_b:
+                    b = (b + rng.integers(-300, 300, b.shape)).astype(np.int32)
+                    ctx.upload(bd, b)
+            op.rebind_constants(wd if dyn_w else None, bd if dyn_b else None)
+            op.execute(xd, od)
+            ctx.sync()
+            y = ctx.download(od, (op.info.out_bytes,), np.uint8)
+            d.weights_as_input = d.bias_as_input = 0
+            y_ref = oracle(d, x, w, b, sc)
+            assert np.array_equal(y, y_ref.view(np.uint8).reshape(-1)), f"round {r}"
+    finally:
+        for p_ in (wd, bd, xd, od):
+            ctx.free(p_)
+        op.release()
+
+
+@pytest.mark.parametrize("dyn_w,dyn_b", [(True, True), (True, False), (False, True)])
+def test_runtime_filter_and_bias_conv(enn, orc, ctx, dyn_w, dyn_b):
+    # CLConvolution.cpp:75-76, CLGEMMConvolutionQuantized.cpp:142-160: filter / bias that are not constant tensors
+    d, x, w, b, sc = cases.conv_case(seed=_seed("dynconv"), n=2, h=20, w=20, cin=32, cout=48, per_channel=False)
+    _rebind_check(enn, orc, ctx, enn.conv2d, orc.conv2d, d, x, w, b, sc, dyn_w, dyn_b)
+
+
+def test_runtime_filter_depthwise_fc_deconv(enn, orc, ctx):
+    d, x, w, b, sc = cases.depthwise_case(seed=_seed("dyndw"), n=1, h=24, w=24, c=32, per_channel=True)
+    _rebind_check(enn, orc, ctx, enn.depthwise, orc.depthwise, d, x, w, b, sc, True, True)
+    d, x, w, b, sc = cases.fc_case(seed=_seed("dynfc"), m=8, k=256, n=64, per_channel=False, w_zp=119)
+    _rebind_check(enn, orc, ctx, enn.fully_connected, orc.fully_connected, d, x, w, b, sc, True, False)
+    d, x, w, b, sc = cases.deconv_case(seed=_seed("dyndc"), n=1, h=8, w=8, cin=32, cout=16)
+    _rebind_check(enn, orc, ctx, enn.deconv, orc.deconv, d, x, w, b, sc, True, True)
+
+
+def test_runtime_constants_limits(enn, ctx):
+    d, x, w, b, sc = cases.conv_case(seed=3, h=8, w=8, cin=8, cout=8)
+    op = enn.conv2d(ctx, d, w, b, sc)
+    with pytest.raises(enn.EnnError):
+        op.rebind_constants(None, None)             # prepared with constant tensors
+    op.release()
+    d.weights_as_input = 1
+    with pytest.raises(enn.EnnError):
+        enn.conv2d(ctx, d, w, None, sc)             # the bias is still a constant and must be given
+    op = enn.conv2d(ctx, d, None, b, sc)
+    with pytest.raises(enn.EnnError):
+        op.rebind_constants(None, None)             # the flagged tensor is missing
+    ol = enn.OpList(ctx)
+    t0, t1 = ol.tensor(x.nbytes), ol.tensor(op.info.out_bytes)
+    with pytest.raises(enn.EnnError):
+        ol.add(op, [t0], t1)                        # a captured launch sequence would hold stale constants
+    ol.destroy()
+    op.release()
+
+
 def test_error_paths(enn, ctx):
     d, x, w, b, sc = cases.conv_case(h=4, w=4, cin=4, cout=4)
     d.cin = 0
@@ -752,8 +821,8 @@ def test_mobilenet_layers_individually(enn, orc, ctx):
 
 
 def test_cpp_adapter_interface(enn):
-    """Builds and runs tests/adapter_test.cpp: the reference KAT and two seeded ops through the C++ classes that
-    mirror CLConvolution / CLDepthwiseConvolution (initialize / execute / release on ITensor inputs)."""
+    """Builds and runs tests/adapter_test.cpp: the reference KAT and seeded operators through the C++ classes that
+    mirror the CL* operators (initialize / execute / release on ITensor inputs)."""
     import subprocess
     root = os.path.dirname(HERE)
     pkg = os.path.join(root, "cl-eden-kernel_b200")
@@ -765,6 +834,12 @@ def test_cpp_adapter_interface(enn):
                     "-Wl,-rpath," + pkg, "-Wl,-rpath," + os.path.join(root, "oracle"), "-fopenmp"], check=True, capture_output=True)
     r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "adapter test: OK" in r.stdout, r.stdout + r.stderr
+    # The same program built against the reference's own ITensor / Common / parameter headers (tests/test_adapter_cpu.py
+    # builds it where the reference tree is mounted); it is run when it is there.
+    ref_exe = os.path.join(HERE, "adapter_test_refhdr.bin")
+    if os.path.exists(ref_exe):
+        r = subprocess.run([ref_exe], capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0 and "adapter test: OK" in r.stdout, r.stdout + r.stderr
 
 
 @pytest.mark.parametrize("name", list(__import__("ref_cases").CASES))

@@ -182,8 +182,8 @@ def test_abi_exports_every_declared_symbol(enn):
 
 
 def test_struct_sizes_match_header(enn):
-    assert C.sizeof(enn.ConvDesc) == 30 * 4
-    assert C.sizeof(enn.FcDesc) == 14 * 4
+    assert C.sizeof(enn.ConvDesc) == 32 * 4
+    assert C.sizeof(enn.FcDesc) == 16 * 4
     assert C.sizeof(enn.AddDesc) == 8 + 8 * 4
     assert C.sizeof(enn.PoolDesc) == 16 * 4
 
