@@ -56,11 +56,16 @@ constexpr int kMaxBN = 256;         // UMMA N limit
 // Epilogue warps: 3 per TMEM lane quarter, splitting the 16-column chunks.  The epilogue is bound by dependent integer
 // latencies, not by warp count: 12 warps with 128 registers (room for the compiler to interleave the 8 outputs of a half
 // chunk) run the MobileNetV2 graph 6 % faster than 24 warps capped at 72 registers; 8 and 16 warps are 1 % behind.
-constexpr int kEpiWarps = 12;
+constexpr int kEpiWarps = 8;
 constexpr int kColGroups = kEpiWarps / 4;
 constexpr int kChunksPerWarp = (kMaxBN / 16 + kColGroups - 1) / kColGroups;   // chunks one warp can own
-constexpr int kThreads = 64 + 32 * kEpiWarps + 32;   // A producer, MMA issuer, epilogue warps, B producer
-constexpr int kThreadsOneProducer = kThreads - 32;    // small problems: warp 0 loads both operands
+// Warp 0 loads the A tiles, warp 1 issues the MMAs, warps 2 .. kEpiWarps + 1 are the epilogue (warp & 3 is the TMEM lane
+// quarter a warp may read); long-K GEMMs are launched with one more warp that loads the B tiles.
+// 128 registers per thread is the ceiling for this shape: a scheduler with four resident warps has 16384 registers.
+// (Handing registers from the producer / MMA warps to the epilogue warps with setmaxnreg was measured: that code needs
+// over 100 registers itself, and with 80 / 144 the 1x1 layers ran 40 % slower.)
+constexpr int kThreadsOneProducer = 64 + 32 * kEpiWarps;
+constexpr int kThreads = kThreadsOneProducer + 32;
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 struct ColParam {   // per output column, 16 bytes
@@ -105,6 +110,8 @@ struct TcParams {
     int32_t *err;           // host-mapped error word
     long long *dbg;         // optional per-CTA cycle counters [grid][8] (null in normal use)
     int32_t dbg_mode;       // development switches (0 in normal use)
+    int32_t sat_plain;      // kModeReluHi whose clamp is [0, 255] on unsigned bytes: run the kModeReluSat kernel
+    int32_t no_wide_store;  // tuning: keep 16-byte stores
     int32_t epi_g;          // M tiles of a work unit the epilogue requantises together per column (1, 2 or 4)
     int32_t test_starve;    // self-test of the bounded waits: no operand copy is issued and the waits give up early
 };
@@ -282,6 +289,13 @@ __device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
                  : "r"(taddr)
                  : "memory");
 }
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr)
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_ld_x1(uint32_t taddr, uint32_t &r) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
 }
@@ -347,27 +361,52 @@ __device__ __forceinline__ void tile_coords(const TcParams &p, int tile, int &tg
 // (shifts = e - 1 for kModeReluHi, (31 - ls) | e << 8 for kModeReluTwo).
 constexpr size_t kWidePackWeightBytes = 100 * 1024;    // resident block-diagonal weights of a wide-row pixel packing
 constexpr int kModeNudge = 0, kModeGeneral = 1, kModeReluHi = 2, kModeReluTwo = 3;
+// kModeReluHi for outputs whose clamp is the whole unsigned byte (lower clamp 0, upper clamp 255, unsigned bytes): the
+// saturating byte pack is the clamp, so the min / max and the add of the lower clamp to the packed word are left out.
+// A kernel template value only: the plan and the ColParam contents are those of kModeReluHi.
+constexpr int kModeReluSat = 4;
 
-// Requantise one accumulator (bias not yet added) to (value - act_min) in [0, act_max - act_min].
+// The constants of one column in registers.  The ReLU modes read {C, (M0, shifts)} as two 64-bit words, so that the
+// 64-bit addend arrives as a register pair and need not be assembled from two 32-bit registers.
+struct ColRegs {
+    int4 v;
+    int64_t cc;
+};
+// `p` points into shared memory (derived from the kernel's shared array, so the compiler emits shared loads with
+// the constant part of the address as the instruction's immediate offset).
+template <int MODE>
+__device__ __forceinline__ void ld_col_shared(const uint8_t *p, ColRegs &c) {
+    __builtin_assume(__isShared(p));
+    if (MODE >= kModeReluHi) {
+        const longlong2 v = *reinterpret_cast<const longlong2 *>(p);
+        c.cc = v.x;
+        asm("mov.b64 {%0, %1}, %2;" : "=r"(c.v.z), "=r"(c.v.w) : "l"(v.y));
+    } else {
+        c.v = *reinterpret_cast<const int4 *>(p);
+    }
+}
+
+// Requantise one accumulator (bias not yet added) to (value - act_min) in [0, act_max - act_min]; kModeReluSat leaves
+// the clamp to the caller's saturating pack.
 // Fast form (esh = right shift e >= 1): stage 1 is one 32x32->64 multiply-add and a funnel shift, stage 2 is
 // (x + addend - [x < 0]) >> e with addend = 2^(e-1) + ((out_zp - act_min) << e), i.e. RoundingDivideByPOT
 // (ties away from zero) with the zero point and the lower clamp folded in.
 template <int MODE>
-__device__ __forceinline__ int32_t tc_requant(int32_t acc, const int4 &c, int32_t hi_clamp, int32_t out_zp, int32_t act_min,
+__device__ __forceinline__ int32_t tc_requant(int32_t acc, const ColRegs &cr, int32_t hi_clamp, int32_t out_zp, int32_t act_min,
                                               int32_t act_max) {
-    if (MODE == kModeReluHi || MODE == kModeReluTwo) {
-        int64_t cc;
-        asm("mov.b64 %0, {%1, %2};" : "=l"(cc) : "r"(c.x), "r"(c.y));
-        const int64_t q = static_cast<int64_t>(acc) * c.z + cc;
+    const int4 &c = cr.v;
+    if (MODE >= kModeReluHi) {
+        const int64_t q = static_cast<int64_t>(acc) * c.z + cr.cc;
         int32_t lo, hi;
         asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(q));
         int32_t v;
-        if (MODE == kModeReluHi) {
-            v = hi >> c.w;
-        } else {
+        if (MODE == kModeReluTwo) {
             const int32_t xa = static_cast<int32_t>(__funnelshift_r(static_cast<uint32_t>(lo), static_cast<uint32_t>(hi), static_cast<uint32_t>(c.w)));
             v = xa >> (c.w >> 8);
+        } else {
+            v = hi >> c.w;
         }
+        if (MODE == kModeReluSat) return v;
         return __vimin_s32_relu(v, hi_clamp);
     }
     acc += c.w;
@@ -376,6 +415,16 @@ __device__ __forceinline__ int32_t tc_requant(int32_t acc, const int4 &c, int32_
     const int32_t x = static_cast<int32_t>(p >> 31);
     const int32_t v = (x + c.y - static_cast<int32_t>(static_cast<uint32_t>(x) >> 31)) >> c.z;
     return __vimin_s32_relu(v, hi_clamp);
+}
+// The same from the four 32-bit words of a ColParam.
+template <int MODE>
+__device__ __forceinline__ int32_t tc_requant(int32_t acc, const int4 &c, int32_t hi_clamp, int32_t out_zp, int32_t act_min,
+                                              int32_t act_max) {
+    ColRegs cr;
+    cr.v = c;
+    cr.cc = 0;
+    if (MODE >= kModeReluHi) asm("mov.b64 %0, {%1, %2};" : "=l"(cr.cc) : "r"(c.x), "r"(c.y));
+    return tc_requant<MODE>(acc, cr, hi_clamp, out_zp, act_min, act_max);
 }
 
 // The k loop of one accumulator tile for the common big-GEMM shape (four K slices per k-block, one k-block per stage),
@@ -442,6 +491,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint8_t *b_resident = smem + static_cast<size_t>(p.stages) * stage_bytes;
     int4 *s_cols = reinterpret_cast<int4 *>(b_resident + (bres ? static_cast<size_t>(p.k_blocks) * b_stride : 0));
     const uint32_t s_cols_u32 = smem_u32(s_cols);
+    // The same place as a pointer that is visibly derived from the shared array (for loads written in C++).
+    const uint8_t *s_cols_sp = smem_raw + (s_cols_u32 - smem_u32(smem_raw));
     uint64_t *bars = reinterpret_cast<uint64_t *>(s_cols + kEpiWarps * kChunksPerWarp * 16);
     // bars: full[stages], empty[stages], tmem_full[2], tmem_empty[2]
     const int nst = p.stages;
@@ -804,8 +855,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int patch_x = p.taps > 0 ? row_in_tile - patch_y * p.conv_wt : 0;
         const int cps_mod = (p.bn_data >> 4) % kColGroups;
         // Several M tiles of a unit requantised together (shared column constants): flat row-major outputs with aligned rows only.
-        const int epi_g = (!TWO && p.epi_g > 1 && st_fast && p.taps == 0 && p.qh == 1 && ENN_DBG_MODE(p) == 0) ? p.epi_g : 1;
-        const uint32_t rot_step = static_cast<uint32_t>((((p.group + epi_g - 1) / epi_g) * (p.bn_data >> 4)) % kColGroups);
+        const bool flat = !TWO && st_fast && p.taps == 0 && p.qh == 1 && ENN_DBG_MODE(p) == 0;
+        // 32-byte stores: rows and pairs of chunks start on 32-byte boundaries, the constants of all columns are shared
+        const bool wide_ok = flat && (st_bits & 31) == 0 && (p.bn_data & 31) == 0 && cols_shared && !p.no_wide_store;
+        uint32_t wrot = 0;
+        const int epi_g = flat && p.epi_g > 1 ? p.epi_g : 0;      // 0: the one-tile loop below
+        const uint32_t rot_step = static_cast<uint32_t>((((p.group + max(epi_g, 1) - 1) / max(epi_g, 1)) * (p.bn_data >> 4)) % kColGroups);
         uint32_t it = 0;
         bool ok = true;
         int loaded_tn = -1;
@@ -855,64 +910,99 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint8_t *out_tile = p.out + p.out_base + n_base;
             // G M tiles at a time: the 16 bytes of constants a column needs are loaded from shared memory once and serve G
             // outputs (those loads are what saturates first in the one-tile form: two LSU wavefronts per output and warp).
+            constexpr bool kPlainPack = MODE == kModeReluSat;      // packed bytes are final: no lower clamp to add, no sign flip
             auto multi_tiles = [&](auto gtag) {
                 constexpr int G = decltype(gtag)::value;
-                for (int j0 = 0; j0 < nsub; j0 += G) {
-                    if (first < cps) {
-                        const int gn = min(G, nsub - j0);
+                for (int j0 = 0; j0 < nsub; j0 += G, ++wrot) {
+                    const int gn = min(G, nsub - j0);
+                    const int m0 = (tg * p.group + j0) * kBM;
+                    // Decided alike by every epilogue warp: all G tiles lie inside the matrix and every chunk is 16 real columns
+                    // (no conditions in the loop); then, where rows and chunk pairs start on 32-byte boundaries, a thread's two
+                    // chunks leave as one 32-byte store (a whole sector, half as many requests to the L2 as 16-byte stores).
+                    const bool full = gn == G && m0 + G * kBM <= p.M && n_cols == (cps << 4);
+                    const bool wide = full && wide_ok;
+                    int wfirst = cgrp + static_cast<int>(wrot % kColGroups);      // 32-column chunk wc belongs to group (wc - wrot) mod kColGroups
+                    if (wfirst >= kColGroups) wfirst -= kColGroups;
+                    if (wide ? wfirst < (cps >> 1) : first < cps) {
                         uint8_t *orow[G];
                         bool live[G];
                         int32_t asum_term[G];
+                        uint32_t t_tile[G];
 #pragma unroll
                         for (int i = 0; i < G; ++i) {
-                            const int m = (tg * p.group + j0 + i) * kBM + row_in_tile;
+                            const int m = m0 + i * kBM + row_in_tile;
                             live[i] = i < gn && m < p.M;
                             orow[i] = const_cast<uint8_t *>(out_tile) + static_cast<int64_t>(live[i] ? m : 0) * p.out_sx;
+                            // a slot the unit does not have re-reads the first one (unused)
+                            t_tile[i] = t_row + (j0 + i < p.group ? j0 + i : j0) * p.bn_rows;
                             asum_term[i] = 0;
                             if (ASUM) {
                                 uint32_t rs;
-                                tmem_ld_x1(t_row + (j0 + i < p.group ? j0 + i : j0) * p.bn_rows + p.bn_data, rs);       // warp-collective
+                                tmem_ld_x1(t_tile[i] + p.bn_data, rs);       // warp-collective
                                 tmem_ld_wait();
                                 asum_term[i] = p.zw_eff * static_cast<int32_t>(rs);
                             }
                         }
-                        for (int c0 = first << 4; c0 < (cps << 4); c0 += kColGroups * 16, lc_private += 256) {
-                            const uint32_t lc = cols_shared ? lc_shared + c0 * 16 : lc_private;
-                            uint32_t w[G][4];
+                        // One chunk loop.  STORE 0: 16-byte global stores under the per-row and per-chunk conditions; 1: stores
+                        // without conditions.  CW: 16-column chunks per step (2 with STORE 1 only).
+                        auto chunks = [&](auto storetag, auto widthtag) {
+                            constexpr int STORE = decltype(storetag)::value;
+                            constexpr int CW = decltype(widthtag)::value;
+                            for (int c0 = CW == 2 ? wfirst << 5 : first << 4; c0 < (cps << 4); c0 += kColGroups * 16 * CW) {
+                                const uint32_t lc = (CW == 2 || cols_shared) ? lc_shared + c0 * 16 : lc_private;
+                                const uint8_t *lcp = s_cols_sp + (lc - s_cols_u32);
+                                if (CW == 1) lc_private += 256;
+                                uint32_t w[G][4 * CW];
+                                // Accumulators: one 16-column load per tile while the registers allow it (G <= 2), else 8 columns.
+                                constexpr int LW = G <= 2 ? 16 : 8;
 #pragma unroll
-                            for (int half = 0; half < 2; ++half) {
-                                uint32_t r[G][8];
+                                for (int part = 0; part < 16 * CW / LW; ++part) {
+                                    uint32_t r[G][LW];
 #pragma unroll
-                                for (int i = 0; i < G; ++i)      // warp-collective; a slot the unit does not have re-reads the first one (unused)
-                                    tmem_ld_x8(t_row + (j0 + i < p.group ? j0 + i : j0) * p.bn_rows + c0 + 8 * half, r[i]);
-                                tmem_ld_wait();
+                                    for (int i = 0; i < G; ++i) {      // warp-collective
+                                        if constexpr (LW == 16) tmem_ld_x16(t_tile[i] + c0 + 16 * part, r[i]);
+                                        else tmem_ld_x8(t_tile[i] + c0 + 8 * part, r[i]);
+                                    }
+                                    tmem_ld_wait();
 #pragma unroll
-                                for (int jj = 0; jj < 2; ++jj) {
-                                    int32_t y[G][4];
+                                    for (int jj = 0; jj < LW / 4; ++jj) {
+                                        int32_t y[G][4];
 #pragma unroll
-                                    for (int b = 0; b < 4; ++b) {
-                                        int4 cv;
-                                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(lc + (half * 8 + jj * 4 + b) * 16));
+                                        for (int b = 0; b < 4; ++b) {
+                                            ColRegs cv;
+                                            ld_col_shared<MODE>(lcp + (part * LW + jj * 4 + b) * 16, cv);
+#pragma unroll
+                                            for (int i = 0; i < G; ++i) {
+                                                int32_t acc = static_cast<int32_t>(r[i][jj * 4 + b]);
+                                                if (ASUM) acc -= asum_term[i];
+                                                y[i][b] = tc_requant<MODE>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
+                                            }
+                                        }
 #pragma unroll
                                         for (int i = 0; i < G; ++i) {
-                                            int32_t acc = static_cast<int32_t>(r[i][jj * 4 + b]);
-                                            if (ASUM) acc -= asum_term[i];
-                                            y[i][b] = tc_requant<MODE>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
+                                            const uint32_t hi = pack_sat_u8_tc(y[i][3], y[i][2], 0);
+                                            const uint32_t pk = pack_sat_u8_tc(y[i][1], y[i][0], hi);
+                                            w[i][part * (LW / 4) + jj] = kPlainPack ? pk : ((pk + lo_word) ^ sign_word);
                                         }
                                     }
+                                }
+                                if constexpr (CW == 2) {
 #pragma unroll
-                                    for (int i = 0; i < G; ++i) {
-                                        const uint32_t hi = pack_sat_u8_tc(y[i][3], y[i][2], 0);
-                                        w[i][half * 2 + jj] = (pack_sat_u8_tc(y[i][1], y[i][0], hi) + lo_word) ^ sign_word;
-                                    }
+                                    for (int i = 0; i < G; ++i)
+                                        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow[i] + c0), "r"(w[i][0]), "r"(w[i][1]),
+                                                     "r"(w[i][2]), "r"(w[i][3]), "r"(w[i][4]), "r"(w[i][5]), "r"(w[i][6]), "r"(w[i][7])
+                                                     : "memory");
+                                } else if (STORE == 1 || c0 < n_cols) {
+#pragma unroll
+                                    for (int i = 0; i < G; ++i)
+                                        if (STORE == 1 || live[i]) *reinterpret_cast<uint4 *>(orow[i] + c0) = make_uint4(w[i][0], w[i][1], w[i][2], w[i][3]);
                                 }
                             }
-                            if (c0 < n_cols) {
-#pragma unroll
-                                for (int i = 0; i < G; ++i)
-                                    if (live[i]) *reinterpret_cast<uint4 *>(orow[i] + c0) = make_uint4(w[i][0], w[i][1], w[i][2], w[i][3]);
-                            }
-                        }
+                        };
+                        constexpr std::integral_constant<int, 1> one{};
+                        if (wide) chunks(one, std::integral_constant<int, 2>{});
+                        else if (full) chunks(one, one);
+                        else chunks(std::integral_constant<int, 0>{}, one);
                     }
                     first -= cps_mod;
                     if (first < 0) first += kColGroups;
@@ -920,7 +1010,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             };
             if (epi_g == 4) multi_tiles(std::integral_constant<int, 4>{});
             else if (epi_g == 2) multi_tiles(std::integral_constant<int, 2>{});
-            for (int j = 0; j < nsub && epi_g == 1 && !(ENN_DBG_MODE(p) & 2); ++j) {
+            for (int j = 0; j < nsub && epi_g == 0 && !(ENN_DBG_MODE(p) & 2); ++j) {
                 if (first < cps) {
                     const int tm = TWO ? tg * 2 + static_cast<int>(rank) : tg * p.group + j;
                     const int m = tm * kBM + row_in_tile;
@@ -956,14 +1046,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             int32_t y[4];
 #pragma unroll
                             for (int b = 0; b < 4; ++b) {
-                                int4 cv;
-                                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(lc_half + (jj * 4 + b) * 16));
+                                ColRegs cv;
+                                ld_col_shared<MODE>(s_cols_sp + (lc_half - s_cols_u32) + (jj * 4 + b) * 16, cv);
                                 int32_t acc = static_cast<int32_t>(r[jj * 4 + b]);
                                 if (ASUM) acc -= asum_term;
                                 y[b] = tc_requant<MODE>(acc, cv, hi_clamp, p.out_zp, p.act_min, p.act_max);
                             }
                             const uint32_t hi = pack_sat_u8_tc(y[3], y[2], 0);
-                            (jj == 0 ? w0 : w1) = (pack_sat_u8_tc(y[1], y[0], hi) + lo_word) ^ sign_word;
+                            const uint32_t pk = pack_sat_u8_tc(y[1], y[0], hi);
+                            (jj == 0 ? w0 : w1) = kPlainPack ? pk : ((pk + lo_word) ^ sign_word);
                         }
                     };
                     if (whole_rows && n_cols == (cps << 4) && m + (kBM - 1 - row_in_tile) < p.M) {
@@ -1624,6 +1715,8 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         if ((bound_v[n] << ls) + (e >= 1 ? (1ll << (e - 1)) : 0) + 1 >= (1ll << 31)) relu_two = false;
     }
     p.mode = relu_hi && !ctx->opt("no_relu_hi") ? kModeReluHi : (relu_two ? kModeReluTwo : kModeNudge);
+    // The clamp is the whole unsigned byte: the saturating pack of the epilogue does it (kModeReluSat).
+    p.sat_plain = p.mode == kModeReluHi && !p.a_signed && p.act_min == 0 && p.act_max >= 255 && !ctx->opt("no_relu_sat");
     for (int32_t n = 0; n < N; ++n) {
         const int32_t tn = n / bn_data, r = n % bn_data;
         const int64_t folded = folded_v[n];
@@ -1705,6 +1798,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     // bound problems are better off without the extra warp.
     gm->threads = (p.kpack == 1 && p.k_blocks >= 8) ? kThreads : kThreadsOneProducer;
     p.epi_g = p.two ? 1 : (p.group >= 4 ? 4 : (p.group >= 2 ? 2 : 1));
+    p.no_wide_store = ctx->opt("no_wide_store") ? 1 : 0;
     if (ctx->has_opt("epi_g")) { const int ev = ctx->opt("epi_g"); p.epi_g = ev == 4 || ev == 2 ? (ev <= p.group ? ev : p.epi_g) : 1; }   // tuning override
     return ENN_B200_SUCCESS;
 }
@@ -1779,7 +1873,10 @@ void launch_tc_gemm_mode(const TcGemm &gm, const CUtensorMap &map_a, const TcPar
     switch (p.mode) {
         case kModeNudge: launch_tc_gemm_variant<ASUM, kModeNudge>(gm, map_a, p, stream); break;
         case kModeGeneral: launch_tc_gemm_variant<ASUM, kModeGeneral>(gm, map_a, p, stream); break;
-        case kModeReluHi: launch_tc_gemm_variant<ASUM, kModeReluHi>(gm, map_a, p, stream); break;
+        case kModeReluHi:
+            if (p.sat_plain) launch_tc_gemm_variant<ASUM, kModeReluSat>(gm, map_a, p, stream);
+            else launch_tc_gemm_variant<ASUM, kModeReluHi>(gm, map_a, p, stream);
+            break;
         default: launch_tc_gemm_variant<ASUM, kModeReluTwo>(gm, map_a, p, stream); break;
     }
 }
@@ -1970,7 +2067,7 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
             } else {
                 gm.prm.qh = 1; gm.prm.qw = static_cast<int32_t>(M64);
                 gm.prm.out_base = 0; gm.prm.out_sn = 0; gm.prm.out_sy = 0; gm.prm.out_sx = N;
-            }
+                }
         }
     } else {
         // Transposed convolution (DeconvolutionKernels.cpp:24-198) split by output parity: outputs with
@@ -2113,10 +2210,12 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         set_tc_gemm_smem_attr<false, kModeGeneral>();
         set_tc_gemm_smem_attr<false, kModeReluHi>();
         set_tc_gemm_smem_attr<false, kModeReluTwo>();
+        set_tc_gemm_smem_attr<false, kModeReluSat>();
         set_tc_gemm_smem_attr<true, kModeNudge>();
         set_tc_gemm_smem_attr<true, kModeGeneral>();
         set_tc_gemm_smem_attr<true, kModeReluHi>();
         set_tc_gemm_smem_attr<true, kModeReluTwo>();
+        set_tc_gemm_smem_attr<true, kModeReluSat>();
         attr_set = true;
     }
     op->tc = plan;

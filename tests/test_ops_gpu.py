@@ -74,6 +74,12 @@ CONV_CASES = {
     "pack_wide_1x1_c96_to_24": dict(n=2, h=48, w=50, cin=96, cout=24, k=1, per_channel=True, out_scale=0.4, act=cases.enn.ACT_NONE),
     "pack_wide_1x1_c144_to_32_u8w": dict(n=1, h=64, w=66, cin=144, cout=32, k=1, w_zp=130, out_scale=0.08, act=cases.enn.ACT_NONE),
     "pack_wide_1x1_c192_to_64_relu": dict(n=2, h=46, w=50, cin=192, cout=64, k=1, per_channel=True, out_scale=0.004, out_zp=0),
+    # several M tiles per work unit requantised together: clamp = the whole byte (the saturating pack clamps), a clamp
+    # below 255, a lower clamp above 0; M not a multiple of the unit; N = 96 (whole chunks) and N = 40
+    "relu_sat_units_n96": dict(n=8, h=32, w=33, cin=16, cout=96, k=1, per_channel=True, out_scale=0.0235, out_zp=0),
+    "relu_clamp120_units_n96": dict(n=8, h=32, w=33, cin=16, cout=96, k=1, per_channel=True, out_scale=0.05, out_zp=0),
+    "relu_zp128_units_n96": dict(n=8, h=32, w=33, cin=16, cout=96, k=1, per_channel=True, out_scale=0.0235, out_zp=128),
+    "relu_sat_units_n40": dict(n=5, h=31, w=33, cin=32, cout=40, k=1, per_channel=True, out_scale=0.0235, out_zp=0),
     "first_layer_s2": dict(n=4, h=66, w=71, cin=3, cout=32, k=3, stride=2, per_channel=True, out_scale=0.1),
     "first_layer_s1_u8w": dict(n=2, h=47, w=53, cin=3, cout=16, k=3, w_zp=121, out_scale=0.05),
     "first_layer_signed": dict(n=1, h=70, w=69, cin=3, cout=48, k=3, act_dtype=cases.enn.S8, in_zp=-7, out_zp=3, per_channel=True, out_scale=0.2),
