@@ -360,9 +360,11 @@ def kernel_of_layer(L, impl):
 class Lane:
     """One operator list with its own context (stream), buffers, CUDA graph and pinned host buffers."""
 
-    def __init__(self, enn, mn, device, layers, batch, x, out_bytes):
+    def __init__(self, enn, mn, device, layers, batch, x, out_bytes, options=()):
         self.enn = enn
         self.ctx = enn.Context(device)
+        for name, value in options:
+            self.ctx.set_option(name, value)
         self.ol, self.info = mn.make_oplist(enn, self.ctx, layers, batch)
         self.ctx.upload(self.ol.tensor_ptr(self.info["tensor_ids"]["input"]), x)
         self.host = []
@@ -406,7 +408,8 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
 
     # ---- lanes: how many operator lists share this GPU.  "auto" times 1, 2 and 3 on a few steps and keeps the best. ----
     max_lanes = args.lanes if args.lanes > 0 else 3
-    lanes = [Lane(enn, mn, local, layers, per_rank, x, out_bytes) for _ in range(max_lanes)]
+    options = [(kv.split("=")[0], int(kv.split("=")[1])) for kv in args.opt]
+    lanes = [Lane(enn, mn, local, layers, per_rank, x, out_bytes, options) for _ in range(max_lanes)]
     info = lanes[0].info
     stats = lanes[0].ol.stats()
 
@@ -577,6 +580,9 @@ def run_ours(args):
     if multi:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ctx = enn.Context(local)
+    options = [(kv.split("=")[0], int(kv.split("=")[1])) for kv in args.opt]      # planner / tuning switches (none changes a result)
+    for name, value in options:
+        ctx.set_option(name, value)
     cu = Cuda()
 
     def barrier():
@@ -801,6 +807,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--lanes", type=int, default=0, help="operator lists per GPU that take the steps in turn (0: time 1..3 and keep the best)")
+    ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE", help="library option for every context (tuning runs), e.g. no_fuse=1")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU leg (profiling runs)")
     ap.add_argument("--skip-per-op", action="store_true", help="omit the single-operator table (profiling runs)")
     args = ap.parse_args()

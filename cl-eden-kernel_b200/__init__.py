@@ -54,6 +54,7 @@ PROTOTYPES = {
     "enn_b200_op_execute_n": (C.c_int32, [_P, C.POINTER(_P), C.c_int32, _P]),
     "enn_b200_op_execute_noalloc": (C.c_int32, [_P, _P, _P]),
     "enn_b200_op_rebind_constants": (C.c_int32, [_P, _P, _P]),
+    "enn_b200_op_fuse_add": (C.c_int32, [_P, _P, C.c_int32]),
     "enn_b200_op_info": (C.c_int32, [_P, C.POINTER(OpInfo)]),
     "enn_b200_op_test_starve_next": (C.c_int32, [_P]),
     "enn_b200_op_clear_error": (C.c_int32, [_P]),
@@ -212,6 +213,13 @@ class Op:
     def rebind_constants(self, weights_dev=None, bias_dev=None):
         """Operators prepared with weights_as_input / bias_as_input: take the tensors' current device contents."""
         self.ctx.check(lib.enn_b200_op_rebind_constants(self.h, weights_dev, bias_dev))
+
+    def fuse_add(self, add_op, conv_is_second_input=False):
+        """Moves a prepared add over this convolution's output into its epilogue; the add is owned by this op afterwards.
+        Raises EnnError(INVALID_PARAMS) and leaves both untouched when the plan cannot take it."""
+        self.ctx.check(lib.enn_b200_op_fuse_add(self.h, add_op.h, int(conv_is_second_input)))
+        add_op.h = None
+        self.ctx.check(lib.enn_b200_op_info(self.h, C.byref(self.info)))
 
     def execute_n(self, in_devs, out_dev):
         arr = (C.c_void_p * len(in_devs))(*[p.value if hasattr(p, "value") else p for p in in_devs])

@@ -103,6 +103,8 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out);
 void tc_release(enn_b200_op *op);
 bool tc_available(const enn_b200_context *ctx);
 int32_t tc_test_starve_next(enn_b200_op *op);
+int32_t tc_fuse_add(enn_b200_op *op, const AddParams &add, bool conv_is_second);
+void tc_set_residual(enn_b200_op *op, const void *res);
 void tc_clear_error(enn_b200_op *op);
 }  // namespace enn_b200
 
@@ -217,7 +219,7 @@ int32_t enn_b200_context_set_option(enn_b200_context *ctx, const char *name, int
     if (!ctx || !name) return ENN_B200_INVALID_PARAMS;
     static const char *const known[] = {"no_pdl", "no_relu_mode", "no_relu_hi", "no_relu_sat", "no_wide_store", "no_first_layer", "no_implicit", "no_gemv",
                                         "no_narrow_span", "no_pack", "pack_wide", "no_bres", "no_bres_k1", "no_fan_out", "tc_bn",
-                                        "tc_pair", "tc_raster", "epi_g", "dw_legacy", "no_fuse", "dw_rows"};
+                                        "tc_pair", "tc_raster", "epi_g", "dw_legacy", "no_fuse", "fuse_all", "dw_rows"};
     bool ok = false;
     for (const char *k : known) ok = ok || std::strcmp(k, name) == 0;
     if (!ok) return fail(ctx, ENN_B200_INVALID_PARAMS, std::string("unknown option: ") + name);
@@ -625,6 +627,7 @@ int32_t enn_b200_op_execute(enn_b200_op *op, const void *in, void *out) {
     enn_b200_context *ctx = op->ctx;
     if (!in || !out) return fail(ctx, ENN_B200_INVALID_PARAMS, "null device pointer");
     if (op->dyn && !op->dyn->bound) return fail(ctx, ENN_B200_FAILURE, "filter / bias are runtime tensors: call enn_b200_op_rebind_constants first");
+    if (op->fused_add && op->impl != ENN_B200_IMPL_TCGEN05) return fail(ctx, ENN_B200_INVALID_PARAMS, "an operator with a fused add runs on the tensor-core path only");
     cudaError_t e = cudaSuccess;
     switch (op->kind) {
         case OP_CONV:
@@ -675,8 +678,12 @@ int32_t enn_b200_op_execute(enn_b200_op *op, const void *in, void *out) {
 
 int32_t enn_b200_op_execute2(enn_b200_op *op, const void *in0, const void *in1, void *out) {
     if (!op) return ENN_B200_INVALID_PARAMS;
-    if (op->kind != OP_ADD) return fail(op->ctx, ENN_B200_INVALID_PARAMS, "not a two-input op");
     if (!in0 || !in1 || !out) return fail(op->ctx, ENN_B200_INVALID_PARAMS, "null device pointer");
+    if (op->fused_add) {      // convolution + add: in0 feeds the convolution, in1 is the add's other input
+        tc_set_residual(op, in1);
+        return enn_b200_op_execute(op, in0, out);
+    }
+    if (op->kind != OP_ADD) return fail(op->ctx, ENN_B200_INVALID_PARAMS, "not a two-input op");
     cudaError_t e = launch_add(op->add, op->count, in0, in1, out, op->ctx->sm_count, op->ctx->stream);
     if (e != cudaSuccess) return cuda_fail(op->ctx, e, "add launch");
     return ENN_B200_SUCCESS;
@@ -693,7 +700,8 @@ int32_t enn_b200_op_execute_n(enn_b200_op *op, const void *const *ins, int32_t n
         if (e != cudaSuccess) return cuda_fail(op->ctx, e, "concat launch");
         return ENN_B200_SUCCESS;
     }
-    if (op->kind == OP_ADD) return n_in == 2 ? enn_b200_op_execute2(op, ins[0], ins[1], out) : fail(op->ctx, ENN_B200_INVALID_PARAMS, "add takes two inputs");
+    if (op->kind == OP_ADD || op->fused_add)
+        return n_in == 2 ? enn_b200_op_execute2(op, ins[0], ins[1], out) : fail(op->ctx, ENN_B200_INVALID_PARAMS, "this operator takes two inputs");
     return n_in == 1 ? enn_b200_op_execute(op, ins[0], out) : fail(op->ctx, ENN_B200_INVALID_PARAMS, "this operator takes one input");
 }
 
@@ -714,6 +722,22 @@ int32_t enn_b200_op_clear_error(enn_b200_op *op) {
     if (!op) return ENN_B200_INVALID_PARAMS;
     if (op->tc) tc_clear_error(op);
     if (op->dw_ring) dw_ring_clear_error(op);
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_op_fuse_add(enn_b200_op *conv, enn_b200_op *add, int32_t conv_is_second_input) {
+    if (!conv || !add || !conv->ctx) return ENN_B200_INVALID_PARAMS;
+    enn_b200_context *ctx = conv->ctx;
+    if (conv->kind != OP_CONV || add->kind != OP_ADD || add->ctx != ctx || conv->fused_add || conv->dyn || conv->impl != ENN_B200_IMPL_TCGEN05 ||
+        !conv->tc || !add->add.lut || add->count != conv->info.out_bytes)
+        return fail(ctx, ENN_B200_INVALID_PARAMS, "fuse_add: not a tensor-core convolution and an add over its output");
+    const int32_t st = tc_fuse_add(conv, add->add, conv_is_second_input != 0);
+    if (st != ENN_B200_SUCCESS) return fail(ctx, st, "fuse_add: this convolution's plan cannot take the add (mode, tiling or shared memory)");
+    conv->fused_add = add;                // owned from here on: the table lives in its allocations
+    conv->info.act_min = add->info.act_min;
+    conv->info.act_max = add->info.act_max;
+    conv->info.in_bytes += conv->info.out_bytes;
+    conv->info.algorithmic_bytes += conv->info.out_bytes;
     return ENN_B200_SUCCESS;
 }
 
@@ -747,6 +771,7 @@ int32_t enn_b200_op_release(enn_b200_op *op) {
     if (op->tc) tc_release(op);
     if (op->dw_ring) dw_ring_release(op);
     if (op->graph_state) graph_op_release(op);
+    if (op->fused_add) enn_b200_op_release(op->fused_add);
     for (void *p : op->owned) cudaFree(p);
     delete op;
     return ENN_B200_SUCCESS;

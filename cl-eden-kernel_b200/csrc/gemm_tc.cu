@@ -36,6 +36,8 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *weights_hwio_host);
 int32_t tc_execute(enn_b200_op *op, const void *in, void *out);
 void tc_release(enn_b200_op *op);
 int32_t tc_test_starve_next(enn_b200_op *op);
+int32_t tc_fuse_add(enn_b200_op *op, const AddParams &add, bool conv_is_second);
+void tc_set_residual(enn_b200_op *op, const void *res);
 void tc_clear_error(enn_b200_op *op);
 
 namespace {
@@ -112,6 +114,13 @@ struct TcParams {
     int32_t dbg_mode;       // development switches (0 in normal use)
     int32_t sat_plain;      // kModeReluHi whose clamp is [0, 255] on unsigned bytes: run the kModeReluSat kernel
     int32_t no_wide_store;  // tuning: keep 16-byte stores
+    // Fused quantized add (kernels with FADD): the add operator's parameters and stage-1 tables (2 x 256 words, staged in
+    // shared memory at add_off), the other addend (same layout as the output), and which addend the convolution's result is.
+    AddParams add;
+    int32_t add_on;
+    const uint8_t *add_res;
+    int32_t add_off;
+    int32_t add_swap;       // 1: the convolution result is the add's second input
     int32_t epi_g;          // M tiles of a work unit the epilogue requantises together per column (1, 2 or 4)
     int32_t test_starve;    // self-test of the bounded waits: no operand copy is issued and the waits give up early
 };
@@ -467,9 +476,41 @@ ENN_TILE_FN(mma_tile_d6, 6, case 0: ENN_KB(0) case 1: ENN_KB(1) case 2: ENN_KB(2
 #undef ENN_TILE_FN
 #undef ENN_KB
 
+// Fused add: the 16 requantised bytes of a chunk (four words) and the 16 bytes of the other addend at the same place go
+// through the quantized add exactly as add_kernel_vec computes it (kernels_direct.cu): stage 1 of either input from the
+// operator's tables in shared memory, stage 2 computed.
+struct FaddCtx {
+    uint32_t lut_u32;       // 2 x 256 words in shared memory: input-0 table, input-1 table
+    int32_t mo, so, out_off, act_min, act_max;
+    bool swap;
+};
+__device__ __forceinline__ uint32_t fadd_word(uint32_t y, uint32_t r, const FaddCtx &f) {
+    const uint32_t a = f.swap ? r : y, b = f.swap ? y : r;
+    uint32_t word = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t ba = (a >> (8 * k)) & 0xff, bb = (b >> (8 * k)) & 0xff;
+        int32_t x0, x1;
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(x0) : "r"(f.lut_u32 + ba * 4));
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(x1) : "r"(f.lut_u32 + 1024 + bb * 4));
+        int32_t o = enn_rdivpot(enn_srdhm(x0 + x1, f.mo), -f.so) + f.out_off;
+        o = max(f.act_min, o);
+        o = min(f.act_max, o);
+        word |= (static_cast<uint32_t>(o) & 0xff) << (8 * k);
+    }
+    return word;
+}
+__device__ __forceinline__ void fadd_chunk(uint32_t (&w)[4], const uint8_t *res, const FaddCtx &f) {
+    const uint4 r = *reinterpret_cast<const uint4 *>(res);      // plain load: the output may be written over this addend
+    w[0] = fadd_word(w[0], r.x, f);
+    w[1] = fadd_word(w[1], r.y, f);
+    w[2] = fadd_word(w[2], r.z, f);
+    w[3] = fadd_word(w[3], r.w, f);
+}
+
 // TWO: CTA-pair mode (launched as clusters of 2; plain GEMM operands only, group == 1, kpack == 1): the pair owns M
 // tiles 2t and 2t + 1 of one N tile, every B byte is read from L2 once per pair, and a stage per CTA is A plus half of B.
-template <bool ASUM, int MODE, bool TWO>
+template <bool ASUM, int MODE, bool TWO, bool FADD = false>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -528,6 +569,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const bool cols_shared = p.tiles_n * p.bn_rows <= kEpiWarps * kChunksPerWarp * 16;
     if (cols_shared)
         for (int i = threadIdx.x; i < p.tiles_n * p.bn_rows; i += blockDim.x) s_cols[i] = __ldg(reinterpret_cast<const int4 *>(p.cols) + i);
+    FaddCtx fadd{};
+    if (FADD) {     // the add operator's stage-1 tables: constants of the plan, staged ahead of the launch dependency
+        fadd.lut_u32 = smem_u32(smem) + static_cast<uint32_t>(p.add_off);
+        fadd.mo = p.add.mo; fadd.so = p.add.so; fadd.out_off = p.add.out_off; fadd.act_min = p.add.act_min; fadd.act_max = p.add.act_max;
+        fadd.swap = p.add_swap != 0;
+        for (int i = threadIdx.x; i < 512; i += blockDim.x)
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(fadd.lut_u32 + i * 4), "r"(__ldg(p.add.lut + i)) : "memory");
+    }
     tc_fence_before();
     __syncthreads();
     if (TWO) cluster_sync_all();        // the peer's barriers exist before anything signals them
@@ -855,6 +904,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int patch_x = p.taps > 0 ? row_in_tile - patch_y * p.conv_wt : 0;
         const int cps_mod = (p.bn_data >> 4) % kColGroups;
         // Several M tiles of a unit requantised together (shared column constants): flat row-major outputs with aligned rows only.
+        const ptrdiff_t res_delta = FADD ? p.add_res - p.out : 0;      // other addend of a fused add: same offsets as the output
         const bool flat = !TWO && st_fast && p.taps == 0 && p.qh == 1 && ENN_DBG_MODE(p) == 0;
         // 32-byte stores: rows and pairs of chunks start on 32-byte boundaries, the constants of all columns are shared
         const bool wide_ok = flat && (st_bits & 31) == 0 && (p.bn_data & 31) == 0 && cols_shared && !p.no_wide_store;
@@ -986,6 +1036,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                         }
                                     }
                                 }
+                                if constexpr (FADD) {
+#pragma unroll
+                                    for (int i = 0; i < G; ++i)
+                                        if (STORE == 1 || (live[i] && c0 < n_cols)) {
+#pragma unroll
+                                            for (int h = 0; h < CW; ++h) {
+                                                uint32_t (&wq)[4] = *reinterpret_cast<uint32_t (*)[4]>(&w[i][4 * h]);
+                                                fadd_chunk(wq, orow[i] + c0 + 16 * h + res_delta, fadd);
+                                            }
+                                        }
+                                }
                                 if constexpr (CW == 2) {
 #pragma unroll
                                     for (int i = 0; i < G; ++i)
@@ -1070,6 +1131,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 tmem_ld_wait();
                                 half_chunk(r, lc + half * 128, w[half * 2], w[half * 2 + 1]);
                             }
+                            if constexpr (FADD) fadd_chunk(w, orow + c0 + res_delta, fadd);
                             *reinterpret_cast<uint4 *>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     } else {
@@ -1085,6 +1147,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             if (row_ok && c0 < n_cols) half_chunk(r, lc + half * 128, w[half * 2], w[half * 2 + 1]);
                         }
                         if (row_ok && c0 < n_cols) {
+                            if constexpr (FADD) fadd_chunk(w, orow + c0 + res_delta, fadd);      // fused operators have 16-byte rows (plan)
                             if (ENN_DBG_MODE(p) & 4) {
                                 // development switch: no stores (isolates the store path; only one lane keeps the values alive)
                                 if ((w[0] ^ w[1] ^ w[2] ^ w[3]) == 0x12345678u && lane == 33) orow[0] = 1;
@@ -1559,6 +1622,8 @@ struct TcPlan {
     int32_t *err_host = nullptr;       // pinned + mapped
     int32_t *err_dev = nullptr;
     bool starve_next = false;          // the next execute runs the bounded-wait self-test (tc_test_starve_next)
+    bool fused_add = false;            // convolution + quantized add (tc_fuse_add)
+    const uint8_t *residual = nullptr; // the add's other input for the next execute
 };
 
 CUtensorMapSwizzle swizzle_of(uint32_t span) {
@@ -1870,6 +1935,15 @@ void launch_first_layer(enn_b200_context *ctx, const TcGemm &gm, const void *in,
 
 template <bool ASUM>
 void launch_tc_gemm_mode(const TcGemm &gm, const CUtensorMap &map_a, const TcParams &p, cudaStream_t stream) {
+    if (p.add_on) {      // fused add: one-CTA kernels of the two-stage modes only (the plan checks)
+        if (p.mode == kModeNudge)
+            launch_pdl(tc_gemm_kernel<ASUM, kModeNudge, false, true>, dim3(static_cast<unsigned>(gm.grid)), dim3(static_cast<unsigned>(gm.threads)), gm.smem_bytes,
+                       stream, map_a, gm.map_b, p);
+        else
+            launch_pdl(tc_gemm_kernel<ASUM, kModeGeneral, false, true>, dim3(static_cast<unsigned>(gm.grid)), dim3(static_cast<unsigned>(gm.threads)), gm.smem_bytes,
+                       stream, map_a, gm.map_b, p);
+        return;
+    }
     switch (p.mode) {
         case kModeNudge: launch_tc_gemm_variant<ASUM, kModeNudge>(gm, map_a, p, stream); break;
         case kModeGeneral: launch_tc_gemm_variant<ASUM, kModeGeneral>(gm, map_a, p, stream); break;
@@ -2216,10 +2290,39 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         set_tc_gemm_smem_attr<true, kModeReluHi>();
         set_tc_gemm_smem_attr<true, kModeReluTwo>();
         set_tc_gemm_smem_attr<true, kModeReluSat>();
+        cudaFuncSetAttribute(tc_gemm_kernel<false, kModeNudge, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(tc_gemm_kernel<false, kModeGeneral, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(tc_gemm_kernel<true, kModeNudge, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(tc_gemm_kernel<true, kModeGeneral, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         attr_set = true;
     }
     op->tc = plan;
     return ENN_B200_SUCCESS;
+}
+
+// Turns a planned convolution into convolution + quantized add (`add`: the prepared add operator's parameters and tables).
+// INVALID_PARAMS when this plan cannot take it; the caller then keeps the two operators.
+int32_t tc_fuse_add(enn_b200_op *op, const AddParams &add, bool conv_is_second) {
+    TcPlan *plan = static_cast<TcPlan *>(op->tc);
+    if (!plan || plan->gemms.size() != 1 || plan->fused_add) return ENN_B200_INVALID_PARAMS;
+    TcGemm &gm = plan->gemms[0];
+    TcParams &p = gm.prm;
+    if (gm.first_layer || gm.use_gemv || p.two || (p.mode != kModeNudge && p.mode != kModeGeneral) || (p.N & 15) != 0 || (p.out_base & 15) != 0 ||
+        (p.out_sx & 15) != 0 || (p.out_sy & 15) != 0 || (p.out_sn & 15) != 0 || p.M == 0 || !add.lut || add.is_signed != p.a_signed)
+        return ENN_B200_INVALID_PARAMS;
+    if (gm.smem_bytes + 2048 > 227 * 1024) return ENN_B200_INVALID_PARAMS;
+    p.add_off = static_cast<int32_t>(gm.smem_bytes - 1024);      // behind the barriers; the last 1024 bytes are the alignment slack
+    gm.smem_bytes += 2048;
+    p.add = add;
+    p.add_on = 1;
+    p.add_swap = conv_is_second ? 1 : 0;
+    plan->fused_add = true;
+    return ENN_B200_SUCCESS;
+}
+
+// The other addend of a fused operator for the next tc_execute.
+void tc_set_residual(enn_b200_op *op, const void *res) {
+    if (TcPlan *plan = static_cast<TcPlan *>(op->tc)) plan->residual = static_cast<const uint8_t *>(res);
 }
 
 int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
@@ -2323,6 +2426,13 @@ int32_t tc_execute(enn_b200_op *op, const void *in, void *out) {
             }
         }
         p.out = static_cast<uint8_t *>(out);
+        if (plan->fused_add) {
+            if (!plan->residual || ((reinterpret_cast<uintptr_t>(plan->residual) | reinterpret_cast<uintptr_t>(out)) & 15) != 0) {
+                ctx->last_error = "fused convolution + add needs the second addend and 16-byte aligned pointers";
+                return ENN_B200_INVALID_PARAMS;
+            }
+            p.add_res = plan->residual;
+        }
         p.test_starve = starve ? 1 : 0;
 #ifdef ENN_B200_DEV
         p.dbg_mode = getenv("ENN_B200_TC_MODE") ? atoi(getenv("ENN_B200_TC_MODE")) : 0;
@@ -2405,8 +2515,8 @@ static std::mutex g_static_scratch_mutex;      // guards the table above (first 
 int32_t tc_execute_static(enn_b200_op *op, const void *in, void *out) {
     enn_b200_context *ctx = op->ctx;
     TcPlan *plan = static_cast<TcPlan *>(op->tc);
-    if (!plan || op->impl != ENN_B200_IMPL_TCGEN05) {
-        ctx->last_error = "enn_b200_op_execute_noalloc: the operator is not bound to the tensor-core path";
+    if (!plan || op->impl != ENN_B200_IMPL_TCGEN05 || plan->fused_add) {
+        ctx->last_error = "enn_b200_op_execute_noalloc: the operator is not bound to the tensor-core path (or has a fused add)";
         return ENN_B200_INVALID_PARAMS;
     }
     size_t need = 0;

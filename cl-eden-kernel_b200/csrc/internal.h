@@ -115,6 +115,7 @@ struct enn_b200_op {
     void *tc = nullptr;                // tensor-core plan (gemm_tc.cu), owned
     void *graph_state = nullptr;       // state of Mean / Concat / Softmax / Resize (graph_ops.cu), owned
     std::unique_ptr<RuntimeConstants> dyn;   // set when the descriptor said weights_as_input / bias_as_input
+    enn_b200_op *fused_add = nullptr;  // convolution + quantized add: the add operator whose table the epilogue uses (owned)
 };
 
 namespace enn_b200 {

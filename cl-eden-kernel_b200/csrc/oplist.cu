@@ -53,6 +53,7 @@ struct enn_b200_oplist {
 };
 
 namespace {
+constexpr int64_t kFuseAddMaxCount = 1 << 21;
 int32_t lfail(enn_b200_oplist *l, int32_t st, const char *msg) {
     if (l && l->ctx) l->ctx->last_error = msg;
     return st;
@@ -141,9 +142,56 @@ int32_t enn_b200_oplist_finalize(enn_b200_oplist *l) {
     if (l->finalized) return ENN_B200_SUCCESS;
     enn_b200_context *ctx = l->ctx;
     if (cudaSetDevice(ctx->device) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "cudaSetDevice failed");
-    const int n_nodes = static_cast<int>(l->nodes.size());
     for (int id : l->inputs) l->tensors[id].is_input = true;
     for (int id : l->outputs) l->tensors[id].is_output = true;
+    // Convolution -> add (the residual blocks): where the convolution's result is read by that add only and its plan can
+    // take it, the add moves into the convolution's epilogue and its node and the tensor between them disappear.
+    if (!ctx->opt("no_fuse")) {
+        std::vector<int> readers(l->tensors.size(), 0);
+        for (auto &n : l->nodes)
+            for (int t : n.ins) ++readers[t];
+        for (size_t a = 0; a < l->nodes.size(); ++a) {
+            auto &add = l->nodes[a];
+            if (add.op->kind != enn_b200::OP_ADD || add.ins.size() != 2 || add.ins[0] == add.ins[1]) continue;
+            // Large adds stay on their own: the stand-alone kernel runs them from the 64 KB pair table at HBM speed, while
+            // the epilogue computes the last stage (about 20 integer instructions per output); below about two million
+            // elements the add kernel is all launch latency and the fused form wins (measured on the MobileNetV2 graph:
+            // fusing every add costs 2 % at 256 images per list, fusing the small ones gains at 32).
+            if (add.op->count > kFuseAddMaxCount && !ctx->opt("fuse_all")) continue;
+            for (int side = 0; side < 2; ++side) {
+                const int mid = add.ins[side];
+                const auto &M = l->tensors[mid];
+                if (M.is_input || M.is_output || readers[mid] != 1) continue;
+                int prod = -1;
+                for (size_t c = 0; c < a; ++c)
+                    if (l->nodes[c].out == mid) prod = static_cast<int>(c);      // the last writer before the add
+                if (prod < 0 || l->nodes[prod].op->kind != enn_b200::OP_CONV || l->nodes[prod].ins.size() != 1) continue;
+                // The other addend must exist before the convolution runs.
+                const int other = add.ins[1 - side];
+                bool other_ready = l->tensors[other].is_input;
+                for (int c = 0; c < prod; ++c)
+                    if (l->nodes[c].out == other) other_ready = true;
+                for (size_t c = prod; c < a; ++c)
+                    if (l->nodes[c].out == other) other_ready = false;            // rewritten in between
+                if (!other_ready) continue;
+                bool touched = false;      // nothing between the two may read or write the add's output tensor
+                for (size_t c = prod; c < a && !touched; ++c) {
+                    touched = l->nodes[c].out == add.out;
+                    for (int t : l->nodes[c].ins) touched = touched || t == add.out;
+                }
+                if (touched) continue;
+                if (enn_b200_op_fuse_add(l->nodes[prod].op, add.op, side) != ENN_B200_SUCCESS) continue;
+                l->nodes[prod].ins.push_back(other);
+                l->nodes[prod].out = add.out;
+                // the convolution now runs where it did, but the other addend must stay alive until then and the add's
+                // output is written earlier: both follow from the node order, which the liveness pass below reads
+                l->nodes.erase(l->nodes.begin() + static_cast<long>(a));
+                --a;
+                break;
+            }
+        }
+    }
+    const int n_nodes = static_cast<int>(l->nodes.size());
     for (int i = 0; i < n_nodes; ++i) {
         auto &n = l->nodes[i];
         for (int t : n.ins) {

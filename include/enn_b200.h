@@ -194,7 +194,7 @@ int32_t enn_b200_last_error(enn_b200_context *ctx, char *buf, size_t buf_len);
 void *enn_b200_stream(enn_b200_context *ctx);
 /* Planner overrides for tests and tuning, read when an operator is prepared (the library reads no environment
  * variable).  Names: no_pdl, no_relu_mode, no_relu_hi, no_relu_sat, no_wide_store, no_first_layer, no_implicit, no_gemv, no_narrow_span, no_pack,
- * pack_wide, no_bres, no_bres_k1, no_fan_out, tc_bn (>= 96), tc_pair, tc_raster, epi_g, dw_legacy, dw_rows, no_fuse.
+ * pack_wide, no_bres, no_bres_k1, no_fan_out, tc_bn (>= 96), tc_pair, tc_raster, epi_g, dw_legacy, dw_rows, no_fuse, fuse_all.
  * Stands where the reference reads its build-time device switches (CLRuntime.cpp:174-213).  Unknown names are
  * rejected with INVALID_PARAMS; none of them changes a result. */
 int32_t enn_b200_context_set_option(enn_b200_context *ctx, const char *name, int32_t value);
@@ -245,6 +245,15 @@ int32_t enn_b200_op_execute(enn_b200_op *op, const void *in_dev, void *out_dev);
 int32_t enn_b200_op_execute2(enn_b200_op *op, const void *in0_dev, const void *in1_dev, void *out_dev);
 /* n-input form (concatenation; also accepts the one- and two-input operators). */
 int32_t enn_b200_op_execute_n(enn_b200_op *op, const void *const *ins_dev, int32_t n_in, void *out_dev);
+/* Fuses a quantized add into the epilogue of the convolution that produces one of its inputs (the MobileNetV2
+ * residual pattern: CONV_2D -> ADD, `CLAddQuantized.cpp:70-165` applied to every output byte before it is stored).
+ * `add` is a prepared add over exactly the convolution's output; on success the convolution owns it, takes two inputs
+ * (enn_b200_op_execute2 / _n: in0 feeds the convolution, in1 is the add's other input, same layout as the output) and
+ * writes the add's result.  INVALID_PARAMS, with both operators unchanged, when the convolution's plan cannot take it
+ * (not on the tensor-core path, ReLU-merged epilogue, output rows not multiples of 16 bytes, no shared memory left for
+ * the add's tables); the caller then runs the two operators one after the other.  Results are those of the two
+ * operators run separately, bit for bit. */
+int32_t enn_b200_op_fuse_add(enn_b200_op *conv, enn_b200_op *add, int32_t conv_is_second_input);
 /* Operators prepared with weights_as_input / bias_as_input take those tensors at run time.  The reference re-runs
  * its weight conversion and bias copy inside every execute() of such an operator
  * (CLGEMMConvolutionQuantized.cpp:142-160, CLConvolution.cpp:496-501); here the caller states when the tensors have

@@ -669,6 +669,65 @@ def test_runtime_constants_limits(enn, ctx):
     op.release()
 
 
+FUSED_ADD_CASES = {
+    # name: (conv case, add is (conv, other) or (other, conv)); shapes of the MobileNetV2 project layers and their tiling modes
+    "project_56x56_144_to_24_packed": (dict(n=64, h=56, w=56, cin=144, cout=24, k=1, per_channel=True, out_scale=0.3, act=0, out_zp=128), False),
+    "project_14x14_384_to_64": (dict(n=6, h=14, w=14, cin=384, cout=64, k=1, per_channel=True, out_scale=0.3, act=0, out_zp=121), True),
+    "project_7x7_960_to_160": (dict(n=9, h=7, w=7, cin=960, cout=160, k=1, per_channel=True, out_scale=0.25, act=0, out_zp=130), False),
+    "u8_weights_partial_tile": (dict(n=1, h=19, w=21, cin=64, cout=48, k=1, w_zp=131, out_scale=0.06, act=0, out_zp=119), False),
+    "implicit_3x3": (dict(n=2, h=12, w=13, cin=32, cout=32, k=3, per_channel=True, out_scale=0.5, act=0, out_zp=125), True),
+}
+
+
+@pytest.mark.parametrize("name", list(FUSED_ADD_CASES))
+def test_conv_with_fused_add(enn, orc, ctx, name):
+    """CONV_2D -> ADD with the add in the convolution's epilogue equals the two operators run one after the other."""
+    kw, conv_second = FUSED_ADD_CASES[name]
+    d, x, w, b, sc = cases.conv_case(seed=_seed("fadd_" + name), **kw)
+    y_conv = orc.conv2d(d, x, w, b, sc)
+    rng = np.random.default_rng(_seed("fadd_res_" + name))
+    res = rng.integers(0, 256, y_conv.shape, dtype=np.int64).astype(np.uint8)
+    ad = enn.AddDesc(count=y_conv.size, activation=0, act_dtype=enn.U8, in0_scale=0.031, in0_zp=120, in1_scale=0.047, in1_zp=131,
+                     out_scale=0.06, out_zp=126)
+    y_ref = orc.add(ad, res, y_conv) if conv_second else orc.add(ad, y_conv, res)
+    op = enn.conv2d(ctx, d, w, b, sc)
+    addop = enn.add(ctx, ad)
+    op.fuse_add(addop, conv_second)
+    xd, rd = ctx.to_device(x), ctx.to_device(res)
+    od = ctx.malloc(y_ref.size)
+    try:
+        with pytest.raises(enn.EnnError):
+            op.execute(xd, od)                      # the second addend is missing
+        op.execute2(xd, rd, od)
+        ctx.sync()
+        y = ctx.download(od, y_ref.shape, np.uint8)
+        assert np.array_equal(y, y_ref), f"{(y != y_ref).sum()} of {y.size} differ"
+        op.execute2(xd, rd, rd)                     # in place over the other addend (what an operator list may do)
+        ctx.sync()
+        assert np.array_equal(ctx.download(rd, y_ref.shape, np.uint8), y_ref)
+    finally:
+        for p_ in (xd, rd, od):
+            ctx.free(p_)
+        op.release()
+
+
+def test_fused_add_refusals(enn, ctx):
+    d, x, w, b, sc = cases.conv_case(seed=5, n=2, h=14, w=14, cin=32, cout=48, k=1, per_channel=True, out_scale=0.0235, out_zp=0)   # ReLU6: merged epilogue
+    op = enn.conv2d(ctx, d, w, b, sc)
+    ad = enn.AddDesc(count=op.info.out_bytes, activation=0, act_dtype=enn.U8, in0_scale=0.03, in0_zp=0, in1_scale=0.04, in1_zp=3, out_scale=0.06, out_zp=1)
+    addop = enn.add(ctx, ad)
+    with pytest.raises(enn.EnnError):
+        op.fuse_add(addop)
+    y = op.run(x)                                   # both operators are still usable
+    assert y.size == op.info.out_bytes
+    ad.count += 16
+    other = enn.add(ctx, ad)
+    with pytest.raises(enn.EnnError):
+        op.fuse_add(other)                          # not an add over this convolution's output
+    for o in (op, addop, other):
+        o.release()
+
+
 def test_error_paths(enn, ctx):
     d, x, w, b, sc = cases.conv_case(h=4, w=4, cin=4, cout=4)
     d.cin = 0
