@@ -70,6 +70,14 @@ PROTOTYPES = {
     "enn_b200_oplist_wait": (C.c_int32, [_P]),
     "enn_b200_oplist_tensor_ptr": (C.c_int32, [_P, C.c_int32, C.POINTER(_P)]),
     "enn_b200_oplist_last_output_ptr": (C.c_int32, [_P, C.c_int32, C.POINTER(_P)]),
+    "enn_b200_oplist_node_count": (C.c_int32, [_P, C.POINTER(C.c_int32)]),
+    "enn_b200_oplist_node_info": (C.c_int32, [_P, C.c_int32, C.POINTER(OpInfo), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "enn_b200_oplist_profile": (C.c_int32, [_P, C.c_int32, C.POINTER(C.c_float), C.c_int32]),
+    "enn_b200_timer_create": (C.c_int32, [_P, C.POINTER(_P)]),
+    "enn_b200_timer_start": (C.c_int32, [_P]),
+    "enn_b200_timer_stop": (C.c_int32, [_P]),
+    "enn_b200_timer_elapsed_us": (C.c_int32, [_P, C.POINTER(C.c_float)]),
+    "enn_b200_timer_destroy": (C.c_int32, [_P]),
     "enn_b200_oplist_stats": (C.c_int32, [_P, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "enn_b200_oplist_destroy": (C.c_int32, [_P]),
     "enn_b200_group_create": (C.c_int32, [C.POINTER(_P), C.c_int32, C.POINTER(_P)]),
@@ -397,6 +405,25 @@ class OpList:
         p = C.c_void_p()
         self.ctx.check(lib.enn_b200_oplist_last_output_ptr(self.h, index, C.byref(p)))
         return p
+
+    def nodes(self):
+        """The nodes after finalize: list of (OpInfo, kind, number of inputs)."""
+        n = C.c_int32()
+        self.ctx.check(lib.enn_b200_oplist_node_count(self.h, C.byref(n)))
+        out = []
+        for i in range(n.value):
+            info, kind, nin = OpInfo(), C.c_int32(), C.c_int32()
+            self.ctx.check(lib.enn_b200_oplist_node_info(self.h, i, C.byref(info), C.byref(kind), C.byref(nin)))
+            out.append((info, kind.value, nin.value))
+        return out
+
+    def profile(self, repeats=5):
+        """Device microseconds per node (eager passes with an event between the nodes)."""
+        n = C.c_int32()
+        self.ctx.check(lib.enn_b200_oplist_node_count(self.h, C.byref(n)))
+        us = (C.c_float * max(1, n.value))()
+        self.ctx.check(lib.enn_b200_oplist_profile(self.h, repeats, us, n.value))
+        return [us[i] for i in range(n.value)]
 
     def stats(self):
         a, b, c = C.c_int64(), C.c_int32(), C.c_int32()

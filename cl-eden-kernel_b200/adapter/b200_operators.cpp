@@ -67,7 +67,29 @@ Status B200OperatorBase::prepare_conv_like(int kind, const enn_b200_conv_desc &d
     return to_status(st);
 }
 
+Status B200OperatorBase::setProfiling(bool on) {
+    if (on && !timer_) return to_status(enn_b200_timer_create(runtime_->context(), &timer_));
+    if (!on && timer_) {
+        enn_b200_timer_destroy(timer_);
+        timer_ = nullptr;
+    }
+    return Status::SUCCESS;
+}
+
+Status B200OperatorBase::lastExecuteMicroseconds(float *us) {
+    if (!timer_ || !us) return Status::INVALID_PARAMS;
+    return to_status(enn_b200_timer_elapsed_us(timer_, us));
+}
+
 Status B200OperatorBase::execute() {
+    if (!timer_) return run();
+    enn_b200_timer_start(timer_);
+    const Status s = run();
+    enn_b200_timer_stop(timer_);
+    return s;
+}
+
+Status B200OperatorBase::run() {
     if (!op_) return Status::FAILURE;
     enn_b200_context *ctx = runtime_->context();
     const void *in = device_ptr(inputs_[0]);
@@ -95,6 +117,8 @@ Status B200OperatorBase::release() {
     if (in_nhwc_) enn_b200_free(runtime_->context(), in_nhwc_);
     if (out_nhwc_) enn_b200_free(runtime_->context(), out_nhwc_);
     in_nhwc_ = out_nhwc_ = nullptr;
+    if (timer_) enn_b200_timer_destroy(timer_);
+    timer_ = nullptr;
     return Status::SUCCESS;
 }
 

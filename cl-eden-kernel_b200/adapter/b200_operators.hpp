@@ -20,7 +20,11 @@ public:
     virtual ~B200OperatorBase() { release(); }
     Status execute();
     Status release();
+    // Device time of execute() (the per-operator bracket of userdriver_operator.h:35-42): off by default.
+    Status setProfiling(bool on);
+    Status lastExecuteMicroseconds(float *us);      // waits for the last execute() to finish
 protected:
+    Status run();
     Status prepare_conv_like(int kind, const enn_b200_conv_desc &desc, const std::shared_ptr<ITensor> &weight,
                              const std::shared_ptr<ITensor> &bias, const std::vector<float> &scales);
     Status ensure_nhwc_staging(bool nchw);
@@ -33,6 +37,7 @@ protected:
     void *in_nhwc_ = nullptr, *out_nhwc_ = nullptr;
     bool two_inputs_ = false;
     bool runtime_weights_ = false, runtime_bias_ = false;   // filter / bias are not constant tensors
+    enn_b200_timer *timer_ = nullptr;
 };
 
 class B200Convolution : public B200OperatorBase {

@@ -196,6 +196,61 @@ int32_t enn_b200_stream_sync(enn_b200_context *ctx) {
     return ENN_B200_SUCCESS;
 }
 
+// Device timer on the context's stream (two events): what an operator-level profiler brackets an execute() with.
+struct enn_b200_timer {
+    enn_b200_context *ctx = nullptr;
+    cudaEvent_t a = nullptr, b = nullptr;
+    bool started = false, stopped = false;
+};
+
+int32_t enn_b200_timer_create(enn_b200_context *ctx, enn_b200_timer **out) {
+    if (!ctx || !out) return ENN_B200_INVALID_PARAMS;
+    *out = nullptr;
+    ENN_CUDA(ctx, cudaSetDevice(ctx->device));
+    enn_b200_timer *t = new (std::nothrow) enn_b200_timer();
+    if (!t) return fail(ctx, ENN_B200_FAILURE, "out of host memory");
+    t->ctx = ctx;
+    if (cudaEventCreate(&t->a) != cudaSuccess || cudaEventCreate(&t->b) != cudaSuccess) {
+        if (t->a) cudaEventDestroy(t->a);
+        delete t;
+        return fail(ctx, ENN_B200_CUDA_FAILURE, "event creation failed");
+    }
+    *out = t;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_timer_start(enn_b200_timer *t) {
+    if (!t) return ENN_B200_INVALID_PARAMS;
+    ENN_CUDA(t->ctx, cudaEventRecord(t->a, t->ctx->stream));
+    t->started = true;
+    t->stopped = false;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_timer_stop(enn_b200_timer *t) {
+    if (!t || !t->started) return ENN_B200_INVALID_PARAMS;
+    ENN_CUDA(t->ctx, cudaEventRecord(t->b, t->ctx->stream));
+    t->stopped = true;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_timer_elapsed_us(enn_b200_timer *t, float *us) {
+    if (!t || !us || !t->stopped) return ENN_B200_INVALID_PARAMS;
+    ENN_CUDA(t->ctx, cudaEventSynchronize(t->b));
+    float ms = 0.f;
+    ENN_CUDA(t->ctx, cudaEventElapsedTime(&ms, t->a, t->b));
+    *us = ms * 1000.f;
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_timer_destroy(enn_b200_timer *t) {
+    if (!t) return ENN_B200_INVALID_PARAMS;
+    cudaEventDestroy(t->a);
+    cudaEventDestroy(t->b);
+    delete t;
+    return ENN_B200_SUCCESS;
+}
+
 int32_t enn_b200_host_alloc(size_t bytes, void **host_ptr) {
     if (!host_ptr) return ENN_B200_INVALID_PARAMS;
     return cudaHostAlloc(host_ptr, bytes ? bytes : 1, cudaHostAllocDefault) == cudaSuccess ? ENN_B200_SUCCESS : ENN_B200_CUDA_FAILURE;
@@ -267,7 +322,8 @@ static int32_t conv_like_prepare_const(enn_b200_context *ctx, const enn_b200_con
     const int32_t groups = d->groups > 0 ? d->groups : 1;
     const int32_t dil_h = d->dil_h > 0 ? d->dil_h : 1, dil_w = d->dil_w > 0 ? d->dil_w : 1;
     if (kind == OP_CONV && (d->cin % groups || d->cout % groups)) return fail(ctx, ENN_B200_INVALID_PARAMS, "channels not divisible by groups");
-    if (kind == OP_DEPTHWISE && d->cout != d->cin * groups) return fail(ctx, ENN_B200_INVALID_PARAMS, "depthwise cout != cin * depth_multiplier");
+    // cout > cin * depth_multiplier: the channels past the filter's are bias only (depthwise_conv_unequal, CLDepthwiseConvolutionQuantized.cpp:183-186)
+    if (kind == OP_DEPTHWISE && d->cout < d->cin * groups) return fail(ctx, ENN_B200_INVALID_PARAMS, "depthwise cout < cin * depth_multiplier");
     if (kind == OP_DECONV && groups != 1) return fail(ctx, ENN_B200_INVALID_PARAMS, "quantized deconvolution supports group_size 1 only");
     if (kind == OP_DECONV && d->weight_layout == ENN_B200_W_OIHW) return fail(ctx, ENN_B200_INVALID_PARAMS, "deconvolution weights are IOHW or OHWI");
     if (kind != OP_DECONV && d->weight_layout == ENN_B200_W_IOHW) return fail(ctx, ENN_B200_INVALID_PARAMS, "IOHW is a deconvolution layout");
@@ -308,6 +364,7 @@ static int32_t conv_like_prepare_const(enn_b200_context *ctx, const enn_b200_con
     // convertToNCHW passes run in initialize().
     const int32_t kh = d->kh, kw = d->kw, cout = d->cout;
     const int32_t cig = kind == OP_DEPTHWISE ? 1 : g.cin_g;
+    const int32_t dw_real = d->cin * groups;      // depthwise: output channels that have a filter
     std::vector<uint8_t> packed(static_cast<size_t>(kh) * kw * cig * cout);
     const uint8_t *src = static_cast<const uint8_t *>(w_host);
     for (int32_t oc = 0; oc < cout; ++oc) {
@@ -317,7 +374,11 @@ static int32_t conv_like_prepare_const(enn_b200_context *ctx, const enn_b200_con
                 for (int32_t ic = 0; ic < cig; ++ic) {
                     int64_t si;
                     if (kind == OP_DEPTHWISE) {
-                        si = d->weight_layout == ENN_B200_W_OHWI ? (static_cast<int64_t>(ky) * kw + kx) * cout + oc
+                        if (oc >= dw_real) {      // no filter for this channel: the zero-point byte makes every product zero
+                            packed[((static_cast<size_t>(ky) * kw + kx) * cig + ic) * cout + oc] = static_cast<uint8_t>(d->per_channel ? 0 : d->w_zp);
+                            continue;
+                        }
+                        si = d->weight_layout == ENN_B200_W_OHWI ? (static_cast<int64_t>(ky) * kw + kx) * dw_real + oc
                                                                   : static_cast<int64_t>(oc) * kh * kw + ky * kw + kx;
                     } else if (d->weight_layout == ENN_B200_W_OHWI) {
                         si = ((static_cast<int64_t>(oc) * kh + ky) * kw + kx) * cig + ic;
@@ -442,6 +503,7 @@ static int32_t conv_like_prepare(enn_b200_context *ctx, const enn_b200_conv_desc
     int64_t w_elems = static_cast<int64_t>(d->cout) * d->kh * d->kw;
     if (kind == OP_CONV) w_elems *= d->cin / groups;
     else if (kind == OP_DECONV) w_elems *= d->cin;
+    else w_elems = static_cast<int64_t>(d->cin) * groups * d->kh * d->kw;      // depthwise: the filter's own channels
     std::unique_ptr<RuntimeConstants> dyn(new (std::nothrow) RuntimeConstants());
     if (!dyn) return fail(ctx, ENN_B200_FAILURE, "out of host memory");
     dyn->weights = d->weights_as_input != 0;

@@ -26,7 +26,8 @@ __global__ void depthwise_generic_kernel(ConvGeom g, Requant rq, const void *__r
     p /= g.ow;
     const int32_t oy = static_cast<int32_t>(p % g.oh);
     const int32_t b = static_cast<int32_t>(p / g.oh);
-    const int32_t c = oc / g.groups;
+    // channels past cin * multiplier carry zero-point weights (prepare): any valid input channel will do
+    const int32_t c = min(oc / g.groups, g.cin - 1);
     int32_t acc = rq.bias[oc];
     for (int32_t ky = 0; ky < g.kh; ++ky) {
         const int32_t iy = oy * g.sh + ky * g.dh - g.pt;
@@ -666,7 +667,7 @@ dw3x3_ring_kernel(const DwRingParams p, const DwChan *__restrict__ chan, const u
 
 bool dw3x3_eligible(const ConvGeom &g) {
     return g.kh == 3 && g.kw == 3 && g.dh == 1 && g.dw == 1 && g.groups == 1 && g.sh == g.sw && (g.sh == 1 || g.sh == 2) &&
-           (g.cin % 4) == 0 && !g.a_signed;
+           (g.cin % 4) == 0 && g.cout == g.cin && !g.a_signed;
 }
 
 // Launch shape of the row-ring kernel for one geometry.

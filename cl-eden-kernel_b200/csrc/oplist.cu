@@ -371,6 +371,55 @@ int32_t enn_b200_oplist_last_output_ptr(enn_b200_oplist *l, int32_t output_index
     return ENN_B200_SUCCESS;
 }
 
+int32_t enn_b200_oplist_node_count(const enn_b200_oplist *l, int32_t *n_nodes) {
+    if (!l || !n_nodes) return ENN_B200_INVALID_PARAMS;
+    *n_nodes = static_cast<int32_t>(l->nodes.size());
+    return ENN_B200_SUCCESS;
+}
+
+int32_t enn_b200_oplist_node_info(const enn_b200_oplist *l, int32_t index, enn_b200_op_info_t *info, int32_t *kind, int32_t *n_inputs) {
+    if (!l || index < 0 || index >= static_cast<int32_t>(l->nodes.size())) return ENN_B200_INVALID_PARAMS;
+    const auto &n = l->nodes[index];
+    if (info) *info = n.op->info;
+    if (kind) *kind = n.op->kind;
+    if (n_inputs) *n_inputs = static_cast<int32_t>(n.ins.size());
+    return ENN_B200_SUCCESS;
+}
+
+// Device time of every node: the nodes are launched one by one on the list's own tensors with an event between them
+// (the role of the PROFILE_FROM / PROFILE_UNTIL pair around every operator, userdriver_operator.h:35-42).
+int32_t enn_b200_oplist_profile(enn_b200_oplist *l, int32_t repeats, float *node_us, int32_t capacity) {
+    if (!l || !l->finalized) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist not finalized");
+    const int n = static_cast<int>(l->nodes.size());
+    if (!node_us || capacity < n || repeats < 1 || repeats > 1000) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_profile: bad argument");
+    enn_b200_context *ctx = l->ctx;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "cudaSetDevice failed");
+    std::vector<cudaEvent_t> ev(n + 1, nullptr);
+    int32_t st = ENN_B200_SUCCESS;
+    for (auto &e : ev)
+        if (cudaEventCreate(&e) != cudaSuccess) st = lfail(l, ENN_B200_CUDA_FAILURE, "oplist_profile: event creation failed");
+    for (int i = 0; i < n; ++i) node_us[i] = 0.f;
+    for (int rep = -1; rep < repeats && st == ENN_B200_SUCCESS; ++rep) {      // pass -1 warms up
+        cudaEventRecord(ev[0], ctx->stream);
+        for (int i = 0; i < n && st == ENN_B200_SUCCESS; ++i) {
+            const auto &nd = l->nodes[i];
+            const void *ins[ENN_B200_CONCAT_MAX_INPUTS];
+            for (size_t k = 0; k < nd.ins.size(); ++k) ins[k] = l->tensors[nd.ins[k]].dev;
+            st = enn_b200_op_execute_n(nd.op, ins, static_cast<int32_t>(nd.ins.size()), l->tensors[nd.out].dev);
+            cudaEventRecord(ev[i + 1], ctx->stream);
+        }
+        if (st == ENN_B200_SUCCESS && cudaStreamSynchronize(ctx->stream) != cudaSuccess) st = lfail(l, ENN_B200_CUDA_FAILURE, "oplist_profile: execution failed");
+        for (int i = 0; i < n && st == ENN_B200_SUCCESS && rep >= 0; ++i) {
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+            node_us[i] += ms * 1000.f / static_cast<float>(repeats);
+        }
+    }
+    for (auto &e : ev)
+        if (e) cudaEventDestroy(e);
+    return st;
+}
+
 int32_t enn_b200_oplist_stats(enn_b200_oplist *l, int64_t *device_bytes, int32_t *n_buffers, int32_t *kernel_launches) {
     if (!l || !l->finalized) return ENN_B200_INVALID_PARAMS;
     if (device_bytes) *device_bytes = l->device_bytes;

@@ -57,7 +57,9 @@ def conv_case(seed=0, n=1, h=56, w=56, cin=64, cout=64, k=3, stride=1, dil=1, gr
 
 def depthwise_case(seed=0, n=2, h=112, w=112, c=32, k=3, stride=1, dm=1, per_channel=True, act=enn.ACT_RELU6,
                    layout=enn.W_OIHW, in_scale=0.02, in_zp=128, out_scale=0.04, out_zp=0, dil=1, w_scale=0.01,
-                   w_zp=121, act_dtype=enn.U8):
+                   w_zp=121, act_dtype=enn.U8, extra_out=0):
+    """extra_out: output channels past c * dm, which have no filter and carry the requantised bias only
+    (depthwise_conv_unequal); bias and per-channel scales cover them, the filter does not."""
     rng = np.random.default_rng(seed)
     cout = c * dm
     if act_dtype == enn.S8:
@@ -69,7 +71,8 @@ def depthwise_case(seed=0, n=2, h=112, w=112, c=32, k=3, stride=1, dm=1, per_cha
         wt = rng.integers(-127, 128, wshape, dtype=np.int64).astype(np.int8)
     else:
         wt = rng.integers(0, 256, wshape, dtype=np.int64).astype(np.uint8)
-    bias = rng.integers(-500, 501, (cout,), dtype=np.int64).astype(np.int32)
+    cout += extra_out
+    bias = rng.integers(-500 if not extra_out else -40000, 501 if not extra_out else 40001, (cout,), dtype=np.int64).astype(np.int32)
     scales = np.exp(rng.uniform(np.log(1e-3), np.log(1e-1), cout)).astype(np.float32) if per_channel else None
     pt, pb = same_pad_tf(h, k, stride, dil)
     pl, pr = same_pad_tf(w, k, stride, dil)

@@ -186,6 +186,15 @@ int32_t enn_b200_download(enn_b200_context *ctx, void *host_dst, const void *dev
 /* Device->device on the stream (CLRuntime::copyBuffer, as used by CLConvolution.cpp:151 for the bias). */
 int32_t enn_b200_copy_device(enn_b200_context *ctx, void *dev_dst, const void *dev_src, size_t bytes);
 int32_t enn_b200_stream_sync(enn_b200_context *ctx);            /* CLComputeLibrary::synchronize */
+/* Device timer on the context's stream: start / stop enqueue an event each, elapsed_us waits for the stop event.  What
+ * EnnUDOperator<T>::execute brackets every operator with (PROFILE_FROM / PROFILE_UNTIL, userdriver_operator.h:35-42),
+ * in device time. */
+typedef struct enn_b200_timer enn_b200_timer;
+int32_t enn_b200_timer_create(enn_b200_context *ctx, enn_b200_timer **timer);
+int32_t enn_b200_timer_start(enn_b200_timer *timer);
+int32_t enn_b200_timer_stop(enn_b200_timer *timer);
+int32_t enn_b200_timer_elapsed_us(enn_b200_timer *timer, float *microseconds);
+int32_t enn_b200_timer_destroy(enn_b200_timer *timer);
 int32_t enn_b200_host_alloc(size_t bytes, void **host_ptr);      /* pinned host staging */
 int32_t enn_b200_host_free(void *host_ptr);
 /* Last error text of this context (empty string if none); never fails. */
@@ -302,6 +311,14 @@ int32_t enn_b200_oplist_wait(enn_b200_oplist *list);
 /* Operators only, on device-resident tensors, asynchronous on the context stream. */
 int32_t enn_b200_oplist_execute_device(enn_b200_oplist *list);
 int32_t enn_b200_oplist_tensor_ptr(enn_b200_oplist *list, int32_t tensor_id, void **dev_ptr);
+/* The list's nodes after finalize (a fused CONV_2D -> ADD pair is one node): count, and per node the operator's info,
+ * its kind (0 conv, 1 depthwise, 2 deconvolution, 3 fully connected, 4 add, 5 average pool, 6 max pool, 7 mean,
+ * 8 concat, 9 softmax, 10 resize) and its number of inputs. */
+int32_t enn_b200_oplist_node_count(const enn_b200_oplist *list, int32_t *n_nodes);
+int32_t enn_b200_oplist_node_info(const enn_b200_oplist *list, int32_t index, enn_b200_op_info_t *info, int32_t *kind, int32_t *n_inputs);
+/* Per-operator device time in microseconds (average over `repeats` eager passes over the list's own tensors, one
+ * event between consecutive nodes): the per-operator bracket of userdriver_operator.h:35-42 for a whole list. */
+int32_t enn_b200_oplist_profile(enn_b200_oplist *list, int32_t repeats, float *node_us, int32_t capacity);
 /* Device address of graph output `output_index` as written by the latest enn_b200_oplist_submit (submissions alternate
  * between two device copies of every graph input / output), for callers that pass results on device-side
  * (CLTensor::getDataPtr on an output tensor). */

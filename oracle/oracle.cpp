@@ -251,6 +251,7 @@ int32_t orc_depthwise(const enn_b200_conv_desc *d, const void *in, const void *w
     int32_t oh, ow;
     orc_conv_out_dims(d, &oh, &ow);
     const int32_t dm = d->groups > 0 ? d->groups : 1;
+    const int32_t real = d->cin * dm;      // channels that have a filter
     std::vector<int32_t> mult(d->cout), shift(d->cout);
     orc_derive_requant(d->cout, d->per_channel, d->in_scale, d->w_scale, d->bias_scale, d->out_scale, pc_scales,
                        mult.data(), shift.data());
@@ -265,14 +266,17 @@ int32_t orc_depthwise(const enn_b200_conv_desc *d, const void *in, const void *w
                 for (int32_t oc = 0; oc < d->cout; ++oc) {
                     const int32_t c = oc / dm;
                     int32_t acc = bias[oc];
-                    for (int32_t i = 0; i < d->kh; ++i) {
+                    // Output channels past cin * depth_multiplier have no filter: bias only
+                    // (depthwise_conv_unequal, DepthwiseconvolutionKernels.cpp:1242-1271; the filter tensor holds
+                    // cin * depth_multiplier channels).
+                    for (int32_t i = 0; i < d->kh && oc < real; ++i) {
                         const int32_t iy = oy * d->stride_h + i * d->dil_h - d->pad_t;
                         if (iy < 0 || iy >= d->h) continue;
                         for (int32_t j = 0; j < d->kw; ++j) {
                             const int32_t ix = ox * d->stride_w + j * d->dil_w - d->pad_l;
                             if (ix < 0 || ix >= d->w) continue;
                             const int64_t widx = d->weight_layout == ENN_B200_W_OHWI
-                                                     ? (static_cast<int64_t>(i) * d->kw + j) * d->cout + oc
+                                                     ? (static_cast<int64_t>(i) * d->kw + j) * real + oc
                                                      : static_cast<int64_t>(oc) * d->kh * d->kw + i * d->kw + j;
                             const int32_t a =
                                 load_act(in, ((static_cast<int64_t>(b) * d->h + iy) * d->w + ix) * d->cin + c, d->act_dtype);

@@ -248,11 +248,15 @@ int32_t ref_depthwise(const enn_b200_conv_desc *d, const uint8_t *in, const void
     for (int b = 0; b < d->n * d->cin; ++b)
         for (int yy = 0; yy < d->h; ++yy)
             std::memcpy(&xp[(static_cast<size_t>(b) * ph + yy + d->pad_t) * pw + d->pad_l], &x[(static_cast<size_t>(b) * d->h + yy) * d->w], d->w);
-    std::vector<uint8_t> wo(static_cast<size_t>(d->cout) * d->kh * d->kw);
+    // The filter holds cin * depth_multiplier channels; output channels past those are written by depthwise_conv_unequal
+    // (per-tensor class only, and its indexing is that of one image: CLDepthwiseConvolutionQuantized.cpp:651-671).
+    const int real = d->cin * dm;
+    if (real > d->cout || (real < d->cout && (d->per_channel || d->n != 1))) return 3;
+    std::vector<uint8_t> wo(static_cast<size_t>(real) * d->kh * d->kw);
     const uint8_t *wsrc = static_cast<const uint8_t *>(w);
-    for (int o = 0; o < d->cout; ++o)
+    for (int o = 0; o < real; ++o)
         for (int k = 0; k < d->kh * d->kw; ++k)
-            wo[static_cast<size_t>(o) * d->kh * d->kw + k] = d->weight_layout == ENN_B200_W_OHWI ? wsrc[static_cast<size_t>(k) * d->cout + o] : wsrc[static_cast<size_t>(o) * d->kh * d->kw + k];
+            wo[static_cast<size_t>(o) * d->kh * d->kw + k] = d->weight_layout == ENN_B200_W_OHWI ? wsrc[static_cast<size_t>(k) * real + o] : wsrc[static_cast<size_t>(o) * d->kh * d->kw + k];
     std::vector<uint8_t> y(static_cast<size_t>(d->n) * d->cout * oh * ow);
     int32_t lo, hi;
     if (d->per_channel) {
@@ -273,6 +277,8 @@ int32_t ref_depthwise(const enn_b200_conv_desc *d, const uint8_t *in, const void
             ocl::depthwise_conv_INT8(xp.data(), wo.data(), bias, y.data(), ph, pw, d->kh, d->kw, d->stride_h, d->stride_w, oh, ow, dm, -d->in_zp,
                                      -d->w_zp, d->out_zp, m, s, lo, hi);
         });
+        if (real < d->cout)
+            ocl::run3(d->n, d->cout - real, static_cast<size_t>(oh) * ow, [&] { ocl::depthwise_conv_unequal_INT8(bias, y.data(), real, d->out_zp, m, s, lo, hi); });
     }
     nchw_to_nhwc(y, out, d->n, oh, ow, d->cout);
     return 0;

@@ -174,7 +174,11 @@ int main() {
         p->activation_info = std::make_shared<ActivationInfo>(ActivationInfo::ActivationType::RELU, true);
         auto fc = lib.createFullyConnected(PrecisionType::UINT8);
         CHECK(fc->initialize({ifm, w, b}, {ofm}, p) == Status::SUCCESS);
+        float us = -1.f;
+        CHECK(fc->lastExecuteMicroseconds(&us) == Status::INVALID_PARAMS);      // profiling is off by default
+        CHECK(fc->setProfiling(true) == Status::SUCCESS);
         CHECK(fc->execute() == Status::SUCCESS);
+        CHECK(fc->lastExecuteMicroseconds(&us) == Status::SUCCESS && us > 0.f && us < 1e5f);
         CHECK(ofm->readData(y.data()) == Status::SUCCESS);
         enn_b200_fc_desc d{};
         d.m = M; d.k = K; d.n = NO; d.activation = ENN_B200_ACT_RELU;

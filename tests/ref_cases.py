@@ -64,6 +64,9 @@ CASES = {
     "dw_pt_s1": ("dw", lambda: cases.depthwise_case(seed=106, n=1, h=10, w=10, c=8, per_channel=False, out_scale=0.08, out_zp=3)),
     "dw_pt_dm2_5x5": ("dw", lambda: cases.depthwise_case(seed=107, n=1, h=9, w=9, c=4, dm=2, k=5, per_channel=False, out_scale=0.2, out_zp=7,
                                                            act=enn.ACT_NONE)),
+    # output channels past cin * depth_multiplier: bias only (depthwise_conv_unequal; one image, as the kernel indexes)
+    "dw_pt_unequal": ("dw", lambda: cases.depthwise_case(seed=131, n=1, h=8, w=9, c=6, dm=2, per_channel=False, out_scale=0.3, out_zp=90,
+                                                           act=enn.ACT_NONE, extra_out=5)),
     "deconv_pt_4x4s2": ("deconv", lambda: cases.deconv_case(seed=108, n=2, h=6, w=5, cin=16, cout=8)),
     "deconv_pt_ohwi_relu6": ("deconv", lambda: cases.deconv_case(seed=109, n=1, h=5, w=5, cin=8, cout=4, layout=enn.W_OHWI, act=enn.ACT_RELU6)),
     "deconv_pc_3x3s2": ("deconv", lambda: cases.deconv_case(seed=110, n=1, h=5, w=6, cin=12, cout=8, k=3, stride=2, pad=0, per_channel=True,

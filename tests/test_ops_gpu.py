@@ -203,6 +203,10 @@ DW_CASES = {
     "ring_per_tensor": dict(n=2, h=20, w=21, c=32, per_channel=False, out_scale=0.08, out_zp=3),
     "ring_per_tensor_s2_relu": dict(n=2, h=22, w=19, c=64, stride=2, per_channel=False, out_scale=0.03, out_zp=0),
     "ring_none_act": dict(n=2, h=13, w=17, c=96, act=cases.enn.ACT_NONE, out_zp=131, out_scale=0.1),
+    # output channels past cin * depth_multiplier: no filter, bias only (depthwise_conv_unequal)
+    "unequal_pt": dict(n=2, h=9, w=10, c=6, dm=2, per_channel=False, out_scale=0.3, out_zp=90, act=cases.enn.ACT_NONE, extra_out=5),
+    "unequal_pc_3x3_c32": dict(n=1, h=12, w=12, c=32, extra_out=16, out_scale=0.8, out_zp=100, act=cases.enn.ACT_NONE),
+    "unequal_ohwi": dict(n=1, h=7, w=8, c=8, per_channel=False, layout=cases.enn.W_OHWI, extra_out=3, out_scale=0.3, out_zp=90, act=cases.enn.ACT_NONE),
 }
 
 
@@ -726,6 +730,26 @@ def test_fused_add_refusals(enn, ctx):
         op.fuse_add(other)                          # not an add over this convolution's output
     for o in (op, addop, other):
         o.release()
+
+
+def test_oplist_profile_and_nodes(enn, ctx):
+    """Per-operator device times of a list (the per-operator bracket the reference's executor puts around every op)."""
+    import importlib
+    mn = importlib.import_module(enn.__name__ + ".mobilenet")
+    layers, _ = mn.build_model(seed=0, calib_images=1)
+    ol, info = mn.make_oplist(enn, ctx, layers, 8)
+    try:
+        nodes = ol.nodes()
+        n_add = sum(1 for L in layers if L["kind"] == "add")
+        fused = sum(1 for (_, kind, nin) in nodes if kind == 0 and nin == 2)
+        assert len(nodes) == len(layers) - fused and 0 < fused <= n_add      # at 8 images every add is small enough to fuse
+        assert ol.stats()["kernel_launches"] == sum(i.kernel_launches for (i, _, _) in nodes)
+        us = ol.profile(3)
+        assert len(us) == len(nodes) and all(0.5 < t < 5000 for t in us), us
+        with pytest.raises(enn.EnnError):
+            enn.lib.enn_b200_oplist_profile(ol.h, 0, None, 0) and ol.ctx.check(enn.INVALID_PARAMS)
+    finally:
+        ol.destroy()
 
 
 def test_error_paths(enn, ctx):
