@@ -39,9 +39,12 @@ DEFAULT_WORKLOAD = "mobilenetv2_u8_b256"
 GLOBAL_BATCH = 256
 WORKLOAD_TEXT = "MobileNetV2-1.0 224x224 uint8 graph (per-channel int8 weights), one batch of 256 images partitioned over the GPUs"
 
-# DRAM traffic of the graph's kernels from one ncu pass over a batch-32 graph replay (profiles/mobilenetv2_graph_dram.md),
-# as measured bytes / algorithmic bytes per kernel family; activations dominate, so traffic grows in proportion to the batch.
-NCU_TRAFFIC_RATIO = {}
+# DRAM traffic of the graph's kernels from one ncu pass (dram__bytes_read.sum + dram__bytes_write.sum per launch) over one
+# step of the batch-256 graph (profiles/mobilenetv2_graph_launch_list.md), as measured bytes / algorithmic bytes per kernel
+# family.  Below 1 because the 126 MB L2 still holds part of every layer's output when the next kernel reads it; the
+# tensors are activations, so the traffic of a smaller per-rank batch is at most this share of its algorithmic bytes.
+NCU_TRAFFIC_RATIO = {"tc_gemm_kernel": 0.653, "dw3x3_ring_kernel": 0.745, "conv3x3c3_kernel": 0.617, "add_kernel_lut2": 0.671,
+                     "avgpool_vec4_kernel": 0.986}
 
 
 def load_package():
