@@ -1476,7 +1476,8 @@ __global__ void __launch_bounds__(256) conv3x3c3_kernel(Conv3x3c3Params g, const
     __syncthreads();
     pdl_wait();         // weights and constants above belong to the plan; the image may come from the kernel before
     pdl_trigger();
-    const uint32_t sw_u32 = smem_u32(s_w), sc_u32 = smem_u32(s_c);
+    const uint8_t *sw_p = reinterpret_cast<const uint8_t *>(s_w), *sc_p = reinterpret_cast<const uint8_t *>(s_c);
+    constexpr bool kPlainPack = MODE == kModeReluSat;      // packed bytes are final: no lower clamp to add, no sign flip
     const int32_t hi_clamp = g.act_max - g.act_min;
     // lower clamp added back per byte; signed outputs go through act_min + 128 and a sign-bit flip (no carries between bytes)
     const uint32_t sign_word = A_SIGNED ? 0x80808080u : 0u;
@@ -1540,17 +1541,18 @@ __global__ void __launch_bounds__(256) conv3x3c3_kernel(Conv3x3c3Params g, const
         uint8_t *orow = out + static_cast<int64_t>(m) * g.N;
         for (int n0 = 0; n0 < g.N; n0 += 16) {
             uint32_t wout[P][4];
+            // Plain shared loads from pointers into the shared array: the per-channel part of every address is an immediate.
+            const uint8_t *wp = sw_p + n0 * 32, *cp = sc_p + n0 * 16;
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
                 int32_t y[P][4];
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
-                    const int nn = n0 + jj * 4 + b;
-                    uint4 w0, w1;
-                    int4 cv;
-                    asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w0.x), "=r"(w0.y), "=r"(w0.z), "=r"(w0.w) : "r"(sw_u32 + nn * 32));
-                    asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w1.x), "=r"(w1.y), "=r"(w1.z), "=r"(w1.w) : "r"(sw_u32 + nn * 32 + 16));
-                    asm("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(cv.x), "=r"(cv.y), "=r"(cv.z), "=r"(cv.w) : "r"(sc_u32 + nn * 16));
+                    const int nl = jj * 4 + b;
+                    const uint4 w0 = *reinterpret_cast<const uint4 *>(wp + nl * 32);
+                    const uint4 w1 = *reinterpret_cast<const uint4 *>(wp + nl * 32 + 16);
+                    ColRegs cv;
+                    ld_col_shared<MODE>(cp + nl * 16, cv);
 #pragma unroll
                     for (int i = 0; i < P; ++i) {
                         int32_t acc = 0;
@@ -1568,7 +1570,8 @@ __global__ void __launch_bounds__(256) conv3x3c3_kernel(Conv3x3c3Params g, const
 #pragma unroll
                 for (int i = 0; i < P; ++i) {
                     const uint32_t hi = pack_sat_u8_tc(y[i][3], y[i][2], 0);
-                    wout[i][jj] = (pack_sat_u8_tc(y[i][1], y[i][0], hi) + lo_word) ^ sign_word;
+                    const uint32_t pk = pack_sat_u8_tc(y[i][1], y[i][0], hi);
+                    wout[i][jj] = kPlainPack ? pk : ((pk + lo_word) ^ sign_word);
                 }
             }
 #pragma unroll
@@ -1921,7 +1924,10 @@ void launch_first_layer(enn_b200_context *ctx, const TcGemm &gm, const void *in,
     switch (p.mode) {                                               \
         case kModeNudge: ENN_FL(S, A, kModeNudge); break;           \
         case kModeGeneral: ENN_FL(S, A, kModeGeneral); break;       \
-        case kModeReluHi: ENN_FL(S, A, kModeReluHi); break;         \
+        case kModeReluHi:                                           \
+            if (p.sat_plain && !S) ENN_FL(S, A, kModeReluSat);      \
+            else ENN_FL(S, A, kModeReluHi);                         \
+            break;                                                  \
         default: ENN_FL(S, A, kModeReluTwo); break;                 \
     }
     if (p.a_signed) {
