@@ -365,7 +365,7 @@ __device__ __forceinline__ void tile_coords(const TcParams &p, int tile, int &tg
 //                e >= 1); result = (q >> (31 - ls)) >> e.  Covers e == 0 and left shifts, which otherwise need the
 //                general code.
 //   kModeReluHi  the same with one shift, hi32(q) >> (e - 1), for operators whose columns all have e >= 1 and ls == 0
-//                (two ALU instructions per output fewer; ENN_B200_NO_RELU_HI=1 keeps the two-shift form).
+//                (two ALU instructions per output fewer; option no_relu_hi keeps the two-shift form).
 // ColParam words: {mult, addend, esh, bias} for the first two modes, {C low, C high, mult, shifts} for the ReLU modes
 // (shifts = e - 1 for kModeReluHi, (31 - ls) | e << 8 for kModeReluTwo).
 constexpr size_t kWidePackWeightBytes = 100 * 1024;    // resident block-diagonal weights of a wide-row pixel packing
@@ -1706,7 +1706,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     }
     // CTA pairs (cta_group::2): two SMs share one 256-row tile and every B byte is fetched once per pair.  Used for plain
     // GEMMs with several waves of 256-wide tiles, long K and operands too large to stay L2 resident ((M+N) K > 48 MB):
-    // 8192^3 runs 7 % faster than on the one-CTA kernel, 4096^3 3 % slower.  ENN_B200_TC_PAIR=0 / 1 overrides the size rule.
+    // 8192^3 runs 7 % faster than on the one-CTA kernel, 4096^3 3 % slower.  Option tc_pair = 0 / 1 overrides the size rule.
     const bool pair_ok = span == kBK && !implicit_span && p.tiles_m >= 2 && (K + kBK - 1) / kBK >= 8 && bn_data >= 128 &&
                          static_cast<int64_t>(p.tiles_m) * tiles_n >= 2ll * ctx->sm_count;
     bool two = pair_ok && (static_cast<int64_t>(M) + N) * K > (48ll << 20);

@@ -120,7 +120,7 @@ struct enn_b200_op {
 
 namespace enn_b200 {
 
-bool pdl_enabled();     // abi.cu: false when ENN_B200_NO_PDL is set (development switch)
+bool pdl_enabled();     // abi.cu: false once option no_pdl has been set on any context
 
 // kernels_direct.cu
 cudaError_t launch_conv_direct(const ConvGeom &g, const Requant &rq, const void *in, const void *w, void *out,
