@@ -272,7 +272,7 @@ void *enn_b200_stream(enn_b200_context *ctx) { return ctx ? static_cast<void *>(
 
 int32_t enn_b200_context_set_option(enn_b200_context *ctx, const char *name, int32_t value) {
     if (!ctx || !name) return ENN_B200_INVALID_PARAMS;
-    static const char *const known[] = {"no_pdl", "no_relu_mode", "no_relu_hi", "no_relu_sat", "no_wide_store", "no_first_layer", "no_implicit", "no_gemv",
+    static const char *const known[] = {"no_pdl", "no_relu_mode", "no_relu_hi", "no_relu_sat", "no_wide_store", "no_grouped_tc", "no_first_layer", "no_implicit", "no_gemv",
                                         "no_narrow_span", "no_pack", "pack_wide", "no_bres", "no_bres_k1", "no_fan_out", "tc_bn",
                                         "tc_pair", "tc_raster", "epi_g", "dw_legacy", "no_fuse", "fuse_all", "dw_rows"};
     bool ok = false;

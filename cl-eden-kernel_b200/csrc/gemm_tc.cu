@@ -1982,9 +1982,15 @@ bool tc_available(const enn_b200_context *ctx) { return ctx && ctx->cc_major == 
 int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
     const ConvGeom &g = op->g;
     enn_b200_context *ctx = op->ctx;
-    if (g.groups != 1) return ENN_B200_INVALID_PARAMS;
     const uint8_t *w = static_cast<const uint8_t *>(w_hwio);
     const int32_t N = g.cout, cin = g.cin;
+    // Grouped convolution (the reference runs one GEMM per group, CLGEMMConvolutionQuantized.cpp:202-265) is the dense
+    // convolution with block-diagonal weights: outside a channel's own group the weight is the weight zero point, whose
+    // terms vanish in the zero-point algebra.  The tensor pipe has the room (it idles in every convolution of this size);
+    // the dense weights must stay small, or the direct kernel takes the operator.
+    if (g.groups != 1 && (op->kind != OP_CONV || g.groups > 32 || static_cast<int64_t>(g.kh) * g.kw * cin * N > (8ll << 20) ||
+                          ctx->opt("no_grouped_tc")))
+        return ENN_B200_INVALID_PARAMS;
 
     QuantHost qh;
     qh.mult.resize(N); qh.shift.resize(N); qh.bias.resize(N);
@@ -2070,7 +2076,14 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         bool in_place = pointwise && (cin & 15) == 0;
         plan->gemms.resize(1);
         TcGemm &gm = plan->gemms[0];
-        auto weight = [&](int32_t n, int32_t k) { return w[static_cast<size_t>(k) * N + n]; };
+        // `w` is [Kh][Kw][Cin / groups][Cout]; k = tap * cin + c over all input channels
+        const int32_t cin_g = cin / g.groups, cout_g = N / g.groups;
+        const uint8_t zero_w = static_cast<uint8_t>(g.w_zp);
+        auto weight = [&](int32_t n, int32_t k) -> uint8_t {
+            if (g.groups == 1) return w[static_cast<size_t>(k) * N + n];
+            const int32_t tap = k / cin, c = k - tap * cin;
+            return c / cin_g == n / cout_g ? w[(static_cast<size_t>(tap) * cin_g + c % cin_g) * N + n] : zero_w;
+        };
         // Pixel packing: with K of 16, 32 or 64 bytes and few output channels, f = 128 / K consecutive pixels are one
         // 128-byte row of the activation tensor.  The GEMM [M/f][fK] x blockdiag(W, ..., W) -> [M/f][fN] is the same
         // memory as [M][K] x W -> [M][N] when the off-diagonal weights equal the weight zero point (their terms vanish
@@ -2117,7 +2130,7 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
             }
             const uint8_t zero_raw = static_cast<uint8_t>(g.w_zp);
             auto packed_weight = [&](int32_t n, int32_t k) -> uint8_t {
-                return n / N == k / K ? w[static_cast<size_t>(k % K) * N + (n % N)] : zero_raw;
+                return n / N == k / K ? weight(n % N, k % K) : zero_raw;
             };
             st = build_gemm(ctx, g, qp, static_cast<int32_t>(M64 / pack), pack * N, pack * K, packed_weight, &gm, 0, wide_pack);
             if (st != ENN_B200_SUCCESS) return bail(st);

@@ -202,7 +202,7 @@ int32_t enn_b200_last_error(enn_b200_context *ctx, char *buf, size_t buf_len);
 /* cudaStream_t of the context, as void*, so a caller can order its own work against it. */
 void *enn_b200_stream(enn_b200_context *ctx);
 /* Planner overrides for tests and tuning, read when an operator is prepared (the library reads no environment
- * variable).  Names: no_pdl, no_relu_mode, no_relu_hi, no_relu_sat, no_wide_store, no_first_layer, no_implicit, no_gemv, no_narrow_span, no_pack,
+ * variable).  Names: no_pdl, no_relu_mode, no_relu_hi, no_relu_sat, no_wide_store, no_grouped_tc, no_first_layer, no_implicit, no_gemv, no_narrow_span, no_pack,
  * pack_wide, no_bres, no_bres_k1, no_fan_out, tc_bn (>= 96), tc_pair, tc_raster, epi_g, dw_legacy, dw_rows, no_fuse, fuse_all.
  * Stands where the reference reads its build-time device switches (CLRuntime.cpp:174-213).  Unknown names are
  * rejected with INVALID_PARAMS; none of them changes a result. */

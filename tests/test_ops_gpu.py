@@ -43,6 +43,12 @@ CONV_CASES = {
     "stride2": dict(n=2, h=15, w=14, cin=8, cout=12, k=3, stride=2),
     "dilated": dict(n=1, h=13, w=13, cin=8, cout=8, k=3, dil=2),
     "grouped_oihw": dict(n=2, h=9, w=9, cin=8, cout=12, k=3, groups=4, layout=cases.enn.W_OIHW),
+    # grouped convolutions on the tensor-core path (block-diagonal weights): gathered 3x3 stride 2, implicit 3x3, in-place 1x1,
+    # u8 per-tensor weights (row-sum correction over the zero-point blocks) and int8 per-channel weights
+    "grouped_tc_gather_s2": dict(n=2, h=17, w=15, cin=24, cout=36, k=3, stride=2, groups=3, w_zp=131, out_scale=0.04),
+    "grouped_tc_implicit": dict(n=2, h=12, w=13, cin=64, cout=64, k=3, groups=2, per_channel=True, out_scale=0.3, act=cases.enn.ACT_NONE),
+    "grouped_tc_1x1_g4": dict(n=3, h=14, w=14, cin=64, cout=96, k=1, groups=4, w_zp=119, out_scale=0.03),
+    "grouped_tc_1x1_g8_pc_relu": dict(n=2, h=20, w=20, cin=128, cout=128, k=1, groups=8, per_channel=True, out_scale=0.002, out_zp=0),
     "pointwise": dict(n=2, h=14, w=14, cin=96, cout=24, k=1, act=cases.enn.ACT_NONE),
     "per_channel": dict(n=2, h=14, w=14, cin=32, cout=48, k=3, per_channel=True, out_scale=0.3),
     "per_channel_1x1": dict(n=3, h=7, w=7, cin=160, cout=320, k=1, per_channel=True, out_scale=0.5, act=cases.enn.ACT_NONE),
@@ -747,9 +753,24 @@ def test_oplist_profile_and_nodes(enn, ctx):
         us = ol.profile(3)
         assert len(us) == len(nodes) and all(0.5 < t < 5000 for t in us), us
         with pytest.raises(enn.EnnError):
-            enn.lib.enn_b200_oplist_profile(ol.h, 0, None, 0) and ol.ctx.check(enn.INVALID_PARAMS)
+            ol.ctx.check(enn.lib.enn_b200_oplist_profile(ol.h, 0, None, 0))      # no repeats, no buffer
     finally:
         ol.destroy()
+
+
+def test_grouped_conv_runs_on_tensor_cores(enn, ctx):
+    d, x, w, b, sc = cases.conv_case(seed=9, n=2, h=14, w=14, cin=64, cout=96, k=1, groups=4)
+    op = enn.conv2d(ctx, d, w, b, sc)
+    assert op.info.impl == enn.IMPL_TCGEN05
+    op.release()
+    c2 = enn.Context(0)
+    try:
+        c2.set_option("no_grouped_tc", 1)
+        op = enn.conv2d(c2, d, w, b, sc)
+        assert op.info.impl == enn.IMPL_DIRECT
+        op.release()
+    finally:
+        c2.close()
 
 
 def test_error_paths(enn, ctx):
