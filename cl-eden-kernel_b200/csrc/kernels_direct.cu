@@ -165,8 +165,7 @@ __global__ void __launch_bounds__(kAddLut2Threads) add_kernel_lut2(AddParams p, 
     pdl_trigger();
     const uint8_t *lut = reinterpret_cast<const uint8_t *>(s_lut2_q);
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count16; i += stride) {
-        const uint4 va = a[i], vb = b[i];
+    auto combine = [&](const uint4 &va, const uint4 &vb) {
         const uint32_t wa[4] = {va.x, va.y, va.z, va.w};
         const uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w};
         uint32_t wo[4];
@@ -181,8 +180,16 @@ __global__ void __launch_bounds__(kAddLut2Threads) add_kernel_lut2(AddParams p, 
             }
             wo[j] = o[0] | (o[1] << 8) | (o[2] << 16) | (o[3] << 24);
         }
-        out[i] = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+        return make_uint4(wo[0], wo[1], wo[2], wo[3]);
+    };
+    // Two steps per iteration with all four loads issued first: the kernel waits on its global loads more than on anything else.
+    int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + stride < count16; i += 2 * stride) {
+        const uint4 va0 = a[i], vb0 = b[i], va1 = a[i + stride], vb1 = b[i + stride];
+        out[i] = combine(va0, vb0);
+        out[i + stride] = combine(va1, vb1);
     }
+    if (i < count16) out[i] = combine(a[i], b[i]);
 }
 
 // Called once per prepared add operator (with its device current): the pair-table kernel needs 64 KB of dynamic shared memory.
