@@ -210,6 +210,7 @@ def op_configs(cases):
         "deconv4x4_s2_8x64x64x128": ("deconv", lambda: cases.deconv_case(seed=0, n=8, h=64, w=64), "tensor"),
         # the MobileNetV2 layers that dominate the graph step, as stand-alone workloads for profiling
         "mnv2_expand_256x112x112x16to96": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=112, w=112, cin=16, cout=96, k=1, per_channel=True, out_scale=0.0235, out_zp=0), "hbm"),
+        "mnv2_expand_256x56x56x24to144": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=56, w=56, cin=24, cout=144, k=1, per_channel=True, out_scale=0.0235, out_zp=0), "hbm"),
         "mnv2_project_256x56x56x144to24": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=56, w=56, cin=144, cout=24, k=1, per_channel=True, out_scale=0.3, act=0, out_zp=128), "hbm"),
         "mnv2_project_256x112x112x32to16": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=112, w=112, cin=32, cout=16, k=1, per_channel=True, out_scale=0.3, act=0, out_zp=128), "hbm"),
         "mnv2_stem_256x224x224x3to32": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=224, w=224, cin=3, cout=32, k=3, stride=2, per_channel=True, out_scale=0.0235, out_zp=0), "hbm"),
