@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantized operator hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--lanes S]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME] [--lanes S] [--grid-cap G]
 
 One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of seeded synthetic input.
 The default workload is the whole MobileNetV2-1.0 224x224 uint8 graph on ONE batch of 256 images: at N GPUs
@@ -13,8 +13,10 @@ report HBM GB/s or int8 TOPS of that operator.
 `value` is measured with inputs resident in HBM (CUDA events on the library's streams); `e2e` is the same metric
 through the operator-list C ABI with HOST buffers: host->device copy of every step's images, the graph, the
 device->host copy of the logits and, at N > 1, the gather of all ranks' logits on rank 0 inside the timed region.
-A rank may run several operator lists ("lanes", each with its own stream, buffers and CUDA graph) and hand
-successive steps to them in turn, so that the kernels of neighbouring steps fill SMs a small slice leaves idle.
+A rank runs several operator lists ("lanes", each with its own stream, buffers and CUDA graph) and hands
+successive steps to them in turn; the persistent kernels of a lane launch on a share of the SMs (context option
+grid_cap, a quarter of the GPU by default), so that kernels of four different steps run side by side and the latency
+of the small layers is hidden (--lanes 3 --grid-cap 0 gives whole-GPU kernels that only overlap at their tails).
 `--impl reference` times the CPU oracle (the reference has no CPU implementation of these operators and its OpenCL
 path cannot run on this machine) on a bounded sample of the same workload, with all host threads.
 """
@@ -410,9 +412,14 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
     out_bytes = per_rank * classes
     multi = world > 1
 
-    # ---- lanes: how many operator lists share this GPU.  "auto" times 1, 2 and 3 on a few steps and keeps the best. ----
-    max_lanes = args.lanes if args.lanes > 0 else 3
-    options = [(kv.split("=")[0], int(kv.split("=")[1])) for kv in args.opt]
+    # ---- lanes: how many operator lists share this GPU, and the share of its SMs each list's kernels may take.
+    # Default: eight lists whose persistent kernels launch at most a quarter of the SMs (option grid_cap), so that four
+    # kernels of different steps run side by side; "auto" times four and eight lists on a few steps and keeps the best.
+    max_lanes = args.lanes if args.lanes > 0 else 8
+    sm_count = torch.cuda.get_device_properties(local).multi_processor_count
+    grid_cap = args.grid_cap if args.grid_cap >= 0 else (sm_count // 4 if max_lanes >= 4 else 0)
+    user_options = [(kv.split("=")[0], int(kv.split("=")[1])) for kv in args.opt]
+    options = user_options + ([("grid_cap", grid_cap)] if grid_cap > 0 else [])
     lanes = [Lane(enn, mn, local, layers, per_rank, x, out_bytes, options) for _ in range(max_lanes)]
     info = lanes[0].info
     stats = lanes[0].ol.stats()
@@ -442,7 +449,7 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
         lane_trials = None
     else:
         lane_trials = {}
-        for s in range(1, max_lanes + 1):
+        for s in (max_lanes // 2, max_lanes):
             device_steps(s, 2 * s)
             lane_trials[s] = device_steps(s, 6 * s) / (6 * s)
         if multi:      # every rank must make the same choice: take rank 0's
@@ -470,16 +477,35 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
             gath = [torch.empty((world, out_bytes), dtype=torch.uint8, device="cuda") for _ in range(use)]
             gath_host = [torch.empty((world, out_bytes), dtype=torch.uint8).pin_memory() for _ in range(use)]
 
+    # Lanes that share the GPU by SM shares are submitted in rounds (enn_b200_oplist_submit_round): the lanes of a round
+    # fill the GPU together and start together, the next round's inputs travel meanwhile.
+    # The end-to-end leg runs on the lanes of one round only: more lanes put two rounds in flight at once, which gains
+    # 1 % on long runs and loses 10 % on a 20-step run that starts from an empty pipeline.
+    round_size = max(1, min(use, sm_count // grid_cap)) if grid_cap > 0 else 1
+    use_dev = use
+    if grid_cap > 0:
+        use = round_size
+
     def e2e_steps(steps):
-        for i in range(steps):
-            k = i % use
-            lanes[k].submit()
-            if multi:
-                with torch.cuda.stream(ext[k]):
-                    src = torch.as_tensor(DevView(lanes[k].ol.last_output_ptr(0).value, out_bytes), device="cuda")
-                    dist.gather(src, list(gath[k].unbind(0)) if rank == 0 else None, dst=0)
-                    if rank == 0:
-                        gath_host[k].copy_(gath[k], non_blocking=True)
+        i = 0
+        while i < steps:
+            first = i % use
+            ks = [(first + j) % use for j in range(min(round_size, steps - i))]
+            if len(ks) == 1:
+                lanes[ks[0]].submit()
+            else:
+                bufs = [lanes[k].host[lanes[k].n & 1] for k in ks]
+                enn.OpList.submit_round([lanes[k].ol for k in ks], [[b[0]] for b in bufs], [[b[1]] for b in bufs])
+                for k in ks:
+                    lanes[k].n += 1
+            for k in ks:
+                if multi:
+                    with torch.cuda.stream(ext[k]):
+                        src = torch.as_tensor(DevView(lanes[k].ol.last_output_ptr(0).value, out_bytes), device="cuda")
+                        dist.gather(src, list(gath[k].unbind(0)) if rank == 0 else None, dst=0)
+                        if rank == 0:
+                            gath_host[k].copy_(gath[k], non_blocking=True)
+            i += len(ks)
         for l in lanes[:use]:
             l.ol.wait()
 
@@ -500,9 +526,13 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
     gathered = gath_host[0].numpy().reshape(GLOBAL_BATCH, classes).copy() if multi and rank == 0 else None
 
     # ---- per-layer timing (rank 0): which kernel dominates, and its achieved bandwidth ----
+    # The layers are timed one at a time with the whole GPU to themselves (a context without the SM share): inside the
+    # timed region a kernel shares the GPU with the kernels of other steps, where a single launch cannot be timed.
     per_kernel = {}
     if rank == 0:
-        ctx, ol = lanes[0].ctx, lanes[0].ol
+        ctx, ol = enn.Context(local), lanes[0].ol
+        for name, value in user_options:
+            ctx.set_option(name, value)
         tid = info["tensor_ids"]
         # eager per-layer timing uses fresh operator handles on the list's buffers (graph nodes are owned by the list)
         for L, pl in zip(layers, info["per_layer"]):
@@ -539,7 +569,7 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
     ol_info = dict(macs=info["macs"], bytes=info["bytes"], launches=info["launches"], stats=stats, layers=len(layers))
     return dict(total_ms=total_ms, e2e_ms=e2e_ms, clocks=clocks, per_rank=per_rank, h2d=int(x.nbytes), d2h=int(out_bytes),
                 per_kernel=per_kernel, info=ol_info, logits=logits, gathered=gathered, layers=layers, x=x, x_full=x_full,
-                lanes=use, lane_trials=lane_trials, mn=mn, lane_objs=lanes)
+                lanes=use_dev, lane_trials=lane_trials, mn=mn, lane_objs=lanes, grid_cap=grid_cap, round_size=round_size, e2e_lanes=use)
 
 
 def cpu_baseline_mobilenet(layers, x, max_images=8):
@@ -622,6 +652,12 @@ def run_ours(args):
                         "peak_source": peaks["source"],
                         "avg_launch_ms": avg_ms, "launches_per_step": launches,
                         "share_of_step": pk[dom]["ms"] / sum(v["ms"] for v in pk.values()),
+                        "timed": "every layer launched alone with all SMs, CUDA events, 5 launches each; in the timed region the "
+                                 "lanes' kernels run side by side on shares of the SMs, see whole_step",
+                        "whole_step": {"algorithmic_gbytes": r["info"]["bytes"] * world / 1e9,
+                                       "achieved": r["info"]["bytes"] * world / (total_ms / args.steps * 1e-3) / 1e9 / world,
+                                       "unit": "GB/s per GPU",
+                                       "frac": r["info"]["bytes"] / (total_ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"]},
                         "per_kernel_ms": {k: round(v["ms"], 4) for k, v in pk.items()},
                         "per_kernel_frac_of_hbm": {k: round(v["bytes"] / (v["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 3) for k, v in pk.items()}}
             result = {
@@ -637,6 +673,9 @@ def run_ours(args):
                 "logits_checksum": int(r["logits"].astype(np.int64).sum()),
             }
             result["lanes_per_gpu"] = r["lanes"]
+            result["sm_share_per_lane"] = r["grid_cap"] if r["grid_cap"] > 0 else "all"
+            result["e2e"]["lanes"] = r["e2e_lanes"]
+            result["e2e"]["lanes_per_round"] = r["round_size"]
             result["device_bytes_per_lane"] = r["info"]["stats"]["device_bytes"]
             if r["lane_trials"]:
                 result["lane_trial_ms_per_step"] = {str(k): round(v, 4) for k, v in r["lane_trials"].items()}
@@ -810,7 +849,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
-    ap.add_argument("--lanes", type=int, default=0, help="operator lists per GPU that take the steps in turn (0: time 1..3 and keep the best)")
+    ap.add_argument("--lanes", type=int, default=0, help="operator lists per GPU that take the steps in turn (0: time 4 and 8 and keep the best)")
+    ap.add_argument("--grid-cap", type=int, default=-1, help="SMs a lane's persistent kernels may occupy (-1: a quarter of the GPU with four or more lanes; 0: all)")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE", help="library option for every context (tuning runs), e.g. no_fuse=1")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU leg (profiling runs)")
     ap.add_argument("--skip-per-op", action="store_true", help="omit the single-operator table (profiling runs)")

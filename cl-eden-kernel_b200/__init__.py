@@ -67,6 +67,7 @@ PROTOTYPES = {
     "enn_b200_oplist_execute": (C.c_int32, [_P, C.POINTER(_P), C.POINTER(_P)]),
     "enn_b200_oplist_execute_device": (C.c_int32, [_P]),
     "enn_b200_oplist_submit": (C.c_int32, [_P, C.POINTER(_P), C.POINTER(_P)]),
+    "enn_b200_oplist_submit_round": (C.c_int32, [C.POINTER(_P), C.c_int32, C.POINTER(C.POINTER(_P)), C.POINTER(C.POINTER(_P))]),
     "enn_b200_oplist_wait": (C.c_int32, [_P]),
     "enn_b200_oplist_tensor_ptr": (C.c_int32, [_P, C.c_int32, C.POINTER(_P)]),
     "enn_b200_oplist_last_output_ptr": (C.c_int32, [_P, C.c_int32, C.POINTER(_P)]),
@@ -382,6 +383,18 @@ class OpList:
         a = (C.c_void_p * len(in_ptrs))(*in_ptrs)
         b = (C.c_void_p * len(out_ptrs))(*out_ptrs)
         self.ctx.check(lib.enn_b200_oplist_submit(self.h, a, b))
+
+    @staticmethod
+    def submit_round(lists, in_ptrs, out_ptrs):
+        """One pipelined submission on every list of `lists` (same device), started together; in_ptrs[k] / out_ptrs[k]
+        are the host pointer lists of lists[k]."""
+        n = len(lists)
+        hs = (C.c_void_p * n)(*[l.h for l in lists])
+        ins = [(C.c_void_p * len(p))(*p) for p in in_ptrs]
+        outs = [(C.c_void_p * len(p))(*p) for p in out_ptrs]
+        pin = (C.POINTER(C.c_void_p) * n)(*[C.cast(a, C.POINTER(C.c_void_p)) for a in ins])
+        pout = (C.POINTER(C.c_void_p) * n)(*[C.cast(a, C.POINTER(C.c_void_p)) for a in outs])
+        lists[0].ctx.check(lib.enn_b200_oplist_submit_round(hs, n, pin, pout))
 
     def wait(self):
         self.ctx.check(lib.enn_b200_oplist_wait(self.h))

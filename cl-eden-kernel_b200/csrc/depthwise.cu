@@ -716,7 +716,7 @@ bool dw_ring_plan(enn_b200_op *op) {
     p.in_zp = g.in_zp; p.w_zp = g.w_zp; p.act_min = g.act_min; p.act_max = g.act_max;
     // One wave of CTAs, each with at least a few output rows so that the two halo rows stay cheap.
     const int64_t units = static_cast<int64_t>(g.n) * g.oh;
-    int per_tx = (per_sm * ctx->sm_count) / tx_n;
+    int per_tx = (per_sm * ctx->launch_sms()) / tx_n;
     if (per_tx < 1) per_tx = 1;
     const int64_t min_rows = 6;
     if (per_tx > (units + min_rows - 1) / min_rows) per_tx = static_cast<int>((units + min_rows - 1) / min_rows);

@@ -1688,7 +1688,7 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     p.tiles_m = (M + kBM - 1) / kBM;
     // N tiling: as few tiles as possible, but split further while the grid would leave SMs idle.
     int32_t tiles_n = (N + max_data - 1) / max_data;
-    while (static_cast<int64_t>(p.tiles_m) * tiles_n < ctx->sm_count && (N + tiles_n) / (tiles_n + 1) >= 32) ++tiles_n;
+    while (static_cast<int64_t>(p.tiles_m) * tiles_n < ctx->launch_sms() && (N + tiles_n) / (tiles_n + 1) >= 32) ++tiles_n;
     int32_t bn_data = (((N + tiles_n - 1) / tiles_n) + 15) & ~15;
     tiles_n = (N + bn_data - 1) / bn_data;
     if (static_cast<int64_t>(p.tiles_m) * tiles_n > ctx->sm_count && bn_data >= 128) {
@@ -1860,8 +1860,8 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     p.stages = stages;
     gm->smem_bytes = stages * stage_bytes + fixed + resident;
     const int total_tiles = p.tiles_mg * p.tiles_n;
-    gm->grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
-    if (p.two) gm->grid = 2 * (total_tiles < ctx->sm_count / 2 ? total_tiles : ctx->sm_count / 2);
+    gm->grid = total_tiles < ctx->launch_sms() ? total_tiles : ctx->launch_sms();
+    if (p.two) gm->grid = 2 * (total_tiles < ctx->launch_sms() / 2 ? total_tiles : ctx->launch_sms() / 2);
     // One thread cannot issue both operands of every k-block fast enough for a long MMA-bound k loop; short, epilogue-
     // bound problems are better off without the extra warp.
     gm->threads = (p.kpack == 1 && p.k_blocks >= 8) ? kThreads : kThreadsOneProducer;
@@ -2214,7 +2214,7 @@ int32_t tc_plan_conv(enn_b200_op *op, const void *w_hwio) {
         for (auto &gm : plan->gemms) all_implicit = all_implicit && gm.implicit;
         if (ncls > 1 && ncls <= enn_b200_context::kAuxStreams + 1 && all_implicit && !ctx->opt("no_fan_out")) {
             plan->fan_out = true;
-            const int share = ctx->sm_count / ncls > 0 ? ctx->sm_count / ncls : 1;
+            const int share = ctx->launch_sms() / ncls > 0 ? ctx->launch_sms() / ncls : 1;
             for (auto &gm : plan->gemms)
                 if (gm.grid > share) gm.grid = share;
         }

@@ -33,6 +33,12 @@ struct enn_b200_context {
         auto it = options.find(name);
         return it == options.end() ? dflt : it->second;
     }
+    // SMs one launch of a persistent kernel may occupy: option grid_cap (several operator lists that share the GPU each
+    // take a share of it, so that their kernels run side by side instead of one after another), else all of them.
+    int launch_sms() const {
+        const int cap = opt("grid_cap");
+        return cap > 0 && cap < sm_count ? cap : sm_count;
+    }
 };
 
 namespace enn_b200 {

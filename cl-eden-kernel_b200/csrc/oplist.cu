@@ -44,7 +44,8 @@ struct enn_b200_oplist {
     cudaGraph_t graph_alt = nullptr;
     cudaGraphExec_t exec_alt = nullptr;
     cudaStream_t copy_stream = nullptr;
-    cudaEvent_t ev_in_ready[2] = {nullptr, nullptr}, ev_slot_free[2] = {nullptr, nullptr};
+    cudaStream_t out_stream = nullptr;      // device-to-host copies of the results: the operators' stream never waits for a copy engine
+    cudaEvent_t ev_in_ready[2] = {nullptr, nullptr}, ev_slot_free[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr};
     bool slot_used[2] = {false, false};
     uint64_t seq = 0;
     bool finalized = false;
@@ -273,8 +274,11 @@ int32_t enn_b200_oplist_finalize(enn_b200_oplist *l) {
         if (e != cudaSuccess || !l->graph_alt) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: stream capture failed");
         if (cudaGraphInstantiate(&l->exec_alt, l->graph_alt, 0) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: graph instantiation failed");
         if (cudaStreamCreateWithFlags(&l->copy_stream, cudaStreamNonBlocking) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: copy stream creation failed");
+        if (!ctx->opt("no_out_stream") && cudaStreamCreateWithFlags(&l->out_stream, cudaStreamNonBlocking) != cudaSuccess)
+            return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: output stream creation failed");
         for (int i = 0; i < 2; ++i)
             if (cudaEventCreateWithFlags(&l->ev_in_ready[i], cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&l->ev_done[i], cudaEventDisableTiming) != cudaSuccess ||
                 cudaEventCreateWithFlags(&l->ev_slot_free[i], cudaEventDisableTiming) != cudaSuccess)
                 return lfail(l, ENN_B200_CUDA_FAILURE, "oplist: event creation failed");
     }
@@ -315,12 +319,10 @@ int32_t enn_b200_oplist_execute(enn_b200_oplist *l, const void *const *host_inpu
 // on a copy stream and overlaps the operators of the previous one (two device copies of every graph input / output
 // alternate); results are valid in host_outputs after enn_b200_oplist_wait.  Host buffers must stay alive and untouched
 // until then and should be pinned.
-int32_t enn_b200_oplist_submit(enn_b200_oplist *l, const void *const *host_inputs, void *const *host_outputs) {
-    if (!l || !l->finalized) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist not finalized");
-    if ((!l->inputs.empty() && !host_inputs) || (!l->outputs.empty() && !host_outputs)) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_submit: null buffer table");
-    if (!l->exec || !l->exec_alt) return enn_b200_oplist_execute(l, host_inputs, host_outputs);
-    const int slot = static_cast<int>(l->seq & 1);
-    cudaStream_t cs = l->copy_stream, s = l->ctx->stream;
+namespace {
+// First half of a pipelined submission: this step's inputs travel to the free buffer set on the list's copy stream.
+int32_t submit_inputs(enn_b200_oplist *l, const void *const *host_inputs, int slot) {
+    cudaStream_t cs = l->copy_stream;
     // the previous user of this buffer set must have finished reading its inputs and copying out its outputs
     if (l->slot_used[slot] && cudaStreamWaitEvent(cs, l->ev_slot_free[slot], 0) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: event wait failed");
     for (size_t i = 0; i < l->inputs.size(); ++i) {
@@ -330,19 +332,77 @@ int32_t enn_b200_oplist_submit(enn_b200_oplist *l, const void *const *host_input
         if (T.bytes && cudaMemcpyAsync(dst, host_inputs[i], static_cast<size_t>(T.bytes), cudaMemcpyHostToDevice, cs) != cudaSuccess)
             return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: input copy failed");
     }
-    if (cudaEventRecord(l->ev_in_ready[slot], cs) != cudaSuccess || cudaStreamWaitEvent(s, l->ev_in_ready[slot], 0) != cudaSuccess)
-        return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: event hand-over failed");
+    if (cudaEventRecord(l->ev_in_ready[slot], cs) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: event record failed");
+    return ENN_B200_SUCCESS;
+}
+// Second half: the graph on the list's stream once its inputs (and those of `others`, the lists of the same round)
+// have landed, then the results on the output stream.
+int32_t submit_run(enn_b200_oplist *l, void *const *host_outputs, int slot, enn_b200_oplist *const *others, int32_t n_others) {
+    cudaStream_t s = l->ctx->stream;
+    if (cudaStreamWaitEvent(s, l->ev_in_ready[slot], 0) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: event hand-over failed");
+    for (int32_t j = 0; j < n_others; ++j)
+        if (others[j] != l && cudaStreamWaitEvent(s, others[j]->ev_in_ready[others[j]->seq & 1], 0) != cudaSuccess)
+            return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: event hand-over failed");
     if (cudaGraphLaunch(slot ? l->exec_alt : l->exec, s) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: graph launch failed");
+    // The results leave on a stream of their own: the next graph of this list starts when this one ends, not when the
+    // copy engine (busy with the other lists' inputs) has served the result copy.
+    cudaStream_t os = l->out_stream ? l->out_stream : s;
+    if (os != s && (cudaEventRecord(l->ev_done[slot], s) != cudaSuccess || cudaStreamWaitEvent(os, l->ev_done[slot], 0) != cudaSuccess))
+        return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: event hand-over failed");
     for (size_t i = 0; i < l->outputs.size(); ++i) {
         auto &T = l->tensors[l->outputs[i]];
         if (!host_outputs[i]) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_submit: null output buffer");
         const void *src = slot ? T.dev_alt : T.dev;
-        if (T.bytes && cudaMemcpyAsync(host_outputs[i], src, static_cast<size_t>(T.bytes), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+        if (T.bytes && cudaMemcpyAsync(host_outputs[i], src, static_cast<size_t>(T.bytes), cudaMemcpyDeviceToHost, os) != cudaSuccess)
             return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: output copy failed");
     }
-    if (cudaEventRecord(l->ev_slot_free[slot], s) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: event record failed");
+    if (cudaEventRecord(l->ev_slot_free[slot], os) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_submit: event record failed");
+    return ENN_B200_SUCCESS;
+}
+}  // namespace
+
+int32_t enn_b200_oplist_submit(enn_b200_oplist *l, const void *const *host_inputs, void *const *host_outputs) {
+    if (!l || !l->finalized) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist not finalized");
+    if ((!l->inputs.empty() && !host_inputs) || (!l->outputs.empty() && !host_outputs)) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_submit: null buffer table");
+    if (!l->exec || !l->exec_alt) return enn_b200_oplist_execute(l, host_inputs, host_outputs);
+    const int slot = static_cast<int>(l->seq & 1);
+    int32_t st = submit_inputs(l, host_inputs, slot);
+    if (st == ENN_B200_SUCCESS) st = submit_run(l, host_outputs, slot, nullptr, 0);
+    if (st != ENN_B200_SUCCESS) return st;
     l->slot_used[slot] = true;
     ++l->seq;
+    return ENN_B200_SUCCESS;
+}
+
+// One step on each of `n` lists of the same device whose operators start together: every list's inputs are copied
+// first, and every list's graph waits for all of them.  Lists that share a GPU (each prepared with option grid_cap, so
+// that their kernels fit side by side) run fastest when they execute the same layer at the same time: kernels of
+// one kind fill every SM, while a mix of kinds leaves SMs that hold a small CTA closed to a large one.
+// host_inputs[k] / host_outputs[k] are the buffer tables of lists[k], as for enn_b200_oplist_submit.
+int32_t enn_b200_oplist_submit_round(enn_b200_oplist *const *lists, int32_t n, const void *const *const *host_inputs,
+                                     void *const *const *host_outputs) {
+    if (!lists || n < 1 || n > 64 || !host_inputs || !host_outputs) return ENN_B200_INVALID_PARAMS;
+    for (int32_t k = 0; k < n; ++k) {
+        enn_b200_oplist *l = lists[k];
+        if (!l || !l->finalized) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist not finalized");
+        if (!l->exec || !l->exec_alt) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_submit_round: a list without operators");
+        if ((!l->inputs.empty() && !host_inputs[k]) || (!l->outputs.empty() && !host_outputs[k])) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_submit_round: null buffer table");
+        if (l->ctx->device != lists[0]->ctx->device) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_submit_round: lists of different devices");
+        for (int32_t j = 0; j < k; ++j)
+            if (lists[j] == l) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist_submit_round: a list named twice");
+    }
+    for (int32_t k = 0; k < n; ++k) {
+        const int32_t st = submit_inputs(lists[k], host_inputs[k], static_cast<int>(lists[k]->seq & 1));
+        if (st != ENN_B200_SUCCESS) return st;
+    }
+    for (int32_t k = 0; k < n; ++k) {
+        const int32_t st = submit_run(lists[k], host_outputs[k], static_cast<int>(lists[k]->seq & 1), lists, n);
+        if (st != ENN_B200_SUCCESS) return st;
+    }
+    for (int32_t k = 0; k < n; ++k) {
+        lists[k]->slot_used[lists[k]->seq & 1] = true;
+        ++lists[k]->seq;
+    }
     return ENN_B200_SUCCESS;
 }
 
@@ -350,6 +410,7 @@ int32_t enn_b200_oplist_wait(enn_b200_oplist *l) {
     if (!l || !l->finalized) return lfail(l, ENN_B200_INVALID_PARAMS, "oplist not finalized");
     if (l->copy_stream && cudaStreamSynchronize(l->copy_stream) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_wait: copy stream failed");
     if (cudaStreamSynchronize(l->ctx->stream) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_wait: stream synchronisation failed");
+    if (l->out_stream && cudaStreamSynchronize(l->out_stream) != cudaSuccess) return lfail(l, ENN_B200_CUDA_FAILURE, "oplist_wait: output stream failed");
     return ENN_B200_SUCCESS;
 }
 
@@ -438,7 +499,12 @@ int32_t enn_b200_oplist_destroy(enn_b200_oplist *l) {
         cudaStreamSynchronize(l->copy_stream);
         cudaStreamDestroy(l->copy_stream);
     }
+    if (l->out_stream) {
+        cudaStreamSynchronize(l->out_stream);
+        cudaStreamDestroy(l->out_stream);
+    }
     for (int i = 0; i < 2; ++i) {
+        if (l->ev_done[i]) cudaEventDestroy(l->ev_done[i]);
         if (l->ev_in_ready[i]) cudaEventDestroy(l->ev_in_ready[i]);
         if (l->ev_slot_free[i]) cudaEventDestroy(l->ev_slot_free[i]);
     }

@@ -872,6 +872,79 @@ def test_oplist_pipelined_submit(enn, ctx):
         ol.destroy()
 
 
+def test_oplist_submit_round_and_sm_share(enn, orc):
+    """Three operator lists in their own contexts, each limited to a share of the SMs (option grid_cap), fed in rounds
+    (enn_b200_oplist_submit_round: all inputs first, then the graphs together): every result equals the oracle, the
+    same lists through plain submit give the same bytes, and a bad round is refused."""
+    import importlib
+    import mobilenet_ref
+    mn = importlib.import_module("cl_eden_kernel_b200.mobilenet")
+    layers, _ = mn.build_model(seed=8, calib_images=1, resolution=64, num_classes=40)
+    rng = np.random.default_rng(13)
+    n_lists, rounds, batch = 3, 4, 2
+    xs = [[rng.integers(0, 256, (batch, 64, 64, 3), dtype=np.int64).astype(np.uint8) for _ in range(n_lists)] for _ in range(rounds)]
+    want = [[mobilenet_ref.run_oracle(layers, x).reshape(-1) for x in row] for row in xs]
+    ctxs = [enn.Context(0) for _ in range(n_lists)]
+    for c in ctxs:
+        c.set_option("grid_cap", 5)
+    lists = [mn.make_oplist(enn, c, layers, batch=batch, resolution=64)[0] for c in ctxs]
+    try:
+        outs = [[np.zeros(batch * 40, np.uint8) for _ in range(n_lists)] for _ in range(rounds)]
+        for r in range(rounds):
+            k = n_lists if r != 2 else 2                # one round with fewer lists than the others
+            enn.OpList.submit_round(lists[:k], [[x.ctypes.data] for x in xs[r][:k]], [[o.ctypes.data] for o in outs[r][:k]])
+            for l, x, o in zip(lists[k:], xs[r][k:], outs[r][k:]):
+                l.submit_host_ptrs([x.ctypes.data], [o.ctypes.data])
+        for l in lists:
+            l.wait()
+        for r in range(rounds):
+            for o, w in zip(outs[r], want[r]):
+                assert np.array_equal(o, w)
+        # refusals: the same list twice, an empty round
+        import ctypes as C
+        hs = (C.c_void_p * 2)(lists[0].h, lists[0].h)
+        buf = (C.c_void_p * 1)(xs[0][0].ctypes.data)
+        tab = (C.POINTER(C.c_void_p) * 2)(C.cast(buf, C.POINTER(C.c_void_p)), C.cast(buf, C.POINTER(C.c_void_p)))
+        assert enn.lib.enn_b200_oplist_submit_round(hs, 2, tab, tab) == enn.INVALID_PARAMS
+        assert enn.lib.enn_b200_oplist_submit_round(hs, 0, tab, tab) == enn.INVALID_PARAMS
+    finally:
+        for l in lists:
+            l.destroy()
+        for c in ctxs:
+            c.close()
+
+
+GRID_CAP_CASES = {
+    "conv1x1_pack": lambda: ("conv", cases.conv_case(seed=61, n=4, h=28, w=28, cin=32, cout=192, k=1, per_channel=True, act=cases.enn.ACT_RELU6)),
+    "conv3x3_tapbox": lambda: ("conv", cases.conv_case(seed=62, n=3, h=20, w=20, cin=64, cout=64, k=3, per_channel=True)),
+    "conv1x1_wide_n": lambda: ("conv", cases.conv_case(seed=63, n=2, h=14, w=14, cin=96, cout=576, k=1, per_channel=True)),
+    "dw_s1": lambda: ("dw", cases.depthwise_case(seed=64, n=3, h=28, w=28, c=96, stride=1)),
+    "dw_s2": lambda: ("dw", cases.depthwise_case(seed=65, n=3, h=28, w=28, c=64, stride=2)),
+    "deconv": lambda: ("deconv", cases.deconv_case(seed=66, n=2, h=12, w=12, cin=32, cout=16)),
+}
+
+
+@pytest.mark.parametrize("name", sorted(GRID_CAP_CASES))
+@pytest.mark.parametrize("cap", [1, 7])
+def test_grid_cap_keeps_results(enn, orc, name, cap):
+    """Option grid_cap (at most that many CTAs per persistent kernel): bit-exact with the oracle whatever the share."""
+    kind, (d, x, w, b, s) = GRID_CAP_CASES[name]()
+    c = enn.Context(0)
+    try:
+        c.set_option("grid_cap", cap)
+        if kind == "conv":
+            op, ref = enn.conv2d(c, d, w, b, s), orc.conv2d(d, x, w, b, s)
+        elif kind == "dw":
+            op, ref = enn.depthwise(c, d, w, b, s), orc.depthwise(d, x, w, b, s)
+        else:
+            op, ref = enn.deconv(c, d, w, b, s), orc.deconv(d, x, w, b, s)
+        y = op.run(x)
+        assert np.array_equal(y.reshape(ref.shape), ref)
+        op.release()
+    finally:
+        c.close()
+
+
 def test_oplist_group_splits_one_batch(enn, orc):
     """enn_b200_group_*: one host batch in, one host buffer out, over three operator lists with slices of 3 + 2 + 1
     images (their own contexts; on a one-GPU machine all on device 0): blocking and pipelined calls equal the oracle on
