@@ -449,9 +449,9 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
         lane_trials = None
     else:
         lane_trials = {}
-        for s in (max_lanes // 2, max_lanes):
+        for s in (max_lanes // 2, max_lanes):      # on the step count that will be timed: K need not divide by the lanes
             device_steps(s, 2 * s)
-            lane_trials[s] = device_steps(s, 6 * s) / (6 * s)
+            lane_trials[s] = device_steps(s, args.steps) / args.steps
         if multi:      # every rank must make the same choice: take rank 0's
             t = torch.tensor([lane_trials[s] for s in sorted(lane_trials)], device="cuda", dtype=torch.float64)
             dist.broadcast(t, 0)
