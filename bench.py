@@ -470,12 +470,13 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
     # Every step copies its images host->device and its logits device->host (the copy-in of a step overlaps the
     # operators of the step before); at N > 1 every step's logits also travel to rank 0 (NCCL gather of the device
     # copy, ordered on the lane's stream, then device->host there).  The region ends when the last result has landed.
-    ext, src_views, gath, gath_host = None, None, None, None
+    ext, src_views, gath, gath_host, gath_rows = None, {}, None, None, None
     if multi:
         ext = [torch.cuda.ExternalStream(l.ctx.stream.value if hasattr(l.ctx.stream, "value") else int(l.ctx.stream)) for l in lanes[:use]]
         if rank == 0:
             gath = [torch.empty((world, out_bytes), dtype=torch.uint8, device="cuda") for _ in range(use)]
             gath_host = [torch.empty((world, out_bytes), dtype=torch.uint8).pin_memory() for _ in range(use)]
+            gath_rows = [list(g.unbind(0)) for g in gath]
 
     # Lanes that share the GPU by SM shares are submitted in rounds (enn_b200_oplist_submit_round): the lanes of a round
     # fill the GPU together and start together, the next round's inputs travel meanwhile.
@@ -500,9 +501,12 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
                     lanes[k].n += 1
             for k in ks:
                 if multi:
+                    ptr = lanes[k].ol.last_output_ptr(0).value
+                    src = src_views.get(ptr)        # a list alternates between two output buffers: wrap each once
+                    if src is None:
+                        src = src_views[ptr] = torch.as_tensor(DevView(ptr, out_bytes), device="cuda")
                     with torch.cuda.stream(ext[k]):
-                        src = torch.as_tensor(DevView(lanes[k].ol.last_output_ptr(0).value, out_bytes), device="cuda")
-                        dist.gather(src, list(gath[k].unbind(0)) if rank == 0 else None, dst=0)
+                        dist.gather(src, gath_rows[k] if rank == 0 else None, dst=0)
                         if rank == 0:
                             gath_host[k].copy_(gath[k], non_blocking=True)
             i += len(ks)
@@ -526,46 +530,82 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
     gathered = gath_host[0].numpy().reshape(GLOBAL_BATCH, classes).copy() if multi and rank == 0 else None
 
     # ---- per-layer timing (rank 0): which kernel dominates, and its achieved bandwidth ----
-    # The layers are timed one at a time with the whole GPU to themselves (a context without the SM share): inside the
-    # timed region a kernel shares the GPU with the kernels of other steps, where a single launch cannot be timed.
+    # Two timings per layer: launched on every lane at once (the regime of the timed region: each launch on its share
+    # of the SMs, four side by side; a single launch cannot be timed there, the elapsed time over the launches can),
+    # and one launch at a time with the whole GPU (a context without the share).
     per_kernel = {}
     if rank == 0:
-        ctx, ol = enn.Context(local), lanes[0].ol
+        alone = enn.Context(local)
         for name, value in user_options:
-            ctx.set_option(name, value)
-        tid = info["tensor_ids"]
-        # eager per-layer timing uses fresh operator handles on the list's buffers (graph nodes are owned by the list)
+            alone.set_option(name, value)
+        shared = lanes[:use_dev] if grid_cap > 0 and use_dev > 1 else []
+
+        def make_op(ctx, L, d):
+            if L["kind"] == "conv":
+                return enn.conv2d(ctx, d, L["w"], L["bias"], L["scales"])
+            if L["kind"] == "dw":
+                return enn.depthwise(ctx, d, L["w"], L["bias"], L["scales"])
+            if L["kind"] == "fc":
+                return enn.fully_connected(ctx, d, L["w"].reshape(L["cout"], L["cin"]), L["bias"], L["scales"])
+            if L["kind"] == "add":
+                return enn.add(ctx, d)
+            return enn.avgpool(ctx, d)
+
+        def runner(op, lane, L):
+            # fresh operator handles on a list's own buffers (graph nodes are owned by the list)
+            tid, ol = lane.info["tensor_ids"], lane.ol
+            a, o = ol.tensor_ptr(tid[L["src"]]), ol.tensor_ptr(tid[L["name"]])
+            if L["kind"] == "add":
+                b2 = ol.tensor_ptr(tid[L["src2"]])
+                return lambda: op.execute2(a, b2, o)
+            return lambda: op.execute(a, o)
+
         for L, pl in zip(layers, info["per_layer"]):
             d = mn.layer_descs(enn, L, per_rank)
-            if L["kind"] == "conv":
-                op = enn.conv2d(ctx, d, L["w"], L["bias"], L["scales"])
-            elif L["kind"] == "dw":
-                op = enn.depthwise(ctx, d, L["w"], L["bias"], L["scales"])
-            elif L["kind"] == "fc":
-                op = enn.fully_connected(ctx, d, L["w"].reshape(L["cout"], L["cin"]), L["bias"], L["scales"])
-            elif L["kind"] == "add":
-                op = enn.add(ctx, d)
-            else:
-                op = enn.avgpool(ctx, d)
-            a = ol.tensor_ptr(tid[L["src"]])
-            o = ol.tensor_ptr(tid[L["name"]])
-            b2 = ol.tensor_ptr(tid[L["src2"]]) if L["kind"] == "add" else None
-            run = (lambda: op.execute2(a, b2, o)) if b2 is not None else (lambda: op.execute(a, o))
+            # (1) alone: the whole GPU to one launch at a time
+            op = make_op(alone, L, d)
+            run = runner(op, lanes[0], L)
             run()
             ea, eb = cu.event(), cu.event()
-            cu.record(ea, ctx.stream)
+            cu.record(ea, alone.stream)
             for _ in range(5):
                 run()
-            cu.record(eb, ctx.stream)
-            ctx.sync()
-            ms = cu.elapsed_ms(ea, eb) / 5
+            cu.record(eb, alone.stream)
+            alone.sync()
+            ms_alone = cu.elapsed_ms(ea, eb) / 5
+            op.release()
+            # (2) as in the timed region: the same layer on every lane at once, each launch on its share of the SMs
+            ms_shared = None
+            if shared:
+                ops = [make_op(l.ctx, L, d) for l in shared]
+                runs = [runner(op_k, l, L) for op_k, l in zip(ops, shared)]
+                for r in runs:
+                    r()
+                for l in shared:
+                    l.ctx.sync()
+                ea, eb = cu.event(), cu.event()
+                tails = [cu.event() for _ in shared]
+                cu.record(ea, shared[0].ctx.stream)
+                for _ in range(5):
+                    for r in runs:
+                        r()
+                for k in range(1, len(shared)):
+                    cu.record(tails[k], shared[k].ctx.stream)
+                    cu.stream_wait(shared[0].ctx.stream, tails[k])
+                cu.record(eb, shared[0].ctx.stream)
+                for l in shared:
+                    l.ctx.sync()
+                ms_shared = cu.elapsed_ms(ea, eb) / (5 * len(shared))
+                for op_k in ops:
+                    op_k.release()
             k = kernel_of_layer(L, pl["impl"])
-            acc = per_kernel.setdefault(k, dict(ms=0.0, bytes=0, macs=0, launches=0))
-            acc["ms"] += ms
+            acc = per_kernel.setdefault(k, dict(ms=0.0, ms_alone=0.0, bytes=0, macs=0, launches=0))
+            acc["ms"] += ms_shared if ms_shared is not None else ms_alone
+            acc["ms_alone"] += ms_alone
             acc["bytes"] += pl["bytes"]
             acc["macs"] += pl["macs"]
             acc["launches"] += pl["launches"]
-            op.release()
+        alone.close()
     ol_info = dict(macs=info["macs"], bytes=info["bytes"], launches=info["launches"], stats=stats, layers=len(layers))
     return dict(total_ms=total_ms, e2e_ms=e2e_ms, clocks=clocks, per_rank=per_rank, h2d=int(x.nbytes), d2h=int(out_bytes),
                 per_kernel=per_kernel, info=ol_info, logits=logits, gathered=gathered, layers=layers, x=x, x_full=x_full,
@@ -652,8 +692,12 @@ def run_ours(args):
                         "peak_source": peaks["source"],
                         "avg_launch_ms": avg_ms, "launches_per_step": launches,
                         "share_of_step": pk[dom]["ms"] / sum(v["ms"] for v in pk.values()),
-                        "timed": "every layer launched alone with all SMs, CUDA events, 5 launches each; in the timed region the "
-                                 "lanes' kernels run side by side on shares of the SMs, see whole_step",
+                        "timed": ("every layer launched on all %d lanes at once, as in the timed region (each launch on its share of "
+                                  "%d SMs, four side by side), CUDA events around 5 such rounds; avg_launch_ms = elapsed / launches. "
+                                  "per_kernel_ms_alone: one launch at a time with all SMs" % (r["lanes"], r["grid_cap"]))
+                                 if r["grid_cap"] > 0 and r["lanes"] > 1 else "every layer launched alone, CUDA events, 5 launches each",
+                        "per_kernel_ms_alone": {k: round(v["ms_alone"], 4) for k, v in pk.items()},
+                        "per_kernel_frac_of_hbm_alone": {k: round(v["bytes"] / (v["ms_alone"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 3) for k, v in pk.items()},
                         "whole_step": {"algorithmic_gbytes": r["info"]["bytes"] * world / 1e9,
                                        "achieved": r["info"]["bytes"] * world / (total_ms / args.steps * 1e-3) / 1e9 / world,
                                        "unit": "GB/s per GPU",
