@@ -213,6 +213,10 @@ def op_configs(cases):
         # the MobileNetV2 layers that dominate the graph step, as stand-alone workloads for profiling
         "mnv2_expand_256x112x112x16to96": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=112, w=112, cin=16, cout=96, k=1, per_channel=True, out_scale=0.0235, out_zp=0), "hbm"),
         "mnv2_expand_256x56x56x24to144": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=56, w=56, cin=24, cout=144, k=1, per_channel=True, out_scale=0.0235, out_zp=0), "hbm"),
+        "mnv2_expand_256x28x28x32to192": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=28, w=28, cin=32, cout=192, k=1, per_channel=True, out_scale=0.0235, out_zp=0), "hbm"),
+        "mnv2_expand_256x14x14x64to384": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=14, w=14, cin=64, cout=384, k=1, per_channel=True, out_scale=0.0235, out_zp=0), "hbm"),
+        "mnv2_expand_256x14x14x96to576": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=14, w=14, cin=96, cout=576, k=1, per_channel=True, out_scale=0.0235, out_zp=0), "hbm"),
+        "mnv2_expand_256x7x7x160to960": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=7, w=7, cin=160, cout=960, k=1, per_channel=True, out_scale=0.0235, out_zp=0), "hbm"),
         "mnv2_project_256x56x56x144to24": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=56, w=56, cin=144, cout=24, k=1, per_channel=True, out_scale=0.3, act=0, out_zp=128), "hbm"),
         "mnv2_project_256x112x112x32to16": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=112, w=112, cin=32, cout=16, k=1, per_channel=True, out_scale=0.3, act=0, out_zp=128), "hbm"),
         "mnv2_stem_256x224x224x3to32": ("conv2d", lambda: cases.conv_case(seed=0, n=256, h=224, w=224, cin=3, cout=32, k=3, stride=2, per_channel=True, out_scale=0.0235, out_zp=0), "hbm"),

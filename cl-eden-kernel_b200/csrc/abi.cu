@@ -274,7 +274,7 @@ int32_t enn_b200_context_set_option(enn_b200_context *ctx, const char *name, int
     if (!ctx || !name) return ENN_B200_INVALID_PARAMS;
     static const char *const known[] = {"no_pdl", "no_relu_mode", "no_relu_hi", "no_relu_sat", "no_wide_store", "no_grouped_tc", "no_first_layer", "no_implicit", "no_gemv",
                                         "no_narrow_span", "no_pack", "pack_wide", "no_bres", "no_bres_k1", "no_fan_out", "tc_bn",
-                                        "tc_pair", "tc_raster", "epi_g", "dw_legacy", "no_fuse", "fuse_all", "dw_rows", "grid_cap", "no_out_stream"};
+                                        "tc_pair", "tc_raster", "epi_g", "dw_legacy", "no_fuse", "fuse_all", "dw_rows", "grid_cap", "no_out_stream", "no_narrow_n"};
     bool ok = false;
     for (const char *k : known) ok = ok || std::strcmp(k, name) == 0;
     if (!ok) return fail(ctx, ENN_B200_INVALID_PARAMS, std::string("unknown option: ") + name);

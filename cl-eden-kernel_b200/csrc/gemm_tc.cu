@@ -1686,6 +1686,14 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
     int32_t max_data = kMaxBN - extra;
     if (ctx->has_opt("tc_bn")) max_data = ctx->opt("tc_bn") >= 96 && ctx->opt("tc_bn") <= max_data ? (ctx->opt("tc_bn") & ~15) : max_data;   // tuning override, 96 columns at least
     p.tiles_m = (M + kBM - 1) / kBM;
+    // One k-block and many output channels (the MobileNetV2 expand layers): the layer's time is its epilogue's.  Tiles of
+    // at most 128 columns let two M tiles share an accumulator buffer and be requantised together, so that every load of
+    // a column's constants serves two outputs (28 x 28 x 32 -> 192 at 256 images: 24.2 -> 21.1 us; 14 x 14 x 96 -> 576:
+    // 21.7 -> 19.9 us; 56 x 56 x 24 -> 144 in its four-pixel packing, 576 columns: 73.8 -> 65.4 us; 384 and 960 columns:
+    // no change).  Not with the extra column of the activation sums, which would leave room for one M tile only.
+    if (!implicit_span && !ctx->has_opt("tc_bn") && !ctx->opt("no_narrow_n") && K <= static_cast<int32_t>(span) && N > 128 && extra == 0 &&
+        M > kGemvMaxM && max_data > 128)
+        max_data = 128;
     // N tiling: as few tiles as possible, but split further while the grid would leave SMs idle.
     int32_t tiles_n = (N + max_data - 1) / max_data;
     while (static_cast<int64_t>(p.tiles_m) * tiles_n < ctx->launch_sms() && (N + tiles_n) / (tiles_n + 1) >= 32) ++tiles_n;

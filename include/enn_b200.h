@@ -203,7 +203,7 @@ int32_t enn_b200_last_error(enn_b200_context *ctx, char *buf, size_t buf_len);
 void *enn_b200_stream(enn_b200_context *ctx);
 /* Planner overrides for tests and tuning, read when an operator is prepared (the library reads no environment
  * variable).  Names: no_pdl, no_relu_mode, no_relu_hi, no_relu_sat, no_wide_store, no_grouped_tc, no_first_layer, no_implicit, no_gemv, no_narrow_span, no_pack,
- * pack_wide, no_bres, no_bres_k1, no_fan_out, tc_bn (>= 96), tc_pair, tc_raster, epi_g, dw_legacy, dw_rows, no_fuse, fuse_all.
+ * pack_wide, no_bres, no_bres_k1, no_fan_out, tc_bn (>= 96), tc_pair, tc_raster, epi_g, dw_legacy, dw_rows, no_fuse, fuse_all, no_out_stream, no_narrow_n.
  * grid_cap = G: operators prepared afterwards launch at most G CTAs of their persistent kernels (tensor-core GEMM /
  * convolution, row-ring depthwise), i.e. occupy at most G SMs.  Meant for several contexts that share one GPU, each
  * running its own operator list: with G = SMs / 4 their kernels run side by side in four shares instead of taking
