@@ -1713,11 +1713,11 @@ int32_t build_gemm(enn_b200_context *ctx, const ConvGeom &g, const QuantHost &qh
         }
     }
     // CTA pairs (cta_group::2): two SMs share one 256-row tile and every B byte is fetched once per pair.  Used for plain
-    // GEMMs with several waves of 256-wide tiles, long K and operands too large to stay L2 resident ((M+N) K > 48 MB):
-    // 8192^3 runs 7 % faster than on the one-CTA kernel, 4096^3 3 % slower.  Option tc_pair = 0 / 1 overrides the size rule.
+    // GEMMs with several waves of 256-wide tiles, long K and large operands ((M+N) K >= 32 MB): 8192^3 runs 7 % faster
+    // than on the one-CTA kernel, 4096^3 6 % (51.6 against 54.7 us).  Option tc_pair = 0 / 1 overrides the size rule.
     const bool pair_ok = span == kBK && !implicit_span && p.tiles_m >= 2 && (K + kBK - 1) / kBK >= 8 && bn_data >= 128 &&
                          static_cast<int64_t>(p.tiles_m) * tiles_n >= 2ll * ctx->sm_count;
-    bool two = pair_ok && (static_cast<int64_t>(M) + N) * K > (48ll << 20);
+    bool two = pair_ok && (static_cast<int64_t>(M) + N) * K >= (32ll << 20);
     int32_t forced_rows = 0;
     if (ctx->has_opt("tc_pair")) {
         const int ev = ctx->opt("tc_pair");
