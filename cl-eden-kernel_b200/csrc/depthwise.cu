@@ -365,7 +365,8 @@ __device__ __forceinline__ uint32_t dw_lds32(uint32_t addr) {
 }
 
 // ------------------------------------------------------------------------------------------------------
-// 3x3 fast path, row-ring form (C % 16 == 0, at most 224 channel quads): the default for the MobileNetV2-style layers.
+// 3x3 fast path, row-ring form (C % 16 == 0, at most 256 channel quads; above 224 as one CTA of eight consumer warps per
+// SM instead of two of seven): the default for the MobileNetV2-style layers.
 //
 // The register-streamed kernel above keeps about 12 KB of loads in flight per SM, a third of what the HBM latency
 // needs, and spends instructions on per-load predicates and addresses.  Here the input reaches shared memory through
@@ -395,8 +396,10 @@ struct DwRingParams {
     int32_t *err;           // host-mapped error word
 };
 
-constexpr int kDwRingConsumers = 224;                   // consumer threads per CTA at most (7 warps)
+constexpr int kDwRingConsumers = 224;                   // consumer threads per CTA (7 warps): two CTAs per SM
 constexpr int kDwRingThreads = kDwRingConsumers + 32;   // + the producer warp
+constexpr int kDwRingConsumersBig = 256;                // layers with 225-256 channel quads (960 channels): 8 consumer warps, one CTA per SM
+constexpr int kDwRingThreadsBig = kDwRingConsumersBig + 32;
 constexpr uint32_t kDwSpinLimit = 1u << 22;
 
 __device__ __forceinline__ bool dw_mbar_try(uint32_t bar, uint32_t parity) {
@@ -418,8 +421,8 @@ __device__ __forceinline__ bool dw_mbar_wait(uint32_t bar, uint32_t parity, vola
 
 // RQ: 0 two-stage requantisation, 1 merged ReLU form, 2 merged ReLU form whose clamp is the saturation of the byte pack
 // itself (lower clamp 0, upper clamp 255: no min / max and no offset to add back).
-template <int STRIDE, bool W_SIGNED, bool NEED_ASUM, int RQ>
-__global__ void __launch_bounds__(kDwRingThreads, 2)
+template <int STRIDE, bool W_SIGNED, bool NEED_ASUM, int RQ, bool BIG = false>
+__global__ void __launch_bounds__(BIG ? kDwRingThreadsBig : kDwRingThreads, BIG ? 1 : 2)
 dw3x3_ring_kernel(const DwRingParams p, const DwChan *__restrict__ chan, const uint32_t *__restrict__ w_packed,
                   const uint8_t *__restrict__ in, uint8_t *__restrict__ out) {
     extern __shared__ uint8_t dw_ring_raw[];
@@ -686,9 +689,9 @@ bool dw_ring_plan(enn_b200_op *op) {
     enn_b200_context *ctx = op->ctx;
     if (!dw3x3_eligible(g) || (g.cin & 15) != 0 || !op->dw_chan || ctx->cc_major < 9 || ctx->opt("dw_legacy")) return false;
     const int q = g.cin / 4, s = g.sh;
-    if (q > kDwRingConsumers || g.n <= 0) return false;
+    if (q > kDwRingConsumersBig || g.n <= 0) return false;
     const int strips = (g.ow + 3) / 4;
-    int ns_max = kDwRingConsumers / q;
+    int ns_max = (q > kDwRingConsumers ? kDwRingConsumersBig : kDwRingConsumers) / q;
     if (ns_max > strips) ns_max = strips;
     const int tx_n = (strips + ns_max - 1) / ns_max;
     const int ns = (strips + tx_n - 1) / tx_n;
@@ -775,14 +778,20 @@ cudaError_t dw_ring_launch(enn_b200_op *op, const void *in, void *out) {
 #define ENN_DWR_ATTR(ST, WS, AS) \
     cudaFuncSetAttribute(dw3x3_ring_kernel<ST, WS, AS, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024); \
     cudaFuncSetAttribute(dw3x3_ring_kernel<ST, WS, AS, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024); \
-    cudaFuncSetAttribute(dw3x3_ring_kernel<ST, WS, AS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024)
+    cudaFuncSetAttribute(dw3x3_ring_kernel<ST, WS, AS, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024); \
+    cudaFuncSetAttribute(dw3x3_ring_kernel<ST, WS, AS, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024); \
+    cudaFuncSetAttribute(dw3x3_ring_kernel<ST, WS, AS, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024); \
+    cudaFuncSetAttribute(dw3x3_ring_kernel<ST, WS, AS, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024)
     if (!attr_set) {
         ENN_DWR_ATTR(1, true, true); ENN_DWR_ATTR(1, true, false); ENN_DWR_ATTR(1, false, true); ENN_DWR_ATTR(1, false, false);
         ENN_DWR_ATTR(2, true, true); ENN_DWR_ATTR(2, true, false); ENN_DWR_ATTR(2, false, true); ENN_DWR_ATTR(2, false, false);
         attr_set = true;
     }
 #undef ENN_DWR_ATTR
-#define ENN_DWR(ST, WS, AS, RQ) launch_pdl(dw3x3_ring_kernel<ST, WS, AS, RQ>, dim3(pl->grid), dim3(pl->threads), pl->smem, s, pl->prm, c, w, i, o)
+    const bool big = pl->threads > kDwRingThreads;
+#define ENN_DWR(ST, WS, AS, RQ)                                                                                                            \
+    (big ? launch_pdl(dw3x3_ring_kernel<ST, WS, AS, RQ, true>, dim3(pl->grid), dim3(pl->threads), pl->smem, s, pl->prm, c, w, i, o) \
+         : launch_pdl(dw3x3_ring_kernel<ST, WS, AS, RQ>, dim3(pl->grid), dim3(pl->threads), pl->smem, s, pl->prm, c, w, i, o))
 #define ENN_DWR_R(ST, WS, AS) (rq == 0 ? ENN_DWR(ST, WS, AS, 0) : (rq == 1 ? ENN_DWR(ST, WS, AS, 1) : ENN_DWR(ST, WS, AS, 2)))
     if (g.sh == 1) {
         if (g.w_signed) { if (asum) ENN_DWR_R(1, true, true); else ENN_DWR_R(1, true, false); }
