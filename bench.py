@@ -22,6 +22,7 @@ path cannot run on this machine) on a bounded sample of the same workload, with 
 """
 import argparse
 import ctypes as C
+import gc
 import importlib
 import importlib.util
 import json
@@ -94,6 +95,7 @@ class ClockSampler:
         self.gpu = gpu_index
         self.proc = None
         self.lines = []
+        self.first = 0
 
     def start(self):
         try:
@@ -108,6 +110,15 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def wait_first_sample(self, timeout=10.0):
+        t0 = time.perf_counter()
+        while self.proc and not self.lines and time.perf_counter() - t0 < timeout and self.proc.poll() is None:
+            time.sleep(0.01)
+
+    def mark(self):
+        """Samples taken before this call are dropped from the summary (they precede the timed regions)."""
+        self.first = len(self.lines)
+
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -118,7 +129,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
-        for ln in self.lines:
+        for ln in self.lines[self.first:]:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -444,6 +455,12 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
         cu.record(e1, lanes[0].ctx.stream)
         return cu.elapsed_ms(e0, e1)
 
+    # The clock sampler starts here, well ahead of the timed regions, so that the start-up of nvidia-smi does not fall
+    # into them; the samples from `mark()` on are the ones summarised.
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        sampler.wait_first_sample()
     for l in lanes:
         for _ in range(args.warmup):
             l.ol.execute_device()
@@ -466,10 +483,13 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
     # trial and, at N > 1, the first collective of the run, whose set-up otherwise slows the next pass by up to 9 %).
     device_steps(use, 2 * use)
 
+    # No collector pause inside the timed regions: a generation-2 collection of this process takes milliseconds, which is
+    # a third of a 20-step region at 2 GPUs (and whether it falls inside depends on how many objects were made before).
+    gc.collect()
+    gc.disable()
+
     # ---- device-resident: K graph launches between two events ----
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.mark()
     barrier()
     total_ms = device_steps(use, args.steps)
     barrier()
@@ -477,10 +497,13 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
     # ---- end to end: host buffers (pinned) through enn_b200_oplist_submit / _wait, logits gathered on rank 0 ----
     # Every step copies its images host->device and its logits device->host (the copy-in of a step overlaps the
     # operators of the step before); at N > 1 every step's logits also travel to rank 0 (NCCL gather of the device
-    # copy, ordered on the lane's stream, then device->host there).  The region ends when the last result has landed.
-    ext, src_views, gath, gath_host, gath_rows = None, {}, None, None, None
+    # copy after the lane's graph, then device->host there).  The region ends when the last result has landed.
+    ext, src_views, gath, gath_host, gath_rows, gstream, gdone = None, {}, None, None, None, None, {}
     if multi:
         ext = [torch.cuda.ExternalStream(l.ctx.stream.value if hasattr(l.ctx.stream, "value") else int(l.ctx.stream)) for l in lanes[:use]]
+        # The gathers run on a stream of their own per lane: a lane's next graph does not wait for the other ranks, only
+        # the graph that will overwrite the gathered output buffer (two submissions later) does.
+        gstream = [torch.cuda.Stream() for _ in lanes[:use]]
         if rank == 0:
             gath = [torch.empty((world, out_bytes), dtype=torch.uint8, device="cuda") for _ in range(use)]
             gath_host = [torch.empty((world, out_bytes), dtype=torch.uint8).pin_memory() for _ in range(use)]
@@ -500,6 +523,11 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
         while i < steps:
             first = i % use
             ks = [(first + j) % use for j in range(min(round_size, steps - i))]
+            if multi:
+                for k in ks:      # the output buffer this submission writes: its last gather must have read it
+                    ev = gdone.get((k, lanes[k].n & 1))
+                    if ev is not None:
+                        ext[k].wait_event(ev)
             if len(ks) == 1:
                 lanes[ks[0]].submit()
             else:
@@ -513,13 +541,22 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
                     src = src_views.get(ptr)        # a list alternates between two output buffers: wrap each once
                     if src is None:
                         src = src_views[ptr] = torch.as_tensor(DevView(ptr, out_bytes), device="cuda")
-                    with torch.cuda.stream(ext[k]):
+                    ready = torch.cuda.Event()
+                    ready.record(ext[k])
+                    with torch.cuda.stream(gstream[k]):
+                        gstream[k].wait_event(ready)
                         dist.gather(src, gath_rows[k] if rank == 0 else None, dst=0)
                         if rank == 0:
                             gath_host[k].copy_(gath[k], non_blocking=True)
+                        done = torch.cuda.Event()
+                        done.record(gstream[k])
+                    gdone[(k, (lanes[k].n - 1) & 1)] = done
             i += len(ks)
         for l in lanes[:use]:
             l.ol.wait()
+        if multi:
+            for g in gstream:
+                g.synchronize()
 
     e2e_steps(2 * use)
     barrier()
@@ -533,6 +570,7 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
     cu.record(t1, lanes[0].ctx.stream)
     barrier()
     e2e_ms = cu.elapsed_ms(t0, t1)
+    gc.enable()
     clocks = sampler.stop() if rank == 0 else None
     logits = lanes[0].logits(1 if (lanes[0].n & 1) == 0 else 0).reshape(per_rank, classes)   # the buffer of lane 0's latest step
     gathered = gath_host[0].numpy().reshape(GLOBAL_BATCH, classes).copy() if multi and rank == 0 else None
@@ -679,12 +717,13 @@ def run_ours(args):
     if args.workload == DEFAULT_WORKLOAD:
         r = run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist)
         total_ms, e2e_ms = r["total_ms"], r["e2e_ms"]
-        by_rank = None
+        by_rank = e2e_by_rank = None
         if multi:
             t = torch.tensor([total_ms, e2e_ms], device="cuda", dtype=torch.float64)
             every = [torch.zeros_like(t) for _ in range(world)]
             dist.all_gather(every, t)
             by_rank = [round(v[0].item() / args.steps, 4) for v in every]
+            e2e_by_rank = [round(v[1].item() / args.steps, 4) for v in every]
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             total_ms, e2e_ms = t.tolist()
         if rank == 0:
@@ -730,6 +769,7 @@ def run_ours(args):
             }
             if by_rank:
                 result["ms_per_step_by_rank"] = by_rank      # `ms_per_step` is their maximum
+                result["e2e"]["ms_per_step_by_rank"] = e2e_by_rank
             result["lanes_per_gpu"] = r["lanes"]
             result["sm_share_per_lane"] = r["grid_cap"] if r["grid_cap"] > 0 else "all"
             result["e2e"]["lanes"] = r["e2e_lanes"]
