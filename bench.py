@@ -763,7 +763,7 @@ def run_ours(args):
                 "roofline": roof,
                 "e2e": {"value": units / (e2e_ms * 1e-3), "unit": "images/s", "h2d_bytes_per_step": r["h2d"] * world,
                         "d2h_bytes_per_step": r["d2h"] * world},
-                "gpu_launches": int(r["info"]["launches"] * args.steps),
+                "gpu_launches": int(r["info"]["stats"]["kernel_launches"] * args.steps * world),      # the lists' own count (fused adds are one launch)
                 "clocks": r["clocks"],
                 "logits_checksum": int(r["logits"].astype(np.int64).sum()),
             }
