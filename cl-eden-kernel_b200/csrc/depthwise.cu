@@ -711,6 +711,9 @@ bool dw_ring_plan(enn_b200_op *op) {
     int nr = static_cast<int>((budget - 512) / p.pitch);
     if (ctx->opt("dw_rows") > 0 && ctx->opt("dw_rows") < nr) nr = ctx->opt("dw_rows");   // tuning override
     if (nr > 16) nr = 16;
+    // the kernels' dynamic shared memory limit is set to 110 KB (a ring of long rows: stride 2 with over 900 channels)
+    const size_t smem_cap = 108 * 1024;
+    if (static_cast<size_t>(nr) * (p.pitch + 16) + 192 > smem_cap) nr = static_cast<int>((smem_cap - 192) / (p.pitch + 16));
     if (nr < 4) {
         delete pl;
         return false;

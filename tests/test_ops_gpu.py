@@ -209,6 +209,11 @@ DW_CASES = {
     "ring_per_tensor": dict(n=2, h=20, w=21, c=32, per_channel=False, out_scale=0.08, out_zp=3),
     "ring_per_tensor_s2_relu": dict(n=2, h=22, w=19, c=64, stride=2, per_channel=False, out_scale=0.03, out_zp=0),
     "ring_none_act": dict(n=2, h=13, w=17, c=96, act=cases.enn.ACT_NONE, out_zp=131, out_scale=0.1),
+    # 225-256 channel quads: the eight-consumer-warp form of the ring kernel (one CTA per SM)
+    "ring_big_c1024": dict(n=3, h=7, w=9, c=1024, in_zp=7),
+    "ring_big_c912_s2": dict(n=5, h=14, w=14, c=912, stride=2),
+    "ring_big_c960_none": dict(n=9, h=7, w=7, c=960, act=cases.enn.ACT_NONE, out_zp=128, out_scale=0.1),
+    "beyond_ring_c1040": dict(n=2, h=7, w=7, c=1040),
     # output channels past cin * depth_multiplier: no filter, bias only (depthwise_conv_unequal)
     "unequal_pt": dict(n=2, h=9, w=10, c=6, dm=2, per_channel=False, out_scale=0.3, out_zp=90, act=cases.enn.ACT_NONE, extra_out=5),
     "unequal_pc_3x3_c32": dict(n=1, h=12, w=12, c=32, extra_out=16, out_scale=0.8, out_zp=100, act=cases.enn.ACT_NONE),
