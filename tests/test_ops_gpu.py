@@ -76,6 +76,8 @@ CONV_CASES = {
     "pack_1x1_c24_to_144_relu": dict(n=2, h=48, w=50, cin=24, cout=144, k=1, per_channel=True, out_scale=0.002, out_zp=0),
     "pack_1x1_c24_to_40_u8w": dict(n=1, h=64, w=66, cin=24, cout=40, k=1, w_zp=130, out_scale=0.03),
     "pack_1x1_c32_to_16": dict(n=2, h=48, w=50, cin=32, cout=16, k=1, per_channel=True, out_scale=0.3, act=cases.enn.ACT_NONE),
+    "pack_1x1_c24_to_144_odd_rows": dict(n=1, h=65, w=65, cin=24, cout=144, k=1, per_channel=True, out_scale=0.002, out_zp=0),   # 4225 rows: no pixel pairs
+    "pack_1x1_c40_to_64_pairs": dict(n=2, h=48, w=50, cin=40, cout=64, k=1, per_channel=True, out_scale=0.05, act=cases.enn.ACT_NONE),
     # rows of 96 / 144 / 192 bytes (not whole 128-byte lines), few output channels: the shapes of the MobileNetV2 project layers
     "pack_wide_1x1_c96_to_24": dict(n=2, h=48, w=50, cin=96, cout=24, k=1, per_channel=True, out_scale=0.4, act=cases.enn.ACT_NONE),
     "pack_wide_1x1_c144_to_32_u8w": dict(n=1, h=64, w=66, cin=144, cout=32, k=1, w_zp=130, out_scale=0.08, act=cases.enn.ACT_NONE),
@@ -373,6 +375,15 @@ FC_CASES = {
     "group3_rowsum_k128_n64": dict(m=120000, k=128, n=64, per_channel=False, w_zp=119),
     "group4_ragged_k128_n64": dict(m=128 * 4 * 300 + 128 * 2 + 5, k=128, n=64),
     "group2_two_n_tiles_k256_n256_relu": dict(m=40000, k=256, n=256, act=cases.enn.ACT_RELU6, out_zp=0, out_scale=0.01),
+    # one k-block and more than 128 output channels: tiles of at most 128 columns, two M tiles per accumulator buffer;
+    # whole and ragged column counts, a half-empty last N tile, general and ReLU-type epilogues, signed activations,
+    # and u8 weights (row-sum column: the rule does not apply)
+    "narrow_n_k32_n192_relu": dict(m=3000, k=32, n=192, act=cases.enn.ACT_RELU6, out_zp=0, out_scale=0.01),
+    "narrow_n_k64_n200_none": dict(m=1000, k=64, n=200, act=cases.enn.ACT_NONE),
+    "narrow_n_k96_n576_relu": dict(m=2000, k=96, n=576, act=cases.enn.ACT_RELU, out_zp=0, out_scale=0.02),
+    "narrow_n_k128_n130_s8": dict(m=700, k=128, n=130, act_dtype=cases.enn.S8, in_zp=-3, out_zp=-7),
+    "narrow_n_k16_n144_ragged_m": dict(m=4097, k=16, n=144, act=cases.enn.ACT_RELU6, out_zp=0, out_scale=0.01),
+    "narrow_n_k32_n192_u8w": dict(m=1500, k=32, n=192, per_channel=False, w_zp=119),
     "pack_wide_k96_n24": dict(m=4104, k=96, n=24, act=cases.enn.ACT_NONE),
     "pack_wide_k144_n24_per_tensor": dict(m=4100, k=144, n=24, per_channel=False, w_zp=119, act=cases.enn.ACT_NONE),
     "pack_wide_k192_n32": dict(m=4098, k=192, n=32, act=cases.enn.ACT_NONE, out_scale=0.3),
