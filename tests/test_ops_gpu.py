@@ -867,11 +867,16 @@ def test_oplist_with_deconvolution(enn, orc, ctx):
         ol.destroy()
 
 
-def test_oplist_pipelined_submit(enn, ctx):
-    """enn_b200_oplist_submit / wait (copy-in overlapped with the previous graph) gives the blocking call's results."""
+@pytest.mark.parametrize("out_stream", [True, False])
+def test_oplist_pipelined_submit(enn, out_stream):
+    """enn_b200_oplist_submit / wait (copy-in overlapped with the previous graph, results on their own stream or, with
+    option no_out_stream, on the operators' stream) gives the blocking call's results."""
     import importlib
     mn = importlib.import_module("cl_eden_kernel_b200.mobilenet")
     layers, _ = mn.build_model(seed=4, calib_images=1, resolution=64, num_classes=50)
+    ctx = enn.Context(0)
+    if not out_stream:
+        ctx.set_option("no_out_stream", 1)
     ol, info = mn.make_oplist(enn, ctx, layers, batch=2, resolution=64)
     try:
         rng = np.random.default_rng(11)
@@ -886,6 +891,7 @@ def test_oplist_pipelined_submit(enn, ctx):
         assert len({w.tobytes() for w in want}) == len(want)      # the five inputs really gave five different results
     finally:
         ol.destroy()
+        ctx.close()
 
 
 def test_oplist_submit_round_and_sm_share(enn, orc):
