@@ -511,12 +511,16 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
 
     # Lanes that share the GPU by SM shares are submitted in rounds (enn_b200_oplist_submit_round): the lanes of a round
     # fill the GPU together and start together, the next round's inputs travel meanwhile.
-    # The end-to-end leg runs on the lanes of one round only: more lanes put two rounds in flight at once, which gains
-    # 1 % on long runs and loses 10 % on a 20-step run that starts from an empty pipeline.
+    # The end-to-end leg of a short run uses the lanes of one round only: all lanes (two rounds in flight at once) gain
+    # 3 % on long runs (160 steps: 199 k against 194 k images/s) and lose 5 % on a 20-step run, which starts from an empty
+    # pipeline (168 k against 177 k).
     round_size = max(1, min(use, sm_count // grid_cap)) if grid_cap > 0 else 1
     use_dev = use
     if grid_cap > 0:
-        use = round_size
+        if args.e2e_lanes > 0:
+            use = max(round_size, min(use, args.e2e_lanes))
+        elif args.steps < 16 * round_size:
+            use = round_size
 
     def e2e_steps(steps):
         i = 0
@@ -948,6 +952,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--lanes", type=int, default=0, help="operator lists per GPU that take the steps in turn (0: time 4 and 8 and keep the best)")
+    ap.add_argument("--e2e-lanes", type=int, default=0, help="lanes of the end-to-end leg (0: the lanes of one round for runs under 64 steps, else all)")
     ap.add_argument("--grid-cap", type=int, default=-1, help="SMs a lane's persistent kernels may occupy (-1: a quarter of the GPU with four or more lanes; 0: all)")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE", help="library option for every context (tuning runs), e.g. no_fuse=1")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU leg (profiling runs)")
