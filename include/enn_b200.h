@@ -207,7 +207,7 @@ void *enn_b200_stream(enn_b200_context *ctx);
  * grid_cap = G: operators prepared afterwards launch at most G CTAs of their persistent kernels (tensor-core GEMM /
  * convolution, row-ring depthwise), i.e. occupy at most G SMs.  Meant for several contexts that share one GPU, each
  * running its own operator list: with G = SMs / 4 their kernels run side by side in four shares instead of taking
- * the whole GPU in turn, which hides the latency of the small layers (MobileNetV2-u8, 256 images: 1.27 ms per step
+ * the whole GPU in turn, which hides the latency of the small layers (MobileNetV2-u8, 256 images: 1.25 ms per step
  * with eight lists of 37 SMs against 1.43 ms with three uncapped lists; 32 images: 0.22 against 0.34 ms).
  * Stands where the reference reads its build-time device switches (CLRuntime.cpp:174-213).  Unknown names are
  * rejected with INVALID_PARAMS; none of them changes a result. */
