@@ -428,9 +428,10 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
     multi = world > 1
 
     # ---- lanes: how many operator lists share this GPU, and the share of its SMs each list's kernels may take.
-    # Default: eight lists whose persistent kernels launch at most a quarter of the SMs (option grid_cap), so that four
-    # kernels of different steps run side by side; "auto" times four and eight lists on a few steps and keeps the best.
-    max_lanes = args.lanes if args.lanes > 0 else 8
+    # Default: up to twelve lists whose persistent kernels launch at most a quarter of the SMs (option grid_cap), so that
+    # four kernels of different steps run side by side; "auto" times 4, 8, 10 and 12 lists on the step count that will
+    # be timed and keeps the best.
+    max_lanes = args.lanes if args.lanes > 0 else 12
     sm_count = torch.cuda.get_device_properties(local).multi_processor_count
     grid_cap = args.grid_cap if args.grid_cap >= 0 else (sm_count // 4 if max_lanes >= 4 else 0)
     user_options = [(kv.split("=")[0], int(kv.split("=")[1])) for kv in args.opt]
@@ -470,7 +471,7 @@ def run_mobilenet(args, enn, cu, cases, rank, world, local, barrier, torch, dist
         lane_trials = None
     else:
         lane_trials = {}
-        for s in (max_lanes // 2, max_lanes):      # on the step count that will be timed: K need not divide by the lanes
+        for s in (4, 8, 10, 12):      # on the step count that will be timed: a K that divides by the lanes leaves no partial round
             device_steps(s, 2 * s)
             lane_trials[s] = device_steps(s, args.steps) / args.steps
         if multi:      # every rank must make the same choice: take rank 0's
@@ -951,7 +952,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
-    ap.add_argument("--lanes", type=int, default=0, help="operator lists per GPU that take the steps in turn (0: time 4 and 8 and keep the best)")
+    ap.add_argument("--lanes", type=int, default=0, help="operator lists per GPU that take the steps in turn (0: time 4, 8, 10 and 12 and keep the best)")
     ap.add_argument("--e2e-lanes", type=int, default=0, help="lanes of the end-to-end leg (0: the lanes of one round for runs under 64 steps, else all)")
     ap.add_argument("--grid-cap", type=int, default=-1, help="SMs a lane's persistent kernels may occupy (-1: a quarter of the GPU with four or more lanes; 0: all)")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE", help="library option for every context (tuning runs), e.g. no_fuse=1")
